@@ -1,0 +1,17 @@
+// Entry point of the `kvtransfer_ops` extension module.  The module keeps the symbol names
+// of the reference binding (kvtransfer/kvtransfer_pybind.cpp:415-522) for the engine API and
+// adds the kernel-level `kvt_*` functions.
+#include <pybind11/pybind11.h>
+
+namespace py = pybind11;
+
+namespace kvx {
+void bind_kernels(py::module_& m);
+void bind_engine(py::module_& m);
+}  // namespace kvx
+
+PYBIND11_MODULE(kvtransfer_ops, m) {
+  m.doc() = "B200-native KV transfer engine: C++ runtime and sm_100a kernels";
+  kvx::bind_kernels(m);
+  kvx::bind_engine(m);
+}

@@ -1,0 +1,175 @@
+// C ABI of the sm_100a transfer kernels.
+//
+// Every launcher here is a plain `extern "C"` function so that the pybind module, the C++
+// engine and ctypes callers all share one entry point.  Pointers are raw device (or
+// peer-mapped / host-mapped) addresses; nothing in this header depends on torch.
+//
+// The kernels replace, in one pass, what the reference does in three places: the CPU
+// ParseBlock offset generators (kvtransfer/src/parse_block_*.cpp), the gather/scatter copy
+// kernels (kvtransfer/src/copy_kernels.cu:105-281) and the wire transfer in between
+// (kvtransfer/src/tcp_channel.cpp:477-588).
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// Byte-stride description of one paged attention cache tensor (one layer, one rank).
+// All cache shapes of the reference (kvtransfer/include/envcfg.h:25-52) reduce to this:
+//   addr(block b, kv, slot t, head h) = base + b*block_stride + kv*kv_stride
+//                                     + t*token_stride + h*head_stride
+// For block-scaled fp8 pages the scale bytes (UE8M0, one per 32 values) sit in the same
+// block at scale_base with their own strides.
+typedef struct KvtLayout {
+  int64_t block_stride;
+  int64_t kv_stride;
+  int64_t token_stride;
+  int64_t head_stride;
+  int64_t scale_base;          // byte offset of the scale region inside a block (fp8 pages)
+  int64_t scale_kv_stride;
+  int64_t scale_token_stride;
+  int64_t scale_head_stride;
+  uint32_t ntpb;               // token slots per block
+  uint32_t num_heads;          // heads held by this rank
+  uint32_t head_bytes;         // payload bytes of one (token, head) row
+  uint32_t num_blocks;         // blocks in the tensor (bounds check)
+  uint32_t kv_count;           // 2 for K+V caches, 1 for MLA latent / indexer caches
+  uint32_t reserved;
+} KvtLayout;
+
+// One request (or one chunk of it) scheduled in this step.  Block ids live in a shared
+// uint32 pool so a 64k-token request needs no per-block host descriptor.
+typedef struct KvtReqDesc {
+  uint32_t src_blk_off;        // index of this request's first src block id in the pool
+  uint32_t dst_blk_off;        // index of this request's first dst block id in the pool
+  uint32_t n_src_blocks;
+  uint32_t n_dst_blocks;
+  uint32_t seen_tokens;        // tokens already transferred by earlier chunks
+  uint32_t new_tokens;         // tokens [seen, seen+new) move in this launch
+  uint32_t flags;              // KVT_REQ_*
+  uint32_t first_tile;         // exclusive prefix sum of tile counts (filled by the host)
+} KvtReqDesc;
+
+#define KVT_REQ_PAD_TAIL 1u    // zero dst slots [seen+new, end of last dst block)
+
+enum KvtMode {
+  KVT_MODE_COPY = 0,           // byte copy
+  KVT_MODE_BF16_TO_MXFP8 = 1,  // bf16 -> e4m3 with one UE8M0 scale per 32 values
+  KVT_MODE_MXFP8_TO_BF16 = 2,  // inverse
+};
+
+enum KvtStatus {
+  KVT_OK = 0,
+  KVT_ERR_BLOCK_RANGE = 1,     // a block id or block index was outside its table / tensor
+  KVT_ERR_TMA_TIMEOUT = 2,     // a bounded mbarrier wait ran out
+  KVT_ERR_BAD_ARGS = 3,
+  KVT_ERR_FLAG_TIMEOUT = 4,    // a bounded wait on a completion flag ran out
+};
+
+typedef struct KvtAttnLaunch {
+  const uint64_t* src_layers;  // device array, one base address per layer (local memory)
+  const uint64_t* dst_layers;  // device array, one base address per layer (local / peer / host-mapped)
+  const void* src_maps;        // device array of CUtensorMap per layer, or NULL (SIMT only)
+  const void* dst_maps;
+  KvtLayout src;
+  KvtLayout dst;
+  uint32_t layer_begin;
+  uint32_t layer_end;
+  const KvtReqDesc* reqs;      // device memory
+  uint32_t n_reqs;
+  uint32_t total_tiles;        // sum over requests of their tile count
+  const uint32_t* block_ids;   // device memory pool
+  uint32_t tile_tokens;        // tokens per tile; divides src.ntpb and dst.ntpb
+  uint32_t src_head0;          // first source head moved
+  uint32_t dst_head0;          // where it lands on the destination rank
+  uint32_t n_heads;            // heads moved
+  uint32_t mode;               // KvtMode
+  uint32_t* status;            // device: [0] first error code, [1] detail
+  uint32_t* done_counter;      // device, zero before launch; may be NULL with flag == NULL
+  uint64_t* flag;              // completion word (device / peer / host-mapped) or NULL
+  uint64_t flag_value;         // value stored to *flag by the last CTA after a system fence
+} KvtAttnLaunch;
+
+// Tile count of one request for a given tile size (host helper, also used by tests).
+uint32_t kvt_req_tiles(uint32_t seen, uint32_t new_tokens, uint32_t tile_tokens, uint32_t flags,
+                       uint32_t dst_ntpb);
+
+// Launch the fused transfer kernel.  grid_ctas <= 0 picks one CTA per SM.  use_tma != 0 moves
+// full tiles with cp.async.bulk.tensor (needs src_maps/dst_maps and KVT_MODE_COPY).
+// Returns a cudaError_t value.
+int kvt_launch_p2d_attn(const KvtAttnLaunch* args, int grid_ctas, int threads, int use_tma,
+                        void* stream);
+
+// Encode one 5-D tensor map {head_bytes/4, heads, slots, blocks, kv} over a cache tensor with
+// box {head_bytes/4, box_heads, box_tokens, 1, 1}.  `out` receives 128 bytes.  Returns 0 on
+// success, a CUresult or -1 otherwise.  No multicast is ever used with these maps.
+int kvt_encode_tensor_map(void* out, uint64_t base, const KvtLayout* layout, uint32_t box_heads,
+                          uint32_t box_tokens);
+
+// ---- block-relative strided segments (GDN / KDA / PLE recurrent state) -------------------
+// One segment rule: for i in [0,count): copy len bytes from
+//   src_block_base + src_off + i*src_stride  to  dst_block_base + dst_off + i*dst_stride.
+typedef struct KvtSegRule {
+  int64_t src_off;
+  int64_t dst_off;
+  int64_t src_stride;
+  int64_t dst_stride;
+  uint32_t len;
+  uint32_t count;
+} KvtSegRule;
+
+typedef struct KvtStateLaunch {
+  const uint64_t* src_layers;
+  const uint64_t* dst_layers;
+  uint32_t layer_begin, layer_end;
+  int64_t src_block_stride;
+  int64_t dst_block_stride;
+  uint32_t src_num_blocks, dst_num_blocks;
+  const uint32_t* src_blocks;  // device: one src block id per state page to move
+  const uint32_t* dst_blocks;  // device: matching dst block ids
+  uint32_t n_pages;
+  const KvtSegRule* rules;     // device
+  uint32_t n_rules;
+  uint32_t* status;
+  uint32_t* done_counter;
+  uint64_t* flag;
+  uint64_t flag_value;
+} KvtStateLaunch;
+
+int kvt_launch_p2d_state(const KvtStateLaunch* args, int grid_ctas, int threads, void* stream);
+
+// ---- IpcBlock list copy (descriptor-driven; TCP/shm staging and the generic fallback) -----
+// Copies n triples {src_off, dst_off, len} (the 24-byte IpcBlock of the wire format,
+// kvtransfer/include/channel.h:15-21) between two bases.
+int kvt_launch_copy_blocks(uint64_t src_base, uint64_t dst_base, const uint64_t* triples,
+                           uint32_t n, uint64_t src_capacity, uint64_t dst_capacity,
+                           uint32_t* status, int grid_ctas, void* stream);
+
+// ---- completion flags ---------------------------------------------------------------------
+// Bounded device-side wait: returns through status[0]=KVT_ERR_FLAG_TIMEOUT when *flag has not
+// reached `value` within timeout_ns.  Never spins without limit.
+int kvt_launch_wait_flag(const uint64_t* flag, uint64_t value, uint64_t timeout_ns,
+                         uint32_t* status, void* stream);
+int kvt_launch_set_flag(uint64_t* flag, uint64_t value, void* stream);
+
+// ---- peer memory / topology ---------------------------------------------------------------
+int kvt_device_count(void);
+int kvt_can_access_peer(int dev, int peer);
+int kvt_enable_peer_access(int dev, int peer);              // idempotent
+int kvt_p2p_attribute(int dev, int peer, int which);        // 0 perf rank, 1 access, 2 native atomics
+int kvt_ipc_get_handle(uint64_t ptr, void* handle64, uint64_t* base, uint64_t* size);
+int kvt_ipc_open_handle(const void* handle64, uint64_t* out_ptr);
+int kvt_ipc_close(uint64_t ptr);
+int kvt_malloc(uint64_t bytes, uint64_t* out_ptr);
+int kvt_free(uint64_t ptr);
+int kvt_host_alloc_mapped(uint64_t bytes, uint64_t* host_ptr, uint64_t* dev_ptr);
+int kvt_host_free(uint64_t host_ptr);
+int kvt_host_register(uint64_t host_ptr, uint64_t bytes, uint64_t* dev_ptr);
+int kvt_host_unregister(uint64_t host_ptr);
+int kvt_sm_count(int dev);
+const char* kvt_error_string(int err);
+
+#ifdef __cplusplus
+}
+#endif

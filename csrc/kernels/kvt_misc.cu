@@ -1,0 +1,325 @@
+// Smaller sm_100a kernels and the CUDA runtime helpers behind the C ABI:
+//   * kvt_p2d_state   - block-relative strided segments; moves GDN / KDA / PLE recurrent state
+//                       pages with the conv-row interleave of TP-mismatched ranks
+//                       (offset rule of kvtransfer/src/parse_block_qwen3_next.cpp:440-502).
+//   * kvt_copy_blocks - descriptor-driven copy of {src_off, dst_off, len} triples, the device
+//                       end of the TCP / shared-memory staging path (what the reference's
+//                       copy_d2h/h2d_direct kernels do, kvtransfer/src/copy_kernels.cu:105-281).
+//   * bounded flag wait / flag set for completion signalling.
+//   * peer-memory, IPC and mapped-host-memory helpers.
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include "kvt_kernels.h"
+
+namespace {
+
+__device__ __forceinline__ void set_status(uint32_t* status, uint32_t code, uint32_t detail) {
+  if (status != nullptr) {
+    if (atomicCAS(status, 0u, code) == 0u) status[1] = detail;
+  }
+}
+
+// Copy `len` bytes with the widest vector both addresses allow.  Called by a whole CTA
+// (stride = blockDim.x) or a warp (stride = 32).
+__device__ __forceinline__ void copy_span(const char* __restrict__ s, char* __restrict__ d, uint32_t len,
+                                          uint32_t lane, uint32_t stride) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(d);
+  if ((a & 15u) == 0) {
+    const uint32_t n16 = len >> 4;
+    const int4* s4 = reinterpret_cast<const int4*>(s);
+    int4* d4 = reinterpret_cast<int4*>(d);
+    uint32_t i = lane;
+    for (; i + 3 * stride < n16; i += 4 * stride) {
+      const int4 v0 = s4[i], v1 = s4[i + stride], v2 = s4[i + 2 * stride], v3 = s4[i + 3 * stride];
+      d4[i] = v0;
+      d4[i + stride] = v1;
+      d4[i + 2 * stride] = v2;
+      d4[i + 3 * stride] = v3;
+    }
+    for (; i < n16; i += stride) d4[i] = s4[i];
+    for (uint32_t b = (n16 << 4) + lane; b < len; b += stride) d[b] = s[b];
+  } else if ((a & 3u) == 0) {
+    const uint32_t n4 = len >> 2;
+    const int* s1 = reinterpret_cast<const int*>(s);
+    int* d1 = reinterpret_cast<int*>(d);
+    for (uint32_t i = lane; i < n4; i += stride) d1[i] = s1[i];
+    for (uint32_t b = (n4 << 2) + lane; b < len; b += stride) d[b] = s[b];
+  } else {
+    for (uint32_t b = lane; b < len; b += stride) d[b] = s[b];
+  }
+}
+
+__global__ void __launch_bounds__(512) kvt_p2d_state_kernel(const __grid_constant__ KvtStateLaunch p) {
+  const uint32_t n_layers = p.layer_end - p.layer_begin;
+  // Work item = (layer, page, rule, repetition); a warp takes one item when segments are
+  // short, a CTA takes one when they are long.
+  const uint32_t warps_per_cta = blockDim.x >> 5;
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  for (uint32_t layer = 0; layer < n_layers; ++layer) {
+    const char* src = reinterpret_cast<const char*>(p.src_layers[p.layer_begin + layer]);
+    char* dst = reinterpret_cast<char*>(p.dst_layers[p.layer_begin + layer]);
+    for (uint32_t r = 0; r < p.n_rules; ++r) {
+      const KvtSegRule rule = p.rules[r];
+      const uint64_t items = (uint64_t)p.n_pages * rule.count;
+      if (rule.len >= 16384) {
+        for (uint64_t it = blockIdx.x; it < items; it += gridDim.x) {
+          const uint32_t page = (uint32_t)(it / rule.count);
+          const uint32_t rep = (uint32_t)(it - (uint64_t)page * rule.count);
+          const uint32_t sb = p.src_blocks[page], db = p.dst_blocks[page];
+          if (sb >= p.src_num_blocks || db >= p.dst_num_blocks) {
+            if (threadIdx.x == 0) set_status(p.status, KVT_ERR_BLOCK_RANGE, page);
+            continue;
+          }
+          copy_span(src + (int64_t)sb * p.src_block_stride + rule.src_off + (int64_t)rep * rule.src_stride,
+                    dst + (int64_t)db * p.dst_block_stride + rule.dst_off + (int64_t)rep * rule.dst_stride,
+                    rule.len, threadIdx.x, blockDim.x);
+        }
+      } else {
+        for (uint64_t it = (uint64_t)blockIdx.x * warps_per_cta + warp; it < items;
+             it += (uint64_t)gridDim.x * warps_per_cta) {
+          const uint32_t page = (uint32_t)(it / rule.count);
+          const uint32_t rep = (uint32_t)(it - (uint64_t)page * rule.count);
+          const uint32_t sb = p.src_blocks[page], db = p.dst_blocks[page];
+          if (sb >= p.src_num_blocks || db >= p.dst_num_blocks) {
+            if (lane == 0) set_status(p.status, KVT_ERR_BLOCK_RANGE, page);
+            continue;
+          }
+          copy_span(src + (int64_t)sb * p.src_block_stride + rule.src_off + (int64_t)rep * rule.src_stride,
+                    dst + (int64_t)db * p.dst_block_stride + rule.dst_off + (int64_t)rep * rule.dst_stride,
+                    rule.len, lane, 32);
+        }
+      }
+    }
+  }
+  if (p.flag != nullptr && p.done_counter != nullptr) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const uint32_t prev = atomicAdd(p.done_counter, 1u);
+      if (prev == gridDim.x - 1) {
+        *p.done_counter = 0;
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p.flag), "l"(p.flag_value) : "memory");
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(512) kvt_copy_blocks_kernel(const char* __restrict__ src, char* __restrict__ dst,
+                                                               const uint64_t* __restrict__ triples, uint32_t n,
+                                                               uint64_t src_cap, uint64_t dst_cap,
+                                                               uint32_t* status) {
+  const uint32_t warps_per_cta = blockDim.x >> 5;
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  // Few descriptors: one CTA per descriptor; many: one warp per descriptor.
+  const bool cta_mode = n <= gridDim.x * 2u;
+  if (cta_mode) {
+    for (uint32_t i = blockIdx.x; i < n; i += gridDim.x) {
+      const uint64_t so = triples[3 * i], dof = triples[3 * i + 1], len = triples[3 * i + 2];
+      if (so > src_cap || len > src_cap - so || dof > dst_cap || len > dst_cap - dof || len > 0xffffffffull) {
+        if (threadIdx.x == 0) set_status(status, KVT_ERR_BLOCK_RANGE, i);
+        continue;
+      }
+      copy_span(src + so, dst + dof, (uint32_t)len, threadIdx.x, blockDim.x);
+    }
+  } else {
+    for (uint32_t i = blockIdx.x * warps_per_cta + warp; i < n; i += gridDim.x * warps_per_cta) {
+      const uint64_t so = triples[3 * i], dof = triples[3 * i + 1], len = triples[3 * i + 2];
+      if (so > src_cap || len > src_cap - so || dof > dst_cap || len > dst_cap - dof || len > 0xffffffffull) {
+        if (lane == 0) set_status(status, KVT_ERR_BLOCK_RANGE, i);
+        continue;
+      }
+      copy_span(src + so, dst + dof, (uint32_t)len, lane, 32);
+    }
+  }
+}
+
+__global__ void kvt_wait_flag_kernel(const uint64_t* flag, uint64_t value, uint64_t timeout_ns, uint32_t* status) {
+  uint64_t t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (;;) {
+    uint64_t v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(flag) : "memory");
+    if (v >= value) return;
+    uint64_t now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    if (now - t0 > timeout_ns) {
+      set_status(status, KVT_ERR_FLAG_TIMEOUT, (uint32_t)v);
+      return;
+    }
+    __nanosleep(200);
+  }
+}
+
+__global__ void kvt_set_flag_kernel(uint64_t* flag, uint64_t value) {
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(flag), "l"(value) : "memory");
+}
+
+int pick_grid(int grid_ctas) {
+  if (grid_ctas > 0) return grid_ctas;
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms > 0 ? sms : 1;
+}
+
+}  // namespace
+
+extern "C" int kvt_launch_p2d_state(const KvtStateLaunch* args, int grid_ctas, int threads, void* stream) {
+  if (args->n_pages == 0 || args->n_rules == 0 || args->layer_end <= args->layer_begin) return (int)cudaSuccess;
+  if (threads <= 0) threads = 512;
+  threads = (threads + 31) / 32 * 32;
+  if (threads > 512) threads = 512;
+  kvt_p2d_state_kernel<<<pick_grid(grid_ctas), threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*args);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int kvt_launch_copy_blocks(uint64_t src_base, uint64_t dst_base, const uint64_t* triples, uint32_t n,
+                                      uint64_t src_capacity, uint64_t dst_capacity, uint32_t* status,
+                                      int grid_ctas, void* stream) {
+  if (n == 0) return (int)cudaSuccess;
+  kvt_copy_blocks_kernel<<<pick_grid(grid_ctas), 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const char*>(src_base), reinterpret_cast<char*>(dst_base), triples, n, src_capacity,
+      dst_capacity, status);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int kvt_launch_wait_flag(const uint64_t* flag, uint64_t value, uint64_t timeout_ns, uint32_t* status,
+                                    void* stream) {
+  kvt_wait_flag_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(flag, value, timeout_ns, status);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int kvt_launch_set_flag(uint64_t* flag, uint64_t value, void* stream) {
+  kvt_set_flag_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(flag, value);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int kvt_device_count(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+extern "C" int kvt_can_access_peer(int dev, int peer) {
+  int ok = 0;
+  if (cudaDeviceCanAccessPeer(&ok, dev, peer) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return ok;
+}
+
+extern "C" int kvt_enable_peer_access(int dev, int peer) {
+  int cur = 0;
+  cudaGetDevice(&cur);
+  cudaError_t e = cudaSetDevice(dev);
+  if (e == cudaSuccess) {
+    e = cudaDeviceEnablePeerAccess(peer, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+      cudaGetLastError();
+      e = cudaSuccess;
+    }
+  }
+  cudaSetDevice(cur);
+  return (int)e;
+}
+
+extern "C" int kvt_p2p_attribute(int dev, int peer, int which) {
+  cudaDeviceP2PAttr attr = cudaDevP2PAttrPerformanceRank;
+  if (which == 1) attr = cudaDevP2PAttrAccessSupported;
+  if (which == 2) attr = cudaDevP2PAttrNativeAtomicSupported;
+  int v = 0;
+  if (cudaDeviceGetP2PAttribute(&v, attr, dev, peer) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return v;
+}
+
+extern "C" int kvt_ipc_get_handle(uint64_t ptr, void* handle64, uint64_t* base, uint64_t* size) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes on the wire");
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(ptr));
+  if (e != cudaSuccess) return (int)e;
+  memcpy(handle64, &h, 64);
+  // The handle names the whole allocation; report its range so the peer can rebase ptr.
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  *base = ptr;
+  *size = 0;
+  if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &q) == cudaSuccess && fn != nullptr) {
+    typedef int (*range_fn)(unsigned long long*, size_t*, unsigned long long);
+    unsigned long long b = 0;
+    size_t s = 0;
+    if (reinterpret_cast<range_fn>(fn)(&b, &s, ptr) == 0) {
+      *base = b;
+      *size = s;
+    }
+  }
+  return 0;
+}
+
+extern "C" int kvt_ipc_open_handle(const void* handle64, uint64_t* out_ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  *out_ptr = reinterpret_cast<uint64_t>(p);
+  return (int)e;
+}
+
+extern "C" int kvt_ipc_close(uint64_t ptr) { return (int)cudaIpcCloseMemHandle(reinterpret_cast<void*>(ptr)); }
+
+extern "C" int kvt_malloc(uint64_t bytes, uint64_t* out_ptr) {
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  *out_ptr = reinterpret_cast<uint64_t>(p);
+  return (int)e;
+}
+
+extern "C" int kvt_free(uint64_t ptr) { return (int)cudaFree(reinterpret_cast<void*>(ptr)); }
+
+extern "C" int kvt_host_alloc_mapped(uint64_t bytes, uint64_t* host_ptr, uint64_t* dev_ptr) {
+  void* h = nullptr;
+  cudaError_t e = cudaHostAlloc(&h, bytes, cudaHostAllocMapped | cudaHostAllocPortable);
+  if (e != cudaSuccess) return (int)e;
+  void* d = nullptr;
+  e = cudaHostGetDevicePointer(&d, h, 0);
+  *host_ptr = reinterpret_cast<uint64_t>(h);
+  *dev_ptr = reinterpret_cast<uint64_t>(d);
+  return (int)e;
+}
+
+extern "C" int kvt_host_free(uint64_t host_ptr) { return (int)cudaFreeHost(reinterpret_cast<void*>(host_ptr)); }
+
+extern "C" int kvt_host_register(uint64_t host_ptr, uint64_t bytes, uint64_t* dev_ptr) {
+  cudaError_t e = cudaHostRegister(reinterpret_cast<void*>(host_ptr), bytes,
+                                   cudaHostRegisterMapped | cudaHostRegisterPortable);
+  if (e != cudaSuccess) return (int)e;
+  void* d = nullptr;
+  e = cudaHostGetDevicePointer(&d, reinterpret_cast<void*>(host_ptr), 0);
+  *dev_ptr = reinterpret_cast<uint64_t>(d);
+  return (int)e;
+}
+
+extern "C" int kvt_host_unregister(uint64_t host_ptr) {
+  return (int)cudaHostUnregister(reinterpret_cast<void*>(host_ptr));
+}
+
+extern "C" int kvt_sm_count(int dev) {
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return sms;
+}
+
+extern "C" const char* kvt_error_string(int err) { return cudaGetErrorString(static_cast<cudaError_t>(err)); }

@@ -1,0 +1,635 @@
+// kvt_p2d_attn: the fused P->D paged-KV transfer kernel for sm_100a.
+//
+// One launch walks the block tables of every request scheduled in a step (the job of the
+// reference's CPU ParseBlock generators, kvtransfer/src/parse_block_flash.cpp:10-130,
+// parse_block_flashinfer.cpp:15-72, parse_block_ragged.cpp:29-217), converts between cache
+// layouts (FlashAttention NHD, FlashInfer HND, ragged, MLA single-tensor), re-shards heads for
+// TP-mismatched prefill/decode ranks (group_off placement of parse_block_common.cpp:81-129),
+// optionally quantises bf16 -> block-scaled e4m3 (the reference only has an unscaled cast,
+// kvtransfer/src/copy_kernels.cu:287-481) and stores straight into the destination cache,
+// which may be local memory, a peer GPU's memory mapped over NVLink, or mapped pinned host
+// memory.  No staging buffer and no library copy is involved.
+//
+// Work unit ("tile"): tile_tokens consecutive token slots of one request for one of K / V in
+// one layer, all transferred heads.  Full tiles move with TMA: one elected thread issues a
+// cp.async.bulk.tensor load of the {head_bytes, heads, tokens} box into shared memory and a
+// cp.async.bulk.tensor store of the same box through a destination map whose strides encode
+// the destination layout, so the NHD<->HND permutation is done by the copy engine and the SM
+// issues two instructions per 8-32 KiB.  Ragged edges (a chunk that starts or ends inside a
+// block), the fp8 paths and layouts TMA cannot describe run on a 16-byte-vector SIMT path in
+// the same launch.  TMA loads never use cluster multicast.
+//
+// Every wait is bounded; on a bad block id or a timeout the kernel records a status word and
+// skips the access instead of faulting.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "kvt_kernels.h"
+
+namespace {
+
+constexpr int kMaxStages = 8;
+constexpr uint32_t kSmemBudget = 200 * 1024;     // bytes of dynamic shared memory we ask for at most
+constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz: bound of an mbarrier wait
+
+struct TileInfo {
+  uint32_t req;        // request index
+  uint32_t tok_lo;     // first absolute token slot of the tile
+  uint32_t copy_lo;    // [copy_lo, copy_hi) are copied
+  uint32_t copy_hi;
+  uint32_t zero_hi;    // [copy_hi', zero_hi) are zero-filled on the destination (tail pad)
+  uint32_t sblk, dblk; // physical block ids
+  uint32_t s_slot0, d_slot0;
+  bool ok;
+};
+
+__device__ __forceinline__ void set_status(uint32_t* status, uint32_t code, uint32_t detail) {
+  if (status != nullptr) {
+    if (atomicCAS(status, 0u, code) == 0u) status[1] = detail;
+  }
+}
+
+// Largest r with reqs[r].first_tile <= t.
+__device__ __forceinline__ uint32_t find_req(const KvtReqDesc* __restrict__ reqs, uint32_t n, uint32_t t) {
+  uint32_t lo = 0, hi = n;
+  while (hi - lo > 1) {
+    uint32_t mid = (lo + hi) >> 1;
+    if (__ldg(&reqs[mid].first_tile) <= t) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+__device__ __forceinline__ TileInfo decode_tile(const KvtAttnLaunch& p, uint32_t tile) {
+  TileInfo ti;
+  const uint32_t r = find_req(p.reqs, p.n_reqs, tile);
+  const KvtReqDesc rd = p.reqs[r];
+  const uint32_t tt = p.tile_tokens;
+  const uint32_t local = tile - rd.first_tile;
+  const uint32_t tok_lo = (rd.seen_tokens / tt + local) * tt;
+  const uint32_t tok_hi = tok_lo + tt;
+  const uint32_t end_tok = rd.seen_tokens + rd.new_tokens;
+  uint32_t end_pad = end_tok;
+  if (rd.flags & KVT_REQ_PAD_TAIL) {
+    end_pad = (end_tok + p.dst.ntpb - 1) / p.dst.ntpb * p.dst.ntpb;
+  }
+  ti.req = r;
+  ti.tok_lo = tok_lo;
+  ti.copy_lo = max(rd.seen_tokens, tok_lo);
+  ti.copy_hi = max(ti.copy_lo, min(end_tok, tok_hi));
+  ti.zero_hi = max(ti.copy_hi, min(end_pad, tok_hi));
+  const uint32_t sbi = tok_lo / p.src.ntpb;
+  const uint32_t dbi = tok_lo / p.dst.ntpb;
+  ti.s_slot0 = tok_lo - sbi * p.src.ntpb;
+  ti.d_slot0 = tok_lo - dbi * p.dst.ntpb;
+  ti.ok = true;
+  ti.sblk = 0;
+  ti.dblk = 0;
+  const bool need_src = ti.copy_hi > ti.copy_lo;
+  if (need_src) {
+    if (sbi >= rd.n_src_blocks) {
+      ti.ok = false;
+    } else {
+      ti.sblk = __ldg(&p.block_ids[rd.src_blk_off + sbi]);
+      if (ti.sblk >= p.src.num_blocks) ti.ok = false;
+    }
+  }
+  if (dbi >= rd.n_dst_blocks) {
+    ti.ok = false;
+  } else {
+    ti.dblk = __ldg(&p.block_ids[rd.dst_blk_off + dbi]);
+    if (ti.dblk >= p.dst.num_blocks) ti.ok = false;
+  }
+  return ti;
+}
+
+__device__ __forceinline__ bool tile_is_full(const KvtAttnLaunch& p, const TileInfo& ti) {
+  return ti.copy_lo == ti.tok_lo && ti.copy_hi == ti.tok_lo + p.tile_tokens;
+}
+
+// ---- PTX wrappers -----------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* ptr) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(ptr));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.b32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ void tma_load_5d(uint32_t smem_dst, const void* map, uint32_t bar, int c0, int c1,
+                                            int c2, int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+      ::"r"(smem_dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_5d(const void* map, uint32_t smem_src, int c0, int c1, int c2, int c3,
+                                             int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.global.shared::cta.bulk_group"
+      " [%0, {%2, %3, %4, %5, %6}], [%1];"
+      ::"l"(map), "r"(smem_src), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+__device__ __forceinline__ int4 ld_nc_16(const void* p) {
+  int4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_16(void* p, int4 v) {
+  asm volatile("st.global.v4.s32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// ---- block-scaled fp8 helpers -----------------------------------------------------------
+// Scale of a 32-value group: the smallest power of two s with amax / s <= 448 (e4m3 max), stored
+// as a biased UE8M0 exponent byte.  amax == 0 maps to exponent 127 (scale 1).
+__device__ __forceinline__ uint32_t ue8m0_from_amax(float amax) {
+  if (!(amax > 0.f)) return 127u;
+  const float ratio = amax * (1.0f / 448.0f);
+  const uint32_t bits = __float_as_uint(ratio);
+  int e = static_cast<int>((bits >> 23) & 0xffu);
+  const uint32_t mant = bits & 0x7fffffu;
+  if (e == 0) {  // subnormal ratio: the smallest normal power of two is already large enough
+    return 1u;
+  }
+  if (mant != 0u) e += 1;  // round the scale up so the largest value does not saturate
+  if (e > 254) e = 254;
+  if (e < 1) e = 1;
+  return static_cast<uint32_t>(e);
+}
+__device__ __forceinline__ float scale_from_ue8m0(uint32_t e) { return __uint_as_float(e << 23); }
+
+__device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+
+// ---- SIMT tile movers ---------------------------------------------------------------------
+// Rows are enumerated in destination order so that consecutive threads write consecutive
+// destination addresses (NVLink and PCIe like long contiguous write runs).
+struct RowIter {
+  uint32_t ntok, nh;
+  bool token_inner;
+  __device__ __forceinline__ void decode(uint32_t row, uint32_t& t, uint32_t& h) const {
+    if (token_inner) {
+      h = row / ntok;
+      t = row - h * ntok;
+    } else {
+      t = row / nh;
+      h = row - t * nh;
+    }
+  }
+};
+
+__device__ __forceinline__ void simt_copy_tile(const KvtAttnLaunch& p, const TileInfo& ti, uint32_t kv,
+                                               const char* __restrict__ src, char* __restrict__ dst) {
+  const uint32_t cpr = p.src.head_bytes >> 4;  // 16-byte chunks per row
+  RowIter it;
+  it.ntok = ti.copy_hi - ti.copy_lo;
+  it.nh = p.n_heads;
+  it.token_inner = p.dst.token_stride < p.dst.head_stride;
+  const uint32_t chunks = it.ntok * it.nh * cpr;
+  const int64_t s_base = (int64_t)ti.sblk * p.src.block_stride + (int64_t)kv * p.src.kv_stride +
+                         (int64_t)(ti.s_slot0 + (ti.copy_lo - ti.tok_lo)) * p.src.token_stride +
+                         (int64_t)p.src_head0 * p.src.head_stride;
+  const int64_t d_base = (int64_t)ti.dblk * p.dst.block_stride + (int64_t)kv * p.dst.kv_stride +
+                         (int64_t)(ti.d_slot0 + (ti.copy_lo - ti.tok_lo)) * p.dst.token_stride +
+                         (int64_t)p.dst_head0 * p.dst.head_stride;
+  constexpr int U = 4;
+  for (uint32_t base = threadIdx.x; base < chunks; base += blockDim.x * U) {
+    int4 v[U];
+    int64_t doff[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t i = base + u * blockDim.x;
+      doff[u] = -1;
+      if (i < chunks) {
+        const uint32_t row = i / cpr;
+        const uint32_t c = i - row * cpr;
+        uint32_t t, h;
+        it.decode(row, t, h);
+        v[u] = ld_nc_16(src + s_base + (int64_t)t * p.src.token_stride + (int64_t)h * p.src.head_stride + (c << 4));
+        doff[u] = d_base + (int64_t)t * p.dst.token_stride + (int64_t)h * p.dst.head_stride + (c << 4);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (doff[u] >= 0) st_16(dst + doff[u], v[u]);
+    }
+  }
+}
+
+// bf16 source rows -> e4m3 rows + UE8M0 scales.  One thread converts 16 values (32 B in,
+// 16 B out); two neighbouring lanes form one 32-value scale group.
+__device__ __forceinline__ void simt_quant_tile(const KvtAttnLaunch& p, const TileInfo& ti, uint32_t kv,
+                                                const char* __restrict__ src, char* __restrict__ dst) {
+  const uint32_t cpr = p.src.head_bytes >> 5;  // 32-byte source chunks per row (even: head_dim % 32 == 0)
+  RowIter it;
+  it.ntok = ti.copy_hi - ti.copy_lo;
+  it.nh = p.n_heads;
+  it.token_inner = p.dst.token_stride < p.dst.head_stride;
+  const uint32_t chunks = it.ntok * it.nh * cpr;
+  const uint32_t slot_s = ti.s_slot0 + (ti.copy_lo - ti.tok_lo);
+  const uint32_t slot_d = ti.d_slot0 + (ti.copy_lo - ti.tok_lo);
+  const int64_t s_base = (int64_t)ti.sblk * p.src.block_stride + (int64_t)kv * p.src.kv_stride +
+                         (int64_t)slot_s * p.src.token_stride + (int64_t)p.src_head0 * p.src.head_stride;
+  const int64_t d_blk = (int64_t)ti.dblk * p.dst.block_stride;
+  const int64_t d_base = d_blk + (int64_t)kv * p.dst.kv_stride + (int64_t)slot_d * p.dst.token_stride +
+                         (int64_t)p.dst_head0 * p.dst.head_stride;
+  const int64_t sc_base = d_blk + p.dst.scale_base + (int64_t)kv * p.dst.scale_kv_stride +
+                          (int64_t)slot_d * p.dst.scale_token_stride +
+                          (int64_t)p.dst_head0 * p.dst.scale_head_stride;
+  const uint32_t rounds = (chunks + blockDim.x - 1) / blockDim.x;
+  for (uint32_t rnd = 0; rnd < rounds; ++rnd) {
+    const uint32_t i = rnd * blockDim.x + threadIdx.x;
+    const bool active = i < chunks;
+    uint32_t w[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    uint32_t row = 0, c = 0, t = 0, h = 0;
+    if (active) {
+      row = i / cpr;
+      c = i - row * cpr;
+      it.decode(row, t, h);
+      const char* sp = src + s_base + (int64_t)t * p.src.token_stride + (int64_t)h * p.src.head_stride + (c << 5);
+      const int4 a = ld_nc_16(sp);
+      const int4 b = ld_nc_16(sp + 16);
+      w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+      w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      amax = fmaxf(amax, fabsf(bf16lo(w[k])));
+      amax = fmaxf(amax, fabsf(bf16hi(w[k])));
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    const uint32_t e = ue8m0_from_amax(amax);
+    const float inv = __uint_as_float((254u - e) << 23);  // 1 / 2^(e-127)
+    if (active) {
+      int4 q;
+      q.x = pack_e4m3x4(bf16lo(w[0]) * inv, bf16hi(w[0]) * inv, bf16lo(w[1]) * inv, bf16hi(w[1]) * inv);
+      q.y = pack_e4m3x4(bf16lo(w[2]) * inv, bf16hi(w[2]) * inv, bf16lo(w[3]) * inv, bf16hi(w[3]) * inv);
+      q.z = pack_e4m3x4(bf16lo(w[4]) * inv, bf16hi(w[4]) * inv, bf16lo(w[5]) * inv, bf16hi(w[5]) * inv);
+      q.w = pack_e4m3x4(bf16lo(w[6]) * inv, bf16hi(w[6]) * inv, bf16lo(w[7]) * inv, bf16hi(w[7]) * inv);
+      st_16(dst + d_base + (int64_t)t * p.dst.token_stride + (int64_t)h * p.dst.head_stride + (c << 4), q);
+      if ((c & 1u) == 0u) {
+        dst[sc_base + (int64_t)t * p.dst.scale_token_stride + (int64_t)h * p.dst.scale_head_stride + (c >> 1)] =
+            static_cast<char>(e);
+      }
+    }
+  }
+}
+
+// e4m3 rows + UE8M0 scales -> bf16 rows.  One thread expands 16 values (16 B in, 32 B out).
+__device__ __forceinline__ void simt_dequant_tile(const KvtAttnLaunch& p, const TileInfo& ti, uint32_t kv,
+                                                  const char* __restrict__ src, char* __restrict__ dst) {
+  const uint32_t cpr = p.src.head_bytes >> 4;
+  RowIter it;
+  it.ntok = ti.copy_hi - ti.copy_lo;
+  it.nh = p.n_heads;
+  it.token_inner = p.dst.token_stride < p.dst.head_stride;
+  const uint32_t chunks = it.ntok * it.nh * cpr;
+  const uint32_t slot_s = ti.s_slot0 + (ti.copy_lo - ti.tok_lo);
+  const uint32_t slot_d = ti.d_slot0 + (ti.copy_lo - ti.tok_lo);
+  const int64_t s_blk = (int64_t)ti.sblk * p.src.block_stride;
+  const int64_t s_base = s_blk + (int64_t)kv * p.src.kv_stride + (int64_t)slot_s * p.src.token_stride +
+                         (int64_t)p.src_head0 * p.src.head_stride;
+  const int64_t sc_base = s_blk + p.src.scale_base + (int64_t)kv * p.src.scale_kv_stride +
+                          (int64_t)slot_s * p.src.scale_token_stride +
+                          (int64_t)p.src_head0 * p.src.scale_head_stride;
+  const int64_t d_base = (int64_t)ti.dblk * p.dst.block_stride + (int64_t)kv * p.dst.kv_stride +
+                         (int64_t)slot_d * p.dst.token_stride + (int64_t)p.dst_head0 * p.dst.head_stride;
+  for (uint32_t i = threadIdx.x; i < chunks; i += blockDim.x) {
+    const uint32_t row = i / cpr;
+    const uint32_t c = i - row * cpr;
+    uint32_t t, h;
+    it.decode(row, t, h);
+    const int4 q = ld_nc_16(src + s_base + (int64_t)t * p.src.token_stride + (int64_t)h * p.src.head_stride + (c << 4));
+    const uint32_t e = static_cast<uint8_t>(
+        src[sc_base + (int64_t)t * p.src.scale_token_stride + (int64_t)h * p.src.scale_head_stride + (c >> 1)]);
+    const float s = scale_from_ue8m0(e);
+    const uint32_t qw[4] = {(uint32_t)q.x, (uint32_t)q.y, (uint32_t)q.z, (uint32_t)q.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const __half2_raw h01 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(qw[k] & 0xffffu), __NV_E4M3);
+      const __half2_raw h23 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(qw[k] >> 16), __NV_E4M3);
+      const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&h01));
+      const float2 f23 = __half22float2(*reinterpret_cast<const __half2*>(&h23));
+      const __nv_bfloat162 b01 = __floats2bfloat162_rn(f01.x * s, f01.y * s);
+      const __nv_bfloat162 b23 = __floats2bfloat162_rn(f23.x * s, f23.y * s);
+      o[2 * k] = *reinterpret_cast<const uint32_t*>(&b01);
+      o[2 * k + 1] = *reinterpret_cast<const uint32_t*>(&b23);
+    }
+    char* dp = dst + d_base + (int64_t)t * p.dst.token_stride + (int64_t)h * p.dst.head_stride + (c << 5);
+    st_16(dp, make_int4(o[0], o[1], o[2], o[3]));
+    st_16(dp + 16, make_int4(o[4], o[5], o[6], o[7]));
+  }
+}
+
+// Zero destination slots [copy_hi, zero_hi) of a tile (tail pad of the last block).
+__device__ __forceinline__ void simt_zero_tail(const KvtAttnLaunch& p, const TileInfo& ti, uint32_t kv,
+                                               char* __restrict__ dst) {
+  const uint32_t ntok = ti.zero_hi - ti.copy_hi;
+  if (ntok == 0) return;
+  const uint32_t cpr = p.dst.head_bytes >> 4;
+  RowIter it;
+  it.ntok = ntok;
+  it.nh = p.n_heads;
+  it.token_inner = p.dst.token_stride < p.dst.head_stride;
+  const uint32_t chunks = ntok * it.nh * cpr;
+  const int64_t d_base = (int64_t)ti.dblk * p.dst.block_stride + (int64_t)kv * p.dst.kv_stride +
+                         (int64_t)(ti.d_slot0 + (ti.copy_hi - ti.tok_lo)) * p.dst.token_stride +
+                         (int64_t)p.dst_head0 * p.dst.head_stride;
+  for (uint32_t i = threadIdx.x; i < chunks; i += blockDim.x) {
+    const uint32_t row = i / cpr;
+    const uint32_t c = i - row * cpr;
+    uint32_t t, h;
+    it.decode(row, t, h);
+    st_16(dst + d_base + (int64_t)t * p.dst.token_stride + (int64_t)h * p.dst.head_stride + (c << 4),
+          make_int4(0, 0, 0, 0));
+  }
+}
+
+// ---- the kernel ---------------------------------------------------------------------------
+template <int MODE, bool USE_TMA>
+__global__ void __launch_bounds__(512) kvt_p2d_attn_kernel(const __grid_constant__ KvtAttnLaunch p,
+                                                            const uint32_t n_stages, const uint32_t tile_bytes) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  const uint32_t n_layers = p.layer_end - p.layer_begin;
+  const uint32_t per_layer = p.total_tiles * p.src.kv_count;
+  const uint64_t total = (uint64_t)n_layers * per_layer;
+
+  // Work index w -> (layer, kv, tile).  Consecutive CTAs take consecutive tiles of one layer.
+  if constexpr (USE_TMA) {
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)n_stages * tile_bytes);
+    if (threadIdx.x == 0) {
+      for (uint32_t s = 0; s < n_stages; ++s) mbar_init(smem_u32(&bars[s]), 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      fence_proxy_async();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      // Single-thread software pipeline over this CTA's full tiles.
+      struct Slot { const void* dmap; int c1, c2, c3, c4; };
+      Slot slots[kMaxStages];
+      uint32_t issued = 0, stored = 0;
+      uint64_t w = blockIdx.x;
+      bool failed = false;
+      auto next_full = [&](uint64_t& wi, TileInfo& ti, uint32_t& layer, uint32_t& kv) -> bool {
+        while (wi < total) {
+          layer = (uint32_t)(wi / per_layer);
+          const uint32_t rem = (uint32_t)(wi - (uint64_t)layer * per_layer);
+          kv = rem / p.total_tiles;
+          const uint32_t tile = rem - kv * p.total_tiles;
+          ti = decode_tile(p, tile);
+          wi += gridDim.x;
+          if (!ti.ok) continue;  // reported by the SIMT pass
+          if (tile_is_full(p, ti)) return true;
+        }
+        return false;
+      };
+      auto issue_load = [&](const TileInfo& ti, uint32_t layer, uint32_t kv) {
+        const uint32_t s = issued % n_stages;
+        const uint32_t bar = smem_u32(&bars[s]);
+        const CUtensorMap* smap = reinterpret_cast<const CUtensorMap*>(p.src_maps) + (p.layer_begin + layer);
+        const CUtensorMap* dmap = reinterpret_cast<const CUtensorMap*>(p.dst_maps) + (p.layer_begin + layer);
+        mbar_expect_tx(bar, tile_bytes);
+        tma_load_5d(smem_u32(smem + (size_t)s * tile_bytes), smap, bar, 0, (int)p.src_head0, (int)ti.s_slot0,
+                    (int)ti.sblk, (int)kv);
+        slots[s].dmap = dmap;
+        slots[s].c1 = (int)p.dst_head0;
+        slots[s].c2 = (int)ti.d_slot0;
+        slots[s].c3 = (int)ti.dblk;
+        slots[s].c4 = (int)kv;
+        ++issued;
+      };
+      TileInfo ti;
+      uint32_t layer, kv;
+      // Prologue: fill all but one stage (the last one is refilled one store behind).
+      while (issued + 1 < n_stages || (n_stages == 1 && issued == 0)) {
+        if (!next_full(w, ti, layer, kv)) break;
+        issue_load(ti, layer, kv);
+      }
+      bool more = true;
+      while (stored < issued) {
+        const uint32_t s = stored % n_stages;
+        const uint32_t bar = smem_u32(&bars[s]);
+        const uint32_t parity = (stored / n_stages) & 1u;
+        const long long t0 = clock64();
+        while (!mbar_try_wait(bar, parity)) {
+          if (clock64() - t0 > kWaitCycles) {
+            failed = true;
+            break;
+          }
+        }
+        if (failed) {
+          set_status(p.status, KVT_ERR_TMA_TIMEOUT, stored);
+          break;
+        }
+        tma_store_5d(slots[s].dmap, smem_u32(smem + (size_t)s * tile_bytes), 0, slots[s].c1, slots[s].c2,
+                     slots[s].c3, slots[s].c4);
+        bulk_commit();
+        ++stored;
+        if (more) {
+          // The stage that becomes free is the one whose store was issued one iteration ago
+          // (or the never-used last stage on the first iterations).
+          if (n_stages > 1) bulk_wait_read<1>(); else bulk_wait_read<0>();
+          if (next_full(w, ti, layer, kv)) issue_load(ti, layer, kv); else more = false;
+        }
+      }
+      bulk_wait_all();
+      fence_proxy_async();
+    }
+  }
+
+  // SIMT pass: everything the TMA pass does not take.
+  for (uint64_t w = blockIdx.x; w < total; w += gridDim.x) {
+    const uint32_t layer = (uint32_t)(w / per_layer);
+    const uint32_t rem = (uint32_t)(w - (uint64_t)layer * per_layer);
+    const uint32_t kv = rem / p.total_tiles;
+    const uint32_t tile = rem - kv * p.total_tiles;
+    const TileInfo ti = decode_tile(p, tile);
+    if (!ti.ok) {
+      if (threadIdx.x == 0) set_status(p.status, KVT_ERR_BLOCK_RANGE, tile);
+      continue;
+    }
+    const char* src = reinterpret_cast<const char*>(p.src_layers[p.layer_begin + layer]);
+    char* dst = reinterpret_cast<char*>(p.dst_layers[p.layer_begin + layer]);
+    if (ti.copy_hi > ti.copy_lo) {
+      if constexpr (MODE == KVT_MODE_COPY) {
+        if (!(USE_TMA && tile_is_full(p, ti))) simt_copy_tile(p, ti, kv, src, dst);
+      } else if constexpr (MODE == KVT_MODE_BF16_TO_MXFP8) {
+        simt_quant_tile(p, ti, kv, src, dst);
+      } else {
+        simt_dequant_tile(p, ti, kv, src, dst);
+      }
+    }
+    if (ti.zero_hi > ti.copy_hi) simt_zero_tail(p, ti, kv, dst);
+  }
+
+  // Completion: the last CTA to finish publishes the flag after a system-scope fence, so a
+  // reader on the destination GPU or on the host that sees the flag also sees the data.
+  if (p.flag != nullptr && p.done_counter != nullptr) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const uint32_t prev = atomicAdd(p.done_counter, 1u);
+      if (prev == gridDim.x - 1) {
+        *p.done_counter = 0;  // re-arm for the next launch on this stream
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p.flag), "l"(p.flag_value) : "memory");
+      }
+    }
+  }
+}
+
+struct DriverApi {
+  CUresult (*encode_tiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                           const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                           CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill) = nullptr;
+  bool tried = false;
+};
+DriverApi g_driver;
+
+bool load_driver_api() {
+  if (g_driver.tried) return g_driver.encode_tiled != nullptr;
+  g_driver.tried = true;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+      qres == cudaDriverEntryPointSuccess) {
+    g_driver.encode_tiled = reinterpret_cast<decltype(g_driver.encode_tiled)>(fn);
+  }
+  return g_driver.encode_tiled != nullptr;
+}
+
+template <int MODE, bool USE_TMA>
+cudaError_t launch_impl(const KvtAttnLaunch& a, int grid, int threads, uint32_t stages, uint32_t tile_bytes,
+                        size_t smem, cudaStream_t stream) {
+  auto kern = kvt_p2d_attn_kernel<MODE, USE_TMA>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  kern<<<grid, threads, smem, stream>>>(a, stages, tile_bytes);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" uint32_t kvt_req_tiles(uint32_t seen, uint32_t new_tokens, uint32_t tile_tokens, uint32_t flags,
+                                  uint32_t dst_ntpb) {
+  if (tile_tokens == 0) return 0;
+  uint64_t end_tok = (uint64_t)seen + new_tokens;
+  if ((flags & KVT_REQ_PAD_TAIL) && dst_ntpb > 0) end_tok = (end_tok + dst_ntpb - 1) / dst_ntpb * dst_ntpb;
+  if (end_tok <= seen && new_tokens == 0) return 0;
+  const uint64_t first = seen / tile_tokens;
+  const uint64_t last = (end_tok + tile_tokens - 1) / tile_tokens;
+  return (uint32_t)(last - first);
+}
+
+extern "C" int kvt_encode_tensor_map(void* out, uint64_t base, const KvtLayout* l, uint32_t box_heads,
+                                     uint32_t box_tokens) {
+  if (!load_driver_api()) return -1;
+  if (l->head_bytes % 16 != 0 || (base & 15) != 0) return -2;
+  if (l->head_bytes / 4 > 256 || box_heads > 256 || box_tokens > 256) return -3;
+  if (box_heads == 0 || box_tokens == 0 || box_heads > l->num_heads || box_tokens > l->ntpb) return -3;
+  const int64_t strides[4] = {l->head_stride, l->token_stride, l->block_stride,
+                              l->kv_count > 1 ? l->kv_stride : l->block_stride * (int64_t)l->num_blocks};
+  for (int i = 0; i < 4; ++i) {
+    if (strides[i] <= 0 || (strides[i] % 16) != 0 || strides[i] >= (1ll << 40)) return -4;
+  }
+  cuuint64_t gdim[5] = {l->head_bytes / 4, l->num_heads, l->ntpb, l->num_blocks, l->kv_count ? l->kv_count : 1};
+  cuuint64_t gstr[4] = {(cuuint64_t)strides[0], (cuuint64_t)strides[1], (cuuint64_t)strides[2],
+                        (cuuint64_t)strides[3]};
+  cuuint32_t box[5] = {l->head_bytes / 4, box_heads, box_tokens, 1, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = g_driver.encode_tiled(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_UINT32, 5,
+                                     reinterpret_cast<void*>(base), gdim, gstr, box, estr,
+                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return (int)r;
+}
+
+extern "C" int kvt_launch_p2d_attn(const KvtAttnLaunch* args, int grid_ctas, int threads, int use_tma,
+                                   void* stream_) {
+  const KvtAttnLaunch& a = *args;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (a.n_reqs == 0 || a.total_tiles == 0 || a.layer_end <= a.layer_begin) return (int)cudaSuccess;
+  if (a.tile_tokens == 0 || a.src.ntpb % a.tile_tokens != 0 || a.dst.ntpb % a.tile_tokens != 0)
+    return (int)cudaErrorInvalidValue;
+  if (a.src.kv_count != a.dst.kv_count || a.n_heads == 0) return (int)cudaErrorInvalidValue;
+  if (a.src_head0 + a.n_heads > a.src.num_heads || a.dst_head0 + a.n_heads > a.dst.num_heads)
+    return (int)cudaErrorInvalidValue;
+  if (a.mode == KVT_MODE_COPY) {
+    if (a.src.head_bytes != a.dst.head_bytes || a.src.head_bytes % 16 != 0) return (int)cudaErrorInvalidValue;
+  } else if (a.mode == KVT_MODE_BF16_TO_MXFP8) {
+    if (a.src.head_bytes != 2 * a.dst.head_bytes || a.src.head_bytes % 64 != 0) return (int)cudaErrorInvalidValue;
+  } else if (a.mode == KVT_MODE_MXFP8_TO_BF16) {
+    if (2 * a.src.head_bytes != a.dst.head_bytes || a.dst.head_bytes % 64 != 0) return (int)cudaErrorInvalidValue;
+  } else {
+    return (int)cudaErrorInvalidValue;
+  }
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int sms = 0;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int grid = grid_ctas > 0 ? grid_ctas : sms;
+  const uint64_t total = (uint64_t)(a.layer_end - a.layer_begin) * a.total_tiles * a.src.kv_count;
+  if ((uint64_t)grid > total) grid = (int)total;
+  if (threads <= 0) threads = use_tma ? 128 : 512;
+  if (threads > 512) threads = 512;
+  threads = (threads + 31) / 32 * 32;
+  const bool tma = use_tma && a.mode == KVT_MODE_COPY && a.src_maps != nullptr && a.dst_maps != nullptr;
+  if (tma) {
+    const uint32_t tile_bytes = a.src.head_bytes * a.n_heads * a.tile_tokens;
+    if (tile_bytes % 128 != 0 || tile_bytes > kSmemBudget) return (int)cudaErrorInvalidValue;
+    uint32_t stages = kSmemBudget / tile_bytes;
+    if (stages > (uint32_t)kMaxStages) stages = kMaxStages;
+    const uint64_t per_cta = (total + grid - 1) / grid;
+    if (stages > per_cta + 1) stages = (uint32_t)per_cta + 1;
+    if (stages < 1) stages = 1;
+    const size_t smem = (size_t)stages * tile_bytes + kMaxStages * sizeof(uint64_t);
+    return (int)launch_impl<KVT_MODE_COPY, true>(a, grid, threads, stages, tile_bytes, smem, stream);
+  }
+  switch (a.mode) {
+    case KVT_MODE_COPY:
+      return (int)launch_impl<KVT_MODE_COPY, false>(a, grid, threads, 0, 0, 0, stream);
+    case KVT_MODE_BF16_TO_MXFP8:
+      return (int)launch_impl<KVT_MODE_BF16_TO_MXFP8, false>(a, grid, threads, 0, 0, 0, stream);
+    default:
+      return (int)launch_impl<KVT_MODE_MXFP8_TO_BF16, false>(a, grid, threads, 0, 0, 0, stream);
+  }
+}

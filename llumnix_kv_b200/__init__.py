@@ -1,0 +1,40 @@
+"""llumnix_kv_b200: a Blackwell-native KV-cache transfer and storage framework.
+
+Public surface (names follow the reference package ``blade_kvt``):
+
+* ``llumnix_kv_b200.hybrid_connector`` - HybridConnector control plane (scheduler / worker
+  halves, backends, RPC protocol).
+* ``llumnix_kv_b200.kv_transfer`` / ``kv_transfer_impl`` - ``KVTransferClient`` /
+  ``KVTransferServer`` over the native engine.
+* ``llumnix_kv_b200.kvtransfer_ops`` - the native extension (C++ engine + sm_100a kernels).
+* ``llumnix_kv_b200.ops`` - kernel-level Python wrappers and their PyTorch oracles.
+"""
+from __future__ import annotations
+
+import importlib
+import os
+
+__version__ = "0.1.0"
+
+
+def load_ops(build_if_missing: bool = True):
+    """Import the native extension, compiling it in-tree first when it is absent.
+
+    Raises if it cannot be loaded: nothing in this package silently falls back to PyTorch.
+    """
+    try:
+        return importlib.import_module("llumnix_kv_b200.kvtransfer_ops")
+    except ImportError:
+        if not build_if_missing or os.environ.get("LLUMNIX_KV_NO_AUTOBUILD") == "1":
+            raise
+    from . import _build
+
+    _build.build()
+    importlib.invalidate_caches()
+    return importlib.import_module("llumnix_kv_b200.kvtransfer_ops")
+
+
+def set_envs() -> None:
+    """Default environment of the native engine (role of blade_kvt/__init__.py:42-61)."""
+    os.environ.setdefault("BLLM_KVTRANS_RDMA_SP", "2")
+    os.environ.setdefault("BLLM_KVTRANS_SDH_KIND", "2")

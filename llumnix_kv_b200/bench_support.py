@@ -1,0 +1,190 @@
+"""Workload builder shared by ``bench.py`` and the profiling commands.
+
+``PDBenchPair`` sets up one prefill->decode pair of the Llama-3-8B-shaped config: a source
+paged cache in FlashAttention NHD on the prefill GPU, a destination cache in FlashInfer HND
+on the decode GPU (peer-mapped through CUDA IPC when the two are different processes), and
+random non-contiguous block tables.  ``step_device`` replays a pre-uploaded plan (kernel-only
+timing); ``step_e2e`` does what a prefill worker does every engine step: pack the block
+tables into pinned memory, upload them, launch one transfer kernel per layer and read the
+completion word and status back.
+"""
+from __future__ import annotations
+
+import ctypes
+import random
+from typing import List
+
+import torch
+
+from .ops.layouts import AttnLayout, CacheShape
+from .ops.p2d_attn import AttnTransfer, ReqChunk
+
+BLOCK = 16
+KV_HEADS = 8
+HEAD_DIM = 128
+
+
+class PDBenchPair:
+    def __init__(self, K, rank: int, world: int, dev, tokens: int, requests: int, slots: int, n_layers: int,
+                 use_tma: bool, grid: int):
+        import torch.distributed as dist
+
+        self.K, self.rank, self.world, self.dev = K, rank, world, dev
+        self.n_pairs = max(world // 2, 1)
+        self.loopback = world == 1
+        self.is_sender = self.loopback or rank < self.n_pairs
+        self.is_receiver = self.loopback or rank >= self.n_pairs
+        self.n_layers, self.grid, self.requests, self.slots = n_layers, grid, requests, slots
+        blocks_per_req = (tokens + BLOCK - 1) // BLOCK
+        self.tokens = tokens
+        n_blocks = slots * requests * blocks_per_req + 1
+        self.src_l = AttnLayout(CacheShape.FLASH, n_blocks, BLOCK, KV_HEADS, HEAD_DIM, 2)
+        self.dst_l = AttnLayout(CacheShape.FLASHINFER, n_blocks, BLOCK, KV_HEADS, HEAD_DIM, 2)
+        self.slot_bytes = requests * blocks_per_req * self.src_l.block_bytes * n_layers
+        self.bytes_per_step = requests * tokens * self.src_l.token_bytes * n_layers
+        self.launches_per_step = n_layers
+        self.stream = torch.cuda.Stream(device=dev)
+        self.touched = set()
+
+        # block tables: a fixed random permutation, identical on every rank (same seed)
+        rng = random.Random(1234)
+        ids_s = list(range(1, n_blocks))
+        ids_d = list(range(1, n_blocks))
+        rng.shuffle(ids_s)
+        rng.shuffle(ids_d)
+        self.slot_chunks: List[List[ReqChunk]] = []
+        k = 0
+        for _ in range(slots):
+            cs = []
+            for _ in range(requests):
+                cs.append(ReqChunk(ids_s[k:k + blocks_per_req], ids_d[k:k + blocks_per_req], 0, tokens))
+                k += blocks_per_req
+            self.slot_chunks.append(cs)
+
+        # caches
+        self.src = self.dst = None
+        if self.is_sender:
+            self.src = torch.empty(n_layers * self.src_l.layer_bytes, dtype=torch.uint8, device=dev)
+            for i in range(n_layers):
+                self._fill_layer(self.src, i, self._pair_id())
+        dst_ptrs = None
+        if self.is_receiver:
+            self.dst = torch.zeros(n_layers * self.dst_l.layer_bytes, dtype=torch.uint8, device=dev)
+        if self.loopback:
+            dst_ptrs = [self.dst.data_ptr() + i * self.dst_l.layer_bytes for i in range(n_layers)]
+            self.transport_name = "local HBM (same GPU)"
+        else:
+            mine = None
+            if self.is_receiver:
+                h, base, _size = K.kvt_ipc_get_handle(self.dst.data_ptr())
+                mine = (h, self.dst.data_ptr() - base)
+            infos = [None] * world
+            dist.all_gather_object(infos, mine)
+            if self.is_sender:
+                h, off = infos[rank + self.n_pairs]
+                self.peer_base = K.kvt_ipc_open_handle(h)
+                dst_ptrs = [self.peer_base + off + i * self.dst_l.layer_bytes for i in range(n_layers)]
+            self.transport_name = "NVLink P2P stores into CUDA-IPC mapped peer cache"
+
+        self.xfer = None
+        self.h2d_bytes_per_step = 0
+        self.d2h_bytes_per_step = 16
+        if self.is_sender:
+            src_ptrs = [self.src.data_ptr() + i * self.src_l.layer_bytes for i in range(n_layers)]
+            self.xfer = AttnTransfer(self.src_l, self.dst_l, src_ptrs, dst_ptrs, dev, use_tma=use_tma)
+            self.use_tma = self.xfer.use_tma
+            with torch.cuda.stream(self.stream):
+                self.plans = [self.xfer.plan(cs, stream=self.stream) for cs in self.slot_chunks]
+            self.h2d_bytes_per_step = self.plans[0].nbytes
+            self.pinned = torch.empty(max(self.plans[0].nbytes, 16), dtype=torch.uint8, pin_memory=True)
+            self.flag_host, self.flag_dev = K.kvt_host_alloc_mapped(64)
+            self.flag = ctypes.c_uint64.from_address(self.flag_host)
+            self.flag.value = 0
+            self.seq = 0
+            self.status_host = torch.zeros(4, dtype=torch.int32, pin_memory=True)
+        torch.cuda.synchronize()
+
+    def _pair_id(self) -> int:
+        return self.rank % self.n_pairs if not self.loopback else 0
+
+    def _fill_layer(self, buf: torch.Tensor, layer: int, pair: int) -> None:
+        g = torch.Generator(device=self.dev)
+        g.manual_seed(977 * pair + layer)
+        n = self.src_l.layer_bytes // 2
+        view = buf[layer * self.src_l.layer_bytes:(layer + 1) * self.src_l.layer_bytes].view(torch.bfloat16)
+        chunk = 1 << 26
+        for o in range(0, n, chunk):
+            m = min(chunk, n - o)
+            view[o:o + m].copy_(torch.randn(m, dtype=torch.float32, device=self.dev, generator=g))
+
+    # ---- steps ------------------------------------------------------------------------
+    def step_device(self, i: int) -> None:
+        if not self.is_sender:
+            return
+        plan = self.plans[i % self.slots]
+        self.touched.add(i % self.slots)
+        with torch.cuda.stream(self.stream):
+            for layer in range(self.n_layers):
+                self.xfer.launch(plan, layer, layer + 1, stream=self.stream, grid=self.grid)
+
+    def step_e2e(self, i: int) -> None:
+        if not self.is_sender:
+            return
+        self.seq += 1
+        self.touched.add(i % self.slots)
+        with torch.cuda.stream(self.stream):
+            plan = self.xfer.plan(self.slot_chunks[i % self.slots], stream=self.stream, pinned=self.pinned)
+            last = self.n_layers - 1
+            for layer in range(self.n_layers):
+                self.xfer.launch(plan, layer, layer + 1, stream=self.stream, grid=self.grid,
+                                 flag_ptr=self.flag_dev if layer == last else 0, flag_value=self.seq)
+            self.status_host.copy_(self.xfer.status, non_blocking=True)
+        self.stream.synchronize()
+        if self.flag.value != self.seq or int(self.status_host[0]) != 0:
+            raise RuntimeError(f"transfer step {self.seq} failed: flag={self.flag.value} "
+                               f"status={self.status_host.tolist()}")
+
+    # ---- correctness after the timed runs ---------------------------------------------------
+    def verify(self, layers=(0,)) -> None:
+        torch.cuda.synchronize()
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
+        touched = sorted(self.touched)
+        if self.world > 1:
+            import torch.distributed as dist
+
+            got = [None] * self.world
+            dist.all_gather_object(got, touched)
+            touched = got[self.rank - self.n_pairs] if self.rank >= self.n_pairs else touched
+        if not self.is_receiver:
+            return
+        pair = (self.rank - self.n_pairs) if not self.loopback else 0
+        for layer in layers:
+            if layer >= self.n_layers:
+                continue
+            if self.loopback:
+                src_layer = self.src[layer * self.src_l.layer_bytes:(layer + 1) * self.src_l.layer_bytes]
+            else:
+                tmp = torch.empty(self.src_l.layer_bytes, dtype=torch.uint8, device=self.dev)
+                saved_l = self.src_l
+                g = torch.Generator(device=self.dev)
+                g.manual_seed(977 * pair + layer)
+                n = saved_l.layer_bytes // 2
+                v = tmp.view(torch.bfloat16)
+                chunk = 1 << 26
+                for o in range(0, n, chunk):
+                    m = min(chunk, n - o)
+                    v[o:o + m].copy_(torch.randn(m, dtype=torch.float32, device=self.dev, generator=g))
+                src_layer = tmp
+            dst_layer = self.dst[layer * self.dst_l.layer_bytes:(layer + 1) * self.dst_l.layer_bytes]
+            sv = self.src_l.view(src_layer, torch.int16)
+            dv = self.dst_l.view(dst_layer, torch.int16)
+            for slot in touched:
+                for c in self.slot_chunks[slot]:
+                    nb_full = c.new_tokens // BLOCK
+                    sb = torch.tensor(list(c.src_blocks[:nb_full]), device=self.dev)
+                    db = torch.tensor(list(c.dst_blocks[:nb_full]), device=self.dev)
+                    if not torch.equal(dv[db], sv[sb]):
+                        raise RuntimeError(f"rank {self.rank}: destination cache mismatch in layer {layer}")
