@@ -44,6 +44,7 @@ def parse_args():
     ap.add_argument("--slots", type=int, default=4, help="distinct request slots cycled through (each larger than L2)")
     ap.add_argument("--grid", type=int, default=0, help="CTAs of the transfer kernel (0 = tuned default)")
     ap.add_argument("--no-tma", action="store_true")
+    ap.add_argument("--streams", type=int, default=2, help="transfer streams the layers alternate over")
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--small", action="store_true", help="tiny case for profiler captures")
     ap.add_argument("--e2e-only", action="store_true")
@@ -51,46 +52,55 @@ def parse_args():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    """Samples SM clock and throttle reasons of one GPU (read-only NVML) while the timed region runs."""
 
-    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown"}
 
-    def __init__(self, index: int):
-        self.proc = None
+    def __init__(self, index: int, period_s: float = 0.002):
+        import threading
+
+        self.samples, self.bits, self.max_mhz, self.err = [], 0, None, None
+        self._stop = threading.Event()
+        self._thread = None
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
-                 str(index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+            import pynvml
+
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = index
+            if visible:
+                ids = [x for x in visible.split(",") if x != ""]
+                if index < len(ids) and ids[index].isdigit():
+                    phys = int(ids[index])
+            h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+
+            def loop():
+                while not self._stop.is_set():
+                    try:
+                        self.samples.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
+                        self.bits |= int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))
+                    except Exception as ex:  # keep the benchmark alive if a query is refused
+                        self.err = str(ex)
+                        return
+                    time.sleep(period_s)
+
+            self._thread = threading.Thread(target=loop, daemon=True)
+            self._thread.start()
+        except Exception as ex:
+            self.err = f"{type(ex).__name__}: {ex}"
 
     def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-            out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.strip().splitlines():
-            f = [x.strip() for x in line.split(",")]
-            if len(f) < 8:
-                continue
-            try:
-                sm.append(float(f[0]))
-                mx.append(float(f[1]))
-            except ValueError:
-                continue
-            for name, v in zip(names, f[4:8]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        reasons = sorted(n for b, n in self.REASONS.items() if self.bits & b)
+        out = {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+               "samples": len(self.samples), "reasons": reasons}
+        if self.err:
+            out["note"] = self.err[:120]
+        return out
 
 
 def reference_arm(args):
@@ -130,7 +140,7 @@ def main():
         args.tokens, args.slots, args.layers = 2048, 2, 4
 
     pair = PDBenchPair(K, rank, world, dev, tokens=args.tokens, requests=args.requests, slots=args.slots,
-                       n_layers=args.layers, use_tma=not args.no_tma, grid=args.grid)
+                       n_layers=args.layers, use_tma=not args.no_tma, grid=args.grid, n_streams=args.streams)
 
     def barrier():
         if world > 1:
@@ -143,10 +153,10 @@ def main():
         barrier()
         sampler = ClockSampler(local_rank)
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ev0.record()
+        ev0.record(pair.stream)
         for i in range(steps):
             run_step(warmup + i)
-        ev1.record()
+        ev1.record(pair.stream)
         torch.cuda.synchronize()
         ms = ev0.elapsed_time(ev1) if pair.is_sender else 0.0
         clocks = sampler.stop()
@@ -198,7 +208,7 @@ def main():
             "e2e": {"value": round(agg(ms_e2e), 2), "unit": "GB/s", "ms_per_step": round(ms_e2e / args.steps, 4),
                     "h2d_bytes_per_step": pair.h2d_bytes_per_step, "d2h_bytes_per_step": pair.d2h_bytes_per_step,
                     "clocks": clocks_e2e},
-            "gpu_launches": pair.launches_per_step * args.steps,
+            "gpu_launches": pair.launches_per_step * args.steps * (1 if args.e2e_only else 2) + args.steps,
         }
         print(json.dumps(out))
     if world > 1:

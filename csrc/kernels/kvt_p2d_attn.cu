@@ -400,50 +400,16 @@ __global__ void __launch_bounds__(512) kvt_p2d_attn_kernel(const __grid_constant
       fence_proxy_async();
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      // Single-thread software pipeline over this CTA's full tiles.
+    if (threadIdx.x < 32) {
+      // Producer warp.  All 32 lanes decode tiles in parallel (the block-table walk is a chain
+      // of dependent loads, so doing it on one thread would serialise ~1 us per tile); lane 0
+      // runs the software pipeline: at most n_stages-1 loads in flight, one store behind.
+      const uint32_t lane = threadIdx.x;
       struct Slot { const void* dmap; int c1, c2, c3, c4; };
       Slot slots[kMaxStages];
       uint32_t issued = 0, stored = 0;
-      uint64_t w = blockIdx.x;
       bool failed = false;
-      auto next_full = [&](uint64_t& wi, TileInfo& ti, uint32_t& layer, uint32_t& kv) -> bool {
-        while (wi < total) {
-          layer = (uint32_t)(wi / per_layer);
-          const uint32_t rem = (uint32_t)(wi - (uint64_t)layer * per_layer);
-          kv = rem / p.total_tiles;
-          const uint32_t tile = rem - kv * p.total_tiles;
-          ti = decode_tile(p, tile);
-          wi += gridDim.x;
-          if (!ti.ok) continue;  // reported by the SIMT pass
-          if (tile_is_full(p, ti)) return true;
-        }
-        return false;
-      };
-      auto issue_load = [&](const TileInfo& ti, uint32_t layer, uint32_t kv) {
-        const uint32_t s = issued % n_stages;
-        const uint32_t bar = smem_u32(&bars[s]);
-        const CUtensorMap* smap = reinterpret_cast<const CUtensorMap*>(p.src_maps) + (p.layer_begin + layer);
-        const CUtensorMap* dmap = reinterpret_cast<const CUtensorMap*>(p.dst_maps) + (p.layer_begin + layer);
-        mbar_expect_tx(bar, tile_bytes);
-        tma_load_5d(smem_u32(smem + (size_t)s * tile_bytes), smap, bar, 0, (int)p.src_head0, (int)ti.s_slot0,
-                    (int)ti.sblk, (int)kv);
-        slots[s].dmap = dmap;
-        slots[s].c1 = (int)p.dst_head0;
-        slots[s].c2 = (int)ti.d_slot0;
-        slots[s].c3 = (int)ti.dblk;
-        slots[s].c4 = (int)kv;
-        ++issued;
-      };
-      TileInfo ti;
-      uint32_t layer, kv;
-      // Prologue: fill all but one stage (the last one is refilled one store behind).
-      while (issued + 1 < n_stages || (n_stages == 1 && issued == 0)) {
-        if (!next_full(w, ti, layer, kv)) break;
-        issue_load(ti, layer, kv);
-      }
-      bool more = true;
-      while (stored < issued) {
+      auto consume_one = [&]() {
         const uint32_t s = stored % n_stages;
         const uint32_t bar = smem_u32(&bars[s]);
         const uint32_t parity = (stored / n_stages) & 1u;
@@ -456,21 +422,71 @@ __global__ void __launch_bounds__(512) kvt_p2d_attn_kernel(const __grid_constant
         }
         if (failed) {
           set_status(p.status, KVT_ERR_TMA_TIMEOUT, stored);
-          break;
+          return;
         }
         tma_store_5d(slots[s].dmap, smem_u32(smem + (size_t)s * tile_bytes), 0, slots[s].c1, slots[s].c2,
                      slots[s].c3, slots[s].c4);
         bulk_commit();
         ++stored;
-        if (more) {
-          // The stage that becomes free is the one whose store was issued one iteration ago
-          // (or the never-used last stage on the first iterations).
-          if (n_stages > 1) bulk_wait_read<1>(); else bulk_wait_read<0>();
-          if (next_full(w, ti, layer, kv)) issue_load(ti, layer, kv); else more = false;
+      };
+      for (uint64_t batch = 0;; batch += 32) {
+        const uint64_t w = blockIdx.x + (batch + lane) * (uint64_t)gridDim.x;
+        bool full = false;
+        TileInfo ti;
+        ti.sblk = ti.dblk = ti.s_slot0 = ti.d_slot0 = 0;
+        uint32_t layer = 0, kv = 0;
+        if (w < total) {
+          layer = (uint32_t)(w / per_layer);
+          const uint32_t rem = (uint32_t)(w - (uint64_t)layer * per_layer);
+          kv = rem / p.total_tiles;
+          ti = decode_tile(p, rem - kv * p.total_tiles);
+          full = ti.ok && tile_is_full(p, ti);  // bad tiles are reported by the SIMT pass
+        }
+        const unsigned any = __ballot_sync(0xffffffffu, w < total);
+        unsigned fullmask = __ballot_sync(0xffffffffu, full);
+        if (any == 0u) break;
+        while (fullmask != 0u) {
+          const int j = __ffs(fullmask) - 1;
+          fullmask &= fullmask - 1u;
+          const uint32_t j_sblk = __shfl_sync(0xffffffffu, ti.sblk, j);
+          const uint32_t j_dblk = __shfl_sync(0xffffffffu, ti.dblk, j);
+          const uint32_t j_ss = __shfl_sync(0xffffffffu, ti.s_slot0, j);
+          const uint32_t j_ds = __shfl_sync(0xffffffffu, ti.d_slot0, j);
+          const uint32_t j_layer = __shfl_sync(0xffffffffu, layer, j);
+          const uint32_t j_kv = __shfl_sync(0xffffffffu, kv, j);
+          if (lane == 0 && !failed) {
+            if (n_stages == 1) {
+              if (issued > stored) consume_one();
+              if (!failed) bulk_wait_read<0>();
+            } else if (issued - stored == n_stages - 1) {
+              consume_one();
+              // the stage refilled below was last read by the store issued one step earlier
+              if (!failed) bulk_wait_read<1>();
+            }
+            if (!failed) {
+              const uint32_t s = issued % n_stages;
+              const uint32_t bar = smem_u32(&bars[s]);
+              const CUtensorMap* smap = reinterpret_cast<const CUtensorMap*>(p.src_maps) + (p.layer_begin + j_layer);
+              const CUtensorMap* dmap = reinterpret_cast<const CUtensorMap*>(p.dst_maps) + (p.layer_begin + j_layer);
+              mbar_expect_tx(bar, tile_bytes);
+              tma_load_5d(smem_u32(smem + (size_t)s * tile_bytes), smap, bar, 0, (int)p.src_head0, (int)j_ss,
+                          (int)j_sblk, (int)j_kv);
+              slots[s].dmap = dmap;
+              slots[s].c1 = (int)p.dst_head0;
+              slots[s].c2 = (int)j_ds;
+              slots[s].c3 = (int)j_dblk;
+              slots[s].c4 = (int)j_kv;
+              ++issued;
+            }
+          }
         }
       }
-      bulk_wait_all();
-      fence_proxy_async();
+      if (lane == 0) {
+        while (!failed && stored < issued) consume_one();
+        bulk_wait_all();
+        fence_proxy_async();
+      }
+      __syncwarp();
     }
   }
 

@@ -26,7 +26,7 @@ HEAD_DIM = 128
 
 class PDBenchPair:
     def __init__(self, K, rank: int, world: int, dev, tokens: int, requests: int, slots: int, n_layers: int,
-                 use_tma: bool, grid: int):
+                 use_tma: bool, grid: int, n_streams: int = 2):
         import torch.distributed as dist
 
         self.K, self.rank, self.world, self.dev = K, rank, world, dev
@@ -44,6 +44,11 @@ class PDBenchPair:
         self.bytes_per_step = requests * tokens * self.src_l.token_bytes * n_layers
         self.launches_per_step = n_layers
         self.stream = torch.cuda.Stream(device=dev)
+        # Layers are independent transfers: alternate them over a few streams so that one
+        # layer's tail overlaps the next layer's ramp-up.  self.stream brackets all of them.
+        self.side = [torch.cuda.Stream(device=dev) for _ in range(max(n_streams - 1, 0))]
+        self.ev_begin = torch.cuda.Event()
+        self.ev_side = [torch.cuda.Event() for _ in self.side]
         self.touched = set()
 
         # block tables: a fixed random permutation, identical on every rank (same seed)
@@ -123,9 +128,22 @@ class PDBenchPair:
             return
         plan = self.plans[i % self.slots]
         self.touched.add(i % self.slots)
-        with torch.cuda.stream(self.stream):
-            for layer in range(self.n_layers):
-                self.xfer.launch(plan, layer, layer + 1, stream=self.stream, grid=self.grid)
+        self._fan_out()
+        lanes = [self.stream] + self.side
+        for layer in range(self.n_layers):
+            self.xfer.launch(plan, layer, layer + 1, stream=lanes[layer % len(lanes)], grid=self.grid)
+        self._fan_in()
+
+    def _fan_out(self) -> None:
+        if self.side:
+            self.ev_begin.record(self.stream)
+            for s in self.side:
+                s.wait_event(self.ev_begin)
+
+    def _fan_in(self) -> None:
+        for s, e in zip(self.side, self.ev_side):
+            e.record(s)
+            self.stream.wait_event(e)
 
     def step_e2e(self, i: int) -> None:
         if not self.is_sender:
@@ -134,10 +152,13 @@ class PDBenchPair:
         self.touched.add(i % self.slots)
         with torch.cuda.stream(self.stream):
             plan = self.xfer.plan(self.slot_chunks[i % self.slots], stream=self.stream, pinned=self.pinned)
-            last = self.n_layers - 1
-            for layer in range(self.n_layers):
-                self.xfer.launch(plan, layer, layer + 1, stream=self.stream, grid=self.grid,
-                                 flag_ptr=self.flag_dev if layer == last else 0, flag_value=self.seq)
+        self._fan_out()
+        lanes = [self.stream] + self.side
+        for layer in range(self.n_layers):
+            self.xfer.launch(plan, layer, layer + 1, stream=lanes[layer % len(lanes)], grid=self.grid)
+        self._fan_in()
+        with torch.cuda.stream(self.stream):
+            self.K.kvt_launch_set_flag(self.flag_dev, self.seq, self.stream.cuda_stream)
             self.status_host.copy_(self.xfer.status, non_blocking=True)
         self.stream.synchronize()
         if self.flag.value != self.seq or int(self.status_host[0]) != 0:
