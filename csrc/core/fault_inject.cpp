@@ -1,0 +1,42 @@
+#include "core/fault_inject.h"
+
+#include <atomic>
+#include <chrono>
+#include <random>
+#include <stdexcept>
+#include <thread>
+
+#include "core/envcfg.h"
+
+namespace kvx {
+
+static std::atomic<int> g_countdown{0};
+
+static bool roll() {
+  const int rate = env_debug_tx_failrate() - 1;
+  if (rate <= 0) return false;
+  thread_local std::mt19937 rng{std::random_device{}()};
+  return static_cast<int>(rng() % 100) < rate;
+}
+
+void fault_inject_arm(int throw_after_n) { g_countdown.store(throw_after_n > 0 ? throw_after_n : 0); }
+
+void fault_inject_throw() {
+  int c = g_countdown.load();
+  while (c > 0) {
+    if (g_countdown.compare_exchange_weak(c, c - 1)) {
+      if (c == 1) throw std::runtime_error("fault_inject: armed failure");
+      break;
+    }
+  }
+  if (roll()) throw std::runtime_error("fault_inject: random failure");
+}
+
+void fault_inject_sleep(int max_us) {
+  if (max_us <= 0 || !roll()) return;
+  const int delay_ms = env_debug_tx_delay_ms();
+  int us = delay_ms > 1 ? delay_ms * 1000 : max_us;
+  std::this_thread::sleep_for(std::chrono::microseconds(us));
+}
+
+}  // namespace kvx

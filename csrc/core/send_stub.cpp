@@ -1,0 +1,268 @@
+#include "core/send_stub.h"
+
+#include <arpa/inet.h>
+#include <sys/socket.h>
+#include <unistd.h>
+
+#include <cstring>
+
+#include "core/envcfg.h"
+#include "core/fault_inject.h"
+#include "plan/planner.h"
+
+namespace kvx {
+
+static constexpr uint32_t SEND_DONE_REQ = 0x20181219u;
+static constexpr uint32_t SAVE_DONE2_REQ = 0x20181223u;
+static constexpr uint32_t HAS_VER2 = 0x40000000u;
+static constexpr uint32_t CODE_INTERNALERROR = 500;
+
+std::vector<char> SendDoneNotifier::encode(uint32_t worker_tp_rank, const std::vector<const ReqSendTask*>& reqs,
+                                           int head_kind, int* resp_size) {
+  std::vector<char> buf;
+  auto put32 = [&](uint32_t v) {
+    const char* p = reinterpret_cast<const char*>(&v);
+    buf.insert(buf.end(), p, p + 4);
+  };
+  RTASSERT(worker_tp_rank < 0xffff);
+  put32(SEND_DONE_REQ);
+  put32(worker_tp_rank | HAS_VER2);
+  put32(static_cast<uint32_t>(reqs.size()));
+  for (const ReqSendTask* r : reqs) {
+    put32(r->end_tokens());
+    put32(r->state() == ReqState::OK ? 0u : CODE_INTERNALERROR);
+    put32(static_cast<uint32_t>(r->req_id().size()));
+    buf.insert(buf.end(), r->req_id().begin(), r->req_id().end());
+  }
+  *resp_size = 4;
+  if (head_kind == SEND_SAVE_DONE_HEAD_KIND) {
+    // the same body once more under the save-done header: the scheduler's connector half and
+    // its backend half each consume one copy
+    const size_t n = buf.size();
+    buf.resize(2 * n);
+    memcpy(buf.data() + n, buf.data(), n);
+    const uint32_t h = SAVE_DONE2_REQ;
+    memcpy(buf.data() + n, &h, 4);
+    *resp_size = 8;
+  }
+  return buf;
+}
+
+void SendDoneNotifier::round_trip(const std::vector<char>& buf, int resp_size) {
+  const sockaddr_in* addr = env_send_done_addr();
+  if (addr == nullptr) return;  // send-done RPC disabled
+  if (!sock_.valid()) {
+    char ip[64];
+    inet_ntop(AF_INET, &addr->sin_addr, ip, sizeof(ip));
+    int fd = tcp_connect(ip, ntohs(addr->sin_port), env_rpc_timeout_s() * 1000);
+    if (fd < 0) throw std::runtime_error("rpc send done: connect error. errno=" + std::to_string(errno));
+    sock_ = FdGuard(fd);
+  }
+  if (write_full(sock_.fd(), buf.data(), buf.size(), env_rpc_timeout_s() * 1000) != static_cast<ssize_t>(buf.size()))
+    throw std::runtime_error("rpc send done: write error. errno=" + std::to_string(errno));
+  char resp[16];
+  if (read_full(sock_.fd(), resp, static_cast<size_t>(resp_size), env_rpc_timeout_s() * 1000) != resp_size)
+    throw std::runtime_error("rpc send done: invalid response");
+}
+
+void SendDoneNotifier::notify(const std::vector<const ReqSendTask*>& reqs) {
+  if (reqs.empty()) return;
+  int resp_size = 4;
+  const std::vector<char> buf = encode(rank_, reqs, env_send_done_head_kind(), &resp_size);
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    try {
+      round_trip(buf, resp_size);
+      return;
+    } catch (const std::exception& ex) {
+      LOG(ERROR) << "do_rpc_send_done failed. ex=" << ex.what();
+      sock_.reset();  // a persistent connection may have gone stale: reconnect once
+    }
+  }
+}
+
+static bool same_dst(const WorkerInfo& a, const WorkerInfo& b) noexcept {
+  return a.inst_id == b.inst_id && a.worker_id == b.worker_id && a.engine_tp_size == b.engine_tp_size &&
+         a.worker_tp_rank == b.worker_tp_rank && a.block_sizes == b.block_sizes && a.token_sizes == b.token_sizes &&
+         a.layer_num_blocks == b.layer_num_blocks && a.num_layers == b.num_layers &&
+         a.transfer_protocols == b.transfer_protocols;
+}
+
+struct KvSendStub::Impl {
+  KvSendStub* stub;
+  WorkerInfo src_info;
+  std::shared_ptr<INamingWorkerClient> naming;
+  uint32_t start_layer, num_layers;
+  std::unique_ptr<IChannelFactory> channel_factory;
+  int cache_shape;
+  SendDoneNotifier notifier;
+
+  std::optional<WorkerInfo> dstinfo;
+  PlanEnv env;
+  PlannerChoice planner;
+  Channel ch;
+
+  std::string flush_out;
+  std::vector<std::vector<IpcBlock>> send_blocks;
+  std::vector<const ReqSendTask*> send_req, finished_req;
+  int64_t wait_us = 0, wait_and_send_us = 0, send_notify_us = 0;
+  Timepoint iter_start, send_finish;
+
+  Impl(KvSendStub* s, const WorkerInfo& src, std::shared_ptr<INamingWorkerClient> n, uint32_t sl, uint32_t nl,
+       std::unique_ptr<IChannelFactory> f, int shape)
+      : stub(s), src_info(src), naming(std::move(n)), start_layer(sl), num_layers(nl), channel_factory(std::move(f)),
+        cache_shape(shape), notifier(src.worker_tp_rank) {}
+
+  void refresh_dst_info() {
+    auto fresh = naming->get_worker_info(stub->dstid(), stub->dstworkerid());
+    if (!fresh.has_value()) {
+      if (dstinfo.has_value()) {
+        LOG(WARNING) << "refresh_dst_info:use origdstinfo=" << dstinfo->to_string();
+        return;
+      }
+      LOG(ERROR) << "refresh_dst_info:origdstinfo=none dstid=" << stub->dstid() << " dstwid=" << stub->dstworkerid();
+      throw std::runtime_error("can't find target worker");
+    }
+    if (dstinfo.has_value()) {
+      if (!same_dst(*dstinfo, *fresh)) {
+        // a different worker took over the id: keep talking to the one this stub was bound to
+        LOG(WARNING) << "TaskContext.dst_info: invalid dst: orig_dst_info=" << dstinfo->to_string()
+                     << "bad_dst_info=" << fresh->to_string();
+        return;
+      }
+      dstinfo->addr = fresh->addr;
+      dstinfo->ext = fresh->ext;
+      return;
+    }
+    dstinfo = std::move(fresh);
+    env = PlanEnv{};
+    env.src = &src_info;
+    env.dst = &*dstinfo;
+    env.cache_shape = cache_shape;
+    env.cast_bf16_to_fp8 = env_bf162fp8_conversion();
+    env.pad_last_attn_block = env_pad_last_attn_block();
+    planner = bind_planner(env);
+    LOG(INFO) << "Get valid_ranks. Src Info: valid_ranks=" << env.valid_ranks.to_string()
+              << ",engine_tp_size=" << src_info.engine_tp_size << ",engine_tp_rank=" << src_info.worker_tp_rank
+              << ",effective_kvt_tp_size=" << env.kvt_tp_size << ",effective_kvt_tp_rank=" << env.kvt_tp_rank
+              << ",planner=" << planner.name << ",Dst Info: engine_tp_size=" << dstinfo->engine_tp_size
+              << ",worker_tp_rank=" << dstinfo->worker_tp_rank;
+  }
+
+  void try_create_channel() {
+    if (ch && ch->is_active()) return;
+    refresh_dst_info();
+    env.dst = &*dstinfo;
+    ch = channel_factory->create(*dstinfo);
+    LOG(INFO) << "create channel. dst=" << dstinfo->to_string() << ";ch=" << ch.get() << ";proto=" << ch->name();
+  }
+
+  void do_send(BatchSendTask& batch, bool device_planned) {
+    wait_us = 0;
+    const bool by_record = ch->device_ordered();
+    for (uint32_t i = start_layer; i < num_layers; ++i) {
+      TimeWatch w;
+      if (by_record) batch.step->wait_layer_recorded(i); else batch.step->wait_layer_ready(i);
+      wait_us += w.get_elapse_us();
+      ch->send_data(i, batch.step.get());  // may be asynchronous
+    }
+    (void)device_planned;
+    fault_inject_throw();
+    ch->flush(flush_out);
+    send_finish = SteadyClock::now();
+    wait_and_send_us = elapse_us(iter_start, send_finish);
+  }
+
+  void do_task(BatchSendTask& batch) noexcept {
+    const size_t step_idx = batch.step->step_idx;
+    fault_inject_sleep(300 * 1000);
+    iter_start = SteadyClock::now();
+    send_finish = iter_start;
+    const int64_t queue_us = elapse_us(batch.send_ts, iter_start);
+    for (const auto& task : batch.tasks) {
+      if (task.reach_last_token) finished_req.push_back(&task);
+      if (task.new_tokens == 0) continue;            // a pure "close this request" marker
+      if (task.state() == ReqState::FAILED) continue;  // an earlier chunk already failed
+      send_req.push_back(&task);
+    }
+    if (!send_req.empty()) {
+      try {
+        try_create_channel();
+        bool device_planned = ch->register_tasks(env, send_req);
+        bool have_data = device_planned;
+        if (!device_planned) {
+          for (const ReqSendTask* t : send_req) plan_request(planner, env, *t, send_blocks);
+          have_data = !send_blocks.empty() && !send_blocks[0].empty();
+          if (have_data) ch->register_data(send_blocks, planner.kind);
+        }
+        if (have_data) do_send(batch, device_planned);
+      } catch (const std::exception& ex) {
+        LOG(ERROR) << "KVT tx_stub fail to send data. DstId=" << stub->dstid() << ",DstWorkerId=" << stub->dstworkerid()
+                   << ",StepIdx=" << step_idx << "." << batch.substepid << ',' << flush_out << ",ex=" << ex.what();
+        ch.reset();
+        for (const auto& task : batch.tasks) task.set_state(ReqState::FAILED);
+      }
+    }
+    for (const ReqSendTask* task : finished_req) {
+      if (task->state() == ReqState::INPROCESS) {
+        // a request closed without ever sending a token counts as failed
+        task->set_state(task->new_tokens == 0 ? ReqState::FAILED : ReqState::OK);
+      }
+      LOG(INFO) << "KVT tx_stub. DstId=" << stub->dstid() << ",DstWorkerId=" << stub->dstworkerid()
+                << ",StepIdx=" << step_idx << "." << batch.substepid << ",State=" << static_cast<int>(task->state())
+                << ",FinishedReq=" << task->req_id();
+    }
+    send_notify_us = 0;
+    if (!finished_req.empty()) {
+      notifier.notify(finished_req);
+      const auto now = SteadyClock::now();
+      send_notify_us = elapse_us(send_finish, now);
+      send_finish = now;
+    }
+    batch.step->update_last_send_finish_ts(send_finish);
+    LOG(INFO) << "SendStubMetrics. DstId=" << stub->dstid() << ",DstWorkerId=" << stub->dstworkerid()
+              << ",StepIdx=" << step_idx << "." << batch.substepid << ",FinishedReqSize=" << finished_req.size() << ","
+              << flush_out << ",QueueUs=" << queue_us << ",WaitUs=" << wait_us << ",WaitAndSendUs=" << wait_and_send_us
+              << ",SendNotifyUs=" << send_notify_us << ",SendFinishTs=" << send_finish.time_since_epoch().count();
+  }
+
+  void clear() noexcept {
+    flush_out.clear();
+    send_blocks.clear();
+    send_blocks.shrink_to_fit();
+    send_req.clear();
+    finished_req.clear();
+  }
+};
+
+KvSendStub::KvSendStub(InstanceId dstid, WorkerId dstworkerid, const WorkerInfo& src_info, uint32_t start_layer,
+                       uint32_t num_layers, std::unique_ptr<IChannelFactory> channel_factory,
+                       std::shared_ptr<INamingWorkerClient> naming, int cache_shape)
+    : ISendStub(std::move(dstid), dstworkerid),
+      impl_(std::make_unique<Impl>(this, src_info, std::move(naming), start_layer, num_layers,
+                                   std::move(channel_factory), cache_shape)) {}
+
+KvSendStub::~KvSendStub() = default;
+
+void KvSendStub::send_batch(BatchSendTask batch) noexcept {
+  impl_->do_task(batch);
+  impl_->clear();
+}
+
+KvSendStubFactory::KvSendStubFactory(Context* ctx, std::shared_ptr<INamingClient> naming)
+    : ctx_(ctx), naming_(std::move(naming)) {
+  if (naming_) naming_worker_ = std::make_shared<WorkerNamingClient>(naming_);
+}
+
+SendStub KvSendStubFactory::create_stub(const InstanceId& dst, WorkerId dst_worker, uint32_t start_layer,
+                                        uint32_t num_layers, std::optional<TransferProtocol> proto,
+                                        const std::optional<WorkerInfo>& dst_info) {
+  std::shared_ptr<INamingWorkerClient> nw;
+  if (dst_info.has_value()) nw = std::make_shared<FakeNamingWorkerClient>(*dst_info);
+  else nw = naming_worker_;
+  if (!nw) throw std::runtime_error("no naming service and no destination info in the request");
+  const int shape = ctx_->worker_info().cache_shape_or(env_cache_shape());
+  return std::make_unique<KvSendStub>(dst, dst_worker, ctx_->worker_info(), start_layer, num_layers,
+                                      std::make_unique<ChannelFactory>(ctx_, proto), std::move(nw), shape);
+}
+
+}  // namespace kvx

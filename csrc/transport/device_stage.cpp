@@ -1,0 +1,134 @@
+#include "transport/device_stage.h"
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+
+#include "core/envcfg.h"
+#include "core/types.h"
+#include "kernels/kvt_kernels.h"
+
+namespace kvx {
+
+void cuda_check(int err, const char* what) {
+  if (err != 0) {
+    throw KVTransferException(ErrorKind::CUDA, std::string(what) + ": " +
+                                                   cudaGetErrorString(static_cast<cudaError_t>(err)));
+  }
+}
+
+PinnedBuffer::~PinnedBuffer() { release(); }
+
+void PinnedBuffer::release() {
+  if (host_ == nullptr) return;
+  if (pinned_) cudaFreeHost(host_); else free(host_);
+  host_ = nullptr;
+  dev_ = 0;
+  cap_ = 0;
+}
+
+char* PinnedBuffer::reserve(size_t bytes, bool pinned) {
+  if (bytes <= cap_ && pinned == pinned_ && host_ != nullptr) return host_;
+  release();
+  size_t cap = std::max<size_t>(bytes, 4096);
+  cap = (cap + (cap >> 2) + 4095) & ~size_t{4095};
+  pinned_ = pinned;
+  if (pinned) {
+    void* h = nullptr;
+    cuda_check(cudaHostAlloc(&h, cap, cudaHostAllocMapped | cudaHostAllocPortable), "cudaHostAlloc");
+    void* d = nullptr;
+    cuda_check(cudaHostGetDevicePointer(&d, h, 0), "cudaHostGetDevicePointer");
+    host_ = static_cast<char*>(h);
+    dev_ = reinterpret_cast<uint64_t>(d);
+  } else {
+    host_ = static_cast<char*>(malloc(cap));
+    if (host_ == nullptr) throw std::bad_alloc();
+  }
+  cap_ = cap;
+  return host_;
+}
+
+DeviceStage::DeviceStage(int device) : device_(device) {
+  cuda_check(cudaSetDevice(device_), "cudaSetDevice");
+  cudaStream_t s;
+  cuda_check(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking), "cudaStreamCreate");
+  stream_ = s;
+  void* st = nullptr;
+  cuda_check(cudaMalloc(&st, 16), "cudaMalloc(status)");
+  d_status_ = static_cast<uint32_t*>(st);
+  cuda_check(cudaMemsetAsync(d_status_, 0, 16, s), "cudaMemsetAsync");
+  h_status_.reserve(16, true);
+}
+
+DeviceStage::~DeviceStage() {
+  cudaSetDevice(device_);
+  if (stream_ != nullptr) {
+    cudaStreamSynchronize(static_cast<cudaStream_t>(stream_));
+    cudaStreamDestroy(static_cast<cudaStream_t>(stream_));
+  }
+  if (d_triples_ != nullptr) cudaFree(d_triples_);
+  if (d_status_ != nullptr) cudaFree(d_status_);
+}
+
+void DeviceStage::wait_event(void* event) {
+  if (event == nullptr) return;
+  cuda_check(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream_), static_cast<cudaEvent_t>(event), 0),
+             "cudaStreamWaitEvent");
+}
+
+void DeviceStage::enqueue(uint64_t src_base, uint64_t dst_base, const std::vector<Triple>& triples, uint64_t src_cap,
+                          uint64_t dst_cap, int grid_ctas) {
+  if (triples.empty()) return;
+  cuda_check(cudaSetDevice(device_), "cudaSetDevice");
+  cudaStream_t s = static_cast<cudaStream_t>(stream_);
+  const size_t n = triples.size();
+  // Descriptors of all launches since the last sync stay resident: the pinned staging must not
+  // be overwritten while an upload is in flight, so grow-and-sync when it would not fit.
+  if (used_ + n > d_cap_) {
+    if (used_ > 0) sync();
+    if (n > d_cap_) {
+      if (d_triples_ != nullptr) cuda_check(cudaFree(d_triples_), "cudaFree");
+      d_cap_ = std::max<size_t>(n + n / 2, 4096);
+      void* p = nullptr;
+      cuda_check(cudaMalloc(&p, d_cap_ * sizeof(Triple)), "cudaMalloc(triples)");
+      d_triples_ = static_cast<uint64_t*>(p);
+      h_triples_.reserve(d_cap_ * sizeof(Triple), true);
+    }
+  }
+  static_assert(sizeof(Triple) == 24, "triples are 3 x u64");
+  char* h = h_triples_.data() + used_ * sizeof(Triple);
+  memcpy(h, triples.data(), n * sizeof(Triple));
+  uint64_t* d = d_triples_ + used_ * 3;
+  cuda_check(cudaMemcpyAsync(d, h, n * sizeof(Triple), cudaMemcpyHostToDevice, s), "cudaMemcpyAsync(triples)");
+  const size_t max_per_launch = env_kernel_copy_max_block_num();
+  int grid = grid_ctas;
+  if (grid <= 0) {
+    const double usage = env_kernel_copy_sm_usage();
+    grid = std::max(1, static_cast<int>(kvt_sm_count(device_) * usage));
+  }
+  for (size_t off = 0; off < n; off += max_per_launch) {
+    const uint32_t cnt = static_cast<uint32_t>(std::min(max_per_launch, n - off));
+    cuda_check(kvt_launch_copy_blocks(src_base, dst_base, d + off * 3, cnt, src_cap, dst_cap, d_status_, grid, s),
+               "kvt_launch_copy_blocks");
+  }
+  used_ += n;
+}
+
+void DeviceStage::sync() {
+  cuda_check(cudaSetDevice(device_), "cudaSetDevice");
+  cudaStream_t s = static_cast<cudaStream_t>(stream_);
+  cuda_check(cudaMemcpyAsync(h_status_.data(), d_status_, 8, cudaMemcpyDeviceToHost, s), "cudaMemcpyAsync(status)");
+  cuda_check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+  used_ = 0;
+  uint32_t st[2];
+  memcpy(st, h_status_.data(), 8);
+  if (st[0] != 0) {
+    cudaMemsetAsync(d_status_, 0, 16, s);
+    throw KVTransferException(ErrorKind::CUDA, "copy kernel rejected descriptor " + std::to_string(st[1]) +
+                                                   " (status " + std::to_string(st[0]) + ")");
+  }
+}
+
+}  // namespace kvx

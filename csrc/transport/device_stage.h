@@ -1,0 +1,66 @@
+// Descriptor-driven copies on a CUDA stream, shared by the host-driven transports and the
+// generic (any cache shape) path of the NVLink transport.  One DeviceStage belongs to one
+// thread: it owns a non-blocking stream, a device array for {src_off, dst_off, len} triples,
+// pinned staging for them and a status word, and turns a list of triples into one or more
+// launches of kvt_copy_blocks (at most BLLM_KVTRANS_KERNEL_COPY_MAX_BLOCK_NUM descriptors per
+// launch, like the reference's batching, kvtransfer/src/copy_kernels.cpp:770-823).
+#pragma once
+#include <cstdint>
+#include <string>
+#include <vector>
+
+namespace kvx {
+
+struct Triple {
+  uint64_t src_off, dst_off, len;
+};
+
+// Pinned (and device-mapped) host buffer that grows on demand.
+class PinnedBuffer {
+ public:
+  PinnedBuffer() = default;
+  ~PinnedBuffer();
+  PinnedBuffer(const PinnedBuffer&) = delete;
+  char* reserve(size_t bytes, bool pinned);  // keeps contents only when no reallocation happens
+  char* data() const { return host_; }
+  uint64_t device_ptr() const { return dev_; }
+  size_t capacity() const { return cap_; }
+  bool pinned() const { return pinned_; }
+
+ private:
+  void release();
+  char* host_{nullptr};
+  uint64_t dev_{0};
+  size_t cap_{0};
+  bool pinned_{false};
+};
+
+class DeviceStage {
+ public:
+  explicit DeviceStage(int device);
+  ~DeviceStage();
+  DeviceStage(const DeviceStage&) = delete;
+  // Enqueue the copy; does not wait.
+  void enqueue(uint64_t src_base, uint64_t dst_base, const std::vector<Triple>& triples, uint64_t src_cap,
+               uint64_t dst_cap, int grid_ctas = 0);
+  // Wait for everything enqueued and throw KVTransferException if the kernel flagged a descriptor.
+  void sync();
+  void* stream() const { return stream_; }
+  int device() const { return device_; }
+  // Make the stream wait for a cudaEvent_t before later work (no host wait).
+  void wait_event(void* event);
+
+ private:
+  int device_;
+  void* stream_{nullptr};
+  uint64_t* d_triples_{nullptr};
+  size_t d_cap_{0};       // triples
+  size_t used_{0};        // triples enqueued since the last sync
+  uint32_t* d_status_{nullptr};
+  PinnedBuffer h_triples_;
+  PinnedBuffer h_status_;
+};
+
+void cuda_check(int err, const char* what);  // throws KVTransferException(CUDA)
+
+}  // namespace kvx
