@@ -1,0 +1,514 @@
+"""Engine tests that need no GPU: codecs, naming, the client/step/stub pipeline over the TCP and
+shared-memory transports with host-resident caches, failure handling and send-done reporting.
+
+The scenarios mirror what the reference covers with fakes in kvtransfer/tests/client_test.cpp,
+send_stub_test.cpp (FaultTolerantTest, CreateChannelFaultTolerantTest), naming_test.cpp and
+common_test.cpp - here the real transports run, between threads of one process and between
+two processes.
+"""
+import multiprocessing as mp
+import os
+import random
+import socket
+import struct
+import threading
+import time
+
+import pytest
+import torch
+
+os.environ.setdefault("BLLM_KVTRANS_QUIET_ENV", "1")
+
+from llumnix_kv_b200.kv_transfer_impl import (KVTransferClient, KVTransferProtocolType as PT, KVTransferServer,
+                                              ReqMeta, encode_send_done)
+
+L, H, D, T, NB = 2, 8, 128, 16, 64
+TOK = 2 * H * D * 2
+BLK = TOK * T
+
+
+def make_cache(seed=None):
+    if seed is None:
+        return [torch.zeros(2, NB, T, H, D, dtype=torch.float16) for _ in range(L)]
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randn(2, NB, T, H, D, dtype=torch.float16, generator=g) for _ in range(L)]
+
+
+def check_tokens(src, dst, sb, db, lo, hi):
+    for layer in range(L):
+        for t in range(lo, hi):
+            assert torch.equal(src[layer][:, sb[t // T], t % T], dst[layer][:, db[t // T], t % T]), (layer, t)
+
+
+class SendDoneSink:
+    """Stands in for the scheduler's RPC port: records every send-done message."""
+
+    def __init__(self):
+        self.sock = socket.socket()
+        self.sock.bind(("127.0.0.1", 0))
+        self.sock.listen(16)
+        self.port = self.sock.getsockname()[1]
+        self.msgs = []
+        self.stop = False
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
+
+    def _recvn(self, c, n):
+        buf = b""
+        while len(buf) < n:
+            chunk = c.recv(n - len(buf))
+            if not chunk:
+                raise EOFError
+            buf += chunk
+        return buf
+
+    def _serve(self, c):
+        try:
+            while True:
+                head, rank, n = struct.unpack("=III", self._recvn(c, 12))
+                reqs = []
+                for _ in range(n):
+                    plen, code, rlen = struct.unpack("=III", self._recvn(c, 12))
+                    reqs.append((self._recvn(c, rlen).decode(), plen, code))
+                self.msgs.append((head, rank & 0xFFFF, bool(rank & 0x40000000), reqs))
+                c.sendall(struct.pack("=I", 0x91218102))
+        except (EOFError, OSError):
+            pass
+
+    def _run(self):
+        while not self.stop:
+            try:
+                c, _ = self.sock.accept()
+            except OSError:
+                return
+            threading.Thread(target=self._serve, args=(c,), daemon=True).start()
+
+    def wait_for(self, n, timeout=10):
+        t0 = time.time()
+        while len(self.msgs) < n and time.time() - t0 < timeout:
+            time.sleep(0.01)
+        return list(self.msgs)
+
+    def close(self):
+        self.stop = True
+        self.sock.close()
+
+
+@pytest.fixture
+def sink(ops):
+    s = SendDoneSink()
+    os.environ["BLLM_KVTRANS_SEND_DONE_ADDR"] = f"127.0.0.1:{s.port}"
+    ops.envcfg_reset_for_test()
+    yield s
+    s.close()
+    os.environ.pop("BLLM_KVTRANS_SEND_DONE_ADDR", None)
+    ops.envcfg_reset_for_test()
+
+
+# ---- codecs ------------------------------------------------------------------------------------
+def test_worker_info_round_trip_and_back_compat(ops):
+    W = ops.WorkerInfo
+    s = "inst|0|2,3,2,1,65536|4096,4096|256,100,32,6,16,0,1,0,10.0.0.7"
+    w = W.from_string(s)
+    assert (w.inst_id, w.worker_id, w.engine_tp_size, w.worker_tp_rank) == ("inst|0|2", 3, 2, 1)
+    assert w.block_sizes == [65536, 4096] and w.token_sizes == [4096, 256]
+    assert (w.layer_num_blocks, w.num_layers, w.transfer_protocols) == (100, 32, 6)
+    assert (w.attn_kernel_blk_ntpb, w.indexer_blk_ntpb, w.attn_pack_size, w.kda_page_stride, w.addr) == (16, 0, 1, 0, "10.0.0.7")
+    assert w.to_string() == s
+    # 11 fields: legacy without attn_pack_size / addr
+    w = W.from_string("a,0,1,0,16384,1024,8,4,2,16,0")
+    assert (w.attn_pack_size, w.kda_page_stride, w.addr) == (1, 0, "")
+    # 12 fields: numeric -> attn_pack_size, otherwise address
+    assert W.from_string("a,0,1,0,16384,1024,8,4,2,16,0,2").attn_pack_size == 2
+    assert W.from_string("a,0,1,0,16384,1024,8,4,2,16,0,10.1.2.3").addr == "10.1.2.3"
+    # 13 fields: {pack, addr} or {pack, stride}
+    w = W.from_string("a,0,1,0,16384,1024,8,4,2,16,0,2,fe80::1")
+    assert (w.attn_pack_size, w.addr) == (2, "fe80::1")
+    w = W.from_string("a,0,1,0,16384,1024,8,4,2,16,0,2,40960")
+    assert (w.attn_pack_size, w.kda_page_stride) == (2, 40960)
+    # extension field survives a round trip and is ignored by the positional rules
+    w = W.from_string("a,0,1,0,16384,1024,8,4,2,16,0,1,0,10.0.0.1,x:dev=3;port=4000;shape=5")
+    assert w.ext == {"dev": "3", "port": "4000", "shape": "5"} and w.addr == "10.0.0.1"
+    assert W.from_string(w.to_string()).ext == w.ext
+    for bad in ("a,b", "a,0,1,0,1,1,1,1,1,1,1,1,1,1,1,1"):
+        with pytest.raises(Exception):
+            W.from_string(bad)
+
+
+def test_send_done_wire_format(ops):
+    buf, resp = ops.encode_send_done(3, [("req-a", 100, True), ("req-bb", 7, False)], 2)
+    assert resp == 8
+    expect = encode_send_done(3, [("req-a", 100, 0), ("req-bb", 7, 500)], 2)
+    assert buf == expect
+    head, rank, n = struct.unpack_from("=III", buf, 0)
+    assert head == 0x20181219 and rank == (3 | 0x40000000) and n == 2
+    half = len(buf) // 2
+    assert struct.unpack_from("=I", buf, half)[0] == 0x20181223 and buf[4:half] == buf[half + 4:]
+    buf1, resp1 = ops.encode_send_done(0, [("r", 1, True)], 1)
+    assert resp1 == 4 and len(buf1) == 12 + 12 + 1
+
+
+# ---- naming ------------------------------------------------------------------------------------
+def test_file_naming(ops, tmp_path):
+    os.environ["BLLM_KVTRANS_FSNAMING_KEEPALIVE_S"] = "1"
+    os.environ["BLLM_KVTRANS_FSNAMING_TOLERATE_S"] = "3"
+    ops.envcfg_reset_for_test()
+    a = ops.connect_naming("instA", f"file:{tmp_path}")
+    b = ops.connect_naming("instB", f"file:{tmp_path}")
+    a.store("worker_0", "hello")
+    a.store("worker_1", "world")
+    a.store("other", "x")
+    assert b.get("instA", "worker_0") == "hello"
+    assert sorted(b.search("instA", "worker_")) == ["hello", "world"]
+    assert b.get("instA", "missing") is None and b.get("nobody", "worker_0") is None
+    assert sorted(b.list()) == ["instA", "instB"]
+    a.remove("other")
+    assert b.get("instA", "other") is None
+    with pytest.raises(Exception):
+        a.store("bad/key", "v")
+    # a stale instance (old timestamp, nobody refreshing it) drops out of the listing
+    stale = tmp_path / "ghost"
+    stale.mkdir()
+    (stale / "_timestamp_").write_text(str(int(time.time()) - 100) + "\n")
+    time.sleep(2.1)
+    assert "ghost" not in b.list() and "instA" in b.list()
+    ts1 = int(b.get("instA", "_timestamp_"))
+    time.sleep(1.3)
+    assert int(b.get("instA", "_timestamp_")) >= ts1
+
+
+def test_tcpstore_and_mem_naming(ops):
+    srv = ops.KvStoreServer()
+    port = srv.start(0)
+    try:
+        a = ops.connect_naming("i1", f"tcpstore:127.0.0.1:{port}")
+        b = ops.connect_naming("i2", f"tcpstore://127.0.0.1:{port}")
+        a.store("worker_3", "w3")
+        a.store("endpoint0", "e0")
+        assert b.get("i1", "worker_3") == "w3" and b.get("i1", "nope") is None
+        assert b.search("i1", "worker_") == ["w3"]
+        assert sorted(b.list()) == ["i1", "i2"]
+        a.remove("worker_3")
+        assert b.get("i1", "worker_3") is None
+    finally:
+        srv.stop()
+    m1 = ops.connect_naming("x", "mem:space1")
+    m2 = ops.connect_naming("y", "mem:space1")
+    m1.store("k", "v")
+    assert m2.get("x", "k") == "v" and m2.list() == ["x"]
+
+
+def test_eas_document_parser(ops):
+    ok, ver, doc = ops.parse_eas_document(
+        '{"version": 7, "instances": {"p0": {"worker_0": "a,b", "endpoint0": "1.2.3.4:5"}, "d0": {}}}')
+    assert ok and ver == 7 and doc == {"p0": {"worker_0": "a,b", "endpoint0": "1.2.3.4:5"}, "d0": {}}
+    assert not ops.parse_eas_document('{"version": ')[0]
+
+
+def test_eas_naming_over_http(ops):
+    import http.server
+
+    state = {"version": 1, "instances": {"d0": {"worker_0": "first"}}}
+
+    class Handler(http.server.BaseHTTPRequestHandler):
+        def do_GET(self):
+            import json
+            body = json.dumps(state).encode()
+            self.send_response(200)
+            self.send_header("Content-Length", str(len(body)))
+            self.end_headers()
+            self.wfile.write(body)
+
+        def log_message(self, *a):
+            pass
+
+    httpd = http.server.HTTPServer(("127.0.0.1", 0), Handler)
+    threading.Thread(target=httpd.serve_forever, daemon=True).start()
+    try:
+        c = ops.connect_naming("me", f"eas:127.0.0.1:{httpd.server_port}/discovery")
+        assert c.get("d0", "worker_0") == "first" and c.list() == ["d0"]
+        state["version"] = 2
+        state["instances"]["d1"] = {"worker_0": "second"}
+        time.sleep(1.1)  # the document is re-fetched at most once a second
+        assert c.get("d1", "worker_0") == "second" and sorted(c.list()) == ["d0", "d1"]
+        c.store("mine", "local")  # the service is read-only: own keys live in an overlay
+        assert c.get("me", "mine") == "local"
+    finally:
+        httpd.shutdown()
+
+
+# ---- transfers ---------------------------------------------------------------------------------
+@pytest.mark.parametrize("proto", [PT.TCP, PT.SHM])
+def test_config1_ten_requests_bit_exact(proto, sink):
+    """BASELINE config 1 inside one process: 2 layers, 8 KV heads, head_dim 128, block 16, 64 blocks,
+    fp16 N(0,1), NHD; 10 requests with random block tables, verified bit-exactly."""
+    src, dst = make_cache(1), make_cache()
+    srv = KVTransferServer("D|0|1", 1, 0, 0, BLK, TOK, "fake://", dst, [proto], num_kv_heads=H, cache_shape=2)
+    cli = KVTransferClient("P|0|1", 1, 0, 0, BLK, TOK, "fake://", src, [proto], num_kv_heads=H, cache_shape=2)
+    try:
+        rng = random.Random(7)
+        done = []
+        stepid = 1024
+        for batch in range(5):
+            free_s, free_d = list(range(NB)), list(range(NB))
+            rng.shuffle(free_s)
+            rng.shuffle(free_d)
+            reqs = []
+            for r in range(2):
+                nb = rng.randint(4, 32)
+                sb, db = [free_s.pop() for _ in range(nb)], [free_d.pop() for _ in range(nb)]
+                ntok = nb * T - rng.randint(0, T - 1)
+                rid = f"req-{batch}-{r}"
+                reqs.append((rid, sb, db, ntok))
+                cli.submit_req_send2("D|0|1", 0, rid, 0, ntok, True, sb, db, srv.worker_info(), stepid=stepid)
+            cli.start_send_step(stepid, 1)
+            for layer in range(L):
+                cli.record_event(layer)
+            cli.flush_send_step()
+            cli.drain()
+            for rid, sb, db, ntok in reqs:
+                check_tokens(src, dst, sb, db, 0, ntok)
+                done.append(rid)
+            stepid += 1
+        msgs = sink.wait_for(10)
+        got = {r[0]: r[2] for m in msgs if m[0] == 0x20181219 for r in m[3]}
+        assert got == {rid: 0 for rid in done}
+    finally:
+        srv.stop()
+
+
+def test_chunked_prefill_deltas_and_unknown_delta(sink):
+    src, dst = make_cache(2), make_cache()
+    srv = KVTransferServer("D|0|1", 1, 0, 0, BLK, TOK, "fake://", dst, [PT.TCP], num_kv_heads=H, cache_shape=2)
+    cli = KVTransferClient("P|0|1", 1, 0, 0, BLK, TOK, "fake://", src, [PT.TCP], num_kv_heads=H, cache_shape=2)
+    try:
+        sb, db = [5, 9, 11, 2], [40, 41, 3, 8]
+        total = 3 * T + 5
+        chunks = [(0, 20, False), (20, 21, False), (41, total - 41, True)]
+        for i, (seen, new, last) in enumerate(chunks):
+            if i == 0:
+                cli.submit_req_send2("D|0|1", 0, "chunky", seen, new, last, sb, db, srv.worker_info(), stepid=2000 + i)
+            else:
+                cli.submit_delta_send("chunky", seen, new, last, stepid=2000 + i)
+            cli.submit_delta_send("never-submitted", 0, 4, True, stepid=2000 + i)  # warns and is ignored
+            cli.start_send_step(2000 + i, 1)
+            for layer in range(L):
+                cli.record_event(layer)
+            cli.flush_send_step()
+            cli.drain()
+            check_tokens(src, dst, sb, db, 0, seen + new)
+            # nothing beyond the chunk has been written yet
+            if not last:
+                nxt = seen + new
+                assert float(dst[0][:, db[nxt // T], nxt % T].abs().sum()) == 0.0
+        msgs = sink.wait_for(1)
+        sd = [m for m in msgs if m[0] == 0x20181219]
+        assert len(sd) == 1 and sd[0][3] == [("chunky", total, 0)]
+        # an empty step returns without opening anything
+        cli.start_send_step(3000, 0)
+        cli.flush_send_step()
+    finally:
+        srv.stop()
+
+
+def test_freeze_send_and_substeps(sink):
+    src, dst = make_cache(3), make_cache()
+    srv = KVTransferServer("D|0|1", 1, 0, 0, BLK, TOK, "fake://", dst, [PT.SHM], num_kv_heads=H, cache_shape=2)
+    cli = KVTransferClient("P|0|1", 1, 0, 0, BLK, TOK, "fake://", src, [PT.SHM], num_kv_heads=H, cache_shape=2)
+    try:
+        def meta(rid, sb, db, n):
+            m = ReqMeta()
+            m.dst_inst, m.dst_worker, m.reqid, m.seen_tokens, m.new_tokens = "D|0|1", 0, rid, 0, n
+            m.src_block_ids, m.dst_block_ids, m.dst_worker_info = [sb], [db], srv.worker_info()
+            return m
+        # freeze: data complete, no layer events involved
+        cli.start_req_send([meta("frozen", [1, 2], [3, 4], 30)], 100, 0)
+        cli.drain()
+        check_tokens(src, dst, [1, 2], [3, 4], 0, 30)
+        # substep for a step that has not started yet: parked, sent when the step opens
+        cli.start_send_substep(200, 1, [meta("parked", [5], [6], 10)])
+        cli.drain()
+        assert float(dst[0][:, 6].abs().sum()) == 0.0
+        cli.start_send_step(200, 1)
+        # substep attached to the running step
+        cli.start_send_substep(200, 2, [meta("attached", [7], [8], 16)])
+        for layer in range(L):
+            cli.record_event(layer)
+        cli.flush_send_step()
+        cli.drain()
+        check_tokens(src, dst, [5], [6], 0, 10)
+        check_tokens(src, dst, [7], [8], 0, 16)
+        # substep for a step that is already over: becomes its own frozen step
+        cli.start_send_substep(200, 3, [meta("late", [9], [10], 16)])
+        cli.drain()
+        check_tokens(src, dst, [9], [10], 0, 16)
+        names = sorted(r[0] for m in sink.wait_for(4) if m[0] == 0x20181219 for r in m[3])
+        assert names == ["attached", "frozen", "late", "parked"]
+    finally:
+        srv.stop()
+
+
+def test_step_protocol_violations(ops):
+    src = make_cache(4)
+    cli = KVTransferClient("P|0|1", 1, 0, 0, BLK, TOK, "fake://", src, [PT.TCP], num_kv_heads=H, cache_shape=2)
+    cli.record_event(0)  # before any step: ignored (warm-up)
+    cli.start_send_step(10, 1)
+    with pytest.raises(RuntimeError):
+        cli.start_send_step(11, 1)
+    cli.flush_send_step()
+    cli.flush_send_step()  # idempotent once closed
+    with pytest.raises(Exception):
+        cli.submit_req_send2("D", 0, "r", 0, 0, True, [1], [1], None)  # new_tokens must be positive
+    cli.submit_req_send2("D", 0, "r", 0, 4, False, [1], [1], None, stepid=20)
+    with pytest.raises(Exception):
+        cli.submit_req_send2("D", 0, "r2", 0, 4, False, [1], [1], None, stepid=21)  # one step id per step
+
+
+def test_failure_marks_batch_failed_and_next_batch_recovers(ops, sink):
+    src, dst = make_cache(5), make_cache()
+    srv = KVTransferServer("D|0|1", 1, 0, 0, BLK, TOK, "fake://", dst, [PT.TCP], num_kv_heads=H, cache_shape=2)
+    cli = KVTransferClient("P|0|1", 1, 0, 0, BLK, TOK, "fake://", src, [PT.TCP], num_kv_heads=H, cache_shape=2)
+    try:
+        def step(stepid, reqs):
+            for rid, sb, db, n, last in reqs:
+                cli.submit_req_send2("D|0|1", 0, rid, 0, n, last, sb, db, srv.worker_info(), stepid=stepid)
+            cli.start_send_step(stepid, 1)
+            for layer in range(L):
+                cli.record_event(layer)
+            cli.flush_send_step()
+            cli.drain()
+        # first batch connects fine
+        step(1, [("warm", [1], [1], 8, True)])
+        # the 1st fault point hit from now on throws: the send of this batch fails after connect
+        ops.fault_inject_arm(1)
+        step(2, [("a", [2], [2], 16, True), ("b", [3], [3], 10, False)])
+        ops.fault_inject_arm(0)
+        # a later chunk of the failed request stays failed; a new request on a fresh channel works
+        cli.submit_delta_send("b", 10, 6, True, stepid=3)
+        step(3, [("c", [4], [4], 16, True)])
+        check_tokens(src, dst, [4], [4], 0, 16)
+        codes = {r[0]: r[2] for m in sink.wait_for(3) if m[0] == 0x20181219 for r in m[3]}
+        assert codes == {"warm": 0, "a": 500, "b": 500, "c": 0}
+    finally:
+        ops.fault_inject_arm(0)
+        srv.stop()
+
+
+def test_unreachable_destination_fails_requests_not_the_engine(ops, sink):
+    src = make_cache(6)
+    cli = KVTransferClient("P|0|1", 1, 0, 0, BLK, TOK, "fake://", src, [PT.TCP], num_kv_heads=H, cache_shape=2)
+    os.environ["BLLM_KVTRANS_RPC_TIMEOUT_S"] = "1"
+    ops.envcfg_reset_for_test()
+    ghost = ops.WorkerInfo.from_string(f"D|0|1,0,1,0,{BLK},{TOK},{NB},{L},2,16,0,1,0,127.0.0.1,x:port=1;shape=2")
+    cli.submit_req_send2("D|0|1", 0, "lost", 0, 8, True, [1], [1], ghost.to_string(), stepid=1)
+    cli.start_send_step(1, 1)
+    for layer in range(L):
+        cli.record_event(layer)
+    cli.flush_send_step()
+    cli.drain()
+    codes = {r[0]: r[2] for m in sink.wait_for(1) if m[0] == 0x20181219 for r in m[3]}
+    assert codes == {"lost": 500}
+    os.environ.pop("BLLM_KVTRANS_RPC_TIMEOUT_S")
+    ops.envcfg_reset_for_test()
+
+
+def test_target_lru_shrink(ops):
+    src = make_cache(7)
+    dsts = [make_cache() for _ in range(3)]
+    srvs = [KVTransferServer(f"D{i}|0|1", 1, 0, 0, BLK, TOK, "fake://", dsts[i], [PT.TCP], num_kv_heads=H,
+                             cache_shape=2) for i in range(3)]
+    cli = KVTransferClient("P|0|1", 1, 0, 0, BLK, TOK, "fake://", src, [PT.TCP], num_kv_heads=H, cache_shape=2)
+    try:
+        for i, s in enumerate(srvs):
+            cli.submit_req_send2(f"D{i}|0|1", 0, f"r{i}", 0, 8, True, [i + 1], [i + 1], s.worker_info(), stepid=1)
+        cli.start_send_step(1, 1)
+        for layer in range(L):
+            cli.record_event(layer)
+        cli.flush_send_step()
+        cli.drain()
+        assert cli._c.target_size() == 3
+        cli._c.target_try_shrink(1)
+        assert cli._c.target_size() == 1
+        # evicted targets are recreated on demand
+        cli.submit_req_send2("D0|0|1", 0, "again", 0, 8, True, [9], [9], srvs[0].worker_info(), stepid=2)
+        cli.start_send_step(2, 1)
+        for layer in range(L):
+            cli.record_event(layer)
+        cli.flush_send_step()
+        cli.drain()
+        check_tokens(src, dsts[0], [9], [9], 0, 8)
+    finally:
+        for s in srvs:
+            s.stop()
+
+
+def test_receiver_rejects_out_of_range_destination(ops, sink):
+    """A sender whose idea of the destination is too big is refused by the receiver's own check."""
+    src, dst = make_cache(8), make_cache()
+    srv = KVTransferServer("D|0|1", 1, 0, 0, BLK, TOK, "fake://", dst, [PT.TCP], num_kv_heads=H, cache_shape=2)
+    cli = KVTransferClient("P|0|1", 1, 0, 0, BLK, TOK, "fake://", src, [PT.TCP], num_kv_heads=H, cache_shape=2)
+    try:
+        lie = ops.WorkerInfo.from_string(srv.worker_info())
+        lie.layer_num_blocks = NB * 4
+        cli.submit_req_send2("D|0|1", 0, "oob", 0, 8, True, [1], [NB * 2], lie.to_string(), stepid=1)
+        cli.start_send_step(1, 1)
+        for layer in range(L):
+            cli.record_event(layer)
+        cli.flush_send_step()
+        cli.drain()
+        codes = {r[0]: r[2] for m in sink.wait_for(1) if m[0] == 0x20181219 for r in m[3]}
+        assert codes == {"oob": 500}
+        assert all(float(d.abs().sum()) == 0.0 for d in dst)
+    finally:
+        srv.stop()
+
+
+# ---- two processes ---------------------------------------------------------------------------------
+def _decode_proc(naming_dir, proto_name, ready, go, result):
+    os.environ["BLLM_KVTRANS_QUIET_ENV"] = "1"
+    from llumnix_kv_b200.kv_transfer_impl import KVTransferProtocolType as P2, KVTransferServer as Srv
+    dst = make_cache()
+    srv = Srv("D|0|1", 1, 0, 0, BLK, TOK, f"file:{naming_dir}", dst, [P2[proto_name]], num_kv_heads=H, cache_shape=2)
+    ready.set()
+    go.wait(60)
+    result.put([d.clone() for d in dst])
+    srv.stop()
+
+
+@pytest.mark.parametrize("proto", ["TCP", "SHM"])
+def test_config1_two_processes_with_file_naming(proto, tmp_path, ops):
+    ctx = mp.get_context("spawn")
+    ready, go, result = ctx.Event(), ctx.Event(), ctx.Queue()
+    p = ctx.Process(target=_decode_proc, args=(str(tmp_path), proto, ready, go, result))
+    p.start()
+    try:
+        assert ready.wait(120)
+        src = make_cache(11)
+        # no destination info in the request: resolved through the naming directory
+        cli = KVTransferClient("P|0|1", 1, 0, 0, BLK, TOK, f"file:{tmp_path}", src, [PT[proto]], num_kv_heads=H,
+                               cache_shape=2)
+        rng = random.Random(3)
+        free_s, free_d = list(range(NB)), list(range(NB))
+        rng.shuffle(free_s)
+        rng.shuffle(free_d)
+        reqs = []
+        for r in range(10):
+            nb = rng.randint(4, 6)
+            sb, db = [free_s.pop() for _ in range(nb)], [free_d.pop() for _ in range(nb)]
+            ntok = nb * T - rng.randint(0, T - 1)
+            reqs.append((sb, db, ntok))
+            cli.submit_req_send2("D|0|1", 0, f"r{r}", 0, ntok, True, sb, db, None, stepid=1)
+        cli.start_send_step(1, 1)
+        for layer in range(L):
+            cli.record_event(layer)
+        cli.flush_send_step()
+        cli.drain()
+        go.set()
+        dst = result.get(timeout=60)
+        for sb, db, ntok in reqs:
+            check_tokens(src, dst, sb, db, 0, ntok)
+    finally:
+        go.set()
+        p.join(30)
+        if p.is_alive():
+            p.kill()
