@@ -308,16 +308,16 @@ void bind_engine(py::module_& m) {
   bind_worker_info(m);
 
   py::class_<INamingClient, std::shared_ptr<INamingClient>>(m, "NamingClient")
-      .def("get", &INamingClient::get)
-      .def("search", &INamingClient::search)
-      .def("store", &INamingClient::store)
-      .def("remove", &INamingClient::remove)
-      .def("list", [](INamingClient& c) { return c.list(); })
+      .def("get", &INamingClient::get, py::call_guard<py::gil_scoped_release>())
+      .def("search", &INamingClient::search, py::call_guard<py::gil_scoped_release>())
+      .def("store", &INamingClient::store, py::call_guard<py::gil_scoped_release>())
+      .def("remove", &INamingClient::remove, py::call_guard<py::gil_scoped_release>())
+      .def("list", [](INamingClient& c) { return c.list(); }, py::call_guard<py::gil_scoped_release>())
       .def("get_schema", &INamingClient::get_schema)
       .def_readonly("inst_id", &INamingClient::inst_id);
   m.def("connect_naming", [](const std::string& name, const std::string& url) {
     return NamingManager::instance().connect_naming(name, url);
-  });
+  }, py::call_guard<py::gil_scoped_release>());
   py::class_<KvStoreServer>(m, "KvStoreServer")
       .def(py::init<>())
       .def("start", &KvStoreServer::start, py::arg("port") = 0, py::call_guard<py::gil_scoped_release>())

@@ -471,7 +471,7 @@ def _decode_proc(naming_dir, proto_name, ready, go, result):
     srv = Srv("D|0|1", 1, 0, 0, BLK, TOK, f"file:{naming_dir}", dst, [P2[proto_name]], num_kv_heads=H, cache_shape=2)
     ready.set()
     go.wait(60)
-    result.put([d.clone() for d in dst])
+    result.put([d.numpy().copy() for d in dst])  # by value: the process exits right after
     srv.stop()
 
 
@@ -504,7 +504,7 @@ def test_config1_two_processes_with_file_naming(proto, tmp_path, ops):
         cli.flush_send_step()
         cli.drain()
         go.set()
-        dst = result.get(timeout=60)
+        dst = [torch.from_numpy(a) for a in result.get(timeout=60)]
         for sb, db, ntok in reqs:
             check_tokens(src, dst, sb, db, 0, ntok)
     finally:

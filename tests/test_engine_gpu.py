@@ -1,0 +1,206 @@
+"""The engine end to end on a GPU: KVTransferClient -> step pipeline -> send stub -> transport ->
+destination cache, checked against the plain-PyTorch oracle / direct tensor comparison.
+
+Single-GPU cases put both caches on cuda:0 (the NVLink transport then runs its kernels with a
+local destination pointer; the code path is the same as for a peer).  Multi-GPU and
+two-process cases are in test_engine_multigpu.py.
+"""
+import os
+import random
+import time
+
+import pytest
+import torch
+
+os.environ.setdefault("BLLM_KVTRANS_QUIET_ENV", "1")
+
+from llumnix_kv_b200.kv_transfer_impl import KVTransferClient, KVTransferProtocolType as PT, KVTransferServer
+from llumnix_kv_b200.ops.layouts import AttnLayout, CacheShape
+from llumnix_kv_b200.ops.p2d_attn import (MODE_BF16_TO_MXFP8, MODE_COPY, HeadMap, ReqChunk, reference_transfer)
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+L = 3
+
+
+def run_step(cli, dst_inst, dst_worker, winfo, reqs, stepid, stream=None):
+    for rid, sb, db, seen, new, last, first in reqs:
+        if first:
+            cli.submit_req_send2(dst_inst, dst_worker, rid, seen, new, last, sb, db, winfo, stepid=stepid)
+        else:
+            cli.submit_delta_send(rid, seen, new, last, stepid=stepid)
+    cli.start_send_step(stepid, 1)
+    for layer in range(L):
+        cli.record_event(layer, stream)
+    cli.flush_send_step()
+    cli.drain()
+    torch.cuda.synchronize()
+
+
+def rand_reqs(rng, n, nb_s, nb_d, ntpb, max_blocks=6):
+    fs, fd = list(range(1, nb_s)), list(range(1, nb_d))
+    rng.shuffle(fs)
+    rng.shuffle(fd)
+    out = []
+    for i in range(n):
+        nb = rng.randint(1, max_blocks)
+        sb, db = [fs.pop() for _ in range(nb)], [fd.pop() for _ in range(nb)]
+        total = nb * ntpb - rng.randint(0, ntpb - 1)
+        out.append((f"r{i}", sb, db, total))
+    return out
+
+
+@pytest.mark.parametrize("proto", [PT.NVLINK, PT.TCP, PT.SHM])
+def test_same_layout_transfer_all_transports(proto):
+    rng = random.Random(1)
+    lay = AttnLayout(CacheShape.FLASH, 48, 16, 8, 128, 2)
+    src = [lay.alloc(DEV, "normal", seed=i) for i in range(L)]
+    dst = [lay.alloc(DEV) for _ in range(L)]
+    srv = KVTransferServer("D|0|1", 1, 0, 0, lay.block_bytes, lay.token_bytes, "fake://", dst, [proto], num_kv_heads=8,
+                           cache_shape=2)
+    cli = KVTransferClient("P|0|1", 1, 0, 0, lay.block_bytes, lay.token_bytes, "fake://", src, [proto], num_kv_heads=8,
+                           cache_shape=2)
+    try:
+        reqs = rand_reqs(rng, 4, 48, 48, 16)
+        # two chunks per request: exercises deltas and ragged block edges on every transport
+        cut = {rid: rng.randint(1, total - 1) if total > 1 else 1 for rid, _, _, total in reqs}
+        run_step(cli, "D|0|1", 0, srv.worker_info(),
+                 [(rid, sb, db, 0, cut[rid], cut[rid] == total, True) for rid, sb, db, total in reqs], 1)
+        run_step(cli, "D|0|1", 0, srv.worker_info(),
+                 [(rid, sb, db, cut[rid], total - cut[rid], True, False) for rid, sb, db, total in reqs
+                  if cut[rid] < total], 2)
+        chunks = [ReqChunk(sb, db, 0, total) for _, sb, db, total in reqs]
+        for i in range(L):
+            expect = torch.zeros_like(dst[i])
+            reference_transfer(lay, lay, src[i], expect, chunks)
+            assert torch.equal(dst[i], expect)
+    finally:
+        srv.stop()
+
+
+def test_nvlink_nhd_to_hnd_cross_layout():
+    rng = random.Random(2)
+    src_l = AttnLayout(CacheShape.FLASH, 40, 16, 8, 128, 2)
+    dst_l = AttnLayout(CacheShape.FLASHINFER, 56, 16, 8, 128, 2)
+    src = [src_l.alloc(DEV, "normal", seed=i) for i in range(L)]
+    dst = [dst_l.alloc(DEV) for _ in range(L)]
+    srv = KVTransferServer("D|0|1", 1, 0, 0, dst_l.block_bytes, dst_l.token_bytes, "fake://", dst, [PT.NVLINK],
+                           num_kv_heads=8, cache_shape=5)
+    cli = KVTransferClient("P|0|1", 1, 0, 0, src_l.block_bytes, src_l.token_bytes, "fake://", src, [PT.NVLINK],
+                           num_kv_heads=8, cache_shape=2)
+    try:
+        reqs = rand_reqs(rng, 5, 40, 56, 16)
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            run_step(cli, "D|0|1", 0, srv.worker_info(), [(rid, sb, db, 0, t, True, True) for rid, sb, db, t in reqs], 7,
+                     stream=side)
+        chunks = [ReqChunk(sb, db, 0, t) for _, sb, db, t in reqs]
+        for i in range(L):
+            expect = torch.zeros_like(dst[i])
+            reference_transfer(src_l, dst_l, src[i], expect, chunks)
+            assert torch.equal(dst[i], expect)
+    finally:
+        srv.stop()
+
+
+def test_nvlink_tp_mismatch_with_block_scaled_fp8_destination():
+    """Config-3 shape in miniature: prefill TP=4 rank 1 (2 of 8 heads, bf16, NHD) -> decode TP=2 rank 0
+    (4 heads, block-scaled e4m3, HND); heads land in the second half of the decode rank's pages."""
+    rng = random.Random(3)
+    src_l = AttnLayout(CacheShape.FLASH, 40, 16, 2, 128, 2)
+    dst_l = AttnLayout(CacheShape.FLASHINFER, 40, 16, 4, 128, 1, mx_scaled=True)
+    src = [src_l.alloc(DEV, "normal", seed=20 + i) for i in range(L)]
+    dst = [dst_l.alloc(DEV) for _ in range(L)]
+    srv = KVTransferServer("D|0|2", 2, 0, 0, dst_l.block_bytes, dst_l.token_bytes, "fake://", dst, [PT.NVLINK],
+                           num_kv_heads=8, cache_shape=5, mx_scaled=True)
+    cli = KVTransferClient("P|0|4", 4, 1, 1, src_l.block_bytes, src_l.token_bytes, "fake://", src, [PT.NVLINK],
+                           num_kv_heads=8, cache_shape=2)
+    try:
+        reqs = rand_reqs(rng, 4, 40, 40, 16)
+        run_step(cli, "D|0|2", 0, srv.worker_info(), [(rid, sb, db, 0, t, True, True) for rid, sb, db, t in reqs], 3)
+        chunks = [ReqChunk(sb, db, 0, t) for _, sb, db, t in reqs]
+        for i in range(L):
+            expect = torch.zeros_like(dst[i])
+            reference_transfer(src_l, dst_l, src[i], expect, chunks, HeadMap(0, 2, 2), MODE_BF16_TO_MXFP8)
+            assert torch.equal(dst[i], expect)
+    finally:
+        srv.stop()
+
+
+@pytest.mark.parametrize("proto", [PT.NVLINK, PT.TCP])
+def test_hybrid_gdn_pages_via_descriptor_path(proto, ops):
+    """Qwen3-Next-like hybrid pages (GDN state + attention in one tensor) with P TP=2 -> D TP=1: no
+    fused kernel for this shape, the planner's IpcBlocks drive the descriptor copy kernel."""
+    rows, dims_p, ssm = 3, [32, 32, 64], [1, 4, 8, 8]
+    hd, heads = 64, 4
+    p_tok, d_tok = 2 * 2 * hd, 2 * 4 * hd
+    ntpb = 16
+    p_bs, d_bs = p_tok * ntpb, d_tok * ntpb
+    nb = 32
+    kw_p = dict(num_kv_heads=heads, num_gdn_layers=1, conv_state_shape=[1, rows, sum(dims_p)], ssm_state_shape=ssm,
+                gdn_conv_channel_dims=dims_p, gdn_conv_elem_size=2, gdn_ssm_elem_size=4)
+    kw_d = dict(kw_p)
+    kw_d.update(conv_state_shape=[1, rows, 2 * sum(dims_p)], gdn_conv_channel_dims=[2 * d for d in dims_p],
+                ssm_state_shape=[1, 8, 8, 8])
+    g = torch.Generator(device=DEV).manual_seed(5)
+    src = [torch.randint(0, 255, (nb * p_bs,), dtype=torch.uint8, device=DEV, generator=g) for _ in range(L)]
+    dst = [torch.zeros(nb * d_bs, dtype=torch.uint8, device=DEV) for _ in range(L)]
+    for s in src:
+        s[:p_bs] = 0  # block 0 is the engine's all-zero block (tail padding reads it)
+    srv = KVTransferServer("D|0|1", 1, 0, 0, d_bs, d_tok, "fake://", dst, [proto], cache_shape=3, **kw_d)
+    cli = KVTransferClient("P|0|2", 2, 1, 1, p_bs, p_tok, "fake://", src, [proto], cache_shape=3, **kw_p)
+    try:
+        sb, db = [[3], [0, 7, 9]], [[5], [2, 6, 11]]
+        total = 2 * ntpb + 5
+        cli.submit_req_send2("D|0|1", 0, "hyb", 0, total, True, sb, db, srv.worker_info(), stepid=1)
+        cli.start_send_step(1, 1)
+        for layer in range(L):
+            cli.record_event(layer)
+        cli.flush_send_step()
+        cli.drain()
+        torch.cuda.synchronize()
+        W = ops.WorkerInfo
+        pw, dw = W.from_string(cli.worker_info()), W.from_string(srv.worker_info())
+        for w, kw in ((pw, kw_p), (dw, kw_d)):
+            for k, v in kw.items():
+                setattr(w, k, v)
+        blocks = ops.plan_ipc_blocks(pw, dw, 3, [("hyb", 0, total, True, sb, db)])[0][0]
+        assert len(blocks) > 20
+        for i in range(L):
+            expect = torch.zeros_like(dst[i])
+            for s_off, d_off, n in blocks:
+                expect[d_off:d_off + n] = src[i][s_off:s_off + n]
+            assert torch.equal(dst[i], expect)
+    finally:
+        srv.stop()
+
+
+def test_layer_overlap_waits_for_the_layer_event():
+    """A transfer enqueued before the forward stream produced the layer must still see the final
+    bytes: the transport orders itself after the layer's CUDA event, not after host time."""
+    lay = AttnLayout(CacheShape.FLASH, 16, 16, 8, 128, 2)
+    src = [lay.alloc(DEV) for _ in range(L)]
+    dst = [lay.alloc(DEV) for _ in range(L)]
+    srv = KVTransferServer("D|0|1", 1, 0, 0, lay.block_bytes, lay.token_bytes, "fake://", dst, [PT.NVLINK],
+                           num_kv_heads=8, cache_shape=2)
+    cli = KVTransferClient("P|0|1", 1, 0, 0, lay.block_bytes, lay.token_bytes, "fake://", src, [PT.NVLINK],
+                           num_kv_heads=8, cache_shape=2)
+    try:
+        fwd = torch.cuda.Stream()
+        big = torch.empty(1 << 28, dtype=torch.uint8, device=DEV)
+        cli.submit_req_send2("D|0|1", 0, "r", 0, 48, True, [1, 2, 3], [4, 5, 6], srv.worker_info(), stepid=1)
+        cli.start_send_step(1, 1)
+        with torch.cuda.stream(fwd):
+            for layer in range(L):
+                for _ in range(4):
+                    big.fill_(layer)  # keeps the stream busy so the layer is produced "late"
+                src[layer].fill_(layer + 1)
+                cli.record_event(layer, fwd)
+        cli.flush_send_step()
+        cli.drain()
+        torch.cuda.synchronize()
+        for layer in range(L):
+            v = lay.view(dst[layer], torch.int16)
+            assert int(v[4:7].min()) == int(v[4:7].max()) == (layer + 1) * 257
+    finally:
+        srv.stop()

@@ -1,0 +1,112 @@
+"""Engine over NVLink between two GPUs: inside one process (peer access) and between two
+processes (CUDA IPC handles fetched from the destination's server).  Plain peer stores only."""
+import multiprocessing as mp
+import os
+import random
+
+import pytest
+import torch
+
+os.environ.setdefault("BLLM_KVTRANS_QUIET_ENV", "1")
+
+from llumnix_kv_b200.kv_transfer_impl import KVTransferClient, KVTransferProtocolType as PT, KVTransferServer
+from llumnix_kv_b200.ops.layouts import AttnLayout, CacheShape
+from llumnix_kv_b200.ops.p2d_attn import ReqChunk, reference_transfer
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+L = 2
+SRC_L = AttnLayout(CacheShape.FLASH, 48, 16, 8, 128, 2)
+DST_L = AttnLayout(CacheShape.FLASHINFER, 48, 16, 8, 128, 2)
+
+
+def _requests():
+    rng = random.Random(5)
+    fs, fd = list(range(1, 48)), list(range(1, 48))
+    rng.shuffle(fs)
+    rng.shuffle(fd)
+    reqs = []
+    for i in range(5):
+        nb = rng.randint(1, 7)
+        reqs.append((f"r{i}", [fs.pop() for _ in range(nb)], [fd.pop() for _ in range(nb)], nb * 16 - rng.randint(0, 15)))
+    return reqs
+
+
+def _send(cli, dst_inst, winfo, reqs):
+    for rid, sb, db, total in reqs:
+        cli.submit_req_send2(dst_inst, 0, rid, 0, total, True, sb, db, winfo, stepid=1)
+    cli.start_send_step(1, 1)
+    for layer in range(L):
+        cli.record_event(layer)
+    cli.flush_send_step()
+    cli.drain()
+
+
+def test_two_gpus_one_process():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    src = [SRC_L.alloc("cuda:0", "normal", seed=i) for i in range(L)]
+    dst = [DST_L.alloc("cuda:1") for _ in range(L)]
+    srv = KVTransferServer("D|0|1", 1, 0, 0, DST_L.block_bytes, DST_L.token_bytes, "fake://", dst, [PT.NVLINK],
+                           num_kv_heads=8, cache_shape=5)
+    cli = KVTransferClient("P|0|1", 1, 0, 0, SRC_L.block_bytes, SRC_L.token_bytes, "fake://", src, [PT.NVLINK],
+                           num_kv_heads=8, cache_shape=2)
+    try:
+        reqs = _requests()
+        _send(cli, "D|0|1", srv.worker_info(), reqs)
+        torch.cuda.synchronize(0)
+        torch.cuda.synchronize(1)
+        chunks = [ReqChunk(sb, db, 0, t) for _, sb, db, t in reqs]
+        for i in range(L):
+            expect = torch.zeros_like(src[i])
+            reference_transfer(SRC_L, DST_L, src[i], expect, chunks)
+            assert torch.equal(dst[i].to("cuda:0"), expect)
+    finally:
+        srv.stop()
+
+
+def _decode_proc(naming_dir, ready, go, result):
+    os.environ["BLLM_KVTRANS_QUIET_ENV"] = "1"
+    # no NVLS / multicast anywhere in this test: plain peer stores, so that a peer process leaving
+    # between steps cannot affect the other GPU
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch as t2
+    from llumnix_kv_b200.kv_transfer_impl import KVTransferProtocolType as P2, KVTransferServer as Srv
+    t2.cuda.set_device(1)
+    dst = [DST_L.alloc("cuda:1") for _ in range(L)]
+    srv = Srv("D|0|1", 1, 0, 0, DST_L.block_bytes, DST_L.token_bytes, f"file:{naming_dir}", dst, [P2.NVLINK],
+              num_kv_heads=8, cache_shape=5)
+    ready.set()
+    go.wait(120)
+    t2.cuda.synchronize()
+    result.put([d.cpu().numpy().copy() for d in dst])
+    srv.stop()
+
+
+def test_two_gpus_two_processes_cuda_ipc(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    ready, go, result = ctx.Event(), ctx.Event(), ctx.Queue()
+    p = ctx.Process(target=_decode_proc, args=(str(tmp_path), ready, go, result))
+    p.start()
+    try:
+        assert ready.wait(180)
+        torch.cuda.set_device(0)
+        src = [SRC_L.alloc("cuda:0", "normal", seed=i) for i in range(L)]
+        cli = KVTransferClient("P|0|1", 1, 0, 0, SRC_L.block_bytes, SRC_L.token_bytes, f"file:{tmp_path}", src,
+                               [PT.NVLINK], num_kv_heads=8, cache_shape=2)
+        reqs = _requests()
+        _send(cli, "D|0|1", None, reqs)
+        torch.cuda.synchronize()
+        go.set()
+        got = [torch.from_numpy(a) for a in result.get(timeout=120)]
+        chunks = [ReqChunk(sb, db, 0, t) for _, sb, db, t in reqs]
+        for i in range(L):
+            expect = torch.zeros_like(src[i])
+            reference_transfer(SRC_L, DST_L, src[i], expect, chunks)
+            assert torch.equal(got[i], expect.cpu())
+    finally:
+        go.set()
+        p.join(60)
+        if p.is_alive():
+            p.kill()
