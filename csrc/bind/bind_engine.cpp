@@ -107,9 +107,10 @@ class KvClient {
            std::vector<size_t> block_sizes, std::vector<size_t> token_sizes, uint32_t layer_num_blocks,
            const std::string& naming_url, const std::vector<uint64_t>& events,
            const std::vector<std::vector<uint64_t>>& layers, const std::vector<TransferProtocol>& protocols,
-           const HybridArgs& h, int cache_shape) {
+           const HybridArgs& h, int cache_shape, const std::string& send_done_addr = "") {
     auto ctx = make_context(inst, tp_size, worker_id, worker_tp_rank, device_id, block_sizes, token_sizes,
                             layer_num_blocks, layers, protocols, h, cache_shape, false);
+    if (!send_done_addr.empty()) ctx->worker_info_mutable()->ext["sdaddr"] = send_done_addr;
     if (!events.empty()) {
       RTASSERT(events.size() == layers.size());
       ctx->set_cuda_barrier(std::make_unique<CudaEventBarrier>(events));
@@ -335,14 +336,12 @@ void bind_engine(py::module_& m) {
                        std::vector<size_t> bs, std::vector<size_t> ts, uint32_t nblocks, const std::string& url,
                        const std::vector<uint64_t>& events, const std::vector<std::vector<uint64_t>>& layers,
                        const std::vector<TransferProtocol>& protocols, int cache_shape, const py::kwargs& kw) {
+             HybridArgs h = hybrid_from_kwargs(kw);
+             std::string sd;
+             if (kw.contains("send_done_addr") && !kw["send_done_addr"].is_none()) sd = kw["send_done_addr"].cast<std::string>();
              py::gil_scoped_release rel;
-             HybridArgs h;
-             {
-               py::gil_scoped_acquire acq;
-               h = hybrid_from_kwargs(kw);
-             }
              return std::make_unique<KvClient>(inst, tp, wid, rank, dev, std::move(bs), std::move(ts), nblocks, url,
-                                               events, layers, protocols, h, cache_shape);
+                                               events, layers, protocols, h, cache_shape, sd);
            }),
            py::arg("inst_name"), py::arg("tp_size"), py::arg("worker_id"), py::arg("worker_tp_rank"),
            py::arg("device_id"), py::arg("block_sizes"), py::arg("token_sizes"), py::arg("layer_num_blocks"),

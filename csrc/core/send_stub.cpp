@@ -49,12 +49,23 @@ std::vector<char> SendDoneNotifier::encode(uint32_t worker_tp_rank, const std::v
 }
 
 void SendDoneNotifier::round_trip(const std::vector<char>& buf, int resp_size) {
-  const sockaddr_in* addr = env_send_done_addr();
-  if (addr == nullptr) return;  // send-done RPC disabled
-  if (!sock_.valid()) {
+  std::string ip_s;
+  int port = 0;
+  if (!addr_.empty()) {
+    const auto pos = addr_.rfind(':');
+    if (pos == std::string::npos) return;
+    ip_s = addr_.substr(0, pos);
+    port = atoi(addr_.c_str() + pos + 1);
+  } else {
+    const sockaddr_in* addr = env_send_done_addr();
+    if (addr == nullptr) return;  // send-done RPC disabled
     char ip[64];
     inet_ntop(AF_INET, &addr->sin_addr, ip, sizeof(ip));
-    int fd = tcp_connect(ip, ntohs(addr->sin_port), env_rpc_timeout_s() * 1000);
+    ip_s = ip;
+    port = ntohs(addr->sin_port);
+  }
+  if (!sock_.valid()) {
+    int fd = tcp_connect(ip_s, port, env_rpc_timeout_s() * 1000);
     if (fd < 0) throw std::runtime_error("rpc send done: connect error. errno=" + std::to_string(errno));
     sock_ = FdGuard(fd);
   }
@@ -108,9 +119,9 @@ struct KvSendStub::Impl {
   Timepoint iter_start, send_finish;
 
   Impl(KvSendStub* s, const WorkerInfo& src, std::shared_ptr<INamingWorkerClient> n, uint32_t sl, uint32_t nl,
-       std::unique_ptr<IChannelFactory> f, int shape)
+       std::unique_ptr<IChannelFactory> f, int shape, std::string sd_addr)
       : stub(s), src_info(src), naming(std::move(n)), start_layer(sl), num_layers(nl), channel_factory(std::move(f)),
-        cache_shape(shape), notifier(src.worker_tp_rank) {}
+        cache_shape(shape), notifier(src.worker_tp_rank, std::move(sd_addr)) {}
 
   void refresh_dst_info() {
     auto fresh = naming->get_worker_info(stub->dstid(), stub->dstworkerid());
@@ -236,10 +247,10 @@ struct KvSendStub::Impl {
 
 KvSendStub::KvSendStub(InstanceId dstid, WorkerId dstworkerid, const WorkerInfo& src_info, uint32_t start_layer,
                        uint32_t num_layers, std::unique_ptr<IChannelFactory> channel_factory,
-                       std::shared_ptr<INamingWorkerClient> naming, int cache_shape)
+                       std::shared_ptr<INamingWorkerClient> naming, int cache_shape, std::string send_done_addr)
     : ISendStub(std::move(dstid), dstworkerid),
       impl_(std::make_unique<Impl>(this, src_info, std::move(naming), start_layer, num_layers,
-                                   std::move(channel_factory), cache_shape)) {}
+                                   std::move(channel_factory), cache_shape, std::move(send_done_addr))) {}
 
 KvSendStub::~KvSendStub() = default;
 
@@ -262,7 +273,8 @@ SendStub KvSendStubFactory::create_stub(const InstanceId& dst, WorkerId dst_work
   if (!nw) throw std::runtime_error("no naming service and no destination info in the request");
   const int shape = ctx_->worker_info().cache_shape_or(env_cache_shape());
   return std::make_unique<KvSendStub>(dst, dst_worker, ctx_->worker_info(), start_layer, num_layers,
-                                      std::make_unique<ChannelFactory>(ctx_, proto), std::move(nw), shape);
+                                      std::make_unique<ChannelFactory>(ctx_, proto), std::move(nw), shape,
+                                      ctx_->worker_info().ext_str("sdaddr"));
 }
 
 }  // namespace kvx

@@ -53,7 +53,8 @@ class ISendStubFactory {
 // body again under SAVE_DONE2_REQ 0x20181223.  One reconnect-and-retry on a stale socket.
 class SendDoneNotifier {
  public:
-  explicit SendDoneNotifier(uint32_t worker_tp_rank) : rank_(worker_tp_rank) {}
+  // `addr` ("ip:port") overrides BLLM_KVTRANS_SEND_DONE_ADDR; empty = use the environment.
+  explicit SendDoneNotifier(uint32_t worker_tp_rank, std::string addr = "") : rank_(worker_tp_rank), addr_(std::move(addr)) {}
   void notify(const std::vector<const ReqSendTask*>& reqs);
   static std::vector<char> encode(uint32_t worker_tp_rank, const std::vector<const ReqSendTask*>& reqs, int head_kind,
                                   int* resp_size);
@@ -61,6 +62,7 @@ class SendDoneNotifier {
  private:
   void round_trip(const std::vector<char>& buf, int resp_size);
   uint32_t rank_;
+  std::string addr_;
   FdGuard sock_;
 };
 
@@ -68,7 +70,7 @@ class KvSendStub : public ISendStub {
  public:
   KvSendStub(InstanceId dstid, WorkerId dstworkerid, const WorkerInfo& src_info, uint32_t start_layer,
              uint32_t num_layers, std::unique_ptr<IChannelFactory> channel_factory,
-             std::shared_ptr<INamingWorkerClient> naming, int cache_shape);
+             std::shared_ptr<INamingWorkerClient> naming, int cache_shape, std::string send_done_addr = "");
   ~KvSendStub() override;
   void send_batch(BatchSendTask batch) noexcept override;
 

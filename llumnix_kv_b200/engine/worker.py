@@ -1,0 +1,138 @@
+"""Worker side of the minimal engine: one ``MiniWorker`` per TP rank owns that rank's paged KV
+cache and runs the "model".
+
+The model is a stand-in whose KV is a closed-form function of (token id, position, layer,
+K/V, global head, dim), written into the paged cache exactly where a real attention layer
+would write it.  That makes every transfer checkable: a decode engine can recompute what any
+slot must contain, whatever layout, TP split or dtype path the bytes took to get there.
+The forward pass drives the connector the way a model runner does: bind metadata,
+``start_load_kv``, ``save_kv_layer`` after each layer, clear.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from llumnix_kv_b200.hybrid_connector import HybridConnector
+from llumnix_kv_b200.hybrid_connector.engine_proxy import KVConnectorRole, WorkerProxy
+from llumnix_kv_b200.ops.layouts import AttnLayout, CacheShape
+
+from .config import KVCacheConfig, KVCacheGroupSpec, VllmConfig
+from .types import SchedulerOutput
+
+
+def layer_name(i: int) -> str:
+    return f"model.layers.{i}.self_attn.attn"
+
+
+def synthetic_kv(token_ids: torch.Tensor, positions: torch.Tensor, layer: int, head0: int, n_heads: int,
+                 head_dim: int, dtype: torch.dtype) -> torch.Tensor:
+    """[tokens, 2(K/V), heads, dim] values in a range every cache dtype represents exactly enough
+    to compare bit-for-bit (multiples of 1/64 below 8)."""
+    dev = token_ids.device
+    t = token_ids.to(torch.int64).view(-1, 1, 1, 1)
+    p = positions.to(torch.int64).view(-1, 1, 1, 1)
+    kv = torch.arange(2, device=dev).view(1, 2, 1, 1)
+    h = (torch.arange(n_heads, device=dev) + head0).view(1, 1, -1, 1)
+    d = torch.arange(head_dim, device=dev).view(1, 1, 1, -1)
+    code = (t * 131 + p * 31 + layer * 17 + kv * 7 + h * 5 + d * 3) % 509
+    return ((code - 254).to(torch.float32) / 64.0).to(dtype)
+
+
+class MiniWorker:
+    def __init__(self, cfg: VllmConfig, tp_rank: int, device: Optional[str] = None, with_connector: bool = True):
+        self.cfg = cfg
+        self.tp_rank = tp_rank
+        self.device = torch.device(device or cfg.device)
+        mc, cc = cfg.model_config, cfg.cache_config
+        tp = cfg.parallel_config.tensor_parallel_size
+        self.heads = max(1, mc.num_kv_heads // tp)
+        self.head0 = (tp_rank * mc.num_kv_heads // tp) if mc.num_kv_heads >= tp else tp_rank * mc.num_kv_heads // tp
+        self.dtype = torch.bfloat16 if mc.dtype_bytes == 2 else torch.uint8
+        elem = 1 if cc.mx_scaled else mc.dtype_bytes
+        self.layout = AttnLayout(CacheShape(cc.cache_shape), cc.num_gpu_blocks, cc.block_size, self.heads, mc.head_dim,
+                                 elem, mx_scaled=cc.mx_scaled)
+        self.kv_caches = {layer_name(i): self.layout.alloc(self.device) for i in range(mc.num_layers)}
+        self.kv_cache_config = KVCacheConfig(
+            num_blocks=cc.num_gpu_blocks,
+            kv_cache_groups=[KVCacheGroupSpec([layer_name(i) for i in range(mc.num_layers)])])
+        self.connector: Optional[HybridConnector] = None
+        self.proxy: Optional[WorkerProxy] = None
+        if with_connector and cfg.kv_transfer_config is not None:
+            self.proxy = WorkerProxy(cfg, tp_rank, str(self.device))
+            self.connector = HybridConnector(cfg, KVConnectorRole.WORKER, self.kv_cache_config, worker=self.proxy)
+            self.connector.register_kv_caches(self.kv_caches)
+        self._req_state: dict = {}   # reqid -> (prompt tokens, block ids of group 0)
+
+    # ---- the "model" ---------------------------------------------------------------------------
+    def _write_layer(self, layer: int, tokens: torch.Tensor, positions: torch.Tensor, blocks: list) -> None:
+        if self.cfg.cache_config.mx_scaled:
+            return  # a block-scaled fp8 cache is only ever filled by transfers in this engine
+        lay = self.layout
+        kv = synthetic_kv(tokens, positions, layer, self.head0, self.heads, lay.head_dim, self.dtype)
+        view = lay.view(self.kv_caches[layer_name(layer)], self.dtype)   # [block, kv, slot, head, dim]
+        blk = torch.tensor([blocks[int(p) // lay.ntpb] for p in positions.tolist()], device=self.device)
+        slot = (positions % lay.ntpb).to(self.device)
+        view[blk, :, slot] = kv
+
+    def expected_kv(self, layer: int, token_ids: list, lo: int, hi: int) -> torch.Tensor:
+        toks = torch.tensor(token_ids[lo:hi], device=self.device)
+        pos = torch.arange(lo, hi, device=self.device)
+        return synthetic_kv(toks, pos, layer, self.head0, self.heads, self.layout.head_dim, self.dtype)
+
+    def read_kv(self, layer: int, blocks: list, lo: int, hi: int) -> torch.Tensor:
+        lay = self.layout
+        view = lay.view(self.kv_caches[layer_name(layer)], self.dtype)
+        pos = torch.arange(lo, hi, device=self.device)
+        blk = torch.tensor([blocks[p // lay.ntpb] for p in range(lo, hi)], device=self.device)
+        return view[blk, :, pos % lay.ntpb]
+
+    def execute_model(self, sout: SchedulerOutput) -> dict:
+        """One forward pass over the scheduled tokens; returns {reqid: sampled token}."""
+        conn = self.connector
+        meta = sout.kv_connector_metadata
+        if conn is not None and meta is not None:
+            conn.bind_connector_metadata(meta)
+            conn.start_load_kv(None)
+        for nr in sout.scheduled_new_reqs:
+            self._req_state[nr.req_id] = [list(nr.prompt_token_ids), [list(g) for g in nr.block_ids]]
+        cached = sout.scheduled_cached_reqs
+        for rid, new_blocks in zip(cached.req_ids, cached.new_block_ids):
+            st = self._req_state.get(rid)
+            if st is not None:
+                for g, extra in zip(st[1], new_blocks):
+                    g.extend(extra)
+        work = []
+        computed = {nr.req_id: nr.num_computed_tokens for nr in sout.scheduled_new_reqs}
+        computed.update(dict(zip(cached.req_ids, cached.num_computed_tokens)))
+        for rid, n in sout.num_scheduled_tokens.items():
+            st = self._req_state.get(rid)
+            if st is None or n <= 0:
+                continue
+            lo = computed[rid]
+            toks = st[0]
+            hi = min(lo + n, len(toks))
+            if hi > lo:
+                work.append((torch.tensor(toks[lo:hi], device=self.device), torch.arange(lo, hi, device=self.device),
+                             st[1][-1] if len(st[1]) > 1 else st[1][0]))
+        for layer in range(self.cfg.model_config.num_layers):
+            for toks, pos, blocks in work:
+                self._write_layer(layer, toks, pos, blocks)
+            if conn is not None and meta is not None:
+                conn.save_kv_layer(layer_name(layer), self.kv_caches[layer_name(layer)], None)
+        if conn is not None and meta is not None:
+            conn.clear_connector_metadata()
+        sampled = {}
+        for rid, n in sout.num_scheduled_tokens.items():
+            st = self._req_state.get(rid)
+            if st is not None:
+                sampled[rid] = (sum(st[0][-4:]) * 7 + len(st[0])) % self.cfg.model_config.vocab_size
+        for rid in sout.finished_req_ids:
+            self._req_state.pop(rid, None)
+        return sampled
+
+    def append_token(self, rid: str, tok: int) -> None:
+        st = self._req_state.get(rid)
+        if st is not None:
+            st[0].append(tok)

@@ -1,0 +1,459 @@
+"""Control-plane plumbing: event-loop threads, the head-dispatch RPC server, connection pools,
+peer discovery, and the per-request completion bookkeeping shared by save and load paths.
+
+Behaviour follows blade_kvt/hybrid_connector/utils.py (RpcServer :88-146, ConnPool/ConnManager
+:152-228, PeerInfo :231-268, PeerManager :271-409, IoRet/IoState/try_advance :412-552,
+handle_done_req :561-627).
+"""
+from __future__ import annotations
+
+import asyncio
+import logging
+import os
+import random
+import struct
+import threading
+from collections import OrderedDict
+from dataclasses import dataclass
+from typing import Any, Callable, Coroutine, Optional
+
+import msgspec
+
+logger = logging.getLogger("llumnix_kv_b200.hybrid_connector")
+
+# Tests flip this off so that a deliberately failing coroutine raises instead of taking the
+# interpreter down.
+ABORT_ON_TASK_EXCEPTION = os.environ.get("LLUMNIX_KV_ABORT_ON_TASK_EXCEPTION", "1") != "0"
+
+
+def kill_me_if_exception(async_func):
+    """Every coroutine that is the main of a task wears this: a control-plane bug must not leave
+    a request silently stuck, so an unexpected exception ends the process."""
+
+    async def wrapper(*args, **kwargs):
+        try:
+            loop = asyncio.get_running_loop()
+            running = getattr(loop, "_kvx_running_tasks", None)
+            if running is None:
+                running = set()
+                loop._kvx_running_tasks = running  # keeps tasks referenced until done
+            task = asyncio.current_task()
+            if task is not None:
+                running.add(task)
+                task.add_done_callback(running.discard)
+            return await async_func(*args, **kwargs)
+        except asyncio.CancelledError:
+            raise
+        except Exception:
+            logger.exception("task %s failed", getattr(async_func, "__name__", async_func))
+            if ABORT_ON_TASK_EXCEPTION:
+                os.abort()
+            raise
+
+    wrapper.__name__ = getattr(async_func, "__name__", "wrapped")
+    return wrapper
+
+
+def start_asyncio_thread(name: str, device: Optional[str] = None) -> asyncio.AbstractEventLoop:
+    """A daemon thread running its own event loop (uvloop when available)."""
+    try:
+        import uvloop
+
+        loop = uvloop.new_event_loop()
+    except Exception:  # pragma: no cover
+        loop = asyncio.new_event_loop()
+
+    def on_ex(_loop, context):
+        logger.error("event loop %s exception: %s", name, context)
+        if ABORT_ON_TASK_EXCEPTION and context.get("exception") is not None:
+            os.abort()
+
+    loop.set_exception_handler(on_ex)
+
+    def main():
+        if device is not None and device.startswith("cuda"):
+            import torch
+
+            torch.cuda.set_device(torch.device(device))
+        asyncio.set_event_loop(loop)
+        loop.run_forever()
+
+    threading.Thread(target=main, name=name, daemon=True).start()
+    return loop
+
+
+# ---- RPC: 4-byte head selects the handler, the handler reads its own body -----------------------
+_RpcMethod = Callable[[asyncio.StreamReader, asyncio.StreamWriter], Coroutine[Any, Any, None]]
+
+
+class RpcServer:
+    def __init__(self, port: int, name: str):
+        self._name, self._port = name, port
+        self._methods: dict[int, _RpcMethod] = {}
+        self._started = threading.Event()
+        self._server: Optional[asyncio.AbstractServer] = None
+
+    def register_method(self, head: int, cb: _RpcMethod) -> None:
+        assert head not in self._methods, f"rpc head {head:#x} registered twice"
+        self._methods[head] = cb
+
+    def port(self) -> int:
+        return self._port
+
+    def start(self, loop: asyncio.AbstractEventLoop, wait: bool = True) -> None:
+        asyncio.run_coroutine_threadsafe(self._main(), loop)
+        if wait:
+            self._started.wait(30)
+
+    async def _client_main(self, reader, writer):
+        try:
+            while True:
+                (head,) = struct.unpack("=I", await reader.readexactly(4))
+                cb = self._methods.get(head)
+                if cb is None:
+                    logger.warning("%s: rpc unknown head=%#x", self._name, head)
+                    break
+                await cb(reader, writer)
+        except asyncio.IncompleteReadError as ex:
+            if ex.partial:
+                logger.warning("%s: connection closed mid-message", self._name)
+        except (ConnectionResetError, BrokenPipeError):
+            pass
+        except Exception:
+            logger.exception("%s: rpc handler failed", self._name)
+            if ABORT_ON_TASK_EXCEPTION:
+                os.abort()
+        try:
+            writer.close()
+            await writer.wait_closed()
+        except Exception:
+            pass
+
+    async def _main(self):
+        self._server = await asyncio.start_server(self._client_main, "0.0.0.0", self._port)
+        if self._port == 0:
+            self._port = self._server.sockets[0].getsockname()[1]
+        logger.info("%s RPC server on port %s", self._name, self._port)
+        self._started.set()
+        async with self._server:
+            await self._server.serve_forever()
+
+    def close(self, loop: asyncio.AbstractEventLoop) -> None:
+        if self._server is not None:
+            loop.call_soon_threadsafe(self._server.close)
+
+
+Conn = tuple
+
+
+class ConnPool:
+    def __init__(self, host: str, port: int, max_conn: int):
+        self._host, self._port, self._max = host, port, max_conn
+        self._conns: list = []
+
+    async def _acquire(self, force_new: bool = False):
+        if not force_new and self._conns:
+            return self._conns.pop()
+        return await asyncio.open_connection(self._host, self._port)
+
+    def _release(self, conn) -> None:
+        if len(self._conns) >= self._max:
+            if not conn[1].is_closing():
+                conn[1].close()
+            return
+        self._conns.append(conn)
+
+    acquire = _acquire
+    release = _release
+
+    def host(self):
+        return self._host
+
+    def port(self):
+        return self._port
+
+    def close(self):
+        for _, w in self._conns:
+            if not w.is_closing():
+                w.close()
+        self._conns.clear()
+
+
+class ConnManager:
+    """LRU of connection pools keyed by (addr, port)."""
+
+    def __init__(self, capacity: int = 512):
+        self._cap = capacity
+        self._pools: "OrderedDict[tuple, ConnPool]" = OrderedDict()
+
+    async def acquire_conn(self, addr_port: tuple, force_new: bool = False):
+        pool = self._pools.get(addr_port)
+        if pool is None:
+            pool = ConnPool(addr_port[0], addr_port[1], 3)
+            self._pools[addr_port] = pool
+            while len(self._pools) > self._cap:
+                _, old = self._pools.popitem(last=False)
+                old.close()
+        else:
+            self._pools.move_to_end(addr_port)
+        return await pool._acquire(force_new)
+
+    def release_conn(self, addr_port: tuple, conn) -> None:
+        pool = self._pools.get(addr_port)
+        if pool is not None:
+            pool._release(conn)
+
+    def pop(self, addr_port, default=None):
+        pool = self._pools.pop(addr_port, default)
+        if isinstance(pool, ConnPool):
+            pool.close()
+        return pool
+
+
+@dataclass
+class PeerInfo:
+    """``role:tpsize:ctime_us:addr:port:dprank`` as published under ``endpoint{dprank}``."""
+
+    role: str = ""
+    tpsize: int = -1
+    ctime_us: int = -1
+    addr: str = ""
+    port: int = 33000
+    dprank: int = 0
+
+    def serialize(self) -> str:
+        return f"{self.role}:{self.tpsize}:{self.ctime_us}:{self.addr}:{self.port}:{self.dprank}"
+
+    @classmethod
+    def deserialize(cls, data: str) -> "PeerInfo":
+        p = data.split(":")
+        if len(p) != 6:
+            raise ValueError(f"PeerInfo.deserialize: BadVal={data}")
+        return cls(role=p[0], tpsize=int(p[1]), ctime_us=int(p[2]), addr=p[3], port=int(p[4]), dprank=int(p[5]))
+
+
+class PeerMap:
+    def __init__(self):
+        self._addr2id: dict = {}
+        self._id2info: dict = {}
+
+    def __bool__(self):
+        return bool(self._id2info)
+
+    def __setitem__(self, peerid: str, peer: PeerInfo):
+        old = self._id2info.pop(peerid, None)
+        if old is not None:
+            self._addr2id.pop((old.addr, old.port), None)
+        self._addr2id[(peer.addr, peer.port)] = peerid
+        self._id2info[peerid] = peer
+
+    def __getitem__(self, peerid: str) -> PeerInfo:
+        return self._id2info[peerid]
+
+    def get_peerid(self, addr: tuple) -> Optional[str]:
+        return self._addr2id.get(addr)
+
+    def items(self):
+        return self._id2info.items()
+
+    def keys(self, exclude: Optional[tuple] = None) -> list:
+        if exclude is None:
+            return list(self._id2info)
+        return [i for i, p in self._id2info.items() if (p.addr, p.port) != tuple(exclude)]
+
+    def pop(self, peerid: str, default=None):
+        info = self._id2info.pop(peerid, default)
+        if info is not None:
+            self._addr2id.pop((info.addr, info.port), None)
+        return info
+
+    def update(self, infos: dict) -> None:
+        for k, v in infos.items():
+            self[k] = v
+
+
+def get_peer_id(inst_id: str, dp_rank: int, tp_size: int) -> str:
+    return f"{inst_id}|{dp_rank}|{tp_size}"
+
+
+class PeerManager:
+    """Polls the naming service, notices peers that left or restarted (``ctime_us`` changed) and
+    drops their pooled connections; hands out a random live peer."""
+
+    POLL_S = 7.0
+
+    def __init__(self, naming_cli, interested_role: Optional[str], conn_mgr: ConnManager):
+        self._naming, self._role, self._conn_mgr = naming_cli, interested_role, conn_mgr
+        self._running = PeerMap()
+
+    def _list_instance(self) -> list:
+        out = []
+        for inst in self._naming.list():
+            for ep in self._naming.search(inst, "endpoint"):
+                info = PeerInfo.deserialize(ep)
+                if self._role is not None and info.role != self._role:
+                    break
+                out.append((get_peer_id(inst, info.dprank, info.tpsize), info))
+        return out
+
+    async def refresh(self) -> None:
+        fresh = dict(self._list_instance())
+        gone, changed = [], {}
+        for pid, peer in self._running.items():
+            new = fresh.pop(pid, None)
+            if new is None:
+                gone.append(pid)
+                logger.info("PeerManager peer exited. peer=%s", peer)
+            elif new.ctime_us != peer.ctime_us:
+                changed[pid] = new
+                logger.info("PeerManager peer updated. before=%s after=%s", peer, new)
+        for pid in gone:
+            info = self._running.pop(pid)
+            if info is not None:
+                self._conn_mgr.pop((info.addr, info.port), None)
+        for pid, new in changed.items():
+            old = self._running[pid]
+            self._conn_mgr.pop((old.addr, old.port), None)
+            self._running[pid] = new
+        if fresh:
+            logger.info("PeerManager peer added. peers=%s", fresh)
+            self._running.update(fresh)
+
+    @kill_me_if_exception
+    async def _main(self):
+        while True:
+            try:
+                await self.refresh()
+            except Exception:
+                logger.exception("PeerManager refresh failed")
+            await asyncio.sleep(self.POLL_S)
+
+    def start(self, loop) -> None:
+        asyncio.run_coroutine_threadsafe(self._main(), loop)
+
+    def get_peer(self, exclude: Optional[tuple] = None) -> Optional[tuple]:
+        peers = self._running.keys(exclude)
+        if not peers:
+            return None
+        info = self._running[random.choice(peers)]
+        return (info.addr, info.port)
+
+
+# ---- completion bookkeeping -----------------------------------------------------------------------
+class IoRet(msgspec.Struct, array_like=True, omit_defaults=True, gc=False):
+    """Outcome of one I/O on one worker: request id, failure, tokens moved, which backend."""
+
+    reqid: Optional[str] = None
+    ex: Optional[Any] = None      # exceptions never cross the wire: only in-process producers set it
+    n: Optional[int] = None
+    source: Optional[str] = None
+
+
+class IoState:
+    """A request is done when every TP rank has reported ``signals_per_worker`` times (or, with
+    ``expected_sources``, once per source)."""
+
+    def __init__(self, signals_per_worker: int = 1):
+        self.signals_per_worker = signals_per_worker
+        self._worker_signals: dict[int, list] = {}
+        self._signals_lock = threading.Lock()
+
+    def merge(self) -> IoRet:
+        """Combine the signals of all ready ranks: first failure wins, token count is the minimum."""
+        rets: list = []
+        for sigs in self._worker_signals.values():
+            if len(sigs) >= self.signals_per_worker:
+                rets.extend(sigs)
+        assert rets
+        out = rets[0]
+        for r in rets[1:]:
+            if r.ex is not None and out.ex is None:
+                out.ex = r.ex
+                break
+            if out.n is None:
+                continue
+            if r.n is None:
+                out.n = None
+            elif out.n > r.n:
+                out.n = r.n
+        return out
+
+
+def try_advance(state_dict: dict, ioret: IoRet, worker_tprank: int, tpsize: int,
+                on_signal_advanced: Optional[Callable[[Any, IoRet], None]] = None):
+    """Record one completion signal; returns the state when the request just became complete."""
+    assert ioret.reqid is not None
+    state: Optional[IoState] = state_dict.get(ioret.reqid)
+    if state is None:
+        logger.warning("try_advance: unknown ioret=%s tprank=%s", ioret, worker_tprank)
+        return None
+    with state._signals_lock:
+        sigs = state._worker_signals.setdefault(worker_tprank, [])
+        expected = tuple(getattr(state, "expected_sources", ()) or ())
+        if expected:
+            if ioret.source is None or ioret.source not in expected:
+                logger.warning("try_advance: bad source ioret=%s expected=%s", ioret, expected)
+                return None
+            if any(s.source == ioret.source for s in sigs):
+                logger.warning("try_advance: dup source worker=%s ioret=%s", worker_tprank, ioret)
+                return None
+            sigs.append(ioret)
+            if on_signal_advanced is not None:
+                on_signal_advanced(state, ioret)
+            ready = sum(1 for s in state._worker_signals.values()
+                        if all(any(x.source == src for x in s) for src in expected))
+        else:
+            if len(sigs) >= state.signals_per_worker:
+                logger.warning("try_advance: dup worker=%s ioret=%s", worker_tprank, ioret)
+                return None
+            sigs.append(ioret)
+            if on_signal_advanced is not None:
+                on_signal_advanced(state, ioret)
+            ready = sum(1 for s in state._worker_signals.values() if len(s) >= state.signals_per_worker)
+        return state if ready >= tpsize else None
+
+
+class CodeError(Exception):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"{code}: {msg}")
+        self.code, self.msg = code, msg
+
+
+async def handle_done_req(reader, writer, cb: Callable[[int, IoRet], Any], respcode: int) -> None:
+    """Parse the native engine's send-done body (the head has been consumed).
+
+    ``worker_tp | flags : u32, n : u32`` then, version 2 (flag 0x40000000), per request
+    ``plen, code, rlen : u32`` + reqid; version 1 is ``len, reqid`` per request followed, with
+    flag 0x80000000, by one ``plen`` per request.
+    """
+    HAS_VER2, HAS_PLEN = 0x40000000, 0x80000000
+    tprank, n = struct.unpack("=II", await reader.readexactly(8))
+    ver2, has_plen = tprank & HAS_VER2, tprank & HAS_PLEN
+    tprank &= 0xFFFF
+    rets: list = []
+    if ver2:
+        for _ in range(n):
+            plen, code, rlen = struct.unpack("=III", await reader.readexactly(12))
+            reqid = (await reader.readexactly(rlen)).decode("utf-8")
+            rets.append(IoRet(reqid=reqid, n=plen, ex=CodeError(code, "done req") if code else None))
+    else:
+        for _ in range(n):
+            (rlen,) = struct.unpack("=I", await reader.readexactly(4))
+            rets.append(IoRet(reqid=(await reader.readexactly(rlen)).decode("utf-8")))
+        if has_plen:
+            for r in rets:
+                (r.n,) = struct.unpack("=I", await reader.readexactly(4))
+    writer.write(struct.pack("=I", respcode))
+    coros = []
+    for r in rets:
+        res = cb(tprank, r)
+        if asyncio.iscoroutine(res):
+            coros.append(res)
+    if coros:
+        await asyncio.gather(*coros)
+    await writer.drain()
+
+
+def pack_rpc(head: int, body: bytes) -> bytes:
+    """``head:u32, len:u32, body`` - the framing of every msgpack-bodied RPC."""
+    return struct.pack("=II", head, len(body)) + body

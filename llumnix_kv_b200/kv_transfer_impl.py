@@ -159,7 +159,8 @@ class KVTransferClient:
                  gdn_conv_channel_dims=None, kda_conv_dim_first: bool = False, hybrid_attn_token_size: int = 0,
                  kda_page_stride: int = 0, attn_pack_size: int = 1, num_ple_layers: int = 0,
                  ple_block_group: int = 0, ple_conv_elem_size: int = 1, ple_conv_state_shape=None,
-                 ple_conv_channel_dims=None, cache_shape: int = -1, process_global: bool = False):
+                 ple_conv_channel_dims=None, cache_shape: int = -1, process_global: bool = False,
+                 send_done_addr: Optional[str] = None):
         block_bytes, token_bytes, layers, layer_num_blocks, device_id = _normalise(block_bytes, token_bytes, layers)
         self._num_layers = len(layers)
         self._device_id = device_id
@@ -184,7 +185,11 @@ class KVTransferClient:
         else:
             self._c = _K.KvClient(inst_id, tp_size, worker_id, worker_tp_rank, device_id, block_bytes, token_bytes,
                                   layer_num_blocks, naming_url, self._event_addrs, layer_addrs, ops_protocols,
-                                  cache_shape, **kw)
+                                  cache_shape, send_done_addr=send_done_addr, **kw)
+        self._send_done_addr = None
+        if send_done_addr:
+            h, p = send_done_addr.rsplit(':', 1)
+            self._send_done_addr = (h, int(p))
         self._layers = layers  # keep the tensors alive as long as the engine holds their addresses
         self._inited = True
         self._cur_step_id: Optional[int] = None
@@ -292,7 +297,7 @@ class KVTransferClient:
         """
         if not reqids:
             return
-        addr = _get_send_done_addr()
+        addr = self._send_done_addr or _get_send_done_addr()
         assert addr is not None, "send_error_done_req: BLLM_KVTRANS_SEND_DONE_ADDR not set"
         body = encode_send_done(self._worker_tp_rank, [(r, plen, CODE_INTERNALERROR) for r in reqids],
                                 _get_send_done_head_kind())
