@@ -48,3 +48,138 @@ def test_push_mode_prefill_on_p_decode_on_d(pd):
         time.sleep(0.01)
     assert p.scheduler.kv_cache_manager.block_pool.num_free_blocks() == 63
     assert not p.connector._sched._saving and not d.connector._sched._loading
+
+
+def _spy_add(d):
+    captured = {}
+    orig = d.scheduler.add_request
+
+    def spy(r):
+        captured[r.request_id] = (r.num_computed_tokens, d.scheduler.kv_cache_manager.get_block_ids(r.request_id))
+        orig(r)
+
+    d.scheduler.add_request = spy
+    return captured
+
+
+def _dual_params(p):
+    return {"do_remote_prefill": True, "remote_host": "127.0.0.1", "remote_port": p.proxy.rpc_port()}
+
+
+@pytest.mark.parametrize("p_first", [True, False])
+def test_dual_request_mode_either_arrival_order(pd, p_first):
+    """The frontend sends one half of the request to P (do_remote_decode) and one to D
+    (do_remote_prefill); whichever arrives first waits for the other."""
+    p, d = pd
+    cap = _spy_add(d)
+    rid = f"dual{int(p_first)}"
+    preq = make_req(rid, 50, max_tokens=1, params={"do_remote_decode": True})
+    dreq = make_req(rid, 50, max_tokens=2, params=_dual_params(p))
+    if p_first:
+        p.add_request(preq)
+        time.sleep(0.2)
+        d.add_request(dreq)
+    else:
+        d.add_request(dreq)
+        time.sleep(0.3)      # D polls P and gets 404 a few times
+        p.add_request(preq)
+    out = d.wait_finished(rid, 30)
+    assert out is not None and out.finish_reason.name == "LENGTH"
+    computed, blocks = cap[rid]
+    assert computed == 49
+    check_decode_cache(d, rid, dreq.prompt_token_ids, blocks[0], 49)
+    deadline = time.time() + 5
+    while time.time() < deadline and p.scheduler.kv_cache_manager.block_pool.num_free_blocks() != 63:
+        time.sleep(0.01)
+    assert p.scheduler.kv_cache_manager.block_pool.num_free_blocks() == 63
+
+
+def test_dual_request_gone_on_p_fails_the_load(pd):
+    """A request P has aborted answers 410: D gives up at once instead of retrying."""
+    p, d = pd
+    preq = make_req("gone", 40, max_tokens=1, params={"do_remote_decode": True})
+    p.add_request(preq)
+    time.sleep(0.3)
+    p.abort_requests(["gone"])
+    time.sleep(0.3)
+    d.add_request(make_req("gone", 40, max_tokens=2, params=_dual_params(p)))
+    out = d.wait_finished("gone", 20)
+    assert out is not None and out.finish_reason.name == "ABORT"
+    deadline = time.time() + 5
+    while time.time() < deadline and d.scheduler.kv_cache_manager.block_pool.num_free_blocks() != 63:
+        time.sleep(0.01)
+    assert d.scheduler.kv_cache_manager.block_pool.num_free_blocks() == 63
+    assert p.scheduler.kv_cache_manager.block_pool.num_free_blocks() == 63
+
+
+def test_chunked_prefill_sends_deltas():
+    """A prompt longer than the prefill engine's token budget goes out chunk by chunk."""
+    p, d = make_pd(p_kw={"max_batched": 32})
+    try:
+        cap = _spy_add(d)
+        req = make_req("chunky", 150, max_tokens=2,
+                       params={"remote_host": "127.0.0.1", "remote_port": p.proxy.rpc_port()})
+        d.add_request(req)
+        out = d.wait_finished("chunky", 30)
+        assert out is not None and out.finish_reason.name == "LENGTH"
+        computed, blocks = cap["chunky"]
+        assert computed == 149
+        check_decode_cache(d, "chunky", req.prompt_token_ids, blocks[0], 149)
+        assert p.steps >= 5
+    finally:
+        d.shutdown()
+        p.shutdown()
+
+
+@pytest.mark.parametrize("ptp,dtp", [(2, 1), (1, 2), (4, 2), (2, 2)])
+def test_tp_mismatch(ptp, dtp):
+    p, d = make_pd(p_kw={"tp": ptp}, d_kw={"tp": dtp})
+    try:
+        cap = _spy_add(d)
+        req = make_req("tp", 45, max_tokens=2, params={"remote_host": "127.0.0.1", "remote_port": p.proxy.rpc_port()})
+        d.add_request(req)
+        out = d.wait_finished("tp", 30)
+        assert out is not None and out.finish_reason.name == "LENGTH"
+        computed, blocks = cap["tp"]
+        assert computed == 44
+        check_decode_cache(d, "tp", req.prompt_token_ids, blocks[0], 44)
+    finally:
+        d.shutdown()
+        p.shutdown()
+
+
+def test_many_concurrent_requests(pd):
+    p, d = pd
+    cap = _spy_add(d)
+    reqs = [make_req(f"c{i}", 20 + 7 * i, max_tokens=2, seed=i,
+                     params={"remote_host": "127.0.0.1", "remote_port": p.proxy.rpc_port()}) for i in range(6)]
+    for r in reqs:
+        d.add_request(r)
+    for r in reqs:
+        out = d.wait_finished(r.request_id, 30)
+        assert out is not None and out.finish_reason.name == "LENGTH", r.request_id
+        computed, blocks = cap[r.request_id]
+        n = len(r.prompt_token_ids) - 1
+        assert computed == n
+    # decode blocks are released after finish; the caches were checked at admission time above
+    deadline = time.time() + 5
+    while time.time() < deadline and p.scheduler.kv_cache_manager.block_pool.num_free_blocks() != 63:
+        time.sleep(0.01)
+    assert p.scheduler.kv_cache_manager.block_pool.num_free_blocks() == 63
+    assert d.scheduler.kv_cache_manager.block_pool.num_free_blocks() == 63
+
+
+def test_abort_on_decode_side_releases_everything(pd):
+    """Abort while the load is outstanding: D drops the request, tells P, both free their blocks."""
+    p, d = pd
+    # P never gets its half, so D keeps polling
+    d.add_request(make_req("ab", 40, max_tokens=2, params=_dual_params(p)))
+    time.sleep(0.3)
+    d.abort_requests(["ab"])
+    out = d.wait_finished("ab", 20)
+    assert out is not None and out.finish_reason.name == "ABORT"
+    deadline = time.time() + 5
+    while time.time() < deadline and d.scheduler.kv_cache_manager.block_pool.num_free_blocks() != 63:
+        time.sleep(0.01)
+    assert d.scheduler.kv_cache_manager.block_pool.num_free_blocks() == 63
+    assert not d.connector._sched._loading
