@@ -146,6 +146,26 @@ int kvt_launch_copy_blocks(uint64_t src_base, uint64_t dst_base, const uint64_t*
                            uint32_t n, uint64_t src_capacity, uint64_t dst_capacity,
                            uint32_t* status, int grid_ctas, void* stream);
 
+// ---- the same copy for callers that must not allocate --------------------------------------
+// This entry point has no counterpart in the reference.  It exists for callers that cannot
+// allocate at call time (a transfer issued in an engine's steady state with a fully sized
+// pool, a recovery path that runs when the device is out of memory, a thread holding a lock the
+// allocator takes): the descriptor array and the status words live in a fixed array inside the
+// module's device image instead of memory the caller would have to allocate.  `host_triples`
+// is HOST memory (n × {src_off, dst_off, len} u64); it is copied to the device on `stream`.
+// `host_status` (optional, 2 × u32: code, detail) receives the status words after the kernel, on
+// `stream`; read it after synchronising the stream.  The call makes no allocation and frees
+// nothing.  The first call on a device (with that device current) also looks up and caches the
+// scratch address; make it before any stream capture begins.  One scratch array exists per
+// device: calls on one device that overlap in time race on it.
+// Returns 0, a positive cudaError_t, or one of the negative codes below.
+#define KVT_NOALLOC_MAX_DESCS 4096u      /* descriptors per call; 96 KiB + 256 B of device image */
+#define KVT_NOALLOC_ERR_TOO_MANY (-1)    /* n > KVT_NOALLOC_MAX_DESCS: rejected, nothing launched */
+#define KVT_NOALLOC_ERR_BAD_ARGS (-2)    /* null descriptors / base, or device index out of range */
+int kvt_copy_blocks_noalloc(uint64_t src_base, uint64_t dst_base, const uint64_t* host_triples,
+                            uint32_t n, uint64_t src_capacity, uint64_t dst_capacity,
+                            uint32_t* host_status, void* stream);
+
 // ---- completion flags ---------------------------------------------------------------------
 // Bounded device-side wait: returns through status[0]=KVT_ERR_FLAG_TIMEOUT when *flag has not
 // reached `value` within timeout_ns.  Never spins without limit.
