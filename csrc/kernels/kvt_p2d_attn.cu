@@ -26,6 +26,7 @@
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "kvt_kernels.h"
 
@@ -634,6 +635,13 @@ extern "C" int kvt_launch_p2d_attn(const KvtAttnLaunch* args, int grid_ctas, int
     if (tile_bytes % 128 != 0 || tile_bytes > kSmemBudget) return (int)cudaErrorInvalidValue;
     uint32_t stages = kSmemBudget / tile_bytes;
     if (stages > (uint32_t)kMaxStages) stages = kMaxStages;
+    // BLLM_KVTRANS_TMA_STAGES caps the pipeline depth: fewer stages = less shared memory per
+    // CTA, so that CTAs of launches on different streams can share an SM.
+    static const int env_stages = [] {
+      const char* v = getenv("BLLM_KVTRANS_TMA_STAGES");
+      return v != nullptr ? atoi(v) : 0;
+    }();
+    if (env_stages > 0 && stages > (uint32_t)env_stages) stages = (uint32_t)env_stages;
     const uint64_t per_cta = (total + grid - 1) / grid;
     if (stages > per_cta + 1) stages = (uint32_t)per_cta + 1;
     if (stages < 1) stages = 1;

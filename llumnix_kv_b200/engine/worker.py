@@ -59,6 +59,8 @@ class MiniWorker:
             kv_cache_groups=[KVCacheGroupSpec([layer_name(i) for i in range(mc.num_layers)])])
         self.connector: Optional[HybridConnector] = None
         self.proxy: Optional[WorkerProxy] = None
+        if self.device.type == "cuda":
+            torch.cuda.set_device(self.device)
         if with_connector and cfg.kv_transfer_config is not None:
             self.proxy = WorkerProxy(cfg, tp_rank, str(self.device))
             self.connector = HybridConnector(cfg, KVConnectorRole.WORKER, self.kv_cache_config, worker=self.proxy)
@@ -76,10 +78,10 @@ class MiniWorker:
         slot = (positions % lay.ntpb).to(self.device)
         view[blk, :, slot] = kv
 
-    def expected_kv(self, layer: int, token_ids: list, lo: int, hi: int) -> torch.Tensor:
+    def expected_kv(self, layer: int, token_ids: list, lo: int, hi: int, dtype=None) -> torch.Tensor:
         toks = torch.tensor(token_ids[lo:hi], device=self.device)
         pos = torch.arange(lo, hi, device=self.device)
-        return synthetic_kv(toks, pos, layer, self.head0, self.heads, self.layout.head_dim, self.dtype)
+        return synthetic_kv(toks, pos, layer, self.head0, self.heads, self.layout.head_dim, dtype or self.dtype)
 
     def read_kv(self, layer: int, blocks: list, lo: int, hi: int) -> torch.Tensor:
         lay = self.layout
@@ -88,8 +90,23 @@ class MiniWorker:
         blk = torch.tensor([blocks[p // lay.ntpb] for p in range(lo, hi)], device=self.device)
         return view[blk, :, pos % lay.ntpb]
 
+    def read_kv_mx(self, layer: int, blocks: list, lo: int, hi: int):
+        """(codes, UE8M0 exponents) of a block-scaled fp8 cache for prompt positions [lo, hi)."""
+        lay = self.layout
+        flat = self.kv_caches[layer_name(layer)]
+        pos = torch.arange(lo, hi, device=self.device)
+        blk = torch.tensor([blocks[p // lay.ntpb] for p in range(lo, hi)], device=self.device)
+        return lay.view(flat, torch.uint8)[blk, :, pos % lay.ntpb], lay.scale_view(flat)[blk, :, pos % lay.ntpb]
+
     def execute_model(self, sout: SchedulerOutput) -> dict:
         """One forward pass over the scheduled tokens; returns {reqid: sampled token}."""
+        if self.device.type == "cuda":
+            # the connector records its per-layer events on this device's current stream
+            with torch.cuda.device(self.device):
+                return self._execute_model(sout)
+        return self._execute_model(sout)
+
+    def _execute_model(self, sout: SchedulerOutput) -> dict:
         conn = self.connector
         meta = sout.kv_connector_metadata
         if conn is not None and meta is not None:
