@@ -8,10 +8,12 @@ namespace py = pybind11;
 namespace kvx {
 void bind_kernels(py::module_& m);
 void bind_engine(py::module_& m);
+void bind_store(py::module_& m);
 }  // namespace kvx
 
 PYBIND11_MODULE(kvtransfer_ops, m) {
   m.doc() = "B200-native KV transfer engine: C++ runtime and sm_100a kernels";
   kvx::bind_kernels(m);
   kvx::bind_engine(m);
+  kvx::bind_store(m);
 }

@@ -51,7 +51,7 @@ def _includes() -> list[str]:
 
 def sources() -> list[Path]:
     out: list[Path] = []
-    for sub in ("core", "plan", "transport", "kernels", "naming", "topo", "bind"):
+    for sub in ("core", "plan", "transport", "kernels", "naming", "topo", "store", "bind"):
         d = CSRC / sub
         if d.is_dir():
             out += sorted(d.glob("*.cpp")) + sorted(d.glob("*.cu"))

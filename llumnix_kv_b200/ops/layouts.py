@@ -44,6 +44,7 @@ class AttnLayout:
     elem_bytes: int         # 2 for bf16/fp16, 1 for fp8
     kv_count: int = 2
     mx_scaled: bool = False  # block-scaled fp8 page: payload followed by UE8M0 scales
+    block_stride_override: int = 0  # bytes between blocks when pages are embedded in larger records (0 = dense)
 
     # ---- derived byte strides -------------------------------------------------------
     @property
@@ -73,14 +74,18 @@ class AttnLayout:
 
     @property
     def layer_bytes(self) -> int:
-        return self.block_bytes * self.num_blocks
+        return (self.block_stride_override or self.block_bytes) * self.num_blocks
 
     def strides(self) -> Tuple[int, int, int, int]:
         """(block, kv, token, head) byte strides of the payload."""
         T, H, hb, B = self.ntpb, self.num_heads, self.head_bytes, self.num_blocks
+        if self.block_stride_override:
+            assert self.shape != CacheShape.FLASH, "K and V planes of this shape are not block-major"
+            dense = dataclasses.replace(self, block_stride_override=0).strides()
+            return (self.block_stride_override,) + dense[1:]
         if self.kv_count == 1:
             # single-tensor caches (MLA latent, indexer keys): [blocks, slots, width]
-            return (T * H * hb, 0, H * hb, hb)
+            return (self.block_bytes, 0, H * hb, hb)
         if self.shape == CacheShape.FLASH:
             assert not self.mx_scaled, "block-scaled pages need K and V inside one block"
             return (T * H * hb, B * T * H * hb, H * hb, hb)
@@ -152,7 +157,7 @@ class AttnLayout:
         return torch.as_strided(
             flat,
             (self.num_blocks, self.kv_count, self.ntpb, self.num_heads, self.scale_row_bytes),
-            (self.block_bytes, ks, ts, hs, 1),
+            (self.strides()[0], ks, ts, hs, 1),
             storage_offset=flat.storage_offset() + base,
         )
 
