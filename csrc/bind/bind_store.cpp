@@ -35,10 +35,10 @@ void bind_store(py::module_& m) {
   py::class_<KvStore, std::unique_ptr<KvStore>>(m, "KvStore")
       .def_static(
           "open",
-          [](const std::string& name, uint64_t slot_bytes, uint32_t n_slots, bool create, const std::string& tag) {
-            return std::unique_ptr<KvStore>(KvStore::open(name, slot_bytes, n_slots, create, tag));
+          [](const std::string& name, uint64_t slot_bytes, uint32_t n_slots, int mode, const std::string& tag) {
+            return std::unique_ptr<KvStore>(KvStore::open(name, slot_bytes, n_slots, mode, tag));
           },
-          py::arg("name"), py::arg("slot_bytes"), py::arg("n_slots"), py::arg("create"), py::arg("format_tag") = "")
+          py::arg("name"), py::arg("slot_bytes"), py::arg("n_slots"), py::arg("mode"), py::arg("format_tag") = "")
       .def_static("unlink", &KvStore::unlink)
       .def("lookup_prefix",
            [](KvStore& s, const py::bytes& keys) {

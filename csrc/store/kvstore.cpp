@@ -64,8 +64,9 @@ int64_t KvStore::now_ns() const {
   return (int64_t)ts.tv_sec * 1000000000ll + ts.tv_nsec + clock_skew_ns_;
 }
 
-KvStore* KvStore::open(const std::string& name, uint64_t slot_bytes, uint32_t n_slots, bool create,
+KvStore* KvStore::open(const std::string& name, uint64_t slot_bytes, uint32_t n_slots, int mode,
                        const std::string& format_tag) {
+  bool create = mode == kCreate;
   if (slot_bytes == 0 || n_slots == 0) throw std::invalid_argument("KvStore: slot_bytes and n_slots must be > 0");
   if (format_tag.size() >= sizeof(Header::format_tag)) throw std::invalid_argument("KvStore: format tag too long");
   const std::string sname = shm_name(name);
@@ -77,10 +78,18 @@ KvStore* KvStore::open(const std::string& name, uint64_t slot_bytes, uint32_t n_
   const uint64_t total = data_off + round_up(slot_bytes * n_slots, kPage);
 
   int fd;
-  if (create) {
+  if (mode == kAttachOrCreate) {
+    // whoever wins the exclusive create initialises the segment; everyone else attaches
+    fd = shm_open(sname.c_str(), O_CREAT | O_EXCL | O_RDWR, 0600);
+    if (fd < 0 && errno == EEXIST) return open(name, slot_bytes, n_slots, kAttach, format_tag);
+    if (fd < 0) throw std::runtime_error("KvStore: shm_open(create) failed: " + std::string(strerror(errno)));
+    create = true;
+  } else if (create) {
     shm_unlink(sname.c_str());
     fd = shm_open(sname.c_str(), O_CREAT | O_EXCL | O_RDWR, 0600);
     if (fd < 0) throw std::runtime_error("KvStore: shm_open(create) failed: " + std::string(strerror(errno)));
+  }
+  if (create) {
     if (ftruncate(fd, (off_t)total) != 0) {
       const int e = errno;
       close(fd);
@@ -90,8 +99,13 @@ KvStore* KvStore::open(const std::string& name, uint64_t slot_bytes, uint32_t n_
   } else {
     fd = shm_open(sname.c_str(), O_RDWR, 0600);
     if (fd < 0) throw std::runtime_error("KvStore: no such store '" + name + "': " + strerror(errno));
-    struct stat st;
-    if (fstat(fd, &st) != 0 || (uint64_t)st.st_size != total) {
+    // the creator may still be sizing the segment: give it a moment
+    struct stat st {};
+    for (int spin = 0; spin < 500; ++spin) {
+      if (fstat(fd, &st) == 0 && st.st_size != 0) break;
+      usleep(10000);
+    }
+    if ((uint64_t)st.st_size != total) {
       close(fd);
       throw std::runtime_error("KvStore: store '" + name + "' has a different geometry");
     }
@@ -129,6 +143,7 @@ KvStore* KvStore::open(const std::string& name, uint64_t slot_bytes, uint32_t n_
     h->n_free = n_slots;
     __atomic_store_n(&h->magic, kMagic, __ATOMIC_RELEASE);
   } else {
+    for (int spin = 0; spin < 500 && __atomic_load_n(&h->magic, __ATOMIC_ACQUIRE) != kMagic; ++spin) usleep(10000);
     if (__atomic_load_n(&h->magic, __ATOMIC_ACQUIRE) != kMagic || h->slot_bytes != slot_bytes ||
         h->n_slots != n_slots || format_tag != h->format_tag) {
       const std::string have = h->format_tag;

@@ -45,10 +45,12 @@ struct StoreStats {
 
 class KvStore {
  public:
-  // Creates (create=true; an existing segment of the same name is replaced) or attaches to
-  // the segment.  `format_tag` describes the slot format (layout id, sizes); attaching with a
-  // different tag, slot size or slot count fails.
-  static KvStore* open(const std::string& name, uint64_t slot_bytes, uint32_t n_slots, bool create,
+  // kAttach: the segment must exist.  kCreate: an existing segment of that name is replaced.
+  // kAttachOrCreate: the first opener creates it, everyone else attaches (engines of one node
+  // sharing a store).  `format_tag` describes the slot format (layout id, sizes); attaching
+  // with a different tag, slot size or slot count fails.
+  enum OpenMode : int { kAttach = 0, kCreate = 1, kAttachOrCreate = 2 };
+  static KvStore* open(const std::string& name, uint64_t slot_bytes, uint32_t n_slots, int mode,
                        const std::string& format_tag);
   static void unlink(const std::string& name);
   ~KvStore();

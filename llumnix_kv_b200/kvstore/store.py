@@ -57,7 +57,7 @@ def store_page_layout(engine: AttnLayout, n_slots: int, num_layers: int, fp8: bo
 
 class PinnedKVStore:
     def __init__(self, name: str, engine_layout: AttnLayout, layers: Sequence[torch.Tensor], tp_rank: int,
-                 tp_size: int, n_slots: int, create: bool, ttl_ms: int = 0, fp8: bool = False,
+                 tp_size: int, n_slots: int, create, ttl_ms: int = 0, fp8: bool = False,
                  model_tag: str = ""):
         from llumnix_kv_b200 import load_ops
 
@@ -74,7 +74,9 @@ class PinnedKVStore:
         self.slot_bytes = self.page_bytes * self.num_layers
         tag = (f"v1;L={self.num_layers};T={engine_layout.ntpb};H={engine_layout.num_heads};D={engine_layout.head_dim};"
                f"E={self.page.elem_bytes};kv={engine_layout.kv_count};mx={int(self.page.mx_scaled)}")
-        self.kv = self.K.KvStore.open(name, self.slot_bytes, n_slots, create, tag)
+        # create: False = attach, True = create (replacing), "auto" = attach or create
+        mode = 2 if create == "auto" else int(bool(create))
+        self.kv = self.K.KvStore.open(name, self.slot_bytes, n_slots, mode, tag)
         self.salt = f"{model_tag};{tp_rank}/{tp_size};{tag}".encode()
         n = self.kv.data_bytes
         self._buf = (ctypes.c_ubyte * n).from_address(self.kv.data_ptr)
