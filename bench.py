@@ -44,7 +44,7 @@ def parse_args():
     ap.add_argument("--slots", type=int, default=4, help="distinct request slots cycled through (each larger than L2)")
     ap.add_argument("--grid", type=int, default=0, help="CTAs of the transfer kernel (0 = tuned default)")
     ap.add_argument("--no-tma", action="store_true")
-    ap.add_argument("--streams", type=int, default=2, help="transfer streams the layers alternate over")
+    ap.add_argument("--streams", type=int, default=8, help="transfer streams the layers alternate over")
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--small", action="store_true", help="tiny case for profiler captures")
     ap.add_argument("--e2e-only", action="store_true")

@@ -87,7 +87,7 @@ bool env_bf162fp8_conversion() noexcept { return anyint("BLLM_KVTRANS_BF162FP8_C
 bool env_pad_last_attn_block() noexcept { return anyint("BLLM_KVTRANS_PAD_LAST_ATTN_BLOCK", 1) != 0; }
 bool env_rdma_staged() noexcept { return anyint("BLLM_KVTRANS_RDMA_STAGED", 0) != 0; }
 int env_nvlink_ctas() { return (int)anyint("BLLM_KVTRANS_NVLINK_CTAS", 0); }
-int env_nvlink_streams() { return (int)posint("BLLM_KVTRANS_NVLINK_STREAMS", 4); }
+int env_nvlink_streams() { return (int)posint("BLLM_KVTRANS_NVLINK_STREAMS", 8); }
 int env_dst_mxfp8() { return (int)anyint("BLLM_KVTRANS_DST_MXFP8", 0); }
 int env_use_tma() { return (int)anyint("BLLM_KVTRANS_USE_TMA", 1); }
 

@@ -623,7 +623,9 @@ extern "C" int kvt_launch_p2d_attn(const KvtAttnLaunch* args, int grid_ctas, int
   cudaGetDevice(&dev);
   int sms = 0;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  int grid = grid_ctas > 0 ? grid_ctas : sms;
+  // Default: four CTAs per SM.  Many small CTAs, each with one tile in flight, measured faster
+  // than one deep software pipeline per SM, and they let launches on different streams share SMs.
+  int grid = grid_ctas > 0 ? grid_ctas : 4 * sms;
   const uint64_t total = (uint64_t)(a.layer_end - a.layer_begin) * a.total_tiles * a.src.kv_count;
   if ((uint64_t)grid > total) grid = (int)total;
   if (threads <= 0) threads = use_tma ? 128 : 512;
@@ -633,8 +635,11 @@ extern "C" int kvt_launch_p2d_attn(const KvtAttnLaunch* args, int grid_ctas, int
   if (tma) {
     const uint32_t tile_bytes = a.src.head_bytes * a.n_heads * a.tile_tokens;
     if (tile_bytes % 128 != 0 || tile_bytes > kSmemBudget) return (int)cudaErrorInvalidValue;
-    uint32_t stages = kSmemBudget / tile_bytes;
+    // the shared-memory budget of an SM is split among the CTAs meant to live on it together
+    const uint32_t ctas_per_sm = sms > 0 ? (uint32_t)((grid + sms - 1) / sms) : 1u;
+    uint32_t stages = kSmemBudget / (ctas_per_sm > 0 ? ctas_per_sm : 1u) / tile_bytes;
     if (stages > (uint32_t)kMaxStages) stages = kMaxStages;
+    if (stages < 1) stages = 1;
     // BLLM_KVTRANS_TMA_STAGES caps the pipeline depth: fewer stages = less shared memory per
     // CTA, so that CTAs of launches on different streams can share an SM.
     static const int env_stages = [] {

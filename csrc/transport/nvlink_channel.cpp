@@ -245,7 +245,8 @@ class NvlinkChannel : public IChannel {
       a.mode = params_.mode;
       a.status = d_status_;
       int grid = env_nvlink_ctas();
-      if (grid <= 0) grid = std::max(1, static_cast<int>(kvt_sm_count(ctx_->device_id()) * env_kernel_copy_sm_usage()));
+      // four small CTAs per SM, scaled by the SM-usage knob that bounds what a transfer may take from the forward pass
+      if (grid <= 0) grid = std::max(1, static_cast<int>(4 * kvt_sm_count(ctx_->device_id()) * env_kernel_copy_sm_usage()));
       cuda_check(kvt_launch_p2d_attn(&a, grid, 0, use_tma_ ? 1 : 0, st.stream()), "kvt_launch_p2d_attn");
       return;
     }

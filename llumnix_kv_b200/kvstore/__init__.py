@@ -3,4 +3,4 @@
 ``KvStore`` (C++, csrc/store/kvstore.cpp) is the shared-memory index + arena; ``PinnedKVStore``
 binds one rank's paged cache to it and moves blocks with the transfer kernels.
 """
-from .store import PinnedKVStore, block_keys, store_page_layout  # noqa: F401
+from .store import PinnedKVStore, block_keys, store_format, store_page_layout, store_salt  # noqa: F401

@@ -55,6 +55,20 @@ def store_page_layout(engine: AttnLayout, n_slots: int, num_layers: int, fp8: bo
     return dataclasses.replace(dense, block_stride_override=dense.block_bytes * num_layers)
 
 
+def store_format(engine: AttnLayout, num_layers: int, fp8: bool = False) -> Tuple[int, str]:
+    """(slot_bytes, format tag) of a store serving caches of this geometry; every opener of one
+    store must agree on both."""
+    page = store_page_layout(engine, 1, num_layers, fp8)
+    tag = (f"v1;L={num_layers};T={engine.ntpb};H={engine.num_heads};D={engine.head_dim};"
+           f"E={page.elem_bytes};kv={engine.kv_count};mx={int(page.mx_scaled)}")
+    return page.block_bytes * num_layers, tag
+
+
+def store_salt(model_tag: str, tp_rank: int, tp_size: int, tag: str) -> bytes:
+    """What distinguishes the keys of one rank / model from another's inside a shared store."""
+    return f"{model_tag};{tp_rank}/{tp_size};{tag}".encode()
+
+
 class PinnedKVStore:
     def __init__(self, name: str, engine_layout: AttnLayout, layers: Sequence[torch.Tensor], tp_rank: int,
                  tp_size: int, n_slots: int, create, ttl_ms: int = 0, fp8: bool = False,
@@ -72,12 +86,12 @@ class PinnedKVStore:
         self.page = store_page_layout(engine_layout, n_slots, self.num_layers, fp8)
         self.page_bytes = self.page.block_bytes
         self.slot_bytes = self.page_bytes * self.num_layers
-        tag = (f"v1;L={self.num_layers};T={engine_layout.ntpb};H={engine_layout.num_heads};D={engine_layout.head_dim};"
-               f"E={self.page.elem_bytes};kv={engine_layout.kv_count};mx={int(self.page.mx_scaled)}")
+        slot_bytes, tag = store_format(engine_layout, self.num_layers, fp8)
+        assert slot_bytes == self.slot_bytes
         # create: False = attach, True = create (replacing), "auto" = attach or create
         mode = 2 if create == "auto" else int(bool(create))
         self.kv = self.K.KvStore.open(name, self.slot_bytes, n_slots, mode, tag)
-        self.salt = f"{model_tag};{tp_rank}/{tp_size};{tag}".encode()
+        self.salt = store_salt(model_tag, tp_rank, tp_size, tag)
         n = self.kv.data_bytes
         self._buf = (ctypes.c_ubyte * n).from_address(self.kv.data_ptr)
         self.host = torch.frombuffer(self._buf, dtype=torch.uint8)   # the arena as a CPU tensor

@@ -1,0 +1,158 @@
+"""The "kvs" backend end to end on CPU: prefixes saved to the shared host-DRAM store by one
+request are loaded by the next, by another engine of the node, and across cache layouts."""
+import os
+import time
+
+import pytest
+import torch
+
+from pd_helpers import make_cfg, make_req
+from llumnix_kv_b200 import load_ops
+from llumnix_kv_b200.engine.core import MiniEngineCore
+
+
+def make_kvs(name, store, **kw):
+    extra = {"kvs_name": store, "kvs_slots": 64}
+    extra.update(kw.pop("extra", {}))
+    return MiniEngineCore(make_cfg("kv_both", name, backend="kvs", extra=extra, **kw))
+
+
+def spy(e):
+    captured = {}
+    orig = e.scheduler.add_request
+
+    def f(r):
+        captured[r.request_id] = (r.num_computed_tokens, e.scheduler.kv_cache_manager.get_block_ids(r.request_id))
+        orig(r)
+
+    e.scheduler.add_request = f
+    return captured
+
+
+def wait_free(e, n, t=5.0):
+    pool = e.scheduler.kv_cache_manager.block_pool
+    end = time.time() + t
+    while time.time() < end and pool.num_free_blocks() != n:
+        time.sleep(0.01)
+    return pool.num_free_blocks()
+
+
+@pytest.fixture
+def store_name():
+    name = f"kvx_kvs_{os.getpid()}_{time.monotonic_ns() & 0xffff}"
+    yield name
+    load_ops().KvStore.unlink(name)
+
+
+def run(e, rid, n, max_tokens=2, seed=0, params=None):
+    req = make_req(rid, n, max_tokens=max_tokens, seed=seed, params=params)
+    e.add_request(req)
+    out = e.wait_finished(rid, 30)
+    assert out is not None and out.finish_reason.name == "LENGTH", rid
+    return req
+
+
+def test_second_request_loads_what_the_first_saved(store_name):
+    e = make_kvs("A", store_name)
+    try:
+        cap = spy(e)
+        r1 = run(e, "a", 100)
+        assert cap["a"][0] == 0                         # nothing in the store yet
+        assert wait_free(e, 63) == 63                   # save finished, extra references dropped
+        st = e.workers[0].connector._worker._backend._store.stats()
+        assert st["sealed"] == 6 and st["writing"] == 0  # 100 tokens = 6 full blocks of 16
+        # wipe the engine's own cache so that only the store can supply the prefix
+        for t in e.workers[0].kv_caches.values():
+            t.zero_()
+        r2 = run(e, "b", 100)
+        computed, blocks = cap["b"]
+        assert computed == 96
+        w = e.workers[0]
+        for layer in range(2):
+            assert torch.equal(w.read_kv(layer, blocks[0], 0, 96), w.expected_kv(layer, r2.prompt_token_ids, 0, 96))
+        assert e.output_tokens("a") == e.output_tokens("b")
+        # a prompt that shares only the first 40 tokens reuses 2 blocks
+        toks = list(r1.prompt_token_ids[:40]) + [5] * 60
+        from llumnix_kv_b200.engine.types import EngineCoreRequest, SamplingParams
+        e.add_request(EngineCoreRequest("c", toks, SamplingParams(max_tokens=1, extra_args={"kv_transfer_params": {}}), None))
+        assert e.wait_finished("c", 30) is not None
+        assert cap["c"][0] == 32
+        assert wait_free(e, 63) == 63
+        stats = e.connector.get_hybrid_connector_stats(64)
+        assert stats.save_done_count == 3 and stats.load_done_count >= 2 and stats.save_failed_count == 0
+    finally:
+        e.shutdown()
+
+
+def test_chunked_prefill_saves_block_by_block(store_name):
+    e = make_kvs("A", store_name, max_batched=40)
+    try:
+        run(e, "a", 130)
+        assert wait_free(e, 63) == 63
+        st = e.workers[0].connector._worker._backend._store.stats()
+        assert st["sealed"] == 8 and st["writing"] == 0
+        assert e.steps >= 4
+    finally:
+        e.shutdown()
+
+
+def test_another_engine_with_another_layout_loads_it(store_name):
+    a = make_kvs("A", store_name, cache_shape=2)
+    b = make_kvs("B", store_name, cache_shape=5)
+    try:
+        r = run(a, "x", 70)
+        assert wait_free(a, 63) == 63
+        cap = spy(b)
+        run(b, "y", 70)
+        computed, blocks = cap["y"]
+        assert computed == 64
+        w = b.workers[0]
+        for layer in range(2):
+            assert torch.equal(w.read_kv(layer, blocks[0], 0, 64), w.expected_kv(layer, r.prompt_token_ids, 0, 64))
+    finally:
+        a.shutdown()
+        b.shutdown()
+
+
+def test_tp2_needs_every_rank(store_name):
+    e = make_kvs("A", store_name, tp=2)
+    try:
+        cap = spy(e)
+        r = run(e, "a", 50)
+        assert wait_free(e, 63) == 63
+        # drop rank 1's copy of the second block: only one block can be loaded now
+        be = e.workers[1].connector._worker._backend
+        keys = be._store.keys(r.prompt_token_ids, 3)
+        assert be._store.kv.discard(keys[1])
+        run(e, "b", 50)
+        assert cap["b"][0] == 16
+    finally:
+        e.shutdown()
+
+
+def test_abort_mid_prefill_discards_unsealed_blocks(store_name):
+    e = make_kvs("A", store_name, max_batched=16, extra={"kvs_abort_grace_s": 0.05})
+    try:
+        e.add_request(make_req("a", 400, max_tokens=2))
+        time.sleep(0.05)
+        e.abort_requests(["a"])
+        out = e.wait_finished("a", 20)
+        assert out is not None and out.finish_reason.name == "ABORT"
+        assert wait_free(e, 63) == 63
+        st = e.workers[0].connector._worker._backend._store.stats()
+        assert st["writing"] == 0
+        assert not e.connector._sched._saving
+    finally:
+        e.shutdown()
+
+
+def test_nosave_and_min_length(store_name, monkeypatch):
+    e = make_kvs("A", store_name)
+    try:
+        run(e, "a", 60, params={"kvs_nosave": True})
+        assert e.workers[0].connector._worker._backend._store.stats()["used"] == 0
+        monkeypatch.setenv("VLLM_KVS_ON_MIN_LENGTH", "100")
+        run(e, "b", 60)
+        assert e.workers[0].connector._worker._backend._store.stats()["used"] == 0
+    finally:
+        e.shutdown()
