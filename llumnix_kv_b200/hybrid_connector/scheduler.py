@@ -515,6 +515,7 @@ class HybridScheduler:
             await self.mark_loaded(req, ioret)
         else:
             # the worker will report LOAD_DONE; make sure a step happens to deliver the metadata
+            set_param(req, "_hb_promised_tokens", rmt)
             self._q_append(self._prepared, req.request_id)
 
     async def mark_loaded(self, req: Request, ioret: Optional[IoRet] = None) -> None:
@@ -560,6 +561,9 @@ class HybridScheduler:
         if state is None:
             return
         merged = state.merge()
+        if merged.n is None and merged.ex is None:
+            # a worker that reports no count loaded everything the backend promised
+            merged.n = get_param(state._req, "_hb_promised_tokens", 0)
         logger.info("mark loaded. reqid=%s ioret=%s", state._req.request_id, merged)
         state._req.trace_wrapper.on_req_kv_end("load")
         self._add_ts(state._req, "load_done")
