@@ -123,6 +123,11 @@ class MiniEngineCore:
     def _publish(self, outputs: Optional[dict]) -> None:
         if not outputs:
             return
+        if self.connector is not None:
+            # outputs of requests that belong to a migration-aware frontend leave through the backend
+            hook = getattr(self.connector._sched._backend, "on_outputs", None)
+            if hook is not None:
+                hook(outputs)
         with self._cv:
             for client, outs in outputs.items():
                 for o in outs:

@@ -112,7 +112,7 @@ class MiniScheduler:
             req.status = RequestStatus.RUNNING
             self.running.append(req)
             sout.scheduled_new_reqs.append(NewRequestData(
-                req.request_id, list(req.prompt_token_ids), self.kv_cache_manager.get_block_ids(req.request_id),
+                req.request_id, list(req.all_token_ids), self.kv_cache_manager.get_block_ids(req.request_id),
                 req.num_computed_tokens))
             self._scheduled_before.add(req.request_id)
             sout.num_scheduled_tokens[req.request_id] = n

@@ -103,6 +103,7 @@ class KVTState:
     dinfo: KVTDInfo
     maxtokens: int
     untouched: bool = True      # no chunk of this request has been planned yet
+    frozen: bool = False        # everything up to maxtokens left in one frozen step: nothing more to plan
 
 
 @dataclass
@@ -444,6 +445,7 @@ class PBackend(HybridBackend):
     # ---- scheduler side: per-step planning (core thread) ----------------------------------------------
     def _freeze_meta(self, reqid: str, pblkids: list, kvtstate: KVTState) -> PReqMeta:
         d = kvtstate.dinfo
+        kvtstate.frozen = True
         return PReqMeta(reqid=reqid, d_inst_id=d.instid, p_block_ids=pblkids, d_block_ids=d.blkids,
                         seen_tokens=d.cached_tokens, new_tokens=kvtstate.maxtokens - d.cached_tokens,
                         has_last_token=True, d_workers_info=d.d_workers_info, has_freeze=True)
@@ -582,8 +584,8 @@ class PBackend(HybridBackend):
             self._update_dual_req_done(req, has_last, p_block_ids)
             return
         d_computed = kvtstate.dinfo.cached_tokens
-        if end <= d_computed:
-            return
+        if end <= d_computed or kvtstate.frozen:
+            return   # (a migrating request keeps decoding here until it is suspended)
         has_last = end >= kvtstate.maxtokens
         if substep_mode and not has_last:
             return

@@ -1,0 +1,130 @@
+"""Live migration between engines on CPU: a frontend hands requests to engines, moves them while
+they decode, and gets one uninterrupted token stream whichever engines produced it."""
+import time
+
+import pytest
+import torch
+
+from pd_helpers import make_cfg, make_req
+from llumnix_kv_b200.engine.core import MiniEngineCore
+from llumnix_kv_b200.hybrid_connector.migration import int2ipport, ipport2int, is_migration
+from llumnix_kv_b200.hybrid_connector.migration.frontend import MigrationCli
+
+LOCAL = {"ali_llumnix_disagg": False}
+
+
+def make_engine(name, **kw):
+    return MiniEngineCore(make_cfg("kv_both", name, backend="kvt+migration", **kw))
+
+
+def addr(e):
+    return ("127.0.0.1", e.proxy.rpc_port())
+
+
+def baseline_tokens(n_prompt, max_tokens, seed=0):
+    """What one engine produces for this prompt without any migration."""
+    e = MiniEngineCore(make_cfg("kv_both", "base", backend="kvt+migration"))
+    try:
+        e.add_request(make_req("b", n_prompt, max_tokens=max_tokens, seed=seed, params=LOCAL))
+        assert e.wait_finished("b", 30) is not None
+        return e.output_tokens("b")
+    finally:
+        e.shutdown()
+
+
+def wait_free(e, n, t=5.0):
+    pool = e.scheduler.kv_cache_manager.block_pool
+    end = time.time() + t
+    while time.time() < end and pool.num_free_blocks() != n:
+        time.sleep(0.01)
+    return pool.num_free_blocks()
+
+
+def test_ipport_roundtrip():
+    v = ipport2int("10.1.2.3", 40000)
+    assert is_migration(v) and int2ipport(v) == ("10.1.2.3", 40000) and not is_migration(7)
+
+
+@pytest.fixture
+def two():
+    a, b = make_engine("A"), make_engine("B")
+    yield a, b
+    a.shutdown()
+    b.shutdown()
+
+
+def test_outputs_reach_the_frontend_without_migration(two):
+    a, b = two
+    cli = MigrationCli([addr(a), addr(b)])
+    try:
+        cli.add_request(make_req("r", 30, max_tokens=5, params=LOCAL))
+        st = cli.wait("r", 30)
+        assert st is not None and st.finish_reason == 1 and st.tokens == baseline_tokens(30, 5)
+        assert st.migrations == 0
+    finally:
+        cli.close()
+
+
+def test_migrate_while_decoding_moves_kv_and_continues_the_stream(two):
+    a, b = two
+    cli = MigrationCli([addr(a), addr(b)], migrate_after_first_token=True)
+    try:
+        slow = a.step
+        a.step = lambda: (time.sleep(0.01), slow())[1]       # keep the source decoding while it is asked to let go
+        cli.add_request(make_req("m", 45, max_tokens=40, params=LOCAL), engine=addr(a))
+        st = cli.wait("m", 60)
+        assert st is not None and st.finish_reason == 1
+        assert st.migrations == 1 and st.engines_seen == [addr(a), addr(b)]
+        assert st.tokens == baseline_tokens(45, 40)
+        assert b.steps > 3                                    # the destination really decoded
+        assert wait_free(a, 63) == 63 and wait_free(b, 63) == 63
+        assert not a.connector._sched._saving and not b.connector._sched._loading
+        assert b.connector._sched._backend.migration_status() == {"migrate_in": {}, "migrate_out": []}
+    finally:
+        cli.close()
+
+
+def test_migrate_before_first_token_restarts_on_destination(two):
+    a, b = two
+    cli = MigrationCli([addr(a), addr(b)])
+    try:
+        a._stop = True           # the source engine loop is frozen: the request stays waiting there
+        a.input_queue.put_nowait((None, None))
+        time.sleep(0.1)
+        cli.add_request(make_req("w", 33, max_tokens=4, params=LOCAL), engine=addr(a))
+        a._stop = False
+        a.start()
+        code = cli.migrate("w", addr(b))
+        assert code == 0
+        st = cli.wait("w", 60)
+        assert st is not None and st.tokens == baseline_tokens(33, 4)
+    finally:
+        cli.close()
+
+
+def test_admission_control_rejects_when_busy(two, monkeypatch):
+    a, b = two
+    cli = MigrationCli([addr(a), addr(b)])
+    try:
+        monkeypatch.setenv("LLUMNIX_MAX_REQ_MIG_IN", "0")
+        cli.add_request(make_req("x", 20, max_tokens=30, params=LOCAL), engine=addr(a))
+        assert cli.migrate("x", addr(b)) == 1001
+        assert cli.rejected == 1
+        st = cli.wait("x", 60)                                # it simply finishes where it was
+        assert st is not None and st.migrations == 0 and len(st.tokens) == 30
+    finally:
+        cli.close()
+
+
+def test_abort_through_the_frontend(two):
+    a, b = two
+    cli = MigrationCli([addr(a), addr(b)])
+    try:
+        cli.add_request(make_req("k", 20, max_tokens=100000, params=LOCAL), engine=addr(a))
+        time.sleep(0.2)
+        cli.abort("k")
+        st = cli.wait("k", 30)
+        assert st is not None and st.finish_reason == 2
+        assert wait_free(a, 63) == 63
+    finally:
+        cli.close()
