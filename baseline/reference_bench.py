@@ -80,7 +80,7 @@ def main(args) -> None:
                                 str(args.warmup), str(args.steps)], capture_output=True, text=True, timeout=1200)
             if r.returncode != 0:
                 raise RuntimeError(f"ref_datapath exit {r.returncode}: {r.stderr[-300:]}")
-            f = r.stdout.split()
+            f = r.stdout.strip().splitlines()[-1].split()   # the reference prints its env settings first
             ms, nbytes, ok = float(f[0]), int(f[1]), f[2] == "1"
         if world > 1:
             import torch
