@@ -28,6 +28,7 @@ import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
+os.environ.setdefault("BLLM_KVTRANS_QUIET_ENV", "1")   # stdout carries exactly one JSON line
 
 METRIC = "p2d_kv_transfer_GBps"
 MODEL = "llama-3-8b-kv(32L,8kvh,128d,bf16,block16,NHD->HND)"
@@ -47,7 +48,12 @@ def parse_args():
     ap.add_argument("--streams", type=int, default=8, help="transfer streams the layers alternate over")
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--small", action="store_true", help="tiny case for profiler captures")
+    ap.add_argument("--mode", default="p2d", choices=["p2d", "kvstore", "migration"],
+                    help="p2d: prefill->decode transfer (the headline); kvstore: host-DRAM store save/load GB/s; "
+                         "migration: decode->decode latency against the number of blocks")
     ap.add_argument("--e2e-only", action="store_true")
+    ap.add_argument("--e2e-path", default="engine", choices=["engine", "ops"],
+                    help="end-to-end number through KVTransferClient/Server (engine) or the AttnTransfer op (ops)")
     return ap.parse_args()
 
 
@@ -139,6 +145,39 @@ def main():
     if args.small:
         args.tokens, args.slots, args.layers = 2048, 2, 4
 
+    if args.mode == "kvstore":
+        from llumnix_kv_b200.bench_support import kvstore_bandwidth
+
+        res = kvstore_bandwidth(dev, n_layers=args.layers, n_blocks=256 if args.small else 1024)
+        if rank == 0:
+            print(json.dumps({"metric": "kvstore_save_load_GBps", "unit": "GB/s", "n_gpus": 1, "dtype": "bf16",
+                              "config": {"model": MODEL, "layers": args.layers, "store": "pinned host DRAM (POSIX shm)"},
+                              "result": res}))
+        return
+    if args.mode == "migration":
+        from llumnix_kv_b200.bench_support import migration_sweep
+        from llumnix_kv_b200.ops.layouts import CacheShape
+
+        blocks = 256 if args.small else 4096
+        pair = PDBenchPair(K, rank, world, dev, tokens=blocks * 16, requests=1, slots=1, n_layers=args.layers,
+                           use_tma=not args.no_tma, grid=args.grid, n_streams=1, src_shape=CacheShape.FLASHINFER,
+                           dst_shape=CacheShape.FLASHINFER)
+        pair.setup_engine()
+        res = migration_sweep(pair)
+        pair.touched.add(0)
+        pair.verify()
+        pair.close_engine()
+        if rank == 0:
+            print(json.dumps({"metric": "migration_latency_us_vs_blocks", "unit": "us", "n_gpus": args.gpus,
+                              "higher_is_better": False, "dtype": "bf16",
+                              "config": {"model": MODEL.replace("NHD->HND", "HND->HND"), "layers": args.layers,
+                                         "transport": pair.transport_name,
+                                         "api": "KVTransferClient.start_req_send (frozen step) + drain"},
+                              "result": res}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
     pair = PDBenchPair(K, rank, world, dev, tokens=args.tokens, requests=args.requests, slots=args.slots,
                        n_layers=args.layers, use_tma=not args.no_tma, grid=args.grid, n_streams=args.streams)
 
@@ -171,8 +210,19 @@ def main():
     ms_dev, clocks = (0.0, {}) if args.e2e_only else timed(pair.step_device, args.steps, args.warmup)
     # ---- end to end through the public API: pinned block tables -> H2D, 32 per-layer
     #      launches, completion word + status read back on the host every step ------------
-    ms_e2e, clocks_e2e = timed(pair.step_e2e, args.steps, args.warmup)
+    if args.e2e_path == "engine":
+        pair.setup_engine()
+        barrier()
+        ms_e2e, clocks_e2e = timed(pair.step_engine, args.steps, args.warmup)
+        h2d_bytes, d2h_bytes = pair.engine_h2d_bytes, pair.engine_d2h_bytes
+        e2e_api = "KVTransferClient.submit_req_send2/start_send_step/record_event x layers/flush_send_step/drain"
+    else:
+        ms_e2e, clocks_e2e = timed(pair.step_e2e, args.steps, args.warmup)
+        h2d_bytes, d2h_bytes = pair.h2d_bytes_per_step, pair.d2h_bytes_per_step
+        e2e_api = "AttnTransfer.plan/launch x layers + completion flag + status read"
     pair.verify()
+    if args.e2e_path == "engine":
+        pair.close_engine()
 
     n_pairs = pair.n_pairs
     bytes_per_step = pair.bytes_per_step
@@ -206,7 +256,7 @@ def main():
                          "fraction": round(value / n_pairs / roof, 3)},
             "clocks": clocks or clocks_e2e,
             "e2e": {"value": round(agg(ms_e2e), 2), "unit": "GB/s", "ms_per_step": round(ms_e2e / args.steps, 4),
-                    "h2d_bytes_per_step": pair.h2d_bytes_per_step, "d2h_bytes_per_step": pair.d2h_bytes_per_step,
+                    "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "api": e2e_api,
                     "clocks": clocks_e2e},
             "gpu_launches": pair.launches_per_step * args.steps * (1 if args.e2e_only else 2) + args.steps,
         }

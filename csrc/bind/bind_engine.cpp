@@ -7,6 +7,8 @@
 
 #include "core/client.h"
 #include "core/envcfg.h"
+#include "core/gdr.h"
+#include "core/monitor.h"
 #include "core/fault_inject.h"
 #include "naming/naming.h"
 #include "plan/device_plan.h"
@@ -521,6 +523,20 @@ void bind_engine(py::module_& m) {
   m.def("env_cache_shape", &env_cache_shape);
   m.def("env_port_base", &env_port_base);
   m.def("new_id", &new_id);
+  m.def("monitor_start", &monitor_start, "start the process monitor; returns its TCP port");
+  m.def("monitor_stop", &monitor_stop);
+  m.def("monitor_port", &monitor_port);
+  m.def("monitor_handle_line", &monitor_handle_line);
+  m.def("envcfg_dump", &envcfg_dump);
+  m.def("gdr_available", [] {
+    std::string why;
+    const bool ok = gdr_available(&why);
+    return py::make_tuple(ok, why);
+  });
+  m.def("crc32_bytes", [](py::bytes b, uint32_t seed) {
+    const std::string s = b;
+    return crc32_bytes(s.data(), s.size(), seed);
+  }, py::arg("data"), py::arg("seed") = 0);
   m.def("discover_topology", [] { return discover_topology().to_json(); },
         "NVLink / NVSwitch topology of this process's visible GPUs as a JSON string");
   m.attr("EMPTY_STEP_ID") = EMPTY_STEP_ID;

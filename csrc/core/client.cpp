@@ -163,6 +163,7 @@ void KvTransferClient::start_req_send(std::vector<ReqMeta>& metas, size_t stepid
   if (st.empty()) return;
   auto step = std::make_shared<Step>(stepid);
   // the data is complete: the step is born with every layer recorded and ready
+  step->frozen = true;
   step->notify_layer_recorded(ctx_->num_layers());
   step->notify_layer_ready(ctx_->num_layers());
   step->flush_send_ts = step->wait_layers_start_ts = step->wait_layers_end_ts = step->start_send_ts;

@@ -18,7 +18,7 @@ bool g_quiet = getenv("BLLM_KVTRANS_QUIET_ENV") != nullptr;
 
 void echo(const char* env, const char* val, const std::string& def) {
   if (g_quiet) return;
-  fprintf(stdout, "kvtenv: env=%s val=%s def=%s\n", env, val == nullptr ? "NULL" : val, def.c_str());
+  fprintf(stderr, "kvtenv: env=%s val=%s def=%s\n", env, val == nullptr ? "NULL" : val, def.c_str());
   fflush(stdout);
 }
 
@@ -165,6 +165,14 @@ const char* env_nic_name() noexcept {
     if (v != nullptr) g_nic = v;
   }
   return g_nic.empty() ? nullptr : g_nic.c_str();
+}
+
+std::string envcfg_dump() {
+  std::lock_guard<std::mutex> g(g_mu);
+  std::string out;
+  for (const auto& kv : g_int_cache) out += kv.first + "=" + std::to_string(kv.second) + "\n";
+  for (const auto& kv : g_dbl_cache) out += kv.first + "=" + std::to_string(kv.second) + "\n";
+  return out.empty() ? "(no setting read yet)\n" : out;
 }
 
 void envcfg_reset_for_test() {

@@ -61,5 +61,6 @@ int env_dst_mxfp8();
 int env_use_tma();
 
 void envcfg_reset_for_test();
+std::string envcfg_dump();   // every setting resolved so far, one key=value per line
 
 }  // namespace kvx

@@ -170,7 +170,9 @@ struct KvSendStub::Impl {
   void do_send(BatchSendTask& batch, bool device_planned) {
     wait_us = 0;
     const bool by_record = ch->device_ordered();
-    for (uint32_t i = start_layer; i < num_layers; ++i) {
+    // a frozen step has nothing to wait for: let the channel move all layers in one go
+    const bool whole = batch.step->frozen && ch->send_layers(start_layer, num_layers, batch.step.get());
+    for (uint32_t i = start_layer; i < num_layers && !whole; ++i) {
       TimeWatch w;
       if (by_record) batch.step->wait_layer_recorded(i); else batch.step->wait_layer_ready(i);
       wait_us += w.get_elapse_us();

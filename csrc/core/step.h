@@ -27,6 +27,7 @@ class Step {
   Timepoint flush_send_ts;                 // written by the engine thread
   Timepoint wait_layers_start_ts;          // written by the wait-layers thread
   Timepoint wait_layers_end_ts;
+  bool frozen = false;                     // born with every layer complete (freeze / migration steps)
 
   explicit Step(size_t idx) : step_idx(idx) {}
   ~Step();

@@ -32,6 +32,12 @@ class IChannel {
   virtual bool device_ordered() const { return false; }
   // May be asynchronous; flush() blocks until every send_data of the batch has landed.
   virtual void send_data(size_t layer_index, Step* step) = 0;
+  // Every layer of [begin, end) at once, for steps whose data is already complete.  Return
+  // false to be driven layer by layer through send_data().
+  virtual bool send_layers(size_t layer_begin, size_t layer_end, Step* step) {
+    (void)layer_begin; (void)layer_end; (void)step;
+    return false;
+  }
   // `out` receives key=value metrics of the batch.
   virtual void flush(std::string& out) = 0;
   virtual bool is_active() { return true; }

@@ -218,13 +218,21 @@ class NvlinkChannel : public IChannel {
     data.clear();
   }
 
-  void send_data(size_t layer, Step* step) override {
+  bool send_layers(size_t layer_begin, size_t layer_end, Step* step) override {
     (void)step;
+    if (!fused_ || layer_end <= layer_begin) return false;
+    if (plan_.n_reqs == 0) return true;
     cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
-    DeviceStage& st = *stages_[layer % stages_.size()];
-    st.wait_event(ctx_->cuda_barrier()->event(static_cast<uint32_t>(layer)));
-    if (fused_) {
-      if (plan_.n_reqs == 0) return;
+    // one launch over the layer range on the stream that carried the plan; layer events are
+    // recorded in order on one stream, so the last one implies the others
+    DeviceStage& st = *stages_[0];
+    st.wait_event(ctx_->cuda_barrier()->event(static_cast<uint32_t>(layer_end - 1)));
+    launch_fused(layer_begin, layer_end, st);
+    return true;
+  }
+
+  void launch_fused(size_t layer_begin, size_t layer_end, DeviceStage& st) {
+    {
       KvtAttnLaunch a{};
       a.src_layers = d_src_layers_.p;
       a.dst_layers = d_dst_layers_.p;
@@ -232,8 +240,8 @@ class NvlinkChannel : public IChannel {
       a.dst_maps = use_tma_ ? d_dst_maps_.p : nullptr;
       a.src = params_.src;
       a.dst = params_.dst;
-      a.layer_begin = static_cast<uint32_t>(layer);
-      a.layer_end = static_cast<uint32_t>(layer) + 1;
+      a.layer_begin = static_cast<uint32_t>(layer_begin);
+      a.layer_end = static_cast<uint32_t>(layer_end);
       a.reqs = reinterpret_cast<const KvtReqDesc*>(d_plan_);
       a.n_reqs = plan_.n_reqs;
       a.total_tiles = plan_.total_tiles;
@@ -248,6 +256,16 @@ class NvlinkChannel : public IChannel {
       // four small CTAs per SM, scaled by the SM-usage knob that bounds what a transfer may take from the forward pass
       if (grid <= 0) grid = std::max(1, static_cast<int>(4 * kvt_sm_count(ctx_->device_id()) * env_kernel_copy_sm_usage()));
       cuda_check(kvt_launch_p2d_attn(&a, grid, 0, use_tma_ ? 1 : 0, st.stream()), "kvt_launch_p2d_attn");
+    }
+  }
+
+  void send_data(size_t layer, Step* step) override {
+    (void)step;
+    cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
+    DeviceStage& st = *stages_[layer % stages_.size()];
+    st.wait_event(ctx_->cuda_barrier()->event(static_cast<uint32_t>(layer)));
+    if (fused_) {
+      if (plan_.n_reqs != 0) launch_fused(layer, layer + 1, st);
       return;
     }
     const auto& addrs = ctx_->layer_data_address();

@@ -26,7 +26,8 @@ HEAD_DIM = 128
 
 class PDBenchPair:
     def __init__(self, K, rank: int, world: int, dev, tokens: int, requests: int, slots: int, n_layers: int,
-                 use_tma: bool, grid: int, n_streams: int = 2):
+                 use_tma: bool, grid: int, n_streams: int = 2, src_shape: CacheShape = CacheShape.FLASH,
+                 dst_shape: CacheShape = CacheShape.FLASHINFER):
         import torch.distributed as dist
 
         self.K, self.rank, self.world, self.dev = K, rank, world, dev
@@ -38,8 +39,8 @@ class PDBenchPair:
         blocks_per_req = (tokens + BLOCK - 1) // BLOCK
         self.tokens = tokens
         n_blocks = slots * requests * blocks_per_req + 1
-        self.src_l = AttnLayout(CacheShape.FLASH, n_blocks, BLOCK, KV_HEADS, HEAD_DIM, 2)
-        self.dst_l = AttnLayout(CacheShape.FLASHINFER, n_blocks, BLOCK, KV_HEADS, HEAD_DIM, 2)
+        self.src_l = AttnLayout(src_shape, n_blocks, BLOCK, KV_HEADS, HEAD_DIM, 2)
+        self.dst_l = AttnLayout(dst_shape, n_blocks, BLOCK, KV_HEADS, HEAD_DIM, 2)
         self.slot_bytes = requests * blocks_per_req * self.src_l.block_bytes * n_layers
         self.bytes_per_step = requests * tokens * self.src_l.token_bytes * n_layers
         self.launches_per_step = n_layers
@@ -165,6 +166,64 @@ class PDBenchPair:
             raise RuntimeError(f"transfer step {self.seq} failed: flag={self.flag.value} "
                                f"status={self.status_host.tolist()}")
 
+    # ---- the same step through the engine's public API ---------------------------------------
+    def setup_engine(self) -> None:
+        """KVTransferServer on the decode rank, KVTransferClient on the prefill rank, NVLink
+        transport; the WorkerInfo string travels the way a decode engine hands it to a prefill
+        engine inside a request."""
+        from .kv_transfer_impl import KVTransferClient, KVTransferProtocolType as PT, KVTransferServer
+
+        pair = self._pair_id() if self.is_sender else self.rank - self.n_pairs
+        self.dst_inst = f"D{pair}|0|1"
+        self.srv = self.cli = None
+        winfo = None
+        if self.is_receiver:
+            lb = self.dst_l.layer_bytes
+            layers = [self.dst[i * lb:(i + 1) * lb] for i in range(self.n_layers)]
+            self.srv = KVTransferServer(self.dst_inst, 1, 0, 0, self.dst_l.block_bytes, self.dst_l.token_bytes, "fake://",
+                                        layers, [PT.NVLINK], num_kv_heads=KV_HEADS, cache_shape=int(self.dst_l.shape))
+            winfo = self.srv.worker_info()
+        if self.world > 1:
+            import torch.distributed as dist
+
+            infos = [None] * self.world
+            dist.all_gather_object(infos, winfo)
+            if self.is_sender:
+                winfo = infos[self.rank + self.n_pairs]
+        self.winfo = winfo
+        if self.is_sender:
+            lb = self.src_l.layer_bytes
+            layers = [self.src[i * lb:(i + 1) * lb] for i in range(self.n_layers)]
+            self.cli = KVTransferClient(f"P{pair}|0|1", 1, 0, 0, self.src_l.block_bytes, self.src_l.token_bytes, "fake://",
+                                        layers, [PT.NVLINK], num_kv_heads=KV_HEADS, cache_shape=int(self.src_l.shape))
+        self.engine_seq = 0
+        self.engine_h2d_bytes = self.h2d_bytes_per_step
+        self.engine_d2h_bytes = 8      # the channel reads its two status words back before it reports a batch done
+
+    def step_engine(self, i: int) -> None:
+        """What a prefill worker does in one engine step, through KVTransferClient: submit the
+        requests, open the step, mark each layer's KV as written on the forward stream, close
+        the step and wait until the engine has reported every request done."""
+        if not self.is_sender:
+            return
+        self.engine_seq += 1
+        stepid = 4096 + self.engine_seq
+        slot = i % self.slots
+        self.touched.add(slot)
+        cli = self.cli
+        for r, c in enumerate(self.slot_chunks[slot]):
+            cli.submit_req_send2(self.dst_inst, 0, f"b{self.engine_seq}.{r}", 0, c.new_tokens, True, list(c.src_blocks),
+                                 list(c.dst_blocks), self.winfo, stepid=stepid)
+        cli.start_send_step(stepid, 1)
+        for layer in range(self.n_layers):
+            cli.record_event(layer, self.stream)
+        cli.flush_send_step()
+        cli.drain()
+
+    def close_engine(self) -> None:
+        if getattr(self, "srv", None) is not None:
+            self.srv.stop()
+
     # ---- correctness after the timed runs ---------------------------------------------------
     def verify(self, layers=(0,)) -> None:
         torch.cuda.synchronize()
@@ -209,3 +268,104 @@ class PDBenchPair:
                     db = torch.tensor(list(c.dst_blocks[:nb_full]), device=self.dev)
                     if not torch.equal(dv[db], sv[sb]):
                         raise RuntimeError(f"rank {self.rank}: destination cache mismatch in layer {layer}")
+
+
+# ---------------------------------------------------------------------------------------------
+# other headline measurements: host-DRAM store bandwidth, migration latency vs. block count
+# ---------------------------------------------------------------------------------------------
+def kvstore_bandwidth(dev, n_layers: int = 32, n_blocks: int = 1024, iters: int = 4) -> dict:
+    """Save / load GB/s of the pinned host-DRAM store for Llama-3-8B-shaped KV (bf16 pages and
+    block-scaled fp8 pages), device-timed on the store's stream, plus the pinned cudaMemcpy
+    baseline of the same box."""
+    import os
+
+    from . import load_ops
+    from .kvstore import PinnedKVStore
+
+    res: dict = {}
+    for fp8 in (False, True):
+        lay = AttnLayout(CacheShape.FLASH, n_blocks + 8, BLOCK, KV_HEADS, HEAD_DIM, 2)
+        layers = [lay.alloc(dev, fill="normal", seed=i) for i in range(n_layers)]
+        name = f"kvx_bw_{os.getpid()}_{int(fp8)}"
+        st = PinnedKVStore(name, lay, layers, 0, 1, n_blocks, create=True, fp8=fp8)
+        try:
+            keys = st.keys(list(range(BLOCK * n_blocks)), n_blocks)
+            new, _full = st.reserve(keys)
+            blocks, slots = list(range(1, n_blocks + 1)), [s for _, s in new]
+            payload = n_blocks * lay.block_bytes * n_layers
+            for what, fn in (("save", st.save_layers), ("load", st.load_layers)):
+                ts = []
+                for _ in range(iters):
+                    torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(st.stream)
+                    fn(0, n_layers, blocks, slots)
+                    e1.record(st.stream)
+                    torch.cuda.synchronize()
+                    ts.append(e0.elapsed_time(e1))
+                st.check_status()
+                ms = min(ts[1:])
+                res[f"{what}_{'fp8' if fp8 else 'bf16'}"] = {
+                    "ms": round(ms, 3), "engine_GBps": round(payload / ms / 1e6, 1),
+                    "pcie_GBps": round(st.slot_bytes * n_blocks / ms / 1e6, 1)}
+            st.seal(keys)
+        finally:
+            st.close()
+            load_ops().KvStore.unlink(name)
+        del layers
+    n = 1 << 30
+    h = torch.empty(n, dtype=torch.uint8, pin_memory=True)
+    d = torch.empty(n, dtype=torch.uint8, device=dev)
+    for what in ("d2h", "h2d"):
+        ts = []
+        for _ in range(3):
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            if what == "d2h":
+                h.copy_(d, non_blocking=True)
+            else:
+                d.copy_(h, non_blocking=True)
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        res[f"cudaMemcpy_pinned_{what}_GBps"] = round(n / min(ts) / 1e6, 1)
+    return res
+
+
+def migration_sweep(pair: "PDBenchPair", counts=(1, 4, 16, 64, 256, 1024, 4096), iters: int = 8) -> list:
+    """Latency of moving a running request's KV (all layers, one frozen step) between two decode
+    caches of the same layout, against the number of blocks, through KVTransferClient.start_req_send.
+    ``pair`` must have been built with identical source and destination layouts and
+    ``setup_engine()`` called."""
+    from .kv_transfer_impl import ReqMeta
+
+    out = []
+    seq = 0
+    for n in counts:
+        chunk = pair.slot_chunks[0][0]
+        if n > len(chunk.src_blocks):
+            break
+        ts = []
+        if pair.is_sender:
+            for _ in range(iters):
+                seq += 1
+                m = ReqMeta()
+                m.dst_inst, m.dst_worker, m.reqid = pair.dst_inst, 0, f"mig{seq}"
+                m.seen_tokens, m.new_tokens = 0, n * BLOCK
+                m.src_block_ids, m.dst_block_ids = [list(chunk.src_blocks[:n])], [list(chunk.dst_blocks[:n])]
+                m.dst_worker_info = pair.winfo
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(pair.stream)
+                pair.cli.start_req_send([m], stepid=100000 + seq)
+                pair.cli.drain()
+                e1.record(pair.stream)
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1) * 1000.0)
+        ts = sorted(ts[2:]) if len(ts) > 2 else ts
+        nbytes = n * pair.src_l.block_bytes * pair.n_layers
+        med = ts[len(ts) // 2] if ts else 0.0
+        out.append({"blocks": n, "bytes": nbytes, "p50_us": round(med, 1), "min_us": round(ts[0], 1) if ts else 0.0,
+                    "GBps_at_p50": round(nbytes / med / 1e3, 1) if med > 0 else 0.0})
+    return out

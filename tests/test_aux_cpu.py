@@ -1,0 +1,84 @@
+"""Auxiliary subsystems on CPU: process monitor line protocol, gdrcopy shim, CRC, NVLink affinity
+table helpers, KV specs of the model families."""
+import socket
+import zlib
+
+from llumnix_kv_b200 import load_ops, nvlink_affinity
+from llumnix_kv_b200.models.kv_spec import DEEPSEEK_V32, LLAMA3_8B, LLAMA3_70B, QWEN3_NEXT_80B, SPECS
+from llumnix_kv_b200.ops.layouts import CacheShape
+
+
+def test_monitor_line_protocol(tmp_path):
+    K = load_ops()
+    port = K.monitor_start()
+    assert port > 0 and K.monitor_port() == port and K.monitor_start() == port    # idempotent
+    try:
+        s = socket.create_connection(("127.0.0.1", port), timeout=5)
+        f = s.makefile("rw")
+
+        def cmd(line):
+            f.write(line + "\n")
+            f.flush()
+            return f.readline().strip()
+
+        assert cmd("prof active").startswith("prev=")        # -33 without jemalloc, 0/1 with it
+        assert cmd("prof deactive").startswith("prev=")
+        dump = tmp_path / "heap.out"
+        assert cmd(f"prof dump {dump}") == "ok" and dump.stat().st_size > 0
+        assert cmd("prof dump ") == "empty filepath"
+        stats = cmd("stats")
+        assert "rss_bytes=" in stats and "malloc_in_use=" in stats
+        assert cmd("bogus") == "unknown command"
+        f.write("quit\n")
+        f.flush()
+        assert f.readline() == ""                               # server closed the connection
+        s.close()
+    finally:
+        K.monitor_stop()
+    assert K.monitor_port() == 0
+
+
+def test_env_dump_lists_resolved_settings():
+    K = load_ops()
+    K.env_port_base()
+    assert "BLLM_KVTRANS_PORT_BASE=" in K.envcfg_dump()
+
+
+def test_gdr_shim_reports_unavailable_and_crc_matches_zlib():
+    K = load_ops()
+    ok, why = K.gdr_available()
+    assert ok or "libgdrapi" in why
+    data = bytes(range(256)) * 37
+    assert K.crc32_bytes(data) == zlib.crc32(data)
+    assert K.crc32_bytes(data[100:], K.crc32_bytes(data[:100])) == zlib.crc32(data)
+
+
+def test_affinity_helpers_on_a_synthetic_switch_topology():
+    n = 8
+    topo = {"gpus": [{"index": i, "multicast_supported": 1, "nvlink_links_up": 18} for i in range(n)],
+            "links": [{"src": a, "dst": b, "access": 1, "perf_rank": 0, "native_atomics": 1}
+                      for a in range(n) for b in range(n) if a != b]}
+    assert nvlink_affinity.best_peers(topo, 2) == [0, 1, 3, 4, 5, 6, 7]
+    assert nvlink_affinity.pair_prefill_decode(topo, 4) == [(0, 4), (1, 5), (2, 6), (3, 7)]
+    assert nvlink_affinity.nvls_capable(topo)
+    topo["links"] = [l for l in topo["links"] if not (l["src"] == 0 and l["dst"] == 4)]
+    assert nvlink_affinity.pair_prefill_decode(topo, 4)[0] == (0, 5)
+    topo["gpus"][3]["multicast_supported"] = 0
+    assert not nvlink_affinity.nvls_capable(topo)
+
+
+def test_affinity_file_roundtrip(tmp_path):
+    path = nvlink_affinity.generate(str(tmp_path / "aff.json"))   # no GPU here: an empty but valid table
+    topo = nvlink_affinity.load(path)
+    assert "gpus" in topo and "links" in topo
+
+
+def test_kv_specs():
+    assert LLAMA3_8B.token_bytes() == 4096 and LLAMA3_8B.token_bytes(tp=4) == 1024
+    assert LLAMA3_70B.heads_on_rank(16) == 1                    # GQA heads replicate beyond 8-way TP
+    lay = LLAMA3_8B.attn_layout(CacheShape.FLASHINFER, 10, tp=2)
+    assert lay.num_heads == 4 and lay.block_bytes == 2 * 16 * 4 * 128 * 2
+    mla = DEEPSEEK_V32.attn_layout(CacheShape.DPSK_V32_SPARSE_MLA, 4)
+    assert mla.kv_count == 1 and mla.block_bytes == 64 * 576 * 2
+    assert QWEN3_NEXT_80B.linear_state_bytes(tp=2) == 3 * 4096 * 2 + 16 * 128 * 128 * 4
+    assert set(SPECS) >= {"llama-3-8b", "deepseek-v3.2", "kimi-k3"}
