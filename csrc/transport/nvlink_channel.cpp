@@ -222,6 +222,10 @@ class NvlinkChannel : public IChannel {
     (void)step;
     if (!fused_ || layer_end <= layer_begin) return false;
     if (plan_.n_reqs == 0) return true;
+    // One launch saves ~100 us of launch and event overhead, which is what matters for a small
+    // migration; a large one is faster layer by layer over several streams (measured crossover
+    // around half a GiB).
+    if (moved_bytes_per_layer_ * (layer_end - layer_begin) > (512ull << 20)) return false;
     cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
     // one launch over the layer range on the stream that carried the plan; layer events are
     // recorded in order on one stream, so the last one implies the others
