@@ -48,7 +48,7 @@ def parse_args():
     ap.add_argument("--streams", type=int, default=8, help="transfer streams the layers alternate over")
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--small", action="store_true", help="tiny case for profiler captures")
-    ap.add_argument("--mode", default="p2d", choices=["p2d", "kvstore", "migration"],
+    ap.add_argument("--mode", default="p2d", choices=["p2d", "kvstore", "migration", "ttft"],
                     help="p2d: prefill->decode transfer (the headline); kvstore: host-DRAM store save/load GB/s; "
                          "migration: decode->decode latency against the number of blocks")
     ap.add_argument("--e2e-only", action="store_true")
@@ -153,6 +153,31 @@ def main():
             print(json.dumps({"metric": "kvstore_save_load_GBps", "unit": "GB/s", "n_gpus": 1, "dtype": "bf16",
                               "config": {"model": MODEL, "layers": args.layers, "store": "pinned host DRAM (POSIX shm)"},
                               "result": res}))
+        return
+    if args.mode == "ttft":
+        from llumnix_kv_b200.bench_support import ttft_added
+
+        res = ttft_added(K, rank, world, dev, tokens=512 if args.small else args.tokens, iters=max(args.steps, 5),
+                         warmup=args.warmup, tiny=args.small)
+        if world > 1:
+            import torch as _t
+
+            t = _t.tensor([res["colocated_ms_p50"], res["disagg_ms_p50"], res["colocated_ms_p99"], res["disagg_ms_p99"]],
+                          dtype=_t.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)      # slowest prefill rank
+            res.update(colocated_ms_p50=float(t[0]), disagg_ms_p50=float(t[1]), colocated_ms_p99=float(t[2]),
+                       disagg_ms_p99=float(t[3]))
+            res["added_ttft_p50_pct"] = round(100.0 * (float(t[1]) - float(t[0])) / float(t[0]), 2)
+            res["added_ttft_p99_pct"] = round(100.0 * (float(t[3]) - float(t[2])) / float(t[2]), 2)
+        if rank == 0:
+            print(json.dumps({"metric": "added_ttft_pct_vs_colocated_prefill", "unit": "%", "n_gpus": args.gpus,
+                              "higher_is_better": False, "dtype": "bf16", "data": "synthetic tokens, random-init weights",
+                              "config": {"model": "llama-3-8b (32L, 4096 hidden, 32q/8kv heads, 14336 ffn)",
+                                         "seq_len": res["tokens"], "parallelism": f"{max(world // 2, 1)}P->{max(world // 2, 1)}D tp1",
+                                         "kv": "NHD -> HND, pushed per layer through KVTransferClient.record_event"},
+                              "result": res}))
+        if world > 1:
+            dist.destroy_process_group()
         return
     if args.mode == "migration":
         from llumnix_kv_b200.bench_support import migration_sweep

@@ -369,3 +369,106 @@ def migration_sweep(pair: "PDBenchPair", counts=(1, 4, 16, 64, 256, 1024, 4096),
         out.append({"blocks": n, "bytes": nbytes, "p50_us": round(med, 1), "min_us": round(ts[0], 1) if ts else 0.0,
                     "GBps_at_p50": round(nbytes / med / 1e3, 1) if med > 0 else 0.0})
     return out
+
+
+def ttft_added(K, rank: int, world: int, dev, tokens: int = 8192, iters: int = 30, warmup: int = 3,
+               tiny: bool = False) -> dict:
+    """Time to first token of a Llama-3-8B-shaped prefill, alone ("colocated") and with every
+    layer's KV pushed to the decode GPU while the next layers compute ("disaggregated", until the
+    first token is on the host AND the decode side holds the whole KV).  Rank r < world/2 prefills,
+    rank r + world/2 is its decode GPU; with one GPU both caches share it."""
+    import random
+
+    from .kv_transfer_impl import KVTransferClient, KVTransferProtocolType as PT, KVTransferServer
+    from .models.llama_prefill import LLAMA3_8B_GEOMETRY, TINY_GEOMETRY, PrefillWorker
+
+    geo = TINY_GEOMETRY if tiny else LLAMA3_8B_GEOMETRY
+    n_pairs = max(world // 2, 1)
+    sender = world == 1 or rank < n_pairs
+    receiver = world == 1 or rank >= n_pairs
+    pair = rank % n_pairs
+    n_blk = (tokens + BLOCK - 1) // BLOCK
+    num_blocks = n_blk + 8
+    rng = random.Random(99)
+    src_ids = rng.sample(range(1, num_blocks), n_blk)
+    dst_ids = rng.sample(range(1, num_blocks), n_blk)
+    dst_l = AttnLayout(CacheShape.FLASHINFER, num_blocks, BLOCK, geo.num_kv_heads, geo.head_dim, 2)
+    srv = cli = worker = None
+    winfo = None
+    dst_inst = f"D{pair}|0|1"
+    if receiver:
+        dst = [dst_l.alloc(dev) for _ in range(geo.num_layers)]
+        srv = KVTransferServer(dst_inst, 1, 0, 0, dst_l.block_bytes, dst_l.token_bytes, "fake://", dst, [PT.NVLINK],
+                               num_kv_heads=geo.num_kv_heads, cache_shape=int(CacheShape.FLASHINFER))
+        winfo = srv.worker_info()
+    if world > 1:
+        import torch.distributed as dist
+
+        infos = [None] * world
+        dist.all_gather_object(infos, winfo)
+        if sender:
+            winfo = infos[rank + n_pairs]
+    colo, disagg = [], []
+    if sender:
+        worker = PrefillWorker(geo, dev, num_blocks, BLOCK, seed=pair)
+        cli = KVTransferClient(f"P{pair}|0|1", 1, 0, 0, worker.layout.block_bytes, worker.layout.token_bytes, "fake://",
+                               worker.kv_caches, [PT.NVLINK], num_kv_heads=geo.num_kv_heads,
+                               cache_shape=int(CacheShape.FLASH))
+        toks = torch.randint(0, geo.vocab, (tokens,), device=dev)
+        blocks = torch.tensor(src_ids, device=dev)
+        stream = torch.cuda.current_stream(dev)
+
+        def run(push: bool, seq: int) -> float:
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            if push:
+                stepid = 9000 + seq
+                cli.submit_req_send2(dst_inst, 0, f"t{seq}", 0, tokens, True, src_ids, dst_ids, winfo, stepid=stepid)
+                cli.start_send_step(stepid, 1)
+                tok = worker.prefill(toks, blocks, after_layer=lambda i: cli.record_event(i, stream))
+                cli.flush_send_step()
+                first = int(tok.item())
+                cli.drain()
+            else:
+                first = int(worker.prefill(toks, blocks).item())
+            e1.record(stream)
+            torch.cuda.synchronize()
+            assert 0 <= first < geo.vocab
+            return e0.elapsed_time(e1)
+
+        for i in range(warmup):
+            run(False, i)
+            run(True, i)
+        for i in range(iters):
+            colo.append(run(False, warmup + i))
+            disagg.append(run(True, warmup + i))
+    torch.cuda.synchronize()
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+    ok = True
+    if world == 1 and sender:
+        # the decode cache must hold what the prefill cache holds, layer 0 and last, all full blocks
+        nb = tokens // BLOCK
+        sb, db = torch.tensor(src_ids[:nb], device=dev), torch.tensor(dst_ids[:nb], device=dev)
+        for layer in (0, geo.num_layers - 1):
+            sv = worker.layout.view(worker.kv_caches[layer], torch.int16)[sb]
+            dv = dst_l.view(dst[layer], torch.int16)[db]
+            ok = ok and bool(torch.equal(sv, dv))
+    if srv is not None:
+        srv.stop()
+
+    def pct(v, p):
+        s = sorted(v)
+        return s[min(len(s) - 1, int(round(p * (len(s) - 1))))] if s else 0.0
+
+    res = {"colocated_ms_p50": round(pct(colo, 0.5), 3), "colocated_ms_p99": round(pct(colo, 0.99), 3),
+           "disagg_ms_p50": round(pct(disagg, 0.5), 3), "disagg_ms_p99": round(pct(disagg, 0.99), 3),
+           "iters": iters, "tokens": tokens, "kv_bytes": tokens * 2 * geo.num_kv_heads * geo.head_dim * 2 * geo.num_layers,
+           "verified": ok}
+    if colo:
+        res["added_ttft_p50_pct"] = round(100.0 * (res["disagg_ms_p50"] - res["colocated_ms_p50"]) / res["colocated_ms_p50"], 2)
+        res["added_ttft_p99_pct"] = round(100.0 * (res["disagg_ms_p99"] - res["colocated_ms_p99"]) / res["colocated_ms_p99"], 2)
+    return res

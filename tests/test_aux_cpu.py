@@ -82,3 +82,26 @@ def test_kv_specs():
     assert mla.kv_count == 1 and mla.block_bytes == 64 * 576 * 2
     assert QWEN3_NEXT_80B.linear_state_bytes(tp=2) == 3 * 4096 * 2 + 16 * 128 * 128 * 4
     assert set(SPECS) >= {"llama-3-8b", "deepseek-v3.2", "kimi-k3"}
+
+
+def test_prefill_worker_fills_the_paged_cache_and_calls_the_layer_hook():
+    import torch
+
+    from llumnix_kv_b200.models.llama_prefill import TINY_GEOMETRY, PrefillWorker
+
+    w = PrefillWorker(TINY_GEOMETRY, "cpu", 12)
+    toks = torch.randint(0, TINY_GEOMETRY.vocab, (70,))
+    blocks = torch.tensor([3, 5, 7, 9, 1])
+    calls = []
+    t1 = w.prefill(toks, blocks, after_layer=calls.append)
+    assert calls == [0, 1]
+    view = w.layout.view(w.kv_caches[1], torch.bfloat16)
+    used = view[blocks]
+    assert used[:4].abs().sum() > 0 and used[4, :, :6].abs().sum() > 0      # 70 tokens = 4 blocks + 6 slots
+    assert view[[0, 2, 4, 6, 8, 10, 11]].abs().sum() == 0 and used[4, :, 6:].abs().sum() == 0
+    # same prompt, same first token; the KV of a prefix does not depend on what follows it (causal)
+    before = view[blocks[:2]].clone()
+    t2 = w.prefill(toks, blocks)
+    assert torch.equal(t1, t2)
+    w.prefill(torch.cat([toks[:32], torch.randint(0, TINY_GEOMETRY.vocab, (38,))]), blocks)
+    assert torch.equal(view[blocks[:2]], before)
