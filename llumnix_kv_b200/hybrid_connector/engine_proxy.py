@@ -250,3 +250,78 @@ def current_engine() -> EngineProxy:
 def current_worker() -> WorkerProxy:
     assert _g_worker is not None, "worker_init() has not been called in this process"
     return _g_worker
+
+
+# ---- which cache shape does this engine's attention backend use --------------------------------------
+def attention_backend() -> str:
+    return os.environ.get("VLLM_ATTENTION_BACKEND", "")
+
+
+def use_mla() -> bool:
+    return "mla" in attention_backend().lower()
+
+
+def use_sparse_mla() -> bool:
+    return use_mla() and "sparse" in attention_backend().lower()
+
+
+def use_flashinfer() -> bool:
+    return "flashinfer" in attention_backend().lower()
+
+
+def use_turboquant(cfg: VllmConfig) -> bool:
+    if os.environ.get("VLLM_FLASH_ATTN_USE_FAST_TURBOQUANT") or os.environ.get("VLLM_FLASH_ATTN_USE_FAKE_TURBOQUANT"):
+        return True
+    dt = cfg.cache_config.cache_dtype
+    return bool(dt and "tq" in dt.lower())
+
+
+def kvt_protocol() -> str:
+    from llumnix_kv_b200 import envs
+
+    return envs.VLLM_KV_TRANS_PROTOCOL
+
+
+def kvt_cache_shape(cfg: VllmConfig, sm_major: Optional[int] = None) -> int:
+    """Cache-shape id of this engine's paged cache, from the attention backend and the GPU
+    generation (blade_kvt/hybrid_connector/kvtbackend.py:524-563, engine_proxy.py:477-507):
+    FlashInfer keeps HND pages on SM 10.x (shapes 5 / 7 for hybrid models) and NHD on SM 12.x
+    (hybrid only, shape 3); sparse MLA registers two tensors per layer (4); TurboQuant is 6; Kimi-K3
+    style KDA models are 8; FlashAttention is NHD (2, or 3 for hybrid models)."""
+    hybrid = cfg.model_config.is_hybrid
+    if use_turboquant(cfg):
+        return 6
+    if use_sparse_mla():
+        return 4
+    if cfg.model_config.use_mla and hybrid:
+        return 8
+    if use_flashinfer():
+        if sm_major is None:
+            import torch
+
+            sm_major = torch.cuda.get_device_capability()[0] if torch.cuda.is_available() else 10
+        if sm_major == 10:
+            return 7 if hybrid else 5
+        if sm_major == 12:
+            if hybrid:
+                return 3
+            raise ValueError("non-hybrid FlashInfer pages are HND only; SM 12.x keeps NHD")
+        raise ValueError(f"the FlashInfer path needs SM 10.x or 12.x, got SM {sm_major}.x")
+    return 3 if hybrid else 2
+
+
+def align_seen_tokens_for_kvt(per_group_hits: list, token_group_block_sizes: list, dcp_world_size: int = 1,
+                              replicated: Optional[list] = None) -> int:
+    """Prefix a decode engine may reuse before asking a prefill engine for the rest: the shortest
+    hit among the token-indexed (attention / indexer) cache groups, rounded down to a common
+    multiple of their block sizes; ordinary attention groups are striped over the decode context
+    parallel ranks, replicated ones (MLA latent, indexer) are not (engine_proxy.py:105-165).
+    Recurrent-state groups are not part of the boundary: their state always travels whole."""
+    import math
+
+    if not per_group_hits:
+        return 0
+    replicated = replicated or [False] * len(per_group_hits)
+    sizes = [b if r else b * dcp_world_size for b, r in zip(token_group_block_sizes, replicated)]
+    align = math.lcm(*sizes)
+    return min(per_group_hits) // align * align

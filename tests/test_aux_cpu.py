@@ -105,3 +105,30 @@ def test_prefill_worker_fills_the_paged_cache_and_calls_the_layer_hook():
     assert torch.equal(t1, t2)
     w.prefill(torch.cat([toks[:32], torch.randint(0, TINY_GEOMETRY.vocab, (38,))]), blocks)
     assert torch.equal(view[blocks[:2]], before)
+
+
+def test_cache_shape_selection_and_prefix_alignment(monkeypatch):
+    import pytest
+
+    from pd_helpers import make_cfg
+    from llumnix_kv_b200.hybrid_connector import engine_proxy as ep
+
+    cfg = make_cfg("kv_producer", "x")
+    monkeypatch.delenv("VLLM_ATTENTION_BACKEND", raising=False)
+    assert ep.kvt_cache_shape(cfg) == 2
+    monkeypatch.setenv("VLLM_ATTENTION_BACKEND", "FLASHINFER")
+    assert ep.kvt_cache_shape(cfg, sm_major=10) == 5
+    with pytest.raises(ValueError):
+        ep.kvt_cache_shape(cfg, sm_major=12)
+    with pytest.raises(ValueError):
+        ep.kvt_cache_shape(cfg, sm_major=9)
+    cfg.model_config.is_hybrid = True
+    assert ep.kvt_cache_shape(cfg, sm_major=10) == 7 and ep.kvt_cache_shape(cfg, sm_major=12) == 3
+    monkeypatch.setenv("VLLM_ATTENTION_BACKEND", "FLASHMLA_SPARSE")
+    assert ep.use_sparse_mla() and ep.kvt_cache_shape(cfg) == 4
+    monkeypatch.setenv("VLLM_ATTENTION_BACKEND", "FLASH_ATTN")
+    cfg.cache_config.cache_dtype = "tq4"
+    assert ep.kvt_cache_shape(cfg) == 6
+    # attention blocks of 16 striped over 2 DCP ranks, indexer blocks of 64 replicated: lcm(32, 64) = 64
+    assert ep.align_seen_tokens_for_kvt([200, 130], [16, 64], dcp_world_size=2, replicated=[False, True]) == 128
+    assert ep.align_seen_tokens_for_kvt([50], [16]) == 48 and ep.align_seen_tokens_for_kvt([], []) == 0
