@@ -276,8 +276,10 @@ class KVTransferClient:
             return
         if self._events and not self._events[-1].query() and not self._async_sched_warned:
             self._async_sched_warned = True
-            logger.warning("flush_send_step called before the last layer event is ready; "
-                           "async scheduling is not supported by the step protocol")
+            # The reference warns here because its step protocol cannot run ahead of the GPU.  Device-ordered
+            # transports (NVLINK) order themselves after each layer's event, so this is only worth a note.
+            logger.info("flush_send_step called before the last layer event is ready: host-staged transports "
+                        "will wait for the events, device-ordered ones already queue behind them")
         self._call("flush_send", self._cur_step_id)
         self._cur_step_id = None
 

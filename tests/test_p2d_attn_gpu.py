@@ -335,3 +335,48 @@ def test_state_segments_and_copy_blocks(ops):
                                status.data_ptr(), 4, torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
     assert status[0].item() == 1
+
+
+def test_per_layer_launches_replay_from_a_cuda_graph(ops):
+    """The launch is fixed-shape and touches no host state, so a step's per-layer launches can be
+    captured once and replayed; new block tables reach the kernel through the plan buffer."""
+    src_l = AttnLayout(CacheShape.FLASH, 40, 16, 8, 128, 2)
+    dst_l = AttnLayout(CacheShape.FLASHINFER, 40, 16, 8, 128, 2)
+    L = 4
+    src = [src_l.alloc("cuda", "normal", seed=40 + i) for i in range(L)]
+    dst = [dst_l.alloc("cuda") for _ in range(L)]
+    xfer = AttnTransfer(src_l, dst_l, [t.data_ptr() for t in src], [t.data_ptr() for t in dst], "cuda")
+    first = [ReqChunk([3, 9, 12], [7, 1, 30], 0, 48), ReqChunk([5], [8], 0, 11)]
+    second = [ReqChunk([20, 21, 22], [2, 3, 4], 0, 48), ReqChunk([33], [35], 0, 11)]   # same shape, other blocks
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        plan = xfer.plan(first, stream=s)
+        for layer in range(L):                      # warm-up outside capture (module load, attributes)
+            xfer.launch(plan, layer, layer + 1, stream=s)
+    s.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=s):
+        for layer in range(L):
+            xfer.launch(plan, layer, layer + 1, stream=s)
+    for d in dst:
+        d.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    for i in range(L):
+        expect = torch.zeros_like(dst[i])
+        reference_transfer(src_l, dst_l, src[i], expect, first)
+        assert torch.equal(dst[i], expect)
+    # next step: overwrite the plan buffer in place, replay the same graph
+    plan2 = xfer.plan(second)
+    torch.cuda.synchronize()
+    assert plan2.nbytes == plan.nbytes and plan2.total_tiles == plan.total_tiles
+    plan.dev.copy_(plan2.dev)
+    for d in dst:
+        d.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    for i in range(L):
+        expect = torch.zeros_like(dst[i])
+        reference_transfer(src_l, dst_l, src[i], expect, second)
+        assert torch.equal(dst[i], expect)
+    assert xfer.check_status() == (0, 0)
