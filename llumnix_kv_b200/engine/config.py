@@ -24,6 +24,37 @@ class ModelConfig:
     qk_rope_head_dim: int = 0
     vocab_size: int = 32000
     name: str = "mini"
+    # hybrid (Qwen3-Next-like) models: layers repeat as [gdn x num_gdn_groups, attention]; layer i of
+    # that pattern lives in KV-cache group i % (num_gdn_groups + 1) and in physical cache tensor
+    # i // (num_gdn_groups + 1), which one GDN layer of every group and one attention layer share
+    num_gdn_groups: int = 0
+    gdn_conv_rows: int = 3
+    gdn_conv_channel_dims: tuple = (32, 32, 64)     # q, k, v channels of the conv state, whole model
+    gdn_ssm_shape: tuple = (4, 8, 8)                # (heads, k_dim, v_dim) of the recurrent state, whole model
+    gdn_conv_elem_size: int = 2
+    gdn_ssm_elem_size: int = 4
+
+    def group_types(self) -> list:
+        return ["gdn"] * self.num_gdn_groups + ["attn"] if self.is_hybrid else ["attn"]
+
+    def layer_group(self, layer: int) -> int:
+        return layer % (self.num_gdn_groups + 1) if self.is_hybrid else 0
+
+    def layer_tensor(self, layer: int) -> int:
+        return layer // (self.num_gdn_groups + 1) if self.is_hybrid else layer
+
+    def is_gdn_layer(self, layer: int) -> bool:
+        return self.is_hybrid and self.layer_group(layer) < self.num_gdn_groups
+
+    def hybrid_kvt_kwargs_for(self, tp: int) -> dict:
+        """Per-rank recurrent-state geometry in the form KVTransferClient / Server take it."""
+        if not self.is_hybrid:
+            return {}
+        dims = [d // tp for d in self.gdn_conv_channel_dims]
+        h, k, v = self.gdn_ssm_shape
+        return dict(num_gdn_layers=self.num_gdn_groups, conv_state_shape=[1, self.gdn_conv_rows, sum(dims)],
+                    ssm_state_shape=[1, max(1, h // tp), k, v], gdn_conv_channel_dims=dims,
+                    gdn_conv_elem_size=self.gdn_conv_elem_size, gdn_ssm_elem_size=self.gdn_ssm_elem_size)
 
 
 @dataclasses.dataclass

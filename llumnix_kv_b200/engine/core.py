@@ -19,10 +19,10 @@ from typing import Callable, Optional
 from llumnix_kv_b200.hybrid_connector import HybridConnector
 from llumnix_kv_b200.hybrid_connector.engine_proxy import EngineProxy, KVConnectorRole
 
-from .config import KVCacheConfig, KVCacheGroupSpec, VllmConfig
+from .config import VllmConfig
 from .scheduler import MiniScheduler
 from .types import EngineCoreOutput, EngineCoreRequest, EngineCoreRequestType, Request
-from .worker import MiniWorker, layer_name
+from .worker import MiniWorker, make_kv_cache_config
 
 logger = logging.getLogger("llumnix_kv_b200.engine")
 
@@ -34,14 +34,12 @@ class MiniEngineCore:
         self.input_queue: "queue.Queue" = queue.Queue()
         self.outputs: "queue.Queue" = queue.Queue()
         self._output_cb = output_cb
-        self.scheduler = MiniScheduler(cfg)
+        self.scheduler = MiniScheduler(cfg, cfg.model_config.group_types())
         self.proxy: Optional[EngineProxy] = None
         self.connector: Optional[HybridConnector] = None
         tp = cfg.parallel_config.tensor_parallel_size
         devices = devices or [cfg.device] * tp
-        kv_cache_config = KVCacheConfig(
-            num_blocks=cfg.cache_config.num_gpu_blocks,
-            kv_cache_groups=[KVCacheGroupSpec([layer_name(i) for i in range(cfg.model_config.num_layers)])])
+        kv_cache_config = make_kv_cache_config(cfg)
         if cfg.kv_transfer_config is not None:
             # the scheduler half opens the RPC port the workers report to, so it comes first
             self.proxy = EngineProxy(self, cfg)

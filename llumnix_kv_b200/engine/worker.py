@@ -22,8 +22,30 @@ from .config import KVCacheConfig, KVCacheGroupSpec, VllmConfig
 from .types import SchedulerOutput
 
 
-def layer_name(i: int) -> str:
-    return f"model.layers.{i}.self_attn.attn"
+def layer_name(i: int, gdn: bool = False) -> str:
+    return f"model.layers.{i}.linear_attn" if gdn else f"model.layers.{i}.self_attn.attn"
+
+
+def make_kv_cache_config(cfg: VllmConfig) -> KVCacheConfig:
+    """KV-cache groups in physical order: one group per GDN position of the layer pattern, then
+    the attention group (a plain model has the attention group only)."""
+    mc = cfg.model_config
+    groups = [[] for _ in mc.group_types()]
+    for i in range(mc.num_layers):
+        groups[mc.layer_group(i)].append(layer_name(i, mc.is_gdn_layer(i)))
+    return KVCacheConfig(num_blocks=cfg.cache_config.num_gpu_blocks,
+                         kv_cache_groups=[KVCacheGroupSpec(g) for g in groups])
+
+
+def synthetic_state(token_ids: list, upto: int, layer: int, col0: int, cols: int, rows: int, dtype: torch.dtype,
+                    device, row0: int = 0) -> torch.Tensor:
+    """[rows, cols] recurrent-state values that depend on the whole prefix ``token_ids[:upto]``, on the
+    layer and on the GLOBAL row / column index, so that any TP slicing of the state can be recomputed."""
+    digest = (sum((j + 1) * t for j, t in enumerate(token_ids[:upto])) + 7919 * upto) % 100003
+    r = (torch.arange(rows, device=device) + row0).view(-1, 1)
+    c = (torch.arange(cols, device=device) + col0).view(1, -1)
+    code = (digest + layer * 131 + r * 17 + c * 3) % 251
+    return ((code - 125).to(torch.float32) / 16.0).to(dtype)
 
 
 def synthetic_kv(token_ids: torch.Tensor, positions: torch.Tensor, layer: int, head0: int, n_heads: int,
@@ -53,10 +75,19 @@ class MiniWorker:
         elem = 1 if cc.mx_scaled else mc.dtype_bytes
         self.layout = AttnLayout(CacheShape(cc.cache_shape), cc.num_gpu_blocks, cc.block_size, self.heads, mc.head_dim,
                                  elem, mx_scaled=cc.mx_scaled)
-        self.kv_caches = {layer_name(i): self.layout.alloc(self.device) for i in range(mc.num_layers)}
-        self.kv_cache_config = KVCacheConfig(
-            num_blocks=cc.num_gpu_blocks,
-            kv_cache_groups=[KVCacheGroupSpec([layer_name(i) for i in range(mc.num_layers)])])
+        # hybrid models: one physical tensor per repetition of the layer pattern, shared by its layers
+        n_tensors = mc.layer_tensor(mc.num_layers - 1) + 1
+        self._tensors = [self.layout.alloc(self.device) for _ in range(n_tensors)]
+        self.names = [layer_name(i, mc.is_gdn_layer(i)) for i in range(mc.num_layers)]
+        self.kv_caches = {self.names[i]: self._tensors[mc.layer_tensor(i)] for i in range(mc.num_layers)}
+        self.kv_cache_config = make_kv_cache_config(cfg)
+        if mc.is_hybrid:
+            tp_ = cfg.parallel_config.tensor_parallel_size
+            self._conv_dims = [d // tp_ for d in mc.gdn_conv_channel_dims]
+            self._ssm_heads = max(1, mc.gdn_ssm_shape[0] // tp_)
+            conv_b = mc.gdn_conv_rows * sum(self._conv_dims) * mc.gdn_conv_elem_size
+            ssm_b = self._ssm_heads * mc.gdn_ssm_shape[1] * mc.gdn_ssm_shape[2] * mc.gdn_ssm_elem_size
+            assert conv_b + ssm_b <= self.layout.block_bytes, "recurrent state does not fit in one cache page"
         self.connector: Optional[HybridConnector] = None
         self.proxy: Optional[WorkerProxy] = None
         if self.device.type == "cuda":
@@ -73,10 +104,46 @@ class MiniWorker:
             return  # a block-scaled fp8 cache is only ever filled by transfers in this engine
         lay = self.layout
         kv = synthetic_kv(tokens, positions, layer, self.head0, self.heads, lay.head_dim, self.dtype)
-        view = lay.view(self.kv_caches[layer_name(layer)], self.dtype)   # [block, kv, slot, head, dim]
+        view = lay.view(self.kv_caches[self.names[layer]], self.dtype)   # [block, kv, slot, head, dim]
         blk = torch.tensor([blocks[int(p) // lay.ntpb] for p in positions.tolist()], device=self.device)
         slot = (positions % lay.ntpb).to(self.device)
         view[blk, :, slot] = kv
+
+    # ---- recurrent (GDN) state of hybrid models: one page per request and GDN group -----------------------
+    def expected_state(self, layer: int, token_ids: list, upto: int) -> tuple:
+        """(conv [rows, q+k+v channels of this rank] bf16, ssm [heads of this rank, k*v] fp32) after
+        the first ``upto`` tokens.  A rank holds a contiguous slice of each of q, k, v and of the heads."""
+        mc = self.cfg.model_config
+        parts, g0 = [], 0
+        for dim_rank, dim_all in zip(self._conv_dims, mc.gdn_conv_channel_dims):
+            parts.append(synthetic_state(token_ids, upto, layer, g0 + self.tp_rank * dim_rank, dim_rank,
+                                         mc.gdn_conv_rows, torch.bfloat16, self.device))
+            g0 += dim_all
+        _h, k, v = mc.gdn_ssm_shape
+        ssm = synthetic_state(token_ids, upto, layer + 1000, 0, k * v, self._ssm_heads, torch.float32, self.device,
+                              row0=self.tp_rank * self._ssm_heads)
+        return torch.cat(parts, dim=1), ssm
+
+    def _state_regions(self, layer: int, block: int) -> tuple:
+        mc = self.cfg.model_config
+        flat = self._tensors[mc.layer_tensor(layer)]
+        cols = sum(self._conv_dims)
+        conv_b = mc.gdn_conv_rows * cols * 2
+        ssm_b = self._ssm_heads * mc.gdn_ssm_shape[1] * mc.gdn_ssm_shape[2] * 4
+        off = block * self.layout.block_bytes
+        conv = flat[off:off + conv_b].view(torch.bfloat16).view(mc.gdn_conv_rows, cols)
+        ssm = flat[off + conv_b:off + conv_b + ssm_b].view(torch.float32).view(self._ssm_heads, -1)
+        return conv, ssm
+
+    def _write_state(self, layer: int, token_ids: list, upto: int, block: int) -> None:
+        conv, ssm = self._state_regions(layer, block)
+        c, s = self.expected_state(layer, token_ids, upto)
+        conv.copy_(c)
+        ssm.copy_(s)
+
+    def read_state(self, layer: int, block: int) -> tuple:
+        conv, ssm = self._state_regions(layer, block)
+        return conv.clone(), ssm.clone()
 
     def expected_kv(self, layer: int, token_ids: list, lo: int, hi: int, dtype=None) -> torch.Tensor:
         toks = torch.tensor(token_ids[lo:hi], device=self.device)
@@ -85,7 +152,7 @@ class MiniWorker:
 
     def read_kv(self, layer: int, blocks: list, lo: int, hi: int) -> torch.Tensor:
         lay = self.layout
-        view = lay.view(self.kv_caches[layer_name(layer)], self.dtype)
+        view = lay.view(self.kv_caches[self.names[layer]], self.dtype)
         pos = torch.arange(lo, hi, device=self.device)
         blk = torch.tensor([blocks[p // lay.ntpb] for p in range(lo, hi)], device=self.device)
         return view[blk, :, pos % lay.ntpb]
@@ -93,7 +160,7 @@ class MiniWorker:
     def read_kv_mx(self, layer: int, blocks: list, lo: int, hi: int):
         """(codes, UE8M0 exponents) of a block-scaled fp8 cache for prompt positions [lo, hi)."""
         lay = self.layout
-        flat = self.kv_caches[layer_name(layer)]
+        flat = self.kv_caches[self.names[layer]]
         pos = torch.arange(lo, hi, device=self.device)
         blk = torch.tensor([blocks[p // lay.ntpb] for p in range(lo, hi)], device=self.device)
         return lay.view(flat, torch.uint8)[blk, :, pos % lay.ntpb], lay.scale_view(flat)[blk, :, pos % lay.ntpb]
@@ -132,12 +199,17 @@ class MiniWorker:
             hi = min(lo + n, len(toks))
             if hi > lo:
                 work.append((torch.tensor(toks[lo:hi], device=self.device), torch.arange(lo, hi, device=self.device),
-                             st[1][-1] if len(st[1]) > 1 else st[1][0]))
-        for layer in range(self.cfg.model_config.num_layers):
-            for toks, pos, blocks in work:
-                self._write_layer(layer, toks, pos, blocks)
+                             st[1][-1] if len(st[1]) > 1 else st[1][0], st, hi))
+        mc = self.cfg.model_config
+        for layer in range(mc.num_layers):
+            for toks, pos, blocks, st, hi in work:
+                if mc.is_gdn_layer(layer):
+                    # the recurrent state after this step's tokens, in the request's page of the layer's group
+                    self._write_state(layer, st[0], hi, st[1][mc.layer_group(layer)][0])
+                else:
+                    self._write_layer(layer, toks, pos, blocks)
             if conn is not None and meta is not None:
-                conn.save_kv_layer(layer_name(layer), self.kv_caches[layer_name(layer)], None)
+                conn.save_kv_layer(self.names[layer], self.kv_caches[self.names[layer]], None)
         if conn is not None and meta is not None:
             conn.clear_connector_metadata()
         sampled = {}

@@ -244,6 +244,17 @@ def build_kvt_args(backend: "HybridBackend", kv_caches: dict, tp_rank: int) -> d
     tp = cfg.parallel_config.tensor_parallel_size
     dp = cfg.parallel_config.data_parallel_rank
     layers = flatten_cache(kv_caches)
+    if backend.is_hybrid:
+        # Several logical layers (one GDN layer of each group and one attention layer) share a
+        # physical cache tensor.  Each tensor is registered once, and the transfer of a tensor
+        # starts when the last logical layer that writes into it has run.
+        order = sorted(kv_caches, key=extract_layer_index)
+        seen: dict = {}
+        for name in order:
+            seen[kv_caches[name].data_ptr()] = (extract_layer_index(name), kv_caches[name])
+        phys = sorted(seen.values(), key=lambda it: it[0])
+        layers = [[t] for _, t in phys]
+        backend.hybrid_model_send_layer = [idx for idx, _ in phys]
     n_tensors = len(layers[0])
     block_bytes, token_bytes = [], []
     for t in range(n_tensors):
@@ -257,7 +268,8 @@ def build_kvt_args(backend: "HybridBackend", kv_caches: dict, tp_rank: int) -> d
     args = dict(inst_id=backend._inst_id, tp_size=tp, worker_id=dp * tp + tp_rank, worker_tp_rank=tp_rank,
                 block_bytes=block_bytes, token_bytes=token_bytes, naming_url=backend._naming_url, layers=layers,
                 protocols=protocols, num_kv_heads=1 if mc.use_mla else mc.num_kv_heads, cache_shape=cc.cache_shape)
-    args.update(getattr(mc, "hybrid_kvt_kwargs", None) or {})
+    if backend.is_hybrid:
+        args.update(mc.hybrid_kvt_kwargs_for(tp))
     return args
 
 

@@ -183,3 +183,58 @@ def test_abort_on_decode_side_releases_everything(pd):
         time.sleep(0.01)
     assert d.scheduler.kv_cache_manager.block_pool.num_free_blocks() == 63
     assert not d.connector._sched._loading
+
+
+def _snapshot_states(d, blocks_by_group):
+    """The recurrent-state pages as they are when the load has finished (the decode engine advances
+    them as soon as it computes its own first token)."""
+    mc = d.cfg.model_config
+    return [{layer: w.read_state(layer, blocks_by_group[mc.layer_group(layer)][0])
+             for layer in range(mc.num_layers) if mc.is_gdn_layer(layer)} for w in d.workers]
+
+
+def _check_hybrid(d, req, blocks_by_group, n_ctx, states):
+    mc = d.cfg.model_config
+    for w, snap in zip(d.workers, states):
+        for layer in range(mc.num_layers):
+            if mc.is_gdn_layer(layer):
+                conv, ssm = snap[layer]
+                ec, es = w.expected_state(layer, req.prompt_token_ids, n_ctx)
+                assert torch.equal(conv, ec) and torch.equal(ssm, es), ("state", layer)
+            else:
+                got = w.read_kv(layer, blocks_by_group[-1], 0, n_ctx)
+                assert torch.equal(got, w.expected_kv(layer, req.prompt_token_ids, 0, n_ctx)), ("kv", layer)
+
+
+@pytest.mark.parametrize("ptp,dtp", [(1, 1), (2, 1), (1, 2)])
+def test_hybrid_gdn_model_state_and_attention_pages(ptp, dtp):
+    """Qwen3-Next-like model: 3 GDN groups + 1 attention group, 8 logical layers in 2 physical tensors.
+    The prefill engine drops the last prompt token, ships attention KV as it is computed and the
+    recurrent state of every GDN layer with the last chunk; TP-mismatched ranks re-slice both."""
+    kw = dict(cache_shape=3, layers=8, gdn_groups=3)
+    p, d = make_pd(p_kw=dict(tp=ptp, max_batched=48, **kw), d_kw=dict(tp=dtp, **kw))
+    try:
+        cap = _spy_add(d)
+        states = {}
+        orig_add = d.scheduler.add_request
+
+        def snap(r):
+            states[r.request_id] = _snapshot_states(d, d.scheduler.kv_cache_manager.get_block_ids(r.request_id))
+            orig_add(r)
+
+        d.scheduler.add_request = snap
+        req = make_req("h", 101, max_tokens=2, params={"remote_host": "127.0.0.1", "remote_port": p.proxy.rpc_port()})
+        d.add_request(req)
+        out = d.wait_finished("h", 30)
+        assert out is not None and out.finish_reason.name == "LENGTH"
+        computed, blocks = cap["h"]
+        assert computed == 100 and len(blocks) == 4 and [len(g) for g in blocks[:3]] == [1, 1, 1]
+        _check_hybrid(d, req, blocks, 100, states["h"])
+        deadline = time.time() + 5
+        free_all = p.cfg.cache_config.num_gpu_blocks - 1
+        while time.time() < deadline and p.scheduler.kv_cache_manager.block_pool.num_free_blocks() != free_all:
+            time.sleep(0.01)
+        assert p.scheduler.kv_cache_manager.block_pool.num_free_blocks() == free_all
+    finally:
+        d.shutdown()
+        p.shutdown()
