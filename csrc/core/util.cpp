@@ -18,6 +18,14 @@
 namespace kvx {
 
 void SyncSemaphore::wait(uint32_t cond) {
+  // Layers of a step are usually signalled a few microseconds apart: spin briefly (a sleeping
+  // waiter costs a futex wake-up per layer), then block.
+  for (int i = 0; i < 1000; ++i) {
+    if (fast_.load(std::memory_order_acquire) > cond) return;
+#if defined(__x86_64__)
+    __builtin_ia32_pause();
+#endif
+  }
   std::unique_lock<std::mutex> lk(mu_);
   cv_.wait(lk, [&] { return ready_ > cond; });
 }
@@ -31,6 +39,7 @@ void SyncSemaphore::release() {
   {
     std::lock_guard<std::mutex> g(mu_);
     ++ready_;
+    fast_.store(ready_, std::memory_order_release);
   }
   cv_.notify_all();
 }
@@ -41,6 +50,7 @@ uint32_t SyncSemaphore::release(uint32_t cond) {
     std::lock_guard<std::mutex> g(mu_);
     if (ready_ < cond) ready_ = cond;
     v = ready_;
+    fast_.store(ready_, std::memory_order_release);
   }
   cv_.notify_all();
   return v;

@@ -48,6 +48,7 @@ class SyncSemaphore {
   alignas(64) std::mutex mu_;
   std::condition_variable cv_;
   uint32_t ready_{0};
+  std::atomic<uint32_t> fast_{0};   // mirror of ready_ for the short spin before blocking
 };
 
 // FIFO pool.  spawn(fn) runs on any worker; spawn(fn, hint) pins all tasks with the same hint

@@ -21,6 +21,8 @@
 //
 // Every wait is bounded; on a bad block id or a timeout the kernel records a status word and
 // skips the access instead of faulting.
+#include <atomic>
+
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
@@ -33,6 +35,7 @@
 namespace {
 
 constexpr int kMaxStages = 8;
+constexpr int kMaxDevices = 64;
 constexpr uint32_t kSmemBudget = 200 * 1024;     // bytes of dynamic shared memory we ask for at most
 constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz: bound of an mbarrier wait
 
@@ -557,8 +560,16 @@ cudaError_t launch_impl(const KvtAttnLaunch& a, int grid, int threads, uint32_t 
                         size_t smem, cudaStream_t stream) {
   auto kern = kvt_p2d_attn_kernel<MODE, USE_TMA>;
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
+    // the opt-in is per device and sticky: ask once per device (and again only for a larger size)
+    static std::atomic<size_t> granted[kMaxDevices];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::atomic<size_t>* slot = dev >= 0 && dev < kMaxDevices ? &granted[dev] : nullptr;
+    if (slot == nullptr || slot->load(std::memory_order_relaxed) < smem) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+      if (slot != nullptr) slot->store(smem, std::memory_order_relaxed);
+    }
   }
   kern<<<grid, threads, smem, stream>>>(a, stages, tile_bytes);
   return cudaGetLastError();
@@ -621,8 +632,12 @@ extern "C" int kvt_launch_p2d_attn(const KvtAttnLaunch* args, int grid_ctas, int
   }
   int dev = 0;
   cudaGetDevice(&dev);
-  int sms = 0;
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  static std::atomic<int> sm_cache[kMaxDevices];
+  int sms = dev >= 0 && dev < kMaxDevices ? sm_cache[dev].load(std::memory_order_relaxed) : 0;
+  if (sms == 0) {
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (dev >= 0 && dev < kMaxDevices) sm_cache[dev].store(sms, std::memory_order_relaxed);
+  }
   // Default: four CTAs per SM.  Many small CTAs, each with one tile in flight, measured faster
   // than one deep software pipeline per SM, and they let launches on different streams share SMs.
   int grid = grid_ctas > 0 ? grid_ctas : 4 * sms;

@@ -79,6 +79,11 @@ class KVSBackend(HybridBackend):
         self._slots_cfg = kcfg.get_from_extra_config("kvs_slots", None)
         self._model_tag = vllm_config.model_config.name
         self._io_timeout = envs.VLLM_KVS_IO_TIMEOUT_SECONDS
+        # "layer": every layer's pages leave right after the layer ran (overlaps the forward pass);
+        # "step": one move of all layers after the last one (fewer, larger transfers, the way the
+        # reference's object-store adapter defers its store to the end of the step,
+        # v6d_object_backend.py:97-658)
+        self._per_step = kcfg.get_from_extra_config("kvs_save_granularity", "layer") == "step"
         # scheduler half
         self._loads: deque = deque()          # KVSReqMeta queued by the disagg thread
         self._index = None                    # KvStore handle used for lookups only
@@ -299,17 +304,20 @@ class KVSBackend(HybridBackend):
         if not self._step_saves:
             return None
         st = self._store
-        after = None
-        if st.device.type == "cuda":
-            import torch
-
-            after = torch.cuda.Event()
-            after.record(torch.cuda.current_stream(st.device))
-        blocks = [b for _, bl, _, _ in self._step_saves for b in bl]
-        slots = [s for _, _, sl, _ in self._step_saves for s in sl]
-        ev = st.save_layers(layer, layer + 1, blocks, slots, after=after)   # one launch for the whole step
-        work = list(self._step_saves)
         last_layer = layer == self._num_layers - 1
+        ev = None
+        if not self._per_step or last_layer:
+            after = None
+            if st.device.type == "cuda":
+                import torch
+
+                after = torch.cuda.Event()
+                after.record(torch.cuda.current_stream(st.device))
+            blocks = [b for _, bl, _, _ in self._step_saves for b in bl]
+            slots = [s for _, _, sl, _ in self._step_saves for s in sl]
+            lo = 0 if self._per_step else layer
+            ev = st.save_layers(lo, layer + 1, blocks, slots, after=after)   # one launch for every request of the step
+        work = list(self._step_saves)
         if last_layer:
             self._step_saves = []
 

@@ -84,14 +84,25 @@ def test_second_request_loads_what_the_first_saved(store_name):
         e.shutdown()
 
 
-def test_chunked_prefill_saves_block_by_block(store_name):
-    e = make_kvs("A", store_name, max_batched=40)
+@pytest.mark.parametrize("gran", ["layer", "step"])
+def test_chunked_prefill_saves_block_by_block(store_name, gran):
+    e = make_kvs("A", store_name, max_batched=40, extra={"kvs_save_granularity": gran})
     try:
         run(e, "a", 130)
         assert wait_free(e, 63) == 63
         st = e.workers[0].connector._worker._backend._store.stats()
         assert st["sealed"] == 8 and st["writing"] == 0
         assert e.steps >= 4
+        # what was stored is what was computed: load it back into a wiped cache
+        cap = spy(e)
+        for t in e.workers[0].kv_caches.values():
+            t.zero_()
+        r = run(e, "b", 130)
+        computed, blocks = cap["b"]
+        assert computed == 128
+        w = e.workers[0]
+        for layer in range(2):
+            assert torch.equal(w.read_kv(layer, blocks[0], 0, 128), w.expected_kv(layer, r.prompt_token_ids, 0, 128))
     finally:
         e.shutdown()
 
