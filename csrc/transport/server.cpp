@@ -12,6 +12,8 @@
 //     rkey exchange plays in kvtransfer/src/rdma_channel.cpp:77-99,298-316).
 #include <cuda_runtime.h>
 #include <fcntl.h>
+#include <netinet/in.h>
+#include <netinet/tcp.h>
 #include <poll.h>
 #include <sys/mman.h>
 #include <sys/socket.h>
@@ -104,6 +106,9 @@ class TransferServer : public ITransferServer {
       if (r <= 0) continue;
       int cfd = ::accept4(listen_fd_.fd(), nullptr, nullptr, SOCK_CLOEXEC);
       if (cfd < 0) continue;
+      // replies are small and latency-bound: without this, Nagle + delayed ACK add ~40 ms per layer
+      int one = 1;
+      setsockopt(cfd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
       std::lock_guard<std::mutex> g(mu_);
       conns_[cfd] = true;
       conn_thds_.emplace_back([this, cfd] { serve(cfd); });

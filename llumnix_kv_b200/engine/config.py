@@ -22,6 +22,7 @@ class ModelConfig:
     use_mla: bool = False
     kv_lora_rank: int = 0
     qk_rope_head_dim: int = 0
+    indexer_token_bytes: int = 0   # sparse MLA: bytes per token of the indexer key cache (second tensor of a layer)
     vocab_size: int = 32000
     name: str = "mini"
     # hybrid (Qwen3-Next-like) models: layers repeat as [gdn x num_gdn_groups, attention]; layer i of

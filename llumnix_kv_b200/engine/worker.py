@@ -26,6 +26,20 @@ def layer_name(i: int, gdn: bool = False) -> str:
     return f"model.layers.{i}.linear_attn" if gdn else f"model.layers.{i}.self_attn.attn"
 
 
+def indexer_name(i: int) -> str:
+    return f"model.layers.{i}.self_attn.indexer"
+
+
+def synthetic_rows(token_ids: torch.Tensor, positions: torch.Tensor, layer: int, tensor_idx: int,
+                   width: int) -> torch.Tensor:
+    """[tokens, width] uint8 rows of a head-less cache (MLA latent + rope, indexer keys): the same
+    on every TP rank, a function of (token, position, layer, tensor, byte)."""
+    t = token_ids.to(torch.int64).view(-1, 1)
+    p = positions.to(torch.int64).view(-1, 1)
+    b = torch.arange(width, device=token_ids.device).view(1, -1)
+    return ((t * 37 + p * 11 + layer * 5 + tensor_idx * 101 + b * 3) % 251 + 1).to(torch.uint8)
+
+
 def make_kv_cache_config(cfg: VllmConfig) -> KVCacheConfig:
     """KV-cache groups in physical order: one group per GDN position of the layer pattern, then
     the attention group (a plain model has the attention group only)."""
@@ -33,6 +47,8 @@ def make_kv_cache_config(cfg: VllmConfig) -> KVCacheConfig:
     groups = [[] for _ in mc.group_types()]
     for i in range(mc.num_layers):
         groups[mc.layer_group(i)].append(layer_name(i, mc.is_gdn_layer(i)))
+        if mc.use_mla and mc.indexer_token_bytes:
+            groups[mc.layer_group(i)].append(indexer_name(i))
     return KVCacheConfig(num_blocks=cfg.cache_config.num_gpu_blocks,
                          kv_cache_groups=[KVCacheGroupSpec(g) for g in groups])
 
@@ -80,6 +96,21 @@ class MiniWorker:
         self._tensors = [self.layout.alloc(self.device) for _ in range(n_tensors)]
         self.names = [layer_name(i, mc.is_gdn_layer(i)) for i in range(mc.num_layers)]
         self.kv_caches = {self.names[i]: self._tensors[mc.layer_tensor(i)] for i in range(mc.num_layers)}
+        self.row_widths: list = []
+        if mc.use_mla:
+            # head-less caches, identical on every TP rank: [blocks, slots, width] rows per tensor
+            self.row_widths = [(mc.kv_lora_rank + mc.qk_rope_head_dim) * mc.dtype_bytes]
+            if mc.indexer_token_bytes:
+                self.row_widths.append(mc.indexer_token_bytes)
+            self.kv_caches = {}
+            self._rows = []          # per layer: one [blocks, slots, width] uint8 tensor per cache tensor
+            for i in range(mc.num_layers):
+                ts = [torch.zeros(cc.num_gpu_blocks, cc.block_size, w, dtype=torch.uint8, device=self.device)
+                      for w in self.row_widths]
+                self._rows.append(ts)
+                self.kv_caches[layer_name(i)] = ts[0].view(-1)
+                if len(ts) > 1:
+                    self.kv_caches[indexer_name(i)] = ts[1].view(-1)
         self.kv_cache_config = make_kv_cache_config(cfg)
         if mc.is_hybrid:
             tp_ = cfg.parallel_config.tensor_parallel_size
@@ -99,7 +130,22 @@ class MiniWorker:
         self._req_state: dict = {}   # reqid -> (prompt tokens, block ids of group 0)
 
     # ---- the "model" ---------------------------------------------------------------------------
+    def expected_rows(self, layer: int, tensor_idx: int, token_ids: list, lo: int, hi: int) -> torch.Tensor:
+        return synthetic_rows(torch.tensor(token_ids[lo:hi], device=self.device), torch.arange(lo, hi, device=self.device),
+                              layer, tensor_idx, self.row_widths[tensor_idx])
+
+    def read_rows(self, layer: int, tensor_idx: int, blocks: list, lo: int, hi: int) -> torch.Tensor:
+        bs = self.cfg.cache_config.block_size
+        blk = torch.tensor([blocks[p // bs] for p in range(lo, hi)], device=self.device)
+        return self._rows[layer][tensor_idx][blk, torch.arange(lo, hi, device=self.device) % bs]
+
     def _write_layer(self, layer: int, tokens: torch.Tensor, positions: torch.Tensor, blocks: list) -> None:
+        if self.cfg.model_config.use_mla:
+            bs = self.cfg.cache_config.block_size
+            blk = torch.tensor([blocks[int(p) // bs] for p in positions.tolist()], device=self.device)
+            for t, w in enumerate(self.row_widths):
+                self._rows[layer][t][blk, positions % bs] = synthetic_rows(tokens, positions, layer, t, w)
+            return
         if self.cfg.cache_config.mx_scaled:
             return  # a block-scaled fp8 cache is only ever filled by transfers in this engine
         lay = self.layout
@@ -210,6 +256,8 @@ class MiniWorker:
                     self._write_layer(layer, toks, pos, blocks)
             if conn is not None and meta is not None:
                 conn.save_kv_layer(self.names[layer], self.kv_caches[self.names[layer]], None)
+                if len(self.row_widths) > 1:
+                    conn.save_kv_layer(indexer_name(layer), self.kv_caches[indexer_name(layer)], None)
         if conn is not None and meta is not None:
             conn.clear_connector_metadata()
         sampled = {}

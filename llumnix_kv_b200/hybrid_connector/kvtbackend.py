@@ -686,6 +686,12 @@ class PBackend(HybridBackend):
         args = build_kvt_args(self, kv_caches, self._worker.get_tensor_model_parallel_rank())
         self._kvt_cli = KVTransferClient(send_done_addr=self._send_done_addr, **args)
         self._layer_index = {name: extract_layer_index(name) for name in kv_caches}
+        # a layer with several cache tensors (latent + indexer keys) is announced once, by the tensor
+        # that is written last
+        last_of: dict = {}
+        for name in sorted(kv_caches):
+            last_of[self._layer_index[name]] = name
+        self._announcing = set(last_of.values())
         logger.info("register_kv_caches (prefill). worker_id=%s winfo=%s", args["worker_id"],
                     self._kvt_cli.worker_info())
 
@@ -797,6 +803,8 @@ class PBackend(HybridBackend):
         idx = self._layer_index.get(layer_name)
         if idx is None:
             idx = extract_layer_index(layer_name)
+        elif layer_name not in self._announcing:
+            return None
         if self.is_hybrid:
             if idx not in self.hybrid_model_send_layer:
                 return None

@@ -11,12 +11,14 @@ from llumnix_kv_b200.engine.types import EngineCoreRequest, SamplingParams
 
 
 def make_cfg(role, name, tp=1, device="cpu", cache_shape=2, num_blocks=64, layers=2, heads=8, head_dim=32,
-             max_batched=8192, backend="kvt", extra=None, mx_scaled=False, block_size=16, gdn_groups=0):
+             max_batched=8192, backend="kvt", extra=None, mx_scaled=False, block_size=16, gdn_groups=0, mla=None):
     ex = {"backend": backend, "kvt_inst_id": name, "naming_url": "fake://", "rpc_port": 0}
     ex.update(extra or {})
     return VllmConfig(
         model_config=ModelConfig(num_layers=layers, num_kv_heads=heads, head_dim=head_dim, is_hybrid=gdn_groups > 0,
-                                 num_gdn_groups=gdn_groups),
+                                 num_gdn_groups=gdn_groups, **(dict(use_mla=True, kv_lora_rank=mla[0],
+                                                                    qk_rope_head_dim=mla[1], indexer_token_bytes=mla[2])
+                                                               if mla else {})),
         cache_config=CacheConfig(block_size=block_size, num_gpu_blocks=num_blocks, cache_shape=cache_shape,
                                  mx_scaled=mx_scaled),
         parallel_config=ParallelConfig(tensor_parallel_size=tp),

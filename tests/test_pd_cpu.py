@@ -238,3 +238,29 @@ def test_hybrid_gdn_model_state_and_attention_pages(ptp, dtp):
     finally:
         d.shutdown()
         p.shutdown()
+
+
+@pytest.mark.parametrize("ptp,dtp,shape,mla", [(1, 1, 4, (64, 16, 36)), (2, 1, 4, (64, 16, 36)), (1, 2, 4, (64, 16, 36)),
+                                              (2, 1, 1, (64, 16, 0))])
+def test_mla_latent_and_indexer_caches(ptp, dtp, shape, mla):
+    """DeepSeek-style caches: one head-less latent+rope row per token (and, for sparse attention, an
+    indexer-key row in a second tensor of the layer), identical on every TP rank: with more prefill
+    ranks than decode ranks only one of them sends, with fewer each one feeds several."""
+    kw = dict(cache_shape=shape, mla=mla, block_size=64 if shape == 4 else 16, num_blocks=24)
+    p, d = make_pd(p_kw=dict(tp=ptp, max_batched=100, **kw), d_kw=dict(tp=dtp, **kw))
+    try:
+        cap = _spy_add(d)
+        req = make_req("m", 230, max_tokens=2, params={"remote_host": "127.0.0.1", "remote_port": p.proxy.rpc_port()})
+        d.add_request(req)
+        out = d.wait_finished("m", 30)
+        assert out is not None and out.finish_reason.name == "LENGTH"
+        computed, blocks = cap["m"]
+        assert computed == 229
+        for w in d.workers:
+            for layer in range(2):
+                for t in range(len(w.row_widths)):
+                    assert torch.equal(w.read_rows(layer, t, blocks[0], 0, 229),
+                                       w.expected_rows(layer, t, req.prompt_token_ids, 0, 229)), (layer, t)
+    finally:
+        d.shutdown()
+        p.shutdown()

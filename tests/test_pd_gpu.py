@@ -106,3 +106,55 @@ def test_pd_tp_mismatch_across_four_gpus():
     finally:
         d.shutdown()
         p.shutdown()
+
+
+def test_pd_hybrid_gdn_model_on_gpu():
+    """Hybrid pages (3 GDN groups + attention sharing physical tensors), prefill TP=2 -> decode TP=1:
+    no fused kernel for this shape, the planner's ranges drive the descriptor copy kernel over the
+    NVLink transport; recurrent state is re-sliced across the TP change."""
+    from test_pd_cpu import _check_hybrid, _snapshot_states
+
+    kw = dict(cache_shape=3, layers=8, gdn_groups=3, heads=8, head_dim=64, num_blocks=48)
+    p, d = make_pd(p_kw=dict(device="cuda:0", tp=2, max_batched=64, **kw), d_kw=dict(device="cuda:0", tp=1, **kw))
+    try:
+        cap = spy_add(d)
+        states = {}
+        orig = d.scheduler.add_request
+
+        def snap(r):
+            torch.cuda.synchronize()
+            states[r.request_id] = _snapshot_states(d, d.scheduler.kv_cache_manager.get_block_ids(r.request_id))
+            orig(r)
+
+        d.scheduler.add_request = snap
+        req = make_req("h", 150, max_tokens=2, params={"remote_host": "127.0.0.1", "remote_port": p.proxy.rpc_port()})
+        d.add_request(req)
+        out = d.wait_finished("h", 60)
+        assert out is not None and out.finish_reason.name == "LENGTH"
+        computed, blocks = cap["h"]
+        assert computed == 149
+        _check_hybrid(d, req, blocks, 149, states["h"])
+    finally:
+        d.shutdown()
+        p.shutdown()
+
+
+def test_pd_mla_latent_and_indexer_on_gpu():
+    kw = dict(cache_shape=4, mla=(512, 64, 132), block_size=64, num_blocks=24, layers=3)
+    p, d = make_pd(p_kw=dict(device="cuda:0", tp=2, max_batched=128, **kw), d_kw=dict(device="cuda:0", tp=1, **kw))
+    try:
+        cap = spy_add(d)
+        req = make_req("m", 300, max_tokens=2, params={"remote_host": "127.0.0.1", "remote_port": p.proxy.rpc_port()})
+        d.add_request(req)
+        out = d.wait_finished("m", 60)
+        assert out is not None and out.finish_reason.name == "LENGTH"
+        computed, blocks = cap["m"]
+        assert computed == 299
+        for w in d.workers:
+            for layer in range(3):
+                for t in range(2):
+                    assert torch.equal(w.read_rows(layer, t, blocks[0], 0, 299),
+                                       w.expected_rows(layer, t, req.prompt_token_ids, 0, 299)), (layer, t)
+    finally:
+        d.shutdown()
+        p.shutdown()
