@@ -34,7 +34,7 @@ from ..engine_proxy import (EngineCoreRequest, KVCacheBlocks, KVConnectorRole, R
                             SchedulerOutput, VllmConfig, core_get_param, core_update_params, get_param, set_param)
 from ..kvtbackend import (CODE_MIGRATE_REJECTED_BUSY, CODE_OK, CODE_REQNOTFOUND, TRANSFER_KV_RESP, KVTDInfo, KVTResp,
                           RKVTDInfo, get_inst_id)
-from ..utils import ConnManager, ConnPool, IoRet, kill_me_if_exception
+from ..utils import ConnManager, ConnPool, IoRet, kill_me_if_exception, spawn_task
 from . import (ABORT_REQS_REQ, ABORT_REQS_RESP, KVT_SUSPEND_REQ, MIGRATE_TO_REQ, MIGRATE_TO_RESP, NEW_OUTPUT_REQ,
                NEW_OUTPUT_RESP, NEW_REQ_REQ, NEW_REQ_RESP, OUTPUT_TOKENS_N, SRC_INFO, SUSPEND_EVT, SUSPEND_REQ,
                SUSPEND_RESP, EngineCoreOutputs, MigrateResp, SuspendReq, SuspendResp, WireOutput, int2ipport,
@@ -298,7 +298,7 @@ class MigrationBackend(HybridBackend):
             q = self._front_outputs.get(front)
             if q is None:
                 q = self._front_outputs[front] = asyncio.Queue()
-                asyncio.ensure_future(self._front_main(front, q))
+                spawn_task(self._front_main(front, q))
             q.put_nowait(outs)
 
     # core thread: called by the engine with every batch of outputs before it publishes them

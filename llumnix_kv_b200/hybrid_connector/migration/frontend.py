@@ -21,7 +21,7 @@ from llumnix_kv_b200 import envs
 
 from ..engine_proxy import EngineCoreRequest, core_update_params
 from ..kvtbackend import CODE_OK
-from ..utils import ConnManager, RpcServer, start_asyncio_thread
+from ..utils import ConnManager, RpcServer, spawn_task, start_asyncio_thread
 from . import (ABORT_REQS_REQ, ABORT_REQS_RESP, MIGRATE_TO_REQ, MIGRATE_TO_RESP, NEW_OUTPUT_REQ, NEW_OUTPUT_RESP,
                NEW_REQ_REQ, NEW_REQ_RESP, OUTPUT_TOKENS_N, SRC_INFO, EngineCoreOutputs, MigrateResp, int2ipport,
                ipport2int)
@@ -132,5 +132,5 @@ class MigrationCli:
             elif first and self.migrate_after_first_token and len(self.engines) > 1 and st.migrations == 0:
                 here = (src[0], src[1])
                 idx = self.engines.index(here) if here in self.engines else 0
-                asyncio.ensure_future(self._migrate(o.request_id, self.engines[(idx + 1) % len(self.engines)]))
+                spawn_task(self._migrate(o.request_id, self.engines[(idx + 1) % len(self.engines)]))
         await writer.drain()

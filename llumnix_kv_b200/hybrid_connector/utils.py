@@ -82,6 +82,18 @@ def start_asyncio_thread(name: str, device: Optional[str] = None) -> asyncio.Abs
     return loop
 
 
+_background_tasks: set = set()
+
+
+def spawn_task(coro) -> "asyncio.Task":
+    """``asyncio.ensure_future`` that keeps the task alive: the event loop only holds weak
+    references to tasks, so a fire-and-forget task can be garbage collected in mid-flight."""
+    task = asyncio.ensure_future(coro)
+    _background_tasks.add(task)
+    task.add_done_callback(_background_tasks.discard)
+    return task
+
+
 # ---- RPC: 4-byte head selects the handler, the handler reads its own body -----------------------
 _RpcMethod = Callable[[asyncio.StreamReader, asyncio.StreamWriter], Coroutine[Any, Any, None]]
 

@@ -21,7 +21,7 @@ import msgspec
 from .backend import (GET_BYPASS_HANDLE, GET_BYPASS_HANDLE_RESP, LOAD_DONE_REQ, LOAD_DONE_RESP, SAVE_DONE_REQ,
                       SAVE_DONE_RESP, HybridMetadata, IoDoneReqs, get_backend_cls)
 from .engine_proxy import KVConnectorRole, VllmConfig, WorkerProxy, scheduler_rpc_host, sched_rpc_server_port
-from .utils import ConnPool, IoRet, kill_me_if_exception
+from .utils import ConnPool, IoRet, kill_me_if_exception, spawn_task
 
 logger = logging.getLogger("llumnix_kv_b200.hybrid_connector")
 
@@ -74,7 +74,7 @@ class HybridWorker:
         self._backend.bypass_bind(meta.reqs)
         self._backend.bypass_clear()
         if self._backend.async_load_kv is not None:
-            asyncio.ensure_future(self._async_load_kv(meta))
+            spawn_task(self._async_load_kv(meta))
 
     @kill_me_if_exception
     async def start_bypass_task_loop(self):
