@@ -48,7 +48,7 @@ def parse_args():
     ap.add_argument("--streams", type=int, default=8, help="transfer streams the layers alternate over")
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--small", action="store_true", help="tiny case for profiler captures")
-    ap.add_argument("--mode", default="p2d", choices=["p2d", "kvstore", "migration", "ttft"],
+    ap.add_argument("--mode", default="p2d", choices=["p2d", "kvstore", "migration", "ttft", "quant"],
                     help="p2d: prefill->decode transfer (the headline); kvstore: host-DRAM store save/load GB/s; "
                          "migration: decode->decode latency against the number of blocks")
     ap.add_argument("--e2e-only", action="store_true")
@@ -145,6 +145,15 @@ def main():
     if args.small:
         args.tokens, args.slots, args.layers = 2048, 2, 4
 
+    if args.mode == "quant":
+        from llumnix_kv_b200.bench_support import quant_reshard_bandwidth
+
+        res = quant_reshard_bandwidth(dev, tokens=2048 if args.small else args.tokens, n_layers=8 if args.small else 80)
+        if rank == 0:
+            print(json.dumps({"metric": "tp_mismatch_fp8_transfer_GBps", "unit": "GB/s", "n_gpus": 1, "dtype": "bf16->mxfp8",
+                              "config": {"model": "llama-3-70b-kv (80L, 8 kv heads, 128d), prefill TP4 rank -> decode TP2 rank, "
+                                                  "NHD -> HND", "seq_len": args.tokens}, "result": res}))
+        return
     if args.mode == "kvstore":
         from llumnix_kv_b200.bench_support import kvstore_bandwidth
 
@@ -275,7 +284,10 @@ def main():
                        "parallelism": f"{n_pairs}P->{n_pairs}D tp1" if world > 1 else "1 GPU loopback pair",
                        "layers": args.layers, "l2": f"inputs larger than L2: {pair.slot_bytes >> 20} MiB per step, "
                                                     f"{args.slots} slots cycled",
-                       "transport": pair.transport_name},
+                       "transport": pair.transport_name,
+                       "scaling_note": "N=1 is a same-GPU loopback bounded by HBM; N>=2 are N/2 one-directional "
+                                       "NVLink pairs bounded by 770 GB/s measured per direction: compare N=2,4,8 "
+                                       "with one another"},
             "per_pair_GBps": round(value / n_pairs, 2),
             "roofline": {"peak_GBps_per_pair": roof, "what": roof_name,
                          "fraction": round(value / n_pairs / roof, 3)},

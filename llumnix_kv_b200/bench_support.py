@@ -472,3 +472,50 @@ def ttft_added(K, rank: int, world: int, dev, tokens: int = 8192, iters: int = 3
         res["added_ttft_p50_pct"] = round(100.0 * (res["disagg_ms_p50"] - res["colocated_ms_p50"]) / res["colocated_ms_p50"], 2)
         res["added_ttft_p99_pct"] = round(100.0 * (res["disagg_ms_p99"] - res["colocated_ms_p99"]) / res["colocated_ms_p99"], 2)
     return res
+
+
+def quant_reshard_bandwidth(dev, tokens: int = 8192, n_layers: int = 80, iters: int = 5, n_streams: int = 8) -> dict:
+    """Llama-3-70B-shaped TP-mismatch transfer on one GPU (kernel-only): a prefill TP=4 rank (2 of the 8
+    KV heads, bf16, NHD) pushes into its half of a decode TP=2 rank's pages (4 heads, HND), as a
+    plain copy and as block-scaled fp8 (one UE8M0 scale per 32 values).  GB/s are bf16 source bytes."""
+    from .ops.p2d_attn import MODE_BF16_TO_MXFP8, MODE_COPY, HeadMap
+
+    n_blk = (tokens + BLOCK - 1) // BLOCK
+    src_l = AttnLayout(CacheShape.FLASH, n_blk + 1, BLOCK, 2, HEAD_DIM, 2)
+    res = {}
+    src = [src_l.alloc(dev, fill="normal", seed=i) for i in range(n_layers)]
+    import random
+
+    rng = random.Random(5)
+    sb, db = rng.sample(range(1, n_blk + 1), n_blk), rng.sample(range(1, n_blk + 1), n_blk)
+    for name, mode, dst_l in (
+            ("copy_bf16", MODE_COPY, AttnLayout(CacheShape.FLASHINFER, n_blk + 1, BLOCK, 4, HEAD_DIM, 2)),
+            ("bf16_to_mxfp8", MODE_BF16_TO_MXFP8, AttnLayout(CacheShape.FLASHINFER, n_blk + 1, BLOCK, 4, HEAD_DIM, 1,
+                                                           mx_scaled=True))):
+        dst = [dst_l.alloc(dev) for _ in range(n_layers)]
+        xfer = AttnTransfer(src_l, dst_l, [t.data_ptr() for t in src], [t.data_ptr() for t in dst], dev,
+                            head_map=HeadMap(0, 2, 2), mode=mode)
+        streams = [torch.cuda.Stream(dev) for _ in range(n_streams)]
+        main = torch.cuda.current_stream(dev)
+        plan = xfer.plan([ReqChunk(sb, db, 0, tokens)])
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(main)
+            for s in streams:
+                s.wait_stream(main)
+            for layer in range(n_layers):
+                xfer.launch(plan, layer, layer + 1, stream=streams[layer % n_streams])
+            for s in streams:
+                main.wait_stream(s)
+            e1.record(main)
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        assert xfer.check_status() == (0, 0)
+        ms = min(ts[1:])
+        nbytes = tokens * 2 * 2 * HEAD_DIM * 2 * n_layers
+        res[name] = {"ms": round(ms, 3), "src_GBps": round(nbytes / ms / 1e6, 1), "tma": bool(xfer.use_tma),
+                     "dst_bytes": tokens * dst_l.token_bytes // 2 * n_layers}
+        del dst
+    return res
