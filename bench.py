@@ -51,6 +51,10 @@ def parse_args():
     ap.add_argument("--mode", default="p2d", choices=["p2d", "kvstore", "migration", "ttft", "quant"],
                     help="p2d: prefill->decode transfer (the headline); kvstore: host-DRAM store save/load GB/s; "
                          "migration: decode->decode latency against the number of blocks")
+    ap.add_argument("--prompt-mix", action="store_true",
+                    help="ttft mode: prompt lengths uniform in [tokens/8, 4*tokens] (1k-32k by default) instead of fixed")
+    ap.add_argument("--graph", action="store_true",
+                    help="kernel-only number: replay each step's per-layer launches from a CUDA graph")
     ap.add_argument("--e2e-only", action="store_true")
     ap.add_argument("--e2e-path", default="engine", choices=["engine", "ops"],
                     help="end-to-end number through KVTransferClient/Server (engine) or the AttnTransfer op (ops)")
@@ -167,7 +171,7 @@ def main():
         from llumnix_kv_b200.bench_support import ttft_added
 
         res = ttft_added(K, rank, world, dev, tokens=512 if args.small else args.tokens, iters=max(args.steps, 5),
-                         warmup=args.warmup, tiny=args.small)
+                         warmup=args.warmup, tiny=args.small, mix=args.prompt_mix)
         if world > 1:
             import torch as _t
 
@@ -240,6 +244,8 @@ def main():
             ms = float(t.item())
         return ms, clocks
 
+    if args.graph and not args.e2e_only:
+        pair.build_graphs()
     # ---- kernel-only number: descriptors resident on the device, device-timed -----------
     ms_dev, clocks = (0.0, {}) if args.e2e_only else timed(pair.step_device, args.steps, args.warmup)
     # ---- end to end through the public API: pinned block tables -> H2D, 32 per-layer
@@ -285,6 +291,7 @@ def main():
                        "layers": args.layers, "l2": f"inputs larger than L2: {pair.slot_bytes >> 20} MiB per step, "
                                                     f"{args.slots} slots cycled",
                        "transport": pair.transport_name,
+                       "launch": "cuda graph replay" if args.graph else "one launch per layer from the host",
                        "scaling_note": "N=1 is a same-GPU loopback bounded by HBM; N>=2 are N/2 one-directional "
                                        "NVLink pairs bounded by 770 GB/s measured per direction: compare N=2,4,8 "
                                        "with one another"},

@@ -135,6 +135,30 @@ class PDBenchPair:
             self.xfer.launch(plan, layer, layer + 1, stream=lanes[layer % len(lanes)], grid=self.grid)
         self._fan_in()
 
+    def build_graphs(self) -> None:
+        """Capture each slot's 32 per-layer launches (with their fan-out over the side streams) into
+        a CUDA graph; ``step_device`` then replays it, which takes the host's launch rate out of the
+        kernel-only number."""
+        self.graphs = []
+        if not self.is_sender:
+            return
+        for i in range(self.slots):
+            self.step_device(i)                 # warm-up outside capture
+        torch.cuda.synchronize()
+        for i in range(self.slots):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=self.stream):
+                self._issue_layers(self.plans[i])
+            self.graphs.append(g)
+        torch.cuda.synchronize()
+
+    def _issue_layers(self, plan) -> None:
+        self._fan_out()
+        lanes = [self.stream] + self.side
+        for layer in range(self.n_layers):
+            self.xfer.launch(plan, layer, layer + 1, stream=lanes[layer % len(lanes)], grid=self.grid)
+        self._fan_in()
+
     def _fan_out(self) -> None:
         if self.side:
             self.ev_begin.record(self.stream)
@@ -372,7 +396,7 @@ def migration_sweep(pair: "PDBenchPair", counts=(1, 4, 16, 64, 256, 1024, 4096),
 
 
 def ttft_added(K, rank: int, world: int, dev, tokens: int = 8192, iters: int = 30, warmup: int = 3,
-               tiny: bool = False) -> dict:
+               tiny: bool = False, mix: bool = False) -> dict:
     """Time to first token of a Llama-3-8B-shaped prefill, alone ("colocated") and with every
     layer's KV pushed to the decode GPU while the next layers compute ("disaggregated", until the
     first token is on the host AND the decode side holds the whole KV).  Rank r < world/2 prefills,
@@ -387,9 +411,13 @@ def ttft_added(K, rank: int, world: int, dev, tokens: int = 8192, iters: int = 3
     sender = world == 1 or rank < n_pairs
     receiver = world == 1 or rank >= n_pairs
     pair = rank % n_pairs
-    n_blk = (tokens + BLOCK - 1) // BLOCK
-    num_blocks = n_blk + 8
+    # ``mix``: every timed request draws its prompt length uniformly from [tokens / 8, 4 * tokens]
+    # (1k-32k for the default 8k), the same sequence on every rank
     rng = random.Random(99)
+    lengths = [rng.randint(max(16, tokens // 8), tokens * 4) for _ in range(iters)] if mix else [tokens] * iters
+    max_tokens = max(lengths + [tokens])
+    n_blk = (max_tokens + BLOCK - 1) // BLOCK
+    num_blocks = n_blk + 8
     src_ids = rng.sample(range(1, num_blocks), n_blk)
     dst_ids = rng.sample(range(1, num_blocks), n_blk)
     dst_l = AttnLayout(CacheShape.FLASHINFER, num_blocks, BLOCK, geo.num_kv_heads, geo.head_dim, 2)
@@ -414,17 +442,20 @@ def ttft_added(K, rank: int, world: int, dev, tokens: int = 8192, iters: int = 3
         cli = KVTransferClient(f"P{pair}|0|1", 1, 0, 0, worker.layout.block_bytes, worker.layout.token_bytes, "fake://",
                                worker.kv_caches, [PT.NVLINK], num_kv_heads=geo.num_kv_heads,
                                cache_shape=int(CacheShape.FLASH))
-        toks = torch.randint(0, geo.vocab, (tokens,), device=dev)
-        blocks = torch.tensor(src_ids, device=dev)
+        all_toks = torch.randint(0, geo.vocab, (max_tokens,), device=dev)
+        all_blocks = torch.tensor(src_ids, device=dev)
         stream = torch.cuda.current_stream(dev)
 
-        def run(push: bool, seq: int) -> float:
+        def run(push: bool, seq: int, n_tok: int = tokens) -> float:
+            nb = (n_tok + BLOCK - 1) // BLOCK
+            toks, blocks = all_toks[:n_tok], all_blocks[:nb]
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(stream)
             if push:
                 stepid = 9000 + seq
-                cli.submit_req_send2(dst_inst, 0, f"t{seq}", 0, tokens, True, src_ids, dst_ids, winfo, stepid=stepid)
+                cli.submit_req_send2(dst_inst, 0, f"t{seq}", 0, n_tok, True, src_ids[:nb], dst_ids[:nb], winfo,
+                                     stepid=stepid)
                 cli.start_send_step(stepid, 1)
                 tok = worker.prefill(toks, blocks, after_layer=lambda i: cli.record_event(i, stream))
                 cli.flush_send_step()
@@ -441,8 +472,8 @@ def ttft_added(K, rank: int, world: int, dev, tokens: int = 8192, iters: int = 3
             run(False, i)
             run(True, i)
         for i in range(iters):
-            colo.append(run(False, warmup + i))
-            disagg.append(run(True, warmup + i))
+            colo.append(run(False, warmup + i, lengths[i]))
+            disagg.append(run(True, warmup + i, lengths[i]))
     torch.cuda.synchronize()
     if world > 1:
         import torch.distributed as dist
@@ -451,7 +482,7 @@ def ttft_added(K, rank: int, world: int, dev, tokens: int = 8192, iters: int = 3
     ok = True
     if world == 1 and sender:
         # the decode cache must hold what the prefill cache holds, layer 0 and last, all full blocks
-        nb = tokens // BLOCK
+        nb = lengths[-1] // BLOCK
         sb, db = torch.tensor(src_ids[:nb], device=dev), torch.tensor(dst_ids[:nb], device=dev)
         for layer in (0, geo.num_layers - 1):
             sv = worker.layout.view(worker.kv_caches[layer], torch.int16)[sb]
@@ -471,6 +502,14 @@ def ttft_added(K, rank: int, world: int, dev, tokens: int = 8192, iters: int = 3
     if colo:
         res["added_ttft_p50_pct"] = round(100.0 * (res["disagg_ms_p50"] - res["colocated_ms_p50"]) / res["colocated_ms_p50"], 2)
         res["added_ttft_p99_pct"] = round(100.0 * (res["disagg_ms_p99"] - res["colocated_ms_p99"]) / res["colocated_ms_p99"], 2)
+    if colo and mix:
+        # per request: the same prompt with and without the transfer
+        per_req = [100.0 * (d - c) / c for c, d in zip(colo, disagg)]
+        res["prompt_tokens_min_max"] = [min(lengths), max(lengths)]
+        res["per_request_added_pct_p50"] = round(pct(per_req, 0.5), 2)
+        res["per_request_added_pct_p99"] = round(pct(per_req, 0.99), 2)
+        res["per_request_added_ms_p50"] = round(pct([d - c for c, d in zip(colo, disagg)], 0.5), 3)
+        res["per_request_added_ms_p99"] = round(pct([d - c for c, d in zip(colo, disagg)], 0.99), 3)
     return res
 
 
@@ -499,23 +538,41 @@ def quant_reshard_bandwidth(dev, tokens: int = 8192, n_layers: int = 80, iters: 
         main = torch.cuda.current_stream(dev)
         plan = xfer.plan([ReqChunk(sb, db, 0, tokens)])
         torch.cuda.synchronize()
-        ts = []
-        for _ in range(iters):
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(main)
+
+        def issue():
             for s in streams:
                 s.wait_stream(main)
             for layer in range(n_layers):
                 xfer.launch(plan, layer, layer + 1, stream=streams[layer % n_streams])
             for s in streams:
                 main.wait_stream(s)
-            e1.record(main)
-            torch.cuda.synchronize()
-            ts.append(e0.elapsed_time(e1))
+
+        def timed(fn):
+            ts = []
+            for _ in range(iters):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(main)
+                fn()
+                e1.record(main)
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            return min(ts[1:])
+
+        ms_host = timed(issue)
+        side = torch.cuda.Stream(dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            main_saved, main = main, side        # capture on a side stream, fan out from it
+            with torch.cuda.graph(g, stream=side):
+                issue()
+            main = main_saved
+        torch.cuda.synchronize()
+        ms_graph = timed(g.replay)
         assert xfer.check_status() == (0, 0)
-        ms = min(ts[1:])
         nbytes = tokens * 2 * 2 * HEAD_DIM * 2 * n_layers
-        res[name] = {"ms": round(ms, 3), "src_GBps": round(nbytes / ms / 1e6, 1), "tma": bool(xfer.use_tma),
+        res[name] = {"ms_host_launched": round(ms_host, 3), "ms_graph_replay": round(ms_graph, 3),
+                     "src_GBps_host_launched": round(nbytes / ms_host / 1e6, 1),
+                     "src_GBps_graph_replay": round(nbytes / ms_graph / 1e6, 1), "tma": bool(xfer.use_tma),
                      "dst_bytes": tokens * dst_l.token_bytes // 2 * n_layers}
         del dst
     return res
