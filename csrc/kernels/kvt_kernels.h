@@ -89,6 +89,8 @@ typedef struct KvtAttnLaunch {
   uint32_t* done_counter;      // device, zero before launch; may be NULL with flag == NULL
   uint64_t* flag;              // completion word (device / peer / host-mapped) or NULL
   uint64_t flag_value;         // value stored to *flag by the last CTA after a system fence
+  uint32_t simt_tile;          // SIMT path: 0 / 1 = a warp per tile (device destinations), 2 = a CTA per tile
+                               // (mapped host destinations: longer contiguous PCIe writes)
 } KvtAttnLaunch;
 
 // Tile count of one request for a given tile size (host helper, also used by tests).

@@ -218,7 +218,8 @@ struct RowIter {
 };
 
 __device__ __forceinline__ void simt_copy_tile(const KvtAttnLaunch& p, const TileInfo& ti, uint32_t kv,
-                                               const char* __restrict__ src, char* __restrict__ dst) {
+                                       const char* __restrict__ src, char* __restrict__ dst, uint32_t tid,
+                                       uint32_t nthr) {
   const uint32_t cpr = p.src.head_bytes >> 4;  // 16-byte chunks per row
   RowIter it;
   it.ntok = ti.copy_hi - ti.copy_lo;
@@ -232,12 +233,12 @@ __device__ __forceinline__ void simt_copy_tile(const KvtAttnLaunch& p, const Til
                          (int64_t)(ti.d_slot0 + (ti.copy_lo - ti.tok_lo)) * p.dst.token_stride +
                          (int64_t)p.dst_head0 * p.dst.head_stride;
   constexpr int U = 4;
-  for (uint32_t base = threadIdx.x; base < chunks; base += blockDim.x * U) {
+  for (uint32_t base = tid; base < chunks; base += nthr * U) {
     int4 v[U];
     int64_t doff[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const uint32_t i = base + u * blockDim.x;
+      const uint32_t i = base + u * nthr;
       doff[u] = -1;
       if (i < chunks) {
         const uint32_t row = i / cpr;
@@ -258,7 +259,8 @@ __device__ __forceinline__ void simt_copy_tile(const KvtAttnLaunch& p, const Til
 // bf16 source rows -> e4m3 rows + UE8M0 scales.  One thread converts 16 values (32 B in,
 // 16 B out); two neighbouring lanes form one 32-value scale group.
 __device__ __forceinline__ void simt_quant_tile(const KvtAttnLaunch& p, const TileInfo& ti, uint32_t kv,
-                                                const char* __restrict__ src, char* __restrict__ dst) {
+                                       const char* __restrict__ src, char* __restrict__ dst, uint32_t tid,
+                                       uint32_t nthr) {
   const uint32_t cpr = p.src.head_bytes >> 5;  // 32-byte source chunks per row (even: head_dim % 32 == 0)
   RowIter it;
   it.ntok = ti.copy_hi - ti.copy_lo;
@@ -275,41 +277,52 @@ __device__ __forceinline__ void simt_quant_tile(const KvtAttnLaunch& p, const Ti
   const int64_t sc_base = d_blk + p.dst.scale_base + (int64_t)kv * p.dst.scale_kv_stride +
                           (int64_t)slot_d * p.dst.scale_token_stride +
                           (int64_t)p.dst_head0 * p.dst.scale_head_stride;
-  const uint32_t rounds = (chunks + blockDim.x - 1) / blockDim.x;
-  for (uint32_t rnd = 0; rnd < rounds; ++rnd) {
-    const uint32_t i = rnd * blockDim.x + threadIdx.x;
-    const bool active = i < chunks;
-    uint32_t w[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    uint32_t row = 0, c = 0, t = 0, h = 0;
-    if (active) {
-      row = i / cpr;
-      c = i - row * cpr;
-      it.decode(row, t, h);
-      const char* sp = src + s_base + (int64_t)t * p.src.token_stride + (int64_t)h * p.src.head_stride + (c << 5);
-      const int4 a = ld_nc_16(sp);
-      const int4 b = ld_nc_16(sp + 16);
-      w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
-      w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
-    }
-    float amax = 0.f;
+  // Two rounds in flight per thread: the loads of both are issued before either is converted.
+  const uint32_t rounds = (chunks + nthr - 1) / nthr;
+  for (uint32_t rnd = 0; rnd < rounds; rnd += 2) {
+    uint32_t w[2][8];
+    uint32_t t[2] = {0, 0}, h[2] = {0, 0}, c[2] = {0, 0};
+    bool active[2];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      amax = fmaxf(amax, fabsf(bf16lo(w[k])));
-      amax = fmaxf(amax, fabsf(bf16hi(w[k])));
+    for (int u = 0; u < 2; ++u) {
+      const uint32_t i = (rnd + u) * nthr + tid;
+      active[u] = (rnd + u) < rounds && i < chunks;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) w[u][k] = 0;
+      if (active[u]) {
+        const uint32_t row = i / cpr;
+        c[u] = i - row * cpr;
+        it.decode(row, t[u], h[u]);
+        const char* sp = src + s_base + (int64_t)t[u] * p.src.token_stride + (int64_t)h[u] * p.src.head_stride + (c[u] << 5);
+        const int4 a = ld_nc_16(sp);
+        const int4 b = ld_nc_16(sp + 16);
+        w[u][0] = a.x; w[u][1] = a.y; w[u][2] = a.z; w[u][3] = a.w;
+        w[u][4] = b.x; w[u][5] = b.y; w[u][6] = b.z; w[u][7] = b.w;
+      }
     }
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    const uint32_t e = ue8m0_from_amax(amax);
-    const float inv = __uint_as_float((254u - e) << 23);  // 1 / 2^(e-127)
-    if (active) {
-      int4 q;
-      q.x = pack_e4m3x4(bf16lo(w[0]) * inv, bf16hi(w[0]) * inv, bf16lo(w[1]) * inv, bf16hi(w[1]) * inv);
-      q.y = pack_e4m3x4(bf16lo(w[2]) * inv, bf16hi(w[2]) * inv, bf16lo(w[3]) * inv, bf16hi(w[3]) * inv);
-      q.z = pack_e4m3x4(bf16lo(w[4]) * inv, bf16hi(w[4]) * inv, bf16lo(w[5]) * inv, bf16hi(w[5]) * inv);
-      q.w = pack_e4m3x4(bf16lo(w[6]) * inv, bf16hi(w[6]) * inv, bf16lo(w[7]) * inv, bf16hi(w[7]) * inv);
-      st_16(dst + d_base + (int64_t)t * p.dst.token_stride + (int64_t)h * p.dst.head_stride + (c << 4), q);
-      if ((c & 1u) == 0u) {
-        dst[sc_base + (int64_t)t * p.dst.scale_token_stride + (int64_t)h * p.dst.scale_head_stride + (c >> 1)] =
-            static_cast<char>(e);
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      float amax = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        amax = fmaxf(amax, fabsf(bf16lo(w[u][k])));
+        amax = fmaxf(amax, fabsf(bf16hi(w[u][k])));
+      }
+      // the partner lane holds the other half of the 32-value group (all lanes take part in the shuffle)
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      const uint32_t e = ue8m0_from_amax(amax);
+      const float inv = __uint_as_float((254u - e) << 23);  // 1 / 2^(e-127)
+      if (active[u]) {
+        int4 q;
+        q.x = pack_e4m3x4(bf16lo(w[u][0]) * inv, bf16hi(w[u][0]) * inv, bf16lo(w[u][1]) * inv, bf16hi(w[u][1]) * inv);
+        q.y = pack_e4m3x4(bf16lo(w[u][2]) * inv, bf16hi(w[u][2]) * inv, bf16lo(w[u][3]) * inv, bf16hi(w[u][3]) * inv);
+        q.z = pack_e4m3x4(bf16lo(w[u][4]) * inv, bf16hi(w[u][4]) * inv, bf16lo(w[u][5]) * inv, bf16hi(w[u][5]) * inv);
+        q.w = pack_e4m3x4(bf16lo(w[u][6]) * inv, bf16hi(w[u][6]) * inv, bf16lo(w[u][7]) * inv, bf16hi(w[u][7]) * inv);
+        st_16(dst + d_base + (int64_t)t[u] * p.dst.token_stride + (int64_t)h[u] * p.dst.head_stride + (c[u] << 4), q);
+        if ((c[u] & 1u) == 0u) {
+          dst[sc_base + (int64_t)t[u] * p.dst.scale_token_stride + (int64_t)h[u] * p.dst.scale_head_stride +
+              (c[u] >> 1)] = static_cast<char>(e);
+        }
       }
     }
   }
@@ -317,7 +330,8 @@ __device__ __forceinline__ void simt_quant_tile(const KvtAttnLaunch& p, const Ti
 
 // e4m3 rows + UE8M0 scales -> bf16 rows.  One thread expands 16 values (16 B in, 32 B out).
 __device__ __forceinline__ void simt_dequant_tile(const KvtAttnLaunch& p, const TileInfo& ti, uint32_t kv,
-                                                  const char* __restrict__ src, char* __restrict__ dst) {
+                                       const char* __restrict__ src, char* __restrict__ dst, uint32_t tid,
+                                       uint32_t nthr) {
   const uint32_t cpr = p.src.head_bytes >> 4;
   RowIter it;
   it.ntok = ti.copy_hi - ti.copy_lo;
@@ -334,7 +348,7 @@ __device__ __forceinline__ void simt_dequant_tile(const KvtAttnLaunch& p, const 
                           (int64_t)p.src_head0 * p.src.scale_head_stride;
   const int64_t d_base = (int64_t)ti.dblk * p.dst.block_stride + (int64_t)kv * p.dst.kv_stride +
                          (int64_t)slot_d * p.dst.token_stride + (int64_t)p.dst_head0 * p.dst.head_stride;
-  for (uint32_t i = threadIdx.x; i < chunks; i += blockDim.x) {
+  for (uint32_t i = tid; i < chunks; i += nthr) {
     const uint32_t row = i / cpr;
     const uint32_t c = i - row * cpr;
     uint32_t t, h;
@@ -364,7 +378,7 @@ __device__ __forceinline__ void simt_dequant_tile(const KvtAttnLaunch& p, const 
 
 // Zero destination slots [copy_hi, zero_hi) of a tile (tail pad of the last block).
 __device__ __forceinline__ void simt_zero_tail(const KvtAttnLaunch& p, const TileInfo& ti, uint32_t kv,
-                                               char* __restrict__ dst) {
+                                               char* __restrict__ dst, uint32_t tid, uint32_t nthr) {
   const uint32_t ntok = ti.zero_hi - ti.copy_hi;
   if (ntok == 0) return;
   const uint32_t cpr = p.dst.head_bytes >> 4;
@@ -376,7 +390,7 @@ __device__ __forceinline__ void simt_zero_tail(const KvtAttnLaunch& p, const Til
   const int64_t d_base = (int64_t)ti.dblk * p.dst.block_stride + (int64_t)kv * p.dst.kv_stride +
                          (int64_t)(ti.d_slot0 + (ti.copy_hi - ti.tok_lo)) * p.dst.token_stride +
                          (int64_t)p.dst_head0 * p.dst.head_stride;
-  for (uint32_t i = threadIdx.x; i < chunks; i += blockDim.x) {
+  for (uint32_t i = tid; i < chunks; i += nthr) {
     const uint32_t row = i / cpr;
     const uint32_t c = i - row * cpr;
     uint32_t t, h;
@@ -386,10 +400,45 @@ __device__ __forceinline__ void simt_zero_tail(const KvtAttnLaunch& p, const Til
   }
 }
 
+// A warp owns a tile (WARP: many tiles in flight per SM, nobody waits at tile boundaries; best when
+// the destination is device memory) or the whole CTA shares one (longer contiguous write runs,
+// which is what a PCIe destination prefers).
+template <int MODE, bool USE_TMA, bool WARP>
+__device__ __forceinline__ void simt_pass(const KvtAttnLaunch& p, uint64_t total, uint32_t per_layer) {
+  const uint32_t tid = WARP ? (threadIdx.x & 31u) : threadIdx.x;
+  const uint32_t nthr = WARP ? 32u : blockDim.x;
+  const uint32_t owners = WARP ? (blockDim.x >> 5) : 1u;
+  const uint32_t me = WARP ? (threadIdx.x >> 5) : 0u;
+  for (uint64_t w = (uint64_t)blockIdx.x * owners + me; w < total; w += (uint64_t)gridDim.x * owners) {
+    const uint32_t layer = (uint32_t)(w / per_layer);
+    const uint32_t rem = (uint32_t)(w - (uint64_t)layer * per_layer);
+    const uint32_t kv = rem / p.total_tiles;
+    const uint32_t tile = rem - kv * p.total_tiles;
+    const TileInfo ti = decode_tile(p, tile);
+    if (!ti.ok) {
+      if (tid == 0) set_status(p.status, KVT_ERR_BLOCK_RANGE, tile);
+      continue;
+    }
+    const char* src = reinterpret_cast<const char*>(p.src_layers[p.layer_begin + layer]);
+    char* dst = reinterpret_cast<char*>(p.dst_layers[p.layer_begin + layer]);
+    if (ti.copy_hi > ti.copy_lo) {
+      if constexpr (MODE == KVT_MODE_COPY) {
+        if (!(USE_TMA && tile_is_full(p, ti))) simt_copy_tile(p, ti, kv, src, dst, tid, nthr);
+      } else if constexpr (MODE == KVT_MODE_BF16_TO_MXFP8) {
+        simt_quant_tile(p, ti, kv, src, dst, tid, nthr);
+      } else {
+        simt_dequant_tile(p, ti, kv, src, dst, tid, nthr);
+      }
+    }
+    if (ti.zero_hi > ti.copy_hi) simt_zero_tail(p, ti, kv, dst, tid, nthr);
+  }
+}
+
 // ---- the kernel ---------------------------------------------------------------------------
 template <int MODE, bool USE_TMA>
 __global__ void __launch_bounds__(512) kvt_p2d_attn_kernel(const __grid_constant__ KvtAttnLaunch p,
-                                                            const uint32_t n_stages, const uint32_t tile_bytes) {
+                                                            const uint32_t n_stages, const uint32_t tile_bytes,
+                                                            const uint32_t warp_tiles) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const uint32_t n_layers = p.layer_end - p.layer_begin;
   const uint32_t per_layer = p.total_tiles * p.src.kv_count;
@@ -495,28 +544,10 @@ __global__ void __launch_bounds__(512) kvt_p2d_attn_kernel(const __grid_constant
   }
 
   // SIMT pass: everything the TMA pass does not take.
-  for (uint64_t w = blockIdx.x; w < total; w += gridDim.x) {
-    const uint32_t layer = (uint32_t)(w / per_layer);
-    const uint32_t rem = (uint32_t)(w - (uint64_t)layer * per_layer);
-    const uint32_t kv = rem / p.total_tiles;
-    const uint32_t tile = rem - kv * p.total_tiles;
-    const TileInfo ti = decode_tile(p, tile);
-    if (!ti.ok) {
-      if (threadIdx.x == 0) set_status(p.status, KVT_ERR_BLOCK_RANGE, tile);
-      continue;
-    }
-    const char* src = reinterpret_cast<const char*>(p.src_layers[p.layer_begin + layer]);
-    char* dst = reinterpret_cast<char*>(p.dst_layers[p.layer_begin + layer]);
-    if (ti.copy_hi > ti.copy_lo) {
-      if constexpr (MODE == KVT_MODE_COPY) {
-        if (!(USE_TMA && tile_is_full(p, ti))) simt_copy_tile(p, ti, kv, src, dst);
-      } else if constexpr (MODE == KVT_MODE_BF16_TO_MXFP8) {
-        simt_quant_tile(p, ti, kv, src, dst);
-      } else {
-        simt_dequant_tile(p, ti, kv, src, dst);
-      }
-    }
-    if (ti.zero_hi > ti.copy_hi) simt_zero_tail(p, ti, kv, dst);
+  if (warp_tiles) {
+    simt_pass<MODE, USE_TMA, true>(p, total, per_layer);
+  } else {
+    simt_pass<MODE, USE_TMA, false>(p, total, per_layer);
   }
 
   // Completion: the last CTA to finish publishes the flag after a system-scope fence, so a
@@ -558,6 +589,13 @@ bool load_driver_api() {
 template <int MODE, bool USE_TMA>
 cudaError_t launch_impl(const KvtAttnLaunch& a, int grid, int threads, uint32_t stages, uint32_t tile_bytes,
                         size_t smem, cudaStream_t stream) {
+  // BLLM_KVTRANS_SIMT_TILE overrides KvtAttnLaunch::simt_tile: 1 = a warp per tile, 2 = a CTA per tile
+  static const int env_simt = [] {
+    const char* v = getenv("BLLM_KVTRANS_SIMT_TILE");
+    return v != nullptr ? atoi(v) : 0;
+  }();
+  const int choice = env_simt != 0 ? env_simt : (int)a.simt_tile;
+  const uint32_t warp_tiles = choice == 2 ? 0u : 1u;
   auto kern = kvt_p2d_attn_kernel<MODE, USE_TMA>;
   if (smem > 48 * 1024) {
     // the opt-in is per device and sticky: ask once per device (and again only for a larger size)
@@ -571,7 +609,7 @@ cudaError_t launch_impl(const KvtAttnLaunch& a, int grid, int threads, uint32_t 
       if (slot != nullptr) slot->store(smem, std::memory_order_relaxed);
     }
   }
-  kern<<<grid, threads, smem, stream>>>(a, stages, tile_bytes);
+  kern<<<grid, threads, smem, stream>>>(a, stages, tile_bytes, warp_tiles);
   return cudaGetLastError();
 }
 

@@ -472,6 +472,8 @@ def ttft_added(K, rank: int, world: int, dev, tokens: int = 8192, iters: int = 3
             run(False, i)
             run(True, i)
         for i in range(iters):
+            if mix:
+                run(False, 0, lengths[i])      # a new prompt length: let the libraries pick their kernels untimed
             colo.append(run(False, warmup + i, lengths[i]))
             disagg.append(run(True, warmup + i, lengths[i]))
     torch.cuda.synchronize()

@@ -108,9 +108,9 @@ class PinnedKVStore:
                 eng_ptrs = [t.data_ptr() for t in self.layers]
                 page_ptrs = [dev_ptr + i * self.page_bytes for i in range(self.num_layers)]
                 self._save_xfer = AttnTransfer(engine_layout, self.page, eng_ptrs, page_ptrs, self.device,
-                                               mode=MODE_BF16_TO_MXFP8 if fp8 else MODE_COPY, use_tma=False)
+                                               mode=MODE_BF16_TO_MXFP8 if fp8 else MODE_COPY, use_tma=False, simt_tile=2)
                 self._load_xfer = AttnTransfer(self.page, engine_layout, page_ptrs, eng_ptrs, self.device,
-                                               mode=MODE_MXFP8_TO_BF16 if fp8 else MODE_COPY, use_tma=False)
+                                               mode=MODE_MXFP8_TO_BF16 if fp8 else MODE_COPY, use_tma=False, simt_tile=2)
 
     # ---- index ----------------------------------------------------------------------------------
     def keys(self, token_ids: Sequence[int], n_blocks: int) -> List[bytes]:
