@@ -48,7 +48,7 @@ def parse_args():
     ap.add_argument("--streams", type=int, default=8, help="transfer streams the layers alternate over")
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--small", action="store_true", help="tiny case for profiler captures")
-    ap.add_argument("--mode", default="p2d", choices=["p2d", "kvstore", "migration", "ttft", "quant"],
+    ap.add_argument("--mode", default="p2d", choices=["p2d", "kvstore", "migration", "ttft", "quant", "gdn", "mla"],
                     help="p2d: prefill->decode transfer (the headline); kvstore: host-DRAM store save/load GB/s; "
                          "migration: decode->decode latency against the number of blocks")
     ap.add_argument("--prompt-mix", action="store_true",
@@ -166,6 +166,21 @@ def main():
             print(json.dumps({"metric": "kvstore_save_load_GBps", "unit": "GB/s", "n_gpus": 1, "dtype": "bf16",
                               "config": {"model": MODEL, "layers": args.layers, "store": "pinned host DRAM (POSIX shm)"},
                               "result": res}))
+        return
+    if args.mode in ("gdn", "mla"):
+        from llumnix_kv_b200.bench_support import hybrid_state_bandwidth
+
+        res = hybrid_state_bandwidth(K, rank, world, dev, which=args.mode, tokens=2048 if args.small else 32768,
+                                     steps=args.steps if args.steps != 20 else 10, warmup=args.warmup, small=args.small)
+        if rank == 0:
+            model = ("qwen3-next-like hybrid pages (GDN state 16x128x128 fp32 + conv, attention 2 kv heads x 256, bf16)"
+                     if args.mode == "gdn" else "deepseek-v3.2-like MLA (latent+rope 656 B/token, indexer 132 B/token, 64-token blocks)")
+            print(json.dumps({"metric": "hybrid_state_transfer_GBps", "unit": "GB/s", "n_gpus": args.gpus,
+                              "higher_is_better": True, "config": {"model": model, "seq_len": res["tokens"],
+                                                                   "api": "KVTransferClient (engine, NVLINK transport, descriptor path)"},
+                              "result": res}))
+        if world > 1:
+            dist.destroy_process_group()
         return
     if args.mode == "ttft":
         from llumnix_kv_b200.bench_support import ttft_added

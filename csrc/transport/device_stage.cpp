@@ -116,6 +116,21 @@ void DeviceStage::enqueue(uint64_t src_base, uint64_t dst_base, const std::vecto
   used_ += n;
 }
 
+void DeviceStage::launch_resident(uint64_t src_base, uint64_t dst_base, const uint64_t* d_triples, size_t n,
+                                  uint64_t src_cap, uint64_t dst_cap, int grid_ctas) {
+  if (n == 0) return;
+  cuda_check(cudaSetDevice(device_), "cudaSetDevice");
+  cudaStream_t s = static_cast<cudaStream_t>(stream_);
+  const size_t max_per_launch = env_kernel_copy_max_block_num();
+  int grid = grid_ctas;
+  if (grid <= 0) grid = std::max(1, static_cast<int>(kvt_sm_count(device_) * env_kernel_copy_sm_usage()));
+  for (size_t off = 0; off < n; off += max_per_launch) {
+    const uint32_t cnt = static_cast<uint32_t>(std::min(max_per_launch, n - off));
+    cuda_check(kvt_launch_copy_blocks(src_base, dst_base, d_triples + off * 3, cnt, src_cap, dst_cap, d_status_, grid, s),
+               "kvt_launch_copy_blocks");
+  }
+}
+
 void DeviceStage::sync() {
   cuda_check(cudaSetDevice(device_), "cudaSetDevice");
   cudaStream_t s = static_cast<cudaStream_t>(stream_);

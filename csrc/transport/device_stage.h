@@ -40,6 +40,10 @@ class DeviceStage {
   explicit DeviceStage(int device);
   ~DeviceStage();
   DeviceStage(const DeviceStage&) = delete;
+  // Launch the copy over descriptors that already sit in device memory (uploaded by the caller and
+  // ordered before this stream by an event); does not wait.
+  void launch_resident(uint64_t src_base, uint64_t dst_base, const uint64_t* d_triples, size_t n, uint64_t src_cap,
+                       uint64_t dst_cap, int grid_ctas = 0);
   // Enqueue the copy; does not wait.
   void enqueue(uint64_t src_base, uint64_t dst_base, const std::vector<Triple>& triples, uint64_t src_cap,
                uint64_t dst_cap, int grid_ctas = 0);

@@ -216,6 +216,39 @@ class NvlinkChannel : public IChannel {
       for (const auto& b : data[t]) generic_[t].push_back(Triple{b.src_offset, b.dst_offset, b.length});
     }
     data.clear();
+    upload_generic();
+  }
+
+  // The descriptor lists are the same for every layer of the batch: upload them once (on stream 0,
+  // the other streams wait for the upload) instead of once per layer.
+  void upload_generic() {
+    size_t total = 0;
+    generic_off_.assign(generic_.size(), 0);
+    for (size_t t = 0; t < generic_.size(); ++t) {
+      generic_off_[t] = total;
+      total += generic_[t].size();
+    }
+    if (total == 0) return;
+    cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
+    const size_t bytes = total * sizeof(Triple);
+    if (bytes > d_plan_cap_) {
+      for (auto& s : stages_) s->sync();   // nothing may still read the old buffer
+      if (d_plan_ != nullptr) cuda_check(cudaFree(d_plan_), "cudaFree");
+      d_plan_cap_ = std::max<size_t>(bytes * 2, 1 << 16);
+      cuda_check(cudaMalloc(reinterpret_cast<void**>(&d_plan_), d_plan_cap_), "cudaMalloc(descriptors)");
+    }
+    char* h = h_plan_.reserve(bytes, true);
+    for (size_t t = 0; t < generic_.size(); ++t)
+      if (!generic_[t].empty()) memcpy(h + generic_off_[t] * sizeof(Triple), generic_[t].data(), generic_[t].size() * sizeof(Triple));
+    cudaStream_t s0 = static_cast<cudaStream_t>(stages_[0]->stream());
+    cuda_check(cudaMemcpyAsync(d_plan_, h, bytes, cudaMemcpyHostToDevice, s0), "cudaMemcpyAsync(descriptors)");
+    if (plan_event_ == nullptr) {
+      cudaEvent_t ev;
+      cuda_check(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate");
+      plan_event_ = ev;
+    }
+    cuda_check(cudaEventRecord(static_cast<cudaEvent_t>(plan_event_), s0), "cudaEventRecord");
+    for (size_t i = 1; i < stages_.size(); ++i) stages_[i]->wait_event(plan_event_);
   }
 
   bool send_layers(size_t layer_begin, size_t layer_end, Step* step) override {
@@ -275,8 +308,10 @@ class NvlinkChannel : public IChannel {
     const auto& addrs = ctx_->layer_data_address();
     RTASSERT(layer < addrs.size() && layer < dst_ptrs_.size());
     for (size_t t = 0; t < generic_.size(); ++t) {
+      if (generic_[t].empty()) continue;
       const size_t dst_cap = dst_.block_sizes.at(t) * static_cast<size_t>(dst_.layer_num_blocks);
-      st.enqueue(addrs[layer][t], dst_ptrs_[layer][t], generic_[t], ctx_->tensor_capacity(t), dst_cap);
+      const uint64_t* d = reinterpret_cast<const uint64_t*>(d_plan_) + generic_off_[t] * 3;
+      st.launch_resident(addrs[layer][t], dst_ptrs_[layer][t], d, generic_[t].size(), ctx_->tensor_capacity(t), dst_cap);
     }
   }
 
@@ -366,6 +401,7 @@ class NvlinkChannel : public IChannel {
   PinnedBuffer h_status_;
   // generic path
   std::vector<std::vector<Triple>> generic_;
+  std::vector<size_t> generic_off_;   // first descriptor of each tensor inside the uploaded buffer
   size_t origin_blocks_{0}, merged_blocks_{0}, moved_bytes_per_layer_{0};
 };
 

@@ -578,3 +578,133 @@ def quant_reshard_bandwidth(dev, tokens: int = 8192, n_layers: int = 80, iters: 
                      "dst_bytes": tokens * dst_l.token_bytes // 2 * n_layers}
         del dst
     return res
+
+
+def hybrid_state_bandwidth(K, rank: int, world: int, dev, which: str = "gdn", tokens: int = 32768, steps: int = 10,
+                           warmup: int = 3, small: bool = False) -> dict:
+    """Hybrid-attention and MLA caches through the engine (KVTransferClient -> NVLink channel ->
+    descriptor copy kernel), rank r -> rank r + world/2 (one GPU: loopback).
+
+    ``gdn``: Qwen3-Next-like pages: 48 layers in a 3:1 GDN:attention pattern = 12 physical cache tensors
+    whose pages hold either attention KV (2 KV heads x 256 dims, bf16, kernel blocks of 16 tokens) or one
+    request's recurrent state of a GDN layer (conv 3 x 8192 bf16 + 16 heads x 128 x 128 fp32).
+    ``mla``: DeepSeek-V3.2-like: 61 layers, two tensors per layer: indexer keys (128 fp8 + scale = 132 B per
+    token) and latent + rope (656 B per token), 64-token blocks, identical on every TP rank."""
+    import random
+
+    from .kv_transfer_impl import KVTransferClient, KVTransferProtocolType as PT, KVTransferServer
+
+    n_pairs = max(world // 2, 1)
+    sender = world == 1 or rank < n_pairs
+    receiver = world == 1 or rank >= n_pairs
+    pair = rank % n_pairs
+    rng = random.Random(17)
+    if which == "gdn":
+        n_tensors_per_layer, n_layers, shape = 1, 2 if small else 12, 3
+        tok = 2 * 2 * 256 * 2
+        conv_rows, dims, ssm = 3, [2048, 2048, 4096], [1, 16, 128, 128]
+        state_bytes = conv_rows * sum(dims) * 2 + 16 * 128 * 128 * 4
+        ntpb = (state_bytes + tok - 1) // tok
+        ntpb = (ntpb + 15) // 16 * 16
+        sizes, toks = [ntpb * tok], [tok]
+        kw = dict(num_kv_heads=2, num_gdn_layers=3, conv_state_shape=[1, conv_rows, sum(dims)], ssm_state_shape=ssm,
+                  gdn_conv_channel_dims=dims, gdn_conv_elem_size=2, gdn_ssm_elem_size=4, attn_kernel_blk_ntpb=16)
+        n_attn = (tokens + ntpb - 1) // ntpb
+        n_blocks = n_attn + 3 + 2
+        ids_s, ids_d = rng.sample(range(1, n_blocks), n_attn + 3), rng.sample(range(1, n_blocks), n_attn + 3)
+        sb = [[ids_s[0]], [ids_s[1]], [ids_s[2]], ids_s[3:]]
+        db = [[ids_d[0]], [ids_d[1]], [ids_d[2]], ids_d[3:]]
+    else:
+        n_tensors_per_layer, n_layers, shape = 2, 4 if small else 61, 4
+        toks, ntpb = [132, 656], 64
+        sizes = [t * ntpb for t in toks]
+        kw = dict(num_kv_heads=1)
+        n_attn = (tokens + ntpb - 1) // ntpb
+        n_blocks = n_attn + 2
+        sb, db = [rng.sample(range(1, n_blocks), n_attn)], [rng.sample(range(1, n_blocks), n_attn)]
+
+    def alloc(fill):
+        out = []
+        for layer in range(n_layers):
+            ts = []
+            for bs in sizes:
+                t = torch.empty(bs * n_blocks, dtype=torch.uint8, device=dev)
+                if fill:
+                    g = torch.Generator(device=dev)
+                    g.manual_seed(layer + 1)
+                    t.copy_(torch.randint(1, 255, t.shape, dtype=torch.uint8, device=dev, generator=g))
+                    t[:bs] = 0
+                else:
+                    t.zero_()
+                ts.append(t)
+            out.append(ts)
+        return out
+
+    dst_inst = f"D{pair}|0|1"
+    srv = cli = None
+    winfo = None
+    if receiver:
+        dst = alloc(False)
+        srv = KVTransferServer(dst_inst, 1, 0, 0, list(sizes), list(toks), "fake://", dst, [PT.NVLINK], cache_shape=shape, **kw)
+        winfo = srv.worker_info()
+    if world > 1:
+        import torch.distributed as dist
+
+        infos = [None] * world
+        dist.all_gather_object(infos, winfo)
+        if sender:
+            winfo = infos[rank + n_pairs]
+    ms = 0.0
+    moved = 0
+    ok = True
+    if sender:
+        src = alloc(True)
+        cli = KVTransferClient(f"P{pair}|0|1", 1, 0, 0, list(sizes), list(toks), "fake://", src, [PT.NVLINK],
+                               cache_shape=shape, **kw)
+        stream = torch.cuda.current_stream(dev)
+        W = K.WorkerInfo
+        pw, dw = W.from_string(cli.worker_info()), W.from_string(winfo)
+        for w_ in (pw, dw):
+            for k_, v_ in kw.items():
+                setattr(w_, k_, v_)
+        per_tensor = K.plan_ipc_blocks(pw, dw, shape, [("x", 0, tokens, True, sb, db)])[0]
+        moved = sum(n for blocks in per_tensor for _, _, n in blocks) * n_layers
+
+        def step(i):
+            stepid = 7000 + i
+            cli.submit_req_send2(dst_inst, 0, f"h{i}", 0, tokens, True, sb, db, winfo, stepid=stepid)
+            cli.start_send_step(stepid, 1)
+            for layer in range(n_layers):
+                cli.record_event(layer, stream)
+            cli.flush_send_step()
+            cli.drain()
+
+        for i in range(warmup):
+            step(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(steps):
+            step(warmup + i)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if world == 1:
+            for layer in (0, n_layers - 1):
+                for t, blocks in enumerate(per_tensor):
+                    s_, d_ = src[layer][t], dst[layer][t]
+                    for s_off, d_off, n in blocks[:64] + blocks[-64:]:
+                        ok = ok and bool(torch.equal(d_[d_off:d_off + n], s_[s_off:s_off + n]))
+    if world > 1:
+        import torch.distributed as dist
+
+        t = torch.tensor([ms, float(moved), float(ok)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, moved = float(t[0]), int(t[1])
+        dist.barrier()
+    if srv is not None:
+        srv.stop()
+    gbps = n_pairs * moved * steps / (ms * 1e-3) / 1e9 if ms > 0 else 0.0
+    return {"which": which, "tokens": tokens, "layers_or_tensors": n_layers * n_tensors_per_layer,
+            "bytes_per_step_per_pair": moved, "ms_per_step": round(ms / max(steps, 1), 4), "GBps": round(gbps, 1),
+            "per_pair_GBps": round(gbps / n_pairs, 1), "verified": ok}
