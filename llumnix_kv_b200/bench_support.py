@@ -608,7 +608,11 @@ def hybrid_state_bandwidth(K, rank: int, world: int, dev, which: str = "gdn", to
         ntpb = (ntpb + 15) // 16 * 16
         sizes, toks = [ntpb * tok], [tok]
         kw = dict(num_kv_heads=2, num_gdn_layers=3, conv_state_shape=[1, conv_rows, sum(dims)], ssm_state_shape=ssm,
-                  gdn_conv_channel_dims=dims, gdn_conv_elem_size=2, gdn_ssm_elem_size=4, attn_kernel_blk_ntpb=16)
+                  gdn_conv_channel_dims=dims, gdn_conv_elem_size=2, gdn_ssm_elem_size=4)
+        # attention kernels see 16-token blocks inside the manager's large pages
+        import os
+
+        os.environ["BLLM_KVTRANS_ATTN_KERNEL_BLK_SIZE"] = "16"
         n_attn = (tokens + ntpb - 1) // ntpb
         n_blocks = n_attn + 3 + 2
         ids_s, ids_d = rng.sample(range(1, n_blocks), n_attn + 3), rng.sample(range(1, n_blocks), n_attn + 3)
