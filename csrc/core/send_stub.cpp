@@ -203,6 +203,16 @@ struct KvSendStub::Impl {
         bool device_planned = ch->register_tasks(env, send_req);
         bool have_data = device_planned;
         if (!device_planned) {
+          // Byte ranges can only describe a transfer between caches of one layout and dtype: a
+          // layout change or a block-scaled fp8 destination needs the fused kernel (NVLINK transport
+          // between GPU caches).  Refuse instead of delivering misplaced bytes.
+          const int dst_shape = dstinfo->cache_shape_or(cache_shape);
+          if (dst_shape != cache_shape || dstinfo->ext_int("mx", 0) != 0) {
+            throw KVTransferException(ErrorKind::INVALID_OPERATION,
+                                      "transfer from cache shape " + std::to_string(cache_shape) + " to shape " +
+                                          std::to_string(dst_shape) + (dstinfo->ext_int("mx", 0) != 0 ? " (block-scaled fp8)" : "") +
+                                          " needs the fused kernel of the NVLINK transport; channel is " + ch->name());
+          }
           for (const ReqSendTask* t : send_req) plan_request(planner, env, *t, send_blocks);
           have_data = !send_blocks.empty() && !send_blocks[0].empty();
           if (have_data) ch->register_data(send_blocks, planner.kind);

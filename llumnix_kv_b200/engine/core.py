@@ -64,6 +64,11 @@ class MiniEngineCore:
         self._tokens: dict[str, list] = {}
         self._cv = threading.Condition()
         self.steps = 0
+        self.bypass_substeps = 0
+        self._last_sout = None
+        from llumnix_kv_b200 import envs as _envs
+
+        self._bypass = bool(_envs.VLLM_ENABLE_BYPASS_TASK)
         if start:
             self.start()
 
@@ -151,8 +156,20 @@ class MiniEngineCore:
                 or (self.connector is not None and self.connector.has_requests())):
             return
         sout = self.scheduler.schedule()
+        if self.connector is not None and self._bypass and sout.total_num_scheduled_tokens == 0 \
+                and not sout.finished_req_ids and self._last_sout is not None:
+            # Nothing to compute, but the connector has work for the workers (a decode engine asked
+            # for KV that is already complete): hand it to them as a substep of the last step
+            # through the bypass channel instead of running an empty forward pass.
+            sout.hc_parent = self._last_sout
+            meta = self.connector.build_connector_meta(sout)
+            if meta.reqs:
+                self.bypass_substeps += 1
+                self.connector._sched.send_bypass_task(meta)
+            return
         if self.connector is not None:
             sout.kv_connector_metadata = self.connector.build_connector_meta(sout)
+            self._last_sout = sout
         if sout.total_num_scheduled_tokens == 0 and not sout.kv_connector_metadata and not sout.finished_req_ids:
             return
         sampled: dict = {}

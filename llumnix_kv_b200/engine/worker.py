@@ -128,6 +128,7 @@ class MiniWorker:
             self.connector = HybridConnector(cfg, KVConnectorRole.WORKER, self.kv_cache_config, worker=self.proxy)
             self.connector.register_kv_caches(self.kv_caches)
         self._req_state: dict = {}   # reqid -> (prompt tokens, block ids of group 0)
+        self.forward_passes = 0
 
     # ---- the "model" ---------------------------------------------------------------------------
     def expected_rows(self, layer: int, tensor_idx: int, token_ids: list, lo: int, hi: int) -> torch.Tensor:
@@ -220,6 +221,7 @@ class MiniWorker:
         return self._execute_model(sout)
 
     def _execute_model(self, sout: SchedulerOutput) -> dict:
+        self.forward_passes += 1
         conn = self.connector
         meta = sout.kv_connector_metadata
         if conn is not None and meta is not None:

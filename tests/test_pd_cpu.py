@@ -264,3 +264,74 @@ def test_mla_latent_and_indexer_caches(ptp, dtp, shape, mla):
     finally:
         d.shutdown()
         p.shutdown()
+
+
+def test_cross_layout_over_a_byte_range_transport_fails_the_request_cleanly():
+    """NHD -> HND needs the fused kernel (GPU caches, NVLINK transport).  Between host-memory caches
+    the transfer is refused: the prefill side marks the request failed, the decode side aborts it
+    and nobody keeps blocks; no misplaced bytes are delivered."""
+    p, d = make_pd(p_kw=dict(cache_shape=2), d_kw=dict(cache_shape=5))
+    try:
+        d.add_request(make_req("x", 40, max_tokens=2, params={"remote_host": "127.0.0.1", "remote_port": p.proxy.rpc_port()}))
+        out = d.wait_finished("x", 30)
+        assert out is not None and out.finish_reason.name == "ABORT"
+        for e in (p, d):
+            deadline = time.time() + 5
+            while time.time() < deadline and e.scheduler.kv_cache_manager.block_pool.num_free_blocks() != 63:
+                time.sleep(0.01)
+            assert e.scheduler.kv_cache_manager.block_pool.num_free_blocks() == 63
+        assert not any(t.any() for t in d.workers[0].kv_caches.values())
+    finally:
+        d.shutdown()
+        p.shutdown()
+
+
+def test_peer_discovery_and_worker_info_through_file_naming(tmp_path):
+    """With a naming service nothing travels inside the request: the decode engine finds a prefill
+    engine through the registry (role "prefill"), and the prefill engine's native stubs look the
+    decode workers' WorkerInfo up there as well."""
+    url = f"file:{tmp_path}"
+    p, d = make_pd(p_kw=dict(extra={"naming_url": url}), d_kw=dict(extra={"naming_url": url}, tp=2))
+    try:
+        cap = _spy_add(d)
+        deadline = time.time() + 10
+        while time.time() < deadline and d.connector._sched._backend.get_peer() is None:
+            time.sleep(0.05)
+        assert d.connector._sched._backend.get_peer() == ("127.0.0.1", p.proxy.rpc_port())
+        req = make_req("n", 55, max_tokens=2)            # no remote_host / remote_port
+        d.add_request(req)
+        out = d.wait_finished("n", 30)
+        assert out is not None and out.finish_reason.name == "LENGTH"
+        computed, blocks = cap["n"]
+        assert computed == 54
+        check_decode_cache(d, "n", req.prompt_token_ids, blocks[0], 54)
+        names = {x.name for x in tmp_path.iterdir()}
+        assert {"P", "D"} <= names
+    finally:
+        d.shutdown()
+        p.shutdown()
+
+
+def test_bypass_substep_delivers_a_late_transfer_without_a_forward_pass(monkeypatch):
+    """Dual-request mode with the prefill half finished long before the decode half arrives: the
+    transfer is handed to the workers as a substep of the last engine step over the bypass channel
+    (ZMQ publish / subscribe), not by running another model step."""
+    monkeypatch.setenv("VLLM_ENABLE_BYPASS_TASK", "1")
+    p, d = make_pd()
+    try:
+        cap = _spy_add(d)
+        p.add_request(make_req("late", 50, max_tokens=1, params={"do_remote_decode": True}))
+        time.sleep(0.5)
+        steps_before = p.workers[0].forward_passes
+        dreq = make_req("late", 50, max_tokens=2, params=_dual_params(p))
+        d.add_request(dreq)
+        out = d.wait_finished("late", 30)
+        assert out is not None and out.finish_reason.name == "LENGTH"
+        computed, blocks = cap["late"]
+        assert computed == 49
+        check_decode_cache(d, "late", dreq.prompt_token_ids, blocks[0], 49)
+        assert p.bypass_substeps >= 1
+        assert p.workers[0].forward_passes == steps_before      # no extra forward pass on the prefill engine
+    finally:
+        d.shutdown()
+        p.shutdown()
