@@ -15,6 +15,8 @@ try:
         KVTransferProtocolType,
         KVTransferServer,
         ReqMeta,
+        alloc_kv_cache_peer_mappable,
+        alloc_phy_cont_mem,
         connect_naming,
         current_worker_info,
         support_transfers_protocols,

@@ -95,6 +95,45 @@ def current_worker_info(kind: str = "any") -> str:
     return _K.current_worker_info(kind)
 
 
+class _DeviceBuffer:
+    """Owner of one ``cudaMalloc`` allocation, exposed to torch through the CUDA array interface."""
+
+    def __init__(self, nbytes: int, device_index: int):
+        with torch.cuda.device(device_index):
+            self.ptr = _K.kvt_malloc(nbytes)
+        self.nbytes, self.device_index = nbytes, device_index
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (self.ptr, False), "version": 3,
+                                         "strides": None}
+
+    def __del__(self):
+        try:
+            with torch.cuda.device(self.device_index):
+                _K.kvt_free(self.ptr)
+        except Exception:  # interpreter shutdown: the driver reclaims it
+            pass
+
+
+def alloc_phy_cont_mem(nbytes: int, device_index: int = 0) -> torch.Tensor:
+    """KV-cache storage from the framework instead of the engine's caching allocator: one whole
+    ``cudaMalloc`` allocation, so its CUDA IPC handle covers exactly this cache and peers can map it
+    (the hook the reference offers for RDMA-registrable memory, kvtransfer/src/barex_protocol.cpp:808-830,
+    blade_kvt/hybrid_connector/kvtbackend.py:330-364).  Returns a flat uint8 tensor that keeps the
+    allocation alive."""
+    buf = _DeviceBuffer(int(nbytes), device_index)
+    t = torch.as_tensor(buf, device=torch.device("cuda", device_index))
+    t._kvx_owner = buf        # the tensor does not own the memory: tie the owner's life to it
+    return t
+
+
+def alloc_kv_cache_peer_mappable(cache: torch.Tensor) -> torch.Tensor:
+    """Same shape / dtype / strides as ``cache`` but backed by :func:`alloc_phy_cont_mem` (the
+    engine swaps its cache tensor for the returned one before registering it)."""
+    flat = alloc_phy_cont_mem(cache.untyped_storage().nbytes(), cache.device.index or 0)
+    out = flat.view(cache.dtype).as_strided(cache.size(), cache.stride(), cache.storage_offset())
+    out._kvx_owner = flat
+    return out
+
+
 def _get_layer_num_blocks(layers: List[torch.Tensor], block_bytes: int) -> int:
     if block_bytes <= 0:
         raise ValueError(f"block_bytes must be positive, got {block_bytes}")

@@ -49,3 +49,22 @@ def test_push_to_peer_gpu(ops, use_tma):
         expect = torch.zeros_like(src[i])
         reference_transfer(src_l, dst_l, src[i], expect, chunks)
         assert torch.equal(dst[i].to("cuda:0"), expect)
+
+
+def test_framework_allocated_cache_storage(ops):
+    """alloc_phy_cont_mem: a whole cudaMalloc allocation wrapped as a tensor; its IPC handle starts at
+    the tensor, and a cache swapped onto it keeps shape and strides."""
+    from llumnix_kv_b200.kv_transfer_impl import alloc_kv_cache_peer_mappable, alloc_phy_cont_mem
+
+    t = alloc_phy_cont_mem(1 << 20, 0)
+    assert t.dtype == torch.uint8 and t.numel() == 1 << 20 and t.is_cuda
+    t.fill_(7)
+    _h, base, size = ops.kvt_ipc_get_handle(t.data_ptr())
+    assert base == t.data_ptr() and size >= 1 << 20
+    cache = torch.zeros(2, 8, 16, 4, 64, dtype=torch.bfloat16, device="cuda:0")
+    swapped = alloc_kv_cache_peer_mappable(cache)
+    assert swapped.shape == cache.shape and swapped.stride() == cache.stride() and swapped.dtype == cache.dtype
+    swapped.copy_(torch.ones_like(cache))
+    assert float(swapped.float().sum()) == cache.numel()
+    del t, swapped
+    torch.cuda.synchronize()
