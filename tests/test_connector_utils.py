@@ -1,0 +1,131 @@
+"""Unit tests of the connector's small parts: completion counting, the native engine's send-done wire
+formats, peer records, operation-plan merging, cleanup reference counts."""
+import asyncio
+import struct
+
+import pytest
+
+from llumnix_kv_b200.engine.types import Request
+from llumnix_kv_b200.hybrid_connector.backend import (dec_cleanup_rc, inc_cleanup_rc, merge_operation_plans,
+                                                       set_operation_sources)
+from llumnix_kv_b200.hybrid_connector.engine_proxy import get_param
+from llumnix_kv_b200.hybrid_connector.utils import (CodeError, IoRet, IoState, PeerInfo, PeerManager, ConnManager,
+                                                     handle_done_req, try_advance)
+
+
+def test_io_state_counts_ranks_and_signals():
+    st = {"r": IoState(signals_per_worker=2)}
+    assert try_advance(st, IoRet(reqid="r", n=10), 0, 2) is None
+    assert try_advance(st, IoRet(reqid="r", n=12), 0, 2) is None          # rank 0 complete, rank 1 missing
+    assert try_advance(st, IoRet(reqid="r", n=9), 0, 2) is None           # a third signal from rank 0 is a duplicate
+    assert try_advance(st, IoRet(reqid="r", n=11), 1, 2) is None
+    done = try_advance(st, IoRet(reqid="r", n=13), 1, 2)
+    assert done is st["r"] and done.merge().n == 10                       # the minimum over all signals
+    assert try_advance(st, IoRet(reqid="unknown"), 0, 2) is None
+
+
+def test_io_state_with_named_sources():
+    s = IoState(signals_per_worker=2)
+    s.expected_sources = ("kvs", "kvt")
+    st = {"r": s}
+    assert try_advance(st, IoRet(reqid="r", source="kvs"), 0, 1) is None
+    assert try_advance(st, IoRet(reqid="r", source="kvs"), 0, 1) is None   # same source twice: ignored
+    assert try_advance(st, IoRet(reqid="r", source="other"), 0, 1) is None
+    assert try_advance(st, IoRet(reqid="r", source="kvt"), 0, 1) is s
+
+
+def test_merge_keeps_the_first_failure():
+    s = IoState()
+    st = {"r": s}
+    try_advance(st, IoRet(reqid="r", n=5), 0, 2)
+    try_advance(st, IoRet(reqid="r", n=0, ex=CodeError(500, "boom")), 1, 2)
+    m = s.merge()
+    assert isinstance(m.ex, CodeError) and m.ex.code == 500
+
+
+class _Writer:
+    def __init__(self):
+        self.buf = b""
+
+    def write(self, b):
+        self.buf += b
+
+    async def drain(self):
+        pass
+
+
+def _parse(body: bytes):
+    got = []
+
+    async def main():
+        reader = asyncio.StreamReader()
+        reader.feed_data(body)
+        reader.feed_eof()
+        w = _Writer()
+        await handle_done_req(reader, w, lambda rank, r: got.append((rank, r.reqid, r.n, getattr(r.ex, "code", None))), 77)
+        return w.buf
+
+    resp = asyncio.run(main())
+    assert resp == struct.pack("=I", 77)
+    return got
+
+
+def test_send_done_version2_body():
+    body = struct.pack("=II", 3 | 0x40000000, 2)
+    body += struct.pack("=III", 100, 0, 2) + b"r1" + struct.pack("=III", 0, 500, 3) + b"bad"
+    assert _parse(body) == [(3, "r1", 100, None), (3, "bad", 0, 500)]
+
+
+def test_send_done_version1_bodies():
+    plain = struct.pack("=II", 1, 2) + struct.pack("=I", 1) + b"a" + struct.pack("=I", 2) + b"bb"
+    assert _parse(plain) == [(1, "a", None, None), (1, "bb", None, None)]
+    with_plen = struct.pack("=II", 1 | 0x80000000, 2) + struct.pack("=I", 1) + b"a" + struct.pack("=I", 2) + b"bb" + \
+        struct.pack("=II", 40, 41)
+    assert _parse(with_plen) == [(1, "a", 40, None), (1, "bb", 41, None)]
+
+
+def test_peer_info_round_trip_and_bad_input():
+    p = PeerInfo(role="prefill", tpsize=4, ctime_us=123456, addr="10.0.0.7", port=33001, dprank=2)
+    assert p.serialize() == "prefill:4:123456:10.0.0.7:33001:2"
+    assert PeerInfo.deserialize(p.serialize()) == p
+    with pytest.raises(ValueError):
+        PeerInfo.deserialize("prefill:4:1")
+
+
+class _FakeNaming:
+    def __init__(self):
+        self.data = {}
+
+    def list(self):
+        return list(self.data)
+
+    def search(self, inst, prefix):
+        return [v for k, v in self.data[inst].items() if k.startswith(prefix)]
+
+
+def test_peer_manager_notices_new_restarted_and_departed_peers():
+    nm = _FakeNaming()
+    nm.data["p1"] = {"endpoint0": PeerInfo("prefill", 1, 10, "127.0.0.1", 4001, 0).serialize()}
+    nm.data["d1"] = {"endpoint0": PeerInfo("decode", 1, 11, "127.0.0.1", 4002, 0).serialize()}
+    pm = PeerManager(nm, "prefill", ConnManager(8))
+    asyncio.run(pm.refresh())
+    assert pm.get_peer() == ("127.0.0.1", 4001)                           # the decode instance is not of interest
+    assert pm.get_peer(exclude=("127.0.0.1", 4001)) is None
+    nm.data["p1"] = {"endpoint0": PeerInfo("prefill", 1, 99, "127.0.0.1", 4011, 0).serialize()}   # restarted elsewhere
+    asyncio.run(pm.refresh())
+    assert pm.get_peer() == ("127.0.0.1", 4011)
+    del nm.data["p1"]
+    asyncio.run(pm.refresh())
+    assert pm.get_peer() is None
+
+
+def test_operation_plans_and_cleanup_refcount():
+    assert merge_operation_plans((1, 0, ("kvs",), ()), (0, 1, (), ("kvt",)), (0, 1, (), ("kvs",))) == \
+        (1, 2, ("kvs",), ("kvt", "kvs"))
+    req = Request("r", [1, 2, 3])
+    set_operation_sources(req, load_sources=("kvs",), save_sources=("kvt", "kvs"))
+    assert get_param(req, "_HybridBackend_SAVE_SOURCES") == ("kvt", "kvs")
+    assert inc_cleanup_rc(req) == 1 and inc_cleanup_rc(req) == 2
+    assert dec_cleanup_rc(req) == 1 and dec_cleanup_rc(req) == 0
+    with pytest.raises(AssertionError):
+        dec_cleanup_rc(req)
