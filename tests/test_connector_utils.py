@@ -129,3 +129,27 @@ def test_operation_plans_and_cleanup_refcount():
     assert dec_cleanup_rc(req) == 1 and dec_cleanup_rc(req) == 0
     with pytest.raises(AssertionError):
         dec_cleanup_rc(req)
+
+
+def test_backend_selection_table():
+    from pd_helpers import make_cfg
+    from llumnix_kv_b200.hybrid_connector.backend import get_backend_cls
+
+    def pick(backend, role):
+        return get_backend_cls(make_cfg(role, "x", backend=backend)).__name__
+
+    assert pick("kvt", "kv_producer") == "PBackend" and pick("kvt", "kv_consumer") == "DBackend"
+    assert pick("kvt", "kv_both") == "FilePBackend"
+    assert pick("migration", "kv_both") == "MigrationBackend"
+    assert pick("kvt+migration", "kv_both") == pick("migration+kvt", "kv_both") == "KVTMigration"
+    assert pick("kvt+kvs", "kv_producer") == pick("kvs+kvt", "kv_producer") == "KVSP"
+    assert pick("local_file", "kv_both") == "FileBackend"
+    for b in ("kvs", "mooncake", "v6d_object"):
+        assert pick(b, "kv_both") == "KVSBackend"
+        with pytest.raises(AssertionError):
+            pick(b, "kv_producer")
+    assert pick("v6d_object+kvt", "kv_producer") == "KVSP"
+    with pytest.raises(ValueError):
+        pick("v6d_object+kvt", "kv_consumer")
+    with pytest.raises(ValueError):
+        pick("nope", "kv_both")
