@@ -152,7 +152,21 @@ def main():
     if args.mode == "quant":
         from llumnix_kv_b200.bench_support import quant_reshard_bandwidth
 
-        res = quant_reshard_bandwidth(dev, tokens=2048 if args.small else args.tokens, n_layers=8 if args.small else 80)
+        if world > 1:
+            from llumnix_kv_b200.bench_support import quant_reshard_nvlink
+
+            res = quant_reshard_nvlink(K, rank, world, dev, tokens=2048 if args.small else args.tokens,
+                                       n_layers=8 if args.small else 80)
+        else:
+            res = quant_reshard_bandwidth(dev, tokens=2048 if args.small else args.tokens, n_layers=8 if args.small else 80)
+        if world > 1:
+            if rank == 0:
+                print(json.dumps({"metric": "tp_mismatch_fp8_transfer_GBps", "unit": "GB/s", "n_gpus": args.gpus,
+                                  "dtype": "bf16->mxfp8", "config": {
+                                      "model": "llama-3-70b-kv (80L, 8 kv heads, 128d), prefill TP4 ranks -> decode TP2 ranks over "
+                                               "NVLink, NHD -> HND", "seq_len": args.tokens}, "result": res}))
+            dist.destroy_process_group()
+            return
         if rank == 0:
             print(json.dumps({"metric": "tp_mismatch_fp8_transfer_GBps", "unit": "GB/s", "n_gpus": 1, "dtype": "bf16->mxfp8",
                               "config": {"model": "llama-3-70b-kv (80L, 8 kv heads, 128d), prefill TP4 rank -> decode TP2 rank, "

@@ -712,3 +712,118 @@ def hybrid_state_bandwidth(K, rank: int, world: int, dev, which: str = "gdn", to
     return {"which": which, "tokens": tokens, "layers_or_tensors": n_layers * n_tensors_per_layer,
             "bytes_per_step_per_pair": moved, "ms_per_step": round(ms / max(steps, 1), 4), "GBps": round(gbps, 1),
             "per_pair_GBps": round(gbps / n_pairs, 1), "verified": ok}
+
+
+def quant_reshard_nvlink(K, rank: int, world: int, dev, tokens: int = 8192, n_layers: int = 80, iters: int = 5,
+                         n_streams: int = 8) -> dict:
+    """The TP-mismatch fp8 transfer across GPUs: ranks [0, world/2) are ranks of a prefill TP=4 group
+    (2 KV heads each, bf16, NHD); prefill ranks 2j and 2j+1 both push into decode rank world/2 + j
+    (TP=2 rank: 4 heads, HND, block-scaled fp8), each into its half of the heads, over NVLink.  world=8
+    is the whole group: GPUs 0-3 -> GPUs 4-5.  Kernel-only, device-timed, max over ranks."""
+    import random
+
+    import torch.distributed as dist
+
+    from .ops.p2d_attn import MODE_BF16_TO_MXFP8, HeadMap, mx_quantize_reference
+
+    n_p = world // 2
+    n_d = max(n_p // 2, 1)
+    sender = rank < n_p
+    receiver = n_p <= rank < n_p + n_d
+    n_blk = (tokens + BLOCK - 1) // BLOCK
+    src_l = AttnLayout(CacheShape.FLASH, n_blk + 1, BLOCK, 2, HEAD_DIM, 2)
+    dst_l = AttnLayout(CacheShape.FLASHINFER, n_blk + 1, BLOCK, 4, HEAD_DIM, 1, mx_scaled=True)
+    rng = random.Random(5)
+    sb, db = rng.sample(range(1, n_blk + 1), n_blk), rng.sample(range(1, n_blk + 1), n_blk)
+    mine = None
+    dst = None
+    if receiver:
+        dst = torch.zeros(n_layers * dst_l.layer_bytes, dtype=torch.uint8, device=dev)
+        h, base, _size = K.kvt_ipc_get_handle(dst.data_ptr())
+        mine = (h, dst.data_ptr() - base)
+    infos = [None] * world
+    dist.all_gather_object(infos, mine)
+    ms_host = ms_graph = 0.0
+    src = None
+    if sender:
+        d_rank = n_p + min(rank // 2, n_d - 1)
+        h, off = infos[d_rank]
+        peer = K.kvt_ipc_open_handle(h)
+        dst_ptrs = [peer + off + i * dst_l.layer_bytes for i in range(n_layers)]
+        src = [src_l.alloc(dev, fill="normal", seed=1000 * rank + i) for i in range(n_layers)]
+        xfer = AttnTransfer(src_l, dst_l, [t.data_ptr() for t in src], dst_ptrs, dev,
+                            head_map=HeadMap(0, (rank % 2) * 2, 2), mode=MODE_BF16_TO_MXFP8)
+        streams = [torch.cuda.Stream(dev) for _ in range(n_streams)]
+        holder = {"main": torch.cuda.current_stream(dev)}
+        plan = xfer.plan([ReqChunk(sb, db, 0, tokens)])
+        torch.cuda.synchronize()
+
+        def issue():
+            for s in streams:
+                s.wait_stream(holder["main"])
+            for layer in range(n_layers):
+                xfer.launch(plan, layer, layer + 1, stream=streams[layer % n_streams])
+            for s in streams:
+                holder["main"].wait_stream(s)
+
+        issue()
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream(dev)
+        g = torch.cuda.CUDAGraph()
+        keep = holder["main"]
+        holder["main"] = side
+        with torch.cuda.graph(g, stream=side):
+            issue()
+        holder["main"] = keep
+        torch.cuda.synchronize()
+    dist.barrier()
+
+    def timed(fn):
+        best = 1e30
+        for _ in range(iters):
+            dist.barrier()
+            torch.cuda.synchronize()
+            ms = 0.0
+            if sender:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                ms = e0.elapsed_time(e1)
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            best = min(best, float(t.item()))
+        return best
+
+    ms_host = timed(issue if sender else (lambda: None))
+    ms_graph = timed(g.replay if sender else (lambda: None))
+    ok = True
+    if sender:
+        ok = xfer.check_status() == (0, 0)
+    dist.barrier()
+    if receiver:
+        # regenerate what both feeding prefill ranks hold for layer 0 and compare codes and scales
+        for j in range(2):
+            p_rank = 2 * (rank - n_p) + j
+            if p_rank >= n_p:
+                continue
+            s0 = src_l.alloc(dev, fill="normal", seed=1000 * p_rank)
+            nb = min(tokens // BLOCK, 64)
+            x = src_l.view(s0, torch.bfloat16)[torch.tensor(sb[:nb], device=dev)].float()       # [blk, kv, slot, 2 heads, dim]
+            codes, exps = mx_quantize_reference(x)
+            layer0 = dst[:dst_l.layer_bytes]
+            got_c = dst_l.view(layer0, torch.uint8)[torch.tensor(db[:nb], device=dev)][:, :, :, 2 * j:2 * j + 2]
+            got_e = dst_l.scale_view(layer0)[torch.tensor(db[:nb], device=dev)][:, :, :, 2 * j:2 * j + 2]
+            ok = ok and bool(torch.equal(got_c, codes)) and bool(torch.equal(got_e, exps))
+    t = torch.tensor([1.0 if ok else 0.0], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    src_bytes = tokens * 2 * 2 * HEAD_DIM * 2 * n_layers
+    link_bytes = tokens * dst_l.token_bytes // 2 * n_layers
+    return {"prefill_ranks": n_p, "decode_ranks": n_d, "src_bytes_per_rank": src_bytes, "link_bytes_per_rank": link_bytes,
+            "ms_host_launched": round(ms_host, 3), "ms_graph_replay": round(ms_graph, 3),
+            "aggregate_src_GBps_host_launched": round(n_p * src_bytes / ms_host / 1e6, 1) if ms_host > 0 else 0.0,
+            "aggregate_src_GBps_graph_replay": round(n_p * src_bytes / ms_graph / 1e6, 1) if ms_graph > 0 else 0.0,
+            "link_GBps_into_each_decode_rank_graph_replay":
+                round(min(2, n_p) * link_bytes / ms_graph / 1e6, 1) if ms_graph > 0 else 0.0,
+            "verified": bool(t.item())}
