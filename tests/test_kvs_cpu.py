@@ -167,3 +167,32 @@ def test_nosave_and_min_length(store_name, monkeypatch):
         assert e.workers[0].connector._worker._backend._store.stats()["used"] == 0
     finally:
         e.shutdown()
+
+
+def test_many_concurrent_requests_with_shared_prefixes(store_name):
+    """Two batches of 16 concurrent requests over 4 distinct prompts while the store is smaller than what they would
+    need without sharing: every request finishes with the right tokens, nothing stays reserved or
+    pinned, and later copies of a prompt are served from the store."""
+    e = make_kvs("A", store_name, num_blocks=256, max_batched=256, extra={"kvs_slots": 40})
+    try:
+        cap = spy(e)
+        lens = [70, 150, 230, 95]
+        first = {}
+        for half in (range(0, 4), range(4, 8)):
+            for wave in half:
+                for k, n in enumerate(lens):
+                    e.add_request(make_req(f"w{wave}k{k}", n, max_tokens=2, seed=k))
+            for wave in half:
+                for k, n in enumerate(lens):
+                    rid = f"w{wave}k{k}"
+                    out = e.wait_finished(rid, 60)
+                    assert out is not None and out.finish_reason.name == "LENGTH", rid
+                    first.setdefault(k, e.output_tokens(rid))
+                    assert e.output_tokens(rid) == first[k]
+        assert wait_free(e, 255, 10) == 255
+        st = e.workers[0].connector._worker._backend._store.stats()
+        assert st["writing"] == 0 and st["pinned"] == 0 and st["sealed"] <= 40
+        reused = sum(1 for rid, (computed, _) in cap.items() if computed > 0)
+        assert reused >= 16, reused      # the second half looked up after the first half had sealed
+    finally:
+        e.shutdown()
