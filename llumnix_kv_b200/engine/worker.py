@@ -14,6 +14,7 @@ from typing import Optional
 
 import torch
 
+from llumnix_kv_b200 import envs
 from llumnix_kv_b200.hybrid_connector import HybridConnector
 from llumnix_kv_b200.hybrid_connector.engine_proxy import KVConnectorRole, WorkerProxy
 from llumnix_kv_b200.ops.layouts import AttnLayout, CacheShape
@@ -129,6 +130,7 @@ class MiniWorker:
             self.connector.register_kv_caches(self.kv_caches)
         self._req_state: dict = {}   # reqid -> (prompt tokens, block ids of group 0)
         self.forward_passes = 0
+        self.hidden_states_hook = None    # callable(forward pass number) -> the pass's hidden states (NaN-check tests)
 
     # ---- the "model" ---------------------------------------------------------------------------
     def expected_rows(self, layer: int, tensor_idx: int, token_ids: list, lo: int, hi: int) -> torch.Tensor:
@@ -261,6 +263,11 @@ class MiniWorker:
                 if len(self.row_widths) > 1:
                     conn.save_kv_layer(indexer_name(layer), self.kv_caches[indexer_name(layer)], None)
         if conn is not None and meta is not None:
+            if envs.VLLM_KVS_STORE_NAN_CHECK and conn.wants_nan_flag():
+                # on the forward stream, so the check precedes anything recorded after the last layer
+                hidden = self.hidden_states_hook(self.forward_passes) if self.hidden_states_hook is not None \
+                    else torch.zeros(8, device=self.device)
+                conn.set_nan_flag(torch.isnan(hidden).any())
             conn.clear_connector_metadata()
         sampled = {}
         for rid, n in sout.num_scheduled_tokens.items():

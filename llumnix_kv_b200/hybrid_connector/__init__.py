@@ -125,6 +125,14 @@ class HybridConnector:
     def wait_for_save(self) -> None:
         return  # saves are asynchronous; completion reaches the scheduler as SAVE_DONE
 
+    def wants_nan_flag(self) -> bool:
+        assert self._worker is not None
+        return self._worker.wants_nan_flag()
+
+    def set_nan_flag(self, flag) -> None:
+        assert self._worker is not None
+        self._worker.set_nan_flag(flag)
+
 
 _g_scheduler: Optional[HybridScheduler] = None
 _g_worker: Optional[HybridWorker] = None

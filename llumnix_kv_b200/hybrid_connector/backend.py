@@ -51,6 +51,14 @@ class BackendMeta:
     def __bool__(self):
         return False
 
+    def wants_nan_flag(self) -> bool:
+        """True when this step stores KV whose validity depends on the forward pass being NaN-free
+        (blade_kvt/hybrid_connector/v6d_object_backend.py:78-90)."""
+        return False
+
+    def set_nan_flag(self, flag) -> None:
+        """The model runner's ``isnan(hidden_states).any()`` tensor of this step."""
+
 
 @dataclasses.dataclass
 class HybridMetadata(KVConnectorMetadata):

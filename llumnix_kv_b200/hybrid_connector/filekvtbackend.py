@@ -24,6 +24,13 @@ class PairMeta(BackendMeta):
     def __bool__(self):
         return bool(self.s) or bool(self.p)
 
+    def wants_nan_flag(self) -> bool:
+        return self.s.wants_nan_flag() or self.p.wants_nan_flag()
+
+    def set_nan_flag(self, flag) -> None:
+        self.s.set_nan_flag(flag)
+        self.p.set_nan_flag(flag)
+
 
 class StorePlusKVT(HybridBackend):
     """A store backend (loads and saves) combined with the KVT prefill sender (saves only)."""

@@ -54,9 +54,16 @@ class KVSReqMeta:
 @dataclasses.dataclass
 class KVSMeta(BackendMeta):
     metas: list = dataclasses.field(default_factory=list)
+    nan_flag: object = None    # set by the model runner after the forward pass when the NaN check is on
 
     def __bool__(self):
         return bool(self.metas)
+
+    def wants_nan_flag(self) -> bool:
+        return any(m.is_store and not m.abort for m in self.metas)
+
+    def set_nan_flag(self, flag) -> None:
+        self.nan_flag = flag
 
 
 def should_use(req: Request) -> bool:
@@ -93,6 +100,13 @@ class KVSBackend(HybridBackend):
         self._store = None
         self._wkeys: dict = {}                # reqid -> chained keys computed so far
         self._wpending: dict = {}             # reqid -> keys reserved by this worker and not sealed yet
+        # NaN gate (the reference's VLLM_V6D_STORE_NAN_CHECK, v6d_object_backend.py:78-90,373-430):
+        # blocks of a step are sealed only once the model runner's isnan flag of that step is known to
+        # be clear; a request that saw a NaN stores nothing from then on
+        self._nan_check = bool(envs.VLLM_KVS_STORE_NAN_CHECK)
+        self._bound_meta = None
+        self._nan_gate = None                 # concurrent Future of this step: resolves to the flag tensor or None
+        self._nan_failed: set = set()
 
     # ---- geometry shared by both halves --------------------------------------------------------------
     def _geometry(self):
@@ -235,6 +249,25 @@ class KVSBackend(HybridBackend):
         logger.info("kvs: rank %d attached to store %s (%d slots of %d bytes, fp8=%s)", rank, self._name, n_slots,
                     self._store.slot_bytes, self._fp8)
 
+    def bind_backend_metadata(self, meta: BackendMeta) -> None:
+        self._bound_meta = meta
+        if self._nan_check and isinstance(meta, KVSMeta) and meta.wants_nan_flag():
+            import concurrent.futures
+
+            self._nan_gate = concurrent.futures.Future()
+
+    def clear_backend_metadata(self) -> None:
+        gate, meta = self._nan_gate, self._bound_meta
+        self._nan_gate = self._bound_meta = None
+        if gate is not None:
+            gate.set_result(getattr(meta, "nan_flag", None))    # the forward pass is over: the flag was set, or never will be
+
+    def bypass_bind(self, meta: BackendMeta) -> None:
+        return   # bypass substeps only carry loads; their metadata reaches async_load_kv directly
+
+    def bypass_clear(self) -> None:
+        return
+
     async def _wait_event(self, ev) -> None:
         if ev is not None:
             await asyncio.wait_for(asyncio.get_running_loop().run_in_executor(None, ev.synchronize), self._io_timeout)
@@ -318,6 +351,7 @@ class KVSBackend(HybridBackend):
             lo = 0 if self._per_step else layer
             ev = st.save_layers(lo, layer + 1, blocks, slots, after=after)   # one launch for every request of the step
         work = list(self._step_saves)
+        gate = self._nan_gate if last_layer else None
         if last_layer:
             self._step_saves = []
 
@@ -329,10 +363,18 @@ class KVSBackend(HybridBackend):
             except Exception as ex:
                 failed = ex
                 logger.warning("kvs: save of layer %d failed: %r", layer, ex)
+            nan = False
+            if gate is not None:
+                flag = await asyncio.wait_for(asyncio.wrap_future(gate), self._io_timeout)
+                nan = flag is not None and bool(flag.item())    # the isnan kernel precedes the save event on the stream
+                if nan:
+                    logger.error("kvs: NaN in this step's hidden states: its %d request(s) store nothing", len(work))
             for r, _, _, mine in work:
                 if last_layer:
                     pend = self._wpending.get(r.reqid, [])
-                    if failed is None:
+                    if nan:
+                        self._nan_failed.add(r.reqid)
+                    if failed is None and r.reqid not in self._nan_failed:
                         st.seal(mine)             # every layer of these blocks has landed
                     else:
                         st.discard(mine)
@@ -341,6 +383,7 @@ class KVSBackend(HybridBackend):
                             pend.remove(k)
                     if r.is_last_chunk:
                         self._wpending.pop(r.reqid, None)
+                        self._nan_failed.discard(r.reqid)
                 if r.is_last_chunk:
                     yield r.reqid
 

@@ -104,6 +104,15 @@ class HybridWorker:
         self._backend.clear_backend_metadata()
         self._meta = None
 
+    def wants_nan_flag(self) -> bool:
+        """Whether the model runner should hand this step's ``isnan(hidden_states).any()`` tensor to
+        ``set_nan_flag`` before it clears the metadata (v6d_object_backend.py:78-90)."""
+        return self._meta is not None and self._meta.reqs.wants_nan_flag()
+
+    def set_nan_flag(self, flag) -> None:
+        if self._meta is not None:
+            self._meta.reqs.set_nan_flag(flag)
+
     def register_kv_caches(self, kv_caches: dict) -> None:
         if self._kv_cache_config is not None and self._kv_cache_config.kv_cache_groups:
             self._num_layers = sum(len(g.layer_names) for g in self._kv_cache_config.kv_cache_groups)

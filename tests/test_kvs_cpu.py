@@ -196,3 +196,28 @@ def test_many_concurrent_requests_with_shared_prefixes(store_name):
         assert reused >= 16, reused      # the second half looked up after the first half had sealed
     finally:
         e.shutdown()
+
+
+def test_nan_in_hidden_states_keeps_the_step_out_of_the_store(store_name, monkeypatch):
+    """With the NaN check on, a forward pass whose hidden states hold a NaN seals nothing: the
+    request finishes, its blocks are released, and the next request with that prompt finds no prefix."""
+    monkeypatch.setenv("VLLM_KVS_STORE_NAN_CHECK", "1")
+    e = make_kvs("A", store_name)
+    try:
+        cap = spy(e)
+        w = e.workers[0]
+        poisoned = {"on": True}
+        w.hidden_states_hook = lambda n: torch.tensor([1.0, float("nan") if poisoned["on"] else 2.0])
+        run(e, "a", 100)
+        assert wait_free(e, 63) == 63
+        st = w.connector._worker._backend._store.stats()
+        assert st["sealed"] == 0 and st["writing"] == 0 and st["used"] == 0
+        poisoned["on"] = False
+        run(e, "b", 100)
+        assert cap["b"][0] == 0                         # nothing was kept from the poisoned pass
+        assert wait_free(e, 63) == 63
+        assert w.connector._worker._backend._store.stats()["sealed"] == 6
+        run(e, "c", 100)
+        assert cap["c"][0] == 96
+    finally:
+        e.shutdown()
