@@ -7,6 +7,8 @@
 
 #include "core/client.h"
 #include "core/envcfg.h"
+#include "transport/copy_policy.h"
+#include "transport/device_stage.h"
 #include "core/gdr.h"
 #include "core/monitor.h"
 #include "core/fault_inject.h"
@@ -528,6 +530,23 @@ void bind_engine(py::module_& m) {
   m.def("monitor_port", &monitor_port);
   m.def("monitor_handle_line", &monitor_handle_line);
   m.def("envcfg_dump", &envcfg_dump);
+  m.def("copy_policy_describe", [](int device) {
+    py::gil_scoped_release nogil;
+    return CopyPolicy::get(device).describe();
+  }, py::arg("device"), "Copy policy of a device (measures at the first call unless the environment forces a path).");
+  m.def("copy_policy_choose", [](const std::string& mode, int dir, size_t n, size_t total, size_t min_len) {
+    return static_cast<int>(CopyPolicy::fixed(mode).choose(static_cast<CopyDir>(dir), n, total, min_len));
+  }, py::arg("mode"), py::arg("dir"), py::arg("n"), py::arg("total_bytes"), py::arg("min_len"),
+        "Decision (0 kernel, 1 memcpy) of a fixed policy: mode 'kernel', 'memcpy' or 'static'.");
+  m.def("copy_policy_bucket", [](size_t n, size_t avg_len) {
+    return std::make_pair(CopyPolicy::count_bucket(n), CopyPolicy::size_bucket(avg_len));
+  });
+  m.def("copy_policy_reset_for_test", &CopyPolicy::reset_for_test);
+  m.def("copy_path_counters", []() {
+    uint64_t a = 0, b = 0;
+    copy_path_counters(&a, &b);
+    return std::make_pair(a, b);
+  }, "(descriptor lists moved by the copy engines, by the copy kernel) in this process.");
   m.def("gdr_available", [] {
     std::string why;
     const bool ok = gdr_available(&why);

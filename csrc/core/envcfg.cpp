@@ -90,6 +90,10 @@ int env_nvlink_ctas() { return (int)anyint("BLLM_KVTRANS_NVLINK_CTAS", 0); }
 int env_nvlink_streams() { return (int)posint("BLLM_KVTRANS_NVLINK_STREAMS", 8); }
 int env_dst_mxfp8() { return (int)anyint("BLLM_KVTRANS_DST_MXFP8", 0); }
 int env_use_tma() { return (int)anyint("BLLM_KVTRANS_USE_TMA", 1); }
+bool env_copy_profile_enable() { return anyint("BLLM_KVTRANS_COPY_PROFILE_ENABLE", 1) != 0; }
+size_t env_copy_memcpy_max_blocks() { return (size_t)posint("BLLM_KVTRANS_COPY_MEMCPY_MAX_BLOCKS", 16); }
+size_t env_copy_memcpy_threshold_bytes() { return (size_t)posint("BLLM_KVTRANS_COPY_MEMCPY_BLOCK_THRESHOLD_BYTES", 256 * 1024); }
+int env_copy_path() { return (int)anyint("BLLM_KVTRANS_COPY_PATH", 0); }
 
 double env_kernel_copy_sm_usage() noexcept {
   std::lock_guard<std::mutex> g(g_mu);

@@ -59,6 +59,12 @@ int env_nvlink_ctas();
 int env_nvlink_streams();
 int env_dst_mxfp8();
 int env_use_tma();
+// Host-staged copies (TCP / SHM transports): start-up measurement of copy kernel against copy
+// engines, the static rule used without it, and a forced path (0 measured or static, 1 kernel, 2 memcpy).
+bool env_copy_profile_enable();
+size_t env_copy_memcpy_max_blocks();
+size_t env_copy_memcpy_threshold_bytes();
+int env_copy_path();
 
 void envcfg_reset_for_test();
 std::string envcfg_dump();   // every setting resolved so far, one key=value per line

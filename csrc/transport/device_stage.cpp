@@ -3,14 +3,26 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
+#include <cstdint>
 #include <cstdlib>
 #include <cstring>
 
 #include "core/envcfg.h"
 #include "core/types.h"
 #include "kernels/kvt_kernels.h"
+#include "transport/copy_policy.h"
 
 namespace kvx {
+
+namespace {
+std::atomic<uint64_t> g_memcpy_lists{0}, g_kernel_lists{0};
+}
+
+void copy_path_counters(uint64_t* memcpy_lists, uint64_t* kernel_lists) {
+  *memcpy_lists = g_memcpy_lists.load();
+  *kernel_lists = g_kernel_lists.load();
+}
 
 void cuda_check(int err, const char* what) {
   if (err != 0) {
@@ -79,11 +91,35 @@ void DeviceStage::wait_event(void* event) {
 }
 
 void DeviceStage::enqueue(uint64_t src_base, uint64_t dst_base, const std::vector<Triple>& triples, uint64_t src_cap,
-                          uint64_t dst_cap, int grid_ctas) {
+                          uint64_t dst_cap, int grid_ctas, int host_side) {
   if (triples.empty()) return;
   cuda_check(cudaSetDevice(device_), "cudaSetDevice");
   cudaStream_t s = static_cast<cudaStream_t>(stream_);
   const size_t n = triples.size();
+  if (host_side != HOST_NONE) {
+    size_t total = 0, min_len = SIZE_MAX;
+    for (const Triple& t : triples) {
+      total += t.len;
+      min_len = std::min<size_t>(min_len, t.len);
+    }
+    const CopyDir dir = host_side == HOST_SRC ? CopyDir::H2D : CopyDir::D2H;
+    if (CopyPolicy::get(device_).choose(dir, n, total, min_len) == CopyPath::MEMCPY) {
+      for (size_t i = 0; i < n; i++) {
+        const Triple& t = triples[i];
+        if (t.src_off > src_cap || t.len > src_cap - t.src_off || t.dst_off > dst_cap || t.len > dst_cap - t.dst_off) {
+          throw KVTransferException(ErrorKind::CUDA, "copy descriptor " + std::to_string(i) + " is out of bounds");
+        }
+        cuda_check(cudaMemcpyAsync(reinterpret_cast<void*>(dst_base + t.dst_off),
+                                   reinterpret_cast<const void*>(src_base + t.src_off), t.len, cudaMemcpyDefault, s),
+                   "cudaMemcpyAsync(block)");
+      }
+      memcpy_lists_++;
+      g_memcpy_lists++;
+      return;
+    }
+  }
+  kernel_lists_++;
+  g_kernel_lists++;
   // Descriptors of all launches since the last sync stay resident: the pinned staging must not
   // be overwritten while an upload is in flight, so grow-and-sync when it would not fit.
   if (used_ + n > d_cap_) {

@@ -44,9 +44,14 @@ class DeviceStage {
   // ordered before this stream by an event); does not wait.
   void launch_resident(uint64_t src_base, uint64_t dst_base, const uint64_t* d_triples, size_t n, uint64_t src_cap,
                        uint64_t dst_cap, int grid_ctas = 0);
-  // Enqueue the copy; does not wait.
+  // Enqueue the copy; does not wait.  host_side says which end is pinned host memory (HOST_NONE,
+  // HOST_SRC, HOST_DST): with a host end the copy policy of the device may hand the list to the copy
+  // engines (one cudaMemcpyAsync per descriptor, bounds checked here) instead of the kernel.
+  enum { HOST_NONE = 0, HOST_SRC = 1, HOST_DST = 2 };
   void enqueue(uint64_t src_base, uint64_t dst_base, const std::vector<Triple>& triples, uint64_t src_cap,
-               uint64_t dst_cap, int grid_ctas = 0);
+               uint64_t dst_cap, int grid_ctas = 0, int host_side = HOST_NONE);
+  uint64_t memcpy_lists() const { return memcpy_lists_; }   // lists that went to the copy engines
+  uint64_t kernel_lists() const { return kernel_lists_; }
   // Wait for everything enqueued and throw KVTransferException if the kernel flagged a descriptor.
   void sync();
   void* stream() const { return stream_; }
@@ -63,7 +68,12 @@ class DeviceStage {
   uint32_t* d_status_{nullptr};
   PinnedBuffer h_triples_;
   PinnedBuffer h_status_;
+  uint64_t memcpy_lists_{0};
+  uint64_t kernel_lists_{0};
 };
+
+// Process-wide count of descriptor lists that went to the copy engines / to the copy kernel.
+void copy_path_counters(uint64_t* memcpy_lists, uint64_t* kernel_lists);
 
 void cuda_check(int err, const char* what);  // throws KVTransferException(CUDA)
 

@@ -149,7 +149,7 @@ class HostChannel : public IChannel {
         c += b.length;
       }
       if (stage_ != nullptr) {
-        stage_->enqueue(addrs[layer][t], blob_dev, triples, ctx_->tensor_capacity(t), blob_cap);
+        stage_->enqueue(addrs[layer][t], blob_dev, triples, ctx_->tensor_capacity(t), blob_cap, 0, DeviceStage::HOST_DST);
       } else {
         const char* src = reinterpret_cast<const char*>(addrs[layer][t]);
         for (const auto& tr : triples) memcpy(blob_base + tr.dst_off, src + tr.src_off, tr.len);

@@ -229,7 +229,7 @@ class TransferServer : public ITransferServer {
           cursor += blen;
         }
         if (stage != nullptr) {
-          stage->enqueue(blob_dev, addrs[layer][t], triples, blob_cap, cap);
+          stage->enqueue(blob_dev, addrs[layer][t], triples, blob_cap, cap, 0, DeviceStage::HOST_SRC);
         } else {
           char* dst = reinterpret_cast<char*>(addrs[layer][t]);
           for (const auto& tr : triples) memcpy(dst + tr.dst_off, blob_host + tr.src_off, tr.len);

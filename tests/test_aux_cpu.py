@@ -132,3 +132,19 @@ def test_cache_shape_selection_and_prefix_alignment(monkeypatch):
     # attention blocks of 16 striped over 2 DCP ranks, indexer blocks of 64 replicated: lcm(32, 64) = 64
     assert ep.align_seen_tokens_for_kvt([200, 130], [16, 64], dcp_world_size=2, replicated=[False, True]) == 128
     assert ep.align_seen_tokens_for_kvt([50], [16]) == 48 and ep.align_seen_tokens_for_kvt([], []) == 0
+
+
+def test_copy_policy_static_rule_and_buckets(ops):
+    """Without a measurement the copy engines take a descriptor list only when it is short and every
+    run is long (the reference's rule, kvtransfer/src/copy_kernels.cpp:495-510); bucket edges."""
+    K, M = 0, 1
+    assert ops.copy_policy_choose("static", 0, 16, 16 * (256 << 10), 256 << 10) == M
+    assert ops.copy_policy_choose("static", 0, 17, 17 * (256 << 10), 256 << 10) == K
+    assert ops.copy_policy_choose("static", 1, 4, 4 << 20, (256 << 10) - 1) == K
+    assert ops.copy_policy_choose("kernel", 1, 1, 8 << 20, 8 << 20) == K
+    assert ops.copy_policy_choose("memcpy", 0, 5000, 5000 * 64, 64) == M
+    assert ops.copy_policy_choose("memcpy", 0, 0, 0, 0) == K          # nothing to move
+    assert ops.copy_policy_bucket(4, 16 << 10) == (0, 0)
+    assert ops.copy_policy_bucket(5, (16 << 10) + 1) == (1, 1)
+    assert ops.copy_policy_bucket(512, 2 << 20) == (2, 2)
+    assert ops.copy_policy_bucket(513, (2 << 20) + 1) == (3, 3)

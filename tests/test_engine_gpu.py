@@ -127,6 +127,49 @@ def test_nvlink_tp_mismatch_with_block_scaled_fp8_destination():
         srv.stop()
 
 
+@pytest.mark.parametrize("path", [1, 2, 0])
+def test_host_staged_copies_by_kernel_by_copy_engines_and_by_measured_policy(path, ops, monkeypatch, capsys):
+    """The TCP transport gathers to / scatters from pinned host memory either with the descriptor kernel
+    or with one cudaMemcpyAsync per run; a forced path must be the one that runs, and the policy measured
+    at start-up must deliver the same bytes whatever it picks."""
+    monkeypatch.setenv("BLLM_KVTRANS_COPY_PATH", str(path))
+    ops.envcfg_reset_for_test()
+    ops.copy_policy_reset_for_test()
+    m0, k0 = ops.copy_path_counters()
+    rng = random.Random(7)
+    lay = AttnLayout(CacheShape.FLASH, 48, 16, 8, 128, 2)
+    src = [lay.alloc(DEV, "normal", seed=i) for i in range(L)]
+    dst = [lay.alloc(DEV) for _ in range(L)]
+    srv = KVTransferServer("D|0|1", 1, 0, 0, lay.block_bytes, lay.token_bytes, "fake://", dst, [PT.TCP], num_kv_heads=8,
+                           cache_shape=2)
+    cli = KVTransferClient("P|0|1", 1, 0, 0, lay.block_bytes, lay.token_bytes, "fake://", src, [PT.TCP], num_kv_heads=8,
+                           cache_shape=2)
+    try:
+        reqs = rand_reqs(rng, 3, 48, 48, 16)
+        run_step(cli, "D|0|1", 0, srv.worker_info(), [(rid, sb, db, 0, total, True, True) for rid, sb, db, total in reqs], 1)
+        chunks = [ReqChunk(sb, db, 0, total) for _, sb, db, total in reqs]
+        for i in range(L):
+            expect = torch.zeros_like(dst[i])
+            reference_transfer(lay, lay, src[i], expect, chunks)
+            assert torch.equal(dst[i], expect)
+        m1, k1 = ops.copy_path_counters()
+        assert (m1 - m0) + (k1 - k0) >= 2 * L          # gather and scatter, per layer
+        if path == 1:
+            assert m1 == m0
+        elif path == 2:
+            assert k1 == k0
+        else:
+            table = ops.copy_policy_describe(0)
+            assert table.startswith("d2h:") and "\nh2d:" in table and "us(kernel/memcpy)" in table
+            with capsys.disabled():
+                print("\n" + table)
+    finally:
+        srv.stop()
+        monkeypatch.delenv("BLLM_KVTRANS_COPY_PATH")
+        ops.envcfg_reset_for_test()
+        ops.copy_policy_reset_for_test()
+
+
 @pytest.mark.parametrize("proto", [PT.NVLINK, PT.TCP])
 def test_hybrid_gdn_pages_via_descriptor_path(proto, ops):
     """Qwen3-Next-like hybrid pages (GDN state + attention in one tensor) with P TP=2 -> D TP=1: no
