@@ -104,6 +104,7 @@ void ThreadPool::run(Worker* w, size_t idx) {
     } catch (...) {
       LOG(ERROR) << "thread pool task threw a non-std exception";
     }
+    w->pending.fetch_sub(1, std::memory_order_release);
   }
 }
 
@@ -117,15 +118,24 @@ void ThreadPool::spawn(std::function<void()> fn, int hint) {
   Worker* w = workers_[static_cast<size_t>(hint < 0 ? -hint : hint) % workers_.size()].get();
   {
     std::lock_guard<std::mutex> g(w->mu);
+    w->pending.fetch_add(1, std::memory_order_relaxed);
     w->q.emplace_back(std::move(fn));
   }
   w->cv.notify_all();
 }
 
 void ThreadPool::drain() {
+  // A caller that drains is about to use the result: poll for a short while (a sleeping thread is
+  // woken some tens of microseconds after the notify), then block.
+  const auto t0 = std::chrono::steady_clock::now();
   for (auto& w : workers_) {
+    while (w->pending.load(std::memory_order_acquire) != 0) {
+      if (std::chrono::steady_clock::now() - t0 > std::chrono::microseconds(500)) break;
+      __builtin_ia32_pause();
+    }
+    if (w->pending.load(std::memory_order_acquire) == 0) continue;
     std::unique_lock<std::mutex> lk(w->mu);
-    w->cv.wait(lk, [&] { return w->q.empty() && !w->busy; });
+    w->cv.wait(lk, [&] { return w->pending.load(std::memory_order_acquire) == 0; });
   }
 }
 

@@ -71,6 +71,7 @@ class ThreadPool {
     std::deque<std::function<void()>> q;
     std::thread thd;
     bool busy{false};
+    std::atomic<uint32_t> pending{0};   // queued + running tasks; drain() polls it before it blocks
   };
   void run(Worker* w, size_t idx);
   std::vector<std::unique_ptr<Worker>> workers_;

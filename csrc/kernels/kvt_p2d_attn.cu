@@ -400,15 +400,22 @@ __device__ __forceinline__ void simt_zero_tail(const KvtAttnLaunch& p, const Til
   }
 }
 
-// A warp owns a tile (WARP: many tiles in flight per SM, nobody waits at tile boundaries; best when
-// the destination is device memory) or the whole CTA shares one (longer contiguous write runs,
-// which is what a PCIe destination prefers).
-template <int MODE, bool USE_TMA, bool WARP>
+// Who owns a tile.  GROUP = 1: a warp (many tiles in flight per SM, nobody waits at tile boundaries;
+// best for long launches into device memory).  GROUP = 4: four warps share a tile, so that a
+// launch with few tiles still spreads over every SM and a whole tile is in flight at once (short
+// launches: one layer of a request).  GROUP = 0: the whole CTA (longer contiguous write runs, which
+// is what a PCIe destination prefers).  The owners of a CTA take consecutive tiles and the launcher
+// sizes the grid to the tiles, so that every resident CTA is full of busy warps: a CTA keeps its
+// registers until its last warp exits, and half-empty CTAs of one launch would keep the CTAs of
+// launches on other streams off the SM.
+template <int MODE, bool USE_TMA, int GROUP>
 __device__ __forceinline__ void simt_pass(const KvtAttnLaunch& p, uint64_t total, uint32_t per_layer) {
-  const uint32_t tid = WARP ? (threadIdx.x & 31u) : threadIdx.x;
-  const uint32_t nthr = WARP ? 32u : blockDim.x;
-  const uint32_t owners = WARP ? (blockDim.x >> 5) : 1u;
-  const uint32_t me = WARP ? (threadIdx.x >> 5) : 0u;
+  constexpr uint32_t kGroupThreads = GROUP > 0 ? 32u * GROUP : 0u;
+  const uint32_t tid = GROUP > 0 ? (threadIdx.x % kGroupThreads) : threadIdx.x;
+  const uint32_t nthr = GROUP > 0 ? kGroupThreads : blockDim.x;
+  const uint32_t owners = GROUP > 0 ? (blockDim.x / kGroupThreads) : 1u;
+  const uint32_t me = GROUP > 0 ? (threadIdx.x / kGroupThreads) : 0u;
+  if (me >= owners) return;   // a block size that is not a multiple of the group: the odd warps sit out
   for (uint64_t w = (uint64_t)blockIdx.x * owners + me; w < total; w += (uint64_t)gridDim.x * owners) {
     const uint32_t layer = (uint32_t)(w / per_layer);
     const uint32_t rem = (uint32_t)(w - (uint64_t)layer * per_layer);
@@ -544,10 +551,12 @@ __global__ void __launch_bounds__(512) kvt_p2d_attn_kernel(const __grid_constant
   }
 
   // SIMT pass: everything the TMA pass does not take.
-  if (warp_tiles) {
-    simt_pass<MODE, USE_TMA, true>(p, total, per_layer);
+  if (warp_tiles == 1u) {
+    simt_pass<MODE, USE_TMA, 1>(p, total, per_layer);
+  } else if (warp_tiles == 4u) {
+    simt_pass<MODE, USE_TMA, 4>(p, total, per_layer);
   } else {
-    simt_pass<MODE, USE_TMA, false>(p, total, per_layer);
+    simt_pass<MODE, USE_TMA, 0>(p, total, per_layer);
   }
 
   // Completion: the last CTA to finish publishes the flag after a system-scope fence, so a
@@ -589,13 +598,30 @@ bool load_driver_api() {
 template <int MODE, bool USE_TMA>
 cudaError_t launch_impl(const KvtAttnLaunch& a, int grid, int threads, uint32_t stages, uint32_t tile_bytes,
                         size_t smem, cudaStream_t stream) {
-  // BLLM_KVTRANS_SIMT_TILE overrides KvtAttnLaunch::simt_tile: 1 = a warp per tile, 2 = a CTA per tile
+  // BLLM_KVTRANS_SIMT_TILE overrides KvtAttnLaunch::simt_tile: 1 = a warp per tile, 4 = four warps per
+  // tile (lower latency of a lone short launch, lower throughput of overlapped ones), 2 = a CTA per tile.
   static const int env_simt = [] {
     const char* v = getenv("BLLM_KVTRANS_SIMT_TILE");
     return v != nullptr ? atoi(v) : 0;
   }();
   const int choice = env_simt != 0 ? env_simt : (int)a.simt_tile;
-  const uint32_t warp_tiles = choice == 2 ? 0u : 1u;
+  uint32_t warp_tiles;
+  const uint64_t total = (uint64_t)(a.layer_end - a.layer_begin) * a.total_tiles * a.src.kv_count;
+  const uint32_t warps = (uint32_t)(threads / 32);
+  if (choice == 2) {
+    warp_tiles = 0u;
+  } else if (choice == 1 || (choice == 4 && threads % 128 == 0)) {
+    warp_tiles = (uint32_t)choice;
+  } else {
+    // Measured with 80 one-layer launches of 1024 tiles on 8 streams: a warp per tile moves 2884 GB/s
+    // through the quantiser, four warps per tile 2046 (every warp of the four walks the block table).
+    warp_tiles = 1u;
+  }
+  if (!USE_TMA && warp_tiles != 0u) {
+    const uint64_t owners = warps / warp_tiles;
+    const uint64_t need = (total + owners - 1) / owners;
+    if ((uint64_t)grid > need) grid = (int)need;
+  }
   auto kern = kvt_p2d_attn_kernel<MODE, USE_TMA>;
   if (smem > 48 * 1024) {
     // the opt-in is per device and sticky: ask once per device (and again only for a larger size)

@@ -80,8 +80,19 @@ DeviceStage::~DeviceStage() {
     cudaStreamSynchronize(static_cast<cudaStream_t>(stream_));
     cudaStreamDestroy(static_cast<cudaStream_t>(stream_));
   }
+  if (done_event_ != nullptr) cudaEventDestroy(static_cast<cudaEvent_t>(done_event_));
   if (d_triples_ != nullptr) cudaFree(d_triples_);
   if (d_status_ != nullptr) cudaFree(d_status_);
+}
+
+void* DeviceStage::record_done() {
+  if (done_event_ == nullptr) {
+    cudaEvent_t e;
+    cuda_check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate");
+    done_event_ = e;
+  }
+  cuda_check(cudaEventRecord(static_cast<cudaEvent_t>(done_event_), static_cast<cudaStream_t>(stream_)), "cudaEventRecord");
+  return done_event_;
 }
 
 void DeviceStage::wait_event(void* event) {

@@ -58,10 +58,14 @@ class DeviceStage {
   int device() const { return device_; }
   // Make the stream wait for a cudaEvent_t before later work (no host wait).
   void wait_event(void* event);
+  // Record this stage's own event behind everything enqueued so far and return it: another
+  // stage can wait_event() on it, which joins the two streams without a host wait.
+  void* record_done();
 
  private:
   int device_;
   void* stream_{nullptr};
+  void* done_event_{nullptr};
   uint64_t* d_triples_{nullptr};
   size_t d_cap_{0};       // triples
   size_t used_{0};        // triples enqueued since the last sync

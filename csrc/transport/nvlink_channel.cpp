@@ -319,9 +319,13 @@ class NvlinkChannel : public IChannel {
     TimeWatch tw;
     cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
     fault_inject_throw();
-    for (auto& s : stages_) s->sync();
     if (fused_) {
-      cuda_check(cudaMemcpy(h_status_.data(), d_status_, 8, cudaMemcpyDeviceToHost), "cudaMemcpy(status)");
+      // one host wait for the batch: the other streams are joined into the first on the device, the
+      // kernels' shared status words follow them, and the host waits for that copy alone
+      cudaStream_t s0 = static_cast<cudaStream_t>(stages_[0]->stream());
+      for (size_t i = 1; i < stages_.size(); ++i) stages_[0]->wait_event(stages_[i]->record_done());
+      cuda_check(cudaMemcpyAsync(h_status_.data(), d_status_, 8, cudaMemcpyDeviceToHost, s0), "cudaMemcpyAsync(status)");
+      cuda_check(cudaStreamSynchronize(s0), "cudaStreamSynchronize");
       uint32_t st[2];
       memcpy(st, h_status_.data(), 8);
       if (st[0] != 0) {
@@ -329,6 +333,8 @@ class NvlinkChannel : public IChannel {
         throw KVTransferException(ErrorKind::CUDA, "transfer kernel reported status " + std::to_string(st[0]) +
                                                        " detail " + std::to_string(st[1]));
       }
+    } else {
+      for (auto& s : stages_) s->sync();
     }
     std::ostringstream ss;
     ss << "Proto=nvlink,Path=" << (fused_ ? "fused" : "descriptors") << ",OriginSbNum=" << origin_blocks_
