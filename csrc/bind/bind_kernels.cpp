@@ -204,6 +204,38 @@ void bind_kernels(py::module_& m) {
       py::arg("src_base"), py::arg("dst_base"), py::arg("triples"), py::arg("n"), py::arg("src_capacity"),
       py::arg("dst_capacity"), py::arg("status"), py::arg("grid"), py::arg("stream"));
 
+  m.def(
+      "kvt_launch_mc_fanout",
+      [](uint64_t src_layers, uint64_t mc_layers, uint32_t layer_begin, uint32_t layer_end, int64_t src_block_stride,
+         int64_t dst_block_stride, uint32_t src_num_blocks, uint32_t dst_num_blocks, uint64_t src_blocks,
+         uint64_t dst_blocks, uint32_t n_blocks, uint32_t block_off, uint32_t block_len, uint64_t status,
+         uint64_t done_counter, uint64_t mc_flag, uint64_t flag_value, int grid, uint64_t stream) {
+        KvtMcFanout a{};
+        a.src_layers = reinterpret_cast<const uint64_t*>(src_layers);
+        a.mc_layers = reinterpret_cast<const uint64_t*>(mc_layers);
+        a.layer_begin = layer_begin;
+        a.layer_end = layer_end;
+        a.src_block_stride = src_block_stride;
+        a.dst_block_stride = dst_block_stride;
+        a.src_num_blocks = src_num_blocks;
+        a.dst_num_blocks = dst_num_blocks;
+        a.src_blocks = reinterpret_cast<const uint32_t*>(src_blocks);
+        a.dst_blocks = reinterpret_cast<const uint32_t*>(dst_blocks);
+        a.n_blocks = n_blocks;
+        a.block_off = block_off;
+        a.block_len = block_len;
+        a.status = reinterpret_cast<uint32_t*>(status);
+        a.done_counter = reinterpret_cast<uint32_t*>(done_counter);
+        a.mc_flag = reinterpret_cast<uint64_t*>(mc_flag);
+        a.flag_value = flag_value;
+        check_cuda(kvt_launch_mc_fanout(&a, grid, reinterpret_cast<void*>(stream)), "kvt_launch_mc_fanout");
+      },
+      py::arg("src_layers"), py::arg("mc_layers"), py::arg("layer_begin"), py::arg("layer_end"),
+      py::arg("src_block_stride"), py::arg("dst_block_stride"), py::arg("src_num_blocks"), py::arg("dst_num_blocks"),
+      py::arg("src_blocks"), py::arg("dst_blocks"), py::arg("n_blocks"), py::arg("block_off"), py::arg("block_len"),
+      py::arg("status"), py::arg("done_counter"), py::arg("mc_flag"), py::arg("flag_value"), py::arg("grid"),
+      py::arg("stream"));
+
   m.def("kvt_launch_wait_flag", [](uint64_t flag, uint64_t value, uint64_t timeout_ns, uint64_t status,
                                    uint64_t stream) {
     check_cuda(kvt_launch_wait_flag(reinterpret_cast<const uint64_t*>(flag), value, timeout_ns,

@@ -168,6 +168,36 @@ int kvt_copy_blocks_noalloc(uint64_t src_base, uint64_t dst_base, const uint64_t
                             uint32_t n, uint64_t src_capacity, uint64_t dst_capacity,
                             uint32_t* host_status, void* stream);
 
+// ---- NVLS fan-out of replicated blocks --------------------------------------------------------
+// Replicates byte range [block_off, block_off + block_len) of the listed source blocks, for layers
+// [layer_begin, layer_end), from this GPU's memory into the listed destination blocks of every GPU
+// bound to a multicast object (multimem.st through NVSwitch).  The source is any local memory: the
+// member's own cache (in place: same tensors, same block ids; its copy is rewritten with the same
+// bytes) or a landing buffer that a prefill GPU pushed into over CUDA-IPC peer memory.  mc_layers
+// holds, per layer, the multicast address of the destination tensor.  Offsets, lengths and strides
+// must be multiples of 16.  mc_flag (optional, multicast address of an 8-byte aligned word)
+// receives flag_value with release semantics after the data.
+typedef struct KvtMcFanout {
+  const uint64_t* src_layers;  // device array: source base address per layer (this GPU's memory)
+  const uint64_t* mc_layers;   // device array: multicast address of the destination tensor per layer
+  uint32_t layer_begin, layer_end;
+  int64_t src_block_stride;
+  int64_t dst_block_stride;
+  uint32_t src_num_blocks;     // bounds checks
+  uint32_t dst_num_blocks;
+  const uint32_t* src_blocks;  // device: source block id per block to replicate
+  const uint32_t* dst_blocks;  // device: destination block id (the same on every GPU of the group)
+  uint32_t n_blocks;
+  uint32_t block_off;
+  uint32_t block_len;
+  uint32_t* status;            // device: [0] first error code, [1] detail
+  uint32_t* done_counter;      // device, zero before launch (needed with mc_flag)
+  uint64_t* mc_flag;
+  uint64_t flag_value;
+} KvtMcFanout;
+
+int kvt_launch_mc_fanout(const KvtMcFanout* args, int grid_ctas, void* stream);
+
 // ---- completion flags ---------------------------------------------------------------------
 // Bounded device-side wait: returns through status[0]=KVT_ERR_FLAG_TIMEOUT when *flag has not
 // reached `value` within timeout_ns.  Never spins without limit.

@@ -1,0 +1,124 @@
+// kvt_mc_fanout: replicate paged-cache blocks of THIS GPU into the same blocks of every GPU bound
+// to an NVLink multicast object, with one store per 16 bytes (`multimem.st` through NVSwitch).
+//
+// Use: data that every tensor-parallel rank of a decode instance holds identically (the MLA
+// latent and indexer caches, replicated KV heads when there are fewer KV heads than ranks).  The
+// reference sends such data once per destination rank (one P rank fans out to d/p D ranks,
+// blade_kvt/hybrid_connector/kvtbackend.py:637-664, kvtransfer/src/tx_stub.cpp:18-114), so the
+// sender's link carries d/p copies.  Here the sender pushes ONE copy to one rank of the group and
+// that rank's GPU replicates it: its NVLink egress carries the bytes once and the switch delivers
+// them to every member (the issuing GPU included: same bytes to the same place).
+//
+// Only stores are multicast.  Sources are read with plain loads from local memory (the member's
+// own cache, or a landing buffer the sender pushed into); nothing here loads through a multicast
+// address.  Every rank of the group uses the same destination block ids for the request, which is
+// how a TP group allocates anyway (one scheduler, one block table).
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "kvt_kernels.h"
+
+namespace {
+
+__device__ __forceinline__ void set_status(uint32_t* status, uint32_t code, uint32_t detail) {
+  if (status != nullptr) {
+    if (atomicCAS(status, 0u, code) == 0u) status[1] = detail;
+  }
+}
+
+__device__ __forceinline__ int4 ld_nc_16(const void* p) {
+  int4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ void mc_st_16(void* mc, int4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(__int_as_float(v.x)),
+               "f"(__int_as_float(v.y)), "f"(__int_as_float(v.z)), "f"(__int_as_float(v.w))
+               : "memory");
+}
+
+constexpr uint32_t kSegBytes = 2048;   // a warp moves 32 lanes x 4 x 16 B per step
+
+__global__ void __launch_bounds__(512) kvt_mc_fanout_kernel(const __grid_constant__ KvtMcFanout p) {
+  const uint32_t n_layers = p.layer_end - p.layer_begin;
+  const uint32_t segs = (p.block_len + kSegBytes - 1) / kSegBytes;
+  const uint64_t per_layer = (uint64_t)p.n_blocks * segs;
+  const uint64_t total = (uint64_t)n_layers * per_layer;
+  const uint32_t warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  for (uint64_t w = (uint64_t)blockIdx.x * warps + warp; w < total; w += (uint64_t)gridDim.x * warps) {
+    const uint32_t layer = (uint32_t)(w / per_layer);
+    const uint64_t rem = w - (uint64_t)layer * per_layer;
+    const uint32_t bi = (uint32_t)(rem / segs);
+    const uint32_t seg = (uint32_t)(rem - (uint64_t)bi * segs);
+    const uint32_t sb = p.src_blocks[bi], db = p.dst_blocks[bi];
+    if (sb >= p.src_num_blocks || db >= p.dst_num_blocks) {
+      if (lane == 0) set_status(p.status, KVT_ERR_BLOCK_RANGE, bi);
+      continue;
+    }
+    const int64_t in_block = (int64_t)p.block_off + (int64_t)seg * kSegBytes;
+    const char* src = reinterpret_cast<const char*>(p.src_layers[p.layer_begin + layer]) +
+                      (int64_t)sb * p.src_block_stride + in_block;
+    char* mc = reinterpret_cast<char*>(p.mc_layers[p.layer_begin + layer]) + (int64_t)db * p.dst_block_stride + in_block;
+    const uint32_t len = min(kSegBytes, p.block_len - seg * kSegBytes);   // multiple of 16 (checked by the launcher)
+    const uint32_t n16 = len >> 4;
+    int4 v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t i = lane + 32u * k;
+      if (i < n16) v[k] = ld_nc_16(src + ((size_t)i << 4));
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t i = lane + 32u * k;
+      if (i < n16) mc_st_16(mc + ((size_t)i << 4), v[k]);
+    }
+  }
+  // Completion word, multicast as well: a member that sees it (acquire at system scope) sees the
+  // blocks.  The last CTA to finish publishes it after every CTA's stores have been fenced.
+  if (p.mc_flag != nullptr && p.done_counter != nullptr) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const uint32_t prev = atomicAdd(p.done_counter, 1u);
+      if (prev == gridDim.x - 1) {
+        *p.done_counter = 0;
+        __threadfence_system();
+        asm volatile("multimem.st.release.sys.global.u64 [%0], %1;" ::"l"(p.mc_flag), "l"(p.flag_value) : "memory");
+      }
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" int kvt_launch_mc_fanout(const KvtMcFanout* args, int grid_ctas, void* stream) {
+  const KvtMcFanout& a = *args;
+  if (a.n_blocks == 0 || a.layer_end <= a.layer_begin || a.block_len == 0) return (int)cudaSuccess;
+  if (a.src_layers == nullptr || a.mc_layers == nullptr || a.src_blocks == nullptr || a.dst_blocks == nullptr)
+    return (int)cudaErrorInvalidValue;
+  // multimem.st.v4.f32 needs 16-byte aligned addresses: the ranges must be made of whole 16-byte words
+  if ((a.block_len & 15u) != 0 || (a.block_off & 15u) != 0 || (a.src_block_stride & 15) != 0 ||
+      (a.dst_block_stride & 15) != 0 || a.src_block_stride <= 0 || a.dst_block_stride <= 0)
+    return (int)cudaErrorInvalidValue;
+  if ((uint64_t)a.block_off + a.block_len > (uint64_t)a.src_block_stride ||
+      (uint64_t)a.block_off + a.block_len > (uint64_t)a.dst_block_stride)
+    return (int)cudaErrorInvalidValue;
+  if (a.mc_flag != nullptr && ((reinterpret_cast<uintptr_t>(a.mc_flag) & 7u) != 0 || a.done_counter == nullptr))
+    return (int)cudaErrorInvalidValue;
+  int grid = grid_ctas;
+  if (grid <= 0) {
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    grid = 2 * (sms > 0 ? sms : 1);
+  }
+  const uint64_t segs = (a.block_len + kSegBytes - 1) / kSegBytes;
+  const uint64_t units = (uint64_t)(a.layer_end - a.layer_begin) * a.n_blocks * segs;
+  const uint64_t need = (units + 15) / 16;
+  if ((uint64_t)grid > need) grid = (int)need;
+  kvt_mc_fanout_kernel<<<grid, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,153 @@
+"""NVLS fan-out (multimem.st through NVSwitch) of replicated KV blocks inside a TP group.
+
+Child processes, one per GPU (2 to 4).  Every rank runs the same sequence of collective steps and
+only records what it finds wrong, so that no rank leaves while its memory is still bound to the
+multicast object; the parent asserts on what the ranks reported."""
+import os
+import socket
+import traceback
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+LAYERS, NUM_BLOCKS, STRIDE = 3, 16, 4096 + 512          # a block of 4608 bytes: not a power of two, 16-byte aligned
+
+
+def _expected(seed: int, n: int) -> torch.Tensor:
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, 256, (n,), dtype=torch.uint8, generator=g)
+
+
+def _child(rank: int, world: int, port: int, q) -> None:
+    errors = []
+    cache = None
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      BLLM_KVTRANS_QUIET_ENV="1")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    try:
+        from llumnix_kv_b200.parallel.nvls import MulticastKVCache
+
+        cache = MulticastKVCache(LAYERS, NUM_BLOCKS * STRIDE, dist.group.WORLD, dev)
+
+        def block(layer, b):
+            return cache.layers[layer][b * STRIDE:(b + 1) * STRIDE]
+
+        # ---- 1. in place: rank 0 holds blocks 3, 7, 1 of every layer; everybody gets them ------------------
+        ids = [3, 7, 1]
+        if rank == 0:
+            for layer in range(LAYERS):
+                for b in ids:
+                    block(layer, b).copy_(_expected(100 * layer + b, STRIDE))
+            torch.cuda.synchronize()
+        dist.barrier()
+        if rank == 0:
+            cache.fanout(ids, STRIDE, NUM_BLOCKS, flag_value=1)
+            torch.cuda.synchronize()
+            try:
+                cache.check_status()
+            except Exception as ex:
+                errors.append(f"in-place status: {ex}")
+        elif not cache.wait(1, timeout_s=5.0):
+            errors.append("in-place: the completion word never arrived")
+        for layer in range(LAYERS):
+            for b in range(NUM_BLOCKS):
+                want = _expected(100 * layer + b, STRIDE) if b in ids else torch.zeros(STRIDE, dtype=torch.uint8)
+                if not torch.equal(block(layer, b).cpu(), want):
+                    errors.append(f"in-place: layer {layer} block {b} differs on rank {rank}")
+        dist.barrier()
+
+        # ---- 2. from a landing buffer, part of a block, other block ids and another stride ---------------
+        l_stride, l_blocks = 2048, 4
+        landing = torch.zeros(LAYERS * l_blocks * l_stride, dtype=torch.uint8, device=dev)
+        src_ptrs = torch.tensor([landing.data_ptr() + i * l_blocks * l_stride for i in range(LAYERS)], dtype=torch.int64,
+                                device=dev)
+        if rank == 0:
+            landing.copy_(_expected(7, landing.numel()))
+            torch.cuda.synchronize()
+            cache.fanout([9, 4], STRIDE, NUM_BLOCKS, block_off=64, block_len=1024, layers=(1, 3), flag_value=2,
+                         src_layers=src_ptrs, src_block_ids=[2, 0], src_block_stride=l_stride, src_num_blocks=l_blocks)
+            torch.cuda.synchronize()
+            try:
+                cache.check_status()
+            except Exception as ex:
+                errors.append(f"landing status: {ex}")
+        elif not cache.wait(2, timeout_s=5.0):
+            errors.append("landing: the completion word never arrived")
+        land = _expected(7, landing.numel())
+        for layer in range(LAYERS):
+            for db, sb in ((9, 2), (4, 0)):
+                got = block(layer, db).cpu()
+                want = torch.zeros(STRIDE, dtype=torch.uint8)
+                if layer >= 1:
+                    o = (layer * l_blocks + sb) * l_stride + 64
+                    want[64:64 + 1024] = land[o:o + 1024]
+                if not torch.equal(got, want):
+                    errors.append(f"landing: layer {layer} block {db} differs on rank {rank}")
+        dist.barrier()
+
+        # ---- 3. a wait that nothing satisfies runs out and leaves the context usable -----------------------
+        if rank == world - 1:
+            if cache.wait(99, timeout_s=0.2):
+                errors.append("bounded wait: returned True although nothing set the word")
+            probe = torch.ones(4, device=dev).sum().item()
+            if probe != 4.0:
+                errors.append("bounded wait: context unusable afterwards")
+        dist.barrier()
+
+        # ---- 4. a block id outside the tensor is reported and skipped ------------------------------------
+        if rank == 0:
+            cache.fanout([5, NUM_BLOCKS + 3], STRIDE, NUM_BLOCKS)
+            torch.cuda.synchronize()
+            try:
+                cache.check_status()
+                errors.append("range check: no status for a block id outside the tensor")
+            except RuntimeError:
+                pass
+        dist.barrier()
+    except Exception:
+        errors.append(f"rank {rank}: {traceback.format_exc()}")
+    finally:
+        try:
+            if cache is not None:
+                cache.close()
+            else:
+                dist.barrier()
+        except Exception:
+            errors.append(f"rank {rank} teardown: {traceback.format_exc()}")
+        q.put((rank, errors))
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def test_multicast_fanout_reaches_every_member():
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs two GPUs")
+    world = min(n, 4)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_child, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    reports = {}
+    try:
+        for _ in range(world):
+            rank, errors = q.get(timeout=300)
+            reports[rank] = errors
+    finally:
+        for p in procs:
+            p.join(120)
+    assert sorted(reports) == list(range(world))
+    assert all(not e for e in reports.values()), reports
