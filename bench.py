@@ -48,9 +48,10 @@ def parse_args():
     ap.add_argument("--streams", type=int, default=8, help="transfer streams the layers alternate over")
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--small", action="store_true", help="tiny case for profiler captures")
-    ap.add_argument("--mode", default="p2d", choices=["p2d", "kvstore", "migration", "ttft", "quant", "gdn", "mla"],
+    ap.add_argument("--mode", default="p2d", choices=["p2d", "kvstore", "migration", "ttft", "quant", "gdn", "mla", "fanout"],
                     help="p2d: prefill->decode transfer (the headline); kvstore: host-DRAM store save/load GB/s; "
-                         "migration: decode->decode latency against the number of blocks")
+                         "migration: decode->decode latency against the number of blocks; fanout (4 or 8 GPUs): replicated "
+                         "MLA pages to a decode TP group, unicast against the NVLS relay")
     ap.add_argument("--prompt-mix", action="store_true",
                     help="ttft mode: prompt lengths uniform in [tokens/8, 4*tokens] (1k-32k by default) instead of fixed")
     ap.add_argument("--graph", action="store_true",
@@ -195,6 +196,21 @@ def main():
                               "result": res}))
         if world > 1:
             dist.destroy_process_group()
+        return
+    if args.mode == "fanout":
+        from llumnix_kv_b200.bench_support import mla_fanout_bandwidth
+
+        assert world >= 3, "--mode fanout needs --gpus 4 or 8 (one prefill GPU, a decode TP group on the others)"
+        res = mla_fanout_bandwidth(K, rank, world, dev, tokens=4096 if args.small else 32768, n_layers=8 if args.small else 61)
+        if rank == 0:
+            print(json.dumps({"metric": "replicated_kv_fanout_GBps", "unit": "GB/s", "n_gpus": args.gpus, "higher_is_better": True,
+                              "dtype": "bytes", "config": {
+                                  "model": "deepseek-v3.2-like MLA latent pages (656 B/token, 64-token blocks), identical on "
+                                           "every decode TP rank", "seq_len": res["tokens"],
+                                  "parallelism": f"1 prefill GPU -> decode TP{world - 1} group",
+                                  "paths": "unicast peer stores per rank vs one peer copy + multimem.st relay through NVSwitch"},
+                              "result": res}))
+        dist.destroy_process_group()
         return
     if args.mode == "ttft":
         from llumnix_kv_b200.bench_support import ttft_added

@@ -827,3 +827,248 @@ def quant_reshard_nvlink(K, rank: int, world: int, dev, tokens: int = 8192, n_la
             "link_GBps_into_each_decode_rank_graph_replay":
                 round(min(2, n_p) * link_bytes / ms_graph / 1e6, 1) if ms_graph > 0 else 0.0,
             "verified": bool(t.item())}
+
+
+def mla_fanout_bandwidth(K, rank: int, world: int, dev, tokens: int = 32768, n_layers: int = 61, iters: int = 5,
+                         warmup: int = 2, n_streams: int = 4) -> dict:
+    """Replicated MLA latent pages from one prefill GPU (rank 0) to every rank of a decode TP group
+    (ranks 1..world-1), two ways, device-timed, max over ranks:
+
+      unicast   the prefill GPU pushes the pages into each decode rank's cache (world-1 copies leave its
+                link; what the reference's P<D fan-out does, kvtbackend.py:637-664);
+      nvls      the prefill GPU pushes ONE copy, layer by layer, into a landing buffer on decode rank 1;
+                that rank waits (bounded) for each layer's flag and replicates the layer into every
+                member's cache with ``multimem.st`` through NVSwitch; the last layer carries the
+                completion word every member waits for (bounded).  The relay rank receives two copies
+                (the push and the echo of its own multicast);
+      scatter   the prefill GPU still sends one copy, but scatters the blocks over landing buffers of ALL
+                members; every member relays its share the same way and signals in its own completion
+                word; everybody waits for all words.  No member receives more than 1 + 1/k copies.
+    """
+    import struct
+
+    import torch.distributed as dist
+
+    from .parallel.nvls import MulticastKVCache
+
+    assert world >= 3, "one prefill rank and a decode group of at least two"
+    blk_tokens, tok_bytes = 64, 656
+    blk = blk_tokens * tok_bytes                      # 41984 bytes, a multiple of 16
+    n_blk = (tokens + blk_tokens - 1) // blk_tokens
+    num_blocks = n_blk + n_blk // 4
+    layer_bytes = num_blocks * blk
+    is_p, r0 = rank == 0, 1
+    k = world - 1
+    bounds = [n_blk * j // k for j in range(k + 1)]          # member j (rank j + 1) relays blocks [bounds[j], bounds[j + 1])
+    share_max = max(bounds[j + 1] - bounds[j] for j in range(k))
+    d_group = dist.new_group(list(range(1, world)))
+    rng = __import__("random").Random(23)
+    sb = rng.sample(range(num_blocks), n_blk)
+    db = rng.sample(range(num_blocks), n_blk)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    rules = torch.frombuffer(bytearray(struct.pack("<qqqqII", 0, 0, 0, 0, blk, 1)), dtype=torch.uint8).to(dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    counter = torch.zeros(n_layers + 1, dtype=torch.int32, device=dev)
+
+    def gen_layer(layer: int) -> torch.Tensor:
+        g = torch.Generator(device=dev)
+        g.manual_seed(977 + layer)
+        return torch.randint(0, 256, (layer_bytes,), dtype=torch.uint8, device=dev, generator=g)
+
+    # ---- memory -------------------------------------------------------------------------------------------
+    cache = plain = landing = flags = src = None
+    mine = None
+    if is_p:
+        src = torch.empty(n_layers * layer_bytes, dtype=torch.uint8, device=dev)
+        for layer in range(n_layers):
+            src[layer * layer_bytes:(layer + 1) * layer_bytes].copy_(gen_layer(layer))
+    else:
+        cache = MulticastKVCache(n_layers, layer_bytes, d_group, dev)
+        plain = torch.zeros(n_layers * layer_bytes, dtype=torch.uint8, device=dev)
+        flags = torch.zeros(n_layers + 8, dtype=torch.int64, device=dev)      # [0, L): per-layer arrival, [L]: unicast done
+        mine = {}
+        tensors = {"plain": plain, "flags": flags}
+        landing = torch.zeros(n_layers * n_blk * blk, dtype=torch.uint8, device=dev) if rank == r0 else \
+            torch.zeros(n_layers * share_max * blk, dtype=torch.uint8, device=dev)
+        tensors["landing"] = landing
+        for name, t in tensors.items():
+            h, base, _size = K.kvt_ipc_get_handle(t.data_ptr())
+            mine[name] = (h, t.data_ptr() - base)
+    infos = [None] * world
+    dist.all_gather_object(infos, mine)
+    torch.cuda.synchronize()
+
+    main = torch.cuda.current_stream(dev)
+    streams = [torch.cuda.Stream(dev) for _ in range(n_streams)]
+    if is_p:
+        opened = {}
+
+        def peer(r, name):
+            h, off = infos[r][name]
+            if h not in opened:
+                opened[h] = K.kvt_ipc_open_handle(h)
+            return opened[h] + off
+
+        src_layers = torch.tensor([src.data_ptr() + i * layer_bytes for i in range(n_layers)], dtype=torch.int64, device=dev)
+        uni_layers = {r: torch.tensor([peer(r, "plain") + i * layer_bytes for i in range(n_layers)], dtype=torch.int64,
+                                      device=dev) for r in range(1, world)}
+        land_layers = torch.tensor([peer(r0, "landing") + i * n_blk * blk for i in range(n_layers)], dtype=torch.int64,
+                                   device=dev)
+        peer_flags = {r: peer(r, "flags") for r in range(1, world)}
+        sb_t, db_t, seq_t = i32(sb), i32(db), i32(list(range(n_blk)))
+        share_layers = {r: torch.tensor([peer(r, "landing") + i * ((n_blk if r == r0 else share_max) * blk)
+                                         for i in range(n_layers)], dtype=torch.int64, device=dev) for r in range(1, world)}
+
+    def push(dst_layers, dst_stride, dst_nblk, dst_ids, layer, stream, flag=0, value=0, lo=0, hi=None, cnt=None):
+        hi = n_blk if hi is None else hi
+        K.kvt_launch_p2d_state(src_layers.data_ptr(), dst_layers.data_ptr(), layer, layer + 1, blk, dst_stride, num_blocks,
+                               dst_nblk, sb_t[lo:].data_ptr(), dst_ids.data_ptr(), hi - lo, rules.data_ptr(), 1,
+                               status.data_ptr(), (counter if cnt is None else cnt)[layer:].data_ptr() if flag else 0, flag,
+                               value, 0, 512, stream.cuda_stream)
+
+    def run_unicast(step: int) -> None:
+        if is_p:
+            for s in streams:
+                s.wait_stream(main)
+            k = 0
+            for layer in range(n_layers):
+                for r in range(1, world):
+                    push(uni_layers[r], blk, num_blocks, db_t, layer, streams[k % n_streams])
+                    k += 1
+            for s in streams:
+                main.wait_stream(s)
+            for r in range(1, world):
+                K.kvt_launch_set_flag(peer_flags[r] + 8 * n_layers, step, main.cuda_stream)
+        else:
+            K.kvt_launch_wait_flag(flags[n_layers:].data_ptr(), step, int(5e9), status.data_ptr(), main.cuda_stream)
+
+    def run_nvls(step: int) -> None:
+        if is_p:
+            for s in streams:
+                s.wait_stream(main)
+            for layer in range(n_layers):
+                push(land_layers, blk, n_blk, seq_t, layer, streams[layer % n_streams], peer_flags[r0] + 8 * layer, step)
+            for s in streams:
+                main.wait_stream(s)
+        elif rank == r0:
+            two = streams[:2]
+            for s in two:
+                s.wait_stream(main)
+            for layer in range(n_layers):
+                last = layer == n_layers - 1
+                st = main if last else two[layer % 2]
+                if last:
+                    for s in two:
+                        main.wait_stream(s)
+                K.kvt_launch_wait_flag(flags[layer:].data_ptr(), step, int(5e9), status.data_ptr(), st.cuda_stream)
+                cache.fanout(db_r0, blk, num_blocks, layers=(layer, layer + 1), flag_value=step if last else 0, stream=st,
+                             src_layers=land_src, src_block_ids=seq_r0, src_block_stride=blk, src_num_blocks=n_blk)
+            cache.wait(step, timeout_s=5.0, stream=main, slots=[r0 - 1], sync=False)
+        else:
+            cache.wait(step, timeout_s=5.0, stream=main, slots=[r0 - 1], sync=False)
+
+    def run_scatter(step: int) -> None:
+        if is_p:
+            for s in streams:
+                s.wait_stream(main)
+            n = 0
+            for layer in range(n_layers):
+                for j in range(k):
+                    r = j + 1
+                    push(share_layers[r], blk, n_blk if r == r0 else share_max, seq_t, layer, streams[n % n_streams],
+                         peer_flags[r] + 8 * layer, step, lo=bounds[j], hi=bounds[j + 1], cnt=counters_by_member[j])
+                    n += 1
+            for s in streams:
+                main.wait_stream(s)
+        else:
+            j = rank - 1
+            two = streams[:2]
+            for s in two:
+                s.wait_stream(main)
+            for layer in range(n_layers):
+                last = layer == n_layers - 1
+                st = main if last else two[layer % 2]
+                if last:
+                    for s in two:
+                        main.wait_stream(s)
+                K.kvt_launch_wait_flag(flags[layer:].data_ptr(), step, int(5e9), status.data_ptr(), st.cuda_stream)
+                cache.fanout(db_mine, blk, num_blocks, layers=(layer, layer + 1), flag_value=step if last else 0, stream=st,
+                             src_layers=land_mine, src_block_ids=seq_mine, src_block_stride=blk,
+                             src_num_blocks=n_blk if rank == r0 else share_max)
+            cache.wait(step, timeout_s=5.0, stream=main, sync=False)
+
+    if is_p:
+        counters_by_member = [torch.zeros(n_layers + 1, dtype=torch.int32, device=dev) for _ in range(k)]
+    else:
+        j = rank - 1
+        db_mine, seq_mine = i32(db[bounds[j]:bounds[j + 1]]), i32(list(range(bounds[j + 1] - bounds[j])))
+        land_mine = torch.tensor([landing.data_ptr() + i * ((n_blk if rank == r0 else share_max) * blk)
+                                  for i in range(n_layers)], dtype=torch.int64, device=dev)
+    if rank == r0:
+        db_r0, seq_r0 = i32(db), i32(list(range(n_blk)))
+        land_src = torch.tensor([landing.data_ptr() + i * n_blk * blk for i in range(n_layers)], dtype=torch.int64, device=dev)
+
+    def timed(fn, first_step: int) -> float:
+        best = 1e30
+        for it in range(warmup + iters):
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn(first_step + it)
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            if it >= warmup:
+                best = min(best, float(t.item()))
+        return best
+
+    errors = []
+    ms_uni = ms_nvls = ms_scatter = 0.0
+    try:
+        ms_uni = timed(run_unicast, 1)
+        ms_nvls = timed(run_nvls, 1)
+        torch.cuda.synchronize()
+
+        def check(name, t):
+            for layer in (0, n_layers - 1):
+                want = gen_layer(layer).view(num_blocks, blk)[i32(sb).long()]
+                got = t[layer * layer_bytes:(layer + 1) * layer_bytes].view(num_blocks, blk)[i32(db).long()]
+                if not torch.equal(got, want):
+                    errors.append(f"rank {rank}: {name} layer {layer} differs")
+
+        if not is_p:
+            check("unicast", plain)
+            check("nvls single relay", cache.buffer)
+            cache.buffer[:n_layers * layer_bytes].zero_()    # the scatter arm must be seen to deliver too
+        ms_scatter = timed(run_scatter, 100)
+        torch.cuda.synchronize()
+        code = int(status[0].item())
+        if code != 0:
+            errors.append(f"rank {rank}: kernel status {code} detail {int(status[1].item())}")
+        if not is_p:
+            if cache.wait_failed():
+                errors.append(f"rank {rank}: a bounded wait for a completion word ran out")
+            cache.check_status()
+            check("nvls scatter", cache.buffer)
+    except Exception as ex:   # every rank still takes part in the collective teardown below
+        errors.append(f"rank {rank}: {type(ex).__name__}: {ex}")
+    all_errors = [None] * world
+    dist.all_gather_object(all_errors, errors)
+    if cache is not None:
+        cache.close()
+    dist.barrier()
+    bytes_per_copy = n_layers * n_blk * blk
+    n_d = world - 1
+    flat = [e for es in all_errors for e in es]
+    return {"decode_ranks": n_d, "tokens": tokens, "layers": n_layers, "bytes_per_copy": bytes_per_copy,
+            "unicast_ms": round(ms_uni, 4), "nvls_single_relay_ms": round(ms_nvls, 4),
+            "nvls_scatter_ms": round(ms_scatter, 4),
+            "unicast_delivered_GBps": round(n_d * bytes_per_copy / (ms_uni * 1e-3) / 1e9, 1) if ms_uni > 0 else 0.0,
+            "nvls_single_relay_delivered_GBps": round(n_d * bytes_per_copy / (ms_nvls * 1e-3) / 1e9, 1) if ms_nvls > 0 else 0.0,
+            "nvls_scatter_delivered_GBps": round(n_d * bytes_per_copy / (ms_scatter * 1e-3) / 1e9, 1) if ms_scatter > 0 else 0.0,
+            "speedup_single_relay": round(ms_uni / ms_nvls, 2) if ms_nvls > 0 else 0.0,
+            "speedup_scatter": round(ms_uni / ms_scatter, 2) if ms_scatter > 0 else 0.0,
+            "prefill_egress_bytes": {"unicast": n_d * bytes_per_copy, "nvls": bytes_per_copy},
+            "verified": not flat, "errors": flat[:4]}

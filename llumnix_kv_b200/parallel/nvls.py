@@ -13,8 +13,12 @@ once and NVSwitch writes them into every member's memory.
     ... prefill pushes the request's blocks into rank r0's cache.layers ...
     if group.rank() == r0:
         cache.fanout(block_ids, block_stride, num_blocks, flag_value=stepid)  # one kernel
-    else:
-        cache.wait(flag_value=stepid, timeout_s=1.0)                           # bounded device wait
+    cache.wait(flag_value=stepid, slots=[r0], timeout_s=1.0)                   # bounded device wait
+
+Better balanced: the prefill rank scatters the request's blocks over landing buffers of ALL members
+(still one copy on its link), every member relays its share from its landing buffer
+(``src_layers=...``) and signals in its own completion word, and everybody waits for all words: no
+member receives more than 1 + 1/k copies, where the single-relay form makes r0 receive two.
 
 Teardown is collective: every rank calls ``close()`` (barrier, then release) while all ranks are
 alive.  Only stores are multicast; nothing loads through the multicast address.
@@ -56,7 +60,8 @@ class MulticastKVCache:
         self.local_ptr = self.buffer.data_ptr()
         self.layers = [self.buffer[i * layer_bytes:(i + 1) * layer_bytes] for i in range(num_layers)]
         self._flag_off = num_layers * layer_bytes
-        self.flag = self.buffer[self._flag_off:self._flag_off + 8].view(torch.int64)
+        assert self.world * 8 <= _FLAG_BYTES
+        self.flags = self.buffer[self._flag_off:self._flag_off + _FLAG_BYTES].view(torch.int64)   # one word per rank
         dev = self.device
         self._src_layers = torch.tensor([self.local_ptr + i * layer_bytes for i in range(num_layers)], dtype=torch.int64,
                                         device=dev)
@@ -67,6 +72,7 @@ class MulticastKVCache:
         self._counter = torch.zeros(1, dtype=torch.int32, device=dev)
         self._ops = load_ops()
         self._closed = False
+        self._keep = __import__("collections").deque(maxlen=256)
 
     # ---- the member that received the blocks -----------------------------------------------------------
     def _ids(self, block_ids) -> torch.Tensor:
@@ -75,7 +81,7 @@ class MulticastKVCache:
         return torch.tensor(list(block_ids), dtype=torch.int32, device=self.device)
 
     def fanout(self, block_ids, block_stride: int, num_blocks: int, block_off: int = 0, block_len: Optional[int] = None,
-               layers: Optional[Sequence[int]] = None, flag_value: int = 0, grid: int = 0,
+               layers: Optional[Sequence[int]] = None, flag_value: int = 0, flag_slot: Optional[int] = None, grid: int = 0,
                stream: Optional[torch.cuda.Stream] = None, src_layers: Optional[torch.Tensor] = None,
                src_block_ids=None, src_block_stride: Optional[int] = None, src_num_blocks: Optional[int] = None) -> None:
         """Replicate blocks of layers ``[layers[0], layers[1])`` into ``block_ids`` of every member.
@@ -84,7 +90,9 @@ class MulticastKVCache:
         ``src_layers`` (an int64 device tensor of per-layer base addresses of any local memory, for
         instance a landing buffer that the sender reaches over CUDA-IPC) the blocks are read from there,
         at ``src_block_ids`` with ``src_block_stride``.  ``block_ids`` may be lists or int32 device tensors.
-        With ``flag_value`` != 0 every member's completion word receives it after the data."""
+        With ``flag_value`` != 0 completion word ``flag_slot`` (default: this rank's) of every member
+        receives it after the data: when several members relay shares of one request, each signals in
+        its own word and ``wait`` looks at all of them."""
         ids = self._ids(block_ids)
         sids = ids if src_block_ids is None else self._ids(src_block_ids)
         assert sids.numel() == ids.numel()
@@ -96,11 +104,12 @@ class MulticastKVCache:
         blen = min(block_stride, sstride) - block_off if block_len is None else block_len
         src = self._src_layers if src_layers is None else src_layers
         st = stream if stream is not None else torch.cuda.current_stream(self.device)
-        self._keep = (ids, sids, src)      # alive until the next call: the launch is asynchronous
+        self._keep.append((ids, sids, src))   # the launches are asynchronous: keep their arguments alive for a while
         self._ops.kvt_launch_mc_fanout(
             src.data_ptr(), self._mc_layers.data_ptr(), lo, hi, sstride, block_stride, snum, num_blocks, sids.data_ptr(),
             ids.data_ptr(), ids.numel(), block_off, blen, self._status.data_ptr(), self._counter.data_ptr(),
-            (self.mc_ptr + self._flag_off) if flag_value else 0, flag_value, grid, st.cuda_stream)
+            (self.mc_ptr + self._flag_off + 8 * (self.rank if flag_slot is None else flag_slot)) if flag_value else 0,
+            flag_value, grid, st.cuda_stream)
 
     def check_status(self) -> None:
         code, detail = (int(x) for x in self._status[:2].tolist())
@@ -109,15 +118,24 @@ class MulticastKVCache:
             raise RuntimeError(f"fan-out kernel reported status {code} (detail {detail})")
 
     # ---- the other members -----------------------------------------------------------------------------
-    def wait(self, flag_value: int, timeout_s: float = 1.0, stream: Optional[torch.cuda.Stream] = None) -> bool:
-        """Device-side wait, bounded by ``timeout_s``, until this member's completion word reaches
-        ``flag_value``; returns False when the wait ran out (the context stays usable)."""
+    def wait(self, flag_value: int, timeout_s: float = 1.0, stream: Optional[torch.cuda.Stream] = None,
+             slots: Optional[Sequence[int]] = None, sync: bool = True) -> bool:
+        """Device-side wait, bounded by ``timeout_s`` per word, until this member's completion words
+        ``slots`` (default: one per rank of the group) reach ``flag_value``; returns False when a wait ran
+        out (the context stays usable).  With ``sync=False`` the waits are only enqueued; read
+        ``wait_failed()`` after synchronising the stream."""
         st = stream if stream is not None else torch.cuda.current_stream(self.device)
         self._wait_status.zero_()
-        self._ops.kvt_launch_wait_flag(self.flag.data_ptr(), flag_value, int(timeout_s * 1e9), self._wait_status.data_ptr(),
-                                       st.cuda_stream)
+        for slot in (range(self.world) if slots is None else slots):
+            self._ops.kvt_launch_wait_flag(self.flags[slot:].data_ptr(), flag_value, int(timeout_s * 1e9),
+                                           self._wait_status.data_ptr(), st.cuda_stream)
+        if not sync:
+            return True
         st.synchronize()
-        return int(self._wait_status[0].item()) == 0
+        return not self.wait_failed()
+
+    def wait_failed(self) -> bool:
+        return int(self._wait_status[0].item()) != 0
 
     # ---- collective teardown ---------------------------------------------------------------------------
     def close(self) -> None:
@@ -129,7 +147,7 @@ class MulticastKVCache:
         torch.cuda.synchronize(self.device)
         self._dist.barrier(self.group)
         self.layers = []
-        self.flag = None
+        self.flags = None
         self._handle = None
         self.buffer = None
         torch.cuda.synchronize(self.device)

@@ -54,7 +54,7 @@ def _child(rank: int, world: int, port: int, q) -> None:
                 cache.check_status()
             except Exception as ex:
                 errors.append(f"in-place status: {ex}")
-        elif not cache.wait(1, timeout_s=5.0):
+        elif not cache.wait(1, timeout_s=5.0, slots=[0]):
             errors.append("in-place: the completion word never arrived")
         for layer in range(LAYERS):
             for b in range(NUM_BLOCKS):
@@ -78,7 +78,7 @@ def _child(rank: int, world: int, port: int, q) -> None:
                 cache.check_status()
             except Exception as ex:
                 errors.append(f"landing status: {ex}")
-        elif not cache.wait(2, timeout_s=5.0):
+        elif not cache.wait(2, timeout_s=5.0, slots=[0]):
             errors.append("landing: the completion word never arrived")
         land = _expected(7, landing.numel())
         for layer in range(LAYERS):
@@ -94,11 +94,32 @@ def _child(rank: int, world: int, port: int, q) -> None:
 
         # ---- 3. a wait that nothing satisfies runs out and leaves the context usable -----------------------
         if rank == world - 1:
-            if cache.wait(99, timeout_s=0.2):
+            if cache.wait(99, timeout_s=0.2, slots=[0]):
                 errors.append("bounded wait: returned True although nothing set the word")
             probe = torch.ones(4, device=dev).sum().item()
             if probe != 4.0:
                 errors.append("bounded wait: context unusable afterwards")
+        dist.barrier()
+
+        # ---- 3b. every member relays its share from its own landing buffer; everybody waits for all words ----
+        all_ids = [12, 2, 14, 6, 10, 8, 13, 11][:2 * world]
+        share = all_ids[2 * rank:2 * rank + 2]
+        mine = torch.zeros(LAYERS * 2 * STRIDE, dtype=torch.uint8, device=dev)
+        mine.copy_(_expected(500 + rank, mine.numel()))
+        mine_ptrs = torch.tensor([mine.data_ptr() + i * 2 * STRIDE for i in range(LAYERS)], dtype=torch.int64, device=dev)
+        torch.cuda.synchronize()
+        dist.barrier()
+        cache.fanout(share, STRIDE, NUM_BLOCKS, flag_value=5, src_layers=mine_ptrs, src_block_ids=[0, 1],
+                     src_block_stride=STRIDE, src_num_blocks=2)
+        if not cache.wait(5, timeout_s=5.0):
+            errors.append("scatter: a completion word never arrived")
+        for r in range(world):
+            theirs = _expected(500 + r, mine.numel())
+            for layer in range(LAYERS):
+                for i, b in enumerate(all_ids[2 * r:2 * r + 2]):
+                    o = (layer * 2 + i) * STRIDE
+                    if not torch.equal(block(layer, b).cpu(), theirs[o:o + STRIDE]):
+                        errors.append(f"scatter: layer {layer} block {b} (share of rank {r}) differs on rank {rank}")
         dist.barrier()
 
         # ---- 4. a block id outside the tensor is reported and skipped ------------------------------------
