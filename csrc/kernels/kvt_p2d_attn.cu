@@ -277,6 +277,10 @@ __device__ __forceinline__ void simt_quant_tile(const KvtAttnLaunch& p, const Ti
   const int64_t sc_base = d_blk + p.dst.scale_base + (int64_t)kv * p.dst.scale_kv_stride +
                           (int64_t)slot_d * p.dst.scale_token_stride +
                           (int64_t)p.dst_head0 * p.dst.scale_head_stride;
+  // rows of a multiple of 128 values, scale rows 4-byte aligned: scales leave as 32-bit words
+  const bool wide_scales = (cpr & 7u) == 0u &&
+                           (((uint64_t)sc_base | (uint64_t)p.dst.scale_token_stride | (uint64_t)p.dst.scale_head_stride |
+                             (uint64_t)p.dst.block_stride | reinterpret_cast<uintptr_t>(dst)) & 3u) == 0u;
   // Two rounds in flight per thread: the loads of both are issued before either is converted.
   const uint32_t rounds = (chunks + nthr - 1) / nthr;
   for (uint32_t rnd = 0; rnd < rounds; rnd += 2) {
@@ -319,10 +323,22 @@ __device__ __forceinline__ void simt_quant_tile(const KvtAttnLaunch& p, const Ti
         q.z = pack_e4m3x4(bf16lo(w[u][4]) * inv, bf16hi(w[u][4]) * inv, bf16lo(w[u][5]) * inv, bf16hi(w[u][5]) * inv);
         q.w = pack_e4m3x4(bf16lo(w[u][6]) * inv, bf16hi(w[u][6]) * inv, bf16lo(w[u][7]) * inv, bf16hi(w[u][7]) * inv);
         st_16(dst + d_base + (int64_t)t[u] * p.dst.token_stride + (int64_t)h[u] * p.dst.head_stride + (c[u] << 4), q);
-        if ((c[u] & 1u) == 0u) {
-          dst[sc_base + (int64_t)t[u] * p.dst.scale_token_stride + (int64_t)h[u] * p.dst.scale_head_stride +
-              (c[u] >> 1)] = static_cast<char>(e);
+      }
+      if (wide_scales) {
+        // eight neighbouring lanes hold 128 values of one row = four scales: one 4-byte store instead of
+        // four 1-byte stores (over NVLink every store is a packet of its own, whatever its size)
+        const uint32_t lane = tid & 31u;
+        const uint32_t e1 = __shfl_sync(0xffffffffu, e, (lane & ~7u) + 2u);
+        const uint32_t e2 = __shfl_sync(0xffffffffu, e, (lane & ~7u) + 4u);
+        const uint32_t e3 = __shfl_sync(0xffffffffu, e, (lane & ~7u) + 6u);
+        if (active[u] && (lane & 7u) == 0u) {
+          *reinterpret_cast<uint32_t*>(dst + sc_base + (int64_t)t[u] * p.dst.scale_token_stride +
+                                       (int64_t)h[u] * p.dst.scale_head_stride + (c[u] >> 1)) =
+              e | (e1 << 8) | (e2 << 16) | (e3 << 24);
         }
+      } else if (active[u] && (c[u] & 1u) == 0u) {
+        dst[sc_base + (int64_t)t[u] * p.dst.scale_token_stride + (int64_t)h[u] * p.dst.scale_head_stride +
+            (c[u] >> 1)] = static_cast<char>(e);
       }
     }
   }

@@ -830,7 +830,7 @@ def quant_reshard_nvlink(K, rank: int, world: int, dev, tokens: int = 8192, n_la
 
 
 def mla_fanout_bandwidth(K, rank: int, world: int, dev, tokens: int = 32768, n_layers: int = 61, iters: int = 5,
-                         warmup: int = 2, n_streams: int = 4) -> dict:
+                         warmup: int = 2, n_streams: int = 4, layer_group: int = 4) -> dict:
     """Replicated MLA latent pages from one prefill GPU (rank 0) to every rank of a decode TP group
     (ranks 1..world-1), two ways, device-timed, max over ranks:
 
@@ -852,6 +852,9 @@ def mla_fanout_bandwidth(K, rank: int, world: int, dev, tokens: int = 32768, n_l
     from .parallel.nvls import MulticastKVCache
 
     assert world >= 3, "one prefill rank and a decode group of at least two"
+    # the relay arms move ``layer_group`` layers per launch and flag: with one launch per layer and member the
+    # prefill GPU's launch rate, not its link, bounds a group of seven
+    groups = [(lo, min(lo + layer_group, n_layers)) for lo in range(0, n_layers, layer_group)]
     blk_tokens, tok_bytes = 64, 656
     blk = blk_tokens * tok_bytes                      # 41984 bytes, a multiple of 16
     n_blk = (tokens + blk_tokens - 1) // blk_tokens
@@ -919,12 +922,14 @@ def mla_fanout_bandwidth(K, rank: int, world: int, dev, tokens: int = 32768, n_l
         share_layers = {r: torch.tensor([peer(r, "landing") + i * ((n_blk if r == r0 else share_max) * blk)
                                          for i in range(n_layers)], dtype=torch.int64, device=dev) for r in range(1, world)}
 
-    def push(dst_layers, dst_stride, dst_nblk, dst_ids, layer, stream, flag=0, value=0, lo=0, hi=None, cnt=None):
+    def push(dst_layers, dst_stride, dst_nblk, dst_ids, layer, stream, flag=0, value=0, lo=0, hi=None, cnt=None,
+             layer_end=None):
         hi = n_blk if hi is None else hi
-        K.kvt_launch_p2d_state(src_layers.data_ptr(), dst_layers.data_ptr(), layer, layer + 1, blk, dst_stride, num_blocks,
-                               dst_nblk, sb_t[lo:].data_ptr(), dst_ids.data_ptr(), hi - lo, rules.data_ptr(), 1,
-                               status.data_ptr(), (counter if cnt is None else cnt)[layer:].data_ptr() if flag else 0, flag,
-                               value, 0, 512, stream.cuda_stream)
+        K.kvt_launch_p2d_state(src_layers.data_ptr(), dst_layers.data_ptr(), layer, layer + 1 if layer_end is None else layer_end,
+                               blk, dst_stride, num_blocks, dst_nblk, sb_t[lo:].data_ptr(), dst_ids.data_ptr(), hi - lo,
+                               rules.data_ptr(), 1, status.data_ptr(),
+                               (counter if cnt is None else cnt)[layer:].data_ptr() if flag else 0, flag, value, 0, 512,
+                               stream.cuda_stream)
 
     def run_unicast(step: int) -> None:
         if is_p:
@@ -946,22 +951,22 @@ def mla_fanout_bandwidth(K, rank: int, world: int, dev, tokens: int = 32768, n_l
         if is_p:
             for s in streams:
                 s.wait_stream(main)
-            for layer in range(n_layers):
-                push(land_layers, blk, n_blk, seq_t, layer, streams[layer % n_streams], peer_flags[r0] + 8 * layer, step)
+            for gi, (lo, hi) in enumerate(groups):
+                push(land_layers, blk, n_blk, seq_t, lo, streams[gi % n_streams], peer_flags[r0] + 8 * lo, step, layer_end=hi)
             for s in streams:
                 main.wait_stream(s)
         elif rank == r0:
             two = streams[:2]
             for s in two:
                 s.wait_stream(main)
-            for layer in range(n_layers):
-                last = layer == n_layers - 1
-                st = main if last else two[layer % 2]
+            for gi, (lo, hi) in enumerate(groups):
+                last = gi == len(groups) - 1
+                st = main if last else two[gi % 2]
                 if last:
                     for s in two:
                         main.wait_stream(s)
-                K.kvt_launch_wait_flag(flags[layer:].data_ptr(), step, int(5e9), status.data_ptr(), st.cuda_stream)
-                cache.fanout(db_r0, blk, num_blocks, layers=(layer, layer + 1), flag_value=step if last else 0, stream=st,
+                K.kvt_launch_wait_flag(flags[lo:].data_ptr(), step, int(5e9), status.data_ptr(), st.cuda_stream)
+                cache.fanout(db_r0, blk, num_blocks, layers=(lo, hi), flag_value=step if last else 0, stream=st,
                              src_layers=land_src, src_block_ids=seq_r0, src_block_stride=blk, src_num_blocks=n_blk)
             cache.wait(step, timeout_s=5.0, stream=main, slots=[r0 - 1], sync=False)
         else:
@@ -972,11 +977,11 @@ def mla_fanout_bandwidth(K, rank: int, world: int, dev, tokens: int = 32768, n_l
             for s in streams:
                 s.wait_stream(main)
             n = 0
-            for layer in range(n_layers):
+            for lo, hi in groups:
                 for j in range(k):
                     r = j + 1
-                    push(share_layers[r], blk, n_blk if r == r0 else share_max, seq_t, layer, streams[n % n_streams],
-                         peer_flags[r] + 8 * layer, step, lo=bounds[j], hi=bounds[j + 1], cnt=counters_by_member[j])
+                    push(share_layers[r], blk, n_blk if r == r0 else share_max, seq_t, lo, streams[n % n_streams],
+                         peer_flags[r] + 8 * lo, step, lo=bounds[j], hi=bounds[j + 1], cnt=counters_by_member[j], layer_end=hi)
                     n += 1
             for s in streams:
                 main.wait_stream(s)
@@ -985,14 +990,14 @@ def mla_fanout_bandwidth(K, rank: int, world: int, dev, tokens: int = 32768, n_l
             two = streams[:2]
             for s in two:
                 s.wait_stream(main)
-            for layer in range(n_layers):
-                last = layer == n_layers - 1
-                st = main if last else two[layer % 2]
+            for gi, (lo, hi) in enumerate(groups):
+                last = gi == len(groups) - 1
+                st = main if last else two[gi % 2]
                 if last:
                     for s in two:
                         main.wait_stream(s)
-                K.kvt_launch_wait_flag(flags[layer:].data_ptr(), step, int(5e9), status.data_ptr(), st.cuda_stream)
-                cache.fanout(db_mine, blk, num_blocks, layers=(layer, layer + 1), flag_value=step if last else 0, stream=st,
+                K.kvt_launch_wait_flag(flags[lo:].data_ptr(), step, int(5e9), status.data_ptr(), st.cuda_stream)
+                cache.fanout(db_mine, blk, num_blocks, layers=(lo, hi), flag_value=step if last else 0, stream=st,
                              src_layers=land_mine, src_block_ids=seq_mine, src_block_stride=blk,
                              src_num_blocks=n_blk if rank == r0 else share_max)
             cache.wait(step, timeout_s=5.0, stream=main, sync=False)
@@ -1062,7 +1067,8 @@ def mla_fanout_bandwidth(K, rank: int, world: int, dev, tokens: int = 32768, n_l
     bytes_per_copy = n_layers * n_blk * blk
     n_d = world - 1
     flat = [e for es in all_errors for e in es]
-    return {"decode_ranks": n_d, "tokens": tokens, "layers": n_layers, "bytes_per_copy": bytes_per_copy,
+    return {"decode_ranks": n_d, "tokens": tokens, "layers": n_layers, "layers_per_launch": layer_group,
+            "bytes_per_copy": bytes_per_copy,
             "unicast_ms": round(ms_uni, 4), "nvls_single_relay_ms": round(ms_nvls, 4),
             "nvls_scatter_ms": round(ms_scatter, 4),
             "unicast_delivered_GBps": round(n_d * bytes_per_copy / (ms_uni * 1e-3) / 1e9, 1) if ms_uni > 0 else 0.0,
