@@ -205,6 +205,32 @@ void bind_kernels(py::module_& m) {
       py::arg("dst_capacity"), py::arg("status"), py::arg("grid"), py::arg("stream"));
 
   m.def(
+      "kvt_launch_copy_blocks_multi",
+      [](const std::vector<uint64_t>& src_bases, const std::vector<uint64_t>& dst_bases,
+         const std::vector<uint64_t>& src_caps, const std::vector<uint64_t>& dst_caps, const std::vector<uint32_t>& first,
+         uint64_t triples, uint64_t status, int grid, uint64_t stream) {
+        const size_t nt = src_bases.size();
+        if (nt == 0 || nt > KVT_COPY_MAX_TENSORS || dst_bases.size() != nt || src_caps.size() != nt ||
+            dst_caps.size() != nt || first.size() != nt + 1)
+          throw std::invalid_argument("kvt_launch_copy_blocks_multi: 1..8 tensors, first has one entry more");
+        KvtCopyMulti a{};
+        for (size_t t = 0; t < nt; ++t) {
+          a.src_base[t] = src_bases[t];
+          a.dst_base[t] = dst_bases[t];
+          a.src_cap[t] = src_caps[t];
+          a.dst_cap[t] = dst_caps[t];
+          a.first[t] = first[t];
+        }
+        a.first[nt] = first[nt];
+        a.n_tensors = static_cast<uint32_t>(nt);
+        a.triples = reinterpret_cast<const uint64_t*>(triples);
+        a.status = reinterpret_cast<uint32_t*>(status);
+        check_cuda(kvt_launch_copy_blocks_multi(&a, grid, reinterpret_cast<void*>(stream)), "kvt_launch_copy_blocks_multi");
+      },
+      py::arg("src_bases"), py::arg("dst_bases"), py::arg("src_caps"), py::arg("dst_caps"), py::arg("first"),
+      py::arg("triples"), py::arg("status"), py::arg("grid"), py::arg("stream"));
+
+  m.def(
       "kvt_launch_mc_fanout",
       [](uint64_t src_layers, uint64_t mc_layers, uint32_t layer_begin, uint32_t layer_end, int64_t src_block_stride,
          int64_t dst_block_stride, uint32_t src_num_blocks, uint32_t dst_num_blocks, uint64_t src_blocks,

@@ -148,6 +148,22 @@ int kvt_launch_copy_blocks(uint64_t src_base, uint64_t dst_base, const uint64_t*
                            uint32_t n, uint64_t src_capacity, uint64_t dst_capacity,
                            uint32_t* status, int grid_ctas, void* stream);
 
+// The same copy over up to KVT_COPY_MAX_TENSORS tensor pairs in ONE launch: descriptors
+// [first[t], first[t+1]) of `triples` are relative to src_base[t] / dst_base[t].  A layer of a
+// multi-tensor cache (MLA latent + indexer keys, hybrid groups) then costs one launch, not one per tensor.
+#define KVT_COPY_MAX_TENSORS 8
+typedef struct KvtCopyMulti {
+  uint64_t src_base[KVT_COPY_MAX_TENSORS];
+  uint64_t dst_base[KVT_COPY_MAX_TENSORS];
+  uint64_t src_cap[KVT_COPY_MAX_TENSORS];
+  uint64_t dst_cap[KVT_COPY_MAX_TENSORS];
+  uint32_t first[KVT_COPY_MAX_TENSORS + 1];
+  uint32_t n_tensors;
+  const uint64_t* triples;     // device
+  uint32_t* status;            // device: [0] first error code, [1] descriptor index
+} KvtCopyMulti;
+int kvt_launch_copy_blocks_multi(const KvtCopyMulti* args, int grid_ctas, void* stream);
+
 // ---- the same copy for callers that must not allocate --------------------------------------
 // This entry point has no counterpart in the reference.  It exists for callers that cannot
 // allocate at call time (a transfer issued in an engine's steady state with a fully sized

@@ -107,31 +107,70 @@ __global__ void __launch_bounds__(512) kvt_p2d_state_kernel(const __grid_constan
   }
 }
 
+// A warp per 4 KiB segment.  The descriptors of one list are usually of one length (the pages of a
+// cache tensor), so the segment count of the FIRST descriptor lays out the work: unit u is segment
+// u % segs0 of descriptor u / segs0, and a descriptor longer than the first has its further
+// segments taken by the same warps in a strided loop.  Few long descriptors thus spread over every
+// SM as well as many short ones do.
+constexpr uint32_t kCopySeg = 4096;
+
 __global__ void __launch_bounds__(512) kvt_copy_blocks_kernel(const char* __restrict__ src, char* __restrict__ dst,
                                                                const uint64_t* __restrict__ triples, uint32_t n,
                                                                uint64_t src_cap, uint64_t dst_cap,
                                                                uint32_t* status) {
   const uint32_t warps_per_cta = blockDim.x >> 5;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-  // Few descriptors: one CTA per descriptor; many: one warp per descriptor.
-  const bool cta_mode = n <= gridDim.x * 2u;
-  if (cta_mode) {
-    for (uint32_t i = blockIdx.x; i < n; i += gridDim.x) {
-      const uint64_t so = triples[3 * i], dof = triples[3 * i + 1], len = triples[3 * i + 2];
-      if (so > src_cap || len > src_cap - so || dof > dst_cap || len > dst_cap - dof || len > 0xffffffffull) {
-        if (threadIdx.x == 0) set_status(status, KVT_ERR_BLOCK_RANGE, i);
-        continue;
-      }
-      copy_span(src + so, dst + dof, (uint32_t)len, threadIdx.x, blockDim.x);
+  const uint64_t len0 = triples[2];
+  const uint32_t segs0 = len0 > kCopySeg ? (uint32_t)min((len0 + kCopySeg - 1) / kCopySeg, (uint64_t)65536) : 1u;
+  const uint64_t total = (uint64_t)n * segs0;
+  for (uint64_t u = (uint64_t)blockIdx.x * warps_per_cta + warp; u < total; u += (uint64_t)gridDim.x * warps_per_cta) {
+    const uint32_t i = (uint32_t)(u / segs0);
+    const uint32_t s0 = (uint32_t)(u - (uint64_t)i * segs0);
+    const uint64_t so = triples[3 * i], dof = triples[3 * i + 1], len = triples[3 * i + 2];
+    if (so > src_cap || len > src_cap - so || dof > dst_cap || len > dst_cap - dof || len > 0xffffffffull) {
+      if (lane == 0 && s0 == 0) set_status(status, KVT_ERR_BLOCK_RANGE, i);
+      continue;
     }
-  } else {
-    for (uint32_t i = blockIdx.x * warps_per_cta + warp; i < n; i += gridDim.x * warps_per_cta) {
-      const uint64_t so = triples[3 * i], dof = triples[3 * i + 1], len = triples[3 * i + 2];
-      if (so > src_cap || len > src_cap - so || dof > dst_cap || len > dst_cap - dof || len > 0xffffffffull) {
-        if (lane == 0) set_status(status, KVT_ERR_BLOCK_RANGE, i);
-        continue;
-      }
-      copy_span(src + so, dst + dof, (uint32_t)len, lane, 32);
+    for (uint64_t off = (uint64_t)s0 * kCopySeg; off < len; off += (uint64_t)segs0 * kCopySeg) {
+      copy_span(src + so + off, dst + dof + off, (uint32_t)min((uint64_t)kCopySeg, len - off), lane, 32);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(512) kvt_copy_blocks_multi_kernel(const __grid_constant__ KvtCopyMulti p) {
+  const uint32_t warps_per_cta = blockDim.x >> 5;
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  // per tensor: segments of its first descriptor lay out its units (see kvt_copy_blocks_kernel)
+  uint32_t segs[KVT_COPY_MAX_TENSORS];
+  uint64_t ends[KVT_COPY_MAX_TENSORS];
+  uint64_t total = 0;
+#pragma unroll
+  for (uint32_t t = 0; t < KVT_COPY_MAX_TENSORS; ++t) {
+    segs[t] = 1;
+    if (t < p.n_tensors && p.first[t + 1] > p.first[t]) {
+      const uint64_t len0 = p.triples[3ull * p.first[t] + 2];
+      if (len0 > kCopySeg) segs[t] = (uint32_t)min((len0 + kCopySeg - 1) / kCopySeg, (uint64_t)65536);
+      total += (uint64_t)(p.first[t + 1] - p.first[t]) * segs[t];
+    }
+    ends[t] = total;
+  }
+  for (uint64_t u = (uint64_t)blockIdx.x * warps_per_cta + warp; u < total; u += (uint64_t)gridDim.x * warps_per_cta) {
+    uint32_t t = 0;
+#pragma unroll
+    for (uint32_t k = 0; k + 1 < KVT_COPY_MAX_TENSORS; ++k) t += (u >= ends[k]) ? 1u : 0u;
+    const uint64_t local = u - (t > 0 ? ends[t - 1] : 0);
+    const uint32_t i = p.first[t] + (uint32_t)(local / segs[t]);
+    const uint32_t s0 = (uint32_t)(local % segs[t]);
+    const uint64_t so = p.triples[3ull * i], dof = p.triples[3ull * i + 1], len = p.triples[3ull * i + 2];
+    if (so > p.src_cap[t] || len > p.src_cap[t] - so || dof > p.dst_cap[t] || len > p.dst_cap[t] - dof ||
+        len > 0xffffffffull) {
+      if (lane == 0 && s0 == 0) set_status(p.status, KVT_ERR_BLOCK_RANGE, i);
+      continue;
+    }
+    const char* src = reinterpret_cast<const char*>(p.src_base[t]) + so;
+    char* dst = reinterpret_cast<char*>(p.dst_base[t]) + dof;
+    for (uint64_t off = (uint64_t)s0 * kCopySeg; off < len; off += (uint64_t)segs[t] * kCopySeg) {
+      copy_span(src + off, dst + off, (uint32_t)min((uint64_t)kCopySeg, len - off), lane, 32);
     }
   }
 }
@@ -181,9 +220,20 @@ extern "C" int kvt_launch_copy_blocks(uint64_t src_base, uint64_t dst_base, cons
                                       uint64_t src_capacity, uint64_t dst_capacity, uint32_t* status,
                                       int grid_ctas, void* stream) {
   if (n == 0) return (int)cudaSuccess;
-  kvt_copy_blocks_kernel<<<pick_grid(grid_ctas), 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  // two CTAs of 512 threads per SM by default: a warp keeps 2 KiB in flight
+  kvt_copy_blocks_kernel<<<grid_ctas > 0 ? grid_ctas : 2 * pick_grid(0), 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const char*>(src_base), reinterpret_cast<char*>(dst_base), triples, n, src_capacity,
       dst_capacity, status);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int kvt_launch_copy_blocks_multi(const KvtCopyMulti* args, int grid_ctas, void* stream) {
+  if (args->n_tensors == 0 || args->n_tensors > KVT_COPY_MAX_TENSORS) return (int)cudaErrorInvalidValue;
+  if (args->first[args->n_tensors] == args->first[0]) return (int)cudaSuccess;
+  for (uint32_t t = 0; t < args->n_tensors; ++t)
+    if (args->first[t + 1] < args->first[t]) return (int)cudaErrorInvalidValue;
+  kvt_copy_blocks_multi_kernel<<<grid_ctas > 0 ? grid_ctas : 2 * pick_grid(0), 512, 0,
+                                 reinterpret_cast<cudaStream_t>(stream)>>>(*args);
   return (int)cudaGetLastError();
 }
 

@@ -153,7 +153,7 @@ void DeviceStage::enqueue(uint64_t src_base, uint64_t dst_base, const std::vecto
   int grid = grid_ctas;
   if (grid <= 0) {
     const double usage = env_kernel_copy_sm_usage();
-    grid = std::max(1, static_cast<int>(kvt_sm_count(device_) * usage));
+    grid = std::max(1, static_cast<int>(2 * kvt_sm_count(device_) * usage));
   }
   for (size_t off = 0; off < n; off += max_per_launch) {
     const uint32_t cnt = static_cast<uint32_t>(std::min(max_per_launch, n - off));
@@ -164,16 +164,17 @@ void DeviceStage::enqueue(uint64_t src_base, uint64_t dst_base, const std::vecto
 }
 
 void DeviceStage::launch_resident(uint64_t src_base, uint64_t dst_base, const uint64_t* d_triples, size_t n,
-                                  uint64_t src_cap, uint64_t dst_cap, int grid_ctas) {
+                                  uint64_t src_cap, uint64_t dst_cap, int grid_ctas, uint32_t* status) {
   if (n == 0) return;
+  uint32_t* st = status != nullptr ? status : d_status_;
   cuda_check(cudaSetDevice(device_), "cudaSetDevice");
   cudaStream_t s = static_cast<cudaStream_t>(stream_);
   const size_t max_per_launch = env_kernel_copy_max_block_num();
   int grid = grid_ctas;
-  if (grid <= 0) grid = std::max(1, static_cast<int>(kvt_sm_count(device_) * env_kernel_copy_sm_usage()));
+  if (grid <= 0) grid = std::max(1, static_cast<int>(2 * kvt_sm_count(device_) * env_kernel_copy_sm_usage()));
   for (size_t off = 0; off < n; off += max_per_launch) {
     const uint32_t cnt = static_cast<uint32_t>(std::min(max_per_launch, n - off));
-    cuda_check(kvt_launch_copy_blocks(src_base, dst_base, d_triples + off * 3, cnt, src_cap, dst_cap, d_status_, grid, s),
+    cuda_check(kvt_launch_copy_blocks(src_base, dst_base, d_triples + off * 3, cnt, src_cap, dst_cap, st, grid, s),
                "kvt_launch_copy_blocks");
   }
 }

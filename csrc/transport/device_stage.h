@@ -42,8 +42,10 @@ class DeviceStage {
   DeviceStage(const DeviceStage&) = delete;
   // Launch the copy over descriptors that already sit in device memory (uploaded by the caller and
   // ordered before this stream by an event); does not wait.
+  // `status` (device, 2 x u32) replaces the stage's own status words, so that several stages can report
+  // into one place that the caller reads back itself.
   void launch_resident(uint64_t src_base, uint64_t dst_base, const uint64_t* d_triples, size_t n, uint64_t src_cap,
-                       uint64_t dst_cap, int grid_ctas = 0);
+                       uint64_t dst_cap, int grid_ctas = 0, uint32_t* status = nullptr);
   // Enqueue the copy; does not wait.  host_side says which end is pinned host memory (HOST_NONE,
   // HOST_SRC, HOST_DST): with a host end the copy policy of the device may hand the list to the copy
   // engines (one cudaMemcpyAsync per descriptor, bounds checked here) instead of the kernel.

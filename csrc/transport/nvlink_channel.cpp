@@ -307,11 +307,34 @@ class NvlinkChannel : public IChannel {
     }
     const auto& addrs = ctx_->layer_data_address();
     RTASSERT(layer < addrs.size() && layer < dst_ptrs_.size());
+    if (generic_.size() <= KVT_COPY_MAX_TENSORS) {
+      // every tensor of the layer in one launch
+      KvtCopyMulti m{};
+      uint32_t nt = 0;
+      for (size_t t = 0; t < generic_.size(); ++t) {
+        if (generic_[t].empty()) continue;
+        m.src_base[nt] = addrs[layer][t];
+        m.dst_base[nt] = dst_ptrs_[layer][t];
+        m.src_cap[nt] = ctx_->tensor_capacity(t);
+        m.dst_cap[nt] = dst_.block_sizes.at(t) * static_cast<uint64_t>(dst_.layer_num_blocks);
+        m.first[nt] = static_cast<uint32_t>(generic_off_[t]);
+        m.first[nt + 1] = static_cast<uint32_t>(generic_off_[t] + generic_[t].size());
+        ++nt;
+      }
+      if (nt == 0) return;
+      m.n_tensors = nt;
+      m.triples = reinterpret_cast<const uint64_t*>(d_plan_);
+      m.status = d_status_;
+      const int grid = std::max(1, static_cast<int>(2 * kvt_sm_count(ctx_->device_id()) * env_kernel_copy_sm_usage()));
+      cuda_check(kvt_launch_copy_blocks_multi(&m, grid, st.stream()), "kvt_launch_copy_blocks_multi");
+      return;
+    }
     for (size_t t = 0; t < generic_.size(); ++t) {
       if (generic_[t].empty()) continue;
       const size_t dst_cap = dst_.block_sizes.at(t) * static_cast<size_t>(dst_.layer_num_blocks);
       const uint64_t* d = reinterpret_cast<const uint64_t*>(d_plan_) + generic_off_[t] * 3;
-      st.launch_resident(addrs[layer][t], dst_ptrs_[layer][t], d, generic_[t].size(), ctx_->tensor_capacity(t), dst_cap);
+      st.launch_resident(addrs[layer][t], dst_ptrs_[layer][t], d, generic_[t].size(), ctx_->tensor_capacity(t), dst_cap, 0,
+                         d_status_);
     }
   }
 
@@ -319,7 +342,7 @@ class NvlinkChannel : public IChannel {
     TimeWatch tw;
     cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
     fault_inject_throw();
-    if (fused_) {
+    {
       // one host wait for the batch: the other streams are joined into the first on the device, the
       // kernels' shared status words follow them, and the host waits for that copy alone
       cudaStream_t s0 = static_cast<cudaStream_t>(stages_[0]->stream());
@@ -330,11 +353,9 @@ class NvlinkChannel : public IChannel {
       memcpy(st, h_status_.data(), 8);
       if (st[0] != 0) {
         cudaMemset(d_status_, 0, 64);
-        throw KVTransferException(ErrorKind::CUDA, "transfer kernel reported status " + std::to_string(st[0]) +
-                                                       " detail " + std::to_string(st[1]));
+        throw KVTransferException(ErrorKind::CUDA, std::string(fused_ ? "transfer" : "copy") + " kernel reported status " +
+                                                       std::to_string(st[0]) + " detail " + std::to_string(st[1]));
       }
-    } else {
-      for (auto& s : stages_) s->sync();
     }
     std::ostringstream ss;
     ss << "Proto=nvlink,Path=" << (fused_ ? "fused" : "descriptors") << ",OriginSbNum=" << origin_blocks_

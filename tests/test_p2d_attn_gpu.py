@@ -337,6 +337,51 @@ def test_state_segments_and_copy_blocks(ops):
     assert status[0].item() == 1
 
 
+def test_copy_blocks_long_mixed_and_multi_tensor(ops):
+    """The descriptor copy splits long runs into 4 KiB segments laid out by the FIRST descriptor's
+    length: lists whose later entries are longer or shorter than the first, and several tensors with
+    their own bases in one launch, must still move exactly the listed bytes."""
+    st = torch.zeros(4, dtype=torch.int32, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator(device=DEV).manual_seed(3)
+    n = 3 << 20
+    for trip in ([(16, 64, 41984), (100000, 50000, 41984), (300000, 200000, 41984 * 3), (900000, 700000, 100)],
+                 [(0, 0, 100), (4096, 8192, 1 << 20), (2 << 20, 1200000, 4097)],
+                 [(48, 1, 65536 + 5)]):
+        a = torch.randint(0, 255, (n,), dtype=torch.uint8, device=DEV, generator=g)
+        b = torch.zeros(n, dtype=torch.uint8, device=DEV)
+        t = torch.tensor([x for tr in trip for x in tr], dtype=torch.int64, device=DEV)
+        ops.kvt_launch_copy_blocks(a.data_ptr(), b.data_ptr(), t.data_ptr(), len(trip), n, n, st.data_ptr(), 0, stream)
+        torch.cuda.synchronize()
+        assert st[0].item() == 0
+        want = torch.zeros_like(b)
+        for so, do, ln in trip:
+            want[do:do + ln] = a[so:so + ln]
+        assert torch.equal(b, want)
+    # three tensors, one launch; the second tensor's list is empty, the third has short runs
+    srcs = [torch.randint(0, 255, (1 << 20,), dtype=torch.uint8, device=DEV, generator=g) for _ in range(3)]
+    dsts = [torch.zeros(1 << 20, dtype=torch.uint8, device=DEV) for _ in range(3)]
+    lists = [[(0, 4096, 41984), (50000, 100000, 41984)], [], [(8, 24, 132 * 64), (9000, 20000, 132 * 64), (30000, 500000, 7)]]
+    flat = [x for lst in lists for tr in lst for x in tr]
+    first = [0, 2, 2, 5]
+    t = torch.tensor(flat, dtype=torch.int64, device=DEV)
+    ops.kvt_launch_copy_blocks_multi([x.data_ptr() for x in srcs], [x.data_ptr() for x in dsts], [1 << 20] * 3,
+                                     [1 << 20] * 3, first, t.data_ptr(), st.data_ptr(), 0, stream)
+    torch.cuda.synchronize()
+    assert st[0].item() == 0
+    for a, b, lst in zip(srcs, dsts, lists):
+        want = torch.zeros_like(b)
+        for so, do, ln in lst:
+            want[do:do + ln] = a[so:so + ln]
+        assert torch.equal(b, want)
+    # a descriptor outside its own tensor is reported with its index and skipped
+    t_bad = torch.tensor([0, 0, 64, 0, (1 << 20) - 8, 64], dtype=torch.int64, device=DEV)
+    ops.kvt_launch_copy_blocks_multi([srcs[0].data_ptr(), srcs[1].data_ptr()], [dsts[0].data_ptr(), dsts[1].data_ptr()],
+                                     [1 << 20] * 2, [1 << 20] * 2, [0, 1, 2], t_bad.data_ptr(), st.data_ptr(), 0, stream)
+    torch.cuda.synchronize()
+    assert st[0].item() == 1 and st[1].item() == 1
+
+
 def test_per_layer_launches_replay_from_a_cuda_graph(ops):
     """The launch is fixed-shape and touches no host state, so a step's per-layer launches can be
     captured once and replayed; new block tables reach the kernel through the plan buffer."""
