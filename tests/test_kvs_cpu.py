@@ -144,8 +144,8 @@ def test_tp2_needs_every_rank(store_name):
 def test_abort_mid_prefill_discards_unsealed_blocks(store_name):
     e = make_kvs("A", store_name, max_batched=16, extra={"kvs_abort_grace_s": 0.05})
     try:
-        e.add_request(make_req("a", 400, max_tokens=2))
-        time.sleep(0.05)
+        e.add_request(make_req("a", 960, max_tokens=2))     # 60 engine steps of 16 tokens: still prefilling below
+        time.sleep(0.02)
         e.abort_requests(["a"])
         out = e.wait_finished("a", 20)
         assert out is not None and out.finish_reason.name == "ABORT"
