@@ -59,12 +59,43 @@ class EngineCoreRequest(msgspec.Struct, omit_defaults=True):
     queue_server_address: Optional[str] = None
 
 
-class _NoTrace:
+class RequestTrace:
+    """Per-request KV timing marks and W3C trace context.
+
+    The scheduler half calls ``on_req_kv_start/end("load" | "save")`` around a request's KV I/O
+    (blade_kvt/hybrid_connector/__init__.py:1185-1186,1304,1345); backends that talk to a store ask
+    ``traceparent(op)`` for the header they hand over as request context
+    (blade_kvt/hybrid_connector/kvsbackend.py:403,481), so that the store's spans hang under the
+    request's trace.  Without an incoming ``traceparent`` header there is no context to propagate."""
+
+    def __init__(self, trace_headers: Optional[dict] = None):
+        self.headers = dict(trace_headers) if trace_headers else {}
+        self.marks: dict = {}          # "load" / "save" -> [start, end] (time.monotonic)
+
     def on_req_kv_start(self, kind: str) -> None:
-        pass
+        self.marks[kind] = [time.monotonic(), None]
 
     def on_req_kv_end(self, kind: str) -> None:
-        pass
+        m = self.marks.get(kind)
+        if m is not None and m[1] is None:
+            m[1] = time.monotonic()
+
+    def elapsed(self, kind: str) -> Optional[float]:
+        m = self.marks.get(kind)
+        return None if m is None or m[1] is None else m[1] - m[0]
+
+    def traceparent(self, op: str) -> Optional[str]:
+        """A child of the request's span, named by ``op``: same trace id, span id derived from (parent, op)."""
+        parent = self.headers.get("traceparent")
+        if not parent:
+            return None
+        parts = parent.split("-")
+        if len(parts) != 4 or len(parts[1]) != 32 or len(parts[2]) != 16:
+            return None
+        import hashlib
+
+        span = hashlib.blake2b(f"{parts[2]}/{op}".encode(), digest_size=8).hexdigest()
+        return f"{parts[0]}-{parts[1]}-{span}-{parts[3]}"
 
 
 class Request:
@@ -92,7 +123,7 @@ class Request:
         self.stop_reason: Any = None
         self._max_computed_tokens: Optional[int] = None
         self.skip_reading_prefix_cache = False
-        self.trace_wrapper = _NoTrace()
+        self.trace_wrapper = RequestTrace(trace_headers)
         self.block_hashes: list = []
 
     @classmethod

@@ -49,6 +49,7 @@ class KVSReqMeta:
     skip_blocks: int = 0       # load: blocks already present locally; save: blocks handled in earlier steps
     is_last_chunk: bool = False
     abort: bool = False        # save was aborted: drop what is not sealed
+    trace: Optional[str] = None  # W3C traceparent of this I/O (child of the request's span), if the request carries one
 
 
 @dataclasses.dataclass
@@ -107,6 +108,9 @@ class KVSBackend(HybridBackend):
         self._bound_meta = None
         self._nan_gate = None                 # concurrent Future of this step: resolves to the flag tensor or None
         self._nan_failed: set = set()
+        # request context of the last store operations, "reqid[;traceparent][;op=start|end]" as the reference
+        # hands it to its stores (kvsbackend.py:232-245,297-323); kept for logs and tests
+        self.request_contexts: deque = deque(maxlen=256)
 
     # ---- geometry shared by both halves --------------------------------------------------------------
     def _geometry(self):
@@ -176,7 +180,8 @@ class KVSBackend(HybridBackend):
         assert len(block_ids) == nblk
         self._engine.sched_discard_zero_block_ids(block_ids)
         self._loads.append(KVSReqMeta(request.request_id, False, list(request.prompt_token_ids[:upto]), list(block_ids),
-                                      skip_blocks=request.num_computed_tokens // self._bs))
+                                      skip_blocks=request.num_computed_tokens // self._bs,
+                                      trace=request.trace_wrapper.traceparent("kv_load")))
         return None   # the workers report LOAD_DONE with what they really loaded
 
     def _save_meta(self, reqid: str, scheduled: int) -> Optional[KVSReqMeta]:
@@ -197,7 +202,7 @@ class KVSBackend(HybridBackend):
             return None
         block_ids = self._engine.sched_get_kvblk_ids(reqid)[0][:done_blocks]
         return KVSReqMeta(reqid, True, list(req.prompt_token_ids[:done_blocks * self._bs]), list(block_ids),
-                          skip_blocks=prev, is_last_chunk=last)
+                          skip_blocks=prev, is_last_chunk=last, trace=req.trace_wrapper.traceparent("kv_save"))
 
     def build_backend_meta(self, sout: SchedulerOutput) -> BackendMeta:
         assert isinstance(sout, HCSchedOutput)
@@ -290,6 +295,7 @@ class KVSBackend(HybridBackend):
             if r.is_store:
                 continue
             st = self._store
+            self._note_context(r, None)
             keys = st.keys(r.token_ids, len(r.block_ids))
             slots = st.pin(keys)
             n = len(slots)
@@ -351,6 +357,9 @@ class KVSBackend(HybridBackend):
             lo = 0 if self._per_step else layer
             ev = st.save_layers(lo, layer + 1, blocks, slots, after=after)   # one launch for every request of the step
         work = list(self._step_saves)
+        if layer == 0 or last_layer:
+            for r, _, _, _ in work:
+                self._note_context(r, "start" if layer == 0 else "end")
         gate = self._nan_gate if last_layer else None
         if last_layer:
             self._step_saves = []
@@ -388,6 +397,15 @@ class KVSBackend(HybridBackend):
                     yield r.reqid
 
         return gen()
+
+    def _note_context(self, r: KVSReqMeta, op: Optional[str]) -> None:
+        ctx = r.reqid
+        if r.trace:
+            ctx += f";{r.trace}"
+            if op:
+                ctx += f";op={op}"
+        self.request_contexts.append(ctx)
+        logger.debug("kvs: %s %s", "save" if r.is_store else "load", ctx)
 
     def stop(self) -> None:
         if self._store is not None:

@@ -221,3 +221,32 @@ def test_nan_in_hidden_states_keeps_the_step_out_of_the_store(store_name, monkey
         assert cap["c"][0] == 96
     finally:
         e.shutdown()
+
+
+def test_trace_context_reaches_the_store_operations(store_name):
+    """A request that carries a W3C traceparent header has its save and its load tagged with child
+    spans of that trace (same trace id, another span id per operation), start and end marked."""
+    e = make_kvs("A", store_name)
+    try:
+        tp = "00-0af7651916cd43dd8448eb211c80319c-b7ad6b7169203331-01"
+        for rid in ("a", "b"):
+            req = make_req(rid, 100, max_tokens=2)
+            req.trace_headers = {"traceparent": tp}
+            e.add_request(req)
+            assert e.wait_finished(rid, 30) is not None
+            assert wait_free(e, 63) == 63
+        ctx = list(e.workers[0].connector._worker._backend.request_contexts)
+        saves = [c for c in ctx if c.startswith("a;")]
+        assert len(saves) == 2 and saves[0].endswith(";op=start") and saves[1].endswith(";op=end")
+        child = saves[0].split(";")[1]
+        ver, trace_id, span, flags = child.split("-")
+        assert (ver, trace_id, flags) == ("00", "0af7651916cd43dd8448eb211c80319c", "01")
+        assert len(span) == 16 and span != "b7ad6b7169203331"
+        loads = [c for c in ctx if c.startswith("b;") and "op=" not in c]
+        assert len(loads) == 1 and loads[0].split(";")[1].split("-")[1] == trace_id
+        assert loads[0].split(";")[1].split("-")[2] not in (span, "b7ad6b7169203331")     # kv_load is its own span
+        # requests without the header are tagged with their id alone
+        run(e, "c", 40)
+        assert "c" in [c for c in e.workers[0].connector._worker._backend.request_contexts if c.startswith("c")]
+    finally:
+        e.shutdown()
