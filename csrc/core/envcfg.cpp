@@ -93,6 +93,7 @@ int env_use_tma() { return (int)anyint("BLLM_KVTRANS_USE_TMA", 1); }
 bool env_copy_profile_enable() { return anyint("BLLM_KVTRANS_COPY_PROFILE_ENABLE", 1) != 0; }
 size_t env_copy_memcpy_max_blocks() { return (size_t)posint("BLLM_KVTRANS_COPY_MEMCPY_MAX_BLOCKS", 16); }
 size_t env_copy_memcpy_threshold_bytes() { return (size_t)posint("BLLM_KVTRANS_COPY_MEMCPY_BLOCK_THRESHOLD_BYTES", 256 * 1024); }
+bool env_device_timestamps() { return anyint("BLLM_KVTRANS_DEVICE_TIMESTAMPS", 0) != 0; }
 int env_copy_path() { return (int)anyint("BLLM_KVTRANS_COPY_PATH", 0); }
 
 double env_kernel_copy_sm_usage() noexcept {

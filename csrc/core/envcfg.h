@@ -65,6 +65,8 @@ bool env_copy_profile_enable();
 size_t env_copy_memcpy_max_blocks();
 size_t env_copy_memcpy_threshold_bytes();
 int env_copy_path();
+// NVLink channel: stamp the GPU timer at the start and the end of every batch and report DeviceUs in the flush line.
+bool env_device_timestamps();
 
 void envcfg_reset_for_test();
 std::string envcfg_dump();   // every setting resolved so far, one key=value per line

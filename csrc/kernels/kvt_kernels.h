@@ -220,6 +220,10 @@ int kvt_launch_mc_fanout(const KvtMcFanout* args, int grid_ctas, void* stream);
 int kvt_launch_wait_flag(const uint64_t* flag, uint64_t value, uint64_t timeout_ns,
                          uint32_t* status, void* stream);
 int kvt_launch_set_flag(uint64_t* flag, uint64_t value, void* stream);
+// Writes the GPU's nanosecond timer (%globaltimer) to *slot (device or mapped host memory) when the
+// stream reaches this point: device-side timestamps around a batch, comparable across the GPUs of a
+// node, without CUDA events.
+int kvt_launch_stamp(uint64_t* slot, void* stream);
 
 // ---- peer memory / topology ---------------------------------------------------------------
 int kvt_device_count(void);

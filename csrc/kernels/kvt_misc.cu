@@ -243,6 +243,18 @@ extern "C" int kvt_launch_wait_flag(const uint64_t* flag, uint64_t value, uint64
   return (int)cudaGetLastError();
 }
 
+__global__ void kvt_stamp_kernel(uint64_t* slot) {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  *slot = t;
+}
+
+extern "C" int kvt_launch_stamp(uint64_t* slot, void* stream) {
+  if (slot == nullptr || (reinterpret_cast<uintptr_t>(slot) & 7u) != 0) return (int)cudaErrorInvalidValue;
+  kvt_stamp_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(slot);
+  return (int)cudaGetLastError();
+}
+
 extern "C" int kvt_launch_set_flag(uint64_t* flag, uint64_t value, void* stream) {
   kvt_set_flag_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(flag, value);
   return (int)cudaGetLastError();

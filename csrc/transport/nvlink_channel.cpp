@@ -191,6 +191,7 @@ class NvlinkChannel : public IChannel {
       cuda_check(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate");
       plan_event_ = ev;
     }
+    stamp_start(s0);
     cuda_check(cudaEventRecord(static_cast<cudaEvent_t>(plan_event_), s0), "cudaEventRecord");
     for (size_t i = 1; i < stages_.size(); ++i) stages_[i]->wait_event(plan_event_);
     fused_ = true;
@@ -247,6 +248,7 @@ class NvlinkChannel : public IChannel {
       cuda_check(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate");
       plan_event_ = ev;
     }
+    stamp_start(s0);
     cuda_check(cudaEventRecord(static_cast<cudaEvent_t>(plan_event_), s0), "cudaEventRecord");
     for (size_t i = 1; i < stages_.size(); ++i) stages_[i]->wait_event(plan_event_);
   }
@@ -347,10 +349,16 @@ class NvlinkChannel : public IChannel {
       // kernels' shared status words follow them, and the host waits for that copy alone
       cudaStream_t s0 = static_cast<cudaStream_t>(stages_[0]->stream());
       for (size_t i = 1; i < stages_.size(); ++i) stages_[0]->wait_event(stages_[i]->record_done());
-      cuda_check(cudaMemcpyAsync(h_status_.data(), d_status_, 8, cudaMemcpyDeviceToHost, s0), "cudaMemcpyAsync(status)");
+      if (stamps_) cuda_check(kvt_launch_stamp(reinterpret_cast<uint64_t*>(d_status_) + 2, s0), "kvt_launch_stamp");
+      cuda_check(cudaMemcpyAsync(h_status_.data(), d_status_, 24, cudaMemcpyDeviceToHost, s0), "cudaMemcpyAsync(status)");
       cuda_check(cudaStreamSynchronize(s0), "cudaStreamSynchronize");
       uint32_t st[2];
       memcpy(st, h_status_.data(), 8);
+      if (stamps_) {
+        uint64_t t[2];
+        memcpy(t, h_status_.data() + 8, 16);
+        device_us_ = t[1] >= t[0] ? static_cast<int64_t>((t[1] - t[0]) / 1000) : -1;
+      }
       if (st[0] != 0) {
         cudaMemset(d_status_, 0, 64);
         throw KVTransferException(ErrorKind::CUDA, std::string(fused_ ? "transfer" : "copy") + " kernel reported status " +
@@ -361,6 +369,7 @@ class NvlinkChannel : public IChannel {
     ss << "Proto=nvlink,Path=" << (fused_ ? "fused" : "descriptors") << ",OriginSbNum=" << origin_blocks_
        << ",MergedSbNum=" << merged_blocks_ << ",BytesPerLayer=" << moved_bytes_per_layer_
        << ",Tiles=" << plan_.total_tiles << ",FlushUs=" << tw.get_elapse_us();
+    if (stamps_) ss << ",DeviceUs=" << device_us_;   // GPU timer from the plan upload to the last kernel of the batch
     out = ss.str();
     generic_.clear();
   }
@@ -381,6 +390,10 @@ class NvlinkChannel : public IChannel {
   }
 
  private:
+  void stamp_start(cudaStream_t s0) {
+    if (stamps_) cuda_check(kvt_launch_stamp(reinterpret_cast<uint64_t*>(d_status_) + 1, s0), "kvt_launch_stamp");
+  }
+
   void ensure_layer_arrays() {
     if (d_src_layers_.p != nullptr) return;
     std::vector<uint64_t> src, dst;
@@ -424,7 +437,9 @@ class NvlinkChannel : public IChannel {
   void* plan_event_{nullptr};
   DevArray<uint64_t> d_src_layers_, d_dst_layers_;
   DevArray<TensorMapBytes> d_src_maps_, d_dst_maps_;
-  uint32_t* d_status_{nullptr};
+  uint32_t* d_status_{nullptr};   // 64 bytes: [0] code, [1] detail, bytes 8..15 start stamp, bytes 16..23 end stamp
+  const bool stamps_{env_device_timestamps()};
+  int64_t device_us_{-1};
   PinnedBuffer h_status_;
   // generic path
   std::vector<std::vector<Triple>> generic_;

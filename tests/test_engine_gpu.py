@@ -247,3 +247,40 @@ def test_layer_overlap_waits_for_the_layer_event():
             assert int(v[4:7].min()) == int(v[4:7].max()) == (layer + 1) * 257
     finally:
         srv.stop()
+
+
+_STAMP_SCRIPT = r"""
+import torch
+from llumnix_kv_b200.kv_transfer_impl import KVTransferClient, KVTransferProtocolType as PT, KVTransferServer
+from llumnix_kv_b200.ops.layouts import AttnLayout, CacheShape
+lay = AttnLayout(CacheShape.FLASH, 48, 16, 8, 128, 2)
+src = [lay.alloc("cuda:0", "normal", seed=i) for i in range(3)]
+dst = [lay.alloc("cuda:0") for _ in range(3)]
+srv = KVTransferServer("D|0|1", 1, 0, 0, lay.block_bytes, lay.token_bytes, "fake://", dst, [PT.NVLINK], num_kv_heads=8, cache_shape=2)
+cli = KVTransferClient("P|0|1", 1, 0, 0, lay.block_bytes, lay.token_bytes, "fake://", src, [PT.NVLINK], num_kv_heads=8, cache_shape=2)
+cli.submit_req_send2("D|0|1", 0, "r", 0, 40, True, [3, 5, 7], [2, 4, 6], srv.worker_info(), stepid=1)
+cli.start_send_step(1, 1)
+for layer in range(3):
+    cli.record_event(layer, None)
+cli.flush_send_step()
+cli.drain()
+torch.cuda.synchronize()
+assert torch.equal(dst[0].view(-1)[:16], dst[0].view(-1)[:16])
+srv.stop()
+"""
+
+
+def test_device_timestamps_in_the_flush_metrics():
+    """With BLLM_KVTRANS_DEVICE_TIMESTAMPS=1 the NVLink channel stamps the GPU timer at the start and the
+    end of a batch and reports the difference as DeviceUs in its metrics line."""
+    import re
+    import subprocess
+    import sys
+
+    env = dict(os.environ, BLLM_KVTRANS_DEVICE_TIMESTAMPS="1", LLMOPS_CPP_MIN_LOG_LEVEL="0")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", _STAMP_SCRIPT], cwd=root, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    m = re.search(r"SendStubMetrics\..*Proto=nvlink,Path=fused.*DeviceUs=(-?\d+)", r.stderr)
+    assert m is not None, r.stderr[-2000:]
+    assert 0 <= int(m.group(1)) < 1_000_000
