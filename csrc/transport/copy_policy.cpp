@@ -70,7 +70,7 @@ float time_pass(Scratch& s, int device, CopyDir dir, CopyPath path, size_t n, si
       s.h_triples[3 * i + 2] = len;
     }
     if (cudaMemcpyAsync(s.d_triples, s.h_triples, n * 24, cudaMemcpyHostToDevice, s.stream) != cudaSuccess) return -1.f;
-    const int grid = std::max(1, static_cast<int>(2 * kvt_sm_count(device) * env_kernel_copy_sm_usage()));
+    const int grid = std::max(1, static_cast<int>(0.5 * kvt_sm_count(device) * env_kernel_copy_sm_usage()));   // as DeviceStage::enqueue
     if (kvt_launch_copy_blocks(src, dst, s.d_triples, static_cast<uint32_t>(n), kScratch, kScratch, s.d_status, grid,
                                s.stream) != 0)
       return -1.f;

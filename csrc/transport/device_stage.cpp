@@ -153,7 +153,9 @@ void DeviceStage::enqueue(uint64_t src_base, uint64_t dst_base, const std::vecto
   int grid = grid_ctas;
   if (grid <= 0) {
     const double usage = env_kernel_copy_sm_usage();
-    grid = std::max(1, static_cast<int>(2 * kvt_sm_count(device_) * usage));
+    // a copy with a host end is PCIe-bound: half a CTA per SM keeps the link full (measured 33 GB/s through the
+    // SHM transport against 28 with two per SM) and leaves the SMs to the forward pass
+    grid = std::max(1, static_cast<int>((host_side != HOST_NONE ? 0.5 : 2.0) * kvt_sm_count(device_) * usage));
   }
   for (size_t off = 0; off < n; off += max_per_launch) {
     const uint32_t cnt = static_cast<uint32_t>(std::min(max_per_launch, n - off));

@@ -191,11 +191,17 @@ class PDBenchPair:
                                f"status={self.status_host.tolist()}")
 
     # ---- the same step through the engine's public API ---------------------------------------
-    def setup_engine(self) -> None:
+    def setup_engine(self, transport: str = "nvlink") -> None:
         """KVTransferServer on the decode rank, KVTransferClient on the prefill rank, NVLink
-        transport; the WorkerInfo string travels the way a decode engine hands it to a prefill
-        engine inside a request."""
+        transport (or one of the host-staged ones: "shm", "tcp"); the WorkerInfo string travels the
+        way a decode engine hands it to a prefill engine inside a request."""
         from .kv_transfer_impl import KVTransferClient, KVTransferProtocolType as PT, KVTransferServer
+
+        proto = {"nvlink": PT.NVLINK, "shm": PT.SHM, "tcp": PT.TCP}[transport]
+        if transport != "nvlink":
+            self.transport_name = {"shm": "host-staged: gather kernel -> pinned POSIX shm -> scatter kernel (SHM transport)",
+                                   "tcp": "host-staged: gather kernel -> pinned host -> TCP loopback -> pinned host -> "
+                                          "scatter kernel (TCP transport, the reference's one-box path)"}[transport]
 
         pair = self._pair_id() if self.is_sender else self.rank - self.n_pairs
         self.dst_inst = f"D{pair}|0|1"
@@ -205,7 +211,7 @@ class PDBenchPair:
             lb = self.dst_l.layer_bytes
             layers = [self.dst[i * lb:(i + 1) * lb] for i in range(self.n_layers)]
             self.srv = KVTransferServer(self.dst_inst, 1, 0, 0, self.dst_l.block_bytes, self.dst_l.token_bytes, "fake://",
-                                        layers, [PT.NVLINK], num_kv_heads=KV_HEADS, cache_shape=int(self.dst_l.shape))
+                                        layers, [proto], num_kv_heads=KV_HEADS, cache_shape=int(self.dst_l.shape))
             winfo = self.srv.worker_info()
         if self.world > 1:
             import torch.distributed as dist
@@ -219,7 +225,7 @@ class PDBenchPair:
             lb = self.src_l.layer_bytes
             layers = [self.src[i * lb:(i + 1) * lb] for i in range(self.n_layers)]
             self.cli = KVTransferClient(f"P{pair}|0|1", 1, 0, 0, self.src_l.block_bytes, self.src_l.token_bytes, "fake://",
-                                        layers, [PT.NVLINK], num_kv_heads=KV_HEADS, cache_shape=int(self.src_l.shape))
+                                        layers, [proto], num_kv_heads=KV_HEADS, cache_shape=int(self.src_l.shape))
         self.engine_seq = 0
         self.engine_h2d_bytes = self.h2d_bytes_per_step
         self.engine_d2h_bytes = 8      # the channel reads its two status words back before it reports a batch done
