@@ -57,6 +57,8 @@ def parse_args():
     ap.add_argument("--graph", action="store_true",
                     help="kernel-only number: replay each step's per-layer launches from a CUDA graph")
     ap.add_argument("--e2e-only", action="store_true")
+    ap.add_argument("--layers-per-launch", type=int, default=1,
+                    help="kernel-only number: layers moved by one launch (1 = the per-layer flow of save_kv_layer)")
     ap.add_argument("--transport", default="nvlink", choices=["nvlink", "shm", "tcp"],
                     help="p2d mode, end to end through the engine: the NVLink transport (default) or one of the host-staged "
                          "fallbacks (1 GPU, same layout on both sides, end-to-end number only)")
@@ -274,6 +276,8 @@ def main():
                        n_layers=args.layers, use_tma=not args.no_tma, grid=args.grid, n_streams=args.streams,
                        **({"dst_shape": _CS.FLASH} if staged else {}))   # the byte-range transports keep the layout
 
+    pair.layers_per_launch = args.layers_per_launch
+
     def barrier():
         if world > 1:
             dist.barrier()
@@ -350,7 +354,9 @@ def main():
                        "layers": args.layers, "l2": f"inputs larger than L2: {pair.slot_bytes >> 20} MiB per step, "
                                                     f"{args.slots} slots cycled",
                        "transport": pair.transport_name,
-                       "launch": "cuda graph replay" if args.graph else "one launch per layer from the host",
+                       "launch": "cuda graph replay" if args.graph else (
+                           "one launch per layer from the host" if args.layers_per_launch == 1 else
+                           f"one launch per {args.layers_per_launch} layers from the host"),
                        "scaling_note": "N=1 is a same-GPU loopback bounded by HBM; N>=2 are N/2 one-directional "
                                        "NVLink pairs bounded by 770 GB/s measured per direction: compare N=2,4,8 "
                                        "with one another"},
@@ -361,7 +367,10 @@ def main():
             "e2e": {"value": round(agg(ms_e2e), 2), "unit": "GB/s", "ms_per_step": round(ms_e2e / args.steps, 4),
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "api": e2e_api,
                     "clocks": clocks_e2e},
-            "gpu_launches": pair.launches_per_step * args.steps * (1 if args.e2e_only else 2) + args.steps,
+            # kernel-only region: one launch per --layers-per-launch layers; end-to-end region: one per layer plus
+            # the plan upload's copy; both regions are timed unless --e2e-only
+            "gpu_launches": ((0 if args.e2e_only else -(-pair.launches_per_step // args.layers_per_launch)) +
+                             pair.launches_per_step) * args.steps + args.steps,
         }
         print(json.dumps(out))
     if world > 1:

@@ -131,8 +131,9 @@ class PDBenchPair:
         self.touched.add(i % self.slots)
         self._fan_out()
         lanes = [self.stream] + self.side
-        for layer in range(self.n_layers):
-            self.xfer.launch(plan, layer, layer + 1, stream=lanes[layer % len(lanes)], grid=self.grid)
+        step = max(1, int(getattr(self, "layers_per_launch", 1)))
+        for k, layer in enumerate(range(0, self.n_layers, step)):
+            self.xfer.launch(plan, layer, min(layer + step, self.n_layers), stream=lanes[k % len(lanes)], grid=self.grid)
         self._fan_in()
 
     def build_graphs(self) -> None:
