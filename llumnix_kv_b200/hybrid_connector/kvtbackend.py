@@ -227,6 +227,36 @@ def extract_layer_index(layer_name: str) -> int:
     return int(nums[0])
 
 
+def turboquant_last_dim_bytes(packed_key_dim: int, head_size: int, fast: bool) -> int:
+    """Bytes of one (token, head) row of a TurboQuant cache: the packed indices plus the per-row scale
+    block (one fp16 per 128 dims in the fast variant, 16 bytes otherwise;
+    blade_kvt/hybrid_connector/kvtbackend.py:122-139)."""
+    return packed_key_dim + (head_size // 128 * 2 if fast else 16)
+
+
+def resolve_raw_cache_tensors(kv_caches: dict) -> dict:
+    """Cache objects that wrap views of one raw buffer -> that buffer as a flat int8 tensor.
+
+    A TurboQuant cache hands the connector an object whose ``key_cache.indices`` and
+    ``value_cache.indices`` are slices of one allocation ``[blocks, 2, block_size, heads * row_bytes]``;
+    the transfer moves raw bytes, so it wants the allocation itself
+    (blade_kvt/hybrid_connector/kvtbackend.py:141-171).  Plain tensors pass through."""
+    import torch
+
+    out = {}
+    for name, cache in kv_caches.items():
+        key, val = getattr(cache, "key_cache", None), getattr(cache, "value_cache", None)
+        if isinstance(cache, torch.Tensor) or key is None or val is None:
+            out[name] = cache
+            continue
+        ks, vs = key.indices.untyped_storage(), val.indices.untyped_storage()
+        assert ks.data_ptr() == vs.data_ptr(), f"layer {name}: key and value indices do not share one allocation"
+        raw = torch.tensor([], dtype=torch.int8, device=key.indices.device)
+        raw.set_(ks, 0, (ks.nbytes(),))
+        out[name] = raw
+    return out
+
+
 def flatten_cache(kv_caches: dict) -> list:
     """layer index -> [cache tensors of that layer] (sparse-MLA models register two per layer)."""
     by_index: dict = defaultdict(list)
@@ -243,6 +273,7 @@ def build_kvt_args(backend: "HybridBackend", kv_caches: dict, tp_rank: int) -> d
     mc, cc = cfg.model_config, cfg.cache_config
     tp = cfg.parallel_config.tensor_parallel_size
     dp = cfg.parallel_config.data_parallel_rank
+    kv_caches = resolve_raw_cache_tensors(kv_caches)
     layers = flatten_cache(kv_caches)
     if backend.is_hybrid:
         # Several logical layers (one GDN layer of each group and one attention layer) share a

@@ -153,3 +153,30 @@ def test_backend_selection_table():
         pick("v6d_object+kvt", "kv_consumer")
     with pytest.raises(ValueError):
         pick("nope", "kv_both")
+
+
+def test_wrapped_cache_objects_resolve_to_their_raw_buffer():
+    """A TurboQuant-style cache object (key / value index views of one allocation) is registered as the
+    flat int8 view of that allocation; plain tensors pass through; row size helper."""
+    import types
+
+    import torch
+
+    from llumnix_kv_b200.hybrid_connector.kvtbackend import resolve_raw_cache_tensors, turboquant_last_dim_bytes
+
+    raw = torch.arange(4 * 2 * 8 * 6, dtype=torch.int8).view(4, 2, 8, 6)
+    wrapped = types.SimpleNamespace(key_cache=types.SimpleNamespace(indices=raw[:, 0]),
+                                    value_cache=types.SimpleNamespace(indices=raw[:, 1]))
+    plain = torch.zeros(16, dtype=torch.bfloat16)
+    out = resolve_raw_cache_tensors({"model.layers.0.attn": wrapped, "model.layers.1.attn": plain})
+    got = out["model.layers.0.attn"]
+    assert got.dtype == torch.int8 and got.numel() == raw.numel() and got.data_ptr() == raw.data_ptr()
+    assert torch.equal(got, raw.reshape(-1))
+    assert out["model.layers.1.attn"] is plain
+    other = torch.zeros(4, 8, 6, dtype=torch.int8)
+    bad = types.SimpleNamespace(key_cache=types.SimpleNamespace(indices=raw[:, 0]), value_cache=types.SimpleNamespace(indices=other))
+    import pytest
+    with pytest.raises(AssertionError):
+        resolve_raw_cache_tensors({"l.0": bad})
+    assert turboquant_last_dim_bytes(64, 128, fast=True) == 66 and turboquant_last_dim_bytes(64, 256, fast=True) == 68
+    assert turboquant_last_dim_bytes(64, 128, fast=False) == 80
