@@ -852,6 +852,7 @@ def mla_fanout_bandwidth(K, rank: int, world: int, dev, tokens: int = 32768, n_l
                 members; every member relays its share the same way and signals in its own completion
                 word; everybody waits for all words.  No member receives more than 1 + 1/k copies.
     """
+    import random
     import struct
 
     import torch.distributed as dist
@@ -872,7 +873,7 @@ def mla_fanout_bandwidth(K, rank: int, world: int, dev, tokens: int = 32768, n_l
     bounds = [n_blk * j // k for j in range(k + 1)]          # member j (rank j + 1) relays blocks [bounds[j], bounds[j + 1])
     share_max = max(bounds[j + 1] - bounds[j] for j in range(k))
     d_group = dist.new_group(list(range(1, world)))
-    rng = __import__("random").Random(23)
+    rng = random.Random(23)
     sb = rng.sample(range(num_blocks), n_blk)
     db = rng.sample(range(num_blocks), n_blk)
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)

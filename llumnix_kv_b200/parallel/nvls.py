@@ -25,6 +25,7 @@ alive.  Only stores are multicast; nothing loads through the multicast address.
 """
 from __future__ import annotations
 
+import collections
 from typing import Optional, Sequence
 
 import torch
@@ -72,7 +73,7 @@ class MulticastKVCache:
         self._counter = torch.zeros(1, dtype=torch.int32, device=dev)
         self._ops = load_ops()
         self._closed = False
-        self._keep = __import__("collections").deque(maxlen=256)
+        self._keep = collections.deque(maxlen=256)
 
     # ---- the member that received the blocks -----------------------------------------------------------
     def _ids(self, block_ids) -> torch.Tensor:
