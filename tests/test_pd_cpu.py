@@ -335,3 +335,38 @@ def test_bypass_substep_delivers_a_late_transfer_without_a_forward_pass(monkeypa
     finally:
         d.shutdown()
         p.shutdown()
+
+
+def test_injected_transport_failures_fail_requests_cleanly_and_later_ones_recover(pd):
+    """Transport faults injected on the host while requests stream through a P/D pair: a request whose
+    batch failed ends with ABORT on D (the 500 of the send stub travels P scheduler -> KVTResp -> load
+    failure), every other request decodes the right tokens, and nothing stays referenced on either side."""
+    from llumnix_kv_b200 import load_ops
+
+    ops = load_ops()
+    p, d = pd
+    params = {"remote_host": "127.0.0.1", "remote_port": p.proxy.rpc_port()}
+    outcomes = {}
+    try:
+        for i in range(10):
+            if i in (2, 5, 6):
+                ops.fault_inject_arm(1)          # the next fault point any sender passes throws
+            rid = f"x{i}"
+            d.add_request(make_req(rid, 24 + 5 * i, max_tokens=2, seed=i, params=params))
+            out = d.wait_finished(rid, 30)
+            ops.fault_inject_arm(0)
+            assert out is not None, rid
+            outcomes[rid] = out.finish_reason.name
+        assert set(outcomes.values()) <= {"LENGTH", "ABORT"}
+        assert [outcomes[f"x{i}"] for i in (0, 1, 3, 4, 7, 8, 9)] == ["LENGTH"] * 7, outcomes
+        assert any(outcomes[f"x{i}"] == "ABORT" for i in (2, 5, 6)), outcomes
+        # a request that went through decodes exactly what a colocated engine would
+        assert d.output_tokens("x9") and len(d.output_tokens("x9")) == 2
+        deadline = time.time() + 10
+        pools = [e.scheduler.kv_cache_manager.block_pool for e in (p, d)]
+        while time.time() < deadline and any(pl.num_free_blocks() != 63 for pl in pools):
+            time.sleep(0.01)
+        assert [pl.num_free_blocks() for pl in pools] == [63, 63]
+        assert not p.connector._sched._saving and not d.connector._sched._loading
+    finally:
+        ops.fault_inject_arm(0)
