@@ -208,11 +208,12 @@ void bind_kernels(py::module_& m) {
       "kvt_launch_copy_blocks_multi",
       [](const std::vector<uint64_t>& src_bases, const std::vector<uint64_t>& dst_bases,
          const std::vector<uint64_t>& src_caps, const std::vector<uint64_t>& dst_caps, const std::vector<uint32_t>& first,
-         uint64_t triples, uint64_t status, int grid, uint64_t stream) {
+         const std::vector<uint32_t>& count, uint64_t triples, uint64_t status, int grid, uint64_t stream,
+         uint32_t bulk_rounds) {
         const size_t nt = src_bases.size();
         if (nt == 0 || nt > KVT_COPY_MAX_TENSORS || dst_bases.size() != nt || src_caps.size() != nt ||
-            dst_caps.size() != nt || first.size() != nt + 1)
-          throw std::invalid_argument("kvt_launch_copy_blocks_multi: 1..8 tensors, first has one entry more");
+            dst_caps.size() != nt || first.size() != nt || count.size() != nt)
+          throw std::invalid_argument("kvt_launch_copy_blocks_multi: 1..8 entries, every list of that length");
         KvtCopyMulti a{};
         for (size_t t = 0; t < nt; ++t) {
           a.src_base[t] = src_bases[t];
@@ -220,15 +221,22 @@ void bind_kernels(py::module_& m) {
           a.src_cap[t] = src_caps[t];
           a.dst_cap[t] = dst_caps[t];
           a.first[t] = first[t];
+          a.count[t] = count[t];
         }
-        a.first[nt] = first[nt];
         a.n_tensors = static_cast<uint32_t>(nt);
         a.triples = reinterpret_cast<const uint64_t*>(triples);
         a.status = reinterpret_cast<uint32_t*>(status);
-        check_cuda(kvt_launch_copy_blocks_multi(&a, grid, reinterpret_cast<void*>(stream)), "kvt_launch_copy_blocks_multi");
+        if (bulk_rounds > 0) {
+          check_cuda(kvt_launch_copy_blocks_bulk(&a, bulk_rounds, grid, reinterpret_cast<void*>(stream)),
+                     "kvt_launch_copy_blocks_bulk");
+        } else {
+          check_cuda(kvt_launch_copy_blocks_multi(&a, grid, reinterpret_cast<void*>(stream)), "kvt_launch_copy_blocks_multi");
+        }
       },
       py::arg("src_bases"), py::arg("dst_bases"), py::arg("src_caps"), py::arg("dst_caps"), py::arg("first"),
-      py::arg("triples"), py::arg("status"), py::arg("grid"), py::arg("stream"));
+      py::arg("count"), py::arg("triples"), py::arg("status"), py::arg("grid"), py::arg("stream"),
+      py::arg("bulk_rounds") = 0);
+  m.def("kvt_bulk_rounds", &kvt_bulk_rounds, py::arg("first_len"), py::arg("max_len"));
 
   m.def(
       "kvt_launch_mc_fanout",

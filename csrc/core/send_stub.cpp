@@ -172,11 +172,18 @@ struct KvSendStub::Impl {
     const bool by_record = ch->device_ordered();
     // a frozen step has nothing to wait for: let the channel move all layers in one go
     const bool whole = batch.step->frozen && ch->send_layers(start_layer, num_layers, batch.step.get());
-    for (uint32_t i = start_layer; i < num_layers && !whole; ++i) {
+    for (uint32_t i = start_layer; i < num_layers && !whole;) {
       TimeWatch w;
       if (by_record) batch.step->wait_layer_recorded(i); else batch.step->wait_layer_ready(i);
       wait_us += w.get_elapse_us();
-      ch->send_data(i, batch.step.get());  // may be asynchronous
+      if (by_record) {
+        // layers recorded while the sender was busy go out together where the channel can do that
+        const uint32_t ready = std::min<uint32_t>(num_layers, std::max<uint32_t>(i + 1, batch.step->layers_recorded()));
+        i += static_cast<uint32_t>(ch->send_range(i, ready, batch.step.get()));
+      } else {
+        ch->send_data(i, batch.step.get());  // may be asynchronous
+        ++i;
+      }
     }
     (void)device_planned;
     fault_inject_throw();

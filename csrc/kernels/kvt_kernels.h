@@ -148,21 +148,30 @@ int kvt_launch_copy_blocks(uint64_t src_base, uint64_t dst_base, const uint64_t*
                            uint32_t n, uint64_t src_capacity, uint64_t dst_capacity,
                            uint32_t* status, int grid_ctas, void* stream);
 
-// The same copy over up to KVT_COPY_MAX_TENSORS tensor pairs in ONE launch: descriptors
-// [first[t], first[t+1]) of `triples` are relative to src_base[t] / dst_base[t].  A layer of a
-// multi-tensor cache (MLA latent + indexer keys, hybrid groups) then costs one launch, not one per tensor.
+// The same copy over up to KVT_COPY_MAX_TENSORS tensor pairs in ONE launch: entry e moves descriptors
+// [first[e], first[e] + count[e]) of `triples`, relative to src_base[e] / dst_base[e].  Entries may
+// share a descriptor range: the tensors of one layer (MLA latent + indexer keys, hybrid groups) cost
+// one launch instead of one each, and so do several layers whose pages use the same descriptors.
 #define KVT_COPY_MAX_TENSORS 8
 typedef struct KvtCopyMulti {
   uint64_t src_base[KVT_COPY_MAX_TENSORS];
   uint64_t dst_base[KVT_COPY_MAX_TENSORS];
   uint64_t src_cap[KVT_COPY_MAX_TENSORS];
   uint64_t dst_cap[KVT_COPY_MAX_TENSORS];
-  uint32_t first[KVT_COPY_MAX_TENSORS + 1];
+  uint32_t first[KVT_COPY_MAX_TENSORS];
+  uint32_t count[KVT_COPY_MAX_TENSORS];
   uint32_t n_tensors;
   const uint64_t* triples;     // device
   uint32_t* status;            // device: [0] first error code, [1] descriptor index
 } KvtCopyMulti;
 int kvt_launch_copy_blocks_multi(const KvtCopyMulti* args, int grid_ctas, void* stream);
+// The same, moved by the TMA engine: runs made of whole 16-byte words at 16-byte aligned addresses go
+// through shared memory as untiled bulk copies of 8 KiB (one thread per CTA issues them, four in
+// flight per CTA), the rest through the SIMT warps.  `rounds` = kvt_bulk_rounds(length of the first
+// descriptor, length of the longest) maximised over the entries: 1 when the descriptors of an entry
+// have one length (pages of a tensor).
+uint32_t kvt_bulk_rounds(uint64_t first_len, uint64_t max_len);
+int kvt_launch_copy_blocks_bulk(const KvtCopyMulti* args, uint32_t rounds, int grid_ctas, void* stream);
 
 // ---- the same copy for callers that must not allocate --------------------------------------
 // This entry point has no counterpart in the reference.  It exists for callers that cannot

@@ -147,10 +147,10 @@ __global__ void __launch_bounds__(512) kvt_copy_blocks_multi_kernel(const __grid
 #pragma unroll
   for (uint32_t t = 0; t < KVT_COPY_MAX_TENSORS; ++t) {
     segs[t] = 1;
-    if (t < p.n_tensors && p.first[t + 1] > p.first[t]) {
+    if (t < p.n_tensors && p.count[t] > 0) {
       const uint64_t len0 = p.triples[3ull * p.first[t] + 2];
       if (len0 > kCopySeg) segs[t] = (uint32_t)min((len0 + kCopySeg - 1) / kCopySeg, (uint64_t)65536);
-      total += (uint64_t)(p.first[t + 1] - p.first[t]) * segs[t];
+      total += (uint64_t)p.count[t] * segs[t];
     }
     ends[t] = total;
   }
@@ -229,9 +229,9 @@ extern "C" int kvt_launch_copy_blocks(uint64_t src_base, uint64_t dst_base, cons
 
 extern "C" int kvt_launch_copy_blocks_multi(const KvtCopyMulti* args, int grid_ctas, void* stream) {
   if (args->n_tensors == 0 || args->n_tensors > KVT_COPY_MAX_TENSORS) return (int)cudaErrorInvalidValue;
-  if (args->first[args->n_tensors] == args->first[0]) return (int)cudaSuccess;
-  for (uint32_t t = 0; t < args->n_tensors; ++t)
-    if (args->first[t + 1] < args->first[t]) return (int)cudaErrorInvalidValue;
+  uint64_t n = 0;
+  for (uint32_t t = 0; t < args->n_tensors; ++t) n += args->count[t];
+  if (n == 0) return (int)cudaSuccess;
   kvt_copy_blocks_multi_kernel<<<grid_ctas > 0 ? grid_ctas : 2 * pick_grid(0), 512, 0,
                                  reinterpret_cast<cudaStream_t>(stream)>>>(*args);
   return (int)cudaGetLastError();

@@ -38,6 +38,13 @@ class IChannel {
     (void)layer_begin; (void)layer_end; (void)step;
     return false;
   }
+  // Layers [layer_begin, layer_end) are all ready (device ordered: all recorded).  Sends the first one
+  // or, when one launch can carry several, the first few; returns how many it took (>= 1).
+  virtual size_t send_range(size_t layer_begin, size_t layer_end, Step* step) {
+    (void)layer_end;
+    send_data(layer_begin, step);
+    return 1;
+  }
   // `out` receives key=value metrics of the batch.
   virtual void flush(std::string& out) = 0;
   virtual bool is_active() { return true; }

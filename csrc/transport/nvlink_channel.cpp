@@ -225,9 +225,14 @@ class NvlinkChannel : public IChannel {
   void upload_generic() {
     size_t total = 0;
     generic_off_.assign(generic_.size(), 0);
+    generic_rounds_ = 1;
     for (size_t t = 0; t < generic_.size(); ++t) {
       generic_off_[t] = total;
       total += generic_[t].size();
+      if (generic_[t].empty()) continue;
+      uint64_t longest = 0;
+      for (const Triple& tr : generic_[t]) longest = std::max<uint64_t>(longest, tr.len);
+      generic_rounds_ = std::max(generic_rounds_, kvt_bulk_rounds(generic_[t][0].len, longest));
     }
     if (total == 0) return;
     cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
@@ -309,28 +314,7 @@ class NvlinkChannel : public IChannel {
     }
     const auto& addrs = ctx_->layer_data_address();
     RTASSERT(layer < addrs.size() && layer < dst_ptrs_.size());
-    if (generic_.size() <= KVT_COPY_MAX_TENSORS) {
-      // every tensor of the layer in one launch
-      KvtCopyMulti m{};
-      uint32_t nt = 0;
-      for (size_t t = 0; t < generic_.size(); ++t) {
-        if (generic_[t].empty()) continue;
-        m.src_base[nt] = addrs[layer][t];
-        m.dst_base[nt] = dst_ptrs_[layer][t];
-        m.src_cap[nt] = ctx_->tensor_capacity(t);
-        m.dst_cap[nt] = dst_.block_sizes.at(t) * static_cast<uint64_t>(dst_.layer_num_blocks);
-        m.first[nt] = static_cast<uint32_t>(generic_off_[t]);
-        m.first[nt + 1] = static_cast<uint32_t>(generic_off_[t] + generic_[t].size());
-        ++nt;
-      }
-      if (nt == 0) return;
-      m.n_tensors = nt;
-      m.triples = reinterpret_cast<const uint64_t*>(d_plan_);
-      m.status = d_status_;
-      const int grid = std::max(1, static_cast<int>(2 * kvt_sm_count(ctx_->device_id()) * env_kernel_copy_sm_usage()));
-      cuda_check(kvt_launch_copy_blocks_multi(&m, grid, st.stream()), "kvt_launch_copy_blocks_multi");
-      return;
-    }
+    if (launch_generic_multi(layer, layer + 1, st)) return;
     for (size_t t = 0; t < generic_.size(); ++t) {
       if (generic_[t].empty()) continue;
       const size_t dst_cap = dst_.block_sizes.at(t) * static_cast<size_t>(dst_.layer_num_blocks);
@@ -338,6 +322,67 @@ class NvlinkChannel : public IChannel {
       st.launch_resident(addrs[layer][t], dst_ptrs_[layer][t], d, generic_[t].size(), ctx_->tensor_capacity(t), dst_cap, 0,
                          d_status_);
     }
+  }
+
+  // Every tensor of layers [lo, hi) in one launch when they fit the kernel's entry table.
+  bool launch_generic_multi(size_t lo, size_t hi, DeviceStage& st) {
+    size_t per_layer = 0;
+    for (const auto& g : generic_) per_layer += g.empty() ? 0 : 1;
+    if (per_layer == 0) return true;
+    if (per_layer * (hi - lo) > KVT_COPY_MAX_TENSORS) return false;
+    const auto& addrs = ctx_->layer_data_address();
+    KvtCopyMulti m{};
+    uint32_t e = 0;
+    for (size_t layer = lo; layer < hi; ++layer) {
+      for (size_t t = 0; t < generic_.size(); ++t) {
+        if (generic_[t].empty()) continue;
+        m.src_base[e] = addrs[layer][t];
+        m.dst_base[e] = dst_ptrs_[layer][t];
+        m.src_cap[e] = ctx_->tensor_capacity(t);
+        m.dst_cap[e] = dst_.block_sizes.at(t) * static_cast<uint64_t>(dst_.layer_num_blocks);
+        m.first[e] = static_cast<uint32_t>(generic_off_[t]);
+        m.count[e] = static_cast<uint32_t>(generic_[t].size());
+        ++e;
+      }
+    }
+    m.n_tensors = e;
+    m.triples = reinterpret_cast<const uint64_t*>(d_plan_);
+    m.status = d_status_;
+    if (env_use_tma() != 0) {
+      // pages are long 16-byte aligned runs: the TMA engine moves them, four CTAs per SM
+      const int grid = std::max(1, static_cast<int>(4 * kvt_sm_count(ctx_->device_id()) * env_kernel_copy_sm_usage()));
+      cuda_check(kvt_launch_copy_blocks_bulk(&m, generic_rounds_, grid, st.stream()), "kvt_launch_copy_blocks_bulk");
+      return true;
+    }
+    const int grid = std::max(1, static_cast<int>(2 * kvt_sm_count(ctx_->device_id()) * env_kernel_copy_sm_usage()));
+    cuda_check(kvt_launch_copy_blocks_multi(&m, grid, st.stream()), "kvt_launch_copy_blocks_multi");
+    return true;
+  }
+
+  size_t send_range(size_t lo, size_t hi, Step* step) override {
+    if (fused_ || hi <= lo + 1) {   // the fused kernel gains nothing from longer launches (measured)
+      send_data(lo, step);
+      return 1;
+    }
+    size_t per_layer = 0;
+    for (const auto& g : generic_) per_layer += g.empty() ? 0 : 1;
+    const size_t fit = per_layer == 0 ? hi - lo : KVT_COPY_MAX_TENSORS / per_layer;
+    const size_t n = std::max<size_t>(1, std::min(hi - lo, fit));
+    if (n == 1) {
+      send_data(lo, step);
+      return 1;
+    }
+    cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
+    const auto& addrs = ctx_->layer_data_address();
+    RTASSERT(lo + n <= addrs.size() && lo + n <= dst_ptrs_.size());
+    DeviceStage& st = *stages_[(range_rr_++) % stages_.size()];
+    // layer events are recorded in order on one stream: the last of the range implies the others
+    st.wait_event(ctx_->cuda_barrier()->event(static_cast<uint32_t>(lo + n - 1)));
+    if (!launch_generic_multi(lo, lo + n, st)) {
+      send_data(lo, step);
+      return 1;
+    }
+    return n;
   }
 
   void flush(std::string& out) override {
@@ -437,6 +482,8 @@ class NvlinkChannel : public IChannel {
   void* plan_event_{nullptr};
   DevArray<uint64_t> d_src_layers_, d_dst_layers_;
   DevArray<TensorMapBytes> d_src_maps_, d_dst_maps_;
+  size_t range_rr_{0};
+  uint32_t generic_rounds_{1};   // bulk copy kernel: segment rounds the longest descriptor needs
   uint32_t* d_status_{nullptr};   // 64 bytes: [0] code, [1] detail, bytes 8..15 start stamp, bytes 16..23 end stamp
   const bool stamps_{env_device_timestamps()};
   int64_t device_us_{-1};

@@ -363,10 +363,10 @@ def test_copy_blocks_long_mixed_and_multi_tensor(ops):
     dsts = [torch.zeros(1 << 20, dtype=torch.uint8, device=DEV) for _ in range(3)]
     lists = [[(0, 4096, 41984), (50000, 100000, 41984)], [], [(8, 24, 132 * 64), (9000, 20000, 132 * 64), (30000, 500000, 7)]]
     flat = [x for lst in lists for tr in lst for x in tr]
-    first = [0, 2, 2, 5]
+    first, count = [0, 2, 2], [2, 0, 3]
     t = torch.tensor(flat, dtype=torch.int64, device=DEV)
     ops.kvt_launch_copy_blocks_multi([x.data_ptr() for x in srcs], [x.data_ptr() for x in dsts], [1 << 20] * 3,
-                                     [1 << 20] * 3, first, t.data_ptr(), st.data_ptr(), 0, stream)
+                                     [1 << 20] * 3, first, count, t.data_ptr(), st.data_ptr(), 0, stream)
     torch.cuda.synchronize()
     assert st[0].item() == 0
     for a, b, lst in zip(srcs, dsts, lists):
@@ -374,10 +374,68 @@ def test_copy_blocks_long_mixed_and_multi_tensor(ops):
         for so, do, ln in lst:
             want[do:do + ln] = a[so:so + ln]
         assert torch.equal(b, want)
+    # two entries that share ONE descriptor range: the same pages of two layers in one launch
+    dsts2 = [torch.zeros(1 << 20, dtype=torch.uint8, device=DEV) for _ in range(2)]
+    ops.kvt_launch_copy_blocks_multi([srcs[0].data_ptr(), srcs[2].data_ptr()], [x.data_ptr() for x in dsts2], [1 << 20] * 2,
+                                     [1 << 20] * 2, [0, 0], [2, 2], t.data_ptr(), st.data_ptr(), 0, stream)
+    torch.cuda.synchronize()
+    assert st[0].item() == 0
+    for a, b in zip((srcs[0], srcs[2]), dsts2):
+        want = torch.zeros_like(b)
+        for so, do, ln in lists[0]:
+            want[do:do + ln] = a[so:so + ln]
+        assert torch.equal(b, want)
     # a descriptor outside its own tensor is reported with its index and skipped
     t_bad = torch.tensor([0, 0, 64, 0, (1 << 20) - 8, 64], dtype=torch.int64, device=DEV)
     ops.kvt_launch_copy_blocks_multi([srcs[0].data_ptr(), srcs[1].data_ptr()], [dsts[0].data_ptr(), dsts[1].data_ptr()],
-                                     [1 << 20] * 2, [1 << 20] * 2, [0, 1, 2], t_bad.data_ptr(), st.data_ptr(), 0, stream)
+                                     [1 << 20] * 2, [1 << 20] * 2, [0, 1], [1, 1], t_bad.data_ptr(), st.data_ptr(), 0, stream)
+    torch.cuda.synchronize()
+    assert st[0].item() == 1 and st[1].item() == 1
+
+
+def test_bulk_copy_moves_aligned_runs_by_tma_and_the_rest_by_simt(ops):
+    """kvt_copy_blocks_bulk: pages (16-byte aligned, whole 16-byte words) go through the TMA engine, odd
+    runs and tails through the SIMT warps; entries whose later descriptors are longer than the first
+    need more rounds; peers of the plain kernel's checks (range report) hold."""
+    st = torch.zeros(4, dtype=torch.int32, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator(device=DEV).manual_seed(11)
+    n = 4 << 20
+    cases = [
+        # MLA-like pages of two tensors
+        ([[(0, 41984 * 3, 41984), (41984 * 5, 41984, 41984), (41984 * 9, 41984 * 20, 41984)],
+          [(0, 8448 * 2, 8448), (8448 * 7, 8448 * 40, 8448)]]),
+        # unaligned starts, odd lengths, a tail that is not a multiple of 16, a run longer than the first
+        ([[(16, 32, 100), (4096, 100000, 8192 * 3 + 40), (500001, 300003, 5000), (1 << 20, 2 << 20, 1 << 20)],
+          [(8, 8, 16), (1000, 2000, 12345)]]),
+    ]
+    for lists in cases:
+        srcs = [torch.randint(0, 255, (n,), dtype=torch.uint8, device=DEV, generator=g) for _ in lists]
+        dsts = [torch.zeros(n, dtype=torch.uint8, device=DEV) for _ in lists]
+        flat = [x for lst in lists for tr in lst for x in tr]
+        first, count, pos, rounds = [], [], 0, 1
+        for lst in lists:
+            first.append(pos)
+            count.append(len(lst))
+            pos += len(lst)
+            rounds = max(rounds, ops.kvt_bulk_rounds(lst[0][2], max(tr[2] for tr in lst)))
+        t = torch.tensor(flat, dtype=torch.int64, device=DEV)
+        ops.kvt_launch_copy_blocks_multi([x.data_ptr() for x in srcs], [x.data_ptr() for x in dsts], [n] * len(lists),
+                                         [n] * len(lists), first, count, t.data_ptr(), st.data_ptr(), 0, stream,
+                                         bulk_rounds=rounds)
+        torch.cuda.synchronize()
+        assert st[0].item() == 0
+        for a, b, lst in zip(srcs, dsts, lists):
+            want = torch.zeros_like(b)
+            for so, do, ln in lst:
+                want[do:do + ln] = a[so:so + ln]
+            assert torch.equal(b, want)
+    assert ops.kvt_bulk_rounds(41984, 41984) == 1 and ops.kvt_bulk_rounds(100, 8192 * 3 + 40) == 4
+    # a descriptor outside its tensor is reported and skipped
+    a = torch.zeros(1 << 16, dtype=torch.uint8, device=DEV)
+    t_bad = torch.tensor([0, 0, 64, 0, (1 << 16) - 8, 64], dtype=torch.int64, device=DEV)
+    ops.kvt_launch_copy_blocks_multi([a.data_ptr()], [a.data_ptr()], [1 << 16], [1 << 16], [0], [2], t_bad.data_ptr(),
+                                     st.data_ptr(), 0, stream, bulk_rounds=1)
     torch.cuda.synchronize()
     assert st[0].item() == 1 and st[1].item() == 1
 
