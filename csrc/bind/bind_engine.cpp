@@ -2,6 +2,8 @@
 // of the reference binding (kvtransfer/kvtransfer_pybind.cpp:415-522) and act on one
 // process-global client / server, as there.  `KvClient` / `KvServer` expose the same engine as
 // objects so that several workers can live in one process (tests, single-process demos).
+#include <chrono>
+
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
@@ -274,6 +276,37 @@ py::tuple py_plan(const WorkerInfo& src, const WorkerInfo& dst, int cache_shape,
   return py::make_tuple(per_tensor, std::string(kind), env.valid_ranks.to_string(), env.kvt_tp_size, env.kvt_tp_rank);
 }
 
+// Host cost of planning one batch, without the conversion to Python objects: microseconds per call of
+// (planner, then merge when asked), averaged over `iters` calls.
+double py_plan_time_us(const WorkerInfo& src, const WorkerInfo& dst, int cache_shape,
+                       const std::vector<std::tuple<std::string, uint32_t, uint32_t, bool, BlockIds, BlockIds>>& tasks,
+                       bool merge, int iters) {
+  PlanEnv env;
+  env.src = &src;
+  env.dst = &dst;
+  env.cache_shape = cache_shape;
+  PlannerChoice c = bind_planner(env);
+  std::vector<ReqSendTask> reqs;
+  for (const auto& t : tasks) {
+    auto info = std::make_shared<RequestInfo>(dst.inst_id, dst.worker_id, std::get<0>(t), std::get<4>(t), std::get<5>(t));
+    reqs.emplace_back(info, std::get<1>(t), std::get<2>(t), std::get<3>(t));
+  }
+  if (iters < 1) iters = 1;
+  const auto t0 = std::chrono::steady_clock::now();
+  size_t sink = 0;
+  for (int i = 0; i < iters; ++i) {
+    std::vector<std::vector<IpcBlock>> out;
+    for (const auto& r : reqs) plan_request(c, env, r, out);
+    for (auto& v : out) {
+      if (merge) merge_interval(v);
+      sink += v.size();
+    }
+  }
+  const auto t1 = std::chrono::steady_clock::now();
+  if (sink == static_cast<size_t>(-1)) throw std::runtime_error("unreachable");
+  return std::chrono::duration<double, std::micro>(t1 - t0).count() / iters;
+}
+
 }  // namespace
 
 void bind_engine(py::module_& m) {
@@ -497,6 +530,8 @@ void bind_engine(py::module_& m) {
   });
   m.def("plan_ipc_blocks", &py_plan, py::arg("src"), py::arg("dst"), py::arg("cache_shape"), py::arg("tasks"),
         py::arg("cast_fp8") = false, py::arg("pad_last") = true, py::arg("merge") = false);
+  m.def("plan_time_us", &py_plan_time_us, py::arg("src"), py::arg("dst"), py::arg("cache_shape"), py::arg("tasks"),
+        py::arg("merge") = true, py::arg("iters") = 100);
   m.def("merge_interval", [](std::vector<std::tuple<size_t, size_t, size_t>> v) {
     std::vector<IpcBlock> b;
     for (auto& t : v) b.emplace_back(std::get<0>(t), std::get<1>(t), std::get<2>(t));

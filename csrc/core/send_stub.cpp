@@ -198,6 +198,7 @@ struct KvSendStub::Impl {
     iter_start = SteadyClock::now();
     send_finish = iter_start;
     const int64_t queue_us = elapse_us(batch.send_ts, iter_start);
+    int64_t plan_us = 0;
     for (const auto& task : batch.tasks) {
       if (task.reach_last_token) finished_req.push_back(&task);
       if (task.new_tokens == 0) continue;            // a pure "close this request" marker
@@ -224,6 +225,7 @@ struct KvSendStub::Impl {
           have_data = !send_blocks.empty() && !send_blocks[0].empty();
           if (have_data) ch->register_data(send_blocks, planner.kind);
         }
+        plan_us = elapse_us(iter_start, SteadyClock::now());   // channel, planning, descriptor upload
         if (have_data) do_send(batch, device_planned);
       } catch (const std::exception& ex) {
         LOG(ERROR) << "KVT tx_stub fail to send data. DstId=" << stub->dstid() << ",DstWorkerId=" << stub->dstworkerid()
@@ -251,7 +253,7 @@ struct KvSendStub::Impl {
     batch.step->update_last_send_finish_ts(send_finish);
     LOG(INFO) << "SendStubMetrics. DstId=" << stub->dstid() << ",DstWorkerId=" << stub->dstworkerid()
               << ",StepIdx=" << step_idx << "." << batch.substepid << ",FinishedReqSize=" << finished_req.size() << ","
-              << flush_out << ",QueueUs=" << queue_us << ",WaitUs=" << wait_us << ",WaitAndSendUs=" << wait_and_send_us
+              << flush_out << ",QueueUs=" << queue_us << ",PlanUs=" << plan_us << ",WaitUs=" << wait_us << ",WaitAndSendUs=" << wait_and_send_us
               << ",SendNotifyUs=" << send_notify_us << ",SendFinishTs=" << send_finish.time_since_epoch().count();
   }
 
