@@ -193,7 +193,7 @@ class NvlinkChannel : public IChannel {
     }
     stamp_start(s0);
     cuda_check(cudaEventRecord(static_cast<cudaEvent_t>(plan_event_), s0), "cudaEventRecord");
-    for (size_t i = 1; i < stages_.size(); ++i) stages_[i]->wait_event(plan_event_);
+    begin_batch();
     fused_ = true;
     moved_bytes_per_layer_ = 0;
     for (const ReqSendTask* t : tasks)
@@ -255,7 +255,7 @@ class NvlinkChannel : public IChannel {
     }
     stamp_start(s0);
     cuda_check(cudaEventRecord(static_cast<cudaEvent_t>(plan_event_), s0), "cudaEventRecord");
-    for (size_t i = 1; i < stages_.size(); ++i) stages_[i]->wait_event(plan_event_);
+    begin_batch();
   }
 
   bool send_layers(size_t layer_begin, size_t layer_end, Step* step) override {
@@ -306,7 +306,7 @@ class NvlinkChannel : public IChannel {
   void send_data(size_t layer, Step* step) override {
     (void)step;
     cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
-    DeviceStage& st = *stages_[layer % stages_.size()];
+    DeviceStage& st = use_stage(layer % stages_.size());
     st.wait_event(ctx_->cuda_barrier()->event(static_cast<uint32_t>(layer)));
     if (fused_) {
       if (plan_.n_reqs != 0) launch_fused(layer, layer + 1, st);
@@ -375,7 +375,7 @@ class NvlinkChannel : public IChannel {
     cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
     const auto& addrs = ctx_->layer_data_address();
     RTASSERT(lo + n <= addrs.size() && lo + n <= dst_ptrs_.size());
-    DeviceStage& st = *stages_[(range_rr_++) % stages_.size()];
+    DeviceStage& st = use_stage((range_rr_++) % stages_.size());
     // layer events are recorded in order on one stream: the last of the range implies the others
     st.wait_event(ctx_->cuda_barrier()->event(static_cast<uint32_t>(lo + n - 1)));
     if (!launch_generic_multi(lo, lo + n, st)) {
@@ -393,7 +393,9 @@ class NvlinkChannel : public IChannel {
       // one host wait for the batch: the other streams are joined into the first on the device, the
       // kernels' shared status words follow them, and the host waits for that copy alone
       cudaStream_t s0 = static_cast<cudaStream_t>(stages_[0]->stream());
-      for (size_t i = 1; i < stages_.size(); ++i) stages_[0]->wait_event(stages_[i]->record_done());
+      for (size_t i = 1; i < stages_.size() && i < stage_used_.size(); ++i)
+        if (stage_used_[i]) stages_[0]->wait_event(stages_[i]->record_done());
+      begin_batch();
       if (stamps_) cuda_check(kvt_launch_stamp(reinterpret_cast<uint64_t*>(d_status_) + 2, s0), "kvt_launch_stamp");
       cuda_check(cudaMemcpyAsync(h_status_.data(), d_status_, 24, cudaMemcpyDeviceToHost, s0), "cudaMemcpyAsync(status)");
       cuda_check(cudaStreamSynchronize(s0), "cudaStreamSynchronize");
@@ -435,6 +437,19 @@ class NvlinkChannel : public IChannel {
   }
 
  private:
+  // Stream 0 carries the plan; another stream joins it (waits for the upload) when the batch first uses
+  // it, and flush() joins back only the streams that were used: a batch of one launch makes no join at all.
+  void begin_batch() { stage_used_.assign(stages_.size(), 0); }
+
+  DeviceStage& use_stage(size_t i) {
+    if (stage_used_.size() != stages_.size()) stage_used_.assign(stages_.size(), 0);
+    if (i != 0 && !stage_used_[i]) {
+      stages_[i]->wait_event(plan_event_);
+      stage_used_[i] = 1;
+    }
+    return *stages_[i];
+  }
+
   void stamp_start(cudaStream_t s0) {
     if (stamps_) cuda_check(kvt_launch_stamp(reinterpret_cast<uint64_t*>(d_status_) + 1, s0), "kvt_launch_stamp");
   }
@@ -483,6 +498,7 @@ class NvlinkChannel : public IChannel {
   DevArray<uint64_t> d_src_layers_, d_dst_layers_;
   DevArray<TensorMapBytes> d_src_maps_, d_dst_maps_;
   size_t range_rr_{0};
+  std::vector<char> stage_used_;
   uint32_t generic_rounds_{1};   // bulk copy kernel: segment rounds the longest descriptor needs
   uint32_t* d_status_{nullptr};   // 64 bytes: [0] code, [1] detail, bytes 8..15 start stamp, bytes 16..23 end stamp
   const bool stamps_{env_device_timestamps()};
