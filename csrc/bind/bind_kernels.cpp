@@ -270,6 +270,18 @@ void bind_kernels(py::module_& m) {
       py::arg("status"), py::arg("done_counter"), py::arg("mc_flag"), py::arg("flag_value"), py::arg("grid"),
       py::arg("stream"));
 
+  m.def("kvt_launch_copy_blocks_cast",
+        [](uint64_t src_base, uint64_t dst_base, uint64_t triples, uint32_t n, uint64_t src_cap, uint64_t dst_cap,
+           uint64_t status, int grid, uint64_t stream) {
+          check_cuda(kvt_launch_copy_blocks_cast(src_base, dst_base, reinterpret_cast<const uint64_t*>(triples), n, src_cap,
+                                                 dst_cap, reinterpret_cast<uint32_t*>(status), grid,
+                                                 reinterpret_cast<void*>(stream)),
+                     "kvt_launch_copy_blocks_cast");
+        },
+        py::arg("src_base"), py::arg("dst_base"), py::arg("triples"), py::arg("n"), py::arg("src_capacity"),
+        py::arg("dst_capacity"), py::arg("status"), py::arg("grid"), py::arg("stream"));
+  m.def("kvt_bf16_to_e4m3", [](uint16_t bits) { return static_cast<int>(kvt_bf16_to_e4m3(bits)); });
+
   m.def("kvt_launch_wait_flag", [](uint64_t flag, uint64_t value, uint64_t timeout_ns, uint64_t status,
                                    uint64_t stream) {
     check_cuda(kvt_launch_wait_flag(reinterpret_cast<const uint64_t*>(flag), value, timeout_ns,

@@ -148,6 +148,16 @@ int kvt_launch_copy_blocks(uint64_t src_base, uint64_t dst_base, const uint64_t*
                            uint32_t n, uint64_t src_capacity, uint64_t dst_capacity,
                            uint32_t* status, int grid_ctas, void* stream);
 
+// Gather with the reference's unscaled cast (kvtransfer/src/copy_kernels.cu:369-481): descriptor
+// {src_off, dst_off, n} reads n bf16 values (2n bytes) at src_off and writes n e4m3 bytes at dst_off,
+// round to nearest even, saturating to +-448, NaN kept.  Used by the host-staged transports when
+// BLLM_KVTRANS_BF162FP8_CONV is set (bf16 prefill cache, fp8 decode cache).
+int kvt_launch_copy_blocks_cast(uint64_t src_base, uint64_t dst_base, const uint64_t* triples, uint32_t n,
+                                uint64_t src_capacity, uint64_t dst_capacity, uint32_t* status, int grid_ctas,
+                                void* stream);
+// The same conversion of one value on the host (the CPU path of those transports, and the oracle).
+uint8_t kvt_bf16_to_e4m3(uint16_t bf16_bits);
+
 // The same copy over up to KVT_COPY_MAX_TENSORS tensor pairs in ONE launch: entry e moves descriptors
 // [first[e], first[e] + count[e]) of `triples`, relative to src_base[e] / dst_base[e].  Entries may
 // share a descriptor range: the tensors of one layer (MLA latent + indexer keys, hybrid groups) cost

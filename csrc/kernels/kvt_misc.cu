@@ -7,7 +7,9 @@
 //                       copy_d2h/h2d_direct kernels do, kvtransfer/src/copy_kernels.cu:105-281).
 //   * bounded flag wait / flag set for completion signalling.
 //   * peer-memory, IPC and mapped-host-memory helpers.
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
+#include <math.h>
 #include <stdint.h>
 #include <string.h>
 
@@ -175,6 +177,58 @@ __global__ void __launch_bounds__(512) kvt_copy_blocks_multi_kernel(const __grid
   }
 }
 
+__device__ __forceinline__ uint32_t cast4_bf16_e4m3(uint32_t lo, uint32_t hi) {
+  // lo, hi: two bf16 pairs; returns four e4m3 bytes in memory order
+  const float a = __uint_as_float(lo << 16), b = __uint_as_float(lo & 0xffff0000u);
+  const float c = __uint_as_float(hi << 16), d = __uint_as_float(hi & 0xffff0000u);
+  const uint32_t ab = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t cd = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return (ab & 0xffffu) | (cd << 16);
+}
+
+// A warp per 2048-value segment of a descriptor.
+__global__ void __launch_bounds__(512) kvt_copy_blocks_cast_kernel(const char* __restrict__ src, char* __restrict__ dst,
+                                                                    const uint64_t* __restrict__ triples, uint32_t n,
+                                                                    uint64_t src_cap, uint64_t dst_cap, uint32_t* status) {
+  constexpr uint32_t kSegVals = 2048;
+  const uint32_t warps_per_cta = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const uint64_t len0 = triples[2];
+  const uint32_t segs0 = len0 > kSegVals ? (uint32_t)min((len0 + kSegVals - 1) / kSegVals, (uint64_t)65536) : 1u;
+  const uint64_t total = (uint64_t)n * segs0;
+  for (uint64_t u = (uint64_t)blockIdx.x * warps_per_cta + warp; u < total; u += (uint64_t)gridDim.x * warps_per_cta) {
+    const uint32_t i = (uint32_t)(u / segs0);
+    const uint32_t s0 = (uint32_t)(u - (uint64_t)i * segs0);
+    const uint64_t so = triples[3 * i], dof = triples[3 * i + 1], len = triples[3 * i + 2];
+    if (len > 0x7fffffffull || so > src_cap || 2 * len > src_cap - so || dof > dst_cap || len > dst_cap - dof) {
+      if (lane == 0 && s0 == 0) set_status(status, KVT_ERR_BLOCK_RANGE, i);
+      continue;
+    }
+    for (uint64_t off = (uint64_t)s0 * kSegVals; off < len; off += (uint64_t)segs0 * kSegVals) {
+      const uint32_t cnt = (uint32_t)min((uint64_t)kSegVals, len - off);
+      const char* s = src + so + 2 * off;
+      char* d = dst + dof + off;
+      if (((reinterpret_cast<uintptr_t>(s) & 7u) | (reinterpret_cast<uintptr_t>(d) & 3u)) == 0) {
+        const uint32_t n4 = cnt >> 2;   // four values per step: 8 bytes in, 4 bytes out
+        const uint2* s2 = reinterpret_cast<const uint2*>(s);
+        uint32_t* d1 = reinterpret_cast<uint32_t*>(d);
+        for (uint32_t k = lane; k < n4; k += 32) {
+          const uint2 v = s2[k];
+          d1[k] = cast4_bf16_e4m3(v.x, v.y);
+        }
+        for (uint32_t k = (n4 << 2) + lane; k < cnt; k += 32) {
+          const uint16_t h = reinterpret_cast<const uint16_t*>(s)[k];
+          d[k] = (char)__nv_cvt_float_to_fp8(__uint_as_float((uint32_t)h << 16), __NV_SATFINITE, __NV_E4M3);
+        }
+      } else {
+        for (uint32_t k = lane; k < cnt; k += 32) {
+          const uint32_t h = (uint32_t)(unsigned char)s[2 * k] | ((uint32_t)(unsigned char)s[2 * k + 1] << 8);
+          d[k] = (char)__nv_cvt_float_to_fp8(__uint_as_float(h << 16), __NV_SATFINITE, __NV_E4M3);
+        }
+      }
+    }
+  }
+}
+
 __global__ void kvt_wait_flag_kernel(const uint64_t* flag, uint64_t value, uint64_t timeout_ns, uint32_t* status) {
   uint64_t t0;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
@@ -225,6 +279,40 @@ extern "C" int kvt_launch_copy_blocks(uint64_t src_base, uint64_t dst_base, cons
       reinterpret_cast<const char*>(src_base), reinterpret_cast<char*>(dst_base), triples, n, src_capacity,
       dst_capacity, status);
   return (int)cudaGetLastError();
+}
+
+extern "C" int kvt_launch_copy_blocks_cast(uint64_t src_base, uint64_t dst_base, const uint64_t* triples, uint32_t n,
+                                           uint64_t src_capacity, uint64_t dst_capacity, uint32_t* status,
+                                           int grid_ctas, void* stream) {
+  if (n == 0) return (int)cudaSuccess;
+  kvt_copy_blocks_cast_kernel<<<grid_ctas > 0 ? grid_ctas : pick_grid(0), 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const char*>(src_base), reinterpret_cast<char*>(dst_base), triples, n, src_capacity, dst_capacity,
+      status);
+  return (int)cudaGetLastError();
+}
+
+extern "C" uint8_t kvt_bf16_to_e4m3(uint16_t bits) {
+  const uint32_t sign = (bits >> 8) & 0x80u;
+  const uint32_t mag = bits & 0x7fffu;
+  if (mag > 0x7f80u) return (uint8_t)0x7fu;                           // NaN: the hardware conversion drops the sign
+  uint32_t fb = mag << 16;
+  float x;
+  memcpy(&x, &fb, 4);
+  if (x >= 464.0f) return (uint8_t)(sign | 0x7eu);                    // beyond the last tie: saturates to 448 (inf too)
+  if (x < 0.015625f) {                                                // below the smallest normal 2^-6: steps of 2^-9
+    const float q = nearbyintf(x * 512.0f);                           // round to nearest even (default rounding mode)
+    return (uint8_t)(sign | (uint32_t)q);                             // q == 8 encodes 2^-6 by itself
+  }
+  int e;
+  const float m = frexpf(x, &e);                                      // x = m * 2^e, m in [0.5, 1)
+  int E = e - 1 + 7;
+  float frac = nearbyintf((m * 2.0f - 1.0f) * 8.0f);
+  if (frac >= 8.0f) {
+    frac = 0.0f;
+    E += 1;
+  }
+  const uint32_t code = ((uint32_t)E << 3) | (uint32_t)frac;
+  return (uint8_t)(sign | (code > 0x7eu ? 0x7eu : code));
 }
 
 extern "C" int kvt_launch_copy_blocks_multi(const KvtCopyMulti* args, int grid_ctas, void* stream) {

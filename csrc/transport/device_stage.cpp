@@ -102,12 +102,12 @@ void DeviceStage::wait_event(void* event) {
 }
 
 void DeviceStage::enqueue(uint64_t src_base, uint64_t dst_base, const std::vector<Triple>& triples, uint64_t src_cap,
-                          uint64_t dst_cap, int grid_ctas, int host_side) {
+                          uint64_t dst_cap, int grid_ctas, int host_side, bool cast_bf16_e4m3) {
   if (triples.empty()) return;
   cuda_check(cudaSetDevice(device_), "cudaSetDevice");
   cudaStream_t s = static_cast<cudaStream_t>(stream_);
   const size_t n = triples.size();
-  if (host_side != HOST_NONE) {
+  if (host_side != HOST_NONE && !cast_bf16_e4m3) {
     size_t total = 0, min_len = SIZE_MAX;
     for (const Triple& t : triples) {
       total += t.len;
@@ -159,8 +159,13 @@ void DeviceStage::enqueue(uint64_t src_base, uint64_t dst_base, const std::vecto
   }
   for (size_t off = 0; off < n; off += max_per_launch) {
     const uint32_t cnt = static_cast<uint32_t>(std::min(max_per_launch, n - off));
-    cuda_check(kvt_launch_copy_blocks(src_base, dst_base, d + off * 3, cnt, src_cap, dst_cap, d_status_, grid, s),
-               "kvt_launch_copy_blocks");
+    if (cast_bf16_e4m3) {
+      cuda_check(kvt_launch_copy_blocks_cast(src_base, dst_base, d + off * 3, cnt, src_cap, dst_cap, d_status_, grid, s),
+                 "kvt_launch_copy_blocks_cast");
+    } else {
+      cuda_check(kvt_launch_copy_blocks(src_base, dst_base, d + off * 3, cnt, src_cap, dst_cap, d_status_, grid, s),
+                 "kvt_launch_copy_blocks");
+    }
   }
   used_ += n;
 }

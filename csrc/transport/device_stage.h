@@ -48,10 +48,11 @@ class DeviceStage {
                        uint64_t dst_cap, int grid_ctas = 0, uint32_t* status = nullptr);
   // Enqueue the copy; does not wait.  host_side says which end is pinned host memory (HOST_NONE,
   // HOST_SRC, HOST_DST): with a host end the copy policy of the device may hand the list to the copy
-  // engines (one cudaMemcpyAsync per descriptor, bounds checked here) instead of the kernel.
+  // engines (one cudaMemcpyAsync per descriptor, bounds checked here) instead of the kernel.  With
+  // cast_bf16_e4m3 a descriptor's length counts values: 2 x len source bytes become len e4m3 bytes.
   enum { HOST_NONE = 0, HOST_SRC = 1, HOST_DST = 2 };
   void enqueue(uint64_t src_base, uint64_t dst_base, const std::vector<Triple>& triples, uint64_t src_cap,
-               uint64_t dst_cap, int grid_ctas = 0, int host_side = HOST_NONE);
+               uint64_t dst_cap, int grid_ctas = 0, int host_side = HOST_NONE, bool cast_bf16_e4m3 = false);
   uint64_t memcpy_lists() const { return memcpy_lists_; }   // lists that went to the copy engines
   uint64_t kernel_lists() const { return kernel_lists_; }
   // Wait for everything enqueued and throw KVTransferException if the kernel flagged a descriptor.

@@ -53,16 +53,18 @@ class HostChannel : public IChannel {
   }
 
   void register_data(std::vector<std::vector<IpcBlock>>& data, TPKind kind) override {
-    (void)kind;
     data_.swap(data);
     data.clear();
+    // The unscaled bf16 -> e4m3 cast of the reference's staged path (tcp_channel.cpp:411-447): only the
+    // P>D planner emits fp8 lengths, and only single-tensor layers are cast.
+    cast_ = env_bf162fp8_conversion() && kind == TPKind::PGTD && data_.size() == 1;
     origin_blocks_ = merged_blocks_ = 0;
     sb_min_ = SIZE_MAX;
     sb_max_ = sb_total_ = 0;
     blob_bytes_.assign(data_.size(), 0);
     for (size_t t = 0; t < data_.size(); ++t) {
       origin_blocks_ += data_[t].size();
-      validate_ipc_block_bounds(data_[t], ctx_->tensor_capacity(t), IpcBlockOffset::SOURCE, name(), 0, t);
+      validate_ipc_block_bounds(data_[t], ctx_->tensor_capacity(t), IpcBlockOffset::SOURCE, name(), 0, t, cast_ ? 2 : 1);
       const MergeStats st = merge_interval(data_[t]);
       merged_blocks_ += st.count;
       if (st.count) {
@@ -149,7 +151,19 @@ class HostChannel : public IChannel {
         c += b.length;
       }
       if (stage_ != nullptr) {
-        stage_->enqueue(addrs[layer][t], blob_dev, triples, ctx_->tensor_capacity(t), blob_cap, 0, DeviceStage::HOST_DST);
+        stage_->enqueue(addrs[layer][t], blob_dev, triples, ctx_->tensor_capacity(t), blob_cap, 0, DeviceStage::HOST_DST,
+                        cast_);
+      } else if (cast_) {
+        const char* src = reinterpret_cast<const char*>(addrs[layer][t]);
+        for (const auto& tr : triples) {
+          const char* sp = src + tr.src_off;
+          char* dp = blob_base + tr.dst_off;
+          for (uint64_t k = 0; k < tr.len; ++k) {
+            uint16_t h;
+            memcpy(&h, sp + 2 * k, 2);
+            dp[k] = static_cast<char>(kvt_bf16_to_e4m3(h));
+          }
+        }
       } else {
         const char* src = reinterpret_cast<const char*>(addrs[layer][t]);
         for (const auto& tr : triples) memcpy(blob_base + tr.dst_off, src + tr.src_off, tr.len);
@@ -200,7 +214,7 @@ class HostChannel : public IChannel {
     TimeWatch tw;
     drain(0);
     std::ostringstream ss;
-    ss << "Proto=" << name() << ",OriginSbNum=" << origin_blocks_ << ",MergedSbNum=" << merged_blocks_
+    ss << "Proto=" << name() << (cast_ ? ",Cast=bf16->e4m3" : "") << ",OriginSbNum=" << origin_blocks_ << ",MergedSbNum=" << merged_blocks_
        << ",SbSizeMin=" << (sb_min_ == SIZE_MAX ? 0 : sb_min_) << ",SbSizeMax=" << sb_max_ << ",SbSizeTotal=" << sb_total_
        << ",SendUs=" << send_us_ << ",D2HUs=" << gather_us_ << ",H2DUsMax=" << recv_us_max_
        << ",FlushUs=" << tw.get_elapse_us();
@@ -330,6 +344,7 @@ class HostChannel : public IChannel {
   std::unique_ptr<DeviceStage> stage_;
   std::vector<std::vector<IpcBlock>> data_;
   std::vector<size_t> blob_bytes_;
+  bool cast_{false};   // gather casts bf16 -> e4m3 (descriptor lengths are fp8 bytes)
   PinnedBuffer tx_;
   std::string msg_buf_;
   std::vector<Pending> pending_;

@@ -202,7 +202,11 @@ class NvlinkChannel : public IChannel {
   }
 
   void register_data(std::vector<std::vector<IpcBlock>>& data, TPKind kind) override {
-    (void)kind;
+    if (env_bf162fp8_conversion() && kind == TPKind::PGTD) {
+      throw KVTransferException(ErrorKind::INVALID_OPERATION,
+                                "nvlink: the unscaled bf16->fp8 cast belongs to the host-staged transports; over NVLink an "
+                                "fp8 decode cache is filled by the block-scaled quantiser (BLLM_KVTRANS_DST_MXFP8)");
+    }
     fused_ = false;
     generic_.assign(data.size(), {});
     moved_bytes_per_layer_ = 0;

@@ -512,3 +512,56 @@ def test_config1_two_processes_with_file_naming(proto, tmp_path, ops):
         p.join(30)
         if p.is_alive():
             p.kill()
+
+
+def test_bf16_to_e4m3_host_conversion_matches_torch(ops):
+    """Every finite bf16 value whose magnitude e4m3 can hold converts like torch's round-to-nearest-even
+    cast; larger ones saturate to 448, NaN stays NaN, signed zero keeps its sign."""
+    bits = torch.arange(0, 1 << 16, dtype=torch.int32)
+    vals = bits.to(torch.int16).view(torch.bfloat16)
+    mask = vals.float().abs() <= 448
+    want = vals[mask].to(torch.float8_e4m3fn).view(torch.uint8).tolist()
+    got = [ops.kvt_bf16_to_e4m3(int(b)) for b in bits[mask].tolist()]
+    assert got == want
+    assert ops.kvt_bf16_to_e4m3(0x7F80) == 0x7E and ops.kvt_bf16_to_e4m3(0xFF80) == 0xFE      # +-inf saturate
+    assert ops.kvt_bf16_to_e4m3(0x4480) == 0x7E                                              # 1024 saturates
+    assert ops.kvt_bf16_to_e4m3(0x7FC0) & 0x7F == 0x7F                                       # NaN
+    assert ops.kvt_bf16_to_e4m3(0x8000) == 0x80 and ops.kvt_bf16_to_e4m3(0x0000) == 0x00
+
+
+@pytest.mark.parametrize("proto", [PT.TCP, PT.SHM])
+def test_staged_transfer_casts_bf16_to_fp8_for_a_smaller_decode_tp(proto, ops, sink, monkeypatch):
+    """BLLM_KVTRANS_BF162FP8_CONV=1 (the reference's staged cast, tcp_channel.cpp:411-447): two prefill
+    TP ranks with bf16 caches fill their head slices of one decode rank's fp8 cache; every byte on the
+    decode side is the unscaled e4m3 cast of the prefill value."""
+    monkeypatch.setenv("BLLM_KVTRANS_BF162FP8_CONV", "1")
+    ops.envcfg_reset_for_test()
+    hp = H // 2
+    g = torch.Generator().manual_seed(3)
+    srcs = [[torch.randn(2, NB, T, hp, D, generator=g).to(torch.bfloat16) for _ in range(L)] for _ in range(2)]
+    dst = [torch.zeros(2, NB, T, H, D, dtype=torch.uint8) for _ in range(L)]
+    p_tok, d_tok = 2 * hp * D * 2, 2 * H * D
+    srv = KVTransferServer("D|0|1", 1, 0, 0, d_tok * T, d_tok, "fake://", dst, [proto], num_kv_heads=H, cache_shape=2)
+    clis = [KVTransferClient("P|0|2", 2, r, r, p_tok * T, p_tok, "fake://", srcs[r], [proto], num_kv_heads=H, cache_shape=2)
+            for r in range(2)]
+    try:
+        sb, db, ntok = [5, 9, 2], [7, 1, 30], 41
+        for r, cli in enumerate(clis):
+            cli.submit_req_send2("D|0|1", 0, "q", 0, ntok, True, sb, db, srv.worker_info(), stepid=7)
+            cli.start_send_step(7, 1)
+            for layer in range(L):
+                cli.record_event(layer)
+            cli.flush_send_step()
+            cli.drain()
+        for layer in range(L):
+            for t in range(ntok):
+                for r in range(2):
+                    want = srcs[r][layer][:, sb[t // T], t % T].to(torch.float8_e4m3fn).view(torch.uint8)
+                    got = dst[layer][:, db[t // T], t % T, r * hp:(r + 1) * hp]
+                    assert torch.equal(got, want), (layer, t, r)
+        # slots past the request stay untouched
+        assert int(dst[0][:, db[2], ntok % T:].sum()) == 0
+    finally:
+        srv.stop()
+        monkeypatch.delenv("BLLM_KVTRANS_BF162FP8_CONV")
+        ops.envcfg_reset_for_test()

@@ -440,6 +440,38 @@ def test_bulk_copy_moves_aligned_runs_by_tma_and_the_rest_by_simt(ops):
     assert st[0].item() == 1 and st[1].item() == 1
 
 
+def test_gather_with_unscaled_bf16_to_e4m3_cast(ops):
+    """kvt_copy_blocks_cast: every bf16 bit pattern converts like the host routine (which matches torch's
+    cast where e4m3 can hold the value and saturates beyond); descriptors with odd alignments and long
+    runs land where they are told."""
+    st = torch.zeros(4, dtype=torch.int32, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    bits = torch.arange(0, 1 << 16, dtype=torch.int32).to(torch.int16)
+    src = torch.cat([bits, bits.flip(0), bits[1:5000]]).to(DEV)          # bf16 words
+    nvals = src.numel()
+    dst = torch.zeros(nvals + 64, dtype=torch.uint8, device=DEV)
+    trip = [(0, 0, 65536), (65536 * 2, 65536, 65536), (65536 * 4 + 2, 65536 * 2 + 3, 4998), (10, 65536 * 2 + 5003, 1)]
+    t = torch.tensor([x for tr in trip for x in tr], dtype=torch.int64, device=DEV)
+    ops.kvt_launch_copy_blocks_cast(src.data_ptr(), dst.data_ptr(), t.data_ptr(), len(trip), nvals * 2, dst.numel(),
+                                    st.data_ptr(), 0, stream)
+    torch.cuda.synchronize()
+    assert st[0].item() == 0
+    table = torch.tensor([ops.kvt_bf16_to_e4m3(b) for b in range(1 << 16)], dtype=torch.uint8)
+    words = src.cpu().to(torch.int32) & 0xFFFF
+    got = dst.cpu()
+    for so, do, n in trip:
+        want = table[words[so // 2: so // 2 + n].long()]
+        assert torch.equal(got[do:do + n], want), (so, do, n)
+    finite = bits.view(torch.bfloat16).float().abs() <= 448
+    assert torch.equal(got[:65536][finite], bits.view(torch.bfloat16)[finite].to(torch.float8_e4m3fn).view(torch.uint8))
+    # a run whose 2 x n source bytes leave the tensor is reported
+    t_bad = torch.tensor([nvals * 2 - 8, 0, 8], dtype=torch.int64, device=DEV)
+    ops.kvt_launch_copy_blocks_cast(src.data_ptr(), dst.data_ptr(), t_bad.data_ptr(), 1, nvals * 2, dst.numel(),
+                                    st.data_ptr(), 0, stream)
+    torch.cuda.synchronize()
+    assert st[0].item() == 1
+
+
 def test_per_layer_launches_replay_from_a_cuda_graph(ops):
     """The launch is fixed-shape and touches no host state, so a step's per-layer launches can be
     captured once and replayed; new block tables reach the kernel through the plan buffer."""
