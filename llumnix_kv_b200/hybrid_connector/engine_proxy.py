@@ -17,6 +17,7 @@ import logging
 import os
 from typing import Any, Iterable, Optional
 
+from llumnix_kv_b200 import envs
 from llumnix_kv_b200.engine.config import VllmConfig
 from llumnix_kv_b200.engine.types import (EngineCoreOutput, EngineCoreRequest, EngineCoreRequestType, FinishReason,
                                           KVCacheBlocks, KVConnectorMetadata, KVConnectorRole, Request,
@@ -142,7 +143,9 @@ class EngineProxy:
         n = req.num_tokens + prealloc
         if save:
             n += gamma + 1
-        new = sched.kv_cache_manager.allocate_slots(req, n, skip_new_block_zeroing=load)
+        # VLLM_ZERO_HYBRID_KV_CACHE=0 turns the zeroing of fresh blocks off altogether (engine_proxy.py:183-199
+        # of the reference: skip_zero_for_kvt_recv or not envs.VLLM_ZERO_HYBRID_KV_CACHE)
+        new = sched.kv_cache_manager.allocate_slots(req, n, skip_new_block_zeroing=load or not envs.VLLM_ZERO_HYBRID_KV_CACHE)
         if new is None:
             return None
         req.num_computed_tokens = 0

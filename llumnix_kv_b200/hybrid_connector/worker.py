@@ -53,6 +53,7 @@ class HybridWorker:
     # ---- bypass: step metadata produced between engine steps ---------------------------------------
     async def _get_bypass_handle(self) -> str:
         host, port = scheduler_rpc_host(self._cfg), sched_rpc_server_port(self._cfg)
+        last_log = 0.0
         while True:
             try:
                 reader, writer = await asyncio.open_connection(host, port)
@@ -66,8 +67,10 @@ class HybridWorker:
                 return handle
             except RuntimeError:
                 raise
-            except Exception as ex:  # scheduler not up yet
-                logger.debug("bypass handle not available yet: %s", ex)
+            except Exception as ex:  # scheduler not up yet: say so once per VLLM_LOG_STATS_INTERVAL, not every 0.1 s
+                if time.time() - last_log > envs.VLLM_LOG_STATS_INTERVAL:
+                    logger.warning("failed to get bypass handle: %s", ex)
+                    last_log = time.time()
                 await asyncio.sleep(0.1)
 
     def _do_bypass_meta(self, meta: HybridMetadata) -> None:
