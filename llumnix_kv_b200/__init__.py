@@ -38,3 +38,29 @@ def set_envs() -> None:
     """Default environment of the native engine (role of blade_kvt/__init__.py:42-61)."""
     os.environ.setdefault("BLLM_KVTRANS_RDMA_SP", "2")
     os.environ.setdefault("BLLM_KVTRANS_SDH_KIND", "2")
+
+
+def support_async_sched() -> bool:
+    """The connector assumes the engine schedules synchronously (blade_kvt/__init__.py:10-11)."""
+    return False
+
+
+def is_nv_gpu() -> bool:
+    import torch
+
+    return torch.cuda.is_available() and "nvidia" in torch.cuda.get_device_name().lower()
+
+
+def is_erdma() -> bool:
+    """Whether the host's RDMA devices are Alibaba eRDMA (blade_kvt/__init__.py:21-39 asks the verbs tools
+    and the module list); False on hosts without an RDMA stack, which is every host this build targets."""
+    import subprocess
+
+    for cmd in ("ibv_devinfo -l", "ibv_devices", "lsmod"):
+        try:
+            out = subprocess.check_output(cmd, shell=True, stderr=subprocess.STDOUT, timeout=5)
+        except Exception:
+            continue
+        if b"erdma" in out.lower():
+            return True
+    return False

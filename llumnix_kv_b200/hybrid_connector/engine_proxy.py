@@ -279,6 +279,25 @@ def use_turboquant(cfg: VllmConfig) -> bool:
     return bool(dt and "tq" in dt.lower())
 
 
+def is_kvt_consumer_backend(cfg: VllmConfig) -> bool:
+    """A decode engine whose KV arrives by transfer (engine_proxy.py:86-90 of the reference)."""
+    kv = cfg.kv_transfer_config
+    return kv is not None and kv.kv_role == "kv_consumer" and kv.get_from_extra_config("backend", None) == "kvt"
+
+
+def is_statemodel(cfg: VllmConfig) -> bool:
+    """Whether any cache group of the model holds recurrent state (GDN / KDA layers) rather than attention KV
+    (engine_proxy.py:579-592 of the reference walks the KV cache groups' specs)."""
+    return cfg.model_config.num_gdn_groups > 0
+
+
+def use_kvt_decode_prefix_cache(cfg: VllmConfig) -> bool:
+    """Prefix reuse on a decode engine that receives KV is only worked out for hybrid models with state
+    layers and prefix caching on (engine_proxy.py:93-102 of the reference); ``align_seen_tokens_for_kvt``
+    then trims what is reused to whole blocks of every attention group."""
+    return bool(getattr(cfg.cache_config, "enable_prefix_caching", False)) and is_statemodel(cfg)
+
+
 def kvt_protocol() -> str:
     from llumnix_kv_b200 import envs
 

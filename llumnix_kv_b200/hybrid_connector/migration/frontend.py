@@ -134,3 +134,17 @@ class MigrationCli:
                 idx = self.engines.index(here) if here in self.engines else 0
                 spawn_task(self._migrate(o.request_id, self.engines[(idx + 1) % len(self.engines)]))
         await writer.drain()
+
+
+_g_is_frontend = False
+
+
+def i_am_frontend() -> None:
+    """Marks this process as the API-server side (blade_kvt/hybrid_connector/migration/frontend.py:314-321):
+    code shared with the engines asks ``is_frontend()`` before it touches engine-only state."""
+    global _g_is_frontend
+    _g_is_frontend = True
+
+
+def is_frontend() -> bool:
+    return _g_is_frontend

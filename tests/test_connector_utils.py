@@ -180,3 +180,19 @@ def test_wrapped_cache_objects_resolve_to_their_raw_buffer():
         resolve_raw_cache_tensors({"l.0": bad})
     assert turboquant_last_dim_bytes(64, 128, fast=True) == 66 and turboquant_last_dim_bytes(64, 256, fast=True) == 68
     assert turboquant_last_dim_bytes(64, 128, fast=False) == 80
+
+
+def test_role_and_model_probes():
+    from pd_helpers import make_cfg
+
+    import llumnix_kv_b200 as pkg
+    from llumnix_kv_b200.hybrid_connector import engine_proxy as ep
+
+    assert pkg.support_async_sched() is False and pkg.is_erdma() is False
+    d = make_cfg("kv_consumer", "D")
+    p = make_cfg("kv_producer", "P")
+    assert ep.is_kvt_consumer_backend(d) and not ep.is_kvt_consumer_backend(p)
+    assert not ep.is_kvt_consumer_backend(make_cfg("kv_both", "S", backend="kvs", extra={"kvs_name": "x"}))
+    hybrid = make_cfg("kv_consumer", "H", gdn_groups=3)
+    assert ep.is_statemodel(hybrid) and not ep.is_statemodel(d)
+    assert not ep.use_kvt_decode_prefix_cache(d)
