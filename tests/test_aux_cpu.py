@@ -148,3 +148,30 @@ def test_copy_policy_static_rule_and_buckets(ops):
     assert ops.copy_policy_bucket(5, (16 << 10) + 1) == (1, 1)
     assert ops.copy_policy_bucket(512, 2 << 20) == (2, 2)
     assert ops.copy_policy_bucket(513, (2 << 20) + 1) == (3, 3)
+
+
+def test_log_line_format_and_level_filter():
+    """The native logger writes glog-style lines to stderr ("date time.us:pid:tid L file:line] text") and
+    drops INFO lines unless LLMOPS_CPP_MIN_LOG_LEVEL=0 (kvtransfer/third_party/logging.cpp:106-147)."""
+    import os
+    import re
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    probe = ("import llumnix_kv_b200 as p\nK = p.load_ops()\n"
+             "try:\n    K.plan_ipc_blocks(K.WorkerInfo(), K.WorkerInfo(), 2, [('x', 0, 4, True, [[1]], [[1]])])\n"
+             "except Exception:\n    pass\nprint(K.new_id(), K.new_id())\n")
+    for level, want_info in (("0", True), ("1", False)):
+        env = dict(os.environ, LLMOPS_CPP_MIN_LOG_LEVEL=level, BLLM_KVTRANS_QUIET_ENV="1")
+        r = subprocess.run([sys.executable, "-c", probe], cwd=root, env=env, capture_output=True, text=True, timeout=120)
+        assert r.returncode == 0, r.stderr[-500:]
+        a, b = (int(x) for x in r.stdout.split())
+        assert a >= 20181218 and b == a + 1                     # ids count up from the reference's seed
+        lines = [ln for ln in r.stderr.splitlines() if "]" in ln and re.match(r"\d{4}-\d\d-\d\d ", ln)]
+        assert lines, r.stderr[-500:]                            # the failed plan logs an ERROR line at either level
+        for ln in lines:
+            assert re.match(r"\d{4}-\d\d-\d\d \d\d:\d\d:\d\d\.\d{6}:\d+:\d+ [IWEF] [\w.]+:\d+\] ", ln), ln
+        assert any(" E " in ln for ln in lines)
+        if not want_info:
+            assert not any(re.search(r":\d+ I ", ln) for ln in lines)
