@@ -125,9 +125,11 @@ void bind_kernels(py::module_& m) {
          const KvtLayout& dst, uint32_t layer_begin, uint32_t layer_end, uint64_t reqs, uint32_t n_reqs,
          uint32_t total_tiles, uint64_t block_ids, uint32_t tile_tokens, uint32_t src_head0, uint32_t dst_head0,
          uint32_t n_heads, uint32_t mode, uint64_t status, uint64_t done_counter, uint64_t flag,
-         uint64_t flag_value, int grid, int threads, int use_tma, uint64_t stream, uint32_t simt_tile) {
+         uint64_t flag_value, int grid, int threads, int use_tma, uint64_t stream, uint32_t simt_tile,
+         uint32_t dst_remote) {
         KvtAttnLaunch a{};
         a.simt_tile = simt_tile;
+        a.dst_remote = dst_remote;
         a.src_layers = reinterpret_cast<const uint64_t*>(src_layers);
         a.dst_layers = reinterpret_cast<const uint64_t*>(dst_layers);
         a.src_maps = reinterpret_cast<const void*>(src_maps);
@@ -157,7 +159,7 @@ void bind_kernels(py::module_& m) {
       py::arg("total_tiles"), py::arg("block_ids"), py::arg("tile_tokens"), py::arg("src_head0"),
       py::arg("dst_head0"), py::arg("n_heads"), py::arg("mode"), py::arg("status"), py::arg("done_counter"),
       py::arg("flag"), py::arg("flag_value"), py::arg("grid"), py::arg("threads"), py::arg("use_tma"),
-      py::arg("stream"), py::arg("simt_tile") = 0);
+      py::arg("stream"), py::arg("simt_tile") = 0, py::arg("dst_remote") = 0);
 
   m.def(
       "kvt_launch_p2d_state",

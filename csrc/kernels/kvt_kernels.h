@@ -91,6 +91,9 @@ typedef struct KvtAttnLaunch {
   uint64_t flag_value;         // value stored to *flag by the last CTA after a system fence
   uint32_t simt_tile;          // SIMT path: 0 / 1 = a warp per tile (device destinations), 2 = a CTA per tile
                                // (mapped host destinations: longer contiguous PCIe writes)
+  uint32_t dst_remote;         // 1: the destination is another GPU's memory.  The quantiser then stages its
+                               // output in shared memory and sends it with bulk stores (256-byte NVLink
+                               // packets); into local memory its own 16-byte stores are faster.
 } KvtAttnLaunch;
 
 // Tile count of one request for a given tile size (host helper, also used by tests).

@@ -38,6 +38,9 @@ constexpr int kMaxStages = 8;
 constexpr int kMaxDevices = 64;
 constexpr uint32_t kSmemBudget = 200 * 1024;     // bytes of dynamic shared memory we ask for at most
 constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz: bound of an mbarrier wait
+constexpr uint32_t kStagePayload = 4096;         // quantiser staging per warp: e4m3 payload of a tile ...
+constexpr uint32_t kStageScales = 256;           // ... and its scale bytes
+constexpr uint32_t kStagePerWarp = kStagePayload + kStageScales;
 
 struct TileInfo {
   uint32_t req;        // request index
@@ -152,6 +155,10 @@ __device__ __forceinline__ void tma_store_5d(const void* map, uint32_t smem_src,
       ::"l"(map), "r"(smem_src), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
       : "memory");
 }
+__device__ __forceinline__ void bulk_store_flat(void* gdst, uint32_t smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_src), "r"(bytes)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void bulk_wait_read() {
@@ -258,9 +265,13 @@ __device__ __forceinline__ void simt_copy_tile(const KvtAttnLaunch& p, const Til
 
 // bf16 source rows -> e4m3 rows + UE8M0 scales.  One thread converts 16 values (32 B in,
 // 16 B out); two neighbouring lanes form one 32-value scale group.
+// With `stage` (a warp's own shared-memory buffer, warp-per-tile mode) a full tile bound for an HND
+// destination is quantised into shared memory and leaves as one bulk copy per head (payload) plus one
+// per head (scales): the async-copy engine writes NVLink packets of 256 bytes where the warp's own
+// 16-byte stores leave as 128-byte ones (measured 615 GB/s of link for those against 705 for bulk stores).
 __device__ __forceinline__ void simt_quant_tile(const KvtAttnLaunch& p, const TileInfo& ti, uint32_t kv,
                                        const char* __restrict__ src, char* __restrict__ dst, uint32_t tid,
-                                       uint32_t nthr) {
+                                       uint32_t nthr, unsigned char* stage) {
   const uint32_t cpr = p.src.head_bytes >> 5;  // 32-byte source chunks per row (even: head_dim % 32 == 0)
   RowIter it;
   it.ntok = ti.copy_hi - ti.copy_lo;
@@ -281,6 +292,18 @@ __device__ __forceinline__ void simt_quant_tile(const KvtAttnLaunch& p, const Ti
   const bool wide_scales = (cpr & 7u) == 0u &&
                            (((uint64_t)sc_base | (uint64_t)p.dst.scale_token_stride | (uint64_t)p.dst.scale_head_stride |
                              (uint64_t)p.dst.block_stride | reinterpret_cast<uintptr_t>(dst)) & 3u) == 0u;
+  const uint32_t run_bytes = it.ntok * p.dst.head_bytes;          // one head's rows of the tile, contiguous in HND
+  const uint32_t sc_run = it.ntok * (cpr >> 1);
+  const bool staged = stage != nullptr && wide_scales && it.token_inner && nthr == 32u &&
+                      p.dst.token_stride == (int64_t)p.dst.head_bytes && p.dst.scale_token_stride == (int64_t)(cpr >> 1) &&
+                      chunks * 16u <= kStagePayload && it.ntok * it.nh * 4u <= kStageScales &&
+                      ((run_bytes | sc_run | (uint32_t)p.dst.head_stride | (uint32_t)p.dst.scale_head_stride) & 15u) == 0u &&
+                      ((reinterpret_cast<uintptr_t>(dst + d_base) | reinterpret_cast<uintptr_t>(dst + sc_base)) & 15u) == 0u;
+  if (staged) {
+    // the bulk stores of this warp's previous tile must have read the buffer before it is refilled
+    if (tid == 0) bulk_wait_read<0>();
+    __syncwarp();
+  }
   // Two rounds in flight per thread: the loads of both are issued before either is converted.
   const uint32_t rounds = (chunks + nthr - 1) / nthr;
   for (uint32_t rnd = 0; rnd < rounds; rnd += 2) {
@@ -322,7 +345,12 @@ __device__ __forceinline__ void simt_quant_tile(const KvtAttnLaunch& p, const Ti
         q.y = pack_e4m3x4(bf16lo(w[u][2]) * inv, bf16hi(w[u][2]) * inv, bf16lo(w[u][3]) * inv, bf16hi(w[u][3]) * inv);
         q.z = pack_e4m3x4(bf16lo(w[u][4]) * inv, bf16hi(w[u][4]) * inv, bf16lo(w[u][5]) * inv, bf16hi(w[u][5]) * inv);
         q.w = pack_e4m3x4(bf16lo(w[u][6]) * inv, bf16hi(w[u][6]) * inv, bf16lo(w[u][7]) * inv, bf16hi(w[u][7]) * inv);
-        st_16(dst + d_base + (int64_t)t[u] * p.dst.token_stride + (int64_t)h[u] * p.dst.head_stride + (c[u] << 4), q);
+        if (staged) {
+          // chunk i of the tile in destination order sits at byte 16 i of the buffer: rows of a head are adjacent
+          *reinterpret_cast<int4*>(stage + (((rnd + u) * nthr + tid) << 4)) = q;
+        } else {
+          st_16(dst + d_base + (int64_t)t[u] * p.dst.token_stride + (int64_t)h[u] * p.dst.head_stride + (c[u] << 4), q);
+        }
       }
       if (wide_scales) {
         // eight neighbouring lanes hold 128 values of one row = four scales: one 4-byte store instead of
@@ -332,15 +360,32 @@ __device__ __forceinline__ void simt_quant_tile(const KvtAttnLaunch& p, const Ti
         const uint32_t e2 = __shfl_sync(0xffffffffu, e, (lane & ~7u) + 4u);
         const uint32_t e3 = __shfl_sync(0xffffffffu, e, (lane & ~7u) + 6u);
         if (active[u] && (lane & 7u) == 0u) {
-          *reinterpret_cast<uint32_t*>(dst + sc_base + (int64_t)t[u] * p.dst.scale_token_stride +
-                                       (int64_t)h[u] * p.dst.scale_head_stride + (c[u] >> 1)) =
-              e | (e1 << 8) | (e2 << 16) | (e3 << 24);
+          const uint32_t packed = e | (e1 << 8) | (e2 << 16) | (e3 << 24);
+          if (staged) {
+            *reinterpret_cast<uint32_t*>(stage + kStagePayload + ((((rnd + u) * nthr + tid) / cpr) * (cpr >> 1))) = packed;
+          } else {
+            *reinterpret_cast<uint32_t*>(dst + sc_base + (int64_t)t[u] * p.dst.scale_token_stride +
+                                         (int64_t)h[u] * p.dst.scale_head_stride + (c[u] >> 1)) = packed;
+          }
         }
       } else if (active[u] && (c[u] & 1u) == 0u) {
         dst[sc_base + (int64_t)t[u] * p.dst.scale_token_stride + (int64_t)h[u] * p.dst.scale_head_stride +
             (c[u] >> 1)] = static_cast<char>(e);
       }
     }
+  }
+  if (staged) {
+    __syncwarp();
+    fence_proxy_async();          // the buffer was written through the generic proxy, the copies read it through the async one
+    if (tid == 0) {
+      for (uint32_t h = 0; h < it.nh; ++h) {
+        bulk_store_flat(dst + d_base + (int64_t)h * p.dst.head_stride, smem_u32(stage + h * run_bytes), run_bytes);
+        bulk_store_flat(dst + sc_base + (int64_t)h * p.dst.scale_head_stride, smem_u32(stage + kStagePayload + h * sc_run),
+                        sc_run);
+      }
+      bulk_commit();
+    }
+    __syncwarp();
   }
 }
 
@@ -425,13 +470,16 @@ __device__ __forceinline__ void simt_zero_tail(const KvtAttnLaunch& p, const Til
 // registers until its last warp exits, and half-empty CTAs of one launch would keep the CTAs of
 // launches on other streams off the SM.
 template <int MODE, bool USE_TMA, int GROUP>
-__device__ __forceinline__ void simt_pass(const KvtAttnLaunch& p, uint64_t total, uint32_t per_layer) {
+__device__ __forceinline__ void simt_pass(const KvtAttnLaunch& p, uint64_t total, uint32_t per_layer,
+                                          unsigned char* stage_base) {
   constexpr uint32_t kGroupThreads = GROUP > 0 ? 32u * GROUP : 0u;
   const uint32_t tid = GROUP > 0 ? (threadIdx.x % kGroupThreads) : threadIdx.x;
   const uint32_t nthr = GROUP > 0 ? kGroupThreads : blockDim.x;
   const uint32_t owners = GROUP > 0 ? (blockDim.x / kGroupThreads) : 1u;
   const uint32_t me = GROUP > 0 ? (threadIdx.x / kGroupThreads) : 0u;
   if (me >= owners) return;   // a block size that is not a multiple of the group: the odd warps sit out
+  unsigned char* stage = (GROUP == 1 && MODE == KVT_MODE_BF16_TO_MXFP8 && stage_base != nullptr)
+                             ? stage_base + (size_t)me * kStagePerWarp : nullptr;
   for (uint64_t w = (uint64_t)blockIdx.x * owners + me; w < total; w += (uint64_t)gridDim.x * owners) {
     const uint32_t layer = (uint32_t)(w / per_layer);
     const uint32_t rem = (uint32_t)(w - (uint64_t)layer * per_layer);
@@ -448,18 +496,24 @@ __device__ __forceinline__ void simt_pass(const KvtAttnLaunch& p, uint64_t total
       if constexpr (MODE == KVT_MODE_COPY) {
         if (!(USE_TMA && tile_is_full(p, ti))) simt_copy_tile(p, ti, kv, src, dst, tid, nthr);
       } else if constexpr (MODE == KVT_MODE_BF16_TO_MXFP8) {
-        simt_quant_tile(p, ti, kv, src, dst, tid, nthr);
+        simt_quant_tile(p, ti, kv, src, dst, tid, nthr, stage);
       } else {
         simt_dequant_tile(p, ti, kv, src, dst, tid, nthr);
       }
     }
     if (ti.zero_hi > ti.copy_hi) simt_zero_tail(p, ti, kv, dst, tid, nthr);
   }
+  if (stage != nullptr) {
+    // the bulk stores of the last tile must be complete before this CTA reports the launch done
+    if (tid == 0) bulk_wait_all();
+    __syncwarp();
+    fence_proxy_async();
+  }
 }
 
 // ---- the kernel ---------------------------------------------------------------------------
 template <int MODE, bool USE_TMA>
-__global__ void __launch_bounds__(512) kvt_p2d_attn_kernel(const __grid_constant__ KvtAttnLaunch p,
+__global__ void __launch_bounds__(512, 2) kvt_p2d_attn_kernel(const __grid_constant__ KvtAttnLaunch p,
                                                             const uint32_t n_stages, const uint32_t tile_bytes,
                                                             const uint32_t warp_tiles) {
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -567,12 +621,14 @@ __global__ void __launch_bounds__(512) kvt_p2d_attn_kernel(const __grid_constant
   }
 
   // SIMT pass: everything the TMA pass does not take.
+  // without TMA tiles a non-zero tile_bytes says that every warp owns a staging buffer of that size
+  unsigned char* stage_base = (!USE_TMA && tile_bytes == kStagePerWarp) ? smem : nullptr;
   if (warp_tiles == 1u) {
-    simt_pass<MODE, USE_TMA, 1>(p, total, per_layer);
+    simt_pass<MODE, USE_TMA, 1>(p, total, per_layer, stage_base);
   } else if (warp_tiles == 4u) {
-    simt_pass<MODE, USE_TMA, 4>(p, total, per_layer);
+    simt_pass<MODE, USE_TMA, 4>(p, total, per_layer, nullptr);
   } else {
-    simt_pass<MODE, USE_TMA, 0>(p, total, per_layer);
+    simt_pass<MODE, USE_TMA, 0>(p, total, per_layer, nullptr);
   }
 
   // Completion: the last CTA to finish publishes the flag after a system-scope fence, so a
@@ -637,6 +693,19 @@ cudaError_t launch_impl(const KvtAttnLaunch& a, int grid, int threads, uint32_t 
     const uint64_t owners = warps / warp_tiles;
     const uint64_t need = (total + owners - 1) / owners;
     if ((uint64_t)grid > need) grid = (int)need;
+  }
+  if (MODE == KVT_MODE_BF16_TO_MXFP8 && !USE_TMA && warp_tiles == 1u) {
+    // BLLM_KVTRANS_QUANT_STAGE: 0 = direct 16-byte stores always, 1 = staged bulk stores always; unset =
+    // staged for a remote destination (668 against 614 GB/s of link), direct for a local one (2842
+    // against 2494 GB/s of source).
+    static const int stage_env = [] {
+      const char* v = getenv("BLLM_KVTRANS_QUANT_STAGE");
+      return v == nullptr ? -1 : atoi(v);
+    }();
+    if (stage_env > 0 || (stage_env < 0 && a.dst_remote != 0)) {
+      tile_bytes = kStagePerWarp;
+      smem = (size_t)warps * kStagePerWarp;
+    }
   }
   auto kern = kvt_p2d_attn_kernel<MODE, USE_TMA>;
   if (smem > 48 * 1024) {

@@ -100,6 +100,7 @@ class NvlinkChannel : public IChannel {
     }
     RTASSERT(info.num_layers == ctx_->num_layers());
     const bool same_process = info.pid == static_cast<int32_t>(getpid());
+    dst_remote_ = info.device != ctx_->device_id();
     if (info.device != ctx_->device_id() && same_process) {
       if (!kvt_can_access_peer(ctx_->device_id(), info.device))
         throw KVTransferException(ErrorKind::TRANSPORT, "nvlink: no peer access to the destination GPU");
@@ -300,6 +301,7 @@ class NvlinkChannel : public IChannel {
       a.n_heads = params_.n_heads;
       a.mode = params_.mode;
       a.status = d_status_;
+      a.dst_remote = dst_remote_ ? 1u : 0u;
       int grid = env_nvlink_ctas();
       // four small CTAs per SM, scaled by the SM-usage knob that bounds what a transfer may take from the forward pass
       if (grid <= 0) grid = std::max(1, static_cast<int>(4 * kvt_sm_count(ctx_->device_id()) * env_kernel_copy_sm_usage()));
@@ -502,6 +504,7 @@ class NvlinkChannel : public IChannel {
   DevArray<uint64_t> d_src_layers_, d_dst_layers_;
   DevArray<TensorMapBytes> d_src_maps_, d_dst_maps_;
   size_t range_rr_{0};
+  bool dst_remote_{false};       // the destination cache lives on another GPU
   std::vector<char> stage_used_;
   uint32_t generic_rounds_{1};   // bulk copy kernel: segment rounds the longest descriptor needs
   uint32_t* d_status_{nullptr};   // 64 bytes: [0] code, [1] detail, bytes 8..15 start stamp, bytes 16..23 end stamp

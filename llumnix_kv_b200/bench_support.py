@@ -783,7 +783,7 @@ def quant_reshard_nvlink(K, rank: int, world: int, dev, tokens: int = 8192, n_la
         dst_ptrs = [peer + off + i * dst_l.layer_bytes for i in range(n_layers)]
         src = [src_l.alloc(dev, fill="normal", seed=1000 * rank + i) for i in range(n_layers)]
         xfer = AttnTransfer(src_l, dst_l, [t.data_ptr() for t in src], dst_ptrs, dev,
-                            head_map=HeadMap(0, (rank % 2) * 2, 2), mode=MODE_BF16_TO_MXFP8)
+                            head_map=HeadMap(0, (rank % 2) * 2, 2), mode=MODE_BF16_TO_MXFP8, dst_remote=True)
         streams = [torch.cuda.Stream(dev) for _ in range(n_streams)]
         holder = {"main": torch.cuda.current_stream(dev)}
         plan = xfer.plan([ReqChunk(sb, db, 0, tokens)])

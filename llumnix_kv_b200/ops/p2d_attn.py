@@ -95,7 +95,8 @@ class AttnTransfer:
 
     def __init__(self, src_layout: AttnLayout, dst_layout: AttnLayout, src_ptrs: Sequence[int],
                  dst_ptrs: Sequence[int], device, head_map: Optional[HeadMap] = None, mode: int = MODE_COPY,
-                 tile_tokens: Optional[int] = None, use_tma: bool = True, simt_tile: int = 0):
+                 tile_tokens: Optional[int] = None, use_tma: bool = True, simt_tile: int = 0,
+                 dst_remote: bool = False):
         K = _ops()
         assert len(src_ptrs) == len(dst_ptrs)
         self.K = K
@@ -105,6 +106,7 @@ class AttnTransfer:
         self.num_layers = len(src_ptrs)
         self.mode = mode
         self.simt_tile = simt_tile      # 2: a CTA per tile (mapped host memory on the other side), else a warp per tile
+        self.dst_remote = dst_remote    # the destination pointers are another GPU's memory (peer-mapped)
         self.head_map = head_map or HeadMap(0, 0, min(src_layout.num_heads, dst_layout.num_heads))
         import math
 
@@ -146,7 +148,7 @@ class AttnTransfer:
             self.src_kvt, self.dst_kvt, layer_begin, layer_end, plan.reqs_ptr, plan.n_reqs, plan.total_tiles,
             plan.block_ids_ptr, self.tile_tokens, hm.src_head0, hm.dst_head0, hm.n_heads, self.mode,
             self.status.data_ptr(), self.status.data_ptr() + 8 if flag_ptr else 0, flag_ptr, flag_value,
-            grid, threads, 1 if tma else 0, s, self.simt_tile)
+            grid, threads, 1 if tma else 0, s, self.simt_tile, 1 if self.dst_remote else 0)
 
     def check_status(self) -> Tuple[int, int]:
         st = self.status[:2].tolist()

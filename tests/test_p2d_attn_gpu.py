@@ -38,7 +38,7 @@ def _rand_chunks(rng, n_req, src_nb, dst_nb, ntpb, max_blocks, partial=True, pad
 
 
 def _run(src_l, dst_l, chunks, n_layers=3, head_map=None, mode=MODE_COPY, use_tma=True, grid=0, threads=0,
-         layer_range=None):
+         layer_range=None, dst_remote=False):
     src = [src_l.alloc(DEV, "normal", seed=10 + i) for i in range(n_layers)]
     dst = [dst_l.alloc(DEV, "normal", seed=100 + i) for i in range(n_layers)]
     if mode == MODE_MXFP8_TO_BF16:
@@ -47,7 +47,7 @@ def _run(src_l, dst_l, chunks, n_layers=3, head_map=None, mode=MODE_COPY, use_tm
             src_l.scale_view(s).copy_(torch.randint(120, 134, src_l.scale_view(s).shape, dtype=torch.uint8, device=DEV))
     expect = [d.clone() for d in dst]
     xfer = AttnTransfer(src_l, dst_l, [s.data_ptr() for s in src], [d.data_ptr() for d in dst], DEV,
-                        head_map=head_map, mode=mode, use_tma=use_tma)
+                        head_map=head_map, mode=mode, use_tma=use_tma, dst_remote=dst_remote)
     if use_tma and mode == MODE_COPY:
         assert xfer.use_tma, "tensor maps must encode on a GPU machine"
     plan = xfer.plan(chunks)
@@ -148,6 +148,23 @@ def test_layer_range_only_touches_those_layers():
     dst_l = AttnLayout(CacheShape.FLASHINFER, 32, 16, 8, 128, 2)
     chunks = _rand_chunks(rng, 3, 32, 32, 16, 4, partial=False)
     _, dst, expect = _run(src_l, dst_l, chunks, n_layers=4, layer_range=(1, 3))
+    for d, e in zip(dst, expect):
+        assert torch.equal(d, e)
+
+
+@pytest.mark.parametrize("partial", [False, True])
+@pytest.mark.parametrize("heads", [(2, 4, HeadMap(0, 2, 2)), (8, 8, None)])
+def test_bf16_to_mxfp8_staged_for_a_remote_destination(heads, partial):
+    """dst_remote=True makes the quantiser stage full HND tiles in shared memory and send them as bulk
+    stores (the form used over NVLink); tiles it cannot stage (too large: 8 heads; ragged edges) take the
+    direct stores.  Same bytes as the oracle either way."""
+    rng = random.Random(18)
+    src_h, dst_h, hm = heads
+    src_l = AttnLayout(CacheShape.FLASH, 40, 16, src_h, 128, 2)
+    dst_l = AttnLayout(CacheShape.FLASHINFER, 48, 16, dst_h, 128, 1, mx_scaled=True)
+    chunks = _rand_chunks(rng, 6, 40, 48, 16, 5, partial=partial)
+    _, dst, expect = _run(src_l, dst_l, chunks, n_layers=3, head_map=hm, mode=MODE_BF16_TO_MXFP8, use_tma=False,
+                          dst_remote=True)
     for d, e in zip(dst, expect):
         assert torch.equal(d, e)
 
