@@ -1045,6 +1045,8 @@ def mla_fanout_bandwidth(K, rank: int, world: int, dev, tokens: int = 32768, n_l
         db_r0, seq_r0 = i32(db), i32(list(range(n_blk)))
         land_src = torch.tensor([landing.data_ptr() + i * n_blk * blk for i in range(n_layers)], dtype=torch.int64, device=dev)
 
+    errors = []
+
     def timed(fn, first_step: int) -> float:
         best = 1e30
         for it in range(warmup + iters):
@@ -1052,7 +1054,10 @@ def mla_fanout_bandwidth(K, rank: int, world: int, dev, tokens: int = 32768, n_l
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            fn(first_step + it)
+            try:
+                fn(first_step + it)
+            except Exception as ex:   # keep every rank in step: the memory is bound to a multicast object
+                errors.append(f"rank {rank}: {type(ex).__name__}: {ex}"[:300])
             e1.record()
             torch.cuda.synchronize()
             t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
@@ -1061,7 +1066,6 @@ def mla_fanout_bandwidth(K, rank: int, world: int, dev, tokens: int = 32768, n_l
                 best = min(best, float(t.item()))
         return best
 
-    errors = []
     ms_uni = ms_nvls = ms_scatter = 0.0
     try:
         ms_uni = timed(run_unicast, 1)
