@@ -13,6 +13,7 @@
 #include <unistd.h>
 
 #include <atomic>
+#include <future>
 #include <sstream>
 
 #include "core/envcfg.h"
@@ -110,6 +111,7 @@ class HostChannel : public IChannel {
     char* blob_base = nullptr;
     uint64_t blob_dev = 0;
     size_t blob_cap = 0;
+    TxSlot* slot = nullptr;
     size_t meta_bytes = head.size();
     for (size_t t = 0; t < data_.size(); ++t) meta_bytes += 2 * sizeof(size_t) + data_[t].size() * sizeof(IpcBlock);
     if (use_shm_) {
@@ -117,11 +119,19 @@ class HostChannel : public IChannel {
       blob_dev = shm_dev_;
       blob_cap = shm_bytes_;
     } else {
-      // one pinned (GPU source) or plain buffer holding metadata and blobs contiguously
-      tx_.reserve(meta_bytes + inline_bytes, stage_ != nullptr);
-      blob_base = tx_.data();
-      blob_dev = tx_.device_ptr();
-      blob_cap = tx_.capacity();
+      // One frame buffer per connection, pinned when the source is a GPU, holding metadata and blobs
+      // contiguously.  The connection's previous frame must have been acknowledged before its buffer is
+      // refilled; frames on the other connections are still on their way meanwhile.
+      if (slots_.size() != socks_.size()) {
+        slots_.clear();
+        for (size_t i = 0; i < socks_.size(); ++i) slots_.emplace_back(std::make_unique<TxSlot>());
+      }
+      slot = slots_[rr_ % slots_.size()].get();
+      wait_slot(*slot);
+      slot->buf.reserve(meta_bytes + inline_bytes, stage_ != nullptr);
+      blob_base = slot->buf.data();
+      blob_dev = slot->buf.device_ptr();
+      blob_cap = slot->buf.capacity();
     }
     std::string meta = head;
     size_t cursor = use_shm_ ? seg_off : 0;  // offset inside blob_base where the next blob goes
@@ -184,7 +194,7 @@ class HostChannel : public IChannel {
       shm_cursor_ = cursor;
     } else {
       // write metadata pieces between the already gathered blobs
-      char* p = tx_.data();
+      char* p = slot->buf.data();
       memcpy(p, head.data(), head.size());
       p += head.size();
       for (size_t t = 0; t < data_.size(); ++t) {
@@ -197,22 +207,47 @@ class HostChannel : public IChannel {
         p += sizeof(size_t);
         p += blob_bytes_[t];
       }
-      ok = send_frame(sock.fd(), tx_.data(), static_cast<size_t>(p - tx_.data()), env_rpc_timeout_s() * 1000);
+      // the frame leaves, and its acknowledgement comes back, on a thread of its own: the next layer is
+      // gathered and sent on another connection meanwhile
+      const int fd = sock.fd();
+      const char* frame = slot->buf.data();
+      const size_t frame_bytes = static_cast<size_t>(p - slot->buf.data());
+      const int timeout_ms = env_rpc_timeout_s() * 1000;
+      slot->layer = layer;
+      slot->fut = std::async(std::launch::async, [fd, frame, frame_bytes, timeout_ms, reqid]() -> int64_t {
+        if (!send_frame(fd, frame, frame_bytes, timeout_ms)) {
+          throw KVTransferException(ErrorKind::TRANSPORT, "tcp send failed, errno=" + std::to_string(errno));
+        }
+        std::string resp;
+        if (!recv_frame(fd, resp, timeout_ms)) throw KVTransferException(ErrorKind::TIMEOUT, "tcp ack timeout/closed");
+        uint32_t magic = 0, status = WIRE_INTERNAL;
+        uint64_t got = 0;
+        int64_t us = 0;
+        if (resp.size() >= RPC_HEADER + 4) {
+          get_rpc_header(resp.data(), &magic, &got);
+          memcpy(&status, resp.data() + RPC_HEADER, 4);
+          if (resp.size() >= RPC_HEADER + 12) memcpy(&us, resp.data() + RPC_HEADER + 4, 8);
+        }
+        if (status != WIRE_OK || got != reqid) {
+          throw KVTransferException(ErrorKind::TRANSPORT, "tcp receiver rejected the layer, status=" + std::to_string(status));
+        }
+        return us;
+      });
+      send_us_ += tw.get_elapse_us();
+      return;
     }
     if (!ok) {
       active_ = false;
       throw KVTransferException(ErrorKind::TRANSPORT, std::string(name()) + " send failed, errno=" + std::to_string(errno));
     }
-    pending_.push_back(Pending{reqid, &sock, layer});
-    // A TCP frame reuses tx_ for the next layer, so wait for this layer's ack first; shm slots
-    // are distinct until the ring wraps.
-    if (!use_shm_) drain(0);
+    pending_.push_back(Pending{reqid, &sock, layer});   // shm slots are distinct until the ring wraps
     send_us_ += tw.get_elapse_us();
   }
 
   void flush(std::string& out) override {
     TimeWatch tw;
     drain(0);
+    for (auto& sl : slots_) wait_slot(*sl);
     std::ostringstream ss;
     ss << "Proto=" << name() << (cast_ ? ",Cast=bf16->e4m3" : "") << ",OriginSbNum=" << origin_blocks_ << ",MergedSbNum=" << merged_blocks_
        << ",SbSizeMin=" << (sb_min_ == SIZE_MAX ? 0 : sb_min_) << ",SbSizeMax=" << sb_max_ << ",SbSizeTotal=" << sb_total_
@@ -225,6 +260,13 @@ class HostChannel : public IChannel {
   bool is_active() override { return active_; }
 
   void close() override {
+    for (auto& sl : slots_) {
+      try {
+        if (sl->fut.valid()) sl->fut.get();   // the sender thread uses the socket and the buffer
+      } catch (const std::exception&) {
+      }
+    }
+    slots_.clear();
     socks_.clear();
     active_ = false;
     if (shm_base_ != nullptr) {
@@ -244,6 +286,21 @@ class HostChannel : public IChannel {
     FdGuard* sock;
     size_t layer;
   };
+  struct TxSlot {
+    PinnedBuffer buf;
+    std::future<int64_t> fut;   // valid while a frame of this connection is unacknowledged
+    size_t layer{0};
+  };
+
+  void wait_slot(TxSlot& sl) {
+    if (!sl.fut.valid()) return;
+    try {
+      recv_us_max_ = std::max(recv_us_max_, sl.fut.get());
+    } catch (const std::exception& ex) {
+      active_ = false;
+      throw KVTransferException(ErrorKind::TRANSPORT, std::string(ex.what()) + " (layer " + std::to_string(sl.layer) + ")");
+    }
+  }
 
   static void kvt_host_unregister_(char* p) { kvt_host_unregister(reinterpret_cast<uint64_t>(p)); }
 
@@ -345,7 +402,7 @@ class HostChannel : public IChannel {
   std::vector<std::vector<IpcBlock>> data_;
   std::vector<size_t> blob_bytes_;
   bool cast_{false};   // gather casts bf16 -> e4m3 (descriptor lengths are fp8 bytes)
-  PinnedBuffer tx_;
+  std::vector<std::unique_ptr<TxSlot>> slots_;   // TCP: one frame buffer and one sender per connection
   std::string msg_buf_;
   std::vector<Pending> pending_;
   size_t origin_blocks_{0}, merged_blocks_{0}, sb_min_{0}, sb_max_{0}, sb_total_{0};
