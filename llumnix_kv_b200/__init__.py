@@ -35,8 +35,12 @@ def load_ops(build_if_missing: bool = True):
 
 
 def set_envs() -> None:
-    """Default environment of the native engine (role of blade_kvt/__init__.py:42-61)."""
-    os.environ.setdefault("BLLM_KVTRANS_RDMA_SP", "2")
+    """Default environment of the native engine (role of blade_kvt/__init__.py:42-61; the ACCL_* settings
+    of the reference configure its RDMA library and have no reader here).  The backends call this before
+    they create a transfer client or server (kvtbackend.py:524-525 of the reference)."""
+    os.environ.setdefault("BLLM_KVTRANS_FSNAMING_KEEPALIVE_S", "36000")
+    os.environ.setdefault("BLLM_KVTRANS_FSNAMING_TOLERATE_S", "360000")
+    os.environ.setdefault("BLLM_KVTRANS_RDMA_SP", "2")      # connections per target of the TCP / SHM transports
     os.environ.setdefault("BLLM_KVTRANS_SDH_KIND", "2")
 
 

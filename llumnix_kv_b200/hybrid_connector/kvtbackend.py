@@ -712,8 +712,10 @@ class PBackend(HybridBackend):
 
     # ---- worker side ---------------------------------------------------------------------------------
     def register_kv_caches(self, kv_caches: dict) -> None:
+        import llumnix_kv_b200
         from llumnix_kv_b200.kv_transfer_impl import KVTransferClient
 
+        llumnix_kv_b200.set_envs()
         args = build_kvt_args(self, kv_caches, self._worker.get_tensor_model_parallel_rank())
         self._kvt_cli = KVTransferClient(send_done_addr=self._send_done_addr, **args)
         self._layer_index = {name: extract_layer_index(name) for name in kv_caches}
@@ -1101,8 +1103,10 @@ class DBackend(HybridBackend):
 
     # ---- worker side -----------------------------------------------------------------------------------
     def register_kv_caches(self, kv_caches: dict) -> None:
+        import llumnix_kv_b200
         from llumnix_kv_b200.kv_transfer_impl import KVTransferServer
 
+        llumnix_kv_b200.set_envs()
         rank = self._worker.get_tensor_model_parallel_rank()
         args = build_kvt_args(self, kv_caches, rank)
         self._kvt_srv = KVTransferServer(mx_scaled=self._cfg.cache_config.mx_scaled, **args)
