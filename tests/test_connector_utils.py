@@ -196,3 +196,16 @@ def test_role_and_model_probes():
     hybrid = make_cfg("kv_consumer", "H", gdn_groups=3)
     assert ep.is_statemodel(hybrid) and not ep.is_statemodel(d)
     assert not ep.use_kvt_decode_prefix_cache(d)
+
+
+def test_set_envs_fills_defaults_without_overriding(monkeypatch):
+    import os
+
+    import llumnix_kv_b200 as pkg
+
+    monkeypatch.delenv("BLLM_KVTRANS_RDMA_SP", raising=False)
+    monkeypatch.setenv("BLLM_KVTRANS_FSNAMING_KEEPALIVE_S", "7")
+    pkg.set_envs()
+    assert os.environ["BLLM_KVTRANS_RDMA_SP"] == "2"                 # two connections per target, as the reference's Python layer
+    assert os.environ["BLLM_KVTRANS_FSNAMING_KEEPALIVE_S"] == "7"    # what the operator set stays
+    monkeypatch.delenv("BLLM_KVTRANS_RDMA_SP", raising=False)
