@@ -64,6 +64,37 @@ def test_two_gpus_one_process():
         srv.stop()
 
 
+def test_two_gpus_fp8_destination_takes_the_staged_quantiser():
+    """Prefill TP=4 rank 1 on cuda:0 (2 of 8 heads, bf16, NHD) -> decode TP=2 rank 0 on cuda:1 (4 heads,
+    block-scaled e4m3, HND).  The channel marks the destination remote, so full tiles leave through the
+    quantiser's shared-memory staging and bulk stores; the bytes must equal the oracle's."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from llumnix_kv_b200.ops.layouts import AttnLayout, CacheShape
+    from llumnix_kv_b200.ops.p2d_attn import MODE_BF16_TO_MXFP8, HeadMap
+
+    src_l = AttnLayout(CacheShape.FLASH, 40, 16, 2, 128, 2)
+    dst_l = AttnLayout(CacheShape.FLASHINFER, 40, 16, 4, 128, 1, mx_scaled=True)
+    src = [src_l.alloc("cuda:0", "normal", seed=40 + i) for i in range(L)]
+    dst = [dst_l.alloc("cuda:1") for _ in range(L)]
+    srv = KVTransferServer("D|0|2", 2, 0, 0, dst_l.block_bytes, dst_l.token_bytes, "fake://", dst, [PT.NVLINK],
+                           num_kv_heads=8, cache_shape=5, mx_scaled=True)
+    cli = KVTransferClient("P|0|4", 4, 1, 1, src_l.block_bytes, src_l.token_bytes, "fake://", src, [PT.NVLINK],
+                           num_kv_heads=8, cache_shape=2)
+    try:
+        reqs = [("a", [3, 9, 1], [7, 2, 30], 48), ("b", [5, 6], [11, 4], 21), ("c", [20], [21], 16)]
+        _send(cli, "D|0|2", srv.worker_info(), reqs)
+        torch.cuda.synchronize(0)
+        torch.cuda.synchronize(1)
+        chunks = [ReqChunk(sb, db, 0, t) for _, sb, db, t in reqs]
+        for i in range(L):
+            expect = torch.zeros_like(dst[i], device="cuda:0")
+            reference_transfer(src_l, dst_l, src[i], expect, chunks, HeadMap(0, 2, 2), MODE_BF16_TO_MXFP8)
+            assert torch.equal(dst[i].to("cuda:0"), expect)
+    finally:
+        srv.stop()
+
+
 def _decode_proc(naming_dir, ready, go, result):
     os.environ["BLLM_KVTRANS_QUIET_ENV"] = "1"
     # no NVLS / multicast anywhere in this test: plain peer stores, so that a peer process leaving
