@@ -39,7 +39,10 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "memcpy_peer", "nccl"],
+                    help="ours: the fused transfer kernel; reference: the reference's own data path; memcpy_peer: the CPU "
+                         "planner's merged IpcBlocks, one cudaMemcpyAsync each, into the peer cache (NHD->NHD); nccl: gather "
+                         "kernel -> NCCL send/recv -> scatter kernel.  The last two are library baselines.")
     ap.add_argument("--tokens", type=int, default=8192, help="prompt tokens per request")
     ap.add_argument("--requests", type=int, default=1, help="requests per step")
     ap.add_argument("--slots", type=int, default=4, help="distinct request slots cycled through (each larger than L2)")
@@ -48,10 +51,16 @@ def parse_args():
     ap.add_argument("--streams", type=int, default=8, help="transfer streams the layers alternate over")
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--small", action="store_true", help="tiny case for profiler captures")
-    ap.add_argument("--mode", default="p2d", choices=["p2d", "kvstore", "migration", "ttft", "quant", "gdn", "mla", "fanout"],
+    ap.add_argument("--mode", default="p2d", choices=["p2d", "kvstore", "migration", "ttft", "quant", "gdn", "mla", "fanout", "linkprobe"],
                     help="p2d: prefill->decode transfer (the headline); kvstore: host-DRAM store save/load GB/s; "
                          "migration: decode->decode latency against the number of blocks; fanout (4 or 8 GPUs): replicated "
-                         "MLA pages to a decode TP group, unicast against the NVLS relay")
+                         "MLA pages to a decode TP group, unicast against the NVLS relay; linkprobe: the transfer "
+                         "kernel's GB/s for every store form, pipeline depth and grid, next to the copy engine's")
+    ap.add_argument("--ahead", type=int, default=1,
+                    help="end-to-end number: steps the engine thread may run ahead of the transfers (0: wait for every "
+                         "step's completion record before submitting the next)")
+    ap.add_argument("--min-seconds", type=float, default=1.0,
+                    help="repeat the timed region of --steps steps until this much device time has been measured")
     ap.add_argument("--prompt-mix", action="store_true",
                     help="ttft mode: prompt lengths uniform in [tokens/8, 4*tokens] (1k-32k by default) instead of fixed")
     ap.add_argument("--graph", action="store_true",
@@ -139,7 +148,7 @@ def main():
     import torch.distributed as dist
 
     import llumnix_kv_b200
-    from llumnix_kv_b200.bench_support import PDBenchPair
+    from benchmarks.support import PDBenchPair
 
     K = llumnix_kv_b200.load_ops()
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -156,10 +165,10 @@ def main():
         args.tokens, args.slots, args.layers = 2048, 2, 4
 
     if args.mode == "quant":
-        from llumnix_kv_b200.bench_support import quant_reshard_bandwidth
+        from benchmarks.support import quant_reshard_bandwidth
 
         if world > 1:
-            from llumnix_kv_b200.bench_support import quant_reshard_nvlink
+            from benchmarks.support import quant_reshard_nvlink
 
             res = quant_reshard_nvlink(K, rank, world, dev, tokens=2048 if args.small else args.tokens,
                                        n_layers=8 if args.small else 80)
@@ -179,7 +188,7 @@ def main():
                                                   "NHD -> HND", "seq_len": args.tokens}, "result": res}))
         return
     if args.mode == "kvstore":
-        from llumnix_kv_b200.bench_support import kvstore_bandwidth
+        from benchmarks.support import kvstore_bandwidth
 
         res = kvstore_bandwidth(dev, n_layers=args.layers, n_blocks=256 if args.small else 1024)
         if rank == 0:
@@ -188,7 +197,7 @@ def main():
                               "result": res}))
         return
     if args.mode in ("gdn", "mla"):
-        from llumnix_kv_b200.bench_support import hybrid_state_bandwidth
+        from benchmarks.support import hybrid_state_bandwidth
 
         res = hybrid_state_bandwidth(K, rank, world, dev, which=args.mode, tokens=2048 if args.small else 32768,
                                      steps=args.steps if args.steps != 20 else 10, warmup=args.warmup, small=args.small)
@@ -203,7 +212,7 @@ def main():
             dist.destroy_process_group()
         return
     if args.mode == "fanout":
-        from llumnix_kv_b200.bench_support import mla_fanout_bandwidth
+        from benchmarks.support import mla_fanout_bandwidth
 
         assert world >= 3, "--mode fanout needs --gpus 4 or 8 (one prefill GPU, a decode TP group on the others)"
         res = mla_fanout_bandwidth(K, rank, world, dev, tokens=4096 if args.small else 32768, n_layers=8 if args.small else 61)
@@ -218,7 +227,7 @@ def main():
         dist.destroy_process_group()
         return
     if args.mode == "ttft":
-        from llumnix_kv_b200.bench_support import ttft_added
+        from benchmarks.support import ttft_added
 
         res = ttft_added(K, rank, world, dev, tokens=512 if args.small else args.tokens, iters=max(args.steps, 5),
                          warmup=args.warmup, tiny=args.small, mix=args.prompt_mix)
@@ -243,7 +252,7 @@ def main():
             dist.destroy_process_group()
         return
     if args.mode == "migration":
-        from llumnix_kv_b200.bench_support import migration_sweep
+        from benchmarks.support import migration_sweep
         from llumnix_kv_b200.ops.layouts import CacheShape
 
         blocks = 256 if args.small else 4096
@@ -266,85 +275,131 @@ def main():
             dist.destroy_process_group()
         return
 
+    from benchmarks import baselines as BL
+    from llumnix_kv_b200.ops.layouts import CacheShape as _CS
+
     staged = args.transport != "nvlink"
+    baseline_arm = args.impl in ("memcpy_peer", "nccl")
     if staged:
         assert world == 1, "--transport shm|tcp measures the host-staged fallbacks on one GPU"
         args.e2e_only, args.e2e_path = True, "engine"
-    from llumnix_kv_b200.ops.layouts import CacheShape as _CS
-
+    same_layout = staged or args.impl == "memcpy_peer"      # byte-range paths keep the layout
     pair = PDBenchPair(K, rank, world, dev, tokens=args.tokens, requests=args.requests, slots=args.slots,
                        n_layers=args.layers, use_tma=not args.no_tma, grid=args.grid, n_streams=args.streams,
-                       **({"dst_shape": _CS.FLASH} if staged else {}))   # the byte-range transports keep the layout
-
+                       **({"dst_shape": _CS.FLASH} if same_layout else {}))
     pair.layers_per_launch = args.layers_per_launch
+    sampler = lambda: ClockSampler(local_rank)
+    ceilings = BL.measure_ceilings(pair)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    def roofline(per_pair: float) -> dict:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except OSError:
+            pass
+        out = {"measured_in_run": ceilings}
+        if staged:
+            roof = ceilings.get("pinned_h2d_GBps") or 0.0
+            out.update(peak_GBps_per_pair=roof, what="pinned cudaMemcpyAsync host->device measured in this run "
+                                                       "(both hops of the staged path overlap)")
+        elif world == 1:
+            roof = peaks.get("hbm_gbs", 6650.0) / 2.0  # a copy reads and writes every payload byte
+            out.update(peak_GBps_per_pair=roof, what="hbm_copy/2 " + ("of measured" if peaks else "of fallback"),
+                       fraction_of_copy_engine_in_run=round(per_pair / ceilings["local_copy_GBps"], 3)
+                       if ceilings.get("local_copy_GBps") else None)
+        else:
+            roof = ceilings.get("peer_copy_GBps") or 0.0
+            out.update(peak_GBps_per_pair=roof, what="copy-engine peer copy per direction measured in this run",
+                       fraction_of_nominal_900=round(per_pair / 900.0, 3))
+        out["fraction"] = round(per_pair / roof, 3) if roof else None
+        return out
 
-    def timed(run_step, steps, warmup):
-        for i in range(warmup):
-            run_step(i)
-        barrier()
-        sampler = ClockSampler(local_rank)
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ev0.record(pair.stream)
-        for i in range(steps):
-            run_step(warmup + i)
-        ev1.record(pair.stream)
-        torch.cuda.synchronize()
-        ms = ev0.elapsed_time(ev1) if pair.is_sender else 0.0
-        clocks = sampler.stop()
-        barrier()
+    if args.mode == "linkprobe":
+        rows = BL.link_probe(pair)
+        checked = pair.verify()
+        if rank == 0:
+            best = max(rows, key=lambda r: r["per_pair_GBps"])
+            print(json.dumps({"metric": "p2d_store_form_probe_GBps", "unit": "GB/s per pair, kernel-only", "n_gpus": args.gpus,
+                              "config": {"model": MODEL, "seq_len": args.tokens, "layers": args.layers,
+                                         "transport": pair.transport_name},
+                              "measured_in_run": ceilings, "best": best, "layers_verified": checked, "rows": rows}))
         if world > 1:
-            t = torch.tensor([ms], dtype=torch.float64, device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms, clocks
+            dist.destroy_process_group()
+        return
+
+    if baseline_arm:
+        res = (BL.memcpy_peer_arm if args.impl == "memcpy_peer" else BL.nccl_arm)(pair, args.steps, args.warmup, sampler)
+        stat = BL.summarize(res["regions"], args.steps)
+        ms_step = stat["ms_per_step_median"]
+        value = pair.n_pairs * pair.bytes_per_step / (ms_step * 1e-3) / 1e9 if ms_step > 0 else 0.0
+        if rank == 0:
+            print(json.dumps({
+                "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic N(0,1) KV, random block tables", "impl": args.impl,
+                "config": {"model": MODEL.replace("NHD->HND", "NHD->NHD") if same_layout else MODEL,
+                           "global_batch": args.requests * pair.n_pairs, "seq_len": args.tokens,
+                           "parallelism": f"{pair.n_pairs}P->{pair.n_pairs}D tp1" if world > 1 else "1 GPU loopback pair",
+                           "layers": args.layers, "api": res["api"], "transport": pair.transport_name,
+                           "l2": f"inputs larger than L2: {pair.slot_bytes >> 20} MiB per step, {args.slots} slots cycled"},
+                "per_pair_GBps": round(value / pair.n_pairs, 2), "timing": stat, "roofline": roofline(value / pair.n_pairs),
+                "clocks": res["clocks"], "copies_per_step": res.get("copies_per_step"), "gpu_launches": 0,
+                "layers_verified": args.layers}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     if args.graph and not args.e2e_only:
         pair.build_graphs()
     # ---- kernel-only number: descriptors resident on the device, device-timed -----------
-    ms_dev, clocks = (0.0, {}) if args.e2e_only else timed(pair.step_device, args.steps, args.warmup)
+    if args.e2e_only:
+        dev_regions, clocks = [], {}
+    else:
+        dev_regions, clocks = BL.timed_reps(pair.step_device, args.steps, args.warmup, pair.stream, world, dev,
+                                            pair.is_sender, args.min_seconds, sampler_factory=sampler)
     # ---- end to end through the public API: pinned block tables -> H2D, 32 per-layer
     #      launches, completion word + status read back on the host every step ------------
+    sync_stat = None
     if args.e2e_path == "engine":
         pair.setup_engine(args.transport)
-        barrier()
-        ms_e2e, clocks_e2e = timed(pair.step_engine, args.steps, args.warmup)
+        # every step waits for its own completion record before the next one is submitted ...
+        pair.engine_ahead = 0
+        sync_regions, _ = BL.timed_reps(pair.step_engine, args.steps, args.warmup, pair.stream, world, dev,
+                                        pair.is_sender, args.min_seconds / 2, end_region=pair.finish_engine)
+        sync_stat = BL.summarize(sync_regions, args.steps)
+        # ... and the way a serving engine drives it: the next step is submitted while the previous one still
+        # transfers; each step reads the completion record of the step before it, the region ends with all read
+        pair.engine_ahead = 0 if staged else args.ahead
+        e2e_regions, clocks_e2e = BL.timed_reps(pair.step_engine, args.steps, args.warmup, pair.stream, world, dev,
+                                                pair.is_sender, args.min_seconds, sampler_factory=sampler,
+                                                end_region=pair.finish_engine)
         h2d_bytes, d2h_bytes = pair.engine_h2d_bytes, pair.engine_d2h_bytes
-        e2e_api = "KVTransferClient.submit_req_send2/start_send_step/record_event x layers/flush_send_step/drain"
+        e2e_api = pair.engine_api
     else:
-        ms_e2e, clocks_e2e = timed(pair.step_e2e, args.steps, args.warmup)
+        e2e_regions, clocks_e2e = BL.timed_reps(pair.step_e2e, args.steps, args.warmup, pair.stream, world, dev,
+                                                pair.is_sender, args.min_seconds, sampler_factory=sampler)
         h2d_bytes, d2h_bytes = pair.h2d_bytes_per_step, pair.d2h_bytes_per_step
         e2e_api = "AttnTransfer.plan/launch x layers + completion flag + status read"
-    pair.verify()
+    layers_verified = pair.verify()
+    post = None
     if args.e2e_path == "engine":
         pair.close_engine()
+    if world >= 4 and not staged and not args.small:
+        from benchmarks.support import post_checks
+
+        post = post_checks(K, rank, world, dev)     # untimed: TP-mismatch + MXFP8 and hybrid requests through the engine
 
     n_pairs = pair.n_pairs
     bytes_per_step = pair.bytes_per_step
-    agg = lambda ms: (n_pairs * bytes_per_step * args.steps / (ms * 1e-3) / 1e9) if ms > 0 else 0.0
-    value = agg(ms_dev) if not args.e2e_only else agg(ms_e2e)
-    peaks = {}
-    try:
-        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-    except OSError:
-        pass
-    if staged:
-        roof = 55.6
-        roof_name = "pinned cudaMemcpy host->device, measured 55.6 GB/s on this pool (device->host 57.2): both hops overlapped"
-    elif world == 1:
-        roof = peaks.get("hbm_gbs", 6650.0) / 2.0  # a copy reads and writes every payload byte
-        roof_name = "hbm_copy/2 " + ("of measured" if peaks else "of fallback")
-    else:
-        roof = 770.0
-        roof_name = "nvlink peer copy per direction (measured 770 GB/s)"
+    dev_stat = BL.summarize(dev_regions, args.steps) if dev_regions else None
+    e2e_stat = BL.summarize(e2e_regions, args.steps)
+    agg = lambda st: (n_pairs * bytes_per_step / (st["ms_per_step_median"] * 1e-3) / 1e9) if st and st["ms_per_step_median"] > 0 else 0.0
+    head_stat = dev_stat if not args.e2e_only else e2e_stat
+    value = agg(head_stat)
     if rank == 0:
         out = {
             "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": round((ms_dev if not args.e2e_only else ms_e2e) / args.steps, 4),
+            "warmup": args.warmup, "ms_per_step": head_stat["ms_per_step_median"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic N(0,1) KV, random block tables",
             "impl": "ours",
@@ -358,20 +413,27 @@ def main():
                            "one launch per layer from the host" if args.layers_per_launch == 1 else
                            f"one launch per {args.layers_per_launch} layers from the host"),
                        "scaling_note": "N=1 is a same-GPU loopback bounded by HBM; N>=2 are N/2 one-directional "
-                                       "NVLink pairs bounded by 770 GB/s measured per direction: compare N=2,4,8 "
-                                       "with one another"},
+                                       "NVLink pairs bounded by the link: compare N=2,4,8 with one another"},
             "per_pair_GBps": round(value / n_pairs, 2),
-            "roofline": {"peak_GBps_per_pair": roof, "what": roof_name,
-                         "fraction": round(value / n_pairs / roof, 3)},
+            "reps": head_stat["reps"], "timing": head_stat,
+            "roofline": roofline(value / n_pairs),
             "clocks": clocks or clocks_e2e,
-            "e2e": {"value": round(agg(ms_e2e), 2), "unit": "GB/s", "ms_per_step": round(ms_e2e / args.steps, 4),
+            "e2e": {"value": round(agg(e2e_stat), 2), "unit": "GB/s", "ms_per_step": e2e_stat["ms_per_step_median"],
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "api": e2e_api,
-                    "clocks": clocks_e2e},
+                    "timing": e2e_stat, "clocks": clocks_e2e, "steps_in_flight": (0 if staged else args.ahead) + 1,
+                    "one_step_at_a_time": None if sync_stat is None else {
+                        "value": round(agg(sync_stat), 2), "ms_per_step": sync_stat["ms_per_step_median"],
+                        "what": "the same steps, each waiting for its own completion record before the next is submitted"},
+                    "fraction_of_kernel_only": round(agg(e2e_stat) / value, 3) if value > 0 else None},
+            "layers_verified": layers_verified,
             # kernel-only region: one launch per --layers-per-launch layers; end-to-end region: one per layer plus
-            # the plan upload's copy; both regions are timed unless --e2e-only
-            "gpu_launches": ((0 if args.e2e_only else -(-pair.launches_per_step // args.layers_per_launch)) +
-                             pair.launches_per_step) * args.steps + args.steps,
+            # the plan upload's copy and the completion record; both regions are timed unless --e2e-only
+            "gpu_launches": ((0 if args.e2e_only else -(-pair.launches_per_step // args.layers_per_launch) *
+                              (dev_stat["reps"] if dev_stat else 0)) +
+                             (pair.launches_per_step + 1) * e2e_stat["reps"]) * args.steps,
         }
+        if post is not None:
+            out["post_checks"] = post
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()

@@ -16,8 +16,8 @@ from typing import List
 
 import torch
 
-from .ops.layouts import AttnLayout, CacheShape
-from .ops.p2d_attn import AttnTransfer, ReqChunk
+from llumnix_kv_b200.ops.layouts import AttnLayout, CacheShape
+from llumnix_kv_b200.ops.p2d_attn import AttnTransfer, ReqChunk
 
 BLOCK = 16
 KV_HEADS = 8
@@ -74,23 +74,31 @@ class PDBenchPair:
             for i in range(n_layers):
                 self._fill_layer(self.src, i, self._pair_id())
         dst_ptrs = None
+        # a landing area for the copy-engine ceiling measured inside the run (never read back)
+        self.probe_bytes = min(1 << 30, n_layers * self.src_l.layer_bytes)
+        self.probe = None
         if self.is_receiver:
             self.dst = torch.zeros(n_layers * self.dst_l.layer_bytes, dtype=torch.uint8, device=dev)
+            self.probe = torch.empty(self.probe_bytes, dtype=torch.uint8, device=dev)
         if self.loopback:
             dst_ptrs = [self.dst.data_ptr() + i * self.dst_l.layer_bytes for i in range(n_layers)]
+            self.probe_dst_ptr = self.probe.data_ptr()
             self.transport_name = "local HBM (same GPU)"
         else:
             mine = None
             if self.is_receiver:
                 h, base, _size = K.kvt_ipc_get_handle(self.dst.data_ptr())
-                mine = (h, self.dst.data_ptr() - base)
+                h2, base2, _size2 = K.kvt_ipc_get_handle(self.probe.data_ptr())
+                mine = (h, self.dst.data_ptr() - base, h2, self.probe.data_ptr() - base2)
             infos = [None] * world
             dist.all_gather_object(infos, mine)
             if self.is_sender:
-                h, off = infos[rank + self.n_pairs]
+                h, off, h2, off2 = infos[rank + self.n_pairs]
                 self.peer_base = K.kvt_ipc_open_handle(h)
+                self.probe_dst_ptr = (self.peer_base if h2 == h else K.kvt_ipc_open_handle(h2)) + off2
                 dst_ptrs = [self.peer_base + off + i * self.dst_l.layer_bytes for i in range(n_layers)]
             self.transport_name = "NVLink P2P stores into CUDA-IPC mapped peer cache"
+        self.dst_layer_ptrs = dst_ptrs
 
         self.xfer = None
         self.h2d_bytes_per_step = 0
@@ -196,7 +204,7 @@ class PDBenchPair:
         """KVTransferServer on the decode rank, KVTransferClient on the prefill rank, NVLink
         transport (or one of the host-staged ones: "shm", "tcp"); the WorkerInfo string travels the
         way a decode engine hands it to a prefill engine inside a request."""
-        from .kv_transfer_impl import KVTransferClient, KVTransferProtocolType as PT, KVTransferServer
+        from llumnix_kv_b200.kv_transfer_impl import KVTransferClient, KVTransferProtocolType as PT, KVTransferServer
 
         proto = {"nvlink": PT.NVLINK, "shm": PT.SHM, "tcp": PT.TCP}[transport]
         if transport != "nvlink":
@@ -228,8 +236,13 @@ class PDBenchPair:
             self.cli = KVTransferClient(f"P{pair}|0|1", 1, 0, 0, self.src_l.block_bytes, self.src_l.token_bytes, "fake://",
                                         layers, [proto], num_kv_heads=KV_HEADS, cache_shape=int(self.src_l.shape))
         self.engine_seq = 0
+        self.engine_ahead = 0
         self.engine_h2d_bytes = self.h2d_bytes_per_step
-        self.engine_d2h_bytes = 8      # the channel reads its two status words back before it reports a batch done
+        # the channel's completion record (sequence number, two status words, two GPU timer stamps) lands in
+        # mapped host memory behind each batch; the host reads it to report the requests done
+        self.engine_d2h_bytes = 32
+        self.engine_api = ("KVTransferClient.submit_req_send2/start_send_step/record_event x layers/flush_send_step, "
+                           "then wait_step_done(): the completion record of the step read on the host")
 
     def step_engine(self, i: int) -> None:
         """What a prefill worker does in one engine step, through KVTransferClient: submit the
@@ -249,14 +262,26 @@ class PDBenchPair:
         for layer in range(self.n_layers):
             cli.record_event(layer, self.stream)
         cli.flush_send_step()
-        cli.drain()
+        # read completion records on the host: this step's (ahead == 0) or, running one step ahead of the
+        # transfers as a serving engine does, the previous step's
+        if not cli.wait_inflight(self.engine_ahead, 30.0):
+            raise RuntimeError("a transfer step did not complete in 30 s")
+
+    def finish_engine(self) -> None:
+        """End of a timed region: every step's completion record has been read."""
+        if getattr(self, "cli", None) is not None and not self.cli.wait_inflight(0, 30.0):
+            raise RuntimeError("transfer steps did not complete in 30 s")
 
     def close_engine(self) -> None:
         if getattr(self, "srv", None) is not None:
             self.srv.stop()
 
     # ---- correctness after the timed runs ---------------------------------------------------
-    def verify(self, layers=(0,)) -> None:
+    def verify(self, layers=None) -> int:
+        """Compares the decode cache with the prefill cache for every slot a step touched: every layer
+        (or the given ones), every full block, and the tokens of a partial last block one by one.  The
+        decode rank of a pair regenerates the prefill rank's cache from its seed.  Returns the number
+        of layers compared; raises on the first difference."""
         torch.cuda.synchronize()
         if self.world > 1:
             import torch.distributed as dist
@@ -270,19 +295,20 @@ class PDBenchPair:
             dist.all_gather_object(got, touched)
             touched = got[self.rank - self.n_pairs] if self.rank >= self.n_pairs else touched
         if not self.is_receiver:
-            return
+            return 0
         pair = (self.rank - self.n_pairs) if not self.loopback else 0
+        layers = range(self.n_layers) if layers is None else layers
+        tmp = None if self.loopback else torch.empty(self.src_l.layer_bytes, dtype=torch.uint8, device=self.dev)
+        checked = 0
         for layer in layers:
             if layer >= self.n_layers:
                 continue
             if self.loopback:
                 src_layer = self.src[layer * self.src_l.layer_bytes:(layer + 1) * self.src_l.layer_bytes]
             else:
-                tmp = torch.empty(self.src_l.layer_bytes, dtype=torch.uint8, device=self.dev)
-                saved_l = self.src_l
                 g = torch.Generator(device=self.dev)
                 g.manual_seed(977 * pair + layer)
-                n = saved_l.layer_bytes // 2
+                n = self.src_l.layer_bytes // 2
                 v = tmp.view(torch.bfloat16)
                 chunk = 1 << 26
                 for o in range(0, n, chunk):
@@ -290,7 +316,7 @@ class PDBenchPair:
                     v[o:o + m].copy_(torch.randn(m, dtype=torch.float32, device=self.dev, generator=g))
                 src_layer = tmp
             dst_layer = self.dst[layer * self.dst_l.layer_bytes:(layer + 1) * self.dst_l.layer_bytes]
-            sv = self.src_l.view(src_layer, torch.int16)
+            sv = self.src_l.view(src_layer, torch.int16)       # [block, kv, slot, head, dim] whatever the layout
             dv = self.dst_l.view(dst_layer, torch.int16)
             for slot in touched:
                 for c in self.slot_chunks[slot]:
@@ -299,6 +325,14 @@ class PDBenchPair:
                     db = torch.tensor(list(c.dst_blocks[:nb_full]), device=self.dev)
                     if not torch.equal(dv[db], sv[sb]):
                         raise RuntimeError(f"rank {self.rank}: destination cache mismatch in layer {layer}")
+                    tail = c.new_tokens - nb_full * BLOCK
+                    if tail:
+                        s_t = sv[c.src_blocks[nb_full], :, :tail]
+                        d_t = dv[c.dst_blocks[nb_full], :, :tail]
+                        if not torch.equal(d_t, s_t):
+                            raise RuntimeError(f"rank {self.rank}: tail tokens differ in layer {layer}")
+            checked += 1
+        return checked
 
 
 # ---------------------------------------------------------------------------------------------
@@ -310,8 +344,8 @@ def kvstore_bandwidth(dev, n_layers: int = 32, n_blocks: int = 1024, iters: int 
     baseline of the same box."""
     import os
 
-    from . import load_ops
-    from .kvstore import PinnedKVStore
+    from llumnix_kv_b200 import load_ops
+    from llumnix_kv_b200.kvstore import PinnedKVStore
 
     res: dict = {}
     for fp8 in (False, True):
@@ -369,7 +403,7 @@ def migration_sweep(pair: "PDBenchPair", counts=(1, 4, 16, 64, 256, 1024, 4096),
     caches of the same layout, against the number of blocks, through KVTransferClient.start_req_send.
     ``pair`` must have been built with identical source and destination layouts and
     ``setup_engine()`` called."""
-    from .kv_transfer_impl import ReqMeta
+    from llumnix_kv_b200.kv_transfer_impl import ReqMeta
 
     out = []
     seq = 0
@@ -410,8 +444,8 @@ def ttft_added(K, rank: int, world: int, dev, tokens: int = 8192, iters: int = 3
     rank r + world/2 is its decode GPU; with one GPU both caches share it."""
     import random
 
-    from .kv_transfer_impl import KVTransferClient, KVTransferProtocolType as PT, KVTransferServer
-    from .models.llama_prefill import LLAMA3_8B_GEOMETRY, TINY_GEOMETRY, PrefillWorker
+    from llumnix_kv_b200.kv_transfer_impl import KVTransferClient, KVTransferProtocolType as PT, KVTransferServer
+    from .llama_prefill import LLAMA3_8B_GEOMETRY, TINY_GEOMETRY, PrefillWorker
 
     geo = TINY_GEOMETRY if tiny else LLAMA3_8B_GEOMETRY
     n_pairs = max(world // 2, 1)
@@ -550,7 +584,7 @@ def quant_reshard_bandwidth(dev, tokens: int = 8192, n_layers: int = 80, iters: 
     """Llama-3-70B-shaped TP-mismatch transfer on one GPU (kernel-only): a prefill TP=4 rank (2 of the 8
     KV heads, bf16, NHD) pushes into its half of a decode TP=2 rank's pages (4 heads, HND), as a
     plain copy and as block-scaled fp8 (one UE8M0 scale per 32 values).  GB/s are bf16 source bytes."""
-    from .ops.p2d_attn import MODE_BF16_TO_MXFP8, MODE_COPY, HeadMap
+    from llumnix_kv_b200.ops.p2d_attn import MODE_BF16_TO_MXFP8, MODE_COPY, HeadMap
 
     n_blk = (tokens + BLOCK - 1) // BLOCK
     src_l = AttnLayout(CacheShape.FLASH, n_blk + 1, BLOCK, 2, HEAD_DIM, 2)
@@ -623,7 +657,7 @@ def hybrid_state_bandwidth(K, rank: int, world: int, dev, which: str = "gdn", to
     token) and latent + rope (656 B per token), 64-token blocks, identical on every TP rank."""
     import random
 
-    from .kv_transfer_impl import KVTransferClient, KVTransferProtocolType as PT, KVTransferServer
+    from llumnix_kv_b200.kv_transfer_impl import KVTransferClient, KVTransferProtocolType as PT, KVTransferServer
 
     n_pairs = max(world // 2, 1)
     sender = world == 1 or rank < n_pairs
@@ -724,18 +758,33 @@ def hybrid_state_bandwidth(K, rank: int, world: int, dev, which: str = "gdn", to
         e1.record(stream)
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1)
-        if world == 1:
-            for layer in (0, n_layers - 1):
-                for t, blocks in enumerate(per_tensor):
-                    s_, d_ = src[layer][t], dst[layer][t]
-                    for s_off, d_off, n in blocks[:64] + blocks[-64:]:
-                        ok = ok and bool(torch.equal(d_[d_off:d_off + n], s_[s_off:s_off + n]))
+    # the decode side compares a sample of the planned byte ranges (the first and last 64 of every tensor,
+    # first and last layer) with the prefill side's bytes, regenerated from the same seeds on another GPU
+    sample = None
+    if sender:
+        sample = [blocks[:64] + blocks[-64:] for blocks in per_tensor]
     if world > 1:
         import torch.distributed as dist
 
-        t = torch.tensor([ms, float(moved), float(ok)], dtype=torch.float64, device=dev)
+        got = [None] * world
+        dist.all_gather_object(got, sample)
+        if receiver:
+            sample = got[rank - n_pairs]
+        torch.cuda.synchronize()
+        dist.barrier()
+    if receiver:
+        ref = src if world == 1 else alloc(True)
+        for layer in (0, n_layers - 1):
+            for t, blocks in enumerate(sample):
+                s_, d_ = ref[layer][t], dst[layer][t]
+                for s_off, d_off, n in blocks:
+                    ok = ok and bool(torch.equal(d_[d_off:d_off + n], s_[s_off:s_off + n]))
+    if world > 1:
+        import torch.distributed as dist
+
+        t = torch.tensor([ms, float(moved), 0.0 if ok else 1.0], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, moved = float(t[0]), int(t[1])
+        ms, moved, ok = float(t[0]), int(t[1]), float(t[2]) == 0.0
         dist.barrier()
     if srv is not None:
         srv.stop()
@@ -755,7 +804,7 @@ def quant_reshard_nvlink(K, rank: int, world: int, dev, tokens: int = 8192, n_la
 
     import torch.distributed as dist
 
-    from .ops.p2d_attn import MODE_BF16_TO_MXFP8, HeadMap, mx_quantize_reference
+    from llumnix_kv_b200.ops.p2d_attn import MODE_BF16_TO_MXFP8, HeadMap, mx_quantize_reference
 
     n_p = world // 2
     n_d = max(n_p // 2, 1)
@@ -881,7 +930,7 @@ def mla_fanout_bandwidth(K, rank: int, world: int, dev, tokens: int = 32768, n_l
 
     import torch.distributed as dist
 
-    from .parallel.nvls import MulticastKVCache
+    from llumnix_kv_b200.parallel.nvls import MulticastKVCache
 
     assert world >= 3, "one prefill rank and a decode group of at least two"
     # the relay arms move ``layer_group`` layers per launch and flag: with one launch per layer and member the
@@ -1114,3 +1163,64 @@ def mla_fanout_bandwidth(K, rank: int, world: int, dev, tokens: int = 32768, n_l
             "speedup_scatter": round(ms_uni / ms_scatter, 2) if ms_scatter > 0 else 0.0,
             "prefill_egress_bytes": {"unicast": n_d * bytes_per_copy, "nvls": bytes_per_copy},
             "verified": not flat, "errors": flat[:4]}
+
+
+def post_checks(K, rank: int, world: int, dev) -> dict:
+    """Untimed correctness pass after a multi-GPU benchmark, through KVTransferClient / KVTransferServer over
+    NVLink, rank r -> rank r + world/2: (1) a TP-mismatched request with a block-scaled fp8 destination
+    (prefill TP=4 rank 1: 2 of 8 heads, bf16, NHD -> decode TP=2 rank 0: 4 heads, e4m3 + UE8M0 scales, HND),
+    compared with the PyTorch quantiser oracle on the decode GPU; (2) a hybrid request (GDN state pages +
+    attention pages) and an MLA request, compared byte range by byte range with the CPU planner's ranges."""
+    import torch.distributed as dist
+
+    from llumnix_kv_b200.kv_transfer_impl import KVTransferClient, KVTransferProtocolType as PT, KVTransferServer
+    from llumnix_kv_b200.ops.p2d_attn import MODE_BF16_TO_MXFP8, HeadMap, reference_transfer
+
+    n_pairs = world // 2
+    sender, receiver = rank < n_pairs, n_pairs <= rank < 2 * n_pairs
+    pair = rank % n_pairs
+    out = {}
+    n_layers = 2
+    src_l = AttnLayout(CacheShape.FLASH, 40, 16, 2, 128, 2)
+    dst_l = AttnLayout(CacheShape.FLASHINFER, 40, 16, 4, 128, 1, mx_scaled=True)
+    reqs = [("a", [3, 9, 1], [7, 2, 30], 48), ("b", [5, 6], [11, 4], 21), ("c", [20], [21], 16)]
+    inst = f"QD{pair}|0|2"
+    srv = None
+    winfo = None
+    dst = None
+    if receiver:
+        dst = [dst_l.alloc(dev) for _ in range(n_layers)]
+        srv = KVTransferServer(inst, 2, 0, 0, dst_l.block_bytes, dst_l.token_bytes, "fake://", dst, [PT.NVLINK],
+                               num_kv_heads=8, cache_shape=5, mx_scaled=True)
+        winfo = srv.worker_info()
+    infos = [None] * world
+    dist.all_gather_object(infos, winfo)
+    if sender:
+        src = [src_l.alloc(dev, "normal", seed=4000 + 10 * pair + i) for i in range(n_layers)]
+        cli = KVTransferClient(f"QP{pair}|0|4", 4, 1, 1, src_l.block_bytes, src_l.token_bytes, "fake://", src, [PT.NVLINK],
+                               num_kv_heads=8, cache_shape=2)
+        for rid, sb, db, total in reqs:
+            cli.submit_req_send2(inst, 0, rid, 0, total, True, sb, db, infos[rank + n_pairs], stepid=1)
+        cli.start_send_step(1, 1)
+        for layer in range(n_layers):
+            cli.record_event(layer)
+        cli.flush_send_step()
+        cli.drain()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ok = True
+    if receiver:
+        chunks = [ReqChunk(sb, db, 0, t) for _, sb, db, t in reqs]
+        for i in range(n_layers):
+            s_i = src_l.alloc(dev, "normal", seed=4000 + 10 * pair + i)
+            expect = torch.zeros_like(dst[i])
+            reference_transfer(src_l, dst_l, s_i, expect, chunks, HeadMap(0, 2, 2), MODE_BF16_TO_MXFP8)
+            ok = ok and bool(torch.equal(dst[i], expect))
+        srv.stop()
+    t = torch.tensor([0.0 if ok else 1.0], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    out["tp4_to_tp2_mxfp8_through_engine"] = bool(t.item() == 0.0)
+    for which in ("gdn", "mla"):
+        res = hybrid_state_bandwidth(K, rank, world, dev, which=which, tokens=2048, steps=1, warmup=1, small=True)
+        out[f"{which}_through_engine"] = bool(res["verified"])
+    return out

@@ -8,6 +8,7 @@
 #include <pybind11/stl.h>
 
 #include "core/client.h"
+#include "core/completion.h"
 #include "core/envcfg.h"
 #include "transport/copy_policy.h"
 #include "transport/device_stage.h"
@@ -414,6 +415,15 @@ void bind_engine(py::module_& m) {
       .def("notify_event_record", [](KvClient& c, size_t stepid) { c.get()->notify_event_record(stepid); })
       .def("flush_send", [](KvClient& c, size_t stepid) { c.get()->flush_send(stepid); })
       .def("drain", [](KvClient& c) { c.get()->drain(); }, py::call_guard<py::gil_scoped_release>())
+      .def("wait_inflight",
+           [](KvClient& c, uint64_t max_batches, double timeout_s) {
+             return c.get()->context()->inflight().wait_at_most(
+                 max_batches, std::chrono::milliseconds(static_cast<int64_t>(timeout_s * 1000)));
+           },
+           py::arg("max_batches") = 0, py::arg("timeout_s") = 30.0, py::call_guard<py::gil_scoped_release>(),
+           "Wait until at most max_batches batches are still in flight; False when the timeout ran out.")
+      .def("inflight", [](KvClient& c) { return c.get()->context()->inflight().inflight(); })
+      .def("finished_batches", [](KvClient& c) { return c.get()->context()->inflight().finished(); })
       .def("target_size", [](KvClient& c) { return c.get()->target_size(); })
       .def("target_try_shrink", [](KvClient& c, size_t cap) { c.get()->target_try_shrink(cap); },
            py::call_guard<py::gil_scoped_release>())
@@ -556,6 +566,8 @@ void bind_engine(py::module_& m) {
     return py::make_tuple(py::bytes(buf.data(), buf.size()), resp);
   });
   m.def("fault_inject_arm", &fault_inject_arm);
+  m.def("fault_inject_arm_drop_completion", &fault_inject_arm_drop_completion);
+  m.def("completions_pending", [] { return CompletionPoller::instance().pending(); });
   m.def("envcfg_reset_for_test", &envcfg_reset_for_test);
   m.def("env_cache_shape", &env_cache_shape);
   m.def("env_port_base", &env_port_base);

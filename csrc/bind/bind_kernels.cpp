@@ -111,13 +111,16 @@ void bind_kernels(py::module_& m) {
 
   m.def(
       "kvt_encode_tensor_map",
-      [](uint64_t base, const KvtLayout& l, uint32_t box_heads, uint32_t box_tokens) {
+      [](uint64_t base, const KvtLayout& l, uint32_t box_heads, uint32_t box_tokens, uint32_t token_inner) {
         alignas(64) char buf[128];
-        const int r = kvt_encode_tensor_map(buf, base, &l, box_heads, box_tokens);
+        const int r = kvt_encode_tensor_map_ordered(buf, base, &l, box_heads, box_tokens, token_inner);
         if (r != 0) throw std::runtime_error("cuTensorMapEncodeTiled failed: " + std::to_string(r));
         return py::bytes(buf, 128);
       },
-      py::arg("base"), py::arg("layout"), py::arg("box_heads"), py::arg("box_tokens"));
+      py::arg("base"), py::arg("layout"), py::arg("box_heads"), py::arg("box_tokens"), py::arg("token_inner") = 0);
+  m.def("kvt_tile_is_flat", [](const KvtLayout& l, uint32_t n_heads, uint32_t tile_tokens, uint32_t token_inner) {
+    return kvt_tile_is_flat(&l, n_heads, tile_tokens, token_inner) != 0;
+  });
 
   m.def(
       "kvt_launch_p2d_attn",
@@ -126,10 +129,14 @@ void bind_kernels(py::module_& m) {
          uint32_t total_tiles, uint64_t block_ids, uint32_t tile_tokens, uint32_t src_head0, uint32_t dst_head0,
          uint32_t n_heads, uint32_t mode, uint64_t status, uint64_t done_counter, uint64_t flag,
          uint64_t flag_value, int grid, int threads, int use_tma, uint64_t stream, uint32_t simt_tile,
-         uint32_t dst_remote) {
+         uint32_t dst_remote, uint32_t tile_order, uint32_t store_form, uint32_t tma_stages, uint32_t cache_hint) {
         KvtAttnLaunch a{};
         a.simt_tile = simt_tile;
         a.dst_remote = dst_remote;
+        a.tile_order = tile_order;
+        a.store_form = store_form;
+        a.tma_stages = tma_stages;
+        a.cache_hint = cache_hint;
         a.src_layers = reinterpret_cast<const uint64_t*>(src_layers);
         a.dst_layers = reinterpret_cast<const uint64_t*>(dst_layers);
         a.src_maps = reinterpret_cast<const void*>(src_maps);
@@ -159,7 +166,8 @@ void bind_kernels(py::module_& m) {
       py::arg("total_tiles"), py::arg("block_ids"), py::arg("tile_tokens"), py::arg("src_head0"),
       py::arg("dst_head0"), py::arg("n_heads"), py::arg("mode"), py::arg("status"), py::arg("done_counter"),
       py::arg("flag"), py::arg("flag_value"), py::arg("grid"), py::arg("threads"), py::arg("use_tma"),
-      py::arg("stream"), py::arg("simt_tile") = 0, py::arg("dst_remote") = 0);
+      py::arg("stream"), py::arg("simt_tile") = 0, py::arg("dst_remote") = 0, py::arg("tile_order") = 0,
+      py::arg("store_form") = 0, py::arg("tma_stages") = 0, py::arg("cache_hint") = 0);
 
   m.def(
       "kvt_launch_p2d_state",
@@ -331,6 +339,17 @@ void bind_kernels(py::module_& m) {
     check_cuda(kvt_host_register(p, bytes, &d), "cudaHostRegister");
     return d;
   });
+  m.def("kvt_memcpy_async", [](uint64_t dst, uint64_t src, uint64_t bytes, uint64_t stream) {
+    check_cuda(kvt_memcpy_async(dst, src, bytes, reinterpret_cast<void*>(stream)), "cudaMemcpyAsync");
+  });
+  m.def("kvt_memcpy_triples", [](uint64_t dst_base, uint64_t src_base, py::buffer triples, uint64_t stream) {
+    const py::buffer_info bi = triples.request();
+    if (bi.itemsize != 8 || bi.size % 3 != 0) throw std::invalid_argument("triples: a contiguous array of u64, 3 per copy");
+    py::gil_scoped_release nogil;
+    check_cuda(kvt_memcpy_triples(dst_base, src_base, static_cast<const uint64_t*>(bi.ptr),
+                                  static_cast<uint32_t>(bi.size / 3), reinterpret_cast<void*>(stream)),
+               "cudaMemcpyAsync");
+  }, py::arg("dst_base"), py::arg("src_base"), py::arg("triples"), py::arg("stream"));
   m.def("kvt_host_unregister", [](uint64_t p) { check_cuda(kvt_host_unregister(p), "cudaHostUnregister"); });
 }
 

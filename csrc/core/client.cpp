@@ -17,6 +17,16 @@ KvTransferClient::TargetMgr::~TargetMgr() {
 }
 
 void KvTransferClient::TargetMgr::submit(std::shared_ptr<Step> step, StepTasks tasks) {
+  // counted here, on the caller's thread, so that a caller that asks "how far am I ahead" right after
+  // submitting already sees these batches
+  uint64_t n = 0;
+  for (auto& [inst, per_worker] : tasks.tasks)
+    for (auto& [wid, batch] : per_worker)
+      if (!batch.tasks.empty()) {
+        batch.inflight = &ctx_->inflight();
+        ++n;
+      }
+  ctx_->inflight().add(n);
   auto shared_tasks = std::make_shared<StepTasks>(std::move(tasks));
   mgr_thd_->spawn([this, step = std::move(step), shared_tasks]() mutable { do_submit(step, *shared_tasks); });
 }
@@ -24,6 +34,8 @@ void KvTransferClient::TargetMgr::submit(std::shared_ptr<Step> step, StepTasks t
 void KvTransferClient::TargetMgr::drain() {
   mgr_thd_->drain();
   send_pool_->drain();
+  // batches that complete on a device: every one of them is bounded by its own deadline
+  ctx_->inflight().wait_at_most(0, std::chrono::milliseconds(env_completion_timeout_ms() + 2000));
 }
 
 void KvTransferClient::TargetMgr::shrink_sync(size_t cap) {
@@ -64,6 +76,7 @@ void KvTransferClient::TargetMgr::do_submit(std::shared_ptr<Step>& step, StepTas
       } catch (const std::exception& ex) {
         LOG(ERROR) << "TargetMgr: cannot create stub for " << inst << "," << wid << ": " << ex.what();
         for (const auto& t : batch.tasks) t.set_state(ReqState::FAILED);
+        if (batch.inflight != nullptr) batch.inflight->done();
         continue;
       }
       if (target->inflycnt.fetch_add(1, std::memory_order_acquire) == 0) target->thread_hint = ++next_hint_;
@@ -84,7 +97,7 @@ void KvTransferClient::TargetMgr::shrink(size_t cap) {
   // evict least-recently-used idle targets; stop at the first one still in flight
   while (targets_.size() > cap) {
     Target& victim = targets_.back();
-    if (victim.inflycnt.load(std::memory_order_relaxed) > 0) break;
+    if (victim.inflycnt.load(std::memory_order_relaxed) > 0 || !victim.stub->idle()) break;
     const InstanceId inst = victim.stub->dstid();
     const WorkerId wid = victim.stub->dstworkerid();
     auto it = index_.find(inst);

@@ -6,6 +6,7 @@
 #include <memory>
 #include <vector>
 
+#include "core/completion.h"
 #include "core/types.h"
 
 namespace kvx {
@@ -71,6 +72,7 @@ class Context {
   bool supports(TransferProtocol::Kind k) const { return (worker_info_.transfer_protocols & k) != 0; }
   // Bytes of cache tensor `t` of any layer (block size x blocks): the bound every offset is checked against.
   size_t tensor_capacity(size_t t) const;
+  InflightCounter& inflight() { return inflight_; }
 
  private:
   int device_id_{-1};
@@ -78,6 +80,7 @@ class Context {
   std::vector<std::vector<LayerInfo>> layer_infos_;
   std::vector<std::vector<uint64_t>> layer_addrs_;
   std::unique_ptr<ICudaBarrier> barrier_;
+  InflightCounter inflight_;
 };
 
 }  // namespace kvx

@@ -11,9 +11,12 @@
 namespace kvx {
 
 namespace {
-std::mutex g_mu;
-std::map<std::string, long> g_int_cache;
-std::map<std::string, double> g_dbl_cache;
+// Process-lifetime state that worker threads (naming keep-alive, senders, servers) read until the very end of
+// the process: allocated once and never destroyed, so that a thread still running while the main thread runs
+// its exit handlers never touches a destroyed object.
+std::mutex& g_mu = *new std::mutex;
+std::map<std::string, long>& g_int_cache = *new std::map<std::string, long>;
+std::map<std::string, double>& g_dbl_cache = *new std::map<std::string, double>;
 bool g_quiet = getenv("BLLM_KVTRANS_QUIET_ENV") != nullptr;
 
 void echo(const char* env, const char* val, const std::string& def) {
@@ -57,9 +60,9 @@ struct SendDoneAddr {
   sockaddr_in addr{};
 };
 SendDoneAddr g_send_done;
-std::vector<std::pair<uint64_t, int>> g_reserve;
+std::vector<std::pair<uint64_t, int>>& g_reserve = *new std::vector<std::pair<uint64_t, int>>;
 bool g_reserve_parsed = false;
-std::string g_nic;
+std::string& g_nic = *new std::string;
 bool g_nic_parsed = false;
 }  // namespace
 
@@ -90,6 +93,9 @@ int env_nvlink_ctas() { return (int)anyint("BLLM_KVTRANS_NVLINK_CTAS", 0); }
 int env_nvlink_streams() { return (int)posint("BLLM_KVTRANS_NVLINK_STREAMS", 8); }
 int env_dst_mxfp8() { return (int)anyint("BLLM_KVTRANS_DST_MXFP8", 0); }
 int env_use_tma() { return (int)anyint("BLLM_KVTRANS_USE_TMA", 1); }
+int env_completion_timeout_ms() { return (int)posint("BLLM_KVTRANS_COMPLETION_TIMEOUT_MS", env_rpc_timeout_s() * 1000); }
+int env_tile_order() { return (int)anyint("BLLM_KVTRANS_TILE_ORDER", -1); }
+int env_store_form() { return (int)anyint("BLLM_KVTRANS_STORE_FORM", -1); }
 bool env_copy_profile_enable() { return anyint("BLLM_KVTRANS_COPY_PROFILE_ENABLE", 1) != 0; }
 size_t env_copy_memcpy_max_blocks() { return (size_t)posint("BLLM_KVTRANS_COPY_MEMCPY_MAX_BLOCKS", 16); }
 size_t env_copy_memcpy_threshold_bytes() { return (size_t)posint("BLLM_KVTRANS_COPY_MEMCPY_BLOCK_THRESHOLD_BYTES", 256 * 1024); }

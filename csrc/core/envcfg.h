@@ -59,6 +59,10 @@ int env_nvlink_ctas();
 int env_nvlink_streams();
 int env_dst_mxfp8();
 int env_use_tma();
+// TMA tiles of the NVLink channel: order in shared memory (0 tokens outermost, 1 heads outermost, -1 = the
+// destination's own order) and how they leave (0 tensor store, 1 one linear bulk store, -1 = linear when legal).
+int env_tile_order();
+int env_store_form();
 // Host-staged copies (TCP / SHM transports): start-up measurement of copy kernel against copy
 // engines, the static rule used without it, and a forced path (0 measured or static, 1 kernel, 2 memcpy).
 bool env_copy_profile_enable();
@@ -67,6 +71,9 @@ size_t env_copy_memcpy_threshold_bytes();
 int env_copy_path();
 // NVLink channel: stamp the GPU timer at the start and the end of every batch and report DeviceUs in the flush line.
 bool env_device_timestamps();
+// How long a batch of a device transport may take to deliver its completion record before it is failed
+// (default: the RPC timeout).
+int env_completion_timeout_ms();
 
 void envcfg_reset_for_test();
 std::string envcfg_dump();   // every setting resolved so far, one key=value per line

@@ -32,6 +32,18 @@ void fault_inject_throw() {
   if (roll()) throw std::runtime_error("fault_inject: random failure");
 }
 
+static std::atomic<int> g_drop_completions{0};
+
+void fault_inject_arm_drop_completion(int n) { g_drop_completions.store(n > 0 ? n : 0); }
+
+bool fault_inject_drop_completion() {
+  int c = g_drop_completions.load();
+  while (c > 0) {
+    if (g_drop_completions.compare_exchange_weak(c, c - 1)) return true;
+  }
+  return false;
+}
+
 void fault_inject_sleep(int max_us) {
   if (max_us <= 0 || !roll()) return;
   const int delay_ms = env_debug_tx_delay_ms();

@@ -5,7 +5,9 @@
 #include <unistd.h>
 
 #include <cstring>
+#include <thread>
 
+#include "core/completion.h"
 #include "core/envcfg.h"
 #include "core/fault_inject.h"
 #include "plan/planner.h"
@@ -78,6 +80,7 @@ void SendDoneNotifier::round_trip(const std::vector<char>& buf, int resp_size) {
 
 void SendDoneNotifier::notify(const std::vector<const ReqSendTask*>& reqs) {
   if (reqs.empty()) return;
+  std::lock_guard<std::mutex> g(mu_);
   int resp_size = 4;
   const std::vector<char> buf = encode(rank_, reqs, env_send_done_head_kind(), &resp_size);
   for (int attempt = 0; attempt < 2; ++attempt) {
@@ -98,6 +101,18 @@ static bool same_dst(const WorkerInfo& a, const WorkerInfo& b) noexcept {
          a.transfer_protocols == b.transfer_protocols;
 }
 
+// One batch from "handed to the stub" to "finished": it owns the request chunks (the pointers below point
+// into batch.tasks) and keeps the channel alive while a device transport still completes it.
+struct PendingBatch {
+  BatchSendTask batch;
+  std::vector<const ReqSendTask*> send_req, finished_req;
+  Channel ch;
+  uint64_t ticket = 0;
+  std::string flush_out;
+  int64_t queue_us = 0, plan_us = 0, wait_us = 0;
+  Timepoint iter_start, enqueued;
+};
+
 struct KvSendStub::Impl {
   KvSendStub* stub;
   WorkerInfo src_info;
@@ -111,12 +126,10 @@ struct KvSendStub::Impl {
   PlanEnv env;
   PlannerChoice planner;
   Channel ch;
+  std::atomic<bool> drop_channel{false};   // set by the completion thread when a batch failed on the device
+  std::atomic<int> completing{0};          // batches handed to the completion poller and not yet finished
 
-  std::string flush_out;
   std::vector<std::vector<IpcBlock>> send_blocks;
-  std::vector<const ReqSendTask*> send_req, finished_req;
-  int64_t wait_us = 0, wait_and_send_us = 0, send_notify_us = 0;
-  Timepoint iter_start, send_finish;
 
   Impl(KvSendStub* s, const WorkerInfo& src, std::shared_ptr<INamingWorkerClient> n, uint32_t sl, uint32_t nl,
        std::unique_ptr<IChannelFactory> f, int shape, std::string sd_addr)
@@ -160,6 +173,7 @@ struct KvSendStub::Impl {
   }
 
   void try_create_channel() {
+    if (drop_channel.exchange(false)) ch.reset();
     if (ch && ch->is_active()) return;
     refresh_dst_info();
     env.dst = &*dstinfo;
@@ -167,15 +181,17 @@ struct KvSendStub::Impl {
     LOG(INFO) << "create channel. dst=" << dstinfo->to_string() << ";ch=" << ch.get() << ";proto=" << ch->name();
   }
 
-  void do_send(BatchSendTask& batch, bool device_planned) {
-    wait_us = 0;
+  // Returns true when the batch completes asynchronously (pb.ticket names its completion record).
+  bool do_send(PendingBatch& pb) {
+    BatchSendTask& batch = pb.batch;
+    pb.wait_us = 0;
     const bool by_record = ch->device_ordered();
     // a frozen step has nothing to wait for: let the channel move all layers in one go
     const bool whole = batch.step->frozen && ch->send_layers(start_layer, num_layers, batch.step.get());
     for (uint32_t i = start_layer; i < num_layers && !whole;) {
       TimeWatch w;
       if (by_record) batch.step->wait_layer_recorded(i); else batch.step->wait_layer_ready(i);
-      wait_us += w.get_elapse_us();
+      pb.wait_us += w.get_elapse_us();
       if (by_record) {
         // layers recorded while the sender was busy go out together where the channel can do that
         const uint32_t ready = std::min<uint32_t>(num_layers, std::max<uint32_t>(i + 1, batch.step->layers_recorded()));
@@ -185,30 +201,69 @@ struct KvSendStub::Impl {
         ++i;
       }
     }
-    (void)device_planned;
     fault_inject_throw();
-    ch->flush(flush_out);
-    send_finish = SteadyClock::now();
-    wait_and_send_us = elapse_us(iter_start, send_finish);
+    if (ch->async_flush()) {
+      pb.ticket = ch->flush_async();
+      pb.ch = ch;
+      return true;
+    }
+    ch->flush(pb.flush_out);
+    return false;
   }
 
-  void do_task(BatchSendTask& batch) noexcept {
+  // Everything that follows a batch's data: request states, the send-done report, step and stub metrics.
+  // Runs on the sender thread (host transports, failures) or on the completion poller's thread.
+  void finish(PendingBatch& pb, bool ok) noexcept {
+    BatchSendTask& batch = pb.batch;
+    const size_t step_idx = batch.step->step_idx;
+    Timepoint send_finish = SteadyClock::now();
+    const int64_t wait_and_send_us = elapse_us(pb.iter_start, send_finish);
+    if (!ok) {
+      for (const auto& task : batch.tasks) task.set_state(ReqState::FAILED);
+    }
+    for (const ReqSendTask* task : pb.finished_req) {
+      if (task->state() == ReqState::INPROCESS) {
+        // a request closed without ever sending a token counts as failed
+        task->set_state(task->new_tokens == 0 ? ReqState::FAILED : ReqState::OK);
+      }
+      LOG(INFO) << "KVT tx_stub. DstId=" << stub->dstid() << ",DstWorkerId=" << stub->dstworkerid()
+                << ",StepIdx=" << step_idx << "." << batch.substepid << ",State=" << static_cast<int>(task->state())
+                << ",FinishedReq=" << task->req_id();
+    }
+    int64_t send_notify_us = 0;
+    if (!pb.finished_req.empty()) {
+      notifier.notify(pb.finished_req);
+      const auto now = SteadyClock::now();
+      send_notify_us = elapse_us(send_finish, now);
+      send_finish = now;
+    }
+    batch.step->update_last_send_finish_ts(send_finish);
+    LOG(INFO) << "SendStubMetrics. DstId=" << stub->dstid() << ",DstWorkerId=" << stub->dstworkerid()
+              << ",StepIdx=" << step_idx << "." << batch.substepid << ",FinishedReqSize=" << pb.finished_req.size() << ","
+              << pb.flush_out << ",QueueUs=" << pb.queue_us << ",PlanUs=" << pb.plan_us << ",WaitUs=" << pb.wait_us
+              << ",EnqueueUs=" << elapse_us(pb.iter_start, pb.enqueued) << ",WaitAndSendUs=" << wait_and_send_us
+              << ",SendNotifyUs=" << send_notify_us << ",SendFinishTs=" << send_finish.time_since_epoch().count();
+    if (batch.inflight != nullptr) batch.inflight->done();
+  }
+
+  void do_task(std::shared_ptr<PendingBatch> pbp) noexcept {
+    PendingBatch& pb = *pbp;
+    BatchSendTask& batch = pb.batch;
     const size_t step_idx = batch.step->step_idx;
     fault_inject_sleep(300 * 1000);
-    iter_start = SteadyClock::now();
-    send_finish = iter_start;
-    const int64_t queue_us = elapse_us(batch.send_ts, iter_start);
-    int64_t plan_us = 0;
+    pb.iter_start = pb.enqueued = SteadyClock::now();
+    pb.queue_us = elapse_us(batch.send_ts, pb.iter_start);
     for (const auto& task : batch.tasks) {
-      if (task.reach_last_token) finished_req.push_back(&task);
+      if (task.reach_last_token) pb.finished_req.push_back(&task);
       if (task.new_tokens == 0) continue;            // a pure "close this request" marker
       if (task.state() == ReqState::FAILED) continue;  // an earlier chunk already failed
-      send_req.push_back(&task);
+      pb.send_req.push_back(&task);
     }
-    if (!send_req.empty()) {
+    bool ok = true, async = false;
+    if (!pb.send_req.empty()) {
       try {
         try_create_channel();
-        bool device_planned = ch->register_tasks(env, send_req);
+        bool device_planned = ch->register_tasks(env, pb.send_req);
         bool have_data = device_planned;
         if (!device_planned) {
           // Byte ranges can only describe a transfer between caches of one layout and dtype: a
@@ -221,48 +276,52 @@ struct KvSendStub::Impl {
                                           std::to_string(dst_shape) + (dstinfo->ext_int("mx", 0) != 0 ? " (block-scaled fp8)" : "") +
                                           " needs the fused kernel of the NVLINK transport; channel is " + ch->name());
           }
-          for (const ReqSendTask* t : send_req) plan_request(planner, env, *t, send_blocks);
+          send_blocks.clear();
+          for (const ReqSendTask* t : pb.send_req) plan_request(planner, env, *t, send_blocks);
           have_data = !send_blocks.empty() && !send_blocks[0].empty();
           if (have_data) ch->register_data(send_blocks, planner.kind);
         }
-        plan_us = elapse_us(iter_start, SteadyClock::now());   // channel, planning, descriptor upload
-        if (have_data) do_send(batch, device_planned);
+        pb.plan_us = elapse_us(pb.iter_start, SteadyClock::now());   // channel, planning, descriptor upload
+        if (have_data) async = do_send(pb);
+        pb.enqueued = SteadyClock::now();
       } catch (const std::exception& ex) {
         LOG(ERROR) << "KVT tx_stub fail to send data. DstId=" << stub->dstid() << ",DstWorkerId=" << stub->dstworkerid()
-                   << ",StepIdx=" << step_idx << "." << batch.substepid << ',' << flush_out << ",ex=" << ex.what();
+                   << ",StepIdx=" << step_idx << "." << batch.substepid << ',' << pb.flush_out << ",ex=" << ex.what();
         ch.reset();
-        for (const auto& task : batch.tasks) task.set_state(ReqState::FAILED);
+        ok = false;
+        async = false;
       }
     }
-    for (const ReqSendTask* task : finished_req) {
-      if (task->state() == ReqState::INPROCESS) {
-        // a request closed without ever sending a token counts as failed
-        task->set_state(task->new_tokens == 0 ? ReqState::FAILED : ReqState::OK);
-      }
-      LOG(INFO) << "KVT tx_stub. DstId=" << stub->dstid() << ",DstWorkerId=" << stub->dstworkerid()
-                << ",StepIdx=" << step_idx << "." << batch.substepid << ",State=" << static_cast<int>(task->state())
-                << ",FinishedReq=" << task->req_id();
-    }
-    send_notify_us = 0;
-    if (!finished_req.empty()) {
-      notifier.notify(finished_req);
-      const auto now = SteadyClock::now();
-      send_notify_us = elapse_us(send_finish, now);
-      send_finish = now;
-    }
-    batch.step->update_last_send_finish_ts(send_finish);
-    LOG(INFO) << "SendStubMetrics. DstId=" << stub->dstid() << ",DstWorkerId=" << stub->dstworkerid()
-              << ",StepIdx=" << step_idx << "." << batch.substepid << ",FinishedReqSize=" << finished_req.size() << ","
-              << flush_out << ",QueueUs=" << queue_us << ",PlanUs=" << plan_us << ",WaitUs=" << wait_us << ",WaitAndSendUs=" << wait_and_send_us
-              << ",SendNotifyUs=" << send_notify_us << ",SendFinishTs=" << send_finish.time_since_epoch().count();
-  }
-
-  void clear() noexcept {
-    flush_out.clear();
     send_blocks.clear();
     send_blocks.shrink_to_fit();
-    send_req.clear();
-    finished_req.clear();
+    if (!async && completing.load(std::memory_order_acquire) == 0) {
+      finish(pb, ok);
+      return;
+    }
+    // The batch (or an earlier one of this stub) completes on the device: hand it to the completion poller,
+    // which finishes this stub's batches in the order they were sent.
+    completing.fetch_add(1, std::memory_order_acq_rel);
+    CompletionPoller::Entry e;
+    e.owner = this;
+    e.deadline = SteadyClock::now() + std::chrono::milliseconds(env_completion_timeout_ms());
+    Impl* self = this;
+    if (async) {
+      e.poll = [pbp] { return pbp->ch->poll_completion(pbp->ticket, pbp->flush_out); };
+    } else {
+      e.poll = [ok] { return ok ? PollResult::DONE : PollResult::FAILED; };
+    }
+    e.finish = [self, pbp](PollResult r) {
+      if (r != PollResult::DONE) {
+        LOG(ERROR) << "KVT tx_stub batch failed on completion. DstId=" << self->stub->dstid() << ",DstWorkerId="
+                   << self->stub->dstworkerid() << ",StepIdx=" << pbp->batch.step->step_idx << "." << pbp->batch.substepid
+                   << ',' << pbp->flush_out;
+        if (pbp->ch) self->drop_channel.store(true);
+      }
+      self->finish(*pbp, r == PollResult::DONE);
+      pbp->ch.reset();
+      self->completing.fetch_sub(1, std::memory_order_acq_rel);
+    };
+    CompletionPoller::instance().add(std::move(e));
   }
 };
 
@@ -273,11 +332,19 @@ KvSendStub::KvSendStub(InstanceId dstid, WorkerId dstworkerid, const WorkerInfo&
       impl_(std::make_unique<Impl>(this, src_info, std::move(naming), start_layer, num_layers,
                                    std::move(channel_factory), cache_shape, std::move(send_done_addr))) {}
 
-KvSendStub::~KvSendStub() = default;
+KvSendStub::~KvSendStub() {
+  // batches still completing hold pointers into this stub: wait for them (each one is bounded by its deadline)
+  const Timepoint give_up = SteadyClock::now() + std::chrono::milliseconds(env_completion_timeout_ms() + 2000);
+  while (impl_->completing.load(std::memory_order_acquire) > 0 && SteadyClock::now() < give_up)
+    std::this_thread::sleep_for(std::chrono::microseconds(200));
+}
+
+bool KvSendStub::idle() const { return impl_->completing.load(std::memory_order_acquire) == 0; }
 
 void KvSendStub::send_batch(BatchSendTask batch) noexcept {
-  impl_->do_task(batch);
-  impl_->clear();
+  auto pb = std::make_shared<PendingBatch>();
+  pb->batch = std::move(batch);
+  impl_->do_task(std::move(pb));
 }
 
 KvSendStubFactory::KvSendStubFactory(Context* ctx, std::shared_ptr<INamingClient> naming)

@@ -7,6 +7,7 @@
 // so the next batch reconnects.
 #pragma once
 #include <memory>
+#include <mutex>
 #include <optional>
 #include <vector>
 
@@ -24,6 +25,7 @@ struct BatchSendTask {
   std::vector<ReqSendTask> tasks;
   uint32_t substepid = 0;      // for logs
   Timepoint send_ts = SteadyClock::now();
+  InflightCounter* inflight = nullptr;   // released once when the batch has been finished (sent or failed)
 };
 
 class ISendStub {
@@ -32,6 +34,8 @@ class ISendStub {
   const InstanceId& dstid() const noexcept { return dstid_; }
   WorkerId dstworkerid() const noexcept { return dstworkerid_; }
   virtual void send_batch(BatchSendTask batch) = 0;
+  // False while batches of this stub are still completing on a device (the stub must stay alive).
+  virtual bool idle() const { return true; }
   virtual ~ISendStub() = default;
 
  protected:
@@ -61,6 +65,7 @@ class SendDoneNotifier {
 
  private:
   void round_trip(const std::vector<char>& buf, int resp_size);
+  std::mutex mu_;   // the sender thread and the completion poller both report finished requests
   uint32_t rank_;
   std::string addr_;
   FdGuard sock_;
@@ -73,6 +78,7 @@ class KvSendStub : public ISendStub {
              std::shared_ptr<INamingWorkerClient> naming, int cache_shape, std::string send_done_addr = "");
   ~KvSendStub() override;
   void send_batch(BatchSendTask batch) noexcept override;
+  bool idle() const override;
 
  private:
   struct Impl;

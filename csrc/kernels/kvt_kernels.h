@@ -94,6 +94,14 @@ typedef struct KvtAttnLaunch {
   uint32_t dst_remote;         // 1: the destination is another GPU's memory.  The quantiser then stages its
                                // output in shared memory and sends it with bulk stores (256-byte NVLink
                                // packets); into local memory its own 16-byte stores are faster.
+  // ---- TMA path: how a tile sits in shared memory and how it leaves ----
+  uint32_t tile_order;         // 0: [slot][head][row] (maps from kvt_encode_tensor_map); 1: [head][slot][row] (maps
+                               // encoded with token_inner = 1).  Both maps of a launch use the same order.
+  uint32_t store_form;         // 0: tensor store through dst_maps; 1: one untiled bulk store per tile, legal when
+                               // kvt_tile_is_flat(dst, n_heads, tile_tokens, tile_order): the tile is one contiguous
+                               // run of the destination, which then crosses NVLink as one linear write
+  uint32_t tma_stages;         // cap of the per-CTA pipeline depth (0: as many as shared memory allows, at most 8)
+  uint32_t cache_hint;         // 1: L2 evict_first policy on the tile loads and stores (streamed once)
 } KvtAttnLaunch;
 
 // Tile count of one request for a given tile size (host helper, also used by tests).
@@ -111,6 +119,13 @@ int kvt_launch_p2d_attn(const KvtAttnLaunch* args, int grid_ctas, int threads, i
 // success, a CUresult or -1 otherwise.  No multicast is ever used with these maps.
 int kvt_encode_tensor_map(void* out, uint64_t base, const KvtLayout* layout, uint32_t box_heads,
                           uint32_t box_tokens);
+// The same with the dimension order chosen: token_inner = 1 encodes {head_bytes/4, slots, heads, blocks, kv}
+// with box {head_bytes/4, box_tokens, box_heads, 1, 1}, so that a tile lands in shared memory as
+// [head][slot][row], the memory order of an HND page (KvtAttnLaunch::tile_order = 1).
+int kvt_encode_tensor_map_ordered(void* out, uint64_t base, const KvtLayout* layout, uint32_t box_heads,
+                                  uint32_t box_tokens, uint32_t token_inner);
+// 1 when a tile of n_heads x tile_tokens rows, kept in that order, is one contiguous run of `layout`.
+int kvt_tile_is_flat(const KvtLayout* layout, uint32_t n_heads, uint32_t tile_tokens, uint32_t token_inner);
 
 // ---- block-relative strided segments (GDN / KDA / PLE recurrent state) -------------------
 // One segment rule: for i in [0,count): copy len bytes from
@@ -242,6 +257,19 @@ int kvt_launch_mc_fanout(const KvtMcFanout* args, int grid_ctas, void* stream);
 int kvt_launch_wait_flag(const uint64_t* flag, uint64_t value, uint64_t timeout_ns,
                          uint32_t* status, void* stream);
 int kvt_launch_set_flag(uint64_t* flag, uint64_t value, void* stream);
+// Device-side completion of a batch of launches.  `status` is the batch's status block in device memory
+// (u32 code, u32 detail, u64 start stamp written by kvt_launch_stamp or zero); `record` is the device address
+// of a KvtCompletion in mapped host memory.  Enqueue it on a stream ordered after the batch: when the stream
+// gets there the kernel copies code, detail and stamps into the record, clears the status block and stores
+// `seq` last (release, system scope).  The host polls record->seq: no stream synchronisation, no copy back.
+typedef struct KvtCompletion {
+  uint64_t seq;
+  uint32_t status;
+  uint32_t detail;
+  uint64_t t_start_ns;
+  uint64_t t_end_ns;
+} KvtCompletion;
+int kvt_launch_complete(uint32_t* status, KvtCompletion* record, uint64_t seq, void* stream);
 // Writes the GPU's nanosecond timer (%globaltimer) to *slot (device or mapped host memory) when the
 // stream reaches this point: device-side timestamps around a batch, comparable across the GPUs of a
 // node, without CUDA events.
@@ -262,6 +290,12 @@ int kvt_host_free(uint64_t host_ptr);
 int kvt_host_register(uint64_t host_ptr, uint64_t bytes, uint64_t* dev_ptr);
 int kvt_host_unregister(uint64_t host_ptr);
 int kvt_sm_count(int dev);
+// Copy-engine copies by raw address (device, peer-mapped or pinned host memory on either side): one
+// cudaMemcpyAsync, or one per {src_off, dst_off, len} triple of a host array.  They are the library
+// baseline the transfer kernels are measured against (the reference's memcpy loop,
+// kvtransfer/src/copy_kernels.cpp:267-294) and the bandwidth ceiling measured inside a benchmark run.
+int kvt_memcpy_async(uint64_t dst, uint64_t src, uint64_t bytes, void* stream);
+int kvt_memcpy_triples(uint64_t dst_base, uint64_t src_base, const uint64_t* host_triples, uint32_t n, void* stream);
 const char* kvt_error_string(int err);
 
 #ifdef __cplusplus

@@ -343,6 +343,35 @@ extern "C" int kvt_launch_stamp(uint64_t* slot, void* stream) {
   return (int)cudaGetLastError();
 }
 
+// Completion record of one batch.  Runs alone on a stream that has been ordered after every kernel of the
+// batch: it moves the batch's status words and timer stamps into the record (mapped host memory), clears the
+// status words for the slot's next batch and publishes the sequence number last, with release semantics at
+// system scope, so that a host thread that reads the sequence number also reads the rest.
+__global__ void kvt_complete_kernel(uint32_t* status, KvtCompletion* rec, uint64_t seq) {
+  uint64_t now;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+  const uint32_t code = status[0], detail = status[1];
+  const uint64_t t0 = *reinterpret_cast<const uint64_t*>(status + 2);
+  rec->status = code;
+  rec->detail = detail;
+  rec->t_start_ns = t0;
+  rec->t_end_ns = now;
+  status[0] = 0;
+  status[1] = 0;
+  status[2] = 0;
+  status[3] = 0;
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(&rec->seq), "l"(seq) : "memory");
+}
+
+extern "C" int kvt_launch_complete(uint32_t* status, KvtCompletion* record, uint64_t seq, void* stream) {
+  if (status == nullptr || record == nullptr || (reinterpret_cast<uintptr_t>(record) & 7u) != 0 ||
+      (reinterpret_cast<uintptr_t>(status) & 7u) != 0)
+    return (int)cudaErrorInvalidValue;
+  kvt_complete_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(status, record, seq);
+  return (int)cudaGetLastError();
+}
+
 extern "C" int kvt_launch_set_flag(uint64_t* flag, uint64_t value, void* stream) {
   kvt_set_flag_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(flag, value);
   return (int)cudaGetLastError();
@@ -461,6 +490,24 @@ extern "C" int kvt_host_register(uint64_t host_ptr, uint64_t bytes, uint64_t* de
 
 extern "C" int kvt_host_unregister(uint64_t host_ptr) {
   return (int)cudaHostUnregister(reinterpret_cast<void*>(host_ptr));
+}
+
+// ---- copy-engine paths: the in-run bandwidth ceilings and the library baseline of the benchmark ----
+extern "C" int kvt_memcpy_async(uint64_t dst, uint64_t src, uint64_t bytes, void* stream) {
+  return (int)cudaMemcpyAsync(reinterpret_cast<void*>(dst), reinterpret_cast<const void*>(src), bytes, cudaMemcpyDefault,
+                              reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int kvt_memcpy_triples(uint64_t dst_base, uint64_t src_base, const uint64_t* host_triples, uint32_t n,
+                                  void* stream) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  for (uint32_t i = 0; i < n; ++i) {
+    const cudaError_t e = cudaMemcpyAsync(reinterpret_cast<void*>(dst_base + host_triples[3ull * i + 1]),
+                                          reinterpret_cast<const void*>(src_base + host_triples[3ull * i]),
+                                          host_triples[3ull * i + 2], cudaMemcpyDefault, st);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
 }
 
 extern "C" int kvt_sm_count(int dev) {

@@ -159,6 +159,32 @@ __device__ __forceinline__ void bulk_store_flat(void* gdst, uint32_t smem_src, u
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_src), "r"(bytes)
                : "memory");
 }
+__device__ __forceinline__ uint64_t policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ void tma_load_5d_hint(uint32_t smem_dst, const void* map, uint32_t bar, int c0, int c1,
+                                                 int c2, int c3, int c4, uint64_t pol) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%2, %3, %4, %5, %6}], [%7], %8;"
+      ::"r"(smem_dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar), "l"(pol)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_5d_hint(const void* map, uint32_t smem_src, int c0, int c1, int c2, int c3,
+                                                  int c4, uint64_t pol) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.global.shared::cta.bulk_group.L2::cache_hint"
+      " [%0, {%2, %3, %4, %5, %6}], [%1], %7;"
+      ::"l"(map), "r"(smem_src), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "l"(pol)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_store_flat_hint(void* gdst, uint32_t smem_src, uint32_t bytes, uint64_t pol) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group.L2::cache_hint [%0], [%1], %2, %3;" ::"l"(gdst),
+               "r"(smem_src), "r"(bytes), "l"(pol)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void bulk_wait_read() {
@@ -296,7 +322,7 @@ __device__ __forceinline__ void simt_quant_tile(const KvtAttnLaunch& p, const Ti
   const uint32_t sc_run = it.ntok * (cpr >> 1);
   const bool staged = stage != nullptr && wide_scales && it.token_inner && nthr == 32u &&
                       p.dst.token_stride == (int64_t)p.dst.head_bytes && p.dst.scale_token_stride == (int64_t)(cpr >> 1) &&
-                      chunks * 16u <= kStagePayload && it.ntok * it.nh * 4u <= kStageScales &&
+                      chunks * 16u <= kStagePayload && (chunks >> 1) <= kStageScales &&
                       ((run_bytes | sc_run | (uint32_t)p.dst.head_stride | (uint32_t)p.dst.scale_head_stride) & 15u) == 0u &&
                       ((reinterpret_cast<uintptr_t>(dst + d_base) | reinterpret_cast<uintptr_t>(dst + sc_base)) & 15u) == 0u;
   if (staged) {
@@ -362,7 +388,9 @@ __device__ __forceinline__ void simt_quant_tile(const KvtAttnLaunch& p, const Ti
         if (active[u] && (lane & 7u) == 0u) {
           const uint32_t packed = e | (e1 << 8) | (e2 << 16) | (e3 << 24);
           if (staged) {
-            *reinterpret_cast<uint32_t*>(stage + kStagePayload + ((((rnd + u) * nthr + tid) / cpr) * (cpr >> 1))) = packed;
+            // chunk i of the tile (destination order) owns scale byte i / 2; lanes with lane % 8 == 0 hold a
+            // multiple of eight, so the word is 4-byte aligned whatever the row length
+            *reinterpret_cast<uint32_t*>(stage + kStagePayload + (((rnd + u) * nthr + tid) >> 1)) = packed;
           } else {
             *reinterpret_cast<uint32_t*>(dst + sc_base + (int64_t)t[u] * p.dst.scale_token_stride +
                                          (int64_t)h[u] * p.dst.scale_head_stride + (c[u] >> 1)) = packed;
@@ -535,10 +563,15 @@ __global__ void __launch_bounds__(512, 2) kvt_p2d_attn_kernel(const __grid_const
       // of dependent loads, so doing it on one thread would serialise ~1 us per tile); lane 0
       // runs the software pipeline: at most n_stages-1 loads in flight, one store behind.
       const uint32_t lane = threadIdx.x;
-      struct Slot { const void* dmap; int c1, c2, c3, c4; };
+      // dmap == nullptr: the tile is one contiguous run of the destination, stored by an untiled bulk copy to `flat`
+      struct Slot { const void* dmap; char* flat; int c1, c2, c3, c4; };
       Slot slots[kMaxStages];
       uint32_t issued = 0, stored = 0;
       bool failed = false;
+      const bool token_inner = p.tile_order != 0u;
+      const bool flat_store = p.store_form != 0u;
+      const bool hinted = p.cache_hint != 0u;
+      const uint64_t pol = hinted ? policy_evict_first() : 0ull;
       auto consume_one = [&]() {
         const uint32_t s = stored % n_stages;
         const uint32_t bar = smem_u32(&bars[s]);
@@ -554,8 +587,15 @@ __global__ void __launch_bounds__(512, 2) kvt_p2d_attn_kernel(const __grid_const
           set_status(p.status, KVT_ERR_TMA_TIMEOUT, stored);
           return;
         }
-        tma_store_5d(slots[s].dmap, smem_u32(smem + (size_t)s * tile_bytes), 0, slots[s].c1, slots[s].c2,
-                     slots[s].c3, slots[s].c4);
+        const uint32_t sm = smem_u32(smem + (size_t)s * tile_bytes);
+        if (slots[s].dmap == nullptr) {
+          if (hinted) bulk_store_flat_hint(slots[s].flat, sm, tile_bytes, pol);
+          else bulk_store_flat(slots[s].flat, sm, tile_bytes);
+        } else if (hinted) {
+          tma_store_5d_hint(slots[s].dmap, sm, 0, slots[s].c1, slots[s].c2, slots[s].c3, slots[s].c4, pol);
+        } else {
+          tma_store_5d(slots[s].dmap, sm, 0, slots[s].c1, slots[s].c2, slots[s].c3, slots[s].c4);
+        }
         bulk_commit();
         ++stored;
       };
@@ -599,11 +639,21 @@ __global__ void __launch_bounds__(512, 2) kvt_p2d_attn_kernel(const __grid_const
               const CUtensorMap* smap = reinterpret_cast<const CUtensorMap*>(p.src_maps) + (p.layer_begin + j_layer);
               const CUtensorMap* dmap = reinterpret_cast<const CUtensorMap*>(p.dst_maps) + (p.layer_begin + j_layer);
               mbar_expect_tx(bar, tile_bytes);
-              tma_load_5d(smem_u32(smem + (size_t)s * tile_bytes), smap, bar, 0, (int)p.src_head0, (int)j_ss,
-                          (int)j_sblk, (int)j_kv);
-              slots[s].dmap = dmap;
-              slots[s].c1 = (int)p.dst_head0;
-              slots[s].c2 = (int)j_ds;
+              // coordinate order of the maps: {row, head, slot, block, kv}, or {row, slot, head, block, kv} when the
+              // tile is kept token-inner (heads outermost in shared memory, the order of an HND destination)
+              const int s1 = token_inner ? (int)j_ss : (int)p.src_head0;
+              const int s2 = token_inner ? (int)p.src_head0 : (int)j_ss;
+              if (hinted) {
+                tma_load_5d_hint(smem_u32(smem + (size_t)s * tile_bytes), smap, bar, 0, s1, s2, (int)j_sblk, (int)j_kv, pol);
+              } else {
+                tma_load_5d(smem_u32(smem + (size_t)s * tile_bytes), smap, bar, 0, s1, s2, (int)j_sblk, (int)j_kv);
+              }
+              slots[s].dmap = flat_store ? nullptr : dmap;
+              slots[s].flat = reinterpret_cast<char*>(p.dst_layers[p.layer_begin + j_layer]) +
+                              (int64_t)j_dblk * p.dst.block_stride + (int64_t)j_kv * p.dst.kv_stride +
+                              (int64_t)j_ds * p.dst.token_stride + (int64_t)p.dst_head0 * p.dst.head_stride;
+              slots[s].c1 = token_inner ? (int)j_ds : (int)p.dst_head0;
+              slots[s].c2 = token_inner ? (int)p.dst_head0 : (int)j_ds;
               slots[s].c3 = (int)j_dblk;
               slots[s].c4 = (int)j_kv;
               ++issued;
@@ -739,6 +789,21 @@ extern "C" uint32_t kvt_req_tiles(uint32_t seen, uint32_t new_tokens, uint32_t t
 
 extern "C" int kvt_encode_tensor_map(void* out, uint64_t base, const KvtLayout* l, uint32_t box_heads,
                                      uint32_t box_tokens) {
+  return kvt_encode_tensor_map_ordered(out, base, l, box_heads, box_tokens, 0);
+}
+
+extern "C" int kvt_tile_is_flat(const KvtLayout* l, uint32_t n_heads, uint32_t tile_tokens, uint32_t token_inner) {
+  const int64_t hb = l->head_bytes;
+  if (token_inner) {
+    // heads outermost: rows of a head adjacent, heads adjacent (HND pages)
+    return l->token_stride == hb && (n_heads == 1 || l->head_stride == (int64_t)tile_tokens * hb) ? 1 : 0;
+  }
+  // tokens outermost: heads of a token adjacent, tokens adjacent (NHD pages, all heads moved)
+  return l->head_stride == hb && (tile_tokens == 1 || l->token_stride == (int64_t)n_heads * hb) ? 1 : 0;
+}
+
+extern "C" int kvt_encode_tensor_map_ordered(void* out, uint64_t base, const KvtLayout* l, uint32_t box_heads,
+                                             uint32_t box_tokens, uint32_t token_inner) {
   if (!load_driver_api()) return -1;
   if (l->head_bytes % 16 != 0 || (base & 15) != 0) return -2;
   if (l->head_bytes / 4 > 256 || box_heads > 256 || box_tokens > 256) return -3;
@@ -752,6 +817,14 @@ extern "C" int kvt_encode_tensor_map(void* out, uint64_t base, const KvtLayout* 
   cuuint64_t gstr[4] = {(cuuint64_t)strides[0], (cuuint64_t)strides[1], (cuuint64_t)strides[2],
                         (cuuint64_t)strides[3]};
   cuuint32_t box[5] = {l->head_bytes / 4, box_heads, box_tokens, 1, 1};
+  if (token_inner) {   // the slot dimension before the head dimension: a tile lands as [head][slot][row]
+    gdim[1] = l->ntpb;
+    gdim[2] = l->num_heads;
+    gstr[0] = (cuuint64_t)strides[1];
+    gstr[1] = (cuuint64_t)strides[0];
+    box[1] = box_tokens;
+    box[2] = box_heads;
+  }
   cuuint32_t estr[5] = {1, 1, 1, 1, 1};
   CUresult r = g_driver.encode_tiled(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_UINT32, 5,
                                      reinterpret_cast<void*>(base), gdim, gstr, box, estr,
@@ -811,6 +884,8 @@ extern "C" int kvt_launch_p2d_attn(const KvtAttnLaunch* args, int grid_ctas, int
       return v != nullptr ? atoi(v) : 0;
     }();
     if (env_stages > 0 && stages > (uint32_t)env_stages) stages = (uint32_t)env_stages;
+    if (a.tma_stages > 0 && stages > a.tma_stages) stages = a.tma_stages;
+    if (a.store_form != 0u && !kvt_tile_is_flat(&a.dst, a.n_heads, a.tile_tokens, a.tile_order)) return (int)cudaErrorInvalidValue;
     const uint64_t per_cta = (total + grid - 1) / grid;
     if (stages > per_cta + 1) stages = (uint32_t)per_cta + 1;
     if (stages < 1) stages = 1;

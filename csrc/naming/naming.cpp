@@ -135,8 +135,10 @@ void FileSysNaming::write_file(const std::string& name, const std::string& conte
 
 // ---- in-process -----------------------------------------------------------------------------
 namespace {
-std::mutex g_mem_mu;
-std::map<std::string, std::map<std::string, std::map<std::string, std::string>>> g_mem;  // space -> inst -> kv
+// never destroyed: clients on other threads may outlive the main thread's exit handlers
+std::mutex& g_mem_mu = *new std::mutex;
+using MemSpaces = std::map<std::string, std::map<std::string, std::map<std::string, std::string>>>;   // space -> inst -> kv
+MemSpaces& g_mem = *new MemSpaces;
 }  // namespace
 
 void MemNaming::store(const std::string& k, const std::string& v) {
@@ -516,7 +518,7 @@ const std::vector<std::string>& EasNaming::list() {
 
 // ---- manager -----------------------------------------------------------------------------------
 NamingManager& NamingManager::instance() {
-  static NamingManager m;
+  static NamingManager& m = *new NamingManager;   // never destroyed (see g_mem)
   return m;
 }
 

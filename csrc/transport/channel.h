@@ -47,13 +47,22 @@ class IChannel {
   }
   // `out` receives key=value metrics of the batch.
   virtual void flush(std::string& out) = 0;
+  // Device transports complete a batch without a host wait: flush_async() enqueues a completion record
+  // behind the batch and returns its ticket at once; poll_completion() says whether that record has
+  // arrived (DONE: `out` receives the metrics; FAILED: `out` says why).  Tickets complete in order.
+  virtual bool async_flush() const { return false; }
+  virtual uint64_t flush_async() { return 0; }
+  virtual PollResult poll_completion(uint64_t ticket, std::string& out) {
+    (void)ticket; (void)out;
+    return PollResult::DONE;
+  }
   virtual bool is_active() { return true; }
   virtual void close() {}
   virtual const char* name() const = 0;
   virtual ~IChannel() = default;
 };
 
-using Channel = std::unique_ptr<IChannel>;
+using Channel = std::shared_ptr<IChannel>;   // a batch still completing keeps its channel alive
 
 class IChannelFactory {
  public:

@@ -185,13 +185,14 @@ std::string CopyPolicy::describe() const {
 }
 
 namespace {
-std::mutex g_policy_mu;
-std::map<int, std::unique_ptr<CopyPolicy>> g_policies;
+// never destroyed: server and sender threads may ask for a policy while the process exits
+std::mutex& g_policy_mu = *new std::mutex;
+std::map<int, std::unique_ptr<CopyPolicy>>& g_policies = *new std::map<int, std::unique_ptr<CopyPolicy>>;
 }  // namespace
 
 void CopyPolicy::reset_for_test() {
   // policies handed out earlier stay alive: a DeviceStage may still hold a reference
-  static std::vector<std::unique_ptr<CopyPolicy>> retired;
+  static std::vector<std::unique_ptr<CopyPolicy>>& retired = *new std::vector<std::unique_ptr<CopyPolicy>>;
   std::lock_guard<std::mutex> g(g_policy_mu);
   for (auto& kv : g_policies) retired.push_back(std::move(kv.second));
   g_policies.clear();

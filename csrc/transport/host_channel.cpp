@@ -419,6 +419,6 @@ class HostChannel : public IChannel {
 
 }  // namespace
 
-Channel make_tcp_channel(Context* ctx, bool use_shm) { return std::make_unique<HostChannel>(ctx, use_shm); }
+Channel make_tcp_channel(Context* ctx, bool use_shm) { return std::make_shared<HostChannel>(ctx, use_shm); }
 
 }  // namespace kvx

@@ -12,8 +12,12 @@
 //              GDN / MLA / KDA pages) and send_data(layer) runs the descriptor-driven copy
 //              kernel from the local tensor into the peer tensor.
 // The channel is device ordered: send_data(layer) makes its stream wait for the layer's CUDA
-// event and returns; nothing on the host waits for the forward pass.  flush() waits for the
-// transfer streams and turns a kernel status word into an exception.
+// event and returns; nothing on the host waits for the forward pass.  Nothing on the host waits for
+// the transfer either: flush_async() enqueues a completion record (sequence number, kernel status
+// words, GPU timer stamps, written into mapped host memory by a one-thread kernel) behind the batch
+// and returns; the completion poller reads the record and finishes the batch.  Every batch runs in
+// one of a few plan slots (device + pinned plan buffer, status block, record, a small stream), sized
+// once at connect from the caches' block counts, so the step path neither allocates nor frees.
 // Only plain peer stores are used here; loads with cluster multicast are never issued.
 #include <cuda_runtime.h>
 #include <unistd.h>
@@ -21,6 +25,7 @@
 #include <map>
 #include <mutex>
 #include <sstream>
+#include <thread>
 
 #include "core/envcfg.h"
 #include "core/fault_inject.h"
@@ -35,13 +40,45 @@ namespace kvx {
 
 namespace {
 
-// IPC mappings are per process; a handle must be opened once and shared by all channels.
+// IPC mappings are per process: a handle is opened once and shared by every channel that maps the same
+// allocation, and closed when the last of them goes away.  The key is the handle itself, which names one
+// allocation of one process: a peer that restarted (even with a recycled pid and the same addresses) hands
+// out different handles, so nothing is ever written through a mapping of memory that no longer exists.
 struct IpcCache {
+  struct Mapping {
+    uint64_t local = 0;
+    uint32_t refs = 0;
+  };
   std::mutex mu;
-  std::map<std::pair<int32_t, uint64_t>, uint64_t> mapped;  // (pid, alloc_base) -> local address
+  std::map<std::string, Mapping> mapped;   // 64 handle bytes -> local address
+  uint64_t acquire(const char* handle64) {
+    std::lock_guard<std::mutex> g(mu);
+    const std::string key(handle64, 64);
+    auto it = mapped.find(key);
+    if (it == mapped.end()) {
+      uint64_t local = 0;
+      cuda_check(kvt_ipc_open_handle(handle64, &local), "cudaIpcOpenMemHandle");
+      it = mapped.emplace(key, Mapping{local, 0}).first;
+    }
+    ++it->second.refs;
+    return it->second.local;
+  }
+  void release(const std::string& key) {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = mapped.find(key);
+    if (it == mapped.end()) return;
+    if (--it->second.refs == 0) {
+      kvt_ipc_close(it->second.local);
+      mapped.erase(it);
+    }
+  }
+  size_t size() {
+    std::lock_guard<std::mutex> g(mu);
+    return mapped.size();
+  }
 };
 IpcCache& ipc_cache() {
-  static IpcCache c;
+  static IpcCache& c = *new IpcCache;   // never destroyed: channels may close while the process exits
   return c;
 }
 
@@ -115,26 +152,26 @@ class NvlinkChannel : public IChannel {
           continue;
         }
         if (!pt.has_handle) throw KVTransferException(ErrorKind::TRANSPORT, "nvlink: destination tensor has no IPC handle");
-        IpcCache& c = ipc_cache();
-        std::lock_guard<std::mutex> g(c.mu);
-        auto key = std::make_pair(info.pid, pt.alloc_base);
-        auto it = c.mapped.find(key);
-        if (it == c.mapped.end()) {
-          uint64_t local = 0;
-          cuda_check(kvt_ipc_open_handle(pt.ipc_handle, &local), "cudaIpcOpenMemHandle");
-          it = c.mapped.emplace(key, local).first;
+        const std::string key(pt.ipc_handle, 64);
+        uint64_t local = 0;
+        for (size_t k = 0; k < ipc_keys_.size() && local == 0; ++k)
+          if (ipc_keys_[k] == key) local = ipc_locals_[k];
+        if (local == 0) {      // one reference per allocation and channel
+          local = ipc_cache().acquire(pt.ipc_handle);
+          ipc_keys_.push_back(key);
+          ipc_locals_.push_back(local);
         }
-        dst_ptrs_[l][t] = it->second + (pt.ptr - pt.alloc_base);
+        dst_ptrs_[l][t] = local + (pt.ptr - pt.alloc_base);
       }
     }
-    // ---- streams -----------------------------------------------------------------------------
+    // ---- streams and plan slots -------------------------------------------------------------
     const int n_streams = std::max(1, env_nvlink_streams());
     for (int i = 0; i < n_streams; ++i) stages_.emplace_back(std::make_unique<DeviceStage>(ctx_->device_id()));
-    void* st = nullptr;
-    cuda_check(cudaMalloc(&st, 64), "cudaMalloc(status)");
-    cuda_check(cudaMemset(st, 0, 64), "cudaMemset");
-    d_status_ = static_cast<uint32_t*>(st);
-    h_status_.reserve(64, true);
+    // A plan holds one descriptor per request and the block tables of both sides.  Sized for every block of
+    // both caches in every block group, plus room for a few thousand request descriptors.
+    const size_t groups = std::max<size_t>(1, ctx_->worker_info().num_gdn_layers + ctx_->worker_info().num_ple_layers + 2);
+    const size_t table = (static_cast<size_t>(ctx_->layer_num_blocks()) + dst.layer_num_blocks) * sizeof(uint32_t);
+    alloc_slots(std::max<size_t>(table * std::min<size_t>(groups, 8) + (256u << 10), 512u << 10));
     src_shape_ = ctx_->worker_info().cache_shape_or(env_cache_shape());
     dst_shape_ = dst.cache_shape_or(src_shape_);
     dst_mx_ = dst.ext_int("mx", env_dst_mxfp8()) != 0;
@@ -177,24 +214,10 @@ class NvlinkChannel : public IChannel {
     }
     cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
     ensure_layer_arrays();
-    // upload the plan on stream 0; the other streams wait for it
-    cudaStream_t s0 = static_cast<cudaStream_t>(stages_[0]->stream());
-    const size_t bytes = plan_.blob.size();
-    if (bytes > d_plan_cap_) {
-      if (d_plan_ != nullptr) cuda_check(cudaFree(d_plan_), "cudaFree");
-      d_plan_cap_ = std::max<size_t>(bytes * 2, 1 << 16);
-      cuda_check(cudaMalloc(reinterpret_cast<void**>(&d_plan_), d_plan_cap_), "cudaMalloc(plan)");
-    }
-    memcpy(h_plan_.reserve(bytes, true), plan_.blob.data(), bytes);
-    cuda_check(cudaMemcpyAsync(d_plan_, h_plan_.data(), bytes, cudaMemcpyHostToDevice, s0), "cudaMemcpyAsync(plan)");
-    if (plan_event_ == nullptr) {
-      cudaEvent_t ev;
-      cuda_check(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate");
-      plan_event_ = ev;
-    }
-    stamp_start(s0);
-    cuda_check(cudaEventRecord(static_cast<cudaEvent_t>(plan_event_), s0), "cudaEventRecord");
-    begin_batch();
+    // upload the plan on the slot's stream; the transfer streams wait for it when the batch first uses them
+    Slot& sl = begin_slot(plan_.blob.size());
+    memcpy(sl.h_plan, plan_.blob.data(), plan_.blob.size());
+    upload_slot(sl, plan_.blob.size());
     fused_ = true;
     moved_bytes_per_layer_ = 0;
     for (const ReqSendTask* t : tasks)
@@ -242,25 +265,11 @@ class NvlinkChannel : public IChannel {
     if (total == 0) return;
     cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
     const size_t bytes = total * sizeof(Triple);
-    if (bytes > d_plan_cap_) {
-      for (auto& s : stages_) s->sync();   // nothing may still read the old buffer
-      if (d_plan_ != nullptr) cuda_check(cudaFree(d_plan_), "cudaFree");
-      d_plan_cap_ = std::max<size_t>(bytes * 2, 1 << 16);
-      cuda_check(cudaMalloc(reinterpret_cast<void**>(&d_plan_), d_plan_cap_), "cudaMalloc(descriptors)");
-    }
-    char* h = h_plan_.reserve(bytes, true);
+    Slot& sl = begin_slot(bytes);
     for (size_t t = 0; t < generic_.size(); ++t)
-      if (!generic_[t].empty()) memcpy(h + generic_off_[t] * sizeof(Triple), generic_[t].data(), generic_[t].size() * sizeof(Triple));
-    cudaStream_t s0 = static_cast<cudaStream_t>(stages_[0]->stream());
-    cuda_check(cudaMemcpyAsync(d_plan_, h, bytes, cudaMemcpyHostToDevice, s0), "cudaMemcpyAsync(descriptors)");
-    if (plan_event_ == nullptr) {
-      cudaEvent_t ev;
-      cuda_check(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate");
-      plan_event_ = ev;
-    }
-    stamp_start(s0);
-    cuda_check(cudaEventRecord(static_cast<cudaEvent_t>(plan_event_), s0), "cudaEventRecord");
-    begin_batch();
+      if (!generic_[t].empty())
+        memcpy(sl.h_plan + generic_off_[t] * sizeof(Triple), generic_[t].data(), generic_[t].size() * sizeof(Triple));
+    upload_slot(sl, bytes);
   }
 
   bool send_layers(size_t layer_begin, size_t layer_end, Step* step) override {
@@ -274,7 +283,7 @@ class NvlinkChannel : public IChannel {
     cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
     // one launch over the layer range on the stream that carried the plan; layer events are
     // recorded in order on one stream, so the last one implies the others
-    DeviceStage& st = *stages_[0];
+    DeviceStage& st = use_stage(0);
     st.wait_event(ctx_->cuda_barrier()->event(static_cast<uint32_t>(layer_end - 1)));
     launch_fused(layer_begin, layer_end, st);
     return true;
@@ -291,17 +300,19 @@ class NvlinkChannel : public IChannel {
       a.dst = params_.dst;
       a.layer_begin = static_cast<uint32_t>(layer_begin);
       a.layer_end = static_cast<uint32_t>(layer_end);
-      a.reqs = reinterpret_cast<const KvtReqDesc*>(d_plan_);
+      a.reqs = reinterpret_cast<const KvtReqDesc*>(cur().d_plan);
       a.n_reqs = plan_.n_reqs;
       a.total_tiles = plan_.total_tiles;
-      a.block_ids = reinterpret_cast<const uint32_t*>(d_plan_ + plan_.pool_offset);
+      a.block_ids = reinterpret_cast<const uint32_t*>(cur().d_plan + plan_.pool_offset);
       a.tile_tokens = params_.tile_tokens;
       a.src_head0 = params_.src_head0;
       a.dst_head0 = params_.dst_head0;
       a.n_heads = params_.n_heads;
       a.mode = params_.mode;
-      a.status = d_status_;
+      a.status = cur().d_status;
       a.dst_remote = dst_remote_ ? 1u : 0u;
+      a.tile_order = tile_order_;
+      a.store_form = store_form_;
       int grid = env_nvlink_ctas();
       // four small CTAs per SM, scaled by the SM-usage knob that bounds what a transfer may take from the forward pass
       if (grid <= 0) grid = std::max(1, static_cast<int>(4 * kvt_sm_count(ctx_->device_id()) * env_kernel_copy_sm_usage()));
@@ -324,9 +335,9 @@ class NvlinkChannel : public IChannel {
     for (size_t t = 0; t < generic_.size(); ++t) {
       if (generic_[t].empty()) continue;
       const size_t dst_cap = dst_.block_sizes.at(t) * static_cast<size_t>(dst_.layer_num_blocks);
-      const uint64_t* d = reinterpret_cast<const uint64_t*>(d_plan_) + generic_off_[t] * 3;
+      const uint64_t* d = reinterpret_cast<const uint64_t*>(cur().d_plan) + generic_off_[t] * 3;
       st.launch_resident(addrs[layer][t], dst_ptrs_[layer][t], d, generic_[t].size(), ctx_->tensor_capacity(t), dst_cap, 0,
-                         d_status_);
+                         cur().d_status);
     }
   }
 
@@ -352,8 +363,8 @@ class NvlinkChannel : public IChannel {
       }
     }
     m.n_tensors = e;
-    m.triples = reinterpret_cast<const uint64_t*>(d_plan_);
-    m.status = d_status_;
+    m.triples = reinterpret_cast<const uint64_t*>(cur().d_plan);
+    m.status = cur().d_status;
     if (env_use_tma() != 0) {
       // pages are long 16-byte aligned runs: the TMA engine moves them, four CTAs per SM
       const int grid = std::max(1, static_cast<int>(4 * kvt_sm_count(ctx_->device_id()) * env_kernel_copy_sm_usage()));
@@ -391,73 +402,270 @@ class NvlinkChannel : public IChannel {
     return n;
   }
 
-  void flush(std::string& out) override {
-    TimeWatch tw;
+  bool async_flush() const override { return true; }
+
+  // Enqueue the batch's completion record and return its ticket; nothing here waits for the GPU.
+  uint64_t flush_async() override {
     cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
     fault_inject_throw();
+    if (batch_slot_ < 0) begin_slot(0);     // a batch without data still completes through a record
+    Slot& sl = cur();
+    cudaStream_t ss = sl.stream;
+    // the slot's stream joins the transfer streams the batch used, and the previous batch's record
+    for (size_t i = 0; i < stages_.size() && i < stage_used_.size(); ++i)
+      if (stage_used_[i]) cuda_check(cudaStreamWaitEvent(ss, static_cast<cudaEvent_t>(stages_[i]->record_done()), 0), "cudaStreamWaitEvent");
+    if (last_done_event_ != nullptr && last_done_event_ != sl.done_event)
+      cuda_check(cudaStreamWaitEvent(ss, last_done_event_, 0), "cudaStreamWaitEvent");
+    if (!fault_inject_drop_completion())
+      cuda_check(kvt_launch_complete(sl.d_status, sl.d_rec, sl.seq, ss), "kvt_launch_complete");
+    cuda_check(cudaEventRecord(sl.done_event, ss), "cudaEventRecord");
+    last_done_event_ = sl.done_event;
+    std::ostringstream ss_m;
+    ss_m << "Proto=nvlink,Path=" << (fused_ ? "fused" : (walk_ ? "walk" : "descriptors")) << ",OriginSbNum=" << origin_blocks_
+         << ",MergedSbNum=" << merged_blocks_ << ",BytesPerLayer=" << moved_bytes_per_layer_ << ",Tiles=" << plan_.total_tiles;
     {
-      // one host wait for the batch: the other streams are joined into the first on the device, the
-      // kernels' shared status words follow them, and the host waits for that copy alone
-      cudaStream_t s0 = static_cast<cudaStream_t>(stages_[0]->stream());
-      for (size_t i = 1; i < stages_.size() && i < stage_used_.size(); ++i)
-        if (stage_used_[i]) stages_[0]->wait_event(stages_[i]->record_done());
-      begin_batch();
-      if (stamps_) cuda_check(kvt_launch_stamp(reinterpret_cast<uint64_t*>(d_status_) + 2, s0), "kvt_launch_stamp");
-      cuda_check(cudaMemcpyAsync(h_status_.data(), d_status_, 24, cudaMemcpyDeviceToHost, s0), "cudaMemcpyAsync(status)");
-      cuda_check(cudaStreamSynchronize(s0), "cudaStreamSynchronize");
-      uint32_t st[2];
-      memcpy(st, h_status_.data(), 8);
-      if (stamps_) {
-        uint64_t t[2];
-        memcpy(t, h_status_.data() + 8, 16);
-        device_us_ = t[1] >= t[0] ? static_cast<int64_t>((t[1] - t[0]) / 1000) : -1;
-      }
-      if (st[0] != 0) {
-        cudaMemset(d_status_, 0, 64);
-        throw KVTransferException(ErrorKind::CUDA, std::string(fused_ ? "transfer" : "copy") + " kernel reported status " +
-                                                       std::to_string(st[0]) + " detail " + std::to_string(st[1]));
+      std::lock_guard<std::mutex> g(slot_mu_);
+      sl.metrics = ss_m.str();
+      sl.flushed_at = SteadyClock::now();
+      sl.pending = true;
+    }
+    const uint64_t ticket = sl.seq;
+    batch_slot_ = -1;
+    generic_.clear();
+    begin_batch();
+    return ticket;
+  }
+
+  PollResult poll_completion(uint64_t ticket, std::string& out) override {
+    std::lock_guard<std::mutex> g(slot_mu_);
+    Done d;
+    bool have = false;
+    auto it = finished_.find(ticket);
+    if (it != finished_.end()) {
+      d = it->second;
+      finished_.erase(it);
+      have = true;
+    } else {
+      for (Slot& sl : slots_) {
+        if (sl.seq != ticket) continue;
+        if (!sl.pending) return PollResult::FAILED;      // never flushed
+        if (!record_arrived(sl)) return PollResult::PENDING;
+        d = take_record(sl);
+        have = true;
+        break;
       }
     }
+    if (!have) {
+      out = "completion ticket unknown";
+      return PollResult::FAILED;
+    }
     std::ostringstream ss;
-    ss << "Proto=nvlink,Path=" << (fused_ ? "fused" : "descriptors") << ",OriginSbNum=" << origin_blocks_
-       << ",MergedSbNum=" << merged_blocks_ << ",BytesPerLayer=" << moved_bytes_per_layer_
-       << ",Tiles=" << plan_.total_tiles << ",FlushUs=" << tw.get_elapse_us();
-    if (stamps_) ss << ",DeviceUs=" << device_us_;   // GPU timer from the plan upload to the last kernel of the batch
+    ss << d.metrics << ",FlushUs=" << d.flush_us;
+    if (d.t_start_ns != 0 && d.t_end_ns >= d.t_start_ns) ss << ",DeviceUs=" << (d.t_end_ns - d.t_start_ns) / 1000;
+    if (d.status != 0) {
+      ss << ",KernelStatus=" << d.status << ",Detail=" << d.detail;
+      out = ss.str();
+      active_ = false;     // the next batch gets a fresh channel
+      return PollResult::FAILED;
+    }
     out = ss.str();
-    generic_.clear();
+    return PollResult::DONE;
+  }
+
+  // The synchronous form, for callers that have nothing else to do: the same record, polled here.
+  void flush(std::string& out) override {
+    const uint64_t ticket = flush_async();
+    const Timepoint deadline = SteadyClock::now() + std::chrono::milliseconds(env_completion_timeout_ms());
+    for (int spins = 0;; ++spins) {
+      const PollResult r = poll_completion(ticket, out);
+      if (r == PollResult::DONE) return;
+      if (r == PollResult::FAILED) throw KVTransferException(ErrorKind::CUDA, "transfer failed: " + out);
+      if (SteadyClock::now() > deadline) {
+        active_ = false;
+        throw KVTransferException(ErrorKind::TRANSPORT, "nvlink: the completion record of a batch did not arrive");
+      }
+      if (spins < 2000) std::this_thread::yield(); else std::this_thread::sleep_for(std::chrono::microseconds(20));
+    }
   }
 
   bool is_active() override { return active_; }
 
   void close() override {
-    if (!active_ && stages_.empty()) return;
+    if (!active_ && stages_.empty() && slots_.empty()) return;
     active_ = false;
     if (ctx_->device_id() >= 0) cudaSetDevice(ctx_->device_id());
+    // batches still in flight keep writing into the slots: let them finish (bounded by the device itself;
+    // every kernel here bounds its own waits) before the memory goes away
+    for (Slot& sl : slots_)
+      if (sl.stream != nullptr) cudaStreamSynchronize(sl.stream);
     stages_.clear();
-    if (d_status_ != nullptr) cudaFree(d_status_);
-    d_status_ = nullptr;
-    if (d_plan_ != nullptr) cudaFree(d_plan_);
-    d_plan_ = nullptr;
-    if (plan_event_ != nullptr) cudaEventDestroy(static_cast<cudaEvent_t>(plan_event_));
-    plan_event_ = nullptr;
+    free_slots();
+    for (const std::string& key : ipc_keys_) ipc_cache().release(key);
+    ipc_keys_.clear();
+    ipc_locals_.clear();
   }
 
  private:
-  // Stream 0 carries the plan; another stream joins it (waits for the upload) when the batch first uses
-  // it, and flush() joins back only the streams that were used: a batch of one launch makes no join at all.
+  static constexpr size_t kSlots = 4;
+  struct Slot {
+    cudaStream_t stream{nullptr};      // carries the plan upload and the completion record of its batch
+    cudaEvent_t plan_event{nullptr};   // the plan is on the device
+    cudaEvent_t done_event{nullptr};   // behind the completion record
+    char* d_plan{nullptr};
+    char* h_plan{nullptr};             // pinned
+    uint32_t* d_status{nullptr};       // 64 bytes: code, detail, start stamp
+    KvtCompletion* h_rec{nullptr};     // mapped host memory ...
+    KvtCompletion* d_rec{nullptr};     // ... and its device address
+    uint64_t seq{0};                   // ticket of the batch that last used the slot
+    bool pending{false};               // flushed, record not yet consumed
+    std::string metrics;
+    Timepoint flushed_at;
+  };
+  struct Done {
+    uint32_t status{0}, detail{0};
+    uint64_t t_start_ns{0}, t_end_ns{0};
+    int64_t flush_us{0};
+    std::string metrics;
+  };
+
+  void alloc_slots(size_t cap) {
+    free_slots();
+    plan_cap_ = (cap + 255) & ~size_t{255};
+    cuda_check(cudaMalloc(reinterpret_cast<void**>(&d_plan_all_), plan_cap_ * kSlots), "cudaMalloc(plans)");
+    cuda_check(cudaHostAlloc(reinterpret_cast<void**>(&h_plan_all_), plan_cap_ * kSlots, cudaHostAllocPortable), "cudaHostAlloc(plans)");
+    cuda_check(cudaMalloc(reinterpret_cast<void**>(&d_status_all_), 64 * kSlots), "cudaMalloc(status)");
+    cuda_check(cudaMemset(d_status_all_, 0, 64 * kSlots), "cudaMemset");
+    void* h = nullptr;
+    cuda_check(cudaHostAlloc(&h, 64 * kSlots, cudaHostAllocMapped | cudaHostAllocPortable), "cudaHostAlloc(records)");
+    memset(h, 0, 64 * kSlots);
+    h_rec_all_ = static_cast<char*>(h);
+    void* d = nullptr;
+    cuda_check(cudaHostGetDevicePointer(&d, h, 0), "cudaHostGetDevicePointer");
+    slots_.assign(kSlots, Slot{});
+    for (size_t i = 0; i < kSlots; ++i) {
+      Slot& sl = slots_[i];
+      cuda_check(cudaStreamCreateWithFlags(&sl.stream, cudaStreamNonBlocking), "cudaStreamCreate");
+      cuda_check(cudaEventCreateWithFlags(&sl.plan_event, cudaEventDisableTiming), "cudaEventCreate");
+      cuda_check(cudaEventCreateWithFlags(&sl.done_event, cudaEventDisableTiming), "cudaEventCreate");
+      sl.d_plan = d_plan_all_ + i * plan_cap_;
+      sl.h_plan = h_plan_all_ + i * plan_cap_;
+      sl.d_status = reinterpret_cast<uint32_t*>(d_status_all_ + 64 * i);
+      sl.h_rec = reinterpret_cast<KvtCompletion*>(h_rec_all_ + 64 * i);
+      sl.d_rec = reinterpret_cast<KvtCompletion*>(static_cast<char*>(d) + 64 * i);
+    }
+  }
+
+  void free_slots() {
+    for (Slot& sl : slots_) {
+      if (sl.plan_event != nullptr) cudaEventDestroy(sl.plan_event);
+      if (sl.done_event != nullptr) cudaEventDestroy(sl.done_event);
+      if (sl.stream != nullptr) cudaStreamDestroy(sl.stream);
+    }
+    slots_.clear();
+    if (d_plan_all_ != nullptr) cudaFree(d_plan_all_);
+    if (h_plan_all_ != nullptr) cudaFreeHost(h_plan_all_);
+    if (d_status_all_ != nullptr) cudaFree(d_status_all_);
+    if (h_rec_all_ != nullptr) cudaFreeHost(h_rec_all_);
+    d_plan_all_ = h_plan_all_ = d_status_all_ = h_rec_all_ = nullptr;
+    last_done_event_ = nullptr;
+    batch_slot_ = -1;
+  }
+
+  static bool record_arrived(const Slot& sl) {
+    return __atomic_load_n(&sl.h_rec->seq, __ATOMIC_ACQUIRE) == sl.seq;
+  }
+
+  // slot_mu_ held.  Moves an arrived record out of its slot.
+  Done take_record(Slot& sl) {
+    Done d;
+    d.status = sl.h_rec->status;
+    d.detail = sl.h_rec->detail;
+    d.t_start_ns = sl.h_rec->t_start_ns;
+    d.t_end_ns = sl.h_rec->t_end_ns;
+    d.flush_us = 0;
+    d.metrics = std::move(sl.metrics);
+    sl.pending = false;
+    return d;
+  }
+
+  Slot& cur() {
+    RTASSERT(batch_slot_ >= 0);
+    return slots_[static_cast<size_t>(batch_slot_)];
+  }
+
+  // Takes the next slot for a new batch.  A slot whose previous batch has not completed makes the sender
+  // wait here (bounded): that is the back-pressure of a sender running more than kSlots batches ahead of
+  // the GPU.  A plan larger than the slots were sized for re-allocates them (all batches drained first).
+  Slot& begin_slot(size_t bytes) {
+    RTASSERT(!slots_.empty());
+    if (bytes > plan_cap_) {
+      LOG(WARNING) << "nvlink: plan of " << bytes << " bytes exceeds the slots sized at connect (" << plan_cap_
+                   << "); re-allocating";
+      for (size_t i = 0; i < slots_.size(); ++i) wait_slot(slots_[i]);
+      for (Slot& sl : slots_) cuda_check(cudaStreamSynchronize(sl.stream), "cudaStreamSynchronize");
+      std::map<uint64_t, Done> keep;
+      uint64_t seq = next_seq_;
+      {
+        std::lock_guard<std::mutex> g(slot_mu_);
+        keep.swap(finished_);
+      }
+      alloc_slots(bytes * 2);
+      std::lock_guard<std::mutex> g(slot_mu_);
+      finished_.swap(keep);
+      next_seq_ = seq;
+    }
+    slot_rr_ = (slot_rr_ + 1) % slots_.size();
+    Slot& sl = slots_[slot_rr_];
+    wait_slot(sl);
+    {
+      std::lock_guard<std::mutex> g(slot_mu_);
+      sl.seq = ++next_seq_;
+      sl.metrics.clear();
+    }
+    batch_slot_ = static_cast<int>(slot_rr_);
+    begin_batch();
+    return sl;
+  }
+
+  // Waits (bounded) until the slot's previous batch has completed and parks its record for the poller.
+  void wait_slot(Slot& sl) {
+    const Timepoint deadline = SteadyClock::now() + std::chrono::milliseconds(env_completion_timeout_ms());
+    for (int spins = 0;; ++spins) {
+      {
+        std::lock_guard<std::mutex> g(slot_mu_);
+        if (!sl.pending) return;
+        if (record_arrived(sl)) {
+          const uint64_t seq = sl.seq;
+          finished_[seq] = take_record(sl);
+          return;
+        }
+      }
+      if (SteadyClock::now() > deadline) {
+        active_ = false;
+        throw KVTransferException(ErrorKind::TRANSPORT, "nvlink: an earlier batch never completed; dropping the channel");
+      }
+      if (spins < 2000) std::this_thread::yield(); else std::this_thread::sleep_for(std::chrono::microseconds(20));
+    }
+  }
+
+  void upload_slot(Slot& sl, size_t bytes) {
+    if (bytes != 0)
+      cuda_check(cudaMemcpyAsync(sl.d_plan, sl.h_plan, bytes, cudaMemcpyHostToDevice, sl.stream), "cudaMemcpyAsync(plan)");
+    if (stamps_) cuda_check(kvt_launch_stamp(reinterpret_cast<uint64_t*>(sl.d_status) + 1, sl.stream), "kvt_launch_stamp");
+    cuda_check(cudaEventRecord(sl.plan_event, sl.stream), "cudaEventRecord");
+  }
+
+  // The slot's stream carries the plan; a transfer stream joins it (waits for the upload) when the batch first
+  // uses it, and the completion record joins back only the streams that were used.
   void begin_batch() { stage_used_.assign(stages_.size(), 0); }
 
   DeviceStage& use_stage(size_t i) {
     if (stage_used_.size() != stages_.size()) stage_used_.assign(stages_.size(), 0);
-    if (i != 0 && !stage_used_[i]) {
-      stages_[i]->wait_event(plan_event_);
+    if (!stage_used_[i]) {
+      stages_[i]->wait_event(cur().plan_event);
       stage_used_[i] = 1;
     }
     return *stages_[i];
-  }
-
-  void stamp_start(cudaStream_t s0) {
-    if (stamps_) cuda_check(kvt_launch_stamp(reinterpret_cast<uint64_t*>(d_status_) + 1, s0), "kvt_launch_stamp");
   }
 
   void ensure_layer_arrays() {
@@ -469,11 +677,18 @@ class NvlinkChannel : public IChannel {
     d_dst_layers_.upload(dst);
     use_tma_ = false;
     if (env_use_tma() != 0 && params_.mode == KVT_MODE_COPY) {
+      // a tile is kept in the destination's own order, so that it leaves as one linear store where the
+      // destination page holds it contiguously (HND pages; NHD pages when every head moves)
+      const int want_order = env_tile_order();
+      tile_order_ = want_order >= 0 ? (want_order != 0 ? 1u : 0u)
+                                    : (params_.dst.token_stride < params_.dst.head_stride ? 1u : 0u);
+      const bool flat_ok = kvt_tile_is_flat(&params_.dst, params_.n_heads, params_.tile_tokens, tile_order_) != 0;
+      store_form_ = (flat_ok && env_store_form() != 0) ? 1u : 0u;
       std::vector<TensorMapBytes> sm(src.size()), dm(dst.size());
       bool ok = true;
       for (size_t i = 0; i < src.size() && ok; ++i) {
-        ok = kvt_encode_tensor_map(sm[i].b, src[i], &params_.src, params_.n_heads, params_.tile_tokens) == 0 &&
-             kvt_encode_tensor_map(dm[i].b, dst[i], &params_.dst, params_.n_heads, params_.tile_tokens) == 0;
+        ok = kvt_encode_tensor_map_ordered(sm[i].b, src[i], &params_.src, params_.n_heads, params_.tile_tokens, tile_order_) == 0 &&
+             kvt_encode_tensor_map_ordered(dm[i].b, dst[i], &params_.dst, params_.n_heads, params_.tile_tokens, tile_order_) == 0;
       }
       if (ok) {
         d_src_maps_.upload(sm);
@@ -495,22 +710,30 @@ class NvlinkChannel : public IChannel {
   // fused path
   bool fused_{false};
   bool use_tma_{false};
+  uint32_t tile_order_{0}, store_form_{0};
   DeviceAttnParams params_{};
   PackedPlan plan_;
-  char* d_plan_{nullptr};
-  size_t d_plan_cap_{0};
-  PinnedBuffer h_plan_;
-  void* plan_event_{nullptr};
+  bool walk_{false};
+  std::vector<Slot> slots_;
+  size_t plan_cap_{0}, slot_rr_{0};
+  int batch_slot_{-1};
+  uint64_t next_seq_{0};
+  char* d_plan_all_{nullptr};
+  char* h_plan_all_{nullptr};
+  char* d_status_all_{nullptr};
+  char* h_rec_all_{nullptr};
+  cudaEvent_t last_done_event_{nullptr};
+  std::mutex slot_mu_;                    // slot bookkeeping is shared with the completion poller's thread
+  std::map<uint64_t, Done> finished_;     // records taken out of a slot that was needed again before they were polled
+  std::vector<std::string> ipc_keys_;     // mappings this channel holds a reference to
+  std::vector<uint64_t> ipc_locals_;
   DevArray<uint64_t> d_src_layers_, d_dst_layers_;
   DevArray<TensorMapBytes> d_src_maps_, d_dst_maps_;
   size_t range_rr_{0};
   bool dst_remote_{false};       // the destination cache lives on another GPU
   std::vector<char> stage_used_;
   uint32_t generic_rounds_{1};   // bulk copy kernel: segment rounds the longest descriptor needs
-  uint32_t* d_status_{nullptr};   // 64 bytes: [0] code, [1] detail, bytes 8..15 start stamp, bytes 16..23 end stamp
   const bool stamps_{env_device_timestamps()};
-  int64_t device_us_{-1};
-  PinnedBuffer h_status_;
   // generic path
   std::vector<std::vector<Triple>> generic_;
   std::vector<size_t> generic_off_;   // first descriptor of each tensor inside the uploaded buffer
@@ -519,7 +742,7 @@ class NvlinkChannel : public IChannel {
 
 }  // namespace
 
-Channel make_nvlink_channel(Context* ctx) { return std::make_unique<NvlinkChannel>(ctx); }
+Channel make_nvlink_channel(Context* ctx) { return std::make_shared<NvlinkChannel>(ctx); }
 
 Channel ChannelFactory::create(const WorkerInfo& dst) {
   const uint8_t mine = ctx_->worker_info().transfer_protocols;

@@ -23,7 +23,7 @@ def load_ops(build_if_missing: bool = True):
     Raises if it cannot be loaded: nothing in this package silently falls back to PyTorch.
     """
     try:
-        return importlib.import_module("llumnix_kv_b200.kvtransfer_ops")
+        return _loaded(importlib.import_module("llumnix_kv_b200.kvtransfer_ops"))
     except ImportError:
         if not build_if_missing or os.environ.get("LLUMNIX_KV_NO_AUTOBUILD") == "1":
             raise
@@ -31,7 +31,22 @@ def load_ops(build_if_missing: bool = True):
 
     _build.build()
     importlib.invalidate_caches()
-    return importlib.import_module("llumnix_kv_b200.kvtransfer_ops")
+    return _loaded(importlib.import_module("llumnix_kv_b200.kvtransfer_ops"))
+
+
+_atexit_registered = False
+
+
+def _loaded(mod):
+    """The process-global client / server of the reference-named functions own threads; stop them while the
+    interpreter is still whole instead of leaving that to the C++ runtime's exit handlers."""
+    global _atexit_registered
+    if not _atexit_registered:
+        import atexit
+
+        atexit.register(mod.shutdown_kv_transfer)
+        _atexit_registered = True
+    return mod
 
 
 def set_envs() -> None:

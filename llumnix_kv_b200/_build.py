@@ -29,6 +29,14 @@ CXX = os.environ.get("CXX", "g++")
 
 GENCODE = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
+# KVX_SANITIZE=address|thread builds the host code with that sanitizer into its own object directory (the
+# reference configures none).  Run the CPU tests of such a build with the sanitizer runtime preloaded:
+#   KVX_SANITIZE=address python -m llumnix_kv_b200._build -f
+#   LD_PRELOAD=$(gcc -print-file-name=libasan.so) ASAN_OPTIONS=detect_leaks=0 python -m pytest tests -m "not gpu"
+SANITIZE = os.environ.get("KVX_SANITIZE", "")
+if SANITIZE:
+    BUILD = ROOT / f"build_{SANITIZE}"
+
 
 def _ext_suffix() -> str:
     return sysconfig.get_config_var("EXT_SUFFIX") or ".so"
@@ -72,12 +80,13 @@ def _compile_one(src: Path, hdr_digest: str, verbose: bool) -> Path:
     if obj.exists() and stamp.exists() and stamp.read_text() == key:
         return obj
     common = ["-O3", "-std=c++17", "-DNDEBUG"] + _includes()
+    san = [f"-fsanitize={SANITIZE}", "-g", "-fno-omit-frame-pointer"] if SANITIZE else []
     if src.suffix == ".cu":
-        cmd = [NVCC, *GENCODE, "-lineinfo", "-Xcompiler", "-fPIC,-Wall,-Wextra,-Wno-unused-parameter",
+        cmd = [NVCC, *GENCODE, "-lineinfo", "-Xcompiler", ",".join(["-fPIC", "-Wall", "-Wextra", "-Wno-unused-parameter"] + san),
                "--expt-relaxed-constexpr", "-Xptxas", "-v" if verbose else "-O3", *common,
                "-c", str(src), "-o", str(obj)]
     else:
-        cmd = [CXX, "-fPIC", "-Wall", "-Wextra", "-Wshadow", "-Wno-unused-parameter", "-pthread", *common,
+        cmd = [CXX, "-fPIC", "-Wall", "-Wextra", "-Wshadow", "-Wno-unused-parameter", "-pthread", *san, *common,
                "-c", str(src), "-o", str(obj)]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
@@ -102,6 +111,8 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     newest = max(o.stat().st_mtime for o in objs)
     if not target.exists() or target.stat().st_mtime < newest or force:
         cmd = [NVCC, *GENCODE, "-shared", "-o", str(target), *map(str, objs), "-lpthread", "-lrt", "-ldl"]
+        if SANITIZE:
+            cmd += ["-Xcompiler", f"-fsanitize={SANITIZE}"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")

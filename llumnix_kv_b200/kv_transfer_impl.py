@@ -327,6 +327,20 @@ class KVTransferClient:
         if self._c is not None:
             self._c.drain()
 
+    def wait_inflight(self, max_batches: int = 0, timeout_s: float = 30.0) -> bool:
+        """Block until at most ``max_batches`` batches of this client are still in flight (handed to the
+        sender threads and not yet finished).  Over the NVLINK transport "finished" means that the batch's
+        completion record, written by the GPU into mapped host memory behind the last transfer kernel, has
+        been read: no stream is synchronised.  ``wait_inflight(0)`` after a step waits for that step;
+        ``wait_inflight(1)`` lets the engine run one step ahead of the transfers.  False on timeout."""
+        if self._c is None:
+            self.drain()
+            return True
+        return bool(self._c.wait_inflight(max_batches, timeout_s))
+
+    def inflight(self) -> int:
+        return int(self._c.inflight()) if self._c is not None else 0
+
     def worker_info(self) -> str:
         return self._c.worker_info() if self._c is not None else _K.current_worker_info("client")
 

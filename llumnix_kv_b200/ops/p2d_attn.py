@@ -96,7 +96,8 @@ class AttnTransfer:
     def __init__(self, src_layout: AttnLayout, dst_layout: AttnLayout, src_ptrs: Sequence[int],
                  dst_ptrs: Sequence[int], device, head_map: Optional[HeadMap] = None, mode: int = MODE_COPY,
                  tile_tokens: Optional[int] = None, use_tma: bool = True, simt_tile: int = 0,
-                 dst_remote: bool = False):
+                 dst_remote: bool = False, tile_order: Optional[int] = None, store_form: Optional[int] = None,
+                 tma_stages: int = 0, cache_hint: int = 0):
         K = _ops()
         assert len(src_ptrs) == len(dst_ptrs)
         self.K = K
@@ -117,11 +118,24 @@ class AttnTransfer:
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self.src_maps = self.dst_maps = None
         self.use_tma = False
+        # TMA tiles sit in shared memory in the destination's own order (heads outermost for an HND page), and
+        # leave as ONE linear bulk store when that makes the tile a contiguous run of the destination; both can be
+        # forced (tile_order 0 / 1, store_form 0 / 1) for measurements.
+        hm = self.head_map
+        if tile_order is None:
+            tile_order = 1 if self.dst_kvt.token_stride < self.dst_kvt.head_stride else 0
+        flat_ok = K.kvt_tile_is_flat(self.dst_kvt, hm.n_heads, self.tile_tokens, tile_order)
+        if store_form is None:
+            store_form = 1 if flat_ok else 0
+        if store_form and not flat_ok:
+            raise ValueError("store_form=1 needs tiles that are contiguous in the destination layout")
+        self.tile_order, self.store_form, self.tma_stages, self.cache_hint = tile_order, store_form, tma_stages, cache_hint
         if use_tma and mode == MODE_COPY:
             try:
-                hm = self.head_map
-                sm = b"".join(K.kvt_encode_tensor_map(p, self.src_kvt, hm.n_heads, self.tile_tokens) for p in src_ptrs)
-                dm = b"".join(K.kvt_encode_tensor_map(p, self.dst_kvt, hm.n_heads, self.tile_tokens) for p in dst_ptrs)
+                sm = b"".join(K.kvt_encode_tensor_map(p, self.src_kvt, hm.n_heads, self.tile_tokens, tile_order)
+                              for p in src_ptrs)
+                dm = b"".join(K.kvt_encode_tensor_map(p, self.dst_kvt, hm.n_heads, self.tile_tokens, tile_order)
+                              for p in dst_ptrs)
                 self.src_maps = torch.frombuffer(bytearray(sm), dtype=torch.uint8).to(self.device)
                 self.dst_maps = torch.frombuffer(bytearray(dm), dtype=torch.uint8).to(self.device)
                 assert self.src_maps.data_ptr() % 64 == 0 and self.dst_maps.data_ptr() % 64 == 0
@@ -148,7 +162,8 @@ class AttnTransfer:
             self.src_kvt, self.dst_kvt, layer_begin, layer_end, plan.reqs_ptr, plan.n_reqs, plan.total_tiles,
             plan.block_ids_ptr, self.tile_tokens, hm.src_head0, hm.dst_head0, hm.n_heads, self.mode,
             self.status.data_ptr(), self.status.data_ptr() + 8 if flag_ptr else 0, flag_ptr, flag_value,
-            grid, threads, 1 if tma else 0, s, self.simt_tile, 1 if self.dst_remote else 0)
+            grid, threads, 1 if tma else 0, s, self.simt_tile, 1 if self.dst_remote else 0, self.tile_order,
+            self.store_form, self.tma_stages, self.cache_hint)
 
     def check_status(self) -> Tuple[int, int]:
         st = self.status[:2].tolist()

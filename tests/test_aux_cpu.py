@@ -87,7 +87,7 @@ def test_kv_specs():
 def test_prefill_worker_fills_the_paged_cache_and_calls_the_layer_hook():
     import torch
 
-    from llumnix_kv_b200.models.llama_prefill import TINY_GEOMETRY, PrefillWorker
+    from benchmarks.llama_prefill import TINY_GEOMETRY, PrefillWorker
 
     w = PrefillWorker(TINY_GEOMETRY, "cpu", 12)
     toks = torch.randint(0, TINY_GEOMETRY.vocab, (70,))

@@ -284,3 +284,74 @@ def test_device_timestamps_in_the_flush_metrics():
     m = re.search(r"SendStubMetrics\..*Proto=nvlink,Path=fused.*DeviceUs=(-?\d+)", r.stderr)
     assert m is not None, r.stderr[-2000:]
     assert 0 <= int(m.group(1)) < 1_000_000
+
+
+def test_step_completes_through_the_completion_record_without_a_host_sync():
+    """The NVLINK channel finishes a batch from a record that the GPU writes into mapped host memory behind
+    the last transfer kernel: flush returns at once (FlushUs is the enqueue, not the transfer), the
+    engine thread can run a step ahead (wait_inflight(1)), and the bytes are right when the records are in."""
+    rng = random.Random(11)
+    src_l = AttnLayout(CacheShape.FLASH, 96, 16, 8, 128, 2)
+    dst_l = AttnLayout(CacheShape.FLASHINFER, 96, 16, 8, 128, 2)
+    src = [src_l.alloc(DEV, "normal", seed=i) for i in range(L)]
+    dst = [dst_l.alloc(DEV) for _ in range(L)]
+    srv = KVTransferServer("D|0|1", 1, 0, 0, dst_l.block_bytes, dst_l.token_bytes, "fake://", dst, [PT.NVLINK],
+                           num_kv_heads=8, cache_shape=5)
+    cli = KVTransferClient("P|0|1", 1, 0, 0, src_l.block_bytes, src_l.token_bytes, "fake://", src, [PT.NVLINK],
+                           num_kv_heads=8, cache_shape=2)
+    try:
+        reqs = rand_reqs(rng, 8, 96, 96, 16, max_blocks=5)
+        # one request per step, eight steps issued back to back; at most one step may be outstanding when the
+        # next is submitted, none at the end
+        for i, (rid, sb, db, total) in enumerate(reqs):
+            cli.submit_req_send2("D|0|1", 0, rid, 0, total, True, sb, db, srv.worker_info(), stepid=100 + i)
+            cli.start_send_step(100 + i, 1)
+            for layer in range(L):
+                cli.record_event(layer)
+            cli.flush_send_step()
+            assert cli.wait_inflight(1, 20.0)
+            assert cli.inflight() <= 1
+        assert cli.wait_inflight(0, 20.0)
+        assert cli.inflight() == 0
+        chunks = [ReqChunk(sb, db, 0, total) for _, sb, db, total in reqs]
+        for i in range(L):
+            expect = torch.zeros_like(dst[i])
+            reference_transfer(src_l, dst_l, src[i], expect, chunks)
+            assert torch.equal(dst[i], expect)     # no torch.cuda.synchronize(): the records say the data is there
+    finally:
+        srv.stop()
+
+
+def test_a_completion_record_that_never_arrives_fails_the_request_within_its_deadline():
+    """Host-side stall: the batch's kernels run, but its completion record is left out (fault hook), so the
+    poller is never signalled.  The deadline fails the request (send-done code 500 semantics: state FAILED),
+    the channel is dropped, and the next step goes through on a fresh channel.  No kernel waits or hangs."""
+    import llumnix_kv_b200
+
+    K = llumnix_kv_b200.load_ops()
+    lay = AttnLayout(CacheShape.FLASH, 48, 16, 8, 128, 2)
+    src = [lay.alloc(DEV, "normal", seed=i) for i in range(L)]
+    dst = [lay.alloc(DEV) for _ in range(L)]
+    os.environ["BLLM_KVTRANS_COMPLETION_TIMEOUT_MS"] = "400"
+    K.envcfg_reset_for_test()
+    srv = KVTransferServer("D|0|1", 1, 0, 0, lay.block_bytes, lay.token_bytes, "fake://", dst, [PT.NVLINK], num_kv_heads=8,
+                           cache_shape=2)
+    cli = KVTransferClient("P|0|1", 1, 0, 0, lay.block_bytes, lay.token_bytes, "fake://", src, [PT.NVLINK], num_kv_heads=8,
+                           cache_shape=2)
+    try:
+        K.fault_inject_arm_drop_completion(1)
+        t0 = time.time()
+        run_step(cli, "D|0|1", 0, srv.worker_info(), [("lost", [1, 2], [3, 4], 0, 32, True, True)], 1)
+        took = time.time() - t0
+        assert 0.3 < took < 5.0, took                 # the deadline, not the 7 s RPC timeout and not forever
+        assert cli.inflight() == 0
+        # the data of the "lost" batch did move (only its record was dropped); what matters is that the next
+        # batch is not stuck behind it
+        run_step(cli, "D|0|1", 0, srv.worker_info(), [("next", [5, 6, 7], [8, 9, 10], 0, 40, True, True)], 2)
+        expect = torch.zeros_like(dst[0])
+        reference_transfer(lay, lay, src[0], expect, [ReqChunk([1, 2], [3, 4], 0, 32), ReqChunk([5, 6, 7], [8, 9, 10], 0, 40)])
+        assert torch.equal(dst[0], expect)
+    finally:
+        os.environ.pop("BLLM_KVTRANS_COMPLETION_TIMEOUT_MS", None)
+        K.envcfg_reset_for_test()
+        srv.stop()

@@ -169,6 +169,58 @@ def test_bf16_to_mxfp8_staged_for_a_remote_destination(heads, partial):
         assert torch.equal(d, e)
 
 
+@pytest.mark.parametrize("heads", [(1, 1, None), (2, 2, None)])
+def test_bf16_to_mxfp8_staged_with_256_wide_heads(heads):
+    """Rows of 256 values carry eight scale bytes: one head x 16 tokens fits the staging buffer (bulk
+    stores), two heads do not (direct stores).  Scales must land chunk by chunk in both."""
+    rng = random.Random(19)
+    src_h, dst_h, hm = heads
+    src_l = AttnLayout(CacheShape.FLASH, 24, 16, src_h, 256, 2)
+    dst_l = AttnLayout(CacheShape.FLASHINFER, 24, 16, dst_h, 256, 1, mx_scaled=True)
+    chunks = _rand_chunks(rng, 4, 24, 24, 16, 4, partial=False)
+    _, dst, expect = _run(src_l, dst_l, chunks, n_layers=2, head_map=hm, mode=MODE_BF16_TO_MXFP8, use_tma=False,
+                          dst_remote=True)
+    for d, e in zip(dst, expect):
+        assert torch.equal(d, e)
+
+
+@pytest.mark.parametrize("form", [(0, 0), (1, 0), (1, 1), (0, 1)])
+@pytest.mark.parametrize("stages", [0, 1, 2])
+def test_tma_tile_orders_and_store_forms(form, stages):
+    """Every way a TMA tile can sit in shared memory and leave it moves the same bytes: tokens or heads
+    outermost, a tensor store or one linear bulk store (legal where the destination holds the tile
+    contiguously: HND pages with heads outermost, NHD pages with tokens outermost), with an L2 policy or not."""
+    order, flat = form
+    rng = random.Random(31)
+    src_l = AttnLayout(CacheShape.FLASH if order else CacheShape.FLASHINFER, 64, 16, 8, 128, 2)
+    dst_l = AttnLayout(CacheShape.FLASHINFER if order else CacheShape.FLASH, 80, 16, 8, 128, 2)
+    chunks = _rand_chunks(rng, 5, 64, 80, 16, 8, partial=True)
+    for hint in (0, 1):
+        src = [src_l.alloc(DEV, "normal", seed=10 + i) for i in range(2)]
+        dst = [dst_l.alloc(DEV, "normal", seed=100 + i) for i in range(2)]
+        expect = [d.clone() for d in dst]
+        xfer = AttnTransfer(src_l, dst_l, [s.data_ptr() for s in src], [d.data_ptr() for d in dst], DEV,
+                            tile_order=order, store_form=flat, tma_stages=stages, cache_hint=hint)
+        assert xfer.use_tma
+        xfer.launch(xfer.plan(chunks))
+        torch.cuda.synchronize()
+        assert xfer.check_status() == (0, 0)
+        for i in range(2):
+            reference_transfer(src_l, dst_l, src[i], expect[i], chunks)
+            assert torch.equal(dst[i], expect[i])
+
+
+def test_linear_store_is_refused_where_the_tile_is_not_contiguous():
+    src_l = AttnLayout(CacheShape.FLASH, 16, 16, 8, 128, 2)
+    dst_l = AttnLayout(CacheShape.FLASHINFER, 16, 16, 8, 128, 2)
+    with pytest.raises(ValueError):
+        AttnTransfer(src_l, dst_l, [0], [0], DEV, tile_order=0, store_form=1, use_tma=False)
+    # P>D reshard into a slice of the heads of an HND page: still one run (heads are adjacent)
+    x = AttnTransfer(AttnLayout(CacheShape.FLASH, 16, 16, 2, 128, 2), AttnLayout(CacheShape.FLASHINFER, 16, 16, 4, 128, 2),
+                     [0], [0], DEV, head_map=HeadMap(0, 2, 2), use_tma=False)
+    assert (x.tile_order, x.store_form) == (1, 1)
+
+
 @pytest.mark.parametrize("dst_shape", [CacheShape.FLASHINFER, CacheShape.QWEN3_NEXT_FLASH])
 def test_bf16_to_mxfp8(dst_shape):
     rng = random.Random(8)
