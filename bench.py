@@ -316,7 +316,7 @@ def main():
 
     if args.mode == "linkprobe":
         rows = BL.link_probe(pair)
-        checked = pair.verify()
+        checked = pair.verified_layers()
         if rank == 0:
             best = max(rows, key=lambda r: r["per_pair_GBps"])
             print(json.dumps({"metric": "p2d_store_form_probe_GBps", "unit": "GB/s per pair, kernel-only", "n_gpus": args.gpus,
@@ -380,7 +380,7 @@ def main():
                                                 pair.is_sender, args.min_seconds, sampler_factory=sampler)
         h2d_bytes, d2h_bytes = pair.h2d_bytes_per_step, pair.d2h_bytes_per_step
         e2e_api = "AttnTransfer.plan/launch x layers + completion flag + status read"
-    layers_verified = pair.verify()
+    layers_verified = pair.verified_layers()
     post = None
     if args.e2e_path == "engine":
         pair.close_engine()

@@ -292,6 +292,52 @@ def link_probe(pair: PDBenchPair, seconds_per_case: float = 0.25) -> List[dict]:
                      "store": "linear bulk" if form else "tensor", "stages": stages or "auto", "ctas": grid,
                      "l2_evict_first": bool(hint), "ms_per_step": round(per_step, 4),
                      "per_pair_GBps": round(pair.bytes_per_step / per_step / 1e6, 1) if per_step > 0 else 0.0})
+    # ---- pull: the decode GPU runs the same kernel and LOADS the tiles over NVLink (plain TMA loads from
+    #      peer memory, no multicast), storing into its own cache -----------------------------------------
+    if not pair.loopback:
+        pair.map_src_on_receiver()
+        pull = None
+        plans = None
+        if pair.is_receiver:
+            dst_ptrs = [pair.dst.data_ptr() + i * pair.dst_l.layer_bytes for i in range(pair.n_layers)]
+            pull = AttnTransfer(pair.src_l, pair.dst_l, pair.src_peer_ptrs, dst_ptrs, dev, tile_order=1, store_form=1)
+            with torch.cuda.stream(pair.stream):
+                plans = [pull.plan(cs, stream=pair.stream) for cs in pair.slot_chunks]
+            torch.cuda.synchronize()
+        for stages, grid in ((0, 592), (2, 592), (4, 296), (0, 1184)):
+            ms_total, n_steps = 0.0, 0
+
+            def pull_step(i, stages=stages, grid=grid):
+                pull.tma_stages = stages
+                pair._fan_out()
+                for layer in range(pair.n_layers):
+                    pull.launch(plans[i % pair.slots], layer, layer + 1, stream=lanes[layer % len(lanes)], grid=grid)
+                pair._fan_in()
+
+            if pair.is_receiver:
+                for i in range(3):
+                    pull_step(i)
+            dist.barrier()
+            torch.cuda.synchronize()
+            if pair.is_receiver:
+                i = 3
+                while ms_total < seconds_per_case * 1e3 and n_steps < 2000:
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(pair.stream)
+                    for _ in range(10):
+                        pull_step(i)
+                        i += 1
+                    e1.record(pair.stream)
+                    torch.cuda.synchronize()
+                    ms_total += e0.elapsed_time(e1)
+                    n_steps += 10
+                assert pull.check_status() == (0, 0)
+            t = torch.tensor([ms_total / max(n_steps, 1)], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            per_step = float(t.item())
+            rows.append({"tile_order": "heads outermost", "store": "PULL: TMA loads from the peer, linear local store",
+                         "stages": stages or "auto", "ctas": grid, "l2_evict_first": False, "ms_per_step": round(per_step, 4),
+                         "per_pair_GBps": round(pair.bytes_per_step / per_step / 1e6, 1) if per_step > 0 else 0.0})
     for s in range(pair.slots):
         pair.touched.add(s)
     return rows

@@ -99,6 +99,7 @@ class PDBenchPair:
                 dst_ptrs = [self.peer_base + off + i * self.dst_l.layer_bytes for i in range(n_layers)]
             self.transport_name = "NVLink P2P stores into CUDA-IPC mapped peer cache"
         self.dst_layer_ptrs = dst_ptrs
+        self.want_pull = False      # set before map_src_on_receiver() by the store-form probe
 
         self.xfer = None
         self.h2d_bytes_per_step = 0
@@ -117,6 +118,25 @@ class PDBenchPair:
             self.seq = 0
             self.status_host = torch.zeros(4, dtype=torch.int32, pin_memory=True)
         torch.cuda.synchronize()
+
+    def map_src_on_receiver(self) -> None:
+        """Maps the prefill cache into the decode rank's address space (CUDA IPC), for the probe's "pull"
+        rows: the decode GPU runs the kernel and loads over NVLink instead of the prefill GPU storing."""
+        import torch.distributed as dist
+
+        self.src_peer_ptrs = None
+        if self.loopback:
+            return
+        mine = None
+        if self.is_sender:
+            h, base, _size = self.K.kvt_ipc_get_handle(self.src.data_ptr())
+            mine = (h, self.src.data_ptr() - base)
+        infos = [None] * self.world
+        dist.all_gather_object(infos, mine)
+        if self.is_receiver:
+            h, off = infos[self.rank - self.n_pairs]
+            base = self.K.kvt_ipc_open_handle(h)
+            self.src_peer_ptrs = [base + off + i * self.src_l.layer_bytes for i in range(self.n_layers)]
 
     def _pair_id(self) -> int:
         return self.rank % self.n_pairs if not self.loopback else 0
@@ -242,7 +262,7 @@ class PDBenchPair:
         # mapped host memory behind each batch; the host reads it to report the requests done
         self.engine_d2h_bytes = 32
         self.engine_api = ("KVTransferClient.submit_req_send2/start_send_step/record_event x layers/flush_send_step, "
-                           "then wait_step_done(): the completion record of the step read on the host")
+                           "then wait_inflight(): completion records read on the host")
 
     def step_engine(self, i: int) -> None:
         """What a prefill worker does in one engine step, through KVTransferClient: submit the
@@ -333,6 +353,17 @@ class PDBenchPair:
                             raise RuntimeError(f"rank {self.rank}: tail tokens differ in layer {layer}")
             checked += 1
         return checked
+
+    def verified_layers(self, layers=None) -> int:
+        """verify() on the decode ranks, the smallest count over them reported on every rank."""
+        n = self.verify(layers)
+        if self.world > 1:
+            import torch.distributed as dist
+
+            t = torch.tensor([n if self.is_receiver else 1 << 30], dtype=torch.int64, device=self.dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+            n = int(t.item())
+        return n
 
 
 # ---------------------------------------------------------------------------------------------

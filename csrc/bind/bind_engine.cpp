@@ -15,6 +15,7 @@
 #include "core/gdr.h"
 #include "core/monitor.h"
 #include "core/fault_inject.h"
+#include "kernels/kvt_kernels.h"
 #include "naming/naming.h"
 #include "plan/device_plan.h"
 #include "plan/planner.h"
@@ -538,6 +539,75 @@ void bind_engine(py::module_& m) {
   m.def("compute_valid_ranks_pd", [](uint32_t p, uint32_t d, int heads) {
     return compute_valid_ranks_pd(p, d, heads).to_string();
   });
+  // The same planner recording walk ops: what the NVLINK transport uploads for the device walk.
+  py::class_<WalkPlan>(m, "WalkPlan")
+      .def_property_readonly("n_ops", [](const WalkPlan& w) { return w.ops.size(); })
+      .def_readonly("n_bulk", &WalkPlan::n_bulk)
+      .def_readonly("bulk_units", &WalkPlan::bulk_units)
+      .def_readonly("simt_units", &WalkPlan::simt_units)
+      .def_readonly("bytes", &WalkPlan::bytes)
+      .def_property_readonly("pool_len", [](const WalkPlan& w) { return w.pool.size(); })
+      .def_property_readonly("pool_offset", [](const WalkPlan& w) { return w.ops.size() * sizeof(KvtWalkOp); })
+      .def("blob", [](const WalkPlan& w) {
+        std::string b(w.ops.size() * sizeof(KvtWalkOp) + w.pool.size() * sizeof(uint32_t), '\0');
+        if (!w.ops.empty()) memcpy(b.data(), w.ops.data(), w.ops.size() * sizeof(KvtWalkOp));
+        if (!w.pool.empty()) memcpy(b.data() + w.ops.size() * sizeof(KvtWalkOp), w.pool.data(), w.pool.size() * sizeof(uint32_t));
+        return py::bytes(b);
+      }, "ops followed by the block-table pool, as uploaded to the device")
+      .def("expand", [](const WalkPlan& w, const std::vector<uint64_t>& src_caps, const std::vector<uint64_t>& dst_caps) {
+        py::list out;
+        for (const WalkPiece& p : expand_walk_plan(w, src_caps, dst_caps))
+          out.append(py::make_tuple(p.tensor, p.zero, p.src_offset, p.dst_offset, p.length));
+        return out;
+      }, "every piece the device walk moves: (tensor, zero_fill, src_offset, dst_offset, length)");
+  m.def("plan_walk", [](const WorkerInfo& src, const WorkerInfo& dst, int cache_shape,
+                        const std::vector<std::tuple<std::string, uint32_t, uint32_t, bool, BlockIds, BlockIds>>& tasks,
+                        bool pad_last) {
+    PlanEnv env;
+    env.src = &src;
+    env.dst = &dst;
+    env.cache_shape = cache_shape;
+    env.pad_last_attn_block = pad_last;
+    PlannerChoice c = bind_planner(env);
+    WalkPlan plan;
+    for (const auto& t : tasks) {
+      auto info = std::make_shared<RequestInfo>(dst.inst_id, dst.worker_id, std::get<0>(t), std::get<4>(t), std::get<5>(t));
+      ReqSendTask task(info, std::get<1>(t), std::get<2>(t), std::get<3>(t));
+      plan_request_ops(c, env, task, plan);
+    }
+    plan.finalize(src.layer_num_blocks, dst.layer_num_blocks);
+    return plan;
+  }, py::arg("src"), py::arg("dst"), py::arg("cache_shape"), py::arg("tasks"), py::arg("pad_last") = true);
+  m.attr("KVT_WALK_OP_BYTES") = static_cast<int>(sizeof(KvtWalkOp));
+  m.def("kvt_launch_walk", [](uint64_t src_ptrs, uint64_t dst_ptrs, uint32_t n_tensors, uint32_t layer_begin, uint32_t layer_end,
+                              const std::vector<uint64_t>& src_caps, const std::vector<uint64_t>& dst_caps, uint64_t ops,
+                              uint32_t n_bulk, uint32_t n_simt, uint64_t bulk_units, uint64_t simt_units, uint64_t pool,
+                              uint32_t pool_len, uint64_t status, int grid, uint64_t stream) {
+    if (n_tensors == 0 || n_tensors > KVT_WALK_MAX_TENSORS || src_caps.size() != n_tensors || dst_caps.size() != n_tensors)
+      throw std::invalid_argument("kvt_launch_walk: 1..8 tensors with one capacity each");
+    KvtWalkLaunch a{};
+    a.src_ptrs = reinterpret_cast<const uint64_t*>(src_ptrs);
+    a.dst_ptrs = reinterpret_cast<const uint64_t*>(dst_ptrs);
+    a.n_tensors = n_tensors;
+    a.layer_begin = layer_begin;
+    a.layer_end = layer_end;
+    for (uint32_t t = 0; t < n_tensors; ++t) {
+      a.src_cap[t] = src_caps[t];
+      a.dst_cap[t] = dst_caps[t];
+    }
+    a.ops = reinterpret_cast<const KvtWalkOp*>(ops);
+    a.n_bulk_ops = n_bulk;
+    a.n_simt_ops = n_simt;
+    a.bulk_units = bulk_units;
+    a.simt_units = simt_units;
+    a.pool = reinterpret_cast<const uint32_t*>(pool);
+    a.pool_len = pool_len;
+    a.status = reinterpret_cast<uint32_t*>(status);
+    const int e = kvt_launch_walk(&a, grid, reinterpret_cast<void*>(stream));
+    if (e != 0) throw std::runtime_error(std::string("kvt_launch_walk: ") + kvt_error_string(e));
+  }, py::arg("src_ptrs"), py::arg("dst_ptrs"), py::arg("n_tensors"), py::arg("layer_begin"), py::arg("layer_end"),
+     py::arg("src_caps"), py::arg("dst_caps"), py::arg("ops"), py::arg("n_bulk"), py::arg("n_simt"), py::arg("bulk_units"),
+     py::arg("simt_units"), py::arg("pool"), py::arg("pool_len"), py::arg("status"), py::arg("grid") = 0, py::arg("stream") = 0);
   m.def("plan_ipc_blocks", &py_plan, py::arg("src"), py::arg("dst"), py::arg("cache_shape"), py::arg("tasks"),
         py::arg("cast_fp8") = false, py::arg("pad_last") = true, py::arg("merge") = false);
   m.def("plan_time_us", &py_plan_time_us, py::arg("src"), py::arg("dst"), py::arg("cache_shape"), py::arg("tasks"),

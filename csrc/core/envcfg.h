@@ -61,6 +61,8 @@ int env_dst_mxfp8();
 int env_use_tma();
 // TMA tiles of the NVLink channel: order in shared memory (0 tokens outermost, 1 heads outermost, -1 = the
 // destination's own order) and how they leave (0 tensor store, 1 one linear bulk store, -1 = linear when legal).
+// 0: the NVLink channel plans hybrid / MLA / KDA shapes on the CPU and uploads byte ranges instead of walk ops.
+int env_nvlink_walk();
 int env_tile_order();
 int env_store_form();
 // Host-staged copies (TCP / SHM transports): start-up measurement of copy kernel against copy

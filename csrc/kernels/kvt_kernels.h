@@ -159,6 +159,81 @@ typedef struct KvtStateLaunch {
 
 int kvt_launch_p2d_state(const KvtStateLaunch* args, int grid_ctas, int threads, void* stream);
 
+// ---- block-table walk for every other cache shape --------------------------------------------
+// The hybrid, MLA and state-page shapes (kvtransfer/include/envcfg.h:25-52: 3, 4, 6, 7, 8) are moved by
+// "walk ops".  One op is an affine rule over a range of positions (tokens, or whole pages) of one request:
+//
+//   for pos in [pos_lo, pos_hi), for i0 < inner[0].count, i1 < inner[1].count, i2 < inner[2].count:
+//     side offset = table[pos / per_block] * block_stride + ((pos % per_block) / per_kb) * kb_stride
+//                   + (pos % per_kb) * pos_stride + add + sum(i_k * inner[k].stride)
+//     copy len bytes from the source offset to the destination offset (or write zeros: KVT_WALK_ZERO)
+//
+// with one table of block ids per side in a shared uint32 pool.  This is what the reference's ParseBlock
+// functions expand on the CPU into one {src, dst, len} triple per piece (kvtransfer/src/parse_block_*.cpp);
+// here the host writes a handful of ops per request, whatever its length, and the kernel does the
+// expansion while it copies.  Positions are grouped in units of `run` (a divisor of both sides' kernel
+// block), inside which both offsets are affine in pos; when pos_stride == len on both sides a unit is one
+// contiguous piece.  Ops whose pieces are long and 16-byte aligned (KVT_WALK_BULK) go through the TMA
+// engine in segments of KVT_WALK_SEG bytes, the others through the SIMT warps.
+#define KVT_WALK_MAX_INNER 3
+#define KVT_WALK_SEG 8192u
+#define KVT_WALK_ZERO 1u         /* write zeros to the destination pieces (tail padding); no source */
+#define KVT_WALK_BULK 2u         /* contiguous, 16-byte aligned pieces: moved by untiled bulk copies */
+#define KVT_WALK_CONTIG 4u       /* pos_stride == len on both sides: the positions of a unit form one piece */
+typedef struct KvtWalkLoop {
+  uint32_t count;
+  uint32_t reserved;
+  int64_t src_stride;
+  int64_t dst_stride;
+} KvtWalkLoop;
+
+typedef struct KvtWalkOp {
+  uint32_t src_tbl, dst_tbl;             // first entry of each side's block table in the pool
+  uint32_t n_src, n_dst;                 // table lengths (bounds)
+  uint32_t pos_lo, pos_hi;
+  uint32_t src_per_block, dst_per_block; // positions per block
+  uint32_t src_per_kb, dst_per_kb;       // positions per kernel block (== per block when pages are not subdivided)
+  int64_t src_block_stride, dst_block_stride;
+  int64_t src_kb_stride, dst_kb_stride;
+  int64_t src_pos_stride, dst_pos_stride;
+  int64_t src_add, dst_add;
+  uint32_t len;                          // bytes per position and inner iteration
+  uint32_t tensor;                       // cache tensor of the layer (multi-tensor shapes)
+  uint32_t flags;                        // KVT_WALK_*
+  uint32_t n_inner;
+  KvtWalkLoop inner[KVT_WALK_MAX_INNER]; // inner[n_inner - 1] varies fastest
+  // filled by kvt_walk_finalize():
+  uint32_t run;                          // positions per unit
+  uint32_t inner_total;                  // product of the inner counts
+  uint32_t segs;                         // KVT_WALK_BULK: segments per piece
+  uint32_t reserved;
+  uint64_t first_unit;                   // exclusive prefix sum of unit counts within the op's class (bulk / simt)
+} KvtWalkOp;
+
+// Completes run / inner_total / segs / flags of every op, orders the array as [bulk ops][simt ops] and
+// fills first_unit.  Returns the number of bulk ops; *bulk_units and *simt_units receive the unit totals.
+// An op whose geometry is not usable (zero run, per_block not a multiple of per_kb, more than
+// KVT_WALK_MAX_INNER loops) makes it return -1.
+int kvt_walk_finalize(KvtWalkOp* ops, uint32_t n_ops, uint64_t* bulk_units, uint64_t* simt_units);
+
+#define KVT_WALK_MAX_TENSORS 8
+typedef struct KvtWalkLaunch {
+  const uint64_t* src_ptrs;    // device: base address per [layer][tensor] (local memory)
+  const uint64_t* dst_ptrs;    // device: the same for the destination (local / peer / host-mapped)
+  uint32_t n_tensors;
+  uint32_t layer_begin, layer_end;
+  uint32_t reserved;
+  uint64_t src_cap[KVT_WALK_MAX_TENSORS];   // bytes of each tensor: every piece is checked against them
+  uint64_t dst_cap[KVT_WALK_MAX_TENSORS];
+  const KvtWalkOp* ops;        // device: [bulk ops][simt ops]
+  uint32_t n_bulk_ops, n_simt_ops;
+  uint64_t bulk_units, simt_units;
+  const uint32_t* pool;        // device: block tables
+  uint32_t pool_len;
+  uint32_t* status;            // device: [0] first error code, [1] detail
+} KvtWalkLaunch;
+int kvt_launch_walk(const KvtWalkLaunch* args, int grid_ctas, void* stream);
+
 // ---- IpcBlock list copy (descriptor-driven; TCP/shm staging and the generic fallback) -----
 // Copies n triples {src_off, dst_off, len} (the 24-byte IpcBlock of the wire format,
 // kvtransfer/include/channel.h:15-21) between two bases.

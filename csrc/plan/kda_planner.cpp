@@ -4,31 +4,19 @@
 #include <algorithm>
 #include <stdexcept>
 
+#include "plan/plan_sink.h"
 #include "plan/planner.h"
 
 namespace kvx {
 
 namespace {
 
-struct Out {
-  std::vector<IpcBlock>& v;
-  size_t src_cap, dst_cap;
-  void put(size_t s, size_t d, size_t len) {
-    if (len == 0 || s > src_cap || len > src_cap - s || d > dst_cap || len > dst_cap - d) {
-      LOG(ERROR) << "KVT GPU buffer range validation failed,copy_path=parse_block_generation,tensor_idx=0"
-                 << ",src_offset=" << s << ",dst_offset=" << d << ",length=" << len << ",src_capacity=" << src_cap
-                 << ",dst_capacity=" << dst_cap;
-      throw std::out_of_range("KVT GPU buffer range validation failed");
-    }
-    v.emplace_back(s, d, len);
-  }
-};
+using namespace plan_detail;
+using Out = Sink;
 
-Out open_out(const PlanEnv& e, std::vector<std::vector<IpcBlock>>& out) {
-  if (out.empty()) out.resize(1);
+Out open_out(const PlanEnv& e, PlanOut& out) {
   RTASSERT(!e.src->block_sizes.empty() && !e.dst->block_sizes.empty());
-  return Out{out[0], e.src->block_sizes[0] * static_cast<size_t>(e.src->layer_num_blocks),
-             e.dst->block_sizes[0] * static_cast<size_t>(e.dst->layer_num_blocks)};
+  return make_sink(e, out, 0);
 }
 
 size_t page_stride(const WorkerInfo& w) { return w.kda_page_stride != 0 ? w.kda_page_stride : w.block_sizes.at(0); }
@@ -112,8 +100,55 @@ void kda_page_split(Out& o, size_t p0, size_t d0, uint32_t g_n, uint32_t g_off, 
 
 enum class Rel { EQ, GT, LT };
 
+// The two page rules above as walk ops over all pages of a group: one op per q / k / v component
+// (with a row loop when the rows come first) and one for the recurrent state.
+void kda_pages_ops(Out& o, const std::vector<uint32_t>& sb, const std::vector<uint32_t>& db, size_t p_stride,
+                   size_t d_stride, uint32_t g_n, uint32_t g_off, const WorkerInfo& src, const KdaGeom& g, bool merge) {
+  const uint32_t rows = static_cast<uint32_t>(g.state_len);
+  if (merge) {
+    size_t pre = 0;
+    if (src.kda_conv_dim_first) {
+      for (size_t dim : src.gdn_conv_channel_dims) {
+        const size_t comp = dim * g.state_len * g.elem;
+        page_op(o, sb, db, p_stride, d_stride, pre, g_n * pre + g_off * comp, comp, {});
+        pre += comp;
+      }
+    } else {
+      const size_t p_row = g.channels * g.elem, d_row = g_n * p_row;
+      for (size_t dim : src.gdn_conv_channel_dims) {
+        const size_t comp = dim * g.elem;
+        page_op(o, sb, db, p_stride, d_stride, pre, g_n * pre + g_off * comp, comp, {{rows, p_row, d_row}});
+        pre += comp;
+      }
+    }
+    page_op(o, sb, db, p_stride, d_stride, g.conv_bytes, g_n * g.conv_bytes + g_off * g.rec_bytes, g.rec_bytes, {});
+    return;
+  }
+  const size_t d_rec = g.rec_bytes / g_n;
+  size_t p_pre = 0, d_pre = 0, d_conv = 0;
+  if (src.kda_conv_dim_first) {
+    for (size_t dim : src.gdn_conv_channel_dims) {
+      const size_t comp = (dim / g_n) * g.state_len * g.elem;
+      page_op(o, sb, db, p_stride, d_stride, p_pre + g_off * comp, d_pre, comp, {});
+      p_pre += g_n * comp;
+      d_pre += comp;
+    }
+    d_conv = d_pre;
+  } else {
+    const size_t p_row = g.channels * g.elem, d_row = p_row / g_n;
+    for (size_t dim : src.gdn_conv_channel_dims) {
+      const size_t comp = (dim / g_n) * g.elem;
+      page_op(o, sb, db, p_stride, d_stride, p_pre + g_off * comp, d_pre, comp, {{rows, p_row, d_row}});
+      p_pre += g_n * comp;
+      d_pre += comp;
+    }
+    d_conv = g.conv_bytes / g_n;
+  }
+  page_op(o, sb, db, p_stride, d_stride, g.conv_bytes + g_off * d_rec, d_conv, d_rec, {});
+}
+
 // KDA state pages leave once, with the request's last chunk.
-void kda_groups(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& out, Rel rel) {
+void kda_groups(const PlanEnv& e, const ReqSendTask& t, PlanOut& out, Rel rel) {
   Out o = open_out(e, out);
   const WorkerInfo& src = *e.src;
   const WorkerInfo& dst = *e.dst;
@@ -133,6 +168,11 @@ void kda_groups(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<
   for (size_t g = 0; g < src.num_gdn_layers; ++g) {
     const auto& sb = t.src_blocks()[g];
     const auto& db = t.dst_blocks()[g];
+    if (o.ops()) {
+      if (rel == Rel::EQ) page_op(o, sb, db, p_stride, d_stride, 0, 0, p_stride, {});
+      else kda_pages_ops(o, sb, db, p_stride, d_stride, g_n, g_off, src, geom, rel == Rel::GT);
+      continue;
+    }
     for (size_t i = 0; i < sb.size(); ++i) {
       const size_t p0 = sb[i] * p_stride, d0 = db[i] * d_stride;
       if (rel == Rel::EQ) o.put(p0, d0, p_stride);
@@ -144,7 +184,7 @@ void kda_groups(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<
 
 // The MLA group is identical on every TP rank; representative ranks send it.  Equal TP moves
 // manager blocks whole; otherwise kernel-block pages move once complete (block-aligned policy).
-void mla_prefix(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& out) {
+void mla_prefix(const PlanEnv& e, const ReqSendTask& t, PlanOut& out) {
   const WorkerInfo& src = *e.src;
   const WorkerInfo& dst = *e.dst;
   if (!e.valid_ranks.test(src.worker_tp_rank)) return;
@@ -160,6 +200,28 @@ void mla_prefix(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<
   const size_t tok = src.hybrid_attn_token_size;
   const size_t kpage = static_cast<size_t>(kb) * tok;
   const size_t p_stride = page_stride(src), d_stride = page_stride(dst);
+  if (o.ops()) {
+    if (src.engine_tp_size == dst.engine_tp_size) {
+      const uint32_t first = t.seen_tokens / s_ntpb;
+      const uint32_t end = t.reach_last_token ? static_cast<uint32_t>(sb.size()) : t.end_tokens() / s_ntpb;
+      const Sink::Side s{&sb, 1, 1, p_stride, 0, 0, 0}, d{&db, 1, 1, d_stride, 0, 0, 0};
+      o.op(&s, d, first, end, static_cast<size_t>(s_ntpb) * tok, {});
+      return;
+    }
+    // positions are kernel-block pages: a page moves once the chunk reaches its end, or with the last chunk
+    RTASSERT(s_ntpb % kb == 0 && d_ntpb % kb == 0);
+    const uint32_t end_tok = t.seen_tokens + t.new_tokens;
+    const uint32_t lo = t.seen_tokens / kb;
+    const uint32_t hi = t.new_tokens == 0 ? lo : (t.reach_last_token ? (end_tok + kb - 1) / kb : end_tok / kb);
+    const Sink::Side s{&sb, s_ntpb / kb, s_ntpb / kb, p_stride, 0, kpage, 0}, d{&db, d_ntpb / kb, d_ntpb / kb, d_stride, 0, kpage, 0};
+    o.op(&s, d, lo, hi, kpage, {});
+    if (!e.pad_last_attn_block || !t.reach_last_token) return;
+    const size_t cap_tok = db.size() * static_cast<size_t>(d_ntpb);
+    if (end_tok >= cap_tok) return;
+    const Sink::Side dz{&db, d_ntpb, d_ntpb, d_stride, 0, tok, 0};
+    o.op(nullptr, dz, end_tok, static_cast<uint32_t>(cap_tok), tok, {});
+    return;
+  }
   if (src.engine_tp_size == dst.engine_tp_size) {
     const size_t first = t.seen_tokens / s_ntpb;
     const size_t end = t.reach_last_token ? sb.size() : t.end_tokens() / s_ntpb;
@@ -206,15 +268,15 @@ void mla_prefix(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<
 
 }  // namespace
 
-void kda_k3_eq(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& out) {
+void kda_k3_eq(const PlanEnv& e, const ReqSendTask& t, PlanOut& out) {
   mla_prefix(e, t, out);
   kda_groups(e, t, out, Rel::EQ);
 }
-void kda_k3_gt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& out) {
+void kda_k3_gt(const PlanEnv& e, const ReqSendTask& t, PlanOut& out) {
   mla_prefix(e, t, out);
   kda_groups(e, t, out, Rel::GT);
 }
-void kda_k3_lt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& out) {
+void kda_k3_lt(const PlanEnv& e, const ReqSendTask& t, PlanOut& out) {
   mla_prefix(e, t, out);
   kda_groups(e, t, out, Rel::LT);
 }

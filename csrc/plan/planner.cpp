@@ -1,4 +1,5 @@
 #include "plan/planner.h"
+#include "plan/plan_sink.h"
 
 #include <algorithm>
 #include <limits>
@@ -41,60 +42,7 @@ RankSet compute_valid_ranks_pd(uint32_t p_tp, uint32_t d_tp, int num_kv_heads) {
 
 namespace {
 
-// Bounds-checked appender for one cache tensor.
-struct Sink {
-  std::vector<IpcBlock>& out;
-  size_t src_cap;
-  size_t dst_cap;
-  size_t src_scale;  // 2 when lengths are fp8 bytes of a bf16 source
-  size_t tensor;
-
-  void put(size_t s, size_t d, size_t len) {
-    const bool scale_bad = src_scale == 0 || len > std::numeric_limits<size_t>::max() / src_scale;
-    const size_t eff = scale_bad ? std::numeric_limits<size_t>::max() : len * src_scale;
-    const bool src_bad = len == 0 || scale_bad || s > src_cap || eff > src_cap - s;
-    const bool dst_bad = len == 0 || d > dst_cap || len > dst_cap - d;
-    if (src_bad || dst_bad) {
-      LOG(ERROR) << "KVT GPU buffer range validation failed,copy_path=parse_block_generation,layer_idx=0"
-                 << ",tensor_idx=" << tensor << ",block_idx=" << out.size()
-                 << ",offset_kind=" << (src_bad ? "src" : "dst") << ",src_offset=" << s << ",dst_offset=" << d
-                 << ",length=" << len << ",length_scale=" << (src_bad ? src_scale : 1)
-                 << ",effective_length=" << (src_bad ? eff : len)
-                 << ",capacity=" << (src_bad ? src_cap : dst_cap);
-      throw std::out_of_range("KVT GPU buffer range validation failed");
-    }
-    out.emplace_back(s, d, len);
-  }
-};
-
-size_t layer_capacity(const WorkerInfo& w, size_t t, const char* side) {
-  if (t >= w.block_sizes.size() || w.layer_num_blocks == 0) {
-    LOG(ERROR) << "KVT parse block capacity metadata mismatch,side=" << side << ",cache_idx=" << t
-               << ",block_size_count=" << w.block_sizes.size() << ",layer_num_blocks=" << w.layer_num_blocks;
-    throw std::out_of_range("KVT parse block capacity metadata mismatch");
-  }
-  const size_t bs = w.block_sizes[t];
-  if (bs > std::numeric_limits<size_t>::max() / w.layer_num_blocks) {
-    throw std::overflow_error("KVT parse block capacity overflow");
-  }
-  return bs * w.layer_num_blocks;
-}
-
-Sink make_sink(const PlanEnv& env, std::vector<std::vector<IpcBlock>>& send_blocks, size_t t) {
-  if (send_blocks.size() <= t) send_blocks.resize(t + 1);
-  return Sink{send_blocks[t], layer_capacity(*env.src, t, "source"), layer_capacity(*env.dst, t, "destination"),
-              env.cast_bf16_to_fp8 ? size_t{2} : size_t{1}, t};
-}
-
-inline size_t at(const std::vector<uint32_t>& v, size_t i) {
-  if (i >= v.size()) throw std::out_of_range("block index beyond the request's block table");
-  return v[i];
-}
-
-inline const std::vector<uint32_t>& group(const BlockIds& ids, size_t g) {
-  if (g >= ids.size()) throw std::out_of_range("block group beyond the request's groups");
-  return ids[g];
-}
+using namespace plan_detail;
 
 // ---- generic walkers -----------------------------------------------------------------------
 
@@ -102,6 +50,11 @@ inline const std::vector<uint32_t>& group(const BlockIds& ids, size_t g) {
 void walk_runs(Sink& k, size_t s_bs, size_t d_bs, size_t tok, uint32_t s_ntpb, uint32_t d_ntpb,
                const std::vector<uint32_t>& sb, const std::vector<uint32_t>& db, uint32_t seen, uint32_t n,
                size_t s_add = 0, size_t d_add = 0) {
+  if (k.ops()) {
+    const Sink::Side s{&sb, s_ntpb, s_ntpb, s_bs, 0, tok, s_add}, d{&db, d_ntpb, d_ntpb, d_bs, 0, tok, d_add};
+    k.op(&s, d, seen, seen + n, tok, {});
+    return;
+  }
   uint32_t pos = seen, left = n;
   while (left > 0) {
     const uint32_t si = pos % s_ntpb, di = pos % d_ntpb;
@@ -120,6 +73,12 @@ void walk_slices(Sink& k, size_t sm_tok, size_t piece, size_t bg_tok, uint32_t n
                  const std::vector<uint32_t>& sm_blocks, const std::vector<uint32_t>& bg_blocks, uint32_t seen,
                  uint32_t n, bool src_is_small, size_t sm_add = 0, size_t bg_add = 0) {
   const size_t sm_bs = sm_tok * ntpb, bg_bs = bg_tok * ntpb;
+  if (k.ops()) {
+    const Sink::Side sm{&sm_blocks, ntpb, ntpb, sm_bs, 0, sm_tok, sm_add};
+    const Sink::Side bg{&bg_blocks, ntpb, ntpb, bg_bs, 0, bg_tok, g_off * piece + bg_add};
+    if (src_is_small) k.op(&sm, bg, seen, seen + n, piece, {}); else k.op(&bg, sm, seen, seen + n, piece, {});
+    return;
+  }
   for (uint32_t pos = seen; pos < seen + n; ++pos) {
     const uint32_t b = pos / ntpb, i = pos % ntpb;
     const size_t sm = at(sm_blocks, b) * sm_bs + i * sm_tok + sm_add;
@@ -142,6 +101,15 @@ void walk_hnd(Sink& k, size_t sm_tok, size_t bg_tok, size_t sm_bs, size_t bg_bs,
   const size_t sm_head = sm_kb * hd, bg_head = bg_kb * hd;
   const size_t group_bytes = static_cast<size_t>(heads) * bg_head;
   RTASSERT(group_bytes * g_n == bg_kbs / 2);
+  if (k.ops()) {
+    RTASSERT(sm_ntpb % sm_kb == 0 && bg_ntpb % bg_kb == 0);
+    const Sink::Side sm{&sm_blocks, sm_ntpb, sm_kb, sm_bs, sm_kbs, hd, 0};
+    const Sink::Side bg{&bg_blocks, bg_ntpb, bg_kb, bg_bs, bg_kbs, hd, g_off * group_bytes};
+    const uint32_t nh = static_cast<uint32_t>(heads);
+    if (src_is_small) k.op(&sm, bg, seen, seen + n, hd, {{nh, sm_head, bg_head}, {2, sm_kbs / 2, bg_kbs / 2}});
+    else k.op(&bg, sm, seen, seen + n, hd, {{nh, bg_head, sm_head}, {2, bg_kbs / 2, sm_kbs / 2}});
+    return;
+  }
   uint32_t pos = seen, left = n;
   while (left > 0) {
     const uint32_t sbi = pos / sm_ntpb, bbi = pos / bg_ntpb;
@@ -178,6 +146,14 @@ void walk_nhd_hybrid(Sink& k, uint32_t sm_ntpb, uint32_t bg_ntpb, size_t sm_tok,
   const size_t sm_step = sm_tok / 2, bg_step = bg_tok / 2;
   const uint32_t sm_layer_ntpb = sm_ntpb / pack, bg_layer_ntpb = bg_ntpb / pack;
   RTASSERT(sm_layer_ntpb * pack == sm_ntpb && bg_layer_ntpb * pack == bg_ntpb);
+  if (k.ops()) {
+    RTASSERT(sm_layer_ntpb % sm_kb == 0 && bg_layer_ntpb % bg_kb == 0);
+    const Sink::Side sm{&sm_blocks, sm_layer_ntpb, sm_kb, sm_bs, pack * sm_kbs, sm_step, 0};
+    const Sink::Side bg{&bg_blocks, bg_layer_ntpb, bg_kb, bg_bs, pack * bg_kbs, bg_step, g_off * sm_step};
+    if (src_is_small) k.op(&sm, bg, seen, seen + n, sm_step, {{pack, sm_kbs, bg_kbs}, {2, sm_kbs / 2, bg_kbs / 2}});
+    else k.op(&bg, sm, seen, seen + n, sm_step, {{pack, bg_kbs, sm_kbs}, {2, bg_kbs / 2, sm_kbs / 2}});
+    return;
+  }
   uint32_t pos = seen, left = n;
   while (left > 0) {
     const uint32_t sbi = pos / sm_layer_ntpb, bbi = pos / bg_layer_ntpb;
@@ -209,6 +185,20 @@ void walk_nhd_hybrid(Sink& k, uint32_t sm_ntpb, uint32_t bg_ntpb, size_t sm_tok,
 // chunk every remaining allocated page (speculative-decode look-ahead) goes too.
 void walk_aligned_pages(Sink& k, size_t bs, const ReqSendTask& task, const std::vector<uint32_t>& sb,
                         const std::vector<uint32_t>& db, uint32_t ntpb) {
+  if (k.ops()) {
+    // the pages the loop below sends: every page the chunk reaches the end of; with the last chunk also the
+    // page it stops in and every allocated page after it
+    const uint32_t end = task.seen_tokens + task.new_tokens;
+    uint32_t lo = task.seen_tokens / ntpb, hi = end / ntpb;
+    if (task.new_tokens == 0) lo = hi = (task.seen_tokens + ntpb - 1) / ntpb;
+    if (task.reach_last_token) {
+      RTASSERT(sb.size() == db.size());
+      hi = std::max<uint32_t>((end + ntpb - 1) / ntpb, static_cast<uint32_t>(sb.size()));
+    }
+    const Sink::Side s{&sb, 1, 1, bs, 0, 0, 0}, d{&db, 1, 1, bs, 0, 0, 0};
+    k.op(&s, d, lo, hi, bs, {});
+    return;
+  }
   uint32_t pos = task.seen_tokens, left = task.new_tokens;
   while (left > 0) {
     const uint32_t b = pos / ntpb, i = pos % ntpb;
@@ -258,6 +248,10 @@ void gdn_equal(Sink& k, size_t bs, size_t n_groups, const BlockIds& sb, const Bl
     const auto& s = group(sb, g);
     const auto& d = group(db, g);
     RTASSERT(s.size() == d.size());
+    if (k.ops()) {
+      page_op(k, s, d, bs, bs, 0, 0, bs, {});
+      continue;
+    }
     for (size_t i = 0; i < s.size(); ++i) k.put(s[i] * bs, d[i] * bs, bs);
   }
 }
@@ -270,6 +264,19 @@ void gdn_merge(Sink& k, size_t p_bs, size_t d_bs, size_t n_groups, uint32_t g_n,
   for (size_t grp = 0; grp < n_groups; ++grp) {
     const auto& s = group(sb, grp);
     const auto& d = group(db, grp);
+    if (k.ops()) {
+      RTASSERT(d.size() >= s.size());
+      size_t pre = 0;
+      for (size_t dim : *g.channel_dims) {
+        const size_t seg = dim * g.elem;
+        page_op(k, s, d, p_bs, d_bs, pre, g_n * pre + g_off * seg, seg,
+                {{static_cast<uint32_t>(g.rows), g.row_bytes, g_n * g.row_bytes}});
+        pre += seg;
+      }
+      RTASSERT(pre == g.row_bytes);
+      page_op(k, s, d, p_bs, d_bs, g.conv_bytes, g_n * g.conv_bytes + g_off * g.ssm_bytes, g.ssm_bytes, {});
+      continue;
+    }
     for (size_t i = 0; i < s.size(); ++i) {
       const size_t p0 = s[i] * p_bs, d0 = at(d, i) * d_bs;
       for (size_t r = 0; r < g.rows; ++r) {
@@ -295,6 +302,20 @@ void gdn_split(Sink& k, size_t p_bs, size_t d_bs, size_t n_groups, uint32_t g_n,
   for (size_t grp = 0; grp < n_groups; ++grp) {
     const auto& s = group(sb, grp);
     const auto& d = group(db, grp);
+    if (k.ops()) {
+      RTASSERT(d.size() >= s.size());
+      size_t p_pre = 0, d_pre = 0;
+      for (size_t dim : *g.channel_dims) {
+        const size_t p_seg = dim * g.elem;
+        RTASSERT(p_seg % g_n == 0);
+        const size_t d_seg = p_seg / g_n;
+        page_op(k, s, d, p_bs, d_bs, p_pre + g_off * d_seg, d_pre, d_seg, {{static_cast<uint32_t>(g.rows), g.row_bytes, d_row}});
+        p_pre += p_seg;
+        d_pre += d_seg;
+      }
+      page_op(k, s, d, p_bs, d_bs, g.conv_bytes + g_off * d_ssm, g.rows * d_row, d_ssm, {});
+      continue;
+    }
     for (size_t i = 0; i < s.size(); ++i) {
       const size_t p0 = s[i] * p_bs, d0 = at(d, i) * d_bs;
       for (size_t r = 0; r < g.rows; ++r) {
@@ -328,6 +349,10 @@ void ple_pages(Sink& k, size_t p_bs, size_t d_bs, const WorkerInfo& src, const B
     const auto& s = group(sb, src.ple_block_group + i);
     const auto& d = group(db, src.ple_block_group + i);
     RTASSERT(s.size() == d.size());
+    if (k.ops()) {
+      page_op(k, s, d, p_bs, d_bs, 0, 0, len, {});
+      continue;
+    }
     for (size_t j = 0; j < s.size(); ++j) k.put(s[j] * p_bs, d[j] * d_bs, len);
   }
 }
@@ -353,7 +378,7 @@ One single_tensor(const PlanEnv& e) {
 }
 
 // ---- shape 1: ragged [block, slot, 2, head, dim] ------------------------------------------------
-void ragged_eq(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& out) {
+void ragged_eq(const PlanEnv& e, const ReqSendTask& t, PlanOut& out) {
   const One o = single_tensor(e);
   RTASSERT(o.p_tok == o.d_tok && o.p_bs == o.d_bs);
   Sink k = make_sink(e, out, 0);
@@ -362,12 +387,12 @@ void ragged_eq(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<I
 }
 
 // Same token size on both sides although P TP > D TP: the cache is replicated (MLA); rank 0 sends.
-void ragged_gt_replicated(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& out) {
+void ragged_gt_replicated(const PlanEnv& e, const ReqSendTask& t, PlanOut& out) {
   if (e.src->worker_tp_rank != 0) return;
   ragged_eq(e, t, out);
 }
 
-void ragged_sliced(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& out, bool p_gt_d) {
+void ragged_sliced(const PlanEnv& e, const ReqSendTask& t, PlanOut& out, bool p_gt_d) {
   const One o = single_tensor(e);
   const size_t sm_tok = p_gt_d ? o.p_tok : o.d_tok, bg_tok = p_gt_d ? o.d_tok : o.p_tok;
   const uint32_t sm_tp = p_gt_d ? e.dst->engine_tp_size : e.kvt_tp_size;
@@ -387,11 +412,11 @@ void ragged_sliced(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vect
   walk_slices(k, sm_tok, sm_k, bg_tok, ntpb, g_off, sm_blocks, bg_blocks, t.seen_tokens, t.new_tokens, p_gt_d,
               sm_k, bg_k);
 }
-void ragged_gt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& o) { ragged_sliced(e, t, o, true); }
-void ragged_lt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& o) { ragged_sliced(e, t, o, false); }
+void ragged_gt(const PlanEnv& e, const ReqSendTask& t, PlanOut& o) { ragged_sliced(e, t, o, true); }
+void ragged_lt(const PlanEnv& e, const ReqSendTask& t, PlanOut& o) { ragged_sliced(e, t, o, false); }
 
 // ---- shape 2: FlashAttention NHD [2, block, slot, head, dim] --------------------------------------
-void flash_eq(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& out) {
+void flash_eq(const PlanEnv& e, const ReqSendTask& t, PlanOut& out) {
   const One o = single_tensor(e);
   RTASSERT(o.p_tok == o.d_tok && o.p_bs == o.d_bs);
   const size_t k_tok = o.p_tok / 2, k_bs = o.p_bs / 2;
@@ -403,7 +428,7 @@ void flash_eq(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<Ip
   walk_runs(k, k_bs, k_bs, k_tok, o.p_ntpb, o.d_ntpb, sb, db, t.seen_tokens, t.new_tokens, s_v, d_v);
 }
 
-void flash_sliced(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& out, bool p_gt_d) {
+void flash_sliced(const PlanEnv& e, const ReqSendTask& t, PlanOut& out, bool p_gt_d) {
   const One o = single_tensor(e);
   uint32_t g_n, g_off;
   if (p_gt_d) {
@@ -432,13 +457,13 @@ void flash_sliced(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vecto
   walk_slices(k, sm_k, piece, bg_k, ntpb, g_off, sm_blocks, bg_blocks, t.seen_tokens, t.new_tokens, p_gt_d,
               p_gt_d ? p_v : d_v, p_gt_d ? d_v : p_v);
 }
-void flash_gt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& o) { flash_sliced(e, t, o, true); }
+void flash_gt(const PlanEnv& e, const ReqSendTask& t, PlanOut& o) { flash_sliced(e, t, o, true); }
 // The reference has no P<D planner for this shape; the mirror rule is provided because the
 // fused kernel supports the fan-out and needs an oracle.
-void flash_lt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& o) { flash_sliced(e, t, o, false); }
+void flash_lt(const PlanEnv& e, const ReqSendTask& t, PlanOut& o) { flash_sliced(e, t, o, false); }
 
 // ---- shape 5: FlashInfer HND [block, 2, head, slot, dim] -----------------------------------------
-void hnd_eq(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& out) {
+void hnd_eq(const PlanEnv& e, const ReqSendTask& t, PlanOut& out) {
   const One o = single_tensor(e);
   RTASSERT(o.p_ntpb == o.d_ntpb);
   Sink k = make_sink(e, out, 0);
@@ -446,7 +471,7 @@ void hnd_eq(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcB
            group(t.src_blocks(), 0), group(t.dst_blocks(), 0), t.seen_tokens, t.new_tokens, true);
 }
 
-void hnd_gt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& out) {
+void hnd_gt(const PlanEnv& e, const ReqSendTask& t, PlanOut& out) {
   if (!e.valid_ranks[e.src->worker_tp_rank]) return;
   const One o = single_tensor(e);
   RTASSERT(o.p_ntpb == o.d_ntpb);
@@ -458,7 +483,7 @@ void hnd_gt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcB
            true);
 }
 
-void hnd_lt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& out) {
+void hnd_lt(const PlanEnv& e, const ReqSendTask& t, PlanOut& out) {
   const One o = single_tensor(e);
   RTASSERT(o.p_ntpb == o.d_ntpb && o.p_tok % o.d_tok == 0);
   const uint32_t g_n = static_cast<uint32_t>(o.p_tok / o.d_tok);
@@ -471,7 +496,7 @@ void hnd_lt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcB
 }
 
 // ---- shape 4: several single-tensor caches per layer (sparse MLA: indexer keys + latent) ------------
-void multi_eq(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& out) {
+void multi_eq(const PlanEnv& e, const ReqSendTask& t, PlanOut& out) {
   if (!e.valid_ranks[e.src->worker_tp_rank]) return;
   RTASSERT(e.src->token_sizes == e.dst->token_sizes && e.src->block_sizes == e.dst->block_sizes);
   for (size_t i = 0; i < e.src->token_sizes.size(); ++i) {
@@ -483,7 +508,7 @@ void multi_eq(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<Ip
   }
 }
 
-void multi_sliced(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& out, bool p_gt_d) {
+void multi_sliced(const PlanEnv& e, const ReqSendTask& t, PlanOut& out, bool p_gt_d) {
   const WorkerInfo& sm = p_gt_d ? *e.src : *e.dst;
   const WorkerInfo& bg = p_gt_d ? *e.dst : *e.src;
   const uint32_t sm_tp = p_gt_d ? e.dst->engine_tp_size : e.kvt_tp_size;
@@ -506,7 +531,7 @@ void multi_sliced(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vecto
   }
 }
 
-void multi_gt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& out) {
+void multi_gt(const PlanEnv& e, const ReqSendTask& t, PlanOut& out) {
   if (e.src->token_sizes == e.dst->token_sizes) {  // replicated latent cache: rank 0 sends everything
     if (e.src->worker_tp_rank != 0) return;
     RTASSERT(e.src->block_sizes == e.dst->block_sizes);
@@ -521,7 +546,7 @@ void multi_gt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<Ip
   }
   multi_sliced(e, t, out, true);
 }
-void multi_lt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& out) {
+void multi_lt(const PlanEnv& e, const ReqSendTask& t, PlanOut& out) {
   if (e.src->token_sizes == e.dst->token_sizes) {  // replicated cache fans out unchanged
     multi_eq(e, t, out);
     return;
@@ -556,7 +581,7 @@ void hybrid_indexer_tokens(Sink& k, const PlanEnv& e, const HybridView& v, const
             group(t.src_blocks(), v.n_gdn), group(t.dst_blocks(), v.n_gdn), t.seen_tokens, t.new_tokens);
 }
 
-void hybrid_eq(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& out, bool hnd) {
+void hybrid_eq(const PlanEnv& e, const ReqSendTask& t, PlanOut& out, bool hnd) {
   const HybridView v = hybrid_view(e);
   RTASSERT(v.o.p_tok == v.o.d_tok && v.o.p_bs == v.o.d_bs);
   RTASSERT(e.src->indexer_blk_ntpb == e.dst->indexer_blk_ntpb);
@@ -574,7 +599,7 @@ void hybrid_eq(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<I
   }
 }
 
-void hybrid_gt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& out, bool hnd) {
+void hybrid_gt(const PlanEnv& e, const ReqSendTask& t, PlanOut& out, bool hnd) {
   const HybridView v = hybrid_view(e);
   const uint32_t p_tp = e.src->engine_tp_size, d_tp = e.dst->engine_tp_size;
   RTASSERT(p_tp > d_tp && p_tp % d_tp == 0);
@@ -599,7 +624,13 @@ void hybrid_gt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<I
     walk_hnd(k, v.o.p_tok, v.o.d_tok, v.o.p_bs, v.o.d_bs, v.o.p_ntpb, v.o.d_ntpb, s_kb, d_kb, heads, attn_n, attn_off,
              sb, db, t.seen_tokens, t.new_tokens, true);
     const uint32_t filled = total % v.o.d_ntpb;
-    if (pad && filled != 0) {
+    if (pad && filled != 0 && k.ops()) {
+      const size_t hd = v.o.p_tok / 2 / static_cast<size_t>(heads);
+      const size_t d_head = static_cast<size_t>(v.o.d_ntpb) * hd;
+      const size_t d_kv = static_cast<size_t>(v.o.d_ntpb) * v.o.d_tok / 2;
+      const Sink::Side d{&db, v.o.d_ntpb, v.o.d_ntpb, v.o.d_bs, 0, hd, attn_off * heads * d_head};
+      k.op(nullptr, d, total, total + (v.o.d_ntpb - filled), hd, {{static_cast<uint32_t>(heads), 0, d_head}, {2, 0, d_kv}});
+    } else if (pad && filled != 0) {
       // one zero run per head and K/V: slots [filled, d_ntpb) of the last destination block
       const size_t hd = v.o.p_tok / 2 / static_cast<size_t>(heads);
       const size_t d_head = static_cast<size_t>(v.o.d_ntpb) * hd;
@@ -619,7 +650,12 @@ void hybrid_gt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<I
                   db, t.seen_tokens, t.new_tokens, true);
   const uint32_t d_layer_ntpb = v.o.d_ntpb / v.pack;
   const uint32_t filled = total % d_layer_ntpb;
-  if (pad && filled != 0) {
+  if (pad && filled != 0 && k.ops()) {
+    const size_t d_kbs = d_kb * v.o.d_tok, p_step = v.o.p_tok / 2, d_step = v.o.d_tok / 2;
+    RTASSERT(d_layer_ntpb % d_kb == 0);
+    const Sink::Side d{&db, d_layer_ntpb, d_kb, v.o.d_bs, v.pack * d_kbs, d_step, attn_off * p_step};
+    k.op(nullptr, d, total, total + (d_layer_ntpb - filled), p_step, {{v.pack, 0, d_kbs}, {2, 0, d_kbs / 2}});
+  } else if (pad && filled != 0) {
     const size_t d_kbs = d_kb * v.o.d_tok, p_step = v.o.p_tok / 2, d_step = v.o.d_tok / 2;
     uint32_t to_fill = d_layer_ntpb - filled, d_pos = total, s_pos = 0;
     while (to_fill > 0) {
@@ -642,7 +678,7 @@ void hybrid_gt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<I
   }
 }
 
-void hybrid_lt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& out, bool hnd) {
+void hybrid_lt(const PlanEnv& e, const ReqSendTask& t, PlanOut& out, bool hnd) {
   const HybridView v = hybrid_view(e);
   const uint32_t p_tp = e.src->engine_tp_size, d_tp = e.dst->engine_tp_size;
   RTASSERT(p_tp < d_tp && d_tp % p_tp == 0);
@@ -674,7 +710,12 @@ void hybrid_lt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<I
       walk_hnd(k, v.o.d_tok, v.o.p_tok, v.o.d_bs, v.o.p_bs, v.o.d_ntpb, v.o.p_ntpb, d_kb, s_kb, d_heads, attn_n,
                attn_off, db, sb, t.seen_tokens, t.new_tokens, false);
       const uint32_t end = static_cast<uint32_t>(db.size()) * v.o.d_ntpb;
-      if (pad && total < end) {
+      if (pad && total < end && k.ops()) {
+        const size_t hd = v.o.d_tok / 2 / static_cast<size_t>(d_heads);
+        const size_t d_head = static_cast<size_t>(v.o.d_ntpb) * hd;
+        const Sink::Side d{&db, v.o.d_ntpb, v.o.d_ntpb, v.o.d_bs, 0, hd, 0};
+        k.op(nullptr, d, total, end, hd, {{static_cast<uint32_t>(d_heads), 0, d_head}, {2, 0, v.o.d_bs / 2}});
+      } else if (pad && total < end) {
         const size_t hd = v.o.d_tok / 2 / static_cast<size_t>(d_heads);
         const size_t d_head = static_cast<size_t>(v.o.d_ntpb) * hd;
         const size_t zero_src = at(sb, 0) * v.o.p_bs;
@@ -695,7 +736,12 @@ void hybrid_lt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<I
                       db, sb, t.seen_tokens, t.new_tokens, false);
       const uint32_t d_layer_ntpb = v.o.d_ntpb / v.pack;
       const uint32_t end = static_cast<uint32_t>(db.size()) * d_layer_ntpb;
-      if (pad && total < end) {
+      if (pad && total < end && k.ops()) {
+        const size_t d_kbs = d_kb * v.o.d_tok, d_step = v.o.d_tok / 2;
+        RTASSERT(d_layer_ntpb % d_kb == 0);
+        const Sink::Side d{&db, d_layer_ntpb, d_kb, v.o.d_bs, v.pack * d_kbs, d_step, 0};
+        k.op(nullptr, d, total, end, d_step, {{v.pack, 0, d_kbs}, {2, 0, d_kbs / 2}});
+      } else if (pad && total < end) {
         const size_t d_kbs = d_kb * v.o.d_tok, d_step = v.o.d_tok / 2;
         const size_t zero_src = at(sb, 0) * v.o.p_bs;
         for (uint32_t pos = total; pos < end;) {
@@ -719,19 +765,19 @@ void hybrid_lt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<I
   }
 }
 
-void hyb_nhd_eq(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& o) { hybrid_eq(e, t, o, false); }
-void hyb_nhd_gt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& o) { hybrid_gt(e, t, o, false); }
-void hyb_nhd_lt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& o) { hybrid_lt(e, t, o, false); }
-void hyb_hnd_eq(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& o) { hybrid_eq(e, t, o, true); }
-void hyb_hnd_gt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& o) { hybrid_gt(e, t, o, true); }
-void hyb_hnd_lt(const PlanEnv& e, const ReqSendTask& t, std::vector<std::vector<IpcBlock>>& o) { hybrid_lt(e, t, o, true); }
+void hyb_nhd_eq(const PlanEnv& e, const ReqSendTask& t, PlanOut& o) { hybrid_eq(e, t, o, false); }
+void hyb_nhd_gt(const PlanEnv& e, const ReqSendTask& t, PlanOut& o) { hybrid_gt(e, t, o, false); }
+void hyb_nhd_lt(const PlanEnv& e, const ReqSendTask& t, PlanOut& o) { hybrid_lt(e, t, o, false); }
+void hyb_hnd_eq(const PlanEnv& e, const ReqSendTask& t, PlanOut& o) { hybrid_eq(e, t, o, true); }
+void hyb_hnd_gt(const PlanEnv& e, const ReqSendTask& t, PlanOut& o) { hybrid_gt(e, t, o, true); }
+void hyb_hnd_lt(const PlanEnv& e, const ReqSendTask& t, PlanOut& o) { hybrid_lt(e, t, o, true); }
 
 }  // namespace
 
 // Defined in kda_planner.cpp (shape 8: KDA state pages + replicated MLA prefix).
-void kda_k3_eq(const PlanEnv&, const ReqSendTask&, std::vector<std::vector<IpcBlock>>&);
-void kda_k3_gt(const PlanEnv&, const ReqSendTask&, std::vector<std::vector<IpcBlock>>&);
-void kda_k3_lt(const PlanEnv&, const ReqSendTask&, std::vector<std::vector<IpcBlock>>&);
+void kda_k3_eq(const PlanEnv&, const ReqSendTask&, PlanOut&);
+void kda_k3_gt(const PlanEnv&, const ReqSendTask&, PlanOut&);
+void kda_k3_lt(const PlanEnv&, const ReqSendTask&, PlanOut&);
 
 PlannerChoice bind_planner(PlanEnv& env) {
   RTASSERT(env.src != nullptr && env.dst != nullptr);

@@ -16,6 +16,7 @@
 
 #include "core/envcfg.h"
 #include "core/types.h"
+#include "kernels/kvt_kernels.h"
 
 namespace kvx {
 
@@ -36,7 +37,36 @@ struct PlanEnv {
   bool pad_last_attn_block{true};
 };
 
-using PlanFn = void (*)(const PlanEnv&, const ReqSendTask&, std::vector<std::vector<IpcBlock>>&);
+// Where a planner function writes: byte ranges per cache tensor (the CPU product: host transports, oracle)
+// or walk ops (the device product: a handful of affine rules per request that the walk kernel expands
+// while it copies, kernels/kvt_kernels.h).  One planner serves both, so the TP relations, group offsets and
+// chunk policies of every cache shape exist once.
+struct WalkPlan {
+  std::vector<KvtWalkOp> ops;
+  std::vector<uint32_t> pool;          // block tables referenced by the ops
+  uint32_t n_bulk = 0;                 // after finalize(): ops[0, n_bulk) go through the TMA engine
+  uint64_t bulk_units = 0, simt_units = 0;
+  uint64_t bytes = 0;                  // payload bytes of one layer (all tensors)
+  void clear() {
+    ops.clear();
+    pool.clear();
+    n_bulk = 0;
+    bulk_units = simt_units = bytes = 0;
+  }
+  // Orders the ops by class, fills their unit bookkeeping and checks every table entry against the block
+  // counts of the two caches (std::out_of_range otherwise).
+  void finalize(uint32_t src_num_blocks, uint32_t dst_num_blocks);
+  bool empty() const { return ops.empty(); }
+};
+
+struct PlanOut {
+  std::vector<std::vector<IpcBlock>>* blocks{nullptr};   // exactly one of the two is set
+  WalkPlan* walk{nullptr};
+  // block tables of the request being planned that are already in walk->pool: (data pointer, pool offset)
+  std::vector<std::pair<const uint32_t*, uint32_t>> tables;
+};
+
+using PlanFn = void (*)(const PlanEnv&, const ReqSendTask&, PlanOut&);
 
 struct PlannerChoice {
   PlanFn fn{nullptr};
@@ -52,8 +82,27 @@ PlannerChoice bind_planner(PlanEnv& env);
 // registered tensor capacities before it is appended (std::out_of_range otherwise).
 inline void plan_request(const PlannerChoice& c, const PlanEnv& env, const ReqSendTask& task,
                          std::vector<std::vector<IpcBlock>>& send_blocks) {
-  c.fn(env, task, send_blocks);
+  PlanOut out;
+  out.blocks = &send_blocks;
+  c.fn(env, task, out);
 }
+
+// The same chunk as walk ops, appended to `plan` (call plan.finalize() after the last request).
+inline void plan_request_ops(const PlannerChoice& c, const PlanEnv& env, const ReqSendTask& task, WalkPlan& plan) {
+  PlanOut out;
+  out.walk = &plan;
+  c.fn(env, task, out);
+}
+
+// Host expansion of walk ops into byte ranges, with the kernel's own unit decode: what the device walk
+// moves, as data.  Every piece is checked against the tensors' capacities (std::out_of_range).
+struct WalkPiece {
+  uint32_t tensor;
+  bool zero;        // destination bytes are zero-filled; src_offset is unused
+  uint64_t src_offset, dst_offset, length;
+};
+std::vector<WalkPiece> expand_walk_plan(const WalkPlan& plan, const std::vector<uint64_t>& src_caps,
+                                        const std::vector<uint64_t>& dst_caps);
 
 // Sort by source offset and coalesce ranges adjacent on both sides.
 // Returns (min_len, max_len, total_len, count) of the merged list.

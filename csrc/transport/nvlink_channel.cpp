@@ -171,7 +171,7 @@ class NvlinkChannel : public IChannel {
     // both caches in every block group, plus room for a few thousand request descriptors.
     const size_t groups = std::max<size_t>(1, ctx_->worker_info().num_gdn_layers + ctx_->worker_info().num_ple_layers + 2);
     const size_t table = (static_cast<size_t>(ctx_->layer_num_blocks()) + dst.layer_num_blocks) * sizeof(uint32_t);
-    alloc_slots(std::max<size_t>(table * std::min<size_t>(groups, 8) + (256u << 10), 512u << 10));
+    alloc_slots(std::max<size_t>(table * std::min<size_t>(groups, 8) + (1u << 20), 2u << 20));
     src_shape_ = ctx_->worker_info().cache_shape_or(env_cache_shape());
     dst_shape_ = dst.cache_shape_or(src_shape_);
     dst_mx_ = dst.ext_int("mx", env_dst_mxfp8()) != 0;
@@ -182,8 +182,10 @@ class NvlinkChannel : public IChannel {
 
   bool register_tasks(const PlanEnv& env, const std::vector<const ReqSendTask*>& tasks) override {
     fused_ = false;
+    walk_ = false;
     generic_.clear();
-    if (dst_ptrs_.empty() || dst_ptrs_[0].size() != 1) return false;
+    origin_blocks_ = merged_blocks_ = 0;
+    if (dst_ptrs_.empty()) return false;
     PlanEnv e = env;
     e.cache_shape = src_shape_;
     PlannerChoice choice;
@@ -193,13 +195,15 @@ class NvlinkChannel : public IChannel {
       return false;
     }
     DeviceAttnParams p;
-    std::string why;
-    if (!device_attn_params(e, choice.kind, src_shape_, dst_shape_, dst_mx_, &p, &why)) {
+    std::string why = "the layer has several cache tensors";
+    if (dst_ptrs_[0].size() != 1 || !device_attn_params(e, choice.kind, src_shape_, dst_shape_, dst_mx_, &p, &why)) {
       if (src_shape_ != dst_shape_ || dst_mx_) {
         throw KVTransferException(ErrorKind::INVALID_OPERATION,
                                   "nvlink: cross-layout / fp8 transfer needs the fused kernel but " + why);
       }
-      return false;
+      // every other shape (hybrid pages, MLA, KDA): the planner records walk ops and the kernel walks the
+      // block tables itself; no per-piece descriptor is built or uploaded
+      return register_walk(e, choice, tasks);
     }
     params_ = p;
     if (p.skip) {
@@ -225,6 +229,61 @@ class NvlinkChannel : public IChannel {
     return true;
   }
 
+  bool register_walk(const PlanEnv& e, const PlannerChoice& choice, const std::vector<const ReqSendTask*>& tasks) {
+    if (env_nvlink_walk() == 0 || e.cast_bf16_to_fp8 || dst_ptrs_[0].size() > KVT_WALK_MAX_TENSORS) return false;
+    walk_plan_.clear();
+    for (const ReqSendTask* t : tasks) plan_request_ops(choice, e, *t, walk_plan_);
+    walk_plan_.finalize(ctx_->layer_num_blocks(), dst_.layer_num_blocks);
+    plan_ = PackedPlan{};
+    moved_bytes_per_layer_ = walk_plan_.bytes;
+    walk_ = true;
+    if (walk_plan_.empty()) return true;       // this rank has nothing to send (not a representative rank)
+    cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
+    ensure_walk_arrays();
+    const size_t ops_bytes = walk_plan_.ops.size() * sizeof(KvtWalkOp);
+    const size_t bytes = ops_bytes + walk_plan_.pool.size() * sizeof(uint32_t);
+    Slot& sl = begin_slot(bytes);
+    memcpy(sl.h_plan, walk_plan_.ops.data(), ops_bytes);
+    memcpy(sl.h_plan + ops_bytes, walk_plan_.pool.data(), walk_plan_.pool.size() * sizeof(uint32_t));
+    upload_slot(sl, bytes);
+    origin_blocks_ = walk_plan_.ops.size();
+    return true;
+  }
+
+  void launch_walk(size_t layer_begin, size_t layer_end, DeviceStage& st) {
+    KvtWalkLaunch a{};
+    a.src_ptrs = d_walk_src_.p;
+    a.dst_ptrs = d_walk_dst_.p;
+    a.n_tensors = static_cast<uint32_t>(dst_ptrs_[0].size());
+    a.layer_begin = static_cast<uint32_t>(layer_begin);
+    a.layer_end = static_cast<uint32_t>(layer_end);
+    for (uint32_t t = 0; t < a.n_tensors; ++t) {
+      a.src_cap[t] = ctx_->tensor_capacity(t);
+      a.dst_cap[t] = dst_.block_sizes.at(t) * static_cast<uint64_t>(dst_.layer_num_blocks);
+    }
+    a.ops = reinterpret_cast<const KvtWalkOp*>(cur().d_plan);
+    a.n_bulk_ops = walk_plan_.n_bulk;
+    a.n_simt_ops = static_cast<uint32_t>(walk_plan_.ops.size()) - walk_plan_.n_bulk;
+    a.bulk_units = walk_plan_.bulk_units;
+    a.simt_units = walk_plan_.simt_units;
+    a.pool = reinterpret_cast<const uint32_t*>(cur().d_plan + walk_plan_.ops.size() * sizeof(KvtWalkOp));
+    a.pool_len = static_cast<uint32_t>(walk_plan_.pool.size());
+    a.status = cur().d_status;
+    int grid = env_nvlink_ctas();
+    if (grid <= 0) grid = std::max(1, static_cast<int>(4 * kvt_sm_count(ctx_->device_id()) * env_kernel_copy_sm_usage()));
+    cuda_check(kvt_launch_walk(&a, grid, st.stream()), "kvt_launch_walk");
+  }
+
+  void ensure_walk_arrays() {
+    if (d_walk_src_.p != nullptr) return;
+    std::vector<uint64_t> src, dst;
+    for (const auto& l : ctx_->layer_data_address()) src.insert(src.end(), l.begin(), l.end());
+    for (const auto& l : dst_ptrs_) dst.insert(dst.end(), l.begin(), l.end());
+    RTASSERT(src.size() == dst.size());
+    d_walk_src_.upload(src);
+    d_walk_dst_.upload(dst);
+  }
+
   void register_data(std::vector<std::vector<IpcBlock>>& data, TPKind kind) override {
     if (env_bf162fp8_conversion() && kind == TPKind::PGTD) {
       throw KVTransferException(ErrorKind::INVALID_OPERATION,
@@ -232,6 +291,7 @@ class NvlinkChannel : public IChannel {
                                 "fp8 decode cache is filled by the block-scaled quantiser (BLLM_KVTRANS_DST_MXFP8)");
     }
     fused_ = false;
+    walk_ = false;
     generic_.assign(data.size(), {});
     moved_bytes_per_layer_ = 0;
     origin_blocks_ = merged_blocks_ = 0;
@@ -274,8 +334,8 @@ class NvlinkChannel : public IChannel {
 
   bool send_layers(size_t layer_begin, size_t layer_end, Step* step) override {
     (void)step;
-    if (!fused_ || layer_end <= layer_begin) return false;
-    if (plan_.n_reqs == 0) return true;
+    if ((!fused_ && !walk_) || layer_end <= layer_begin) return false;
+    if (walk_ ? walk_plan_.empty() : plan_.n_reqs == 0) return true;
     // One launch saves ~100 us of launch and event overhead, which is what matters for a small
     // migration; a large one is faster layer by layer over several streams (measured crossover
     // around half a GiB).
@@ -285,7 +345,7 @@ class NvlinkChannel : public IChannel {
     // recorded in order on one stream, so the last one implies the others
     DeviceStage& st = use_stage(0);
     st.wait_event(ctx_->cuda_barrier()->event(static_cast<uint32_t>(layer_end - 1)));
-    launch_fused(layer_begin, layer_end, st);
+    if (walk_) launch_walk(layer_begin, layer_end, st); else launch_fused(layer_begin, layer_end, st);
     return true;
   }
 
@@ -323,10 +383,15 @@ class NvlinkChannel : public IChannel {
   void send_data(size_t layer, Step* step) override {
     (void)step;
     cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
+    if ((fused_ && plan_.n_reqs == 0) || (walk_ && walk_plan_.empty())) return;   // nothing to send from this rank
     DeviceStage& st = use_stage(layer % stages_.size());
     st.wait_event(ctx_->cuda_barrier()->event(static_cast<uint32_t>(layer)));
     if (fused_) {
       if (plan_.n_reqs != 0) launch_fused(layer, layer + 1, st);
+      return;
+    }
+    if (walk_) {
+      if (!walk_plan_.empty()) launch_walk(layer, layer + 1, st);
       return;
     }
     const auto& addrs = ctx_->layer_data_address();
@@ -381,6 +446,17 @@ class NvlinkChannel : public IChannel {
       send_data(lo, step);
       return 1;
     }
+    if (walk_) {
+      // the layers recorded so far leave in one launch: short per-layer work (state pages, MLA tokens) would
+      // otherwise be bounded by the launch rate
+      if (walk_plan_.empty()) return hi - lo;
+      cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
+      const size_t n = std::min<size_t>(hi - lo, 8);
+      DeviceStage& st = use_stage((range_rr_++) % stages_.size());
+      st.wait_event(ctx_->cuda_barrier()->event(static_cast<uint32_t>(lo + n - 1)));
+      launch_walk(lo, lo + n, st);
+      return n;
+    }
     size_t per_layer = 0;
     for (const auto& g : generic_) per_layer += g.empty() ? 0 : 1;
     const size_t fit = per_layer == 0 ? hi - lo : KVT_COPY_MAX_TENSORS / per_layer;
@@ -422,7 +498,7 @@ class NvlinkChannel : public IChannel {
     last_done_event_ = sl.done_event;
     std::ostringstream ss_m;
     ss_m << "Proto=nvlink,Path=" << (fused_ ? "fused" : (walk_ ? "walk" : "descriptors")) << ",OriginSbNum=" << origin_blocks_
-         << ",MergedSbNum=" << merged_blocks_ << ",BytesPerLayer=" << moved_bytes_per_layer_ << ",Tiles=" << plan_.total_tiles;
+         << ",MergedSbNum=" << merged_blocks_ << ",BytesPerLayer=" << moved_bytes_per_layer_ << ",Tiles=" << (walk_ ? walk_plan_.bulk_units + walk_plan_.simt_units : plan_.total_tiles);
     {
       std::lock_guard<std::mutex> g(slot_mu_);
       sl.metrics = ss_m.str();
@@ -714,6 +790,8 @@ class NvlinkChannel : public IChannel {
   DeviceAttnParams params_{};
   PackedPlan plan_;
   bool walk_{false};
+  WalkPlan walk_plan_;
+  DevArray<uint64_t> d_walk_src_, d_walk_dst_;   // [layer][tensor] base addresses
   std::vector<Slot> slots_;
   size_t plan_cap_{0}, slot_rr_{0};
   int batch_slot_{-1};
