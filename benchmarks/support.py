@@ -754,7 +754,7 @@ def hybrid_state_bandwidth(K, rank: int, world: int, dev, which: str = "gdn", to
         dist.all_gather_object(infos, winfo)
         if sender:
             winfo = infos[rank + n_pairs]
-    ms = 0.0
+    ms = ms_sync = 0.0
     moved = 0
     ok = True
     if sender:
@@ -770,25 +770,31 @@ def hybrid_state_bandwidth(K, rank: int, world: int, dev, which: str = "gdn", to
         per_tensor = K.plan_ipc_blocks(pw, dw, shape, [("x", 0, tokens, True, sb, db)])[0]
         moved = sum(n for blocks in per_tensor for _, _, n in blocks) * n_layers
 
-        def step(i):
+        def step(i, ahead):
             stepid = 7000 + i
             cli.submit_req_send2(dst_inst, 0, f"h{i}", 0, tokens, True, sb, db, winfo, stepid=stepid)
             cli.start_send_step(stepid, 1)
             for layer in range(n_layers):
                 cli.record_event(layer, stream)
             cli.flush_send_step()
-            cli.drain()
+            assert cli.wait_inflight(ahead, 30.0)      # completion records read on the host
 
-        for i in range(warmup):
-            step(i)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for i in range(steps):
-            step(warmup + i)
-        e1.record(stream)
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1)
+        def timed(ahead, first):
+            for i in range(warmup):
+                step(first + i, ahead)
+            assert cli.wait_inflight(0, 30.0)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for i in range(steps):
+                step(first + warmup + i, ahead)
+            assert cli.wait_inflight(0, 30.0)
+            e1.record(stream)
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1)
+
+        ms_sync = timed(0, 0)                 # every step waits for its own completion before the next is submitted
+        ms = timed(1, 1000)                   # one step ahead of the transfers, as a serving engine runs
     # the decode side compares a sample of the planned byte ranges (the first and last 64 of every tensor,
     # first and last layer) with the prefill side's bytes, regenerated from the same seeds on another GPU
     sample = None
@@ -813,16 +819,18 @@ def hybrid_state_bandwidth(K, rank: int, world: int, dev, which: str = "gdn", to
     if world > 1:
         import torch.distributed as dist
 
-        t = torch.tensor([ms, float(moved), 0.0 if ok else 1.0], dtype=torch.float64, device=dev)
+        t = torch.tensor([ms, float(moved), 0.0 if ok else 1.0, ms_sync], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, moved, ok = float(t[0]), int(t[1]), float(t[2]) == 0.0
+        ms, moved, ok, ms_sync = float(t[0]), int(t[1]), float(t[2]) == 0.0, float(t[3])
         dist.barrier()
     if srv is not None:
         srv.stop()
     gbps = n_pairs * moved * steps / (ms * 1e-3) / 1e9 if ms > 0 else 0.0
     return {"which": which, "tokens": tokens, "layers_or_tensors": n_layers * n_tensors_per_layer,
             "bytes_per_step_per_pair": moved, "ms_per_step": round(ms / max(steps, 1), 4), "GBps": round(gbps, 1),
-            "per_pair_GBps": round(gbps / n_pairs, 1), "verified": ok}
+            "per_pair_GBps": round(gbps / n_pairs, 1), "steps_in_flight": 2,
+            "one_step_at_a_time_GBps": round(n_pairs * moved * steps / (ms_sync * 1e-3) / 1e9, 1) if ms_sync > 0 else 0.0,
+            "verified": ok}
 
 
 def quant_reshard_nvlink(K, rank: int, world: int, dev, tokens: int = 8192, n_layers: int = 80, iters: int = 5,

@@ -543,8 +543,11 @@ void bind_engine(py::module_& m) {
   py::class_<WalkPlan>(m, "WalkPlan")
       .def_property_readonly("n_ops", [](const WalkPlan& w) { return w.ops.size(); })
       .def_readonly("n_bulk", &WalkPlan::n_bulk)
+      .def_readonly("n_simt", &WalkPlan::n_simt)
+      .def_readonly("n_zero", &WalkPlan::n_zero)
       .def_readonly("bulk_units", &WalkPlan::bulk_units)
       .def_readonly("simt_units", &WalkPlan::simt_units)
+      .def_readonly("zero_units", &WalkPlan::zero_units)
       .def_readonly("bytes", &WalkPlan::bytes)
       .def_property_readonly("pool_len", [](const WalkPlan& w) { return w.pool.size(); })
       .def_property_readonly("pool_offset", [](const WalkPlan& w) { return w.ops.size() * sizeof(KvtWalkOp); })

@@ -210,11 +210,18 @@ typedef struct KvtWalkOp {
   uint64_t first_unit;                   // exclusive prefix sum of unit counts within the op's class (bulk / simt)
 } KvtWalkOp;
 
-// Completes run / inner_total / segs / flags of every op, orders the array as [bulk ops][simt ops] and
-// fills first_unit.  Returns the number of bulk ops; *bulk_units and *simt_units receive the unit totals.
-// An op whose geometry is not usable (zero run, per_block not a multiple of per_kb, more than
+// Completes run / inner_total / segs / flags of every op, orders the array as [bulk ops][simt ops][zero ops]
+// and fills first_unit (counted within each of the three classes).  Returns the number of bulk ops; the
+// counts and unit totals of the classes come back through the pointers.  Zero fills form a class of their own
+// because they must land AFTER the copies: the reference pads a tail after it has copied the tokens, and in
+// some geometries the padded range covers bytes the copies wrote; launch them behind the copies, on the same
+// stream.  An op whose geometry is not usable (zero run, per_block not a multiple of per_kb, more than
 // KVT_WALK_MAX_INNER loops) makes it return -1.
-int kvt_walk_finalize(KvtWalkOp* ops, uint32_t n_ops, uint64_t* bulk_units, uint64_t* simt_units);
+typedef struct KvtWalkCounts {
+  uint32_t n_bulk, n_simt, n_zero, reserved;
+  uint64_t bulk_units, simt_units, zero_units;
+} KvtWalkCounts;
+int kvt_walk_finalize(KvtWalkOp* ops, uint32_t n_ops, KvtWalkCounts* counts);
 
 #define KVT_WALK_MAX_TENSORS 8
 typedef struct KvtWalkLaunch {

@@ -44,14 +44,16 @@ struct PlanEnv {
 struct WalkPlan {
   std::vector<KvtWalkOp> ops;
   std::vector<uint32_t> pool;          // block tables referenced by the ops
-  uint32_t n_bulk = 0;                 // after finalize(): ops[0, n_bulk) go through the TMA engine
-  uint64_t bulk_units = 0, simt_units = 0;
+  // after finalize(): ops = [n_bulk through the TMA engine][n_simt through the SIMT warps][n_zero zero fills, which
+  // a second launch writes after the copies]
+  uint32_t n_bulk = 0, n_simt = 0, n_zero = 0;
+  uint64_t bulk_units = 0, simt_units = 0, zero_units = 0;
   uint64_t bytes = 0;                  // payload bytes of one layer (all tensors)
   void clear() {
     ops.clear();
     pool.clear();
-    n_bulk = 0;
-    bulk_units = simt_units = bytes = 0;
+    n_bulk = n_simt = n_zero = 0;
+    bulk_units = simt_units = zero_units = bytes = 0;
   }
   // Orders the ops by class, fills their unit bookkeeping and checks every table entry against the block
   // counts of the two caches (std::out_of_range otherwise).

@@ -45,27 +45,28 @@ bool finalize_one(KvtWalkOp& op) {
 
 }  // namespace
 
-extern "C" int kvt_walk_finalize(KvtWalkOp* ops, uint32_t n_ops, uint64_t* bulk_units, uint64_t* simt_units) {
+extern "C" int kvt_walk_finalize(KvtWalkOp* ops, uint32_t n_ops, KvtWalkCounts* counts) {
   for (uint32_t i = 0; i < n_ops; ++i)
     if (!finalize_one(ops[i])) return -1;
-  KvtWalkOp* mid = std::stable_partition(ops, ops + n_ops, [](const KvtWalkOp& o) { return (o.flags & KVT_WALK_BULK) != 0; });
-  const uint32_t n_bulk = static_cast<uint32_t>(mid - ops);
-  uint64_t b = 0, s = 0;
+  auto cls = [](const KvtWalkOp& o) { return (o.flags & KVT_WALK_ZERO) ? 2 : ((o.flags & KVT_WALK_BULK) ? 0 : 1); };
+  std::stable_sort(ops, ops + n_ops, [&](const KvtWalkOp& a, const KvtWalkOp& b) { return cls(a) < cls(b); });
+  KvtWalkCounts c{};
   for (uint32_t i = 0; i < n_ops; ++i) {
-    uint64_t& acc = i < n_bulk ? b : s;
+    const int k = cls(ops[i]);
+    uint64_t& acc = k == 0 ? c.bulk_units : (k == 1 ? c.simt_units : c.zero_units);
+    (k == 0 ? c.n_bulk : (k == 1 ? c.n_simt : c.n_zero)) += 1;
     ops[i].first_unit = acc;
     acc += kvt_walk_units(ops[i]);
   }
-  *bulk_units = b;
-  *simt_units = s;
-  return static_cast<int>(n_bulk);
+  *counts = c;
+  return static_cast<int>(c.n_bulk);
 }
 
 namespace kvx {
 
 void WalkPlan::finalize(uint32_t src_num_blocks, uint32_t dst_num_blocks) {
-  n_bulk = 0;
-  bulk_units = simt_units = 0;
+  n_bulk = n_simt = n_zero = 0;
+  bulk_units = simt_units = zero_units = 0;
   if (ops.empty()) return;
   // every table entry an op can reach must name a block of its cache: the kernel then needs no per-piece check
   // of the block id, only of the index into the table
@@ -79,9 +80,15 @@ void WalkPlan::finalize(uint32_t src_num_blocks, uint32_t dst_num_blocks) {
     for (uint32_t i = 0; i < op.n_dst; ++i)
       if (pool[op.dst_tbl + i] >= dst_num_blocks) throw std::out_of_range("walk op: destination block id beyond the cache");
   }
-  const int nb = kvt_walk_finalize(ops.data(), static_cast<uint32_t>(ops.size()), &bulk_units, &simt_units);
-  if (nb < 0) throw std::invalid_argument("walk op with unusable geometry");
-  n_bulk = static_cast<uint32_t>(nb);
+  KvtWalkCounts c{};
+  if (kvt_walk_finalize(ops.data(), static_cast<uint32_t>(ops.size()), &c) < 0)
+    throw std::invalid_argument("walk op with unusable geometry");
+  n_bulk = c.n_bulk;
+  n_simt = c.n_simt;
+  n_zero = c.n_zero;
+  bulk_units = c.bulk_units;
+  simt_units = c.simt_units;
+  zero_units = c.zero_units;
 }
 
 std::vector<WalkPiece> expand_walk_plan(const WalkPlan& plan, const std::vector<uint64_t>& src_caps,

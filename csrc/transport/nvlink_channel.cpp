@@ -263,7 +263,7 @@ class NvlinkChannel : public IChannel {
     }
     a.ops = reinterpret_cast<const KvtWalkOp*>(cur().d_plan);
     a.n_bulk_ops = walk_plan_.n_bulk;
-    a.n_simt_ops = static_cast<uint32_t>(walk_plan_.ops.size()) - walk_plan_.n_bulk;
+    a.n_simt_ops = walk_plan_.n_simt;
     a.bulk_units = walk_plan_.bulk_units;
     a.simt_units = walk_plan_.simt_units;
     a.pool = reinterpret_cast<const uint32_t*>(cur().d_plan + walk_plan_.ops.size() * sizeof(KvtWalkOp));
@@ -271,7 +271,17 @@ class NvlinkChannel : public IChannel {
     a.status = cur().d_status;
     int grid = env_nvlink_ctas();
     if (grid <= 0) grid = std::max(1, static_cast<int>(4 * kvt_sm_count(ctx_->device_id()) * env_kernel_copy_sm_usage()));
-    cuda_check(kvt_launch_walk(&a, grid, st.stream()), "kvt_launch_walk");
+    if (a.n_bulk_ops + a.n_simt_ops != 0) cuda_check(kvt_launch_walk(&a, grid, st.stream()), "kvt_launch_walk");
+    if (walk_plan_.n_zero != 0) {
+      // tail padding lands after the copies (same stream): where both touch a byte, the zero wins, as it does
+      // when the byte ranges are applied in the planner's order
+      a.ops += walk_plan_.n_bulk + walk_plan_.n_simt;
+      a.n_bulk_ops = 0;
+      a.bulk_units = 0;
+      a.n_simt_ops = walk_plan_.n_zero;
+      a.simt_units = walk_plan_.zero_units;
+      cuda_check(kvt_launch_walk(&a, grid, st.stream()), "kvt_launch_walk(zero fill)");
+    }
   }
 
   void ensure_walk_arrays() {

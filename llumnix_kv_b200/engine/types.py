@@ -126,6 +126,24 @@ class Request:
         self.trace_wrapper = RequestTrace(trace_headers)
         self.block_hashes: list = []
 
+    def compute_block_hashes(self, block_size: int) -> list:
+        """Chained hashes of the prompt's full blocks (32 bytes each): hash_i covers every token up to the end
+        of block i, the property the engine's prefix cache and the store backends key on.  Cached per request."""
+        n = self.num_prompt_tokens // block_size
+        if len(self.block_hashes) < n or getattr(self, "_block_hash_size", block_size) != block_size:
+            import hashlib
+            import struct
+
+            self._block_hash_size = block_size
+            out, prev = [], b""
+            for i in range(n):
+                h = hashlib.sha256(prev)
+                h.update(struct.pack(f"<{block_size}q", *self.prompt_token_ids[i * block_size:(i + 1) * block_size]))
+                prev = h.digest()
+                out.append(prev)
+            self.block_hashes = out
+        return self.block_hashes
+
     @classmethod
     def from_engine_core_request(cls, r: EngineCoreRequest) -> "Request":
         params = None

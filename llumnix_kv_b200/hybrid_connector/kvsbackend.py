@@ -50,6 +50,7 @@ class KVSReqMeta:
     is_last_chunk: bool = False
     abort: bool = False        # save was aborted: drop what is not sealed
     trace: Optional[str] = None  # W3C traceparent of this I/O (child of the request's span), if the request carries one
+    block_hashes: list = dataclasses.field(default_factory=list)   # engine block hashes of those blocks (hash-keyed flavours)
 
 
 @dataclasses.dataclass
@@ -72,7 +73,15 @@ def should_use(req: Request) -> bool:
 
 
 class KVSBackend(HybridBackend):
+    """The store backend, and its Vineyard flavour: keys made from the token ids (or, with
+    VLLM_KVS_USE_REQUEST_HASH, from xxh64 of the engine's block hashes, as kvsbackend.py:381-399 of the
+    reference maps them), every layer saved right after it ran with one CUDA event per layer
+    (kvsbackend.py:111-514).  The flavours in kvs_flavours.py change the keys, when a step's pages leave,
+    and who seals them."""
+
     SOURCE_LABEL = "kvs"
+    FLAVOUR = "vineyard"
+    NEEDS_BLOCK_HASHES = False     # the scheduler half ships the engine's block hashes with every request
 
     def __init__(self, vllm_config: VllmConfig, role: KVConnectorRole, kv_cache_config=None, **kw):
         super().__init__(vllm_config, role, kv_cache_config, **kw)
@@ -155,12 +164,40 @@ class KVSBackend(HybridBackend):
         if not self._open_index():
             return max_blocks
         n = max_blocks
-        for salt in self._salts:
-            keys = block_keys(req.prompt_token_ids, self._bs, n, salt)
+        hashes = self._hashes_of(req, n)
+        for rank in range(self._tp):
+            keys = self.store_keys(req.prompt_token_ids, hashes, n, rank)
             n = min(n, self._index.lookup_prefix(b"".join(keys)))
             if n == 0:
                 break
         return n
+
+    # ---- naming of blocks at rest (flavours override) -------------------------------------------------
+    def _hashes_of(self, req: Request, n_blocks: int) -> list:
+        if not (self.NEEDS_BLOCK_HASHES or envs.VLLM_KVS_USE_REQUEST_HASH):
+            return []
+        return list(req.compute_block_hashes(self._bs)[:n_blocks])
+
+    def block_names(self, token_ids: list, block_hashes: list, n_blocks: int, tp_rank: int) -> list:
+        """The flavour's own name of each of the first ``n_blocks`` blocks on ``tp_rank`` (what an external
+        store of that kind would be asked for); None for the token-keyed default, which has no name but the key."""
+        if envs.VLLM_KVS_USE_REQUEST_HASH and block_hashes:
+            import xxhash
+
+            return [xxhash.xxh64(h).intdigest() for h in block_hashes[:n_blocks]]
+        return [None] * n_blocks
+
+    def store_keys(self, token_ids: list, block_hashes: list, n_blocks: int, tp_rank: int) -> list:
+        """16-byte keys of those blocks in the shared store."""
+        import struct
+
+        from llumnix_kv_b200.kvstore import block_keys, store_salt
+
+        names = self.block_names(token_ids, block_hashes, n_blocks, tp_rank)
+        if names and names[0] is not None:
+            return [struct.pack("<QII", int(x) & 0xFFFFFFFFFFFFFFFF, tp_rank, self._tp) for x in names]
+        _, _, tag, _ = self._geometry()
+        return block_keys(token_ids, self._bs, n_blocks, store_salt(self._model_tag, tp_rank, self._tp, tag))
 
     async def async_get_num_new_matched_tokens(self, req: Request, num_computed_tokens: int) -> int:
         assert num_computed_tokens % self._bs == 0
@@ -181,7 +218,8 @@ class KVSBackend(HybridBackend):
         self._engine.sched_discard_zero_block_ids(block_ids)
         self._loads.append(KVSReqMeta(request.request_id, False, list(request.prompt_token_ids[:upto]), list(block_ids),
                                       skip_blocks=request.num_computed_tokens // self._bs,
-                                      trace=request.trace_wrapper.traceparent("kv_load")))
+                                      trace=request.trace_wrapper.traceparent("kv_load"),
+                                      block_hashes=self._hashes_of(request, nblk)))
         return None   # the workers report LOAD_DONE with what they really loaded
 
     def _save_meta(self, reqid: str, scheduled: int) -> Optional[KVSReqMeta]:
@@ -202,7 +240,8 @@ class KVSBackend(HybridBackend):
             return None
         block_ids = self._engine.sched_get_kvblk_ids(reqid)[0][:done_blocks]
         return KVSReqMeta(reqid, True, list(req.prompt_token_ids[:done_blocks * self._bs]), list(block_ids),
-                          skip_blocks=prev, is_last_chunk=last, trace=req.trace_wrapper.traceparent("kv_save"))
+                          skip_blocks=prev, is_last_chunk=last, trace=req.trace_wrapper.traceparent("kv_save"),
+                          block_hashes=self._hashes_of(req, done_blocks))
 
     def build_backend_meta(self, sout: SchedulerOutput) -> BackendMeta:
         assert isinstance(sout, HCSchedOutput)
@@ -245,7 +284,7 @@ class KVSBackend(HybridBackend):
         layers = [t[0] for t in flatten_cache(kv_caches)]
         layout, _, _, n_slots = self._geometry()
         assert layers[0].nbytes == layout.layer_bytes, "cache tensor does not match the configured cache shape"
-        rank = self._worker.get_tensor_model_parallel_rank()
+        rank = self._rank = self._worker.get_tensor_model_parallel_rank()
         self._store = PinnedKVStore(self._name, layout, layers, rank, self._tp, n_slots, create="auto",
                                     ttl_ms=self._ttl_ms, fp8=self._fp8, model_tag=self._model_tag)
         self._layer_index = {name: i for i, name in enumerate(sorted(kv_caches, key=_layer_key))}
@@ -280,6 +319,8 @@ class KVSBackend(HybridBackend):
     def _keys_for(self, m: KVSReqMeta) -> list:
         """Chained keys of the request's blocks, extended from what earlier steps computed."""
         n = len(m.block_ids)
+        if m.block_hashes:       # hash-keyed flavours: nothing to chain, the engine's hashes already are
+            return self.store_keys(m.token_ids, m.block_hashes, n, self._rank)
         have = self._wkeys.get(m.reqid, [])
         if len(have) < n:
             from llumnix_kv_b200.kvstore.store import block_keys
@@ -296,7 +337,8 @@ class KVSBackend(HybridBackend):
                 continue
             st = self._store
             self._note_context(r, None)
-            keys = st.keys(r.token_ids, len(r.block_ids))
+            keys = self._keys_for(r)
+            self._wkeys.pop(r.reqid, None)
             slots = st.pin(keys)
             n = len(slots)
             loaded = max(0, n - r.skip_blocks) * self._bs

@@ -26,6 +26,19 @@ def K(ops):
     return ops
 
 
+def launch_plan(K, plan, blob, sp, dp, nt, src_caps, dst_caps, status, grid=0, layers=(0, N_LAYERS)):
+    """The copies, then (same stream) the zero fills: the order the NVLINK channel launches them in."""
+    stream = torch.cuda.current_stream().cuda_stream
+    pool = blob.data_ptr() + plan.pool_offset
+    if plan.n_bulk + plan.n_simt:
+        K.kvt_launch_walk(sp.data_ptr(), dp.data_ptr(), nt, layers[0], layers[1], src_caps, dst_caps, blob.data_ptr(), plan.n_bulk,
+                          plan.n_simt, plan.bulk_units, plan.simt_units, pool, plan.pool_len, status.data_ptr(), grid, stream)
+    if plan.n_zero:
+        zero_ops = blob.data_ptr() + (plan.n_bulk + plan.n_simt) * K.KVT_WALK_OP_BYTES
+        K.kvt_launch_walk(sp.data_ptr(), dp.data_ptr(), nt, layers[0], layers[1], src_caps, dst_caps, zero_ops, 0, plan.n_zero, 0,
+                          plan.zero_units, pool, plan.pool_len, status.data_ptr(), grid, stream)
+
+
 def run_walk(K, shape, src, dst, tasks, pad=True, grid=0):
     src_caps = [bs * src.layer_num_blocks for bs in src.block_sizes]
     dst_caps = [bs * dst.layer_num_blocks for bs in dst.block_sizes]
@@ -53,9 +66,7 @@ def run_walk(K, shape, src, dst, tasks, pad=True, grid=0):
             sp = torch.tensor([t.data_ptr() for layer in s_dev for t in layer], dtype=torch.int64, device=DEV)
             dp = torch.tensor([t.data_ptr() for layer in d_dev for t in layer], dtype=torch.int64, device=DEV)
             status = torch.zeros(4, dtype=torch.int32, device=DEV)
-            K.kvt_launch_walk(sp.data_ptr(), dp.data_ptr(), nt, 0, N_LAYERS, src_caps, dst_caps, blob.data_ptr(), plan.n_bulk,
-                              plan.n_ops - plan.n_bulk, plan.bulk_units, plan.simt_units, blob.data_ptr() + plan.pool_offset,
-                              plan.pool_len, status.data_ptr(), grid, torch.cuda.current_stream().cuda_stream)
+            launch_plan(K, plan, blob, sp, dp, nt, src_caps, dst_caps, status, grid)
             torch.cuda.synchronize()
             assert status[:2].tolist() == [0, 0]
         for layer in range(N_LAYERS):
@@ -123,8 +134,6 @@ def test_walk_reports_a_table_that_is_too_short(K):
     sp = torch.tensor([s.data_ptr()], dtype=torch.int64, device=DEV)
     dp = torch.tensor([d.data_ptr()], dtype=torch.int64, device=DEV)
     status = torch.zeros(4, dtype=torch.int32, device=DEV)
-    K.kvt_launch_walk(sp.data_ptr(), dp.data_ptr(), 1, 0, 1, [s.numel()], [d.numel()], blob.data_ptr(), plan.n_bulk,
-                      plan.n_ops - plan.n_bulk, plan.bulk_units, plan.simt_units, blob.data_ptr() + plan.pool_offset,
-                      plan.pool_len, status.data_ptr(), 0, torch.cuda.current_stream().cuda_stream)
+    launch_plan(K, plan, blob, sp, dp, 1, [s.numel()], [d.numel()], status, layers=(0, 1))
     torch.cuda.synchronize()
     assert int(status[0]) == 1      # KVT_ERR_BLOCK_RANGE
