@@ -56,6 +56,9 @@ def parse_args():
                          "migration: decode->decode latency against the number of blocks; fanout (4 or 8 GPUs): replicated "
                          "MLA pages to a decode TP group, unicast against the NVLS relay; linkprobe: the transfer "
                          "kernel's GB/s for every store form, pipeline depth and grid, next to the copy engine's")
+    ap.add_argument("--kernels-on", default="decode", choices=["decode", "prefill"],
+                    help="kernel-only number between two GPUs: the decode GPU loads over NVLink (pull, what the transport "
+                         "does) or the prefill GPU stores (push)")
     ap.add_argument("--ahead", type=int, default=1,
                     help="end-to-end number: steps the engine thread may run ahead of the transfers (0: wait for every "
                          "step's completion record before submitting the next)")
@@ -290,6 +293,8 @@ def main():
     pair.layers_per_launch = args.layers_per_launch
     sampler = lambda: ClockSampler(local_rank)
     ceilings = BL.measure_ceilings(pair)
+    if args.kernels_on == "decode" and world > 1 and not baseline_arm and args.mode == "p2d":
+        pair.use_pull_kernels()
 
     def roofline(per_pair: float) -> dict:
         peaks = {}
@@ -356,7 +361,7 @@ def main():
         dev_regions, clocks = [], {}
     else:
         dev_regions, clocks = BL.timed_reps(pair.step_device, args.steps, args.warmup, pair.stream, world, dev,
-                                            pair.is_sender, args.min_seconds, sampler_factory=sampler)
+                                            pair.kernel_measures, args.min_seconds, sampler_factory=sampler)
     # ---- end to end through the public API: pinned block tables -> H2D, 32 per-layer
     #      launches, completion word + status read back on the host every step ------------
     sync_stat = None

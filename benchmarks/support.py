@@ -99,7 +99,8 @@ class PDBenchPair:
                 dst_ptrs = [self.peer_base + off + i * self.dst_l.layer_bytes for i in range(n_layers)]
             self.transport_name = "NVLink P2P stores into CUDA-IPC mapped peer cache"
         self.dst_layer_ptrs = dst_ptrs
-        self.want_pull = False      # set before map_src_on_receiver() by the store-form probe
+        self.pull = False
+        self.kernel_measures = self.is_sender     # the rank that launches (and times) the kernel-only steps
 
         self.xfer = None
         self.h2d_bytes_per_step = 0
@@ -138,6 +139,22 @@ class PDBenchPair:
             base = self.K.kvt_ipc_open_handle(h)
             self.src_peer_ptrs = [base + off + i * self.src_l.layer_bytes for i in range(self.n_layers)]
 
+    def use_pull_kernels(self) -> None:
+        """Kernel-only number with the kernels on the DECODE GPU (what the NVLINK transport does between two
+        GPUs): the decode rank maps the prefill cache, builds the plans and launches; it is the rank that times."""
+        if self.loopback:
+            return
+        self.map_src_on_receiver()
+        self.pull = True
+        self.kernel_measures = self.is_receiver
+        if self.is_receiver:
+            dst_ptrs = [self.dst.data_ptr() + i * self.dst_l.layer_bytes for i in range(self.n_layers)]
+            self.xfer = AttnTransfer(self.src_l, self.dst_l, self.src_peer_ptrs, dst_ptrs, self.dev, use_tma=True)
+            with torch.cuda.stream(self.stream):
+                self.plans = [self.xfer.plan(cs, stream=self.stream) for cs in self.slot_chunks]
+            torch.cuda.synchronize()
+            self.transport_name = "NVLink: TMA loads by the decode GPU from the CUDA-IPC mapped prefill cache (pull)"
+
     def _pair_id(self) -> int:
         return self.rank % self.n_pairs if not self.loopback else 0
 
@@ -153,7 +170,7 @@ class PDBenchPair:
 
     # ---- steps ------------------------------------------------------------------------
     def step_device(self, i: int) -> None:
-        if not self.is_sender:
+        if not self.kernel_measures:
             return
         plan = self.plans[i % self.slots]
         self.touched.add(i % self.slots)
@@ -169,7 +186,7 @@ class PDBenchPair:
         a CUDA graph; ``step_device`` then replays it, which takes the host's launch rate out of the
         kernel-only number."""
         self.graphs = []
-        if not self.is_sender:
+        if not self.kernel_measures:
             return
         for i in range(self.slots):
             self.step_device(i)                 # warm-up outside capture

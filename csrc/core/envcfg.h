@@ -63,6 +63,9 @@ int env_use_tma();
 // destination's own order) and how they leave (0 tensor store, 1 one linear bulk store, -1 = linear when legal).
 // 0: the NVLink channel plans hybrid / MLA / KDA shapes on the CPU and uploads byte ranges instead of walk ops.
 int env_nvlink_walk();
+// 0: the NVLink channel always pushes (kernels on the prefill GPU); default: it asks the destination for a pull session
+// (kernels on the decode GPU, loads over NVLink) when the destination is another GPU and takes the bytes unconverted.
+int env_nvlink_pull();
 int env_tile_order();
 int env_store_form();
 // Host-staged copies (TCP / SHM transports): start-up measurement of copy kernel against copy

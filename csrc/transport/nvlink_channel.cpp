@@ -1,25 +1,32 @@
-// NVLink transport: kernels on the prefill GPU store straight into the decode GPU's paged
-// cache through peer-mapped memory (NVLink 5 / NVSwitch).  No staging buffer, no library copy.
+// NVLink transport: the KV of a prefill GPU reaches the decode GPU's paged cache through peer-mapped
+// memory (NVLink 5 / NVSwitch).  No staging buffer, no library copy.
 //
 // connect() asks the destination's server for the CUDA IPC handles of its layer tensors
 // (MEM_HANDLES_REQ) and maps them; a destination in the same process is used by pointer after
-// enabling peer access.  Two data paths share the channel:
-//   * fused:   register_tasks() packs the requests' block tables; send_data(layer) launches
-//              kvt_p2d_attn, which walks the tables, converts the layout (NHD<->HND), re-shards
-//              heads for TP-mismatched pairs, optionally quantises to block-scaled e4m3 and
-//              stores into the peer cache.  Serves cache shapes 1, 2 and 5 on either side.
-//   * generic: register_data() takes the planner's IpcBlocks (any cache shape, including hybrid
-//              GDN / MLA / KDA pages) and send_data(layer) runs the descriptor-driven copy
-//              kernel from the local tensor into the peer tensor.
-// The channel is device ordered: send_data(layer) makes its stream wait for the layer's CUDA
-// event and returns; nothing on the host waits for the forward pass.  Nothing on the host waits for
-// the transfer either: flush_async() enqueues a completion record (sequence number, kernel status
-// words, GPU timer stamps, written into mapped host memory by a one-thread kernel) behind the batch
-// and returns; the completion poller reads the record and finishes the batch.  Every batch runs in
-// one of a few plan slots (device + pinned plan buffer, status block, record, a small stream), sized
-// once at connect from the caches' block counts, so the step path neither allocates nor frees.
-// Only plain peer stores are used here; loads with cluster multicast are never issued.
+// enabling peer access.  Then one of two modes serves the channel:
+//
+//   push   the transfer kernels run on the prefill GPU: local loads, stores into the peer cache.  Serves a
+//          destination on the same GPU, a block-scaled fp8 destination (the quantiser halves the bytes that
+//          cross the link) and a destination whose server offers no pull session.
+//   pull   the kernels run on the DECODE GPU: a session on the destination's server maps this worker's cache
+//          and layer events, and executes the plans this channel sends (transport/pull_session.h).  TMA loads
+//          over NVLink run at the copy engine's rate (measured 772 against 705 GB/s for SM-issued stores of any
+//          form), and the prefill GPU spends no SM on the transfer.
+//
+// In both modes the kernels are the same two:
+//   * kvt_p2d_attn walks the requests' block tables, converts the layout (NHD<->HND), re-shards heads for
+//     TP-mismatched pairs and optionally quantises to block-scaled e4m3: cache shapes 1, 2 and 5;
+//   * kvt_walk expands the planner's walk ops (hybrid GDN / MLA / KDA pages, any TP relation).
+// A third, push-only path takes the planner's IpcBlocks (BLLM_KVTRANS_NVLINK_WALK=0, or a layer of more
+// tensors than the walk kernel addresses) and runs the descriptor copy kernel over them.
+//
+// The channel is device ordered: a layer's kernel is enqueued behind the layer's CUDA event, nothing on the
+// host waits for the forward pass.  Nothing on the host waits for the transfer either: flush_async()
+// enqueues a completion record behind the batch and returns; the completion poller reads it and finishes
+// the batch.  Only plain peer loads and stores are used; loads with cluster multicast are never issued.
 #include <cuda_runtime.h>
+#include <poll.h>
+#include <sys/socket.h>
 #include <unistd.h>
 
 #include <map>
@@ -32,76 +39,16 @@
 #include "core/util.h"
 #include "kernels/kvt_kernels.h"
 #include "plan/device_plan.h"
+#include "transport/batch_engine.h"
 #include "transport/channel.h"
 #include "transport/device_stage.h"
+#include "transport/peer_memory.h"
+#include "transport/pull_session.h"
 #include "transport/wire.h"
 
 namespace kvx {
 
 namespace {
-
-// IPC mappings are per process: a handle is opened once and shared by every channel that maps the same
-// allocation, and closed when the last of them goes away.  The key is the handle itself, which names one
-// allocation of one process: a peer that restarted (even with a recycled pid and the same addresses) hands
-// out different handles, so nothing is ever written through a mapping of memory that no longer exists.
-struct IpcCache {
-  struct Mapping {
-    uint64_t local = 0;
-    uint32_t refs = 0;
-  };
-  std::mutex mu;
-  std::map<std::string, Mapping> mapped;   // 64 handle bytes -> local address
-  uint64_t acquire(const char* handle64) {
-    std::lock_guard<std::mutex> g(mu);
-    const std::string key(handle64, 64);
-    auto it = mapped.find(key);
-    if (it == mapped.end()) {
-      uint64_t local = 0;
-      cuda_check(kvt_ipc_open_handle(handle64, &local), "cudaIpcOpenMemHandle");
-      it = mapped.emplace(key, Mapping{local, 0}).first;
-    }
-    ++it->second.refs;
-    return it->second.local;
-  }
-  void release(const std::string& key) {
-    std::lock_guard<std::mutex> g(mu);
-    auto it = mapped.find(key);
-    if (it == mapped.end()) return;
-    if (--it->second.refs == 0) {
-      kvt_ipc_close(it->second.local);
-      mapped.erase(it);
-    }
-  }
-  size_t size() {
-    std::lock_guard<std::mutex> g(mu);
-    return mapped.size();
-  }
-};
-IpcCache& ipc_cache() {
-  static IpcCache& c = *new IpcCache;   // never destroyed: channels may close while the process exits
-  return c;
-}
-
-template <typename T>
-struct DevArray {
-  T* p{nullptr};
-  size_t n{0};
-  ~DevArray() {
-    if (p != nullptr) cudaFree(p);
-  }
-  void upload(const std::vector<T>& v) {
-    if (p != nullptr) cudaFree(p);
-    p = nullptr;
-    n = v.size();
-    if (n == 0) return;
-    cuda_check(cudaMalloc(reinterpret_cast<void**>(&p), n * sizeof(T)), "cudaMalloc");
-    cuda_check(cudaMemcpy(p, v.data(), n * sizeof(T), cudaMemcpyHostToDevice), "cudaMemcpy");
-  }
-};
-
-struct alignas(64) TensorMapBytes {
-  char b[128];
-};
 
 class NvlinkChannel : public IChannel {
  public:
@@ -136,48 +83,39 @@ class NvlinkChannel : public IChannel {
       throw KVTransferException(ErrorKind::TRANSPORT, "nvlink: destination is on another host");
     }
     RTASSERT(info.num_layers == ctx_->num_layers());
-    const bool same_process = info.pid == static_cast<int32_t>(getpid());
     dst_remote_ = info.device != ctx_->device_id();
-    if (info.device != ctx_->device_id() && same_process) {
-      if (!kvt_can_access_peer(ctx_->device_id(), info.device))
-        throw KVTransferException(ErrorKind::TRANSPORT, "nvlink: no peer access to the destination GPU");
-      cuda_check(kvt_enable_peer_access(ctx_->device_id(), info.device), "cudaDeviceEnablePeerAccess");
-    }
-    dst_ptrs_.assign(info.num_layers, std::vector<uint64_t>(info.num_tensors, 0));
-    for (uint32_t l = 0; l < info.num_layers; ++l) {
-      for (uint32_t t = 0; t < info.num_tensors; ++t) {
-        const PeerTensor& pt = info.tensors[static_cast<size_t>(l) * info.num_tensors + t];
-        if (same_process) {
-          dst_ptrs_[l][t] = pt.ptr;
-          continue;
-        }
-        if (!pt.has_handle) throw KVTransferException(ErrorKind::TRANSPORT, "nvlink: destination tensor has no IPC handle");
-        const std::string key(pt.ipc_handle, 64);
-        uint64_t local = 0;
-        for (size_t k = 0; k < ipc_keys_.size() && local == 0; ++k)
-          if (ipc_keys_[k] == key) local = ipc_locals_[k];
-        if (local == 0) {      // one reference per allocation and channel
-          local = ipc_cache().acquire(pt.ipc_handle);
-          ipc_keys_.push_back(key);
-          ipc_locals_.push_back(local);
-        }
-        dst_ptrs_[l][t] = local + (pt.ptr - pt.alloc_base);
-      }
-    }
-    // ---- streams and plan slots -------------------------------------------------------------
-    const int n_streams = std::max(1, env_nvlink_streams());
-    for (int i = 0; i < n_streams; ++i) stages_.emplace_back(std::make_unique<DeviceStage>(ctx_->device_id()));
-    // A plan holds one descriptor per request and the block tables of both sides.  Sized for every block of
-    // both caches in every block group, plus room for a few thousand request descriptors.
-    const size_t groups = std::max<size_t>(1, ctx_->worker_info().num_gdn_layers + ctx_->worker_info().num_ple_layers + 2);
-    const size_t table = (static_cast<size_t>(ctx_->layer_num_blocks()) + dst.layer_num_blocks) * sizeof(uint32_t);
-    alloc_slots(std::max<size_t>(table * std::min<size_t>(groups, 8) + (1u << 20), 2u << 20));
+    dst_map_.map(info, ctx_->device_id());
+    n_tensors_ = info.num_tensors;
     src_shape_ = ctx_->worker_info().cache_shape_or(env_cache_shape());
     dst_shape_ = dst.cache_shape_or(src_shape_);
     dst_mx_ = dst.ext_int("mx", env_dst_mxfp8()) != 0;
+    for (size_t t = 0; t < ctx_->block_sizes().size(); ++t) src_caps_.push_back(ctx_->tensor_capacity(t));
+    for (size_t t = 0; t < dst.block_sizes.size(); ++t)
+      dst_caps_.push_back(dst.block_sizes[t] * static_cast<uint64_t>(dst.layer_num_blocks));
+    // ---- pull session on the destination, where that is the faster way ----------------------------
+    pull_ = false;
+    if (dst_remote_ && !dst_mx_ && env_nvlink_pull() != 0) pull_ = open_pull(sock);
+    if (pull_) {
+      pull_sock_ = std::move(sock);
+    } else {
+      // ---- push: streams and plan slots on this GPU ----------------------------------------------
+      BatchEngineConfig cfg;
+      cfg.device = ctx_->device_id();
+      cfg.n_streams = std::max(1, env_nvlink_streams());
+      // A plan holds one descriptor per request and the block tables of both sides.  Sized for every block of
+      // both caches in every block group, plus room for a few thousand request descriptors / walk ops.
+      const size_t groups = std::max<size_t>(1, ctx_->worker_info().num_gdn_layers + ctx_->worker_info().num_ple_layers + 2);
+      const size_t table = (static_cast<size_t>(ctx_->layer_num_blocks()) + dst.layer_num_blocks) * sizeof(uint32_t);
+      cfg.plan_capacity = std::max<size_t>(table * std::min<size_t>(groups, 8) + (1u << 20), 2u << 20);
+      cfg.stamps = env_device_timestamps();
+      cfg.dst_remote = dst_remote_;
+      cfg.grid_ctas = env_nvlink_ctas();
+      eng_ = std::make_unique<BatchEngine>(cfg, ctx_->layer_data_address(), dst_map_.ptrs(), src_caps_, dst_caps_);
+    }
     active_ = true;
-    LOG(INFO) << "nvlink channel connected. dst=" << dst.to_string() << " same_process=" << same_process
-              << " src_shape=" << src_shape_ << " dst_shape=" << dst_shape_ << " dst_mx=" << dst_mx_;
+    LOG(INFO) << "nvlink channel connected. dst=" << dst.to_string() << " same_process=" << dst_map_.same_process()
+              << " src_shape=" << src_shape_ << " dst_shape=" << dst_shape_ << " dst_mx=" << dst_mx_
+              << " mode=" << (pull_ ? "pull" : "push");
   }
 
   bool register_tasks(const PlanEnv& env, const std::vector<const ReqSendTask*>& tasks) override {
@@ -185,7 +123,7 @@ class NvlinkChannel : public IChannel {
     walk_ = false;
     generic_.clear();
     origin_blocks_ = merged_blocks_ = 0;
-    if (dst_ptrs_.empty()) return false;
+    if (n_tensors_ == 0) return false;
     PlanEnv e = env;
     e.cache_shape = src_shape_;
     PlannerChoice choice;
@@ -196,7 +134,7 @@ class NvlinkChannel : public IChannel {
     }
     DeviceAttnParams p;
     std::string why = "the layer has several cache tensors";
-    if (dst_ptrs_[0].size() != 1 || !device_attn_params(e, choice.kind, src_shape_, dst_shape_, dst_mx_, &p, &why)) {
+    if (n_tensors_ != 1 || !device_attn_params(e, choice.kind, src_shape_, dst_shape_, dst_mx_, &p, &why)) {
       if (src_shape_ != dst_shape_ || dst_mx_) {
         throw KVTransferException(ErrorKind::INVALID_OPERATION,
                                   "nvlink: cross-layout / fp8 transfer needs the fused kernel but " + why);
@@ -206,92 +144,59 @@ class NvlinkChannel : public IChannel {
       return register_walk(e, choice, tasks);
     }
     params_ = p;
-    if (p.skip) {
-      plan_ = PackedPlan{};
-      fused_ = true;
-      return true;
-    }
-    plan_ = pack_device_plan(tasks, 0, p.tile_tokens, p.dst.ntpb, false);
-    if (plan_.n_reqs == 0) {
-      fused_ = true;
-      return true;
-    }
-    cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
-    ensure_layer_arrays();
-    // upload the plan on the slot's stream; the transfer streams wait for it when the batch first uses them
-    Slot& sl = begin_slot(plan_.blob.size());
-    memcpy(sl.h_plan, plan_.blob.data(), plan_.blob.size());
-    upload_slot(sl, plan_.blob.size());
     fused_ = true;
+    plan_ = p.skip ? PackedPlan{} : pack_device_plan(tasks, 0, p.tile_tokens, p.dst.ntpb, false);
+    if (plan_.n_reqs == 0) return true;     // this rank holds only replicas, or nothing is due
     moved_bytes_per_layer_ = 0;
     for (const ReqSendTask* t : tasks)
       moved_bytes_per_layer_ += static_cast<size_t>(t->new_tokens) * 2 * p.n_heads * p.src.head_bytes;
+    if (pull_) {
+      PullPlanHead h{};
+      h.kind = PULL_KIND_ATTN;
+      h.n_reqs = plan_.n_reqs;
+      h.total_tiles = plan_.total_tiles;
+      h.pool_offset = plan_.pool_offset;
+      h.attn = p;
+      send_plan(h, plan_.blob.data(), plan_.blob.size(), nullptr, 0);
+      return true;
+    }
+    BatchEngine::SlotView sl = eng_->begin(plan_.blob.size());
+    memcpy(sl.h_plan, plan_.blob.data(), plan_.blob.size());
+    eng_->upload(plan_.blob.size());
     return true;
   }
 
   bool register_walk(const PlanEnv& e, const PlannerChoice& choice, const std::vector<const ReqSendTask*>& tasks) {
-    if (env_nvlink_walk() == 0 || e.cast_bf16_to_fp8 || dst_ptrs_[0].size() > KVT_WALK_MAX_TENSORS) return false;
+    if (env_nvlink_walk() == 0 || e.cast_bf16_to_fp8 || n_tensors_ > KVT_WALK_MAX_TENSORS) {
+      if (pull_) throw KVTransferException(ErrorKind::INVALID_OPERATION, "nvlink: the pull mode needs the walk kernel for this shape");
+      return false;
+    }
     walk_plan_.clear();
     for (const ReqSendTask* t : tasks) plan_request_ops(choice, e, *t, walk_plan_);
     walk_plan_.finalize(ctx_->layer_num_blocks(), dst_.layer_num_blocks);
     plan_ = PackedPlan{};
     moved_bytes_per_layer_ = walk_plan_.bytes;
-    walk_ = true;
-    if (walk_plan_.empty()) return true;       // this rank has nothing to send (not a representative rank)
-    cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
-    ensure_walk_arrays();
-    const size_t ops_bytes = walk_plan_.ops.size() * sizeof(KvtWalkOp);
-    const size_t bytes = ops_bytes + walk_plan_.pool.size() * sizeof(uint32_t);
-    Slot& sl = begin_slot(bytes);
-    memcpy(sl.h_plan, walk_plan_.ops.data(), ops_bytes);
-    memcpy(sl.h_plan + ops_bytes, walk_plan_.pool.data(), walk_plan_.pool.size() * sizeof(uint32_t));
-    upload_slot(sl, bytes);
     origin_blocks_ = walk_plan_.ops.size();
+    walk_ = true;
+    walk_counts_ = KvtWalkCounts{walk_plan_.n_bulk, walk_plan_.n_simt, walk_plan_.n_zero, 0, walk_plan_.bulk_units,
+                                 walk_plan_.simt_units, walk_plan_.zero_units};
+    if (walk_plan_.empty()) return true;       // this rank has nothing to send (not a representative rank)
+    const size_t ops_bytes = walk_plan_.ops.size() * sizeof(KvtWalkOp);
+    const size_t pool_bytes = walk_plan_.pool.size() * sizeof(uint32_t);
+    if (pull_) {
+      PullPlanHead h{};
+      h.kind = PULL_KIND_WALK;
+      h.n_ops = static_cast<uint32_t>(walk_plan_.ops.size());
+      h.pool_len = static_cast<uint32_t>(walk_plan_.pool.size());
+      h.walk = walk_counts_;
+      send_plan(h, walk_plan_.ops.data(), ops_bytes, walk_plan_.pool.data(), pool_bytes);
+      return true;
+    }
+    BatchEngine::SlotView sl = eng_->begin(ops_bytes + pool_bytes);
+    memcpy(sl.h_plan, walk_plan_.ops.data(), ops_bytes);
+    memcpy(sl.h_plan + ops_bytes, walk_plan_.pool.data(), pool_bytes);
+    eng_->upload(ops_bytes + pool_bytes);
     return true;
-  }
-
-  void launch_walk(size_t layer_begin, size_t layer_end, DeviceStage& st) {
-    KvtWalkLaunch a{};
-    a.src_ptrs = d_walk_src_.p;
-    a.dst_ptrs = d_walk_dst_.p;
-    a.n_tensors = static_cast<uint32_t>(dst_ptrs_[0].size());
-    a.layer_begin = static_cast<uint32_t>(layer_begin);
-    a.layer_end = static_cast<uint32_t>(layer_end);
-    for (uint32_t t = 0; t < a.n_tensors; ++t) {
-      a.src_cap[t] = ctx_->tensor_capacity(t);
-      a.dst_cap[t] = dst_.block_sizes.at(t) * static_cast<uint64_t>(dst_.layer_num_blocks);
-    }
-    a.ops = reinterpret_cast<const KvtWalkOp*>(cur().d_plan);
-    a.n_bulk_ops = walk_plan_.n_bulk;
-    a.n_simt_ops = walk_plan_.n_simt;
-    a.bulk_units = walk_plan_.bulk_units;
-    a.simt_units = walk_plan_.simt_units;
-    a.pool = reinterpret_cast<const uint32_t*>(cur().d_plan + walk_plan_.ops.size() * sizeof(KvtWalkOp));
-    a.pool_len = static_cast<uint32_t>(walk_plan_.pool.size());
-    a.status = cur().d_status;
-    int grid = env_nvlink_ctas();
-    if (grid <= 0) grid = std::max(1, static_cast<int>(4 * kvt_sm_count(ctx_->device_id()) * env_kernel_copy_sm_usage()));
-    if (a.n_bulk_ops + a.n_simt_ops != 0) cuda_check(kvt_launch_walk(&a, grid, st.stream()), "kvt_launch_walk");
-    if (walk_plan_.n_zero != 0) {
-      // tail padding lands after the copies (same stream): where both touch a byte, the zero wins, as it does
-      // when the byte ranges are applied in the planner's order
-      a.ops += walk_plan_.n_bulk + walk_plan_.n_simt;
-      a.n_bulk_ops = 0;
-      a.bulk_units = 0;
-      a.n_simt_ops = walk_plan_.n_zero;
-      a.simt_units = walk_plan_.zero_units;
-      cuda_check(kvt_launch_walk(&a, grid, st.stream()), "kvt_launch_walk(zero fill)");
-    }
-  }
-
-  void ensure_walk_arrays() {
-    if (d_walk_src_.p != nullptr) return;
-    std::vector<uint64_t> src, dst;
-    for (const auto& l : ctx_->layer_data_address()) src.insert(src.end(), l.begin(), l.end());
-    for (const auto& l : dst_ptrs_) dst.insert(dst.end(), l.begin(), l.end());
-    RTASSERT(src.size() == dst.size());
-    d_walk_src_.upload(src);
-    d_walk_dst_.upload(dst);
   }
 
   void register_data(std::vector<std::vector<IpcBlock>>& data, TPKind kind) override {
@@ -300,6 +205,7 @@ class NvlinkChannel : public IChannel {
                                 "nvlink: the unscaled bf16->fp8 cast belongs to the host-staged transports; over NVLink an "
                                 "fp8 decode cache is filled by the block-scaled quantiser (BLLM_KVTRANS_DST_MXFP8)");
     }
+    if (pull_) throw KVTransferException(ErrorKind::INVALID_OPERATION, "nvlink: byte-range descriptors are a push-mode path");
     fused_ = false;
     walk_ = false;
     generic_.assign(data.size(), {});
@@ -318,8 +224,7 @@ class NvlinkChannel : public IChannel {
     upload_generic();
   }
 
-  // The descriptor lists are the same for every layer of the batch: upload them once (on stream 0,
-  // the other streams wait for the upload) instead of once per layer.
+  // The descriptor lists are the same for every layer of the batch: upload them once instead of once per layer.
   void upload_generic() {
     size_t total = 0;
     generic_off_.assign(generic_.size(), 0);
@@ -333,86 +238,62 @@ class NvlinkChannel : public IChannel {
       generic_rounds_ = std::max(generic_rounds_, kvt_bulk_rounds(generic_[t][0].len, longest));
     }
     if (total == 0) return;
-    cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
     const size_t bytes = total * sizeof(Triple);
-    Slot& sl = begin_slot(bytes);
+    BatchEngine::SlotView sl = eng_->begin(bytes);
     for (size_t t = 0; t < generic_.size(); ++t)
       if (!generic_[t].empty())
         memcpy(sl.h_plan + generic_off_[t] * sizeof(Triple), generic_[t].data(), generic_[t].size() * sizeof(Triple));
-    upload_slot(sl, bytes);
+    eng_->upload(bytes);
   }
+
+  bool nothing_to_send() const { return (fused_ && plan_.n_reqs == 0) || (walk_ && walk_plan_.empty()); }
 
   bool send_layers(size_t layer_begin, size_t layer_end, Step* step) override {
     (void)step;
     if ((!fused_ && !walk_) || layer_end <= layer_begin) return false;
-    if (walk_ ? walk_plan_.empty() : plan_.n_reqs == 0) return true;
+    if (nothing_to_send()) return true;
     // One launch saves ~100 us of launch and event overhead, which is what matters for a small
     // migration; a large one is faster layer by layer over several streams (measured crossover
     // around half a GiB).
     if (moved_bytes_per_layer_ * (layer_end - layer_begin) > (512ull << 20)) return false;
-    cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
-    // one launch over the layer range on the stream that carried the plan; layer events are
-    // recorded in order on one stream, so the last one implies the others
-    DeviceStage& st = use_stage(0);
-    st.wait_event(ctx_->cuda_barrier()->event(static_cast<uint32_t>(layer_end - 1)));
-    if (walk_) launch_walk(layer_begin, layer_end, st); else launch_fused(layer_begin, layer_end, st);
-    return true;
-  }
-
-  void launch_fused(size_t layer_begin, size_t layer_end, DeviceStage& st) {
-    {
-      KvtAttnLaunch a{};
-      a.src_layers = d_src_layers_.p;
-      a.dst_layers = d_dst_layers_.p;
-      a.src_maps = use_tma_ ? d_src_maps_.p : nullptr;
-      a.dst_maps = use_tma_ ? d_dst_maps_.p : nullptr;
-      a.src = params_.src;
-      a.dst = params_.dst;
-      a.layer_begin = static_cast<uint32_t>(layer_begin);
-      a.layer_end = static_cast<uint32_t>(layer_end);
-      a.reqs = reinterpret_cast<const KvtReqDesc*>(cur().d_plan);
-      a.n_reqs = plan_.n_reqs;
-      a.total_tiles = plan_.total_tiles;
-      a.block_ids = reinterpret_cast<const uint32_t*>(cur().d_plan + plan_.pool_offset);
-      a.tile_tokens = params_.tile_tokens;
-      a.src_head0 = params_.src_head0;
-      a.dst_head0 = params_.dst_head0;
-      a.n_heads = params_.n_heads;
-      a.mode = params_.mode;
-      a.status = cur().d_status;
-      a.dst_remote = dst_remote_ ? 1u : 0u;
-      a.tile_order = tile_order_;
-      a.store_form = store_form_;
-      int grid = env_nvlink_ctas();
-      // four small CTAs per SM, scaled by the SM-usage knob that bounds what a transfer may take from the forward pass
-      if (grid <= 0) grid = std::max(1, static_cast<int>(4 * kvt_sm_count(ctx_->device_id()) * env_kernel_copy_sm_usage()));
-      cuda_check(kvt_launch_p2d_attn(&a, grid, 0, use_tma_ ? 1 : 0, st.stream()), "kvt_launch_p2d_attn");
+    if (pull_) {
+      send_layers_msg(layer_begin, layer_end, true);
+      return true;
     }
+    // layer events are recorded in order on one stream, so the last one implies the others
+    void* ev = ctx_->cuda_barrier()->event(static_cast<uint32_t>(layer_end - 1));
+    if (walk_) eng_->launch_walk(walk_counts_, walk_plan_.ops.size(), walk_plan_.pool.size(), layer_begin, layer_end, 0, ev);
+    else eng_->launch_attn(params_, plan_, layer_begin, layer_end, 0, ev);
+    return true;
   }
 
   void send_data(size_t layer, Step* step) override {
     (void)step;
-    cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
-    if ((fused_ && plan_.n_reqs == 0) || (walk_ && walk_plan_.empty())) return;   // nothing to send from this rank
-    DeviceStage& st = use_stage(layer % stages_.size());
-    st.wait_event(ctx_->cuda_barrier()->event(static_cast<uint32_t>(layer)));
+    if (nothing_to_send()) return;
+    if (pull_) {
+      send_layers_msg(layer, layer + 1, false);
+      return;
+    }
+    void* ev = ctx_->cuda_barrier()->event(static_cast<uint32_t>(layer));
     if (fused_) {
-      if (plan_.n_reqs != 0) launch_fused(layer, layer + 1, st);
+      eng_->launch_attn(params_, plan_, layer, layer + 1, layer % eng_->n_stages(), ev);
       return;
     }
     if (walk_) {
-      if (!walk_plan_.empty()) launch_walk(layer, layer + 1, st);
+      eng_->launch_walk(walk_counts_, walk_plan_.ops.size(), walk_plan_.pool.size(), layer, layer + 1, layer % eng_->n_stages(), ev);
       return;
     }
+    cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
+    DeviceStage& st = eng_->stage(layer % eng_->n_stages());
+    st.wait_event(ev);
     const auto& addrs = ctx_->layer_data_address();
-    RTASSERT(layer < addrs.size() && layer < dst_ptrs_.size());
+    RTASSERT(layer < addrs.size() && layer < dst_map_.ptrs().size());
     if (launch_generic_multi(layer, layer + 1, st)) return;
     for (size_t t = 0; t < generic_.size(); ++t) {
       if (generic_[t].empty()) continue;
-      const size_t dst_cap = dst_.block_sizes.at(t) * static_cast<size_t>(dst_.layer_num_blocks);
-      const uint64_t* d = reinterpret_cast<const uint64_t*>(cur().d_plan) + generic_off_[t] * 3;
-      st.launch_resident(addrs[layer][t], dst_ptrs_[layer][t], d, generic_[t].size(), ctx_->tensor_capacity(t), dst_cap, 0,
-                         cur().d_status);
+      const uint64_t* d = reinterpret_cast<const uint64_t*>(eng_->current().d_plan) + generic_off_[t] * 3;
+      st.launch_resident(addrs[layer][t], dst_map_.ptrs()[layer][t], d, generic_[t].size(), src_caps_.at(t), dst_caps_.at(t), 0,
+                         eng_->current().d_status);
     }
   }
 
@@ -429,17 +310,17 @@ class NvlinkChannel : public IChannel {
       for (size_t t = 0; t < generic_.size(); ++t) {
         if (generic_[t].empty()) continue;
         m.src_base[e] = addrs[layer][t];
-        m.dst_base[e] = dst_ptrs_[layer][t];
-        m.src_cap[e] = ctx_->tensor_capacity(t);
-        m.dst_cap[e] = dst_.block_sizes.at(t) * static_cast<uint64_t>(dst_.layer_num_blocks);
+        m.dst_base[e] = dst_map_.ptrs()[layer][t];
+        m.src_cap[e] = src_caps_.at(t);
+        m.dst_cap[e] = dst_caps_.at(t);
         m.first[e] = static_cast<uint32_t>(generic_off_[t]);
         m.count[e] = static_cast<uint32_t>(generic_[t].size());
         ++e;
       }
     }
     m.n_tensors = e;
-    m.triples = reinterpret_cast<const uint64_t*>(cur().d_plan);
-    m.status = cur().d_status;
+    m.triples = reinterpret_cast<const uint64_t*>(eng_->current().d_plan);
+    m.status = eng_->current().d_status;
     if (env_use_tma() != 0) {
       // pages are long 16-byte aligned runs: the TMA engine moves them, four CTAs per SM
       const int grid = std::max(1, static_cast<int>(4 * kvt_sm_count(ctx_->device_id()) * env_kernel_copy_sm_usage()));
@@ -452,6 +333,13 @@ class NvlinkChannel : public IChannel {
   }
 
   size_t send_range(size_t lo, size_t hi, Step* step) override {
+    if (nothing_to_send()) return hi - lo;
+    if (pull_) {
+      // one message for everything recorded so far; the session launches layer by layer (attention) or once (walk)
+      const size_t n = walk_ ? std::min<size_t>(hi - lo, 8) : hi - lo;
+      send_layers_msg(lo, lo + n, false);
+      return n;
+    }
     if (fused_ || hi <= lo + 1) {   // the fused kernel gains nothing from longer launches (measured)
       send_data(lo, step);
       return 1;
@@ -459,12 +347,9 @@ class NvlinkChannel : public IChannel {
     if (walk_) {
       // the layers recorded so far leave in one launch: short per-layer work (state pages, MLA tokens) would
       // otherwise be bounded by the launch rate
-      if (walk_plan_.empty()) return hi - lo;
-      cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
       const size_t n = std::min<size_t>(hi - lo, 8);
-      DeviceStage& st = use_stage((range_rr_++) % stages_.size());
-      st.wait_event(ctx_->cuda_barrier()->event(static_cast<uint32_t>(lo + n - 1)));
-      launch_walk(lo, lo + n, st);
+      eng_->launch_walk(walk_counts_, walk_plan_.ops.size(), walk_plan_.pool.size(), lo, lo + n, eng_->next_stage(),
+                        ctx_->cuda_barrier()->event(static_cast<uint32_t>(lo + n - 1)));
       return n;
     }
     size_t per_layer = 0;
@@ -477,8 +362,8 @@ class NvlinkChannel : public IChannel {
     }
     cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
     const auto& addrs = ctx_->layer_data_address();
-    RTASSERT(lo + n <= addrs.size() && lo + n <= dst_ptrs_.size());
-    DeviceStage& st = use_stage((range_rr_++) % stages_.size());
+    RTASSERT(lo + n <= addrs.size() && lo + n <= dst_map_.ptrs().size());
+    DeviceStage& st = eng_->stage(eng_->next_stage());
     // layer events are recorded in order on one stream: the last of the range implies the others
     st.wait_event(ctx_->cuda_barrier()->event(static_cast<uint32_t>(lo + n - 1)));
     if (!launch_generic_multi(lo, lo + n, st)) {
@@ -490,63 +375,82 @@ class NvlinkChannel : public IChannel {
 
   bool async_flush() const override { return true; }
 
+  std::string metrics_prefix() const {
+    std::ostringstream ss;
+    ss << "Proto=nvlink,Mode=" << (pull_ ? "pull" : "push") << ",Path=" << (fused_ ? "fused" : (walk_ ? "walk" : "descriptors"))
+       << ",OriginSbNum=" << origin_blocks_ << ",MergedSbNum=" << merged_blocks_ << ",BytesPerLayer=" << moved_bytes_per_layer_
+       << ",Tiles=" << (walk_ ? walk_plan_.bulk_units + walk_plan_.simt_units : plan_.total_tiles);
+    return ss.str();
+  }
+
   // Enqueue the batch's completion record and return its ticket; nothing here waits for the GPU.
   uint64_t flush_async() override {
-    cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
     fault_inject_throw();
-    if (batch_slot_ < 0) begin_slot(0);     // a batch without data still completes through a record
-    Slot& sl = cur();
-    cudaStream_t ss = sl.stream;
-    // the slot's stream joins the transfer streams the batch used, and the previous batch's record
-    for (size_t i = 0; i < stages_.size() && i < stage_used_.size(); ++i)
-      if (stage_used_[i]) cuda_check(cudaStreamWaitEvent(ss, static_cast<cudaEvent_t>(stages_[i]->record_done()), 0), "cudaStreamWaitEvent");
-    if (last_done_event_ != nullptr && last_done_event_ != sl.done_event)
-      cuda_check(cudaStreamWaitEvent(ss, last_done_event_, 0), "cudaStreamWaitEvent");
-    if (!fault_inject_drop_completion())
-      cuda_check(kvt_launch_complete(sl.d_status, sl.d_rec, sl.seq, ss), "kvt_launch_complete");
-    cuda_check(cudaEventRecord(sl.done_event, ss), "cudaEventRecord");
-    last_done_event_ = sl.done_event;
-    std::ostringstream ss_m;
-    ss_m << "Proto=nvlink,Path=" << (fused_ ? "fused" : (walk_ ? "walk" : "descriptors")) << ",OriginSbNum=" << origin_blocks_
-         << ",MergedSbNum=" << merged_blocks_ << ",BytesPerLayer=" << moved_bytes_per_layer_ << ",Tiles=" << (walk_ ? walk_plan_.bulk_units + walk_plan_.simt_units : plan_.total_tiles);
-    {
-      std::lock_guard<std::mutex> g(slot_mu_);
-      sl.metrics = ss_m.str();
-      sl.flushed_at = SteadyClock::now();
-      sl.pending = true;
+    const bool drop = fault_inject_drop_completion();
+    TimeWatch tw;
+    uint64_t ticket = 0;
+    if (pull_) {
+      if (!pull_batch_open_) {        // a batch without data still completes through the session, in order
+        PullPlanHead h{};
+        h.kind = PULL_KIND_WALK;
+        send_plan(h, nullptr, 0, nullptr, 0);
+      }
+      std::string msg(RPC_HEADER, '\0');
+      put_rpc_header(msg.data(), PULL_FLUSH_REQ, pull_seq_);
+      put(msg, static_cast<uint8_t>(drop ? 1 : 0));
+      send_msg(msg);
+      ticket = pull_seq_;
+      pull_batch_open_ = false;
+      std::lock_guard<std::mutex> g(pull_mu_);
+      pull_metrics_[ticket] = metrics_prefix() + ",FlushUs=" + std::to_string(tw.get_elapse_us());
+    } else {
+      cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
+      ticket = eng_->flush_async(metrics_prefix(), drop);
+      std::lock_guard<std::mutex> g(pull_mu_);
+      pull_metrics_[ticket] = ",FlushUs=" + std::to_string(tw.get_elapse_us());
     }
-    const uint64_t ticket = sl.seq;
-    batch_slot_ = -1;
     generic_.clear();
-    begin_batch();
     return ticket;
   }
 
   PollResult poll_completion(uint64_t ticket, std::string& out) override {
-    std::lock_guard<std::mutex> g(slot_mu_);
-    Done d;
-    bool have = false;
-    auto it = finished_.find(ticket);
-    if (it != finished_.end()) {
+    BatchEngine::Done d;
+    std::string tail;
+    if (pull_) {
+      std::lock_guard<std::mutex> g(pull_mu_);
+      drain_done_frames();
+      auto it = pull_done_.find(ticket);
+      if (it == pull_done_.end()) {
+        if (pull_broken_) {
+          out = "the pull session's connection broke";
+          active_ = false;
+          return PollResult::FAILED;
+        }
+        return PollResult::PENDING;
+      }
       d = it->second;
-      finished_.erase(it);
-      have = true;
+      pull_done_.erase(it);
+      auto mt = pull_metrics_.find(ticket);
+      if (mt != pull_metrics_.end()) {
+        d.metrics = mt->second;
+        pull_metrics_.erase(mt);
+      }
     } else {
-      for (Slot& sl : slots_) {
-        if (sl.seq != ticket) continue;
-        if (!sl.pending) return PollResult::FAILED;      // never flushed
-        if (!record_arrived(sl)) return PollResult::PENDING;
-        d = take_record(sl);
-        have = true;
-        break;
+      const PollResult r = eng_->poll(ticket, &d);
+      if (r == PollResult::PENDING) return r;
+      if (r == PollResult::FAILED) {
+        out = "completion ticket unknown";
+        return r;
+      }
+      std::lock_guard<std::mutex> g(pull_mu_);
+      auto mt = pull_metrics_.find(ticket);
+      if (mt != pull_metrics_.end()) {
+        tail = mt->second;
+        pull_metrics_.erase(mt);
       }
     }
-    if (!have) {
-      out = "completion ticket unknown";
-      return PollResult::FAILED;
-    }
     std::ostringstream ss;
-    ss << d.metrics << ",FlushUs=" << d.flush_us;
+    ss << d.metrics << tail;
     if (d.t_start_ns != 0 && d.t_end_ns >= d.t_start_ns) ss << ",DeviceUs=" << (d.t_end_ns - d.t_start_ns) / 1000;
     if (d.status != 0) {
       ss << ",KernelStatus=" << d.status << ",Detail=" << d.detail;
@@ -577,252 +481,138 @@ class NvlinkChannel : public IChannel {
   bool is_active() override { return active_; }
 
   void close() override {
-    if (!active_ && stages_.empty() && slots_.empty()) return;
     active_ = false;
     if (ctx_->device_id() >= 0) cudaSetDevice(ctx_->device_id());
-    // batches still in flight keep writing into the slots: let them finish (bounded by the device itself;
-    // every kernel here bounds its own waits) before the memory goes away
-    for (Slot& sl : slots_)
-      if (sl.stream != nullptr) cudaStreamSynchronize(sl.stream);
-    stages_.clear();
-    free_slots();
-    for (const std::string& key : ipc_keys_) ipc_cache().release(key);
-    ipc_keys_.clear();
-    ipc_locals_.clear();
+    if (eng_) eng_->close();
+    eng_.reset();
+    pull_sock_.reset();      // the server ends the session when the connection goes away
+    dst_map_.release();
   }
 
  private:
-  static constexpr size_t kSlots = 4;
-  struct Slot {
-    cudaStream_t stream{nullptr};      // carries the plan upload and the completion record of its batch
-    cudaEvent_t plan_event{nullptr};   // the plan is on the device
-    cudaEvent_t done_event{nullptr};   // behind the completion record
-    char* d_plan{nullptr};
-    char* h_plan{nullptr};             // pinned
-    uint32_t* d_status{nullptr};       // 64 bytes: code, detail, start stamp
-    KvtCompletion* h_rec{nullptr};     // mapped host memory ...
-    KvtCompletion* d_rec{nullptr};     // ... and its device address
-    uint64_t seq{0};                   // ticket of the batch that last used the slot
-    bool pending{false};               // flushed, record not yet consumed
-    std::string metrics;
-    Timepoint flushed_at;
-  };
-  struct Done {
-    uint32_t status{0}, detail{0};
-    uint64_t t_start_ns{0}, t_end_ns{0};
-    int64_t flush_us{0};
-    std::string metrics;
-  };
+  // ---- pull mode: messages to the session ------------------------------------------------------------
+  bool open_pull(FdGuard& sock) {
+    const PeerMemInfo mine = export_peer_mem_info(ctx_);
+    const PeerEvents evs = export_peer_events(ctx_);
+    if (evs.events.size() != ctx_->num_layers()) return false;
+    if (!dst_map_.same_process())
+      for (const auto& e : evs.events)
+        if (!e.has_handle) return false;      // layer events were not created for interprocess use
+    std::string msg(RPC_HEADER, '\0');
+    put_rpc_header(msg.data(), PULL_OPEN_REQ, new_id());
+    put(msg, pull_protocol_version());
+    put(msg, static_cast<uint32_t>(src_caps_.size()));
+    for (uint64_t c : src_caps_) put(msg, c);
+    const std::string mem = mine.serialize(), ev = evs.serialize();
+    put(msg, static_cast<uint32_t>(mem.size()));
+    msg += mem;
+    put(msg, static_cast<uint32_t>(ev.size()));
+    msg += ev;
+    std::string resp;
+    if (!send_frame(sock.fd(), msg.data(), msg.size(), env_rpc_timeout_s() * 1000) ||
+        !recv_frame(sock.fd(), resp, env_rpc_timeout_s() * 1000) || resp.size() < RPC_HEADER + 4) {
+      throw KVTransferException(ErrorKind::TRANSPORT, "nvlink: pull-session request failed");
+    }
+    uint32_t status = 0;
+    memcpy(&status, resp.data() + RPC_HEADER, 4);
+    if (status != WIRE_OK) LOG(INFO) << "nvlink: destination offers no pull session (status " << status << "), pushing";
+    return status == WIRE_OK;
+  }
 
-  void alloc_slots(size_t cap) {
-    free_slots();
-    plan_cap_ = (cap + 255) & ~size_t{255};
-    cuda_check(cudaMalloc(reinterpret_cast<void**>(&d_plan_all_), plan_cap_ * kSlots), "cudaMalloc(plans)");
-    cuda_check(cudaHostAlloc(reinterpret_cast<void**>(&h_plan_all_), plan_cap_ * kSlots, cudaHostAllocPortable), "cudaHostAlloc(plans)");
-    cuda_check(cudaMalloc(reinterpret_cast<void**>(&d_status_all_), 64 * kSlots), "cudaMalloc(status)");
-    cuda_check(cudaMemset(d_status_all_, 0, 64 * kSlots), "cudaMemset");
-    void* h = nullptr;
-    cuda_check(cudaHostAlloc(&h, 64 * kSlots, cudaHostAllocMapped | cudaHostAllocPortable), "cudaHostAlloc(records)");
-    memset(h, 0, 64 * kSlots);
-    h_rec_all_ = static_cast<char*>(h);
-    void* d = nullptr;
-    cuda_check(cudaHostGetDevicePointer(&d, h, 0), "cudaHostGetDevicePointer");
-    slots_.assign(kSlots, Slot{});
-    for (size_t i = 0; i < kSlots; ++i) {
-      Slot& sl = slots_[i];
-      cuda_check(cudaStreamCreateWithFlags(&sl.stream, cudaStreamNonBlocking), "cudaStreamCreate");
-      cuda_check(cudaEventCreateWithFlags(&sl.plan_event, cudaEventDisableTiming), "cudaEventCreate");
-      cuda_check(cudaEventCreateWithFlags(&sl.done_event, cudaEventDisableTiming), "cudaEventCreate");
-      sl.d_plan = d_plan_all_ + i * plan_cap_;
-      sl.h_plan = h_plan_all_ + i * plan_cap_;
-      sl.d_status = reinterpret_cast<uint32_t*>(d_status_all_ + 64 * i);
-      sl.h_rec = reinterpret_cast<KvtCompletion*>(h_rec_all_ + 64 * i);
-      sl.d_rec = reinterpret_cast<KvtCompletion*>(static_cast<char*>(d) + 64 * i);
+  void send_msg(const std::string& msg) {
+    if (!send_frame(pull_sock_.fd(), msg.data(), msg.size(), env_rpc_timeout_s() * 1000)) {
+      active_ = false;
+      throw KVTransferException(ErrorKind::TRANSPORT, "nvlink: the pull session's connection broke");
     }
   }
 
-  void free_slots() {
-    for (Slot& sl : slots_) {
-      if (sl.plan_event != nullptr) cudaEventDestroy(sl.plan_event);
-      if (sl.done_event != nullptr) cudaEventDestroy(sl.done_event);
-      if (sl.stream != nullptr) cudaStreamDestroy(sl.stream);
-    }
-    slots_.clear();
-    if (d_plan_all_ != nullptr) cudaFree(d_plan_all_);
-    if (h_plan_all_ != nullptr) cudaFreeHost(h_plan_all_);
-    if (d_status_all_ != nullptr) cudaFree(d_status_all_);
-    if (h_rec_all_ != nullptr) cudaFreeHost(h_rec_all_);
-    d_plan_all_ = h_plan_all_ = d_status_all_ = h_rec_all_ = nullptr;
-    last_done_event_ = nullptr;
-    batch_slot_ = -1;
+  void send_plan(const PullPlanHead& head, const void* a, size_t a_len, const void* b, size_t b_len) {
+    PullPlanHead h = head;
+    h.blob_bytes = a_len + b_len;
+    ++pull_seq_;
+    std::string msg(RPC_HEADER, '\0');
+    put_rpc_header(msg.data(), PULL_PLAN_REQ, pull_seq_);
+    msg.append(reinterpret_cast<const char*>(&h), sizeof(h));
+    if (a_len) msg.append(static_cast<const char*>(a), a_len);
+    if (b_len) msg.append(static_cast<const char*>(b), b_len);
+    send_msg(msg);
+    pull_batch_open_ = true;
   }
 
-  static bool record_arrived(const Slot& sl) {
-    return __atomic_load_n(&sl.h_rec->seq, __ATOMIC_ACQUIRE) == sl.seq;
+  void send_layers_msg(size_t lo, size_t hi, bool one_launch) {
+    std::string msg(RPC_HEADER, '\0');
+    put_rpc_header(msg.data(), PULL_LAYERS_REQ, pull_seq_);
+    put(msg, static_cast<uint32_t>(lo));
+    put(msg, static_cast<uint32_t>(hi));
+    put(msg, static_cast<uint8_t>(one_launch ? 1 : 0));
+    send_msg(msg);
   }
 
-  // slot_mu_ held.  Moves an arrived record out of its slot.
-  Done take_record(Slot& sl) {
-    Done d;
-    d.status = sl.h_rec->status;
-    d.detail = sl.h_rec->detail;
-    d.t_start_ns = sl.h_rec->t_start_ns;
-    d.t_end_ns = sl.h_rec->t_end_ns;
-    d.flush_us = 0;
-    d.metrics = std::move(sl.metrics);
-    sl.pending = false;
-    return d;
-  }
-
-  Slot& cur() {
-    RTASSERT(batch_slot_ >= 0);
-    return slots_[static_cast<size_t>(batch_slot_)];
-  }
-
-  // Takes the next slot for a new batch.  A slot whose previous batch has not completed makes the sender
-  // wait here (bounded): that is the back-pressure of a sender running more than kSlots batches ahead of
-  // the GPU.  A plan larger than the slots were sized for re-allocates them (all batches drained first).
-  Slot& begin_slot(size_t bytes) {
-    RTASSERT(!slots_.empty());
-    if (bytes > plan_cap_) {
-      LOG(WARNING) << "nvlink: plan of " << bytes << " bytes exceeds the slots sized at connect (" << plan_cap_
-                   << "); re-allocating";
-      for (size_t i = 0; i < slots_.size(); ++i) wait_slot(slots_[i]);
-      for (Slot& sl : slots_) cuda_check(cudaStreamSynchronize(sl.stream), "cudaStreamSynchronize");
-      std::map<uint64_t, Done> keep;
-      uint64_t seq = next_seq_;
-      {
-        std::lock_guard<std::mutex> g(slot_mu_);
-        keep.swap(finished_);
+  // pull_mu_ held.  Reads whatever PULL_DONE frames have arrived, without blocking.
+  void drain_done_frames() {
+    if (!pull_sock_.valid() || pull_broken_) return;
+    for (;;) {
+      char tmp[4096];
+      const ssize_t n = ::recv(pull_sock_.fd(), tmp, sizeof(tmp), MSG_DONTWAIT);
+      if (n > 0) {
+        pull_rx_.append(tmp, static_cast<size_t>(n));
+        continue;
       }
-      alloc_slots(bytes * 2);
-      std::lock_guard<std::mutex> g(slot_mu_);
-      finished_.swap(keep);
-      next_seq_ = seq;
+      if (n == 0 || (errno != EAGAIN && errno != EWOULDBLOCK && errno != EINTR)) pull_broken_ = true;
+      break;
     }
-    slot_rr_ = (slot_rr_ + 1) % slots_.size();
-    Slot& sl = slots_[slot_rr_];
-    wait_slot(sl);
-    {
-      std::lock_guard<std::mutex> g(slot_mu_);
-      sl.seq = ++next_seq_;
-      sl.metrics.clear();
-    }
-    batch_slot_ = static_cast<int>(slot_rr_);
-    begin_batch();
-    return sl;
-  }
-
-  // Waits (bounded) until the slot's previous batch has completed and parks its record for the poller.
-  void wait_slot(Slot& sl) {
-    const Timepoint deadline = SteadyClock::now() + std::chrono::milliseconds(env_completion_timeout_ms());
-    for (int spins = 0;; ++spins) {
-      {
-        std::lock_guard<std::mutex> g(slot_mu_);
-        if (!sl.pending) return;
-        if (record_arrived(sl)) {
-          const uint64_t seq = sl.seq;
-          finished_[seq] = take_record(sl);
-          return;
+    size_t off = 0;
+    while (pull_rx_.size() - off >= 4) {
+      uint32_t len = 0;
+      memcpy(&len, pull_rx_.data() + off, 4);
+      if (pull_rx_.size() - off - 4 < len) break;
+      const char* p = pull_rx_.data() + off + 4;
+      if (len >= RPC_HEADER + 24) {
+        uint32_t magic = 0;
+        uint64_t seq = 0;
+        get_rpc_header(p, &magic, &seq);
+        if (magic == PULL_DONE) {
+          BatchEngine::Done d;
+          memcpy(&d.status, p + RPC_HEADER, 4);
+          memcpy(&d.detail, p + RPC_HEADER + 4, 4);
+          memcpy(&d.t_start_ns, p + RPC_HEADER + 8, 8);
+          memcpy(&d.t_end_ns, p + RPC_HEADER + 16, 8);
+          pull_done_[seq] = d;
         }
       }
-      if (SteadyClock::now() > deadline) {
-        active_ = false;
-        throw KVTransferException(ErrorKind::TRANSPORT, "nvlink: an earlier batch never completed; dropping the channel");
-      }
-      if (spins < 2000) std::this_thread::yield(); else std::this_thread::sleep_for(std::chrono::microseconds(20));
+      off += 4 + len;
     }
-  }
-
-  void upload_slot(Slot& sl, size_t bytes) {
-    if (bytes != 0)
-      cuda_check(cudaMemcpyAsync(sl.d_plan, sl.h_plan, bytes, cudaMemcpyHostToDevice, sl.stream), "cudaMemcpyAsync(plan)");
-    if (stamps_) cuda_check(kvt_launch_stamp(reinterpret_cast<uint64_t*>(sl.d_status) + 1, sl.stream), "kvt_launch_stamp");
-    cuda_check(cudaEventRecord(sl.plan_event, sl.stream), "cudaEventRecord");
-  }
-
-  // The slot's stream carries the plan; a transfer stream joins it (waits for the upload) when the batch first
-  // uses it, and the completion record joins back only the streams that were used.
-  void begin_batch() { stage_used_.assign(stages_.size(), 0); }
-
-  DeviceStage& use_stage(size_t i) {
-    if (stage_used_.size() != stages_.size()) stage_used_.assign(stages_.size(), 0);
-    if (!stage_used_[i]) {
-      stages_[i]->wait_event(cur().plan_event);
-      stage_used_[i] = 1;
-    }
-    return *stages_[i];
-  }
-
-  void ensure_layer_arrays() {
-    if (d_src_layers_.p != nullptr) return;
-    std::vector<uint64_t> src, dst;
-    for (const auto& l : ctx_->layer_data_address()) src.push_back(l.at(0));
-    for (const auto& l : dst_ptrs_) dst.push_back(l.at(0));
-    d_src_layers_.upload(src);
-    d_dst_layers_.upload(dst);
-    use_tma_ = false;
-    if (env_use_tma() != 0 && params_.mode == KVT_MODE_COPY) {
-      // a tile is kept in the destination's own order, so that it leaves as one linear store where the
-      // destination page holds it contiguously (HND pages; NHD pages when every head moves)
-      const int want_order = env_tile_order();
-      tile_order_ = want_order >= 0 ? (want_order != 0 ? 1u : 0u)
-                                    : (params_.dst.token_stride < params_.dst.head_stride ? 1u : 0u);
-      const bool flat_ok = kvt_tile_is_flat(&params_.dst, params_.n_heads, params_.tile_tokens, tile_order_) != 0;
-      store_form_ = (flat_ok && env_store_form() != 0) ? 1u : 0u;
-      std::vector<TensorMapBytes> sm(src.size()), dm(dst.size());
-      bool ok = true;
-      for (size_t i = 0; i < src.size() && ok; ++i) {
-        ok = kvt_encode_tensor_map_ordered(sm[i].b, src[i], &params_.src, params_.n_heads, params_.tile_tokens, tile_order_) == 0 &&
-             kvt_encode_tensor_map_ordered(dm[i].b, dst[i], &params_.dst, params_.n_heads, params_.tile_tokens, tile_order_) == 0;
-      }
-      if (ok) {
-        d_src_maps_.upload(sm);
-        d_dst_maps_.upload(dm);
-        use_tma_ = true;
-      } else {
-        LOG(WARNING) << "nvlink: tensor maps not encodable for this layout, using the SIMT path";
-      }
-    }
+    if (off) pull_rx_.erase(0, off);
   }
 
   Context* ctx_;
   WorkerInfo dst_;
   bool active_{false};
-  std::vector<std::vector<uint64_t>> dst_ptrs_;
-  std::vector<std::unique_ptr<DeviceStage>> stages_;
+  PeerMapping dst_map_;
+  uint32_t n_tensors_{0};
+  std::vector<uint64_t> src_caps_, dst_caps_;
+  std::unique_ptr<BatchEngine> eng_;     // push mode
   int src_shape_{0}, dst_shape_{0};
   bool dst_mx_{false};
-  // fused path
-  bool fused_{false};
-  bool use_tma_{false};
-  uint32_t tile_order_{0}, store_form_{0};
+  bool dst_remote_{false};       // the destination cache lives on another GPU
+  // what the current batch is
+  bool fused_{false}, walk_{false};
   DeviceAttnParams params_{};
   PackedPlan plan_;
-  bool walk_{false};
   WalkPlan walk_plan_;
-  DevArray<uint64_t> d_walk_src_, d_walk_dst_;   // [layer][tensor] base addresses
-  std::vector<Slot> slots_;
-  size_t plan_cap_{0}, slot_rr_{0};
-  int batch_slot_{-1};
-  uint64_t next_seq_{0};
-  char* d_plan_all_{nullptr};
-  char* h_plan_all_{nullptr};
-  char* d_status_all_{nullptr};
-  char* h_rec_all_{nullptr};
-  cudaEvent_t last_done_event_{nullptr};
-  std::mutex slot_mu_;                    // slot bookkeeping is shared with the completion poller's thread
-  std::map<uint64_t, Done> finished_;     // records taken out of a slot that was needed again before they were polled
-  std::vector<std::string> ipc_keys_;     // mappings this channel holds a reference to
-  std::vector<uint64_t> ipc_locals_;
-  DevArray<uint64_t> d_src_layers_, d_dst_layers_;
-  DevArray<TensorMapBytes> d_src_maps_, d_dst_maps_;
-  size_t range_rr_{0};
-  bool dst_remote_{false};       // the destination cache lives on another GPU
-  std::vector<char> stage_used_;
+  KvtWalkCounts walk_counts_{};
+  // pull mode
+  bool pull_{false};
+  FdGuard pull_sock_;
+  uint64_t pull_seq_{0};
+  bool pull_batch_open_{false};
+  std::mutex pull_mu_;                                   // shared with the completion poller's thread
+  std::string pull_rx_;
+  std::map<uint64_t, BatchEngine::Done> pull_done_;
+  std::map<uint64_t, std::string> pull_metrics_;
+  bool pull_broken_{false};
+  // descriptor path (push only)
   uint32_t generic_rounds_{1};   // bulk copy kernel: segment rounds the longest descriptor needs
-  const bool stamps_{env_device_timestamps()};
-  // generic path
   std::vector<std::vector<Triple>> generic_;
   std::vector<size_t> generic_off_;   // first descriptor of each tensor inside the uploaded buffer
   size_t origin_blocks_{0}, merged_blocks_{0}, moved_bytes_per_layer_{0};

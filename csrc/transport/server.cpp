@@ -29,6 +29,7 @@
 #include "kernels/kvt_kernels.h"
 #include "transport/channel.h"
 #include "transport/device_stage.h"
+#include "transport/pull_session.h"
 #include "transport/wire.h"
 
 namespace kvx {
@@ -121,6 +122,9 @@ class TransferServer : public ITransferServer {
     PinnedBuffer rx;
     ShmSeg shm;
     const bool gpu = ctx_->device_id() >= 0;
+    // a pull session answers finished batches from the completion thread: every write to this connection is locked
+    auto write_mu = std::make_shared<std::mutex>();
+    std::shared_ptr<PullSession> pull;
     try {
       if (gpu) stage = std::make_unique<DeviceStage>(ctx_->device_id());
       for (;;) {
@@ -149,6 +153,27 @@ class TransferServer : public ITransferServer {
           resp = on_attach(buf, n, shm, gpu);
         } else if (magic == MEM_HANDLES_REQ) {
           resp = on_mem_handles(buf, n);
+        } else if (magic == PULL_OPEN_REQ) {
+          uint64_t reqid = 0;
+          if (n < RPC_HEADER) break;
+          get_rpc_header(buf, &magic, &reqid);
+          uint32_t status = WIRE_BAD_REQUEST;
+          if (gpu && env_nvlink_pull() != 0) {
+            pull = std::make_shared<PullSession>(ctx_, cfd, write_mu);
+            status = pull->open(buf + RPC_HEADER, n - RPC_HEADER);
+            if (status != WIRE_OK) pull.reset();
+          }
+          resp.resize(RPC_HEADER);
+          put_rpc_header(resp.data(), PULL_OPEN_REQ, reqid);
+          put(resp, status);
+        } else if (magic == PULL_PLAN_REQ || magic == PULL_LAYERS_REQ || magic == PULL_FLUSH_REQ) {
+          uint64_t seq = 0;
+          if (n < RPC_HEADER || !pull) break;
+          get_rpc_header(buf, &magic, &seq);
+          if (magic == PULL_PLAN_REQ) pull->on_plan(seq, buf + RPC_HEADER, n - RPC_HEADER);
+          else if (magic == PULL_LAYERS_REQ) pull->on_layers(seq, buf + RPC_HEADER, n - RPC_HEADER);
+          else pull->on_flush(seq, buf + RPC_HEADER, n - RPC_HEADER);
+          continue;     // one-way: a flushed batch is answered with PULL_DONE when its completion record arrives
         } else if (magic == PING_REQ) {
           resp.assign(buf, std::min<size_t>(n, RPC_HEADER));
           put(resp, static_cast<uint32_t>(WIRE_OK));
@@ -156,10 +181,16 @@ class TransferServer : public ITransferServer {
           LOG(ERROR) << "KVT server: unknown message magic=" << magic << " len=" << n;
           break;
         }
+        std::lock_guard<std::mutex> wg(*write_mu);
         if (!send_frame(cfd, resp.data(), resp.size(), env_rpc_timeout_s() * 1000)) break;
       }
     } catch (const std::exception& ex) {
       LOG(ERROR) << "KVT server connection failed: " << ex.what();
+    }
+    if (pull) {
+      pull->close();      // no more PULL_DONE frames; batches still completing keep the session alive until they end
+      // the descriptor is about to close: wait (bounded) until nothing can write to it any more
+      std::lock_guard<std::mutex> wg(*write_mu);
     }
     shm.reset();
     std::lock_guard<std::mutex> g(mu_);

@@ -25,6 +25,15 @@ constexpr uint32_t KV_CACHE_SHM_MAGIC = 0x4B565368;    // 'KVSh': blob lives in 
 constexpr uint32_t SHM_ATTACH_REQ = 0x4B565341;        // 'KVSA': [name_len u32][name][bytes u64]
 constexpr uint32_t MEM_HANDLES_REQ = 0x20181218;       // peer-memory handles of every layer tensor
 constexpr uint32_t PING_REQ = 0x4B565069;              // 'KVPi'
+// Pull transfers: the decode GPU runs the transfer kernels and loads the prefill cache over NVLink.  The
+// prefill side opens a session on the decode worker's server (its own memory handles and layer-event handles
+// travel in the request), then drives it with one-way messages; the server answers each flushed batch with
+// PULL_DONE when the batch's completion record has arrived.
+constexpr uint32_t PULL_OPEN_REQ = 0x4B56504F;         // 'KVPO': [version u32][src caps][PeerMemInfo][PeerEvents] -> [status u32]
+constexpr uint32_t PULL_PLAN_REQ = 0x4B565050;         // 'KVPP': a batch's plan (reqid = batch sequence number)
+constexpr uint32_t PULL_LAYERS_REQ = 0x4B56504C;       // 'KVPL': layers [lo, hi) of the batch are recorded: enqueue them
+constexpr uint32_t PULL_FLUSH_REQ = 0x4B565046;        // 'KVPF': the batch is complete: enqueue its completion record
+constexpr uint32_t PULL_DONE = 0x4B565044;             // 'KVPD': [status u32][detail u32][t_start u64][t_end u64]
 constexpr size_t RPC_HEADER = sizeof(uint32_t) + sizeof(uint64_t);
 
 enum WireStatus : uint32_t { WIRE_OK = 0, WIRE_BAD_REQUEST = 400, WIRE_INTERNAL = 500 };

@@ -24,6 +24,7 @@ _DEFS: dict[str, tuple[Callable[[str], Any], Any]] = {
     "VLLM_KVS_TTL_SECONDS": (float, 300.0),
     "VLLM_KVS_CAPACITY_BYTES": (int, 1 << 30),
     "VLLM_KVS_STORE_NAN_CHECK": (int, 0),
+    "VLLM_KVS_USE_REQUEST_HASH": (lambda v: v not in ("0", "", "false"), False),
     "VLLM_ZERO_HYBRID_KV_CACHE": (lambda v: v not in ("0", "", "false"), True),
     "VLLM_LOG_STATS_INTERVAL": (float, 10.0),
     "VLLM_HOST_IP": (str, ""),

@@ -260,11 +260,12 @@ def get_backend_cls(cfg: VllmConfig) -> type:
         raise ValueError("kv_role must be kv_producer or kv_consumer for the 'kvt' backend")
     if backend in ("kvs", "mooncake", "v6d_object"):
         assert kcfg.kv_role == "kv_both", f"kv_role must be 'kv_both' for the {backend} backend"
-        from .kvsbackend import KVSBackend
-        return KVSBackend
+        from .kvs_flavours import flavour_class
+        # "kvs" is the Vineyard-style adapter unless kvs_backend names another flavour (kvsbackend.py:158 of the reference)
+        return flavour_class(kcfg.get_from_extra_config("kvs_backend", backend) if backend == "kvs" else backend)
     if backend in ("v6d_object+kvt", "kvt+v6d_object"):
         if not kcfg.is_kv_producer:
             raise ValueError("the KVT half of this composite is producer-only: kv_role must be kv_producer or kv_both")
-        from .kvsp import KVSP
-        return KVSP
+        from .kvsp import V6dObjectKVTBackend
+        return V6dObjectKVTBackend
     raise ValueError(f"Unknown backend: {backend}")

@@ -238,7 +238,9 @@ class KVTransferClient:
     def _init_events(self):
         if self._device_id >= 0:
             with torch.cuda.device(self._device_id):
-                self._events = [torch.cuda.Event() for _ in range(self._num_layers)]
+                # interprocess: a decode worker that pulls this cache orders its streams after these events
+                # (CUDA IPC event handles), so nobody's host waits for the forward pass
+                self._events = [torch.cuda.Event(interprocess=True) for _ in range(self._num_layers)]
                 for ev in self._events:
                     ev.record()
             self._event_addrs = [ev.cuda_event for ev in self._events]
