@@ -144,11 +144,11 @@ def test_backend_selection_table():
     assert pick("kvt+migration", "kv_both") == pick("migration+kvt", "kv_both") == "KVTMigration"
     assert pick("kvt+kvs", "kv_producer") == pick("kvs+kvt", "kv_producer") == "KVSP"
     assert pick("local_file", "kv_both") == "FileBackend"
-    for b in ("kvs", "mooncake", "v6d_object"):
-        assert pick(b, "kv_both") == "KVSBackend"
+    for b, cls in (("kvs", "KVSBackend"), ("mooncake", "MooncakeKVSBackend"), ("v6d_object", "V6dObjectBackend")):
+        assert pick(b, "kv_both") == cls
         with pytest.raises(AssertionError):
             pick(b, "kv_producer")
-    assert pick("v6d_object+kvt", "kv_producer") == "KVSP"
+    assert pick("v6d_object+kvt", "kv_producer") == pick("kvt+v6d_object", "kv_both") == "V6dObjectKVTBackend"
     with pytest.raises(ValueError):
         pick("v6d_object+kvt", "kv_consumer")
     with pytest.raises(ValueError):
