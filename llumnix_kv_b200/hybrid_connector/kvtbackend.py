@@ -275,7 +275,21 @@ def build_kvt_args(backend: "HybridBackend", kv_caches: dict, tp_rank: int) -> d
     dp = cfg.parallel_config.data_parallel_rank
     kv_caches = resolve_raw_cache_tensors(kv_caches)
     layers = flatten_cache(kv_caches)
-    if backend.is_hybrid:
+    derived = None
+    kcc = backend._kv_cache_config
+    hf = getattr(mc, "hf_text_config", None)
+    if backend.is_hybrid and kcc is not None and getattr(kcc, "kv_cache_tensors", None) and hf is not None:
+        # an engine that registers its caches the way vLLM does (recurrent state as lists, attention pages as
+        # views of shared physical tensors, a KV-cache configuration that says who shares what): everything the
+        # native engine needs is worked out from those objects (kvt_args.py)
+        from .kvt_args import derive_hybrid_kvt_args
+
+        derived = derive_hybrid_kvt_args(kv_caches, kcc, hf, tp, cc.block_size, getattr(cc, "attn_pack_size", 1),
+                                         kda_page_stride=getattr(cc, "kda_page_stride", 0),
+                                         kda_conv_dim_first=bool(getattr(mc, "kda_conv_dim_first", False)))
+        layers = [[t] for t in derived.physical_tensors.values()]
+        backend.hybrid_model_send_layer = list(derived.send_layers)
+    elif backend.is_hybrid:
         # Several logical layers (one GDN layer of each group and one attention layer) share a
         # physical cache tensor.  Each tensor is registered once, and the transfer of a tensor
         # starts when the last logical layer that writes into it has run.
@@ -288,18 +302,23 @@ def build_kvt_args(backend: "HybridBackend", kv_caches: dict, tp_rank: int) -> d
         backend.hybrid_model_send_layer = [idx for idx, _ in phys]
     n_tensors = len(layers[0])
     block_bytes, token_bytes = [], []
-    for t in range(n_tensors):
-        nbytes = layers[0][t].nbytes
-        assert nbytes % cc.num_gpu_blocks == 0
-        bb = nbytes // cc.num_gpu_blocks
-        block_bytes.append(bb)
-        token_bytes.append(bb // cc.block_size)
+    if derived is not None:
+        block_bytes, token_bytes = list(derived.block_bytes), list(derived.token_bytes)
+    else:
+        for t in range(n_tensors):
+            nbytes = layers[0][t].nbytes
+            assert nbytes % cc.num_gpu_blocks == 0
+            bb = nbytes // cc.num_gpu_blocks
+            block_bytes.append(bb)
+            token_bytes.append(bb // cc.block_size)
     proto = envs.VLLM_KV_TRANS_PROTOCOL or cfg.kv_transfer_config.get_from_extra_config("kvt_protocol", "")
     protocols = [PT.to_protocol_type(p) for p in proto.split(",") if p] if proto else []
     args = dict(inst_id=backend._inst_id, tp_size=tp, worker_id=dp * tp + tp_rank, worker_tp_rank=tp_rank,
                 block_bytes=block_bytes, token_bytes=token_bytes, naming_url=backend._naming_url, layers=layers,
                 protocols=protocols, num_kv_heads=1 if mc.use_mla else mc.num_kv_heads, cache_shape=cc.cache_shape)
-    if backend.is_hybrid:
+    if derived is not None:
+        args.update(derived.kwargs)
+    elif backend.is_hybrid:
         args.update(mc.hybrid_kvt_kwargs_for(tp))
     return args
 
