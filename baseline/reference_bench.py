@@ -29,8 +29,18 @@ WHY = ("reference not installable offline: setup.py needs setuptools_scm (absent
        "extension links the closed libaccl_barex.so + libibverbs; the control plane needs a vLLM fork")
 
 
-def build(reference_root: str = "/root/reference", verbose: bool = False) -> str:
+def reference_checkout() -> str:
+    """Where the reference's sources are: LLUMNIX_KV_REFERENCE, else a ``reference`` folder next to this
+    repository's checkout."""
+    env = os.environ.get("LLUMNIX_KV_REFERENCE")
+    if env:
+        return env
+    return os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build(reference_root: str = "", verbose: bool = False) -> str:
     """Compile the reference's own sources (unmodified, read in place) plus the harness."""
+    reference_root = reference_root or reference_checkout()
     root = os.path.join(reference_root, "kvtransfer")
     if not os.path.isdir(root):
         raise RuntimeError("no reference checkout to build the data path from")

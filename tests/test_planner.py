@@ -14,8 +14,9 @@ import subprocess
 
 import pytest
 
-REF = os.environ.get("LLUMNIX_KV_REFERENCE", "/root/reference")
 HERE = os.path.dirname(os.path.abspath(__file__))
+# the reference's sources: LLUMNIX_KV_REFERENCE, else a "reference" folder next to this repository's checkout
+REF = os.environ.get("LLUMNIX_KV_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 @pytest.fixture(scope="module")
