@@ -79,6 +79,16 @@ struct Layout {
   uint64_t total;
 };
 
+// Units that a descriptor of this length is split over: one per 8 KiB segment, at most kMaxSegs
+// (longer descriptors take further segments in later rounds).  The host's round count and the
+// kernel's layout both come from here.
+constexpr uint64_t kMaxSegs = 65536;
+__host__ __device__ __forceinline__ uint32_t segs_of(uint64_t len) {
+  if (len <= kSeg) return 1;
+  const uint64_t s = (len + kSeg - 1) / kSeg;
+  return (uint32_t)(s < kMaxSegs ? s : kMaxSegs);
+}
+
 __device__ __forceinline__ Layout make_layout(const KvtCopyMulti& p) {
   Layout l;
   l.total = 0;
@@ -87,7 +97,7 @@ __device__ __forceinline__ Layout make_layout(const KvtCopyMulti& p) {
     l.segs[t] = 1;
     if (t < p.n_tensors && p.count[t] > 0) {
       const uint64_t len0 = p.triples[3ull * p.first[t] + 2];
-      if (len0 > kSeg) l.segs[t] = (uint32_t)min((len0 + kSeg - 1) / kSeg, (uint64_t)65536);
+      l.segs[t] = segs_of(len0);
       l.total += (uint64_t)p.count[t] * l.segs[t];
     }
     l.ends[t] = l.total;
@@ -246,7 +256,8 @@ __global__ void __launch_bounds__(128) kvt_copy_blocks_bulk_kernel(const __grid_
 }  // namespace
 
 extern "C" uint32_t kvt_bulk_rounds(uint64_t first_len, uint64_t max_len) {
-  const uint64_t segs0 = first_len > kSeg ? (first_len + kSeg - 1) / kSeg : 1;
+  // rounds x segs_of(first_len) x 8 KiB covers the longest descriptor
+  const uint64_t segs0 = segs_of(first_len);
   const uint64_t segs_max = max_len > kSeg ? (max_len + kSeg - 1) / kSeg : 1;
   return (uint32_t)((segs_max + segs0 - 1) / segs0);
 }

@@ -290,11 +290,15 @@ int kvt_launch_copy_blocks_bulk(const KvtCopyMulti* args, uint32_t rounds, int g
 // allocator takes): the descriptor array and the status words live in a fixed array inside the
 // module's device image instead of memory the caller would have to allocate.  `host_triples`
 // is HOST memory (n × {src_off, dst_off, len} u64); it is copied to the device on `stream`.
+// When it is pinned memory the copy reads it when the stream reaches that point, not when the call
+// returns: leave it untouched until the stream has passed the call (pageable memory is staged
+// before the call returns).
 // `host_status` (optional, 2 × u32: code, detail) receives the status words after the kernel, on
 // `stream`; read it after synchronising the stream.  The call makes no allocation and frees
 // nothing.  The first call on a device (with that device current) also looks up and caches the
-// scratch address; make it before any stream capture begins.  One scratch array exists per
-// device: calls on one device that overlap in time race on it.
+// scratch address; make it before any stream capture begins.  First calls from several threads at
+// once are safe (each publishes the same cached values).  One scratch array exists per device:
+// calls on one device that overlap in time race on it.
 // Returns 0, a positive cudaError_t, or one of the negative codes below.
 #define KVT_NOALLOC_MAX_DESCS 4096u      /* descriptors per call; 96 KiB + 256 B of device image */
 #define KVT_NOALLOC_ERR_TOO_MANY (-1)    /* n > KVT_NOALLOC_MAX_DESCS: rejected, nothing launched */

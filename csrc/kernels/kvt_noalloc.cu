@@ -16,12 +16,20 @@
 //     KVT_NOALLOC_ERR_TOO_MANY and nothing is launched;
 //   * the first call on a device looks up the address of the scratch array
 //     (cudaGetSymbolAddress, with that device current) and caches it; make that first call
-//     before any stream capture begins;
+//     before any stream capture begins.  Threads that make their first calls at the same time
+//     each do the lookup and publish the same values (the address with release order, after the
+//     SM count), so none of them can see a half-filled entry;
+//   * host_triples is read by an async copy on the stream: in pinned memory it is read when the
+//     stream reaches the copy, so it must stay untouched until then (an event recorded after
+//     the call, or the status words' arrival, tells); pageable memory is staged before the call
+//     returns;
 //   * the status words are cleared on the stream before every launch;
 //   * there is ONE scratch array per device: two calls on the same device that overlap in time
 //     (different streams, or different threads) race on it.  Serialise them.
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+#include <atomic>
 
 #include "kvt_kernels.h"
 
@@ -35,8 +43,8 @@ constexpr int kMaxDevices = 64;
 static __device__ __align__(256) unsigned char g_scratch[kStatusWords * 4 + (size_t)kMaxDescs * 24];
 
 struct DevSlot {
-  unsigned char* ptr = nullptr;
-  int sms = 0;
+  std::atomic<unsigned char*> ptr{nullptr};   // published last: a reader that sees it also sees sms
+  std::atomic<int> sms{0};
 };
 DevSlot g_slots[kMaxDevices];
 
@@ -89,15 +97,15 @@ int device_slot(DevSlot** out) {
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= kMaxDevices) return KVT_NOALLOC_ERR_BAD_ARGS;
   DevSlot& s = g_slots[dev];
-  if (s.ptr == nullptr) {
+  if (s.ptr.load(std::memory_order_acquire) == nullptr) {
     unsigned char* p = nullptr;
     e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_scratch);
     if (e != cudaSuccess) return (int)e;
     int sms = 0;
     e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return (int)e;
-    s.sms = sms > 0 ? sms : 1;
-    s.ptr = p;
+    s.sms.store(sms > 0 ? sms : 1, std::memory_order_relaxed);
+    s.ptr.store(p, std::memory_order_release);
   }
   *out = &s;
   return 0;
@@ -114,23 +122,24 @@ extern "C" int kvt_copy_blocks_noalloc(uint64_t src_base, uint64_t dst_base, con
   const int rc = device_slot(&slot);
   if (rc != 0) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  cudaError_t e = cudaMemsetAsync(slot->ptr, 0, kStatusWords * 4, st);
+  unsigned char* const scratch = slot->ptr.load(std::memory_order_acquire);
+  cudaError_t e = cudaMemsetAsync(scratch, 0, kStatusWords * 4, st);
   if (e != cudaSuccess) return (int)e;
   if (n > 0) {
-    e = cudaMemcpyAsync(slot->ptr + kStatusWords * 4, host_triples, (size_t)n * 24, cudaMemcpyHostToDevice, st);
+    e = cudaMemcpyAsync(scratch + kStatusWords * 4, host_triples, (size_t)n * 24, cudaMemcpyHostToDevice, st);
     if (e != cudaSuccess) return (int)e;
     const uint32_t wpc = 256 / 32;
     uint32_t grid = (n + wpc - 1) / wpc;
-    const uint32_t cap = (uint32_t)slot->sms * 8u;
+    const uint32_t cap = (uint32_t)slot->sms.load(std::memory_order_relaxed) * 8u;
     if (grid > cap) grid = cap;
     kvt_copy_blocks_noalloc_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const char*>(src_base),
-                                                         reinterpret_cast<char*>(dst_base), slot->ptr, n, src_capacity,
+                                                         reinterpret_cast<char*>(dst_base), scratch, n, src_capacity,
                                                          dst_capacity);
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
   }
   if (host_status != nullptr) {
-    e = cudaMemcpyAsync(host_status, slot->ptr, 8, cudaMemcpyDeviceToHost, st);
+    e = cudaMemcpyAsync(host_status, scratch, 8, cudaMemcpyDeviceToHost, st);
     if (e != cudaSuccess) return (int)e;
   }
   return 0;

@@ -175,3 +175,19 @@ def test_log_line_format_and_level_filter():
         assert any(" E " in ln for ln in lines)
         if not want_info:
             assert not any(re.search(r":\d+ I ", ln) for ln in lines)
+
+
+def test_bulk_copy_round_count_covers_the_longest_descriptor(ops):
+    """rounds x units-per-descriptor x 8 KiB must reach the end of the longest descriptor; the
+    kernel splits a descriptor over at most 65536 units, so beyond 512 MiB the rounds grow."""
+    seg, max_segs = 8192, 65536
+
+    def segs(n):
+        return 1 if n <= seg else min(-(-n // seg), max_segs)
+
+    for first, longest in ((100, 100), (41984, 41984), (100, 3 * seg + 40), (1 << 30, 1 << 30),
+                           ((1 << 29) + 16, 3 << 30), (seg, (4 << 30) - 16), (5 << 20, 700 << 20)):
+        r = ops.kvt_bulk_rounds(first, longest)
+        assert r * segs(first) * seg >= longest, (first, longest, r)
+        assert r == 1 or (r - 1) * segs(first) * seg < longest, (first, longest, r)   # and no more than needed
+    assert ops.kvt_bulk_rounds(1 << 30, 1 << 30) == 2          # 131072 segments over 65536 units
