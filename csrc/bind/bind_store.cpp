@@ -73,6 +73,7 @@ void bind_store(py::module_& m) {
              s.unpin(k);
            })
       .def("reap_dead_writers", &KvStore::reap_dead_writers)
+      .def("reap_dead_readers", &KvStore::reap_dead_readers)
       .def("clear", &KvStore::clear)
       .def("advance_clock_for_test", &KvStore::advance_clock_for_test)
       .def("stats",

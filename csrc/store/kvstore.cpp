@@ -15,7 +15,7 @@
 namespace kvx {
 
 namespace {
-constexpr uint64_t kMagic = 0x4b5653544f524531ull;  // "KVSTORE1"
+constexpr uint64_t kMagic = 0x4b5653544f524532ull;  // "KVSTORE2"
 constexpr uint32_t kEmpty = 0, kWriting = 1, kSealed = 2;
 constexpr uint64_t kPage = 4096;
 
@@ -38,14 +38,20 @@ struct KvStore::Header {
   uint64_t hits, misses, evictions, expired, reserve_fail, discards;
 };
 
+constexpr uint32_t kPinOwners = 4;
+
 struct KvStore::Entry {
   uint64_t hi, lo;
   uint32_t slot;
   uint32_t state;
-  uint32_t pins;
+  uint32_t pins;       // all pins on the entry, whoever holds them
   uint32_t owner_pid;
   int64_t expire_ns;  // 0 = never
   uint64_t last_use;
+  // Who holds the pins, so that a reader that died can be released: up to kPinOwners processes
+  // are tracked per entry; pins of further processes count in `pins` only and stay until unpinned.
+  uint32_t pin_pid[kPinOwners];
+  uint32_t pin_cnt[kPinOwners];
 };
 
 // Takes the process-shared mutex; a holder that died leaves it recoverable (robust mutex).
@@ -280,6 +286,8 @@ ReserveResult KvStore::reserve(const StoreKey& key, int64_t ttl_ms, uint32_t* sl
   e->slot = free_[--hdr_->n_free];
   e->state = kWriting;
   e->pins = 0;
+  memset(e->pin_pid, 0, sizeof(e->pin_pid));
+  memset(e->pin_cnt, 0, sizeof(e->pin_cnt));
   e->owner_pid = (uint32_t)getpid();
   e->expire_ns = ttl_ms > 0 ? now + ttl_ms * 1000000 : 0;
   e->last_use = ++hdr_->clock;
@@ -311,12 +319,27 @@ bool KvStore::discard(const StoreKey& key) {
 std::vector<uint32_t> KvStore::pin_prefix(const std::vector<StoreKey>& keys) {
   Guard g(hdr_);
   const int64_t now = now_ns();
+  const uint32_t me = (uint32_t)getpid();
   std::vector<uint32_t> out;
   for (const StoreKey& k : keys) {
     Entry* e = find(k, false);
     if (e == nullptr || e->state != kSealed) break;
     if (e->expire_ns != 0 && e->expire_ns <= now && e->pins == 0) break;
     e->pins++;
+    for (uint32_t r = 0, spare = kPinOwners; r <= kPinOwners; ++r) {
+      if (r == kPinOwners) {     // not yet listed: take a spare record if there is one
+        if (spare < kPinOwners) {
+          e->pin_pid[spare] = me;
+          e->pin_cnt[spare] = 1;
+        }
+        break;
+      }
+      if (e->pin_cnt[r] != 0 && e->pin_pid[r] == me) {
+        e->pin_cnt[r]++;
+        break;
+      }
+      if (e->pin_cnt[r] == 0 && spare == kPinOwners) spare = r;
+    }
     e->last_use = ++hdr_->clock;
     out.push_back(e->slot);
   }
@@ -325,10 +348,37 @@ std::vector<uint32_t> KvStore::pin_prefix(const std::vector<StoreKey>& keys) {
 
 void KvStore::unpin(const std::vector<StoreKey>& keys) {
   Guard g(hdr_);
+  const uint32_t me = (uint32_t)getpid();
   for (const StoreKey& k : keys) {
     Entry* e = find(k, false);
-    if (e != nullptr && e->state == kSealed && e->pins > 0) e->pins--;
+    if (e == nullptr || e->state != kSealed || e->pins == 0) continue;
+    e->pins--;
+    for (uint32_t r = 0; r < kPinOwners; ++r) {
+      if (e->pin_cnt[r] != 0 && e->pin_pid[r] == me) {
+        e->pin_cnt[r]--;
+        break;
+      }
+    }
   }
+}
+
+uint32_t KvStore::reap_dead_readers() {
+  Guard g(hdr_);
+  uint32_t n = 0;
+  for (uint32_t i = 0; i < hdr_->table_cap; ++i) {
+    Entry* e = &table_[i];
+    if (e->state != kSealed || e->pins == 0) continue;
+    for (uint32_t r = 0; r < kPinOwners; ++r) {
+      if (e->pin_cnt[r] == 0 || e->pin_pid[r] == (uint32_t)getpid()) continue;
+      if (kill((pid_t)e->pin_pid[r], 0) != 0 && errno == ESRCH) {
+        const uint32_t c = e->pin_cnt[r] < e->pins ? e->pin_cnt[r] : e->pins;
+        e->pins -= c;
+        e->pin_cnt[r] = 0;
+        n += c;
+      }
+    }
+  }
+  return n;
 }
 
 uint32_t KvStore::reap_dead_writers() {
@@ -347,12 +397,28 @@ uint32_t KvStore::reap_dead_writers() {
   return n;
 }
 
-void KvStore::clear() {
+uint32_t KvStore::clear() {
   Guard g(hdr_);
-  memset(table_, 0, (size_t)hdr_->table_cap * sizeof(Entry));
-  for (uint32_t i = 0; i < hdr_->n_slots; ++i) free_[i] = hdr_->n_slots - 1 - i;
-  hdr_->n_free = hdr_->n_slots;
-  hdr_->n_entries = 0;
+  uint32_t kept = 0;
+  for (uint32_t i = 0; i < hdr_->table_cap; ++i)
+    if (table_[i].state == kSealed && table_[i].pins != 0) ++kept;
+  if (kept == 0) {
+    memset(table_, 0, (size_t)hdr_->table_cap * sizeof(Entry));
+    for (uint32_t i = 0; i < hdr_->n_slots; ++i) free_[i] = hdr_->n_slots - 1 - i;
+    hdr_->n_free = hdr_->n_slots;
+    hdr_->n_entries = 0;
+    return 0;
+  }
+  // a reader is still copying out of a pinned slot: drop everything else, entry by entry
+  for (uint32_t i = 0; i < hdr_->table_cap;) {
+    Entry* e = &table_[i];
+    if (e->state != kEmpty && !(e->state == kSealed && e->pins != 0)) {
+      free_entry(e);  // may shift another entry into bucket i: look at i again
+      continue;
+    }
+    ++i;
+  }
+  return kept;
 }
 
 StoreStats KvStore::stats() {

@@ -65,7 +65,11 @@ class KvStore {
   void unpin(const std::vector<StoreKey>& keys);
   // Drops WRITING entries whose writer process no longer exists; returns how many.
   uint32_t reap_dead_writers();
-  void clear();
+  // Releases the pins of reader processes that no longer exist (a reader that died between
+  // pin_prefix and unpin would otherwise make its slots unevictable); returns how many pins.
+  uint32_t reap_dead_readers();
+  // Drops every entry that no reader has pinned; returns how many pinned entries stayed.
+  uint32_t clear();
 
   StoreStats stats();
   uint8_t* data() const { return data_; }

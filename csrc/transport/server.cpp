@@ -17,10 +17,12 @@
 #include <poll.h>
 #include <sys/mman.h>
 #include <sys/socket.h>
+#include <sys/stat.h>
 #include <unistd.h>
 
 #include <atomic>
 #include <map>
+#include <memory>
 #include <mutex>
 #include <thread>
 
@@ -89,14 +91,14 @@ class TransferServer : public ITransferServer {
     if (listen_fd_.valid()) ::shutdown(listen_fd_.fd(), SHUT_RDWR);
     if (accept_thd_.joinable()) accept_thd_.join();
     listen_fd_.reset();
-    std::vector<std::thread> thds;
+    std::vector<ConnThread> thds;
     {
       std::lock_guard<std::mutex> g(mu_);
       for (auto& kv : conns_) ::shutdown(kv.first, SHUT_RDWR);
       thds.swap(conn_thds_);
     }
     for (auto& t : thds)
-      if (t.joinable()) t.join();
+      if (t.thd.joinable()) t.thd.join();
   }
 
  private:
@@ -110,10 +112,40 @@ class TransferServer : public ITransferServer {
       // replies are small and latency-bound: without this, Nagle + delayed ACK add ~40 ms per layer
       int one = 1;
       setsockopt(cfd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
-      std::lock_guard<std::mutex> g(mu_);
-      conns_[cfd] = true;
-      conn_thds_.emplace_back([this, cfd] { serve(cfd); });
+      std::vector<std::thread> ended;
+      {
+        std::lock_guard<std::mutex> g(mu_);
+        // connections come and go over a long run: join the threads of those that ended
+        for (auto it = conn_thds_.begin(); it != conn_thds_.end();) {
+          if (it->done->load(std::memory_order_acquire)) {
+            ended.push_back(std::move(it->thd));
+            it = conn_thds_.erase(it);
+          } else {
+            ++it;
+          }
+        }
+        conns_[cfd] = true;
+        auto done = std::make_shared<std::atomic<bool>>(false);
+        conn_thds_.push_back(ConnThread{std::thread([this, cfd, done] {
+                                          serve(cfd);
+                                          done->store(true, std::memory_order_release);
+                                        }),
+                                        done});
+      }
+      for (auto& t : ended)
+        if (t.joinable()) t.join();
     }
+  }
+
+  // The longest frame a well-behaved peer sends: one layer's data for every tensor, plus its block
+  // metadata (which a sender keeps far below the data it describes) and the headers.
+  size_t frame_limit() const {
+    size_t cap = 0;
+    const auto& addrs = ctx_->layer_data_address();
+    const size_t n_tensors = addrs.empty() ? 0 : addrs[0].size();
+    for (size_t t = 0; t < n_tensors; ++t) cap += ctx_->tensor_capacity(t);
+    const size_t lim = 2 * cap + (size_t{1} << 20);
+    return std::min<size_t>(lim, 0xffffffffu);
   }
 
   void serve(int cfd) {
@@ -125,12 +157,17 @@ class TransferServer : public ITransferServer {
     // a pull session answers finished batches from the completion thread: every write to this connection is locked
     auto write_mu = std::make_shared<std::mutex>();
     std::shared_ptr<PullSession> pull;
+    const size_t frame_max = frame_limit();
     try {
       if (gpu) stage = std::make_unique<DeviceStage>(ctx_->device_id());
       for (;;) {
         uint32_t n = 0;
         // Idle connections block here; stop() shuts the socket down to wake them.
         if (read_full(cfd, &n, 4, 0) != 4) break;
+        if (n > frame_max) {      // nothing is pinned or read for a length no sender of ours produces
+          LOG(ERROR) << "KVT server: frame of " << n << " bytes exceeds the limit of " << frame_max << ", closing";
+          break;
+        }
         char* buf = rx.reserve(n, gpu);
         if (n > 0 && read_full(cfd, buf, n, env_rpc_timeout_s() * 1000) != static_cast<ssize_t>(n)) break;
         if (n < 4) break;
@@ -291,6 +328,13 @@ class TransferServer : public ITransferServer {
         take(p, end, &bytes);
         shm.reset();
         int sfd = shm_open(name.c_str(), O_RDWR, 0600);
+        struct stat st {};
+        if (sfd >= 0 && (fstat(sfd, &st) != 0 || bytes == 0 || bytes > static_cast<uint64_t>(st.st_size))) {
+          // a mapping longer than the segment would fault on first touch
+          LOG(ERROR) << "KVT server: shm attach of " << bytes << " bytes refused, segment has " << st.st_size;
+          ::close(sfd);
+          sfd = -1;
+        }
         if (sfd >= 0) {
           void* m = mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED, sfd, 0);
           ::close(sfd);
@@ -366,7 +410,11 @@ class TransferServer : public ITransferServer {
   std::thread accept_thd_;
   std::mutex mu_;
   std::map<int, bool> conns_;
-  std::vector<std::thread> conn_thds_;
+  struct ConnThread {
+    std::thread thd;
+    std::shared_ptr<std::atomic<bool>> done;   // set by the thread as its last act
+  };
+  std::vector<ConnThread> conn_thds_;
   std::mutex handle_mu_;
   std::vector<PeerTensor> handle_cache_;
 };

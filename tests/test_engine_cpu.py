@@ -565,3 +565,36 @@ def test_staged_transfer_casts_bf16_to_fp8_for_a_smaller_decode_tp(proto, ops, s
         srv.stop()
         monkeypatch.delenv("BLLM_KVTRANS_BF162FP8_CONV")
         ops.envcfg_reset_for_test()
+
+
+def test_server_refuses_oversized_frames_and_oversized_shm_attach(ops):
+    """A peer that announces a frame no sender of ours produces is dropped before anything is read or
+    pinned for it; a shared-memory attach larger than the segment is refused; the server stays up."""
+    import socket
+    from multiprocessing import shared_memory
+
+    dst = make_cache()
+    srv = KVTransferServer("D|0|1", 1, 0, 0, BLK, TOK, "fake://", dst, [PT.TCP], num_kv_heads=H, cache_shape=2)
+    port = int(ops.WorkerInfo.from_string(srv.worker_info()).ext["port"])
+
+    def rpc(sock, magic, body=b""):
+        msg = struct.pack("=IQ", magic, 7) + body
+        sock.sendall(struct.pack("=I", len(msg)) + msg)
+        n = struct.unpack("=I", sock.recv(4, socket.MSG_WAITALL))[0]
+        return sock.recv(n, socket.MSG_WAITALL)
+
+    seg = shared_memory.SharedMemory(create=True, size=8192)
+    try:
+        with socket.create_connection(("127.0.0.1", port), timeout=10) as c:
+            c.sendall(struct.pack("=I", 0xFFFFFF00))
+            assert c.recv(4) == b""                               # closed, nothing allocated for 4 GiB
+        with socket.create_connection(("127.0.0.1", port), timeout=10) as c:
+            assert struct.unpack("=I", rpc(c, 0x4B565069)[12:16])[0] == 0          # ping still answered
+            name = ("/" + seg.name.lstrip("/")).encode()
+            attach = struct.pack("=I", len(name)) + name
+            assert struct.unpack("=I", rpc(c, 0x4B565341, attach + struct.pack("=Q", 1 << 30))[12:16])[0] == 400
+            assert struct.unpack("=I", rpc(c, 0x4B565341, attach + struct.pack("=Q", 8192))[12:16])[0] == 0
+    finally:
+        seg.close()
+        seg.unlink()
+        srv.stop()

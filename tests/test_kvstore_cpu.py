@@ -167,3 +167,31 @@ def test_cpu_round_trip_across_layouts(shape):
         a.close()
         b.close()
         load_ops().KvStore.unlink(name)
+
+
+def _child_reader(name, q):
+    K = load_ops()
+    s = K.KvStore.open(name, 4096, 8, False, "t")
+    q.put(s.pin_prefix(k(0) + k(1)))          # exits holding both pins
+
+
+def test_pins_of_a_dead_reader_are_released_and_clear_keeps_pinned_slots(store):
+    K, s, name = store
+    for i in range(4):
+        s.reserve(k(i))
+        s.seal(k(i))
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_child_reader, args=(name, q))
+    p.start()
+    assert q.get(timeout=60) == [0, 1]
+    p.join(30)
+    assert s.pin_prefix(k(1)) == [1]                             # our own pin on top of the dead reader's
+    assert not s.discard(k(0)) and s.stats()["pinned"] == 2
+    assert s.reap_dead_readers() == 2                            # the child's two pins, not ours
+    assert s.discard(k(0)) and not s.discard(k(1))
+    assert s.clear() == 1                                        # entry 1 is being read: it stays
+    assert s.lookup_prefix(k(1)) == 1 and s.lookup_prefix(k(2)) == 0 and s.stats()["used"] == 1
+    assert s.reserve(k(2))[0] == K.STORE_RESERVE_NEW             # freed slots are usable again
+    s.unpin(k(1))
+    assert s.reap_dead_readers() == 0 and s.clear() == 0 and s.stats()["used"] == 0
