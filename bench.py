@@ -151,6 +151,7 @@ def main():
     import torch.distributed as dist
 
     import llumnix_kv_b200
+    from benchmarks import hostsync as HS
     from benchmarks.support import PDBenchPair
 
     K = llumnix_kv_b200.load_ops()
@@ -163,6 +164,7 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
+        HS.init()      # barriers and small exchanges go over the host: no rank waits inside a NCCL kernel
 
     if args.small:
         args.tokens, args.slots, args.layers = 2048, 2, 4
@@ -209,7 +211,7 @@ def main():
                      if args.mode == "gdn" else "deepseek-v3.2-like MLA (latent+rope 656 B/token, indexer 132 B/token, 64-token blocks)")
             print(json.dumps({"metric": "hybrid_state_transfer_GBps", "unit": "GB/s", "n_gpus": args.gpus,
                               "higher_is_better": True, "config": {"model": model, "seq_len": res["tokens"],
-                                                                   "api": "KVTransferClient (engine, NVLINK transport, descriptor path)"},
+                                                                   "api": "KVTransferClient (engine, NVLINK transport: the walk kernel expands the planner's affine rules on the device)"},
                               "result": res}))
         if world > 1:
             dist.destroy_process_group()
@@ -239,7 +241,7 @@ def main():
 
             t = _t.tensor([res["colocated_ms_p50"], res["disagg_ms_p50"], res["colocated_ms_p99"], res["disagg_ms_p99"]],
                           dtype=_t.float64, device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)      # slowest prefill rank
+            HS.all_reduce(t, op=dist.ReduceOp.MAX)      # slowest prefill rank
             res.update(colocated_ms_p50=float(t[0]), disagg_ms_p50=float(t[1]), colocated_ms_p99=float(t[2]),
                        disagg_ms_p99=float(t[3]))
             res["added_ttft_p50_pct"] = round(100.0 * (float(t[1]) - float(t[0])) / float(t[0]), 2)

@@ -22,6 +22,7 @@ import torch
 from llumnix_kv_b200.ops.layouts import AttnLayout, CacheShape
 from llumnix_kv_b200.ops.p2d_attn import AttnTransfer, ReqChunk
 
+from . import hostsync as HS
 from .support import BLOCK, HEAD_DIM, KV_HEADS, PDBenchPair
 
 
@@ -40,7 +41,7 @@ def timed_reps(run_step: Callable[[int], None], steps: int, warmup: int, stream,
 
     def barrier():
         if world > 1:
-            dist.barrier()
+            HS.barrier()
         torch.cuda.synchronize()
 
     for i in range(warmup):
@@ -65,7 +66,7 @@ def timed_reps(run_step: Callable[[int], None], steps: int, warmup: int, stream,
         ms = ev0.elapsed_time(ev1) if measures else 0.0
         if world > 1:
             t = torch.tensor([ms], dtype=torch.float64, device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            HS.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
         barrier()
         regions.append(ms)
@@ -120,7 +121,7 @@ def measure_ceilings(pair: PDBenchPair, nbytes: int = 1 << 30, host_bytes: int =
         s.synchronize()
     t = torch.tensor([ms, hms_h2d, hms_d2h], dtype=torch.float64, device=dev)
     if world > 1:
-        _dist().all_reduce(t, op=_dist().ReduceOp.MAX)
+        HS.all_reduce(t, op=_dist().ReduceOp.MAX)
     ms, hms_h2d, hms_d2h = (float(x) for x in t)
     gbs = lambda b, m: round(b / m / 1e6, 1) if m > 0 else None
     if world > 1:
@@ -267,7 +268,7 @@ def link_probe(pair: PDBenchPair, seconds_per_case: float = 0.25) -> List[dict]:
             for i in range(3):
                 one_step(i)
         if pair.world > 1:
-            dist.barrier()
+            HS.barrier()
         torch.cuda.synchronize()
         if pair.is_sender:
             i = 3
@@ -286,7 +287,7 @@ def link_probe(pair: PDBenchPair, seconds_per_case: float = 0.25) -> List[dict]:
         per_step = ms_total / max(n_steps, 1)
         t = torch.tensor([per_step], dtype=torch.float64, device=dev)
         if pair.world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            HS.all_reduce(t, op=dist.ReduceOp.MAX)
         per_step = float(t.item())
         rows.append({"tile_order": "heads outermost" if order else "tokens outermost",
                      "store": "linear bulk" if form else "tensor", "stages": stages or "auto", "ctas": grid,
@@ -317,7 +318,7 @@ def link_probe(pair: PDBenchPair, seconds_per_case: float = 0.25) -> List[dict]:
             if pair.is_receiver:
                 for i in range(3):
                     pull_step(i)
-            dist.barrier()
+            HS.barrier()
             torch.cuda.synchronize()
             if pair.is_receiver:
                 i = 3
@@ -333,7 +334,7 @@ def link_probe(pair: PDBenchPair, seconds_per_case: float = 0.25) -> List[dict]:
                     n_steps += 10
                 assert pull.check_status() == (0, 0)
             t = torch.tensor([ms_total / max(n_steps, 1)], dtype=torch.float64, device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            HS.all_reduce(t, op=dist.ReduceOp.MAX)
             per_step = float(t.item())
             rows.append({"tile_order": "heads outermost", "store": "PULL: TMA loads from the peer, linear local store",
                          "stages": stages or "auto", "ctas": grid, "l2_evict_first": False, "ms_per_step": round(per_step, 4),

@@ -16,6 +16,7 @@ from typing import List
 
 import torch
 
+from . import hostsync as HS
 from llumnix_kv_b200.ops.layouts import AttnLayout, CacheShape
 from llumnix_kv_b200.ops.p2d_attn import AttnTransfer, ReqChunk
 
@@ -91,7 +92,7 @@ class PDBenchPair:
                 h2, base2, _size2 = K.kvt_ipc_get_handle(self.probe.data_ptr())
                 mine = (h, self.dst.data_ptr() - base, h2, self.probe.data_ptr() - base2)
             infos = [None] * world
-            dist.all_gather_object(infos, mine)
+            HS.all_gather_object(infos, mine)
             if self.is_sender:
                 h, off, h2, off2 = infos[rank + self.n_pairs]
                 self.peer_base = K.kvt_ipc_open_handle(h)
@@ -133,7 +134,7 @@ class PDBenchPair:
             h, base, _size = self.K.kvt_ipc_get_handle(self.src.data_ptr())
             mine = (h, self.src.data_ptr() - base)
         infos = [None] * self.world
-        dist.all_gather_object(infos, mine)
+        HS.all_gather_object(infos, mine)
         if self.is_receiver:
             h, off = infos[self.rank - self.n_pairs]
             base = self.K.kvt_ipc_open_handle(h)
@@ -263,7 +264,7 @@ class PDBenchPair:
             import torch.distributed as dist
 
             infos = [None] * self.world
-            dist.all_gather_object(infos, winfo)
+            HS.all_gather_object(infos, winfo)
             if self.is_sender:
                 winfo = infos[self.rank + self.n_pairs]
         self.winfo = winfo
@@ -306,8 +307,12 @@ class PDBenchPair:
 
     def finish_engine(self) -> None:
         """End of a timed region: every step's completion record has been read."""
-        if getattr(self, "cli", None) is not None and not self.cli.wait_inflight(0, 30.0):
+        if getattr(self, "cli", None) is None:
+            return
+        if not self.cli.wait_inflight(0, 30.0):
             raise RuntimeError("transfer steps did not complete in 30 s")
+        if self.cli.failed_batches():
+            raise RuntimeError(f"{self.cli.failed_batches()} transfer steps failed: a timing that includes them means nothing")
 
     def close_engine(self) -> None:
         if getattr(self, "srv", None) is not None:
@@ -323,13 +328,13 @@ class PDBenchPair:
         if self.world > 1:
             import torch.distributed as dist
 
-            dist.barrier()
+            HS.barrier()
         touched = sorted(self.touched)
         if self.world > 1:
             import torch.distributed as dist
 
             got = [None] * self.world
-            dist.all_gather_object(got, touched)
+            HS.all_gather_object(got, touched)
             touched = got[self.rank - self.n_pairs] if self.rank >= self.n_pairs else touched
         if not self.is_receiver:
             return 0
@@ -378,7 +383,7 @@ class PDBenchPair:
             import torch.distributed as dist
 
             t = torch.tensor([n if self.is_receiver else 1 << 30], dtype=torch.int64, device=self.dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+            HS.all_reduce(t, op=dist.ReduceOp.MIN)
             n = int(t.item())
         return n
 
@@ -522,7 +527,7 @@ def ttft_added(K, rank: int, world: int, dev, tokens: int = 8192, iters: int = 3
         import torch.distributed as dist
 
         infos = [None] * world
-        dist.all_gather_object(infos, winfo)
+        HS.all_gather_object(infos, winfo)
         if sender:
             winfo = infos[rank + n_pairs]
     colo, disagg = [], []
@@ -569,7 +574,7 @@ def ttft_added(K, rank: int, world: int, dev, tokens: int = 8192, iters: int = 3
     if world > 1:
         import torch.distributed as dist
 
-        dist.barrier()
+        HS.barrier()
     ok = True
     if world == 1 and sender:
         # the decode cache must hold what the prefill cache holds, layer 0 and last, all full blocks
@@ -768,7 +773,7 @@ def hybrid_state_bandwidth(K, rank: int, world: int, dev, which: str = "gdn", to
         import torch.distributed as dist
 
         infos = [None] * world
-        dist.all_gather_object(infos, winfo)
+        HS.all_gather_object(infos, winfo)
         if sender:
             winfo = infos[rank + n_pairs]
     ms = ms_sync = 0.0
@@ -808,6 +813,7 @@ def hybrid_state_bandwidth(K, rank: int, world: int, dev, which: str = "gdn", to
             assert cli.wait_inflight(0, 30.0)
             e1.record(stream)
             torch.cuda.synchronize()
+            assert cli.failed_batches() == 0, "transfer steps failed: a timing that includes them means nothing"
             return e0.elapsed_time(e1)
 
         ms_sync = timed(0, 0)                 # every step waits for its own completion before the next is submitted
@@ -821,11 +827,11 @@ def hybrid_state_bandwidth(K, rank: int, world: int, dev, which: str = "gdn", to
         import torch.distributed as dist
 
         got = [None] * world
-        dist.all_gather_object(got, sample)
+        HS.all_gather_object(got, sample)
         if receiver:
             sample = got[rank - n_pairs]
         torch.cuda.synchronize()
-        dist.barrier()
+        HS.barrier()
     if receiver:
         ref = src if world == 1 else alloc(True)
         for layer in (0, n_layers - 1):
@@ -837,9 +843,9 @@ def hybrid_state_bandwidth(K, rank: int, world: int, dev, which: str = "gdn", to
         import torch.distributed as dist
 
         t = torch.tensor([ms, float(moved), 0.0 if ok else 1.0, ms_sync], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        HS.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, moved, ok, ms_sync = float(t[0]), int(t[1]), float(t[2]) == 0.0, float(t[3])
-        dist.barrier()
+        HS.barrier()
     if srv is not None:
         srv.stop()
     gbps = n_pairs * moved * steps / (ms * 1e-3) / 1e9 if ms > 0 else 0.0
@@ -878,7 +884,7 @@ def quant_reshard_nvlink(K, rank: int, world: int, dev, tokens: int = 8192, n_la
         h, base, _size = K.kvt_ipc_get_handle(dst.data_ptr())
         mine = (h, dst.data_ptr() - base)
     infos = [None] * world
-    dist.all_gather_object(infos, mine)
+    HS.all_gather_object(infos, mine)
     ms_host = ms_graph = 0.0
     src = None
     if sender:
@@ -912,12 +918,12 @@ def quant_reshard_nvlink(K, rank: int, world: int, dev, tokens: int = 8192, n_la
             issue()
         holder["main"] = keep
         torch.cuda.synchronize()
-    dist.barrier()
+    HS.barrier()
 
     def timed(fn):
         best = 1e30
         for _ in range(iters):
-            dist.barrier()
+            HS.barrier()
             torch.cuda.synchronize()
             ms = 0.0
             if sender:
@@ -928,7 +934,7 @@ def quant_reshard_nvlink(K, rank: int, world: int, dev, tokens: int = 8192, n_la
                 torch.cuda.synchronize()
                 ms = e0.elapsed_time(e1)
             t = torch.tensor([ms], dtype=torch.float64, device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            HS.all_reduce(t, op=dist.ReduceOp.MAX)
             best = min(best, float(t.item()))
         return best
 
@@ -937,7 +943,7 @@ def quant_reshard_nvlink(K, rank: int, world: int, dev, tokens: int = 8192, n_la
     ok = True
     if sender:
         ok = xfer.check_status() == (0, 0)
-    dist.barrier()
+    HS.barrier()
     if receiver:
         # regenerate what both feeding prefill ranks hold for layer 0 and compare codes and scales
         for j in range(2):
@@ -953,7 +959,7 @@ def quant_reshard_nvlink(K, rank: int, world: int, dev, tokens: int = 8192, n_la
             got_e = dst_l.scale_view(layer0)[torch.tensor(db[:nb], device=dev)][:, :, :, 2 * j:2 * j + 2]
             ok = ok and bool(torch.equal(got_c, codes)) and bool(torch.equal(got_e, exps))
     t = torch.tensor([1.0 if ok else 0.0], device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    HS.all_reduce(t, op=dist.ReduceOp.MIN)
     src_bytes = tokens * 2 * 2 * HEAD_DIM * 2 * n_layers
     link_bytes = tokens * dst_l.token_bytes // 2 * n_layers
     return {"prefill_ranks": n_p, "decode_ranks": n_d, "src_bytes_per_rank": src_bytes, "link_bytes_per_rank": link_bytes,
@@ -1035,7 +1041,7 @@ def mla_fanout_bandwidth(K, rank: int, world: int, dev, tokens: int = 32768, n_l
             h, base, _size = K.kvt_ipc_get_handle(t.data_ptr())
             mine[name] = (h, t.data_ptr() - base)
     infos = [None] * world
-    dist.all_gather_object(infos, mine)
+    HS.all_gather_object(infos, mine)
     torch.cuda.synchronize()
 
     main = torch.cuda.current_stream(dev)
@@ -1155,7 +1161,7 @@ def mla_fanout_bandwidth(K, rank: int, world: int, dev, tokens: int = 32768, n_l
     def timed(fn, first_step: int) -> float:
         best = 1e30
         for it in range(warmup + iters):
-            dist.barrier()
+            HS.barrier()
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
@@ -1166,7 +1172,7 @@ def mla_fanout_bandwidth(K, rank: int, world: int, dev, tokens: int = 32768, n_l
             e1.record()
             torch.cuda.synchronize()
             t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            HS.all_reduce(t, op=dist.ReduceOp.MAX)
             if it >= warmup:
                 best = min(best, float(t.item()))
         return best
@@ -1201,10 +1207,10 @@ def mla_fanout_bandwidth(K, rank: int, world: int, dev, tokens: int = 32768, n_l
     except Exception as ex:   # every rank still takes part in the collective teardown below
         errors.append(f"rank {rank}: {type(ex).__name__}: {ex}")
     all_errors = [None] * world
-    dist.all_gather_object(all_errors, errors)
+    HS.all_gather_object(all_errors, errors)
     if cache is not None:
         cache.close()
-    dist.barrier()
+    HS.barrier()
     bytes_per_copy = n_layers * n_blk * blk
     n_d = world - 1
     flat = [e for es in all_errors for e in es]
@@ -1250,7 +1256,7 @@ def post_checks(K, rank: int, world: int, dev) -> dict:
                                num_kv_heads=8, cache_shape=5, mx_scaled=True)
         winfo = srv.worker_info()
     infos = [None] * world
-    dist.all_gather_object(infos, winfo)
+    HS.all_gather_object(infos, winfo)
     if sender:
         src = [src_l.alloc(dev, "normal", seed=4000 + 10 * pair + i) for i in range(n_layers)]
         cli = KVTransferClient(f"QP{pair}|0|4", 4, 1, 1, src_l.block_bytes, src_l.token_bytes, "fake://", src, [PT.NVLINK],
@@ -1263,7 +1269,7 @@ def post_checks(K, rank: int, world: int, dev) -> dict:
         cli.flush_send_step()
         cli.drain()
     torch.cuda.synchronize()
-    dist.barrier()
+    HS.barrier()
     ok = True
     if receiver:
         chunks = [ReqChunk(sb, db, 0, t) for _, sb, db, t in reqs]
@@ -1274,7 +1280,7 @@ def post_checks(K, rank: int, world: int, dev) -> dict:
             ok = ok and bool(torch.equal(dst[i], expect))
         srv.stop()
     t = torch.tensor([0.0 if ok else 1.0], device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    HS.all_reduce(t, op=dist.ReduceOp.MAX)
     out["tp4_to_tp2_mxfp8_through_engine"] = bool(t.item() == 0.0)
     for which in ("gdn", "mla"):
         res = hybrid_state_bandwidth(K, rank, world, dev, which=which, tokens=2048, steps=1, warmup=1, small=True)

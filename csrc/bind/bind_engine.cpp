@@ -425,6 +425,7 @@ void bind_engine(py::module_& m) {
            "Wait until at most max_batches batches are still in flight; False when the timeout ran out.")
       .def("inflight", [](KvClient& c) { return c.get()->context()->inflight().inflight(); })
       .def("finished_batches", [](KvClient& c) { return c.get()->context()->inflight().finished(); })
+      .def("failed_batches", [](KvClient& c) { return c.get()->context()->inflight().failed(); })
       .def("target_size", [](KvClient& c) { return c.get()->target_size(); })
       .def("target_try_shrink", [](KvClient& c, size_t cap) { c.get()->target_try_shrink(cap); },
            py::call_guard<py::gil_scoped_release>())

@@ -76,7 +76,7 @@ void KvTransferClient::TargetMgr::do_submit(std::shared_ptr<Step>& step, StepTas
       } catch (const std::exception& ex) {
         LOG(ERROR) << "TargetMgr: cannot create stub for " << inst << "," << wid << ": " << ex.what();
         for (const auto& t : batch.tasks) t.set_state(ReqState::FAILED);
-        if (batch.inflight != nullptr) batch.inflight->done();
+        if (batch.inflight != nullptr) batch.inflight->done(false);
         continue;
       }
       if (target->inflycnt.fetch_add(1, std::memory_order_acquire) == 0) target->thread_hint = ++next_hint_;

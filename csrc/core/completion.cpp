@@ -113,7 +113,8 @@ void CompletionPoller::run() {
   }
 }
 
-void InflightCounter::done() {
+void InflightCounter::done(bool ok) {
+  if (!ok) failed_.fetch_add(1, std::memory_order_release);
   done_.fetch_add(1, std::memory_order_release);
   std::lock_guard<std::mutex> g(mu_);
   cv_.notify_all();

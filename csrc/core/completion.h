@@ -53,14 +53,15 @@ class CompletionPoller {
 class InflightCounter {
  public:
   void add(uint64_t n) { submitted_.fetch_add(n, std::memory_order_relaxed); }
-  void done();
+  void done(bool ok = true);
   uint64_t inflight() const;
   uint64_t finished() const { return done_.load(std::memory_order_acquire); }
+  uint64_t failed() const { return failed_.load(std::memory_order_acquire); }   // finished batches that did not arrive
   // Waits until at most `max_inflight` batches are outstanding; false when the timeout ran out.
   bool wait_at_most(uint64_t max_inflight, std::chrono::milliseconds timeout);
 
  private:
-  std::atomic<uint64_t> submitted_{0}, done_{0};
+  std::atomic<uint64_t> submitted_{0}, done_{0}, failed_{0};
   std::mutex mu_;
   std::condition_variable cv_;
 };

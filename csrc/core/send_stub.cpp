@@ -243,7 +243,7 @@ struct KvSendStub::Impl {
               << pb.flush_out << ",QueueUs=" << pb.queue_us << ",PlanUs=" << pb.plan_us << ",WaitUs=" << pb.wait_us
               << ",EnqueueUs=" << elapse_us(pb.iter_start, pb.enqueued) << ",WaitAndSendUs=" << wait_and_send_us
               << ",SendNotifyUs=" << send_notify_us << ",SendFinishTs=" << send_finish.time_since_epoch().count();
-    if (batch.inflight != nullptr) batch.inflight->done();
+    if (batch.inflight != nullptr) batch.inflight->done(ok);
   }
 
   void do_task(std::shared_ptr<PendingBatch> pbp) noexcept {

@@ -274,31 +274,23 @@ class HybridScheduler:
         if state is not None:
             self._track_extra_kv_blocks("save", reqid, state.kvblks)
 
-    def _source_done_for_all_workers(self, worker_signals: dict, source: str) -> bool:
-        return all(any(s.source == source for s in worker_signals.get(r, [])) for r in range(self._tp_size()))
-
-    @staticmethod
-    def _source_failed(worker_signals: dict, source: str) -> bool:
-        return any(s.source == source and s.n is not None and s.n == 0 for sigs in worker_signals.values() for s in sigs)
-
     def _mark_save_source_done_time(self, state: _SavingReq, ioret: IoRet) -> None:
-        # called by try_advance with state._signals_lock held
+        """Runs under the ledger's lock after each accepted signal: stamps a backend's save as done
+        once every rank has reported it."""
         src = ioret.source
-        if src is None or src in state.source_done_times:
-            return
-        if not self._source_done_for_all_workers(state._worker_signals, src):
+        if src is None or src in state.source_done_times or state.ranks_reporting(src) < self._tp_size():
             return
         state.source_done_times[src] = time.monotonic()
-        state.source_failed[src] = self._source_failed(state._worker_signals, src)
+        state.source_failed[src] = state.source_moved_nothing(src)
 
     def _saving_req_status(self) -> tuple:
         counts: dict = defaultdict(int)
         ready = 0
         for state in tuple(self._saving.values()):
             sources = tuple(get_param(state._req, HB_SAVE_SOURCES, ()))
-            with state._signals_lock:
+            with state.lock:
                 if sources:
-                    pending = tuple(s for s in sources if not self._source_done_for_all_workers(state._worker_signals, s))
+                    pending = tuple(s for s in sources if state.ranks_reporting(s) < self._tp_size())
                     if not pending:
                         ready += 1
                         continue
@@ -331,7 +323,7 @@ class HybridScheduler:
                 save_ioret: Optional[IoRet] = get_param(req, HB_SAVE_IORET, None)
                 save_failed = save_ioret is not None and save_ioret.n is not None and save_ioret.n == 0
                 self._record_lifecycle_done("save", state.start_time, save_failed or req_aborted(req))
-                with state._signals_lock:
+                with state.lock:
                     done_times, failed = dict(state.source_done_times), dict(state.source_failed)
                 for src, t_done in done_times.items():
                     ms = max(0.0, (t_done - state.start_time) * 1000)
@@ -529,7 +521,7 @@ class HybridScheduler:
                                                   on_signal_advanced=self._mark_save_source_done_time)
         if state is None:
             return
-        with state._signals_lock:
+        with state.lock:
             failed = any(state.source_failed.values())
         if failed:
             set_param(state._req, HB_SAVE_IORET, IoRet(n=0))

@@ -362,67 +362,98 @@ class IoRet(msgspec.Struct, array_like=True, omit_defaults=True, gc=False):
 
 
 class IoState:
-    """A request is done when every TP rank has reported ``signals_per_worker`` times (or, with
-    ``expected_sources``, once per source)."""
+    """Completion ledger of one request across the TP ranks of an instance.
+
+    Every rank owes a quota of completion signals: one per name in ``expected_sources`` when the
+    request is served by several backends at once, else ``signals_per_worker`` anonymous ones.  The
+    ledger is kept incrementally: each accepted signal updates the rank's tally, the per-source
+    tallies and a running summary (first failure, smallest token count), so completion and the
+    summary are O(1) to read however many ranks report.  Same contract as the reference's
+    per-request state (blade_kvt/hybrid_connector/utils.py: IoState / try_advance)."""
 
     def __init__(self, signals_per_worker: int = 1):
         self.signals_per_worker = signals_per_worker
-        self._worker_signals: dict[int, list] = {}
-        self._signals_lock = threading.Lock()
+        self.expected_sources: tuple = ()
+        self.lock = threading.Lock()
+        self._got: dict[int, set | int] = {}        # rank -> names seen (named mode) or count (anonymous mode)
+        self._full_ranks = 0
+        self._src_ranks: dict[str, int] = {}         # source -> ranks that reported it
+        self._src_zero: set[str] = set()             # sources with a signal that moved nothing
+        self._head: Optional[IoRet] = None           # first accepted signal: names the request in the summary
+        self._failure: Optional[Any] = None
+        self._fewest: Optional[int] = None
+        self._uncounted = False                      # some signal carried no token count
+
+    # -- writing (callers hold ``lock``) ----------------------------------------------------------
+    def accept(self, rank: int, sig: IoRet) -> Optional[str]:
+        """Books one signal; returns why it was refused, or None when it counted."""
+        names = tuple(self.expected_sources or ())
+        if names:
+            if sig.source not in names:
+                return "source not expected"
+            seen = self._got.setdefault(rank, set())
+            if sig.source in seen:
+                return "source already reported by this rank"
+            seen.add(sig.source)
+            if len(seen) == len(names):
+                self._full_ranks += 1
+        else:
+            have = self._got.get(rank, 0)
+            if have >= self.signals_per_worker:
+                return "rank already reported its quota"
+            self._got[rank] = have + 1
+            if have + 1 == self.signals_per_worker:
+                self._full_ranks += 1
+        if sig.source is not None:
+            self._src_ranks[sig.source] = self._src_ranks.get(sig.source, 0) + 1
+            if sig.n == 0:
+                self._src_zero.add(sig.source)
+        if self._head is None:
+            self._head = sig
+        if sig.ex is not None and self._failure is None:
+            self._failure = sig.ex
+        if sig.n is None:
+            self._uncounted = True
+        elif self._fewest is None or sig.n < self._fewest:
+            self._fewest = sig.n
+        return None
+
+    # -- reading ------------------------------------------------------------------------------------
+    def full_ranks(self) -> int:
+        return self._full_ranks
+
+    def ranks_reporting(self, source: str) -> int:
+        return self._src_ranks.get(source, 0)
+
+    def source_moved_nothing(self, source: str) -> bool:
+        return source in self._src_zero
 
     def merge(self) -> IoRet:
-        """Combine the signals of all ready ranks: first failure wins, token count is the minimum."""
-        rets: list = []
-        for sigs in self._worker_signals.values():
-            if len(sigs) >= self.signals_per_worker:
-                rets.extend(sigs)
-        assert rets
-        out = rets[0]
-        for r in rets[1:]:
-            if r.ex is not None and out.ex is None:
-                out.ex = r.ex
-                break
-            if out.n is None:
-                continue
-            if r.n is None:
-                out.n = None
-            elif out.n > r.n:
-                out.n = r.n
-        return out
+        """The request's outcome: the first failure any rank reported; the token count every rank
+        reached (the smallest), unknown as soon as one rank gave none."""
+        assert self._head is not None, "no signal was accepted"
+        return IoRet(reqid=self._head.reqid, ex=self._failure, n=None if self._uncounted else self._fewest,
+                     source=self._head.source)
 
 
 def try_advance(state_dict: dict, ioret: IoRet, worker_tprank: int, tpsize: int,
                 on_signal_advanced: Optional[Callable[[Any, IoRet], None]] = None):
-    """Record one completion signal; returns the state when the request just became complete."""
+    """Books one completion signal in its request's ledger; returns the ledger when this signal
+    completed the request (every one of ``tpsize`` ranks has met its quota), else None.
+    ``on_signal_advanced(state, ioret)`` runs under the ledger's lock after an accepted signal."""
     assert ioret.reqid is not None
     state: Optional[IoState] = state_dict.get(ioret.reqid)
     if state is None:
-        logger.warning("try_advance: unknown ioret=%s tprank=%s", ioret, worker_tprank)
+        logger.warning("completion signal for a request that is not tracked: %s (rank %s)", ioret, worker_tprank)
         return None
-    with state._signals_lock:
-        sigs = state._worker_signals.setdefault(worker_tprank, [])
-        expected = tuple(getattr(state, "expected_sources", ()) or ())
-        if expected:
-            if ioret.source is None or ioret.source not in expected:
-                logger.warning("try_advance: bad source ioret=%s expected=%s", ioret, expected)
-                return None
-            if any(s.source == ioret.source for s in sigs):
-                logger.warning("try_advance: dup source worker=%s ioret=%s", worker_tprank, ioret)
-                return None
-            sigs.append(ioret)
-            if on_signal_advanced is not None:
-                on_signal_advanced(state, ioret)
-            ready = sum(1 for s in state._worker_signals.values()
-                        if all(any(x.source == src for x in s) for src in expected))
-        else:
-            if len(sigs) >= state.signals_per_worker:
-                logger.warning("try_advance: dup worker=%s ioret=%s", worker_tprank, ioret)
-                return None
-            sigs.append(ioret)
-            if on_signal_advanced is not None:
-                on_signal_advanced(state, ioret)
-            ready = sum(1 for s in state._worker_signals.values() if len(s) >= state.signals_per_worker)
-        return state if ready >= tpsize else None
+    with state.lock:
+        refused = state.accept(worker_tprank, ioret)
+        if refused is not None:
+            logger.warning("completion signal ignored (%s): %s (rank %s)", refused, ioret, worker_tprank)
+            return None
+        if on_signal_advanced is not None:
+            on_signal_advanced(state, ioret)
+        return state if state.full_ranks() >= tpsize else None
 
 
 class CodeError(Exception):

@@ -343,6 +343,12 @@ class KVTransferClient:
     def inflight(self) -> int:
         return int(self._c.inflight()) if self._c is not None else 0
 
+    def failed_batches(self) -> int:
+        """Batches of this client that finished without their data having arrived (unreachable
+        destination, refused plan, kernel status, missing completion record).  Their requests were
+        reported as failed to the scheduler; this counter lets a caller without one notice."""
+        return int(self._c.failed_batches()) if self._c is not None else 0
+
     def worker_info(self) -> str:
         return self._c.worker_info() if self._c is not None else _K.current_worker_info("client")
 

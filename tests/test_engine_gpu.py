@@ -281,7 +281,7 @@ def test_device_timestamps_in_the_flush_metrics():
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     r = subprocess.run([sys.executable, "-c", _STAMP_SCRIPT], cwd=root, env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stderr[-2000:]
-    m = re.search(r"SendStubMetrics\..*Proto=nvlink,Path=fused.*DeviceUs=(-?\d+)", r.stderr)
+    m = re.search(r"SendStubMetrics\..*Proto=nvlink,Mode=push,Path=fused.*DeviceUs=(-?\d+)", r.stderr)
     assert m is not None, r.stderr[-2000:]
     assert 0 <= int(m.group(1)) < 1_000_000
 

@@ -141,3 +141,97 @@ def test_two_gpus_two_processes_cuda_ipc(tmp_path):
         p.join(60)
         if p.is_alive():
             p.kill()
+
+
+# ---- which GPU runs the kernels ---------------------------------------------------------------------
+# The mode is read from the environment once per process, so each mode runs in a process of its own:
+# it repeats the one-process and the two-process transfer above and prints the transport's metrics.
+_MODE_SCRIPT = r"""
+import os, sys
+sys.path.insert(0, os.path.join(os.getcwd(), "tests"))
+import multiprocessing as mp
+import torch
+import test_engine_multigpu as T
+
+def main():
+    # one process, two devices
+    src = [T.SRC_L.alloc("cuda:0", "normal", seed=i) for i in range(T.L)]
+    dst = [T.DST_L.alloc("cuda:1") for _ in range(T.L)]
+    srv = T.KVTransferServer("D|0|1", 1, 0, 0, T.DST_L.block_bytes, T.DST_L.token_bytes, "fake://", dst, [T.PT.NVLINK],
+                             num_kv_heads=8, cache_shape=5)
+    cli = T.KVTransferClient("P|0|1", 1, 0, 0, T.SRC_L.block_bytes, T.SRC_L.token_bytes, "fake://", src, [T.PT.NVLINK],
+                             num_kv_heads=8, cache_shape=2)
+    reqs = T._requests()
+    chunks = [T.ReqChunk(sb, db, 0, t) for _, sb, db, t in reqs]
+    for step in (1, 2, 3):          # several batches through one session
+        for d in dst:
+            d.zero_()
+        torch.cuda.synchronize(1)
+        for rid, sb, db, total in reqs:
+            cli.submit_req_send2("D|0|1", 0, f"{rid}.{step}", 0, total, True, sb, db, srv.worker_info(), stepid=step)
+        cli.start_send_step(step, 1)
+        for layer in range(T.L):
+            cli.record_event(layer)
+        cli.flush_send_step()
+        assert cli.wait_inflight(0, 30.0) and cli.failed_batches() == 0
+        for i in range(T.L):
+            expect = torch.zeros_like(src[i])
+            T.reference_transfer(T.SRC_L, T.DST_L, src[i], expect, chunks)
+            assert torch.equal(dst[i].to("cuda:0"), expect), (step, i)
+    srv.stop()
+    print("one-process ok", flush=True)
+
+    # two processes: CUDA IPC memory and event handles
+    import tempfile
+    tmp = tempfile.mkdtemp()
+    ctx = mp.get_context("spawn")
+    ready, go, result = ctx.Event(), ctx.Event(), ctx.Queue()
+    p = ctx.Process(target=T._decode_proc, args=(tmp, ready, go, result))
+    p.start()
+    try:
+        assert ready.wait(180)
+        cli2 = T.KVTransferClient("P2|0|1", 1, 0, 0, T.SRC_L.block_bytes, T.SRC_L.token_bytes, f"file:{tmp}", src,
+                                  [T.PT.NVLINK], num_kv_heads=8, cache_shape=2)
+        for rid, sb, db, total in reqs:
+            cli2.submit_req_send2("D|0|1", 0, rid, 0, total, True, sb, db, None, stepid=1)
+        cli2.start_send_step(1, 1)
+        for layer in range(T.L):
+            cli2.record_event(layer)
+        cli2.flush_send_step()
+        assert cli2.wait_inflight(0, 30.0) and cli2.failed_batches() == 0
+        go.set()
+        got = [torch.from_numpy(a) for a in result.get(timeout=120)]
+        for i in range(T.L):
+            expect = torch.zeros_like(src[i])
+            T.reference_transfer(T.SRC_L, T.DST_L, src[i], expect, chunks)
+            assert torch.equal(got[i], expect.cpu()), i
+    finally:
+        go.set()
+        p.join(60)
+        if p.is_alive():
+            p.kill()
+    print("two-process ok", flush=True)
+
+if __name__ == "__main__":
+    main()
+"""
+
+
+@pytest.mark.parametrize("pull", [1, 0])
+def test_kernels_on_the_decode_gpu_or_on_the_prefill_gpu(pull):
+    """Pull (default between GPUs): a session on the decode worker's server maps the prefill cache and
+    its layer events and runs the kernels there, loading over NVLink.  Push: the prefill GPU stores.
+    Same bytes either way; the metrics line names the mode."""
+    import re
+    import subprocess
+    import sys
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, BLLM_KVTRANS_NVLINK_PULL=str(pull), LLMOPS_CPP_MIN_LOG_LEVEL="0", NCCL_NVLS_ENABLE="0")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", _MODE_SCRIPT], cwd=root, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-3000:]
+    assert "one-process ok" in r.stdout and "two-process ok" in r.stdout
+    modes = re.findall(r"SendStubMetrics\..*Proto=nvlink,Mode=(\w+),Path=fused", r.stderr)
+    assert len(modes) >= 4 and set(modes) == {"pull" if pull else "push"}, modes
