@@ -3,6 +3,8 @@
 // adds the kernel-level `kvt_*` functions.
 #include <pybind11/pybind11.h>
 
+#include "core/crash_trace.h"
+
 namespace py = pybind11;
 
 namespace kvx {
@@ -16,4 +18,7 @@ PYBIND11_MODULE(kvtransfer_ops, m) {
   kvx::bind_kernels(m);
   kvx::bind_engine(m);
   kvx::bind_store(m);
+  kvx::install_crash_trace();      // only with BLLM_KVTRANS_CRASH_TRACE=1
+  m.def("install_crash_trace", [] { return kvx::install_crash_trace(true); },
+        "Write the native frames of a crashing engine thread to stderr before the process dies.");
 }

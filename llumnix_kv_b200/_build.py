@@ -82,11 +82,11 @@ def _compile_one(src: Path, hdr_digest: str, verbose: bool) -> Path:
     common = ["-O3", "-std=c++17", "-DNDEBUG"] + _includes()
     san = [f"-fsanitize={SANITIZE}", "-g", "-fno-omit-frame-pointer"] if SANITIZE else []
     if src.suffix == ".cu":
-        cmd = [NVCC, *GENCODE, "-lineinfo", "-Xcompiler", ",".join(["-fPIC", "-Wall", "-Wextra", "-Wno-unused-parameter"] + san),
+        cmd = [NVCC, *GENCODE, "-lineinfo", "-Xcompiler", ",".join(["-fPIC", "-g1", "-Wall", "-Wextra", "-Wno-unused-parameter"] + san),
                "--expt-relaxed-constexpr", "-Xptxas", "-v" if verbose else "-O3", *common,
                "-c", str(src), "-o", str(obj)]
     else:
-        cmd = [CXX, "-fPIC", "-Wall", "-Wextra", "-Wshadow", "-Wno-unused-parameter", "-pthread", *san, *common,
+        cmd = [CXX, "-fPIC", "-g1", "-Wall", "-Wextra", "-Wshadow", "-Wno-unused-parameter", "-pthread", *san, *common,
                "-c", str(src), "-o", str(obj)]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:

@@ -43,6 +43,7 @@ from .utils import IoRet, IoState, handle_done_req, kill_me_if_exception, try_ad
 logger = logging.getLogger("llumnix_kv_b200.hybrid_connector")
 
 FAKE_REQID = "__FAKE_REQID_FOR_HYBRID_CONNECTOR__"
+_ALREADY_ABORTED = object()      # an abort that found its request aborted before: no second answer
 
 
 @dataclass
@@ -342,7 +343,7 @@ class HybridScheduler:
                 else:
                     # the save finished first: request_finished_all_groups will announce it
                     set_param(req, PD_SAVED, True)
-            self._try_teardown_save(reqid)
+            self._release_save(reqid)
         return kvt_done
 
     def _setup_save(self, req: Request, kvblks: KVCacheBlocks, save_count: int = 1) -> None:
@@ -356,15 +357,17 @@ class HybridScheduler:
         self._engine.sched_acquire_blocks(kvblks)   # the blocks now outlive the request
         set_param(req, SAVE_PREPARED, True)
 
-    def _try_teardown_save(self, reqid: str) -> None:
+    def _release_save(self, reqid: str) -> None:
+        """Undoes _setup_save once the save has ended and the request has finished: the blocks go back
+        to the engine.  Idempotent: whichever of the two events comes second finds nothing left."""
         state = self._saving.pop(reqid, None)
         if state is None:
-            logger.info("teardown save twice: reqid=%s", reqid)
+            logger.info("save of %s was already released", reqid)
             return
-        self._untrack_extra_kv_blocks("save", reqid)
         assert has_setup_save(state._req)
-        self._engine.sched_free_blocks(state.kvblks)
         set_param(state._req, SAVE_PREPARED, False)
+        self._untrack_extra_kv_blocks("save", reqid)
+        self._engine.sched_free_blocks(state.kvblks)
 
     async def _cleanup(self, req: Request) -> None:
         if dec_cleanup_rc(req) <= 0:
@@ -392,7 +395,7 @@ class HybridScheduler:
                 self._loading[req.request_id] = _LoadingReq(req)
                 self._track_extra_kv_blocks("load", req.request_id, kvblks)
                 self._add_ts(req, "load_enqueue")
-                asyncio.run_coroutine_threadsafe(self._on_add_req(req, kvblks), self.loop)
+                asyncio.run_coroutine_threadsafe(self._resolve_load(req, kvblks), self.loop)
             else:
                 self._loaded.append(req)   # nothing to load: visible to the engine right away
 
@@ -439,48 +442,65 @@ class HybridScheduler:
         return False
 
     def _step_aborting(self) -> Optional[dict]:
-        out: dict = defaultdict(list)
+        """Serves the queued aborts.  Where a request is decides what an abort means: still queued
+        here (never reached the engine), loading (the backend must be told, the engine does not know
+        it yet), known to the engine (finish it there), and - independently - saving."""
+        replies: dict = defaultdict(list)
         while self._aborting:
             areq: AbortReq = self._aborting.popleft()
-            waiting_req = None
-            for i, (req, _, _) in enumerate(self._waiting):
-                if req.request_id == areq.reqid:
-                    waiting_req = req
-                    del self._waiting[i]
-                    break
-            if waiting_req is not None:
-                logger.info("abort waiting. areq=%s", areq)
-                self._engine.sched_add_req(waiting_req)
-                self._engine.sched_finish_req(areq.reqid)
-                if areq.output:
-                    _put_abort_resp(out, waiting_req)
-                continue
-            loadreq = self._loading.get(areq.reqid)
-            if loadreq is not None:
-                if get_param(loadreq._req, ABORTED, False):
-                    continue  # already forwarded to the backend
-                logger.info("abort loading. areq=%s", areq)
-                assert self._engine.sched_get_req(areq.reqid) is None
-                set_param(loadreq._req, ABORTED, True)
-                self._abortmeta_load.append(loadreq._req)
-                if areq.output:
-                    _put_abort_resp(out, loadreq._req)
-                continue
-            req = self._engine.sched_get_req(areq.reqid)
-            if req is not None:
-                logger.info("abort req. areq=%s status=%s totaltokens=%s", areq, req.status, req.num_tokens)
-                self._engine.sched_finish_req(areq.reqid)
-                with contextlib.suppress(ValueError):
-                    self._stop0.remove(req)
-                if areq.output:
-                    _put_abort_resp(out, req)
-            savereq = self._saving.get(areq.reqid)
-            if savereq is not None and not get_param(savereq._req, SAVE_ABORTED, False):
-                logger.info("abort saving. areq=%s", areq)
-                set_param(savereq._req, SAVE_ABORTED, True)
-                assert has_setup_save(savereq._req)
-                self._abortmeta_save.append(savereq._req)
-        return out
+            victim = self._abort_queued(areq)
+            if victim is None:
+                victim = self._abort_loading(areq)
+            if victim is None:
+                victim = self._abort_in_engine(areq)
+                self._abort_saving(areq)
+            if victim is not None and victim is not _ALREADY_ABORTED and areq.output:
+                _put_abort_resp(replies, victim)
+        return replies
+
+    def _abort_queued(self, areq: AbortReq) -> Optional[Request]:
+        pos = next((i for i, entry in enumerate(self._waiting) if entry[0].request_id == areq.reqid), None)
+        if pos is None:
+            return None
+        req = self._waiting[pos][0]
+        del self._waiting[pos]
+        logger.info("abort of a queued request: %s", areq)
+        # the engine frees what it knows: hand the request over and finish it at once
+        self._engine.sched_add_req(req)
+        self._engine.sched_finish_req(areq.reqid)
+        return req
+
+    def _abort_loading(self, areq: AbortReq):
+        state = self._loading.get(areq.reqid)
+        if state is None:
+            return None
+        req = state._req
+        if get_param(req, ABORTED, False):
+            return _ALREADY_ABORTED      # the backend has been told; nothing is answered twice
+        logger.info("abort of a loading request: %s", areq)
+        assert self._engine.sched_get_req(areq.reqid) is None
+        set_param(req, ABORTED, True)
+        self._abortmeta_load.append(req)
+        return req
+
+    def _abort_in_engine(self, areq: AbortReq) -> Optional[Request]:
+        req = self._engine.sched_get_req(areq.reqid)
+        if req is None:
+            return None
+        logger.info("abort of a scheduled request: %s status=%s tokens=%s", areq, req.status, req.num_tokens)
+        self._engine.sched_finish_req(areq.reqid)
+        if req in self._stop0:
+            self._stop0.remove(req)
+        return req
+
+    def _abort_saving(self, areq: AbortReq) -> None:
+        state = self._saving.get(areq.reqid)
+        if state is None or get_param(state._req, SAVE_ABORTED, False):
+            return
+        logger.info("abort of a saving request: %s", areq)
+        assert has_setup_save(state._req)
+        set_param(state._req, SAVE_ABORTED, True)
+        self._abortmeta_save.append(state._req)
 
     # thread safe
     def on_abort_req(self, areq: AbortReq, iscore: bool) -> None:
@@ -496,19 +516,21 @@ class HybridScheduler:
             self._engine.wakeup_core()
 
     @kill_me_if_exception
-    async def _on_add_req(self, req: Request, kvblks: KVCacheBlocks):
-        local = req.num_computed_tokens
-        rmt = await self._backend.async_get_num_new_matched_tokens(req, local)
-        ioret = await self._backend.async_update_state_after_alloc(req, kvblks, rmt)
+    async def _resolve_load(self, req: Request, kvblks: KVCacheBlocks):
+        """Asks the backend how many tokens it can bring and binds them to the allocated blocks.
+        Three outcomes: nothing to bring, or the backend finished (or failed) on the spot - the
+        request is loaded now; otherwise the workers will report, and a step must run to hand them
+        the metadata."""
+        promised = await self._backend.async_get_num_new_matched_tokens(req, req.num_computed_tokens)
+        outcome = await self._backend.async_update_state_after_alloc(req, kvblks, promised)
         self._add_ts(req, "after_alloc")
-        if ioret is not None and ioret.n is None:
-            ioret.n = rmt
-        if rmt <= 0 or ioret is not None:
-            await self.mark_loaded(req, ioret)
-        else:
-            # the worker will report LOAD_DONE; make sure a step happens to deliver the metadata
-            set_param(req, "_hb_promised_tokens", rmt)
+        if outcome is None and promised > 0:
+            set_param(req, "_hb_promised_tokens", promised)
             self._q_append(self._prepared, req.request_id)
+            return
+        if outcome is not None and outcome.n is None:
+            outcome.n = promised      # an immediate answer without a count covers the whole promise
+        await self.mark_loaded(req, outcome)
 
     async def mark_loaded(self, req: Request, ioret: Optional[IoRet] = None) -> None:
         set_param(req, HB_IORET, ioret)

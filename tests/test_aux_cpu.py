@@ -1,5 +1,6 @@
 """Auxiliary subsystems on CPU: process monitor line protocol, gdrcopy shim, CRC, NVLink affinity
 table helpers, KV specs of the model families."""
+import os
 import socket
 import zlib
 
@@ -191,3 +192,20 @@ def test_bulk_copy_round_count_covers_the_longest_descriptor(ops):
         assert r * segs(first) * seg >= longest, (first, longest, r)
         assert r == 1 or (r - 1) * segs(first) * seg < longest, (first, longest, r)   # and no more than needed
     assert ops.kvt_bulk_rounds(1 << 30, 1 << 30) == 2          # 131072 segments over 65536 units
+
+
+def test_crash_trace_prints_native_frames_then_chains(ops):
+    """A child process with BLLM_KVTRANS_CRASH_TRACE=1 that dereferences a null pointer on the host
+    writes its native frames to stderr before it dies of the signal."""
+    import subprocess
+    import sys
+
+    code = ("import ctypes, llumnix_kv_b200\n"
+            "llumnix_kv_b200.load_ops()\n"
+            "ctypes.string_at(0)\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], cwd=root, capture_output=True, text=True, timeout=120,
+                       env=dict(os.environ, BLLM_KVTRANS_CRASH_TRACE="1"))
+    assert r.returncode == -11, (r.returncode, r.stderr[-500:])
+    assert "kvtransfer crash trace: signal 11" in r.stderr and "end of trace" in r.stderr
+    assert "(+0x" in r.stderr or "[0x" in r.stderr
