@@ -297,6 +297,9 @@ def main():
     ceilings = BL.measure_ceilings(pair)
     if args.kernels_on == "decode" and world > 1 and not baseline_arm and args.mode == "p2d":
         pair.use_pull_kernels()
+    elif world > 1:
+        # the engine region follows the kernel-only region: the prefill GPU stores
+        os.environ["BLLM_KVTRANS_NVLINK_PULL"] = "0"
 
     def roofline(per_pair: float) -> dict:
         peaks = {}

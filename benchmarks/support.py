@@ -154,7 +154,7 @@ class PDBenchPair:
             with torch.cuda.stream(self.stream):
                 self.plans = [self.xfer.plan(cs, stream=self.stream) for cs in self.slot_chunks]
             torch.cuda.synchronize()
-            self.transport_name = "NVLink: TMA loads by the decode GPU from the CUDA-IPC mapped prefill cache (pull)"
+        self.transport_name = "NVLink: TMA loads by the decode GPU from the CUDA-IPC mapped prefill cache (pull)"
 
     def _pair_id(self) -> int:
         return self.rank % self.n_pairs if not self.loopback else 0

@@ -2,6 +2,8 @@
 
 #include <thread>
 
+#include <unistd.h>
+
 #include "core/completion.h"
 #include "core/envcfg.h"
 #include "core/log.h"
@@ -39,6 +41,10 @@ uint32_t PullSession::open(const char* body, size_t len) {
   // A pull between two caches on ONE GPU would make the kernels that wait for a layer and the kernels that
   // produce it share a device; the push path serves that case.
   if (mem.device == ctx_->device_id()) return WIRE_BAD_REQUEST;
+  // Two workers inside ONE process (a test arrangement; serving engines run one process per GPU) stay with the
+  // push path as well: this session would wait on the prefill worker's own event objects from another device's
+  // stream, and with events created for interprocess use that wait crashed inside the driver.
+  if (mem.pid == static_cast<int32_t>(getpid())) return WIRE_BAD_REQUEST;
   try {
     src_map_.map(mem, ctx_->device_id());
     events_ = open_peer_events(ev_info_);

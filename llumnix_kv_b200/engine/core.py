@@ -100,6 +100,7 @@ class MiniEngineCore:
         if self._thread is not None:
             self._thread.join(10)
         if self.connector is not None and self.proxy is not None:
+            self.connector._sched.close_bypass()
             self.proxy.rpc_server.close(self.proxy.sched_loop)
         for w in self.workers:
             if w.connector is not None:

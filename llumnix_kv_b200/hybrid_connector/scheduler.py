@@ -154,18 +154,37 @@ class HybridScheduler:
         import zmq
         import zmq.asyncio
 
-        ctx = zmq.asyncio.Context()
-        self._bypass_socket = ctx.socket(zmq.XPUB)
+        # the context is kept: one that is only reachable through its socket is torn down by the garbage
+        # collector, and a teardown waits for unsent messages unless the socket says not to (LINGER 0)
+        self._bypass_ctx = zmq.asyncio.Context()
+        self._bypass_socket = self._bypass_ctx.socket(zmq.XPUB)
+        self._bypass_socket.setsockopt(zmq.LINGER, 0)
         self._bypass_socket.setsockopt(zmq.XPUB_VERBOSE, True)
         port = self._bypass_socket.bind_to_random_port("tcp://127.0.0.1")
         self.bypass_remote_subscribe_addr = f"tcp://127.0.0.1:{port}"
         logger.info("bypass server socket started at: %s", self.bypass_remote_subscribe_addr)
 
+    def close_bypass(self) -> None:
+        """Engine shutdown: closes the publisher on its own loop; unsent metadata is dropped."""
+        sock, self._bypass_socket = self._bypass_socket, None
+        if sock is None:
+            return
+
+        async def _close():
+            sock.close(linger=0)
+
+        try:
+            asyncio.run_coroutine_threadsafe(_close(), self.loop).result(5)
+        except Exception:       # the loop is gone already: the socket dies with the process
+            logger.debug("bypass publisher not closed cleanly", exc_info=True)
+
     @kill_me_if_exception
     async def _send_bypass_task(self, meta: HybridMetadata):
         import pickle
 
-        await self._bypass_socket.send(pickle.dumps(meta))
+        sock = self._bypass_socket
+        if sock is not None:
+            await sock.send(pickle.dumps(meta))
 
     def send_bypass_task(self, meta: HybridMetadata) -> None:
         if meta.reqs and self._bypass_socket is not None:

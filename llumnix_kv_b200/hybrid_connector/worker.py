@@ -87,7 +87,9 @@ class HybridWorker:
         addr = await self._get_bypass_handle()
         if not addr:
             return
-        sock = zmq.asyncio.Context().socket(zmq.SUB)
+        self._bypass_ctx = zmq.asyncio.Context()      # kept: see the publisher's note on teardown
+        sock = self._bypass_ctx.socket(zmq.SUB)
+        sock.setsockopt(zmq.LINGER, 0)
         sock.setsockopt_string(zmq.SUBSCRIBE, "")
         sock.connect(addr)
         while True:

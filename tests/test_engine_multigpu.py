@@ -219,9 +219,10 @@ if __name__ == "__main__":
 
 @pytest.mark.parametrize("pull", [1, 0])
 def test_kernels_on_the_decode_gpu_or_on_the_prefill_gpu(pull):
-    """Pull (default between GPUs): a session on the decode worker's server maps the prefill cache and
-    its layer events and runs the kernels there, loading over NVLink.  Push: the prefill GPU stores.
-    Same bytes either way; the metrics line names the mode."""
+    """Pull (default between two worker processes): a session on the decode worker's server maps the
+    prefill cache and its layer events and runs the kernels there, loading over NVLink.  Push: the
+    prefill GPU stores; two workers inside one process always push.  Same bytes either way; the
+    metrics line names the mode."""
     import re
     import subprocess
     import sys
@@ -234,4 +235,5 @@ def test_kernels_on_the_decode_gpu_or_on_the_prefill_gpu(pull):
     assert r.returncode == 0, r.stderr[-3000:]
     assert "one-process ok" in r.stdout and "two-process ok" in r.stdout
     modes = re.findall(r"SendStubMetrics\..*Proto=nvlink,Mode=(\w+),Path=fused", r.stderr)
-    assert len(modes) >= 4 and set(modes) == {"pull" if pull else "push"}, modes
+    assert modes[:3] == ["push"] * 3 and len(modes) >= 4, modes
+    assert set(modes[3:]) == {"pull" if pull else "push"}, modes
