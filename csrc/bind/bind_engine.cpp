@@ -44,6 +44,9 @@ struct HybridArgs {
   uint32_t ple_block_group = 0;
   uint32_t ple_conv_elem_size = 1;
   std::vector<size_t> ple_conv_state_shape, ple_conv_channel_dims;
+  // the worker's cache as a member of an NVLink multicast group: multicast address per [layer][tensor], group size
+  std::vector<std::vector<uint64_t>> mc_layers;
+  uint32_t mc_size = 0;
 };
 
 void apply_hybrid(WorkerInfo* wi, const HybridArgs& h) {
@@ -106,6 +109,12 @@ std::unique_ptr<Context> make_context(const std::string& inst, uint32_t tp_size,
     wi->ext["heads"] = std::to_string(per_rank);
   }
   wi->ext["dev"] = std::to_string(device_id);
+  if (!h.mc_layers.empty() && h.mc_size > 1) {
+    RTASSERT(h.mc_layers.size() == layers.size());
+    for (size_t l = 0; l < layers.size(); ++l) RTASSERT(h.mc_layers[l].size() == layers[l].size());
+    ctx->set_multicast_address(h.mc_layers);
+    wi->ext["mcn"] = std::to_string(h.mc_size);     // senders may hand this worker a request for the whole group
+  }
   return ctx;
 }
 
@@ -208,6 +217,8 @@ HybridArgs hybrid_from_kwargs(const py::kwargs& kw) {
   geti("ple_conv_elem_size", h.ple_conv_elem_size);
   geti("ple_conv_state_shape", h.ple_conv_state_shape);
   geti("ple_conv_channel_dims", h.ple_conv_channel_dims);
+  geti("mc_layers", h.mc_layers);
+  geti("mc_size", h.mc_size);
   return h;
 }
 
@@ -389,14 +400,16 @@ void bind_engine(py::module_& m) {
       .def("submit_req_send2",
            [](KvClient& c, const std::string& dst_inst, uint32_t dst_worker, const std::string& reqid, uint32_t seen,
               uint32_t new_tokens, bool last, const BlockIds& src, const BlockIds& dst, const py::object& info,
-              size_t stepid, uint32_t substepid) {
+              size_t stepid, uint32_t substepid, uint32_t fanout) {
              std::optional<std::string> s;
              if (!info.is_none()) s = info.cast<std::string>();
-             c.get()->submit_req_send(dst_inst, dst_worker, reqid, seen, new_tokens, last, src, dst, s, stepid, substepid);
+             c.get()->submit_req_send(dst_inst, dst_worker, reqid, seen, new_tokens, last, src, dst, s, stepid, substepid,
+                                      fanout);
            },
            py::arg("dst_inst"), py::arg("dst_worker"), py::arg("reqid"), py::arg("seen_tokens"), py::arg("new_tokens"),
            py::arg("has_last_token"), py::arg("src_block_ids"), py::arg("dst_block_ids"),
-           py::arg("dst_worker_info") = py::none(), py::arg("stepid") = 1024, py::arg("substepid") = 0)
+           py::arg("dst_worker_info") = py::none(), py::arg("stepid") = 1024, py::arg("substepid") = 0,
+           py::arg("fanout") = 0)
       .def("submit_delta_send",
            [](KvClient& c, const std::string& reqid, uint32_t seen, uint32_t new_tokens, bool last, size_t stepid,
               uint32_t substepid) { c.get()->submit_delta_send(reqid, seen, new_tokens, last, stepid, substepid); },
@@ -502,13 +515,15 @@ void bind_engine(py::module_& m) {
       "submit_req_send2",
       [](const std::string& dst_inst, uint32_t dst_worker, const std::string& reqid, uint32_t seen, uint32_t new_tokens,
          bool last, const BlockIds& src, const BlockIds& dst, const py::object& info, size_t stepid,
-         uint32_t substepid) {
+         uint32_t substepid, uint32_t fanout) {
         std::optional<std::string> s;
         if (!info.is_none()) s = info.cast<std::string>();
         need_client()->submit_req_send(dst_inst, dst_worker, reqid, seen, new_tokens, last, src, dst, s, stepid,
-                                       substepid);
+                                       substepid, fanout);
       },
-      "submit kv send to kv client;");
+      py::arg("dst_inst"), py::arg("dst_worker"), py::arg("reqid"), py::arg("seen_tokens"), py::arg("new_tokens"),
+      py::arg("has_last_token"), py::arg("src_block_ids"), py::arg("dst_block_ids"), py::arg("dst_worker_info") = py::none(),
+      py::arg("stepid") = 1024, py::arg("substepid") = 0, py::arg("fanout") = 0, "submit kv send to kv client;");
   m.def("start_req_send", [](std::vector<ReqMeta> metas, size_t stepid, uint32_t substepid) {
     need_client()->start_req_send(metas, stepid, substepid);
   });

@@ -185,7 +185,8 @@ void KvTransferClient::start_req_send(std::vector<ReqMeta>& metas, size_t stepid
 
 void KvTransferClient::submit_req_send(InstanceId dst_inst, WorkerId dst_worker, RequestId reqid, uint32_t seen,
                                        uint32_t new_tokens, bool last, BlockIds src_blocks, BlockIds dst_blocks,
-                                       std::optional<std::string> dst_worker_info, size_t stepid, uint32_t substepid) {
+                                       std::optional<std::string> dst_worker_info, size_t stepid, uint32_t substepid,
+                                       uint32_t fanout) {
   RTASSERT(substepid == 0);
   RTASSERT(new_tokens > 0);
   auto parsed = parse_worker_info(dst_worker_info);
@@ -199,6 +200,7 @@ void KvTransferClient::submit_req_send(InstanceId dst_inst, WorkerId dst_worker,
   }
   auto info = std::make_shared<RequestInfo>(std::move(dst_inst), dst_worker, std::move(parsed), std::move(reqid),
                                             std::move(src_blocks), std::move(dst_blocks));
+  info->replicas = fanout > 1 ? fanout : 1;
   add_send_task(pending_buf_, info, seen, new_tokens, last);
   LOG(INFO) << "submit_req_send: StepIdx=" << stepid << "." << substepid << ";req_id=" << info->req_id
             << ";dst_worker=" << info->dst_inst_id << ',' << dst_worker << ";seen_tokens=" << seen

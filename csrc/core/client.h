@@ -52,7 +52,8 @@ class KvTransferClient {
   void start_req_send(std::vector<ReqMeta>& metas, size_t stepid, uint32_t substepid);  // thread safe
   void submit_req_send(InstanceId dst_inst, WorkerId dst_worker, RequestId reqid, uint32_t seen_tokens,
                        uint32_t new_tokens, bool has_last_token, BlockIds src_block_ids, BlockIds dst_block_ids,
-                       std::optional<std::string> dst_worker_info, size_t stepid, uint32_t substepid);
+                       std::optional<std::string> dst_worker_info, size_t stepid, uint32_t substepid,
+                       uint32_t fanout = 0);
   void submit_delta_send(const RequestId& reqid, uint32_t seen_tokens, uint32_t new_tokens, bool has_last_token,
                          size_t stepid, uint32_t substepid);
   size_t start_send(size_t stepid, size_t sched_tokens);

@@ -65,6 +65,10 @@ class Context {
   ICudaBarrier* cuda_barrier() { return barrier_.get(); }
   const std::vector<std::vector<LayerInfo>>& all_layer_infos() const { return layer_infos_; }
   const std::vector<std::vector<uint64_t>>& layer_data_address() const { return layer_addrs_; }
+  // NVLink multicast addresses of the same tensors, when this worker's cache is a member of a multicast group
+  // (a tensor-parallel decode group whose caches live in one symmetric allocation); empty otherwise.
+  const std::vector<std::vector<uint64_t>>& multicast_address() const { return mc_addrs_; }
+  void set_multicast_address(std::vector<std::vector<uint64_t>> a) { mc_addrs_ = std::move(a); }
   int device_id() const { return device_id_; }
   uint32_t num_layers() const { return worker_info_.num_layers; }
   uint32_t layer_num_blocks() const { return worker_info_.layer_num_blocks; }
@@ -79,6 +83,7 @@ class Context {
   WorkerInfo worker_info_;
   std::vector<std::vector<LayerInfo>> layer_infos_;
   std::vector<std::vector<uint64_t>> layer_addrs_;
+  std::vector<std::vector<uint64_t>> mc_addrs_;
   std::unique_ptr<ICudaBarrier> barrier_;
   InflightCounter inflight_;
 };

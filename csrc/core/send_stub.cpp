@@ -232,7 +232,17 @@ struct KvSendStub::Impl {
     }
     int64_t send_notify_us = 0;
     if (!pb.finished_req.empty()) {
-      notifier.notify(pb.finished_req);
+      // a request that the destination relayed to k workers of its group reports k times: the scheduler counts one
+      // completion per worker that this rank would otherwise have served itself
+      bool relayed = false;
+      for (const ReqSendTask* task : pb.finished_req) relayed = relayed || task->req().replicas > 1;
+      if (relayed) {
+        std::vector<const ReqSendTask*> expanded;
+        for (const ReqSendTask* task : pb.finished_req) expanded.insert(expanded.end(), task->req().replicas, task);
+        notifier.notify(expanded);
+      } else {
+        notifier.notify(pb.finished_req);
+      }
       const auto now = SteadyClock::now();
       send_notify_us = elapse_us(send_finish, now);
       send_finish = now;
@@ -263,6 +273,10 @@ struct KvSendStub::Impl {
     if (!pb.send_req.empty()) {
       try {
         try_create_channel();
+        for (const ReqSendTask* t : pb.send_req)
+          if (t->req().replicas > 1 && !ch->relays_to_group())
+            throw KVTransferException(ErrorKind::INVALID_OPERATION,
+                                      "a relayed transfer (fanout) needs the NVLINK transport and a destination in a multicast group");
         bool device_planned = ch->register_tasks(env, pb.send_req);
         bool have_data = device_planned;
         if (!device_planned) {

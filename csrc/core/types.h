@@ -148,6 +148,10 @@ class RequestInfo {
   const RequestId req_id;
   const BlockIds src_blocks;
   const BlockIds dst_blocks;
+  // Members of the destination's multicast group that this one transfer serves (1: only dst_worker_id).  With k > 1
+  // the destination worker relays the bytes to its whole group and the send-done report counts k times, one for
+  // each worker that a sender without the relay would have served.  Set before the first chunk is queued.
+  uint32_t replicas{1};
 
   RequestInfo(InstanceId dst_inst, WorkerId dst_worker, std::optional<WorkerInfo> dst_info, RequestId rid,
               BlockIds src, BlockIds dst)

@@ -337,6 +337,15 @@ typedef struct KvtMcFanout {
 
 int kvt_launch_mc_fanout(const KvtMcFanout* args, int grid_ctas, void* stream);
 
+// The same replication driven by a walk plan: the member that received a request through walk ops
+// (kvt_launch_walk, with `args` as launched there: its dst_ptrs are this GPU's cache) stores exactly
+// the destination pieces of those ops - copies and zero fills - to the same offsets behind
+// mc_ptrs[layer * n_tensors + tensor], the multicast addresses of the group's cache tensors.  The
+// zero-fill class follows the two classes of `args` in the ops array.  Pieces must be made of whole
+// 4-byte words (16-byte ones take the wide store); anything else reports KVT_ERR_BAD_ARGS.
+int kvt_launch_walk_fanout(const KvtWalkLaunch* args, uint32_t n_zero_ops, uint64_t zero_units,
+                           const uint64_t* mc_ptrs, int grid_ctas, void* stream);
+
 // ---- completion flags ---------------------------------------------------------------------
 // Bounded device-side wait: returns through status[0]=KVT_ERR_FLAG_TIMEOUT when *flag has not
 // reached `value` within timeout_ns.  Never spins without limit.

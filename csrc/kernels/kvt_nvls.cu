@@ -17,6 +17,7 @@
 #include <stdint.h>
 
 #include "kvt_kernels.h"
+#include "kvt_walk.h"
 
 namespace {
 
@@ -92,7 +93,107 @@ __global__ void __launch_bounds__(512) kvt_mc_fanout_kernel(const __grid_constan
   }
 }
 
+// ---- fan-out of what a walk plan wrote ----------------------------------------------------------------
+// The member that received a request through walk ops (kvt_walk.cu) replicates exactly the bytes the ops
+// wrote: every unit of every op is decoded with the shared kvt_walk_unit, and its DESTINATION pieces are
+// read from this GPU's cache and stored to the same offsets of the multicast mapping.  Nothing but the
+// transferred bytes is touched, so members may relay different requests, or different chunks of one
+// request, without overwriting one another.
+__device__ __forceinline__ void mc_st_4(void* mc, int v) {
+  asm volatile("multimem.st.relaxed.sys.global.u32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ uint32_t find_walk_op(const KvtWalkOp* __restrict__ ops, uint32_t n, uint64_t u) {
+  uint32_t lo = 0, hi = n;
+  while (hi - lo > 1) {
+    const uint32_t mid = (lo + hi) >> 1;
+    if (ops[mid].first_unit <= u) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+// One class of ops (bulk, simt or zero: first_unit counts within the class), `units` units per layer.
+__global__ void __launch_bounds__(256) kvt_walk_fanout_kernel(const __grid_constant__ KvtWalkLaunch p,
+                                                               const KvtWalkOp* __restrict__ ops, const uint32_t n_ops,
+                                                               const uint64_t units, const uint64_t* __restrict__ mc_ptrs) {
+  const uint32_t n_layers = p.layer_end - p.layer_begin;
+  const uint64_t total = units * n_layers;
+  const uint32_t warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  for (uint64_t w = (uint64_t)blockIdx.x * warps + warp; w < total; w += (uint64_t)gridDim.x * warps) {
+    const uint32_t layer = p.layer_begin + (uint32_t)(w / units);
+    const uint64_t u = w % units;
+    const uint32_t oi = find_walk_op(ops, n_ops, u);
+    const KvtWalkOp& op = ops[oi];
+    const KvtWalkPieces pc = kvt_walk_unit(op, p.pool, u - op.first_unit);
+    if (pc.error != 0) {
+      if (lane == 0) set_status(p.status, KVT_ERR_BLOCK_RANGE, oi);
+      continue;
+    }
+    if (pc.n == 0) continue;
+    const uint32_t t = op.tensor;
+    const int64_t d_last = pc.dst_off + (int64_t)(pc.n - 1) * pc.dst_step;
+    if (t >= p.n_tensors || pc.dst_off < 0 || d_last < 0 || (uint64_t)pc.dst_off + pc.len > p.dst_cap[t] ||
+        (uint64_t)d_last + pc.len > p.dst_cap[t]) {
+      if (lane == 0) set_status(p.status, KVT_ERR_BLOCK_RANGE, oi);
+      continue;
+    }
+    const uint64_t idx = (uint64_t)layer * p.n_tensors + t;
+    const char* own = reinterpret_cast<const char*>(p.dst_ptrs[idx]) + pc.dst_off;
+    char* mc = reinterpret_cast<char*>(mc_ptrs[idx]) + pc.dst_off;
+    const uintptr_t a = reinterpret_cast<uintptr_t>(own) | reinterpret_cast<uintptr_t>(mc) | (uintptr_t)pc.dst_step | pc.len;
+    if ((a & 15u) == 0) {
+      const uint32_t cpp = pc.len >> 4, n16 = cpp * pc.n;
+      for (uint32_t i = lane; i < n16; i += 32) {
+        const uint32_t j = i / cpp, c = i - j * cpp;
+        const int64_t off = (int64_t)j * pc.dst_step + ((int64_t)c << 4);
+        mc_st_16(mc + off, ld_nc_16(own + off));
+      }
+    } else if ((a & 3u) == 0) {
+      const uint32_t cpp = pc.len >> 2, n4 = cpp * pc.n;
+      for (uint32_t i = lane; i < n4; i += 32) {
+        const uint32_t j = i / cpp, c = i - j * cpp;
+        const int64_t off = (int64_t)j * pc.dst_step + ((int64_t)c << 2);
+        mc_st_4(mc + off, *reinterpret_cast<const int*>(own + off));
+      }
+    } else {
+      // multicast stores are at least four bytes wide; cache pieces are made of 2- and 4-byte elements in
+      // multiples of two, so this is a geometry nobody registers
+      if (lane == 0) set_status(p.status, KVT_ERR_BAD_ARGS, oi);
+    }
+  }
+  __threadfence_system();      // the stores of this grid are performed before whatever follows on the stream
+}
+
 }  // namespace
+
+extern "C" int kvt_launch_walk_fanout(const KvtWalkLaunch* args, uint32_t n_zero_ops, uint64_t zero_units,
+                                      const uint64_t* mc_ptrs, int grid_ctas, void* stream) {
+  const KvtWalkLaunch& a = *args;
+  if (a.layer_end <= a.layer_begin) return (int)cudaSuccess;
+  if (a.n_tensors == 0 || a.n_tensors > KVT_WALK_MAX_TENSORS || a.ops == nullptr || a.pool == nullptr || mc_ptrs == nullptr ||
+      a.dst_ptrs == nullptr)
+    return (int)cudaErrorInvalidValue;
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (sms <= 0) sms = 1;
+  const uint64_t n_layers = a.layer_end - a.layer_begin;
+  const KvtWalkOp* ops = a.ops;
+  const uint32_t counts[3] = {a.n_bulk_ops, a.n_simt_ops, n_zero_ops};
+  const uint64_t units[3] = {a.bulk_units, a.simt_units, zero_units};
+  for (int c = 0; c < 3; ++c) {
+    if (counts[c] != 0 && units[c] != 0) {
+      const uint64_t need = (units[c] * n_layers + 7) / 8;       // eight warps per CTA
+      int grid = grid_ctas > 0 ? grid_ctas : 4 * sms;
+      if ((uint64_t)grid > need) grid = (int)need;
+      kvt_walk_fanout_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a, ops, counts[c], units[c], mc_ptrs);
+      const cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) return (int)e;
+    }
+    ops += counts[c];
+  }
+  return (int)cudaSuccess;
+}
 
 extern "C" int kvt_launch_mc_fanout(const KvtMcFanout* args, int grid_ctas, void* stream) {
   const KvtMcFanout& a = *args;

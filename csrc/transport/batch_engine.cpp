@@ -316,6 +316,45 @@ void BatchEngine::launch_walk(const KvtWalkCounts& c, size_t n_ops, size_t pool_
   }
 }
 
+void BatchEngine::set_multicast(std::vector<std::vector<uint64_t>> mc_ptrs) {
+  RTASSERT(mc_ptrs.size() == dst_ptrs_.size());
+  for (size_t l = 0; l < mc_ptrs.size(); ++l) RTASSERT(mc_ptrs[l].size() == dst_ptrs_[l].size());
+  cuda_check(cudaSetDevice(cfg_.device), "cudaSetDevice");
+  mc_ptrs_ = std::move(mc_ptrs);
+  std::vector<uint64_t> flat;
+  for (const auto& l : mc_ptrs_) flat.insert(flat.end(), l.begin(), l.end());
+  d_walk_mc_.upload(flat);
+}
+
+void BatchEngine::launch_walk_fanout(const KvtWalkCounts& c, size_t n_ops, size_t pool_len, size_t lo, size_t hi,
+                                     size_t stage_idx) {
+  if (n_ops == 0 || hi <= lo) return;
+  RTASSERT(has_multicast());
+  cuda_check(cudaSetDevice(cfg_.device), "cudaSetDevice");
+  ensure_walk_arrays();
+  DeviceStage& st = stage(stage_idx);
+  Slot& sl = cur();
+  KvtWalkLaunch a{};
+  a.src_ptrs = d_walk_src_.p;
+  a.dst_ptrs = d_walk_dst_.p;
+  a.n_tensors = static_cast<uint32_t>(dst_ptrs_[0].size());
+  a.layer_begin = static_cast<uint32_t>(lo);
+  a.layer_end = static_cast<uint32_t>(hi);
+  for (uint32_t t = 0; t < a.n_tensors; ++t) {
+    a.src_cap[t] = src_caps_[t];
+    a.dst_cap[t] = dst_caps_[t];
+  }
+  a.ops = reinterpret_cast<const KvtWalkOp*>(sl.d_plan);
+  a.n_bulk_ops = c.n_bulk;
+  a.n_simt_ops = c.n_simt;
+  a.bulk_units = c.bulk_units;
+  a.simt_units = c.simt_units;
+  a.pool = reinterpret_cast<const uint32_t*>(sl.d_plan + n_ops * sizeof(KvtWalkOp));
+  a.pool_len = static_cast<uint32_t>(pool_len);
+  a.status = sl.d_status;
+  cuda_check(kvt_launch_walk_fanout(&a, c.n_zero, c.zero_units, d_walk_mc_.p, grid(), st.stream()), "kvt_launch_walk_fanout");
+}
+
 uint64_t BatchEngine::flush_async(std::string metrics, bool drop_record) {
   cuda_check(cudaSetDevice(cfg_.device), "cudaSetDevice");
   if (batch_slot_ < 0) begin(0);     // a batch without data still completes through a record

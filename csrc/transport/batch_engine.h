@@ -76,6 +76,13 @@ class BatchEngine {
   // The walk kernel (copies, then zero fills) over layers [lo, hi).
   void launch_walk(const KvtWalkCounts& counts, size_t n_ops, size_t pool_len, size_t lo, size_t hi, size_t stage_idx,
                    void* wait_event);
+  // Multicast addresses of the destination tensors ([layer][tensor], as dst_ptrs): set once when the destination
+  // cache is a member of an NVLink multicast group.
+  void set_multicast(std::vector<std::vector<uint64_t>> mc_ptrs);
+  bool has_multicast() const { return !mc_ptrs_.empty(); }
+  // Behind launch_walk on the same stage: store what those ops wrote into this GPU's cache to every member
+  // of the group (multimem stores through NVSwitch).
+  void launch_walk_fanout(const KvtWalkCounts& counts, size_t n_ops, size_t pool_len, size_t lo, size_t hi, size_t stage_idx);
 
   uint64_t flush_async(std::string metrics, bool drop_record = false);
   // DONE: `out` holds the record; FAILED: the ticket is unknown or was never flushed.
@@ -148,6 +155,8 @@ class BatchEngine {
   DevArray<TensorMapBytes> d_src_maps_, d_dst_maps_;
   // walk path
   DevArray<uint64_t> d_walk_src_, d_walk_dst_;
+  std::vector<std::vector<uint64_t>> mc_ptrs_;
+  DevArray<uint64_t> d_walk_mc_;
 };
 
 }  // namespace kvx

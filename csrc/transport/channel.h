@@ -57,6 +57,8 @@ class IChannel {
     return PollResult::DONE;
   }
   virtual bool is_active() { return true; }
+  // Can the destination relay a request to its NVLink multicast group (RequestInfo::replicas > 1)?
+  virtual bool relays_to_group() const { return false; }
   virtual void close() {}
   virtual const char* name() const = 0;
   virtual ~IChannel() = default;

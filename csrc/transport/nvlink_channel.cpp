@@ -84,7 +84,7 @@ class NvlinkChannel : public IChannel {
     }
     RTASSERT(info.num_layers == ctx_->num_layers());
     dst_remote_ = info.device != ctx_->device_id();
-    dst_map_.map(info, ctx_->device_id());
+    same_process_ = info.pid == static_cast<int32_t>(getpid());
     n_tensors_ = info.num_tensors;
     src_shape_ = ctx_->worker_info().cache_shape_or(env_cache_shape());
     dst_shape_ = dst.cache_shape_or(src_shape_);
@@ -96,9 +96,12 @@ class NvlinkChannel : public IChannel {
     pull_ = false;
     if (dst_remote_ && !dst_mx_ && env_nvlink_pull() != 0) pull_ = open_pull(sock);
     if (pull_) {
+      // the decode GPU reads this worker's cache; its own cache is never mapped here, so it may live in memory that
+      // has no IPC handle (a symmetric allocation bound to a multicast group)
       pull_sock_ = std::move(sock);
     } else {
-      // ---- push: streams and plan slots on this GPU ----------------------------------------------
+      // ---- push: the destination's cache mapped here, streams and plan slots on this GPU ------------
+      dst_map_.map(info, ctx_->device_id());
       BatchEngineConfig cfg;
       cfg.device = ctx_->device_id();
       cfg.n_streams = std::max(1, env_nvlink_streams());
@@ -113,7 +116,7 @@ class NvlinkChannel : public IChannel {
       eng_ = std::make_unique<BatchEngine>(cfg, ctx_->layer_data_address(), dst_map_.ptrs(), src_caps_, dst_caps_);
     }
     active_ = true;
-    LOG(INFO) << "nvlink channel connected. dst=" << dst.to_string() << " same_process=" << dst_map_.same_process()
+    LOG(INFO) << "nvlink channel connected. dst=" << dst.to_string() << " same_process=" << same_process_
               << " src_shape=" << src_shape_ << " dst_shape=" << dst_shape_ << " dst_mx=" << dst_mx_
               << " mode=" << (pull_ ? "pull" : "push");
   }
@@ -131,6 +134,24 @@ class NvlinkChannel : public IChannel {
       choice = bind_planner(e);
     } catch (const std::exception&) {
       return false;
+    }
+    // requests that the destination relays to its multicast group: all of a batch or none of it
+    fanout_ = 0;
+    for (const ReqSendTask* t : tasks) fanout_ = std::max(fanout_, t->req().replicas > 1 ? t->req().replicas : 0u);
+    if (fanout_ != 0) {
+      for (const ReqSendTask* t : tasks)
+        if (t->req().replicas != fanout_)
+          throw KVTransferException(ErrorKind::INVALID_OPERATION, "nvlink: a batch mixes relayed and plain requests");
+      const uint32_t group = static_cast<uint32_t>(dst_.ext_int("mcn", 0));
+      if (!pull_ || group < fanout_)
+        throw KVTransferException(ErrorKind::INVALID_OPERATION,
+                                  "nvlink: the destination cannot relay to " + std::to_string(fanout_) +
+                                      " workers (multicast group of " + std::to_string(group) + ", pull session " +
+                                      (pull_ ? "open" : "absent") + ")");
+      if (src_shape_ != dst_shape_ || dst_mx_)
+        throw KVTransferException(ErrorKind::INVALID_OPERATION, "nvlink: a relayed transfer keeps the cache layout");
+      // the relay replicates what walk ops wrote, so these batches take the walk path whatever their shape
+      return register_walk(e, choice, tasks);
     }
     DeviceAttnParams p;
     std::string why = "the layer has several cache tensors";
@@ -189,6 +210,7 @@ class NvlinkChannel : public IChannel {
       h.n_ops = static_cast<uint32_t>(walk_plan_.ops.size());
       h.pool_len = static_cast<uint32_t>(walk_plan_.pool.size());
       h.walk = walk_counts_;
+      h.fanout = fanout_;
       send_plan(h, walk_plan_.ops.data(), ops_bytes, walk_plan_.pool.data(), pool_bytes);
       return true;
     }
@@ -374,12 +396,14 @@ class NvlinkChannel : public IChannel {
   }
 
   bool async_flush() const override { return true; }
+  bool relays_to_group() const override { return pull_ && dst_.ext_int("mcn", 0) > 1; }
 
   std::string metrics_prefix() const {
     std::ostringstream ss;
     ss << "Proto=nvlink,Mode=" << (pull_ ? "pull" : "push") << ",Path=" << (fused_ ? "fused" : (walk_ ? "walk" : "descriptors"))
        << ",OriginSbNum=" << origin_blocks_ << ",MergedSbNum=" << merged_blocks_ << ",BytesPerLayer=" << moved_bytes_per_layer_
        << ",Tiles=" << (walk_ ? walk_plan_.bulk_units + walk_plan_.simt_units : plan_.total_tiles);
+    if (fanout_ > 1) ss << ",Fanout=" << fanout_;
     return ss.str();
   }
 
@@ -495,7 +519,7 @@ class NvlinkChannel : public IChannel {
     const PeerMemInfo mine = export_peer_mem_info(ctx_);
     const PeerEvents evs = export_peer_events(ctx_);
     if (evs.events.size() != ctx_->num_layers()) return false;
-    if (!dst_map_.same_process())
+    if (!same_process_)
       for (const auto& e : evs.events)
         if (!e.has_handle) return false;      // layer events were not created for interprocess use
     std::string msg(RPC_HEADER, '\0');
@@ -595,8 +619,10 @@ class NvlinkChannel : public IChannel {
   int src_shape_{0}, dst_shape_{0};
   bool dst_mx_{false};
   bool dst_remote_{false};       // the destination cache lives on another GPU
+  bool same_process_{false};
   // what the current batch is
   bool fused_{false}, walk_{false};
+  uint32_t fanout_{0};           // > 1: the destination relays this batch to that many workers of its group
   DeviceAttnParams params_{};
   PackedPlan plan_;
   WalkPlan walk_plan_;

@@ -63,6 +63,7 @@ uint32_t PullSession::open(const char* body, size_t len) {
     std::vector<uint64_t> dst_caps;
     for (size_t t = 0; t < ctx_->block_sizes().size(); ++t) dst_caps.push_back(ctx_->tensor_capacity(t));
     eng_ = std::make_unique<BatchEngine>(cfg, src_map_.ptrs(), ctx_->layer_data_address(), std::move(src_caps), std::move(dst_caps));
+    if (!ctx_->multicast_address().empty()) eng_->set_multicast(ctx_->multicast_address());
   } catch (const std::exception& ex) {
     LOG(ERROR) << "pull session: open failed: " << ex.what();
     return WIRE_INTERNAL;
@@ -80,6 +81,8 @@ void PullSession::on_plan(uint64_t seq, const char* body, size_t len) {
     if (!eng_ || len < sizeof(PullPlanHead)) throw std::runtime_error("bad plan message");
     memcpy(&head_, body, sizeof(PullPlanHead));
     if (head_.blob_bytes != len - sizeof(PullPlanHead)) throw std::runtime_error("plan blob length mismatch");
+    if (head_.fanout != 0 && (head_.kind != PULL_KIND_WALK || !eng_->has_multicast()))
+      throw std::runtime_error("fan-out asked of a worker whose cache is not in a multicast group");
     BatchEngine::SlotView sl = eng_->begin(head_.blob_bytes);
     memcpy(sl.h_plan, body + sizeof(PullPlanHead), head_.blob_bytes);
     eng_->upload(head_.blob_bytes);
@@ -107,7 +110,10 @@ void PullSession::on_layers(uint64_t seq, const char* body, size_t len) {
   try {
     if (head_.kind == PULL_KIND_WALK) {
       // one launch for the range, behind the last of its layer events (recorded in order on one stream)
-      eng_->launch_walk(head_.walk, head_.n_ops, head_.pool_len, lo, hi, eng_->next_stage(), events_[hi - 1]);
+      const size_t stage = eng_->next_stage();
+      eng_->launch_walk(head_.walk, head_.n_ops, head_.pool_len, lo, hi, stage, events_[hi - 1]);
+      // the bytes are here: the switch delivers them to the other members of the group from this GPU
+      if (head_.fanout != 0) eng_->launch_walk_fanout(head_.walk, head_.n_ops, head_.pool_len, lo, hi, stage);
     } else if (one_launch) {
       eng_->launch_attn(head_.attn, attn_plan_, lo, hi, 0, events_[hi - 1]);
     } else {

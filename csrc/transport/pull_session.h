@@ -29,7 +29,7 @@ struct PullPlanHead {
   uint32_t pool_len;         // walk
   uint32_t n_reqs;           // attn
   uint32_t total_tiles;      // attn
-  uint32_t reserved;
+  uint32_t fanout;           // walk: replicate what the ops wrote to the destination's multicast group
   uint64_t pool_offset;      // attn
   uint64_t blob_bytes;
   KvtWalkCounts walk;

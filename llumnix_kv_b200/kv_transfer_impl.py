@@ -278,15 +278,22 @@ class KVTransferClient:
         self._call("start_req_send", metas, stepid, substepid)
 
     def submit_req_send2(self, dst_inst_id, dst_worker_id, req_id, seen_tokens, new_tokens, has_last_token,
-                         src_block_ids, dst_block_ids, dst_worker_info=None, stepid: int = DEFAULT_STEPID):
-        """Queue tokens ``[seen, seen+new)`` of a request for the coming step (does not start any transfer)."""
+                         src_block_ids, dst_block_ids, dst_worker_info=None, stepid: int = DEFAULT_STEPID,
+                         fanout: int = 0):
+        """Queue tokens ``[seen, seen+new)`` of a request for the coming step (does not start any transfer).
+
+        ``fanout=k`` (k > 1) asks the destination worker to relay the bytes to k workers of its NVLink
+        multicast group (itself included) instead of this rank sending k copies: for data that those
+        workers hold identically, at the same block ids (MLA latent caches, replicated KV heads).  The
+        destination must advertise a group of at least k (``mc_layers`` / ``mc_size`` of its server);
+        the send-done report then counts k completions."""
         if not self._inited:
             raise RuntimeError("KVTransferClient not inited")
         if isinstance(src_block_ids, list) and src_block_ids and isinstance(src_block_ids[0], int):
             assert isinstance(dst_block_ids, list) and dst_block_ids and isinstance(dst_block_ids[0], int)
             src_block_ids, dst_block_ids = [src_block_ids], [dst_block_ids]
         self._call("submit_req_send2", dst_inst_id, dst_worker_id, req_id, seen_tokens, new_tokens, has_last_token,
-                   src_block_ids, dst_block_ids, dst_worker_info, stepid, 0)
+                   src_block_ids, dst_block_ids, dst_worker_info, stepid, 0, int(fanout))
 
     def submit_delta_send(self, req_id, seen_tokens, new_tokens, has_last_token, stepid: int = DEFAULT_STEPID):
         if not self._inited:
@@ -400,7 +407,12 @@ class KVTransferServer:
                  kda_page_stride: int = 0, attn_pack_size: int = 1, num_ple_layers: int = 0,
                  ple_block_group: int = 0, ple_conv_elem_size: int = 1, ple_conv_state_shape=None,
                  ple_conv_channel_dims=None, cache_shape: int = -1, mx_scaled: bool = False,
-                 process_global: bool = False):
+                 process_global: bool = False, mc_layers=None, mc_size: int = 0):
+        """``mc_layers`` / ``mc_size``: this worker's cache tensors are members of an NVLink multicast
+        group of ``mc_size`` workers (a tensor-parallel decode group whose caches live in one symmetric
+        allocation, ``parallel.nvls.MulticastKVCache``); ``mc_layers`` gives the multicast address of
+        every tensor, shaped like ``layers``.  A sender may then hand this worker a request for the
+        whole group (``submit_req_send2(..., fanout=k)``)."""
         block_bytes, token_bytes, layers, layer_num_blocks, device_id = _normalise(block_bytes, token_bytes, layers)
         layer_addrs = [[t.data_ptr() for t in layer] for layer in layers]
         kw = _hybrid_kwargs(num_kv_heads, num_gdn_layers, indexer_blk_ntpb, hybrid_indexer_token_size,
@@ -408,6 +420,10 @@ class KVTransferServer:
                             gdn_conv_channel_dims, kda_conv_dim_first, hybrid_attn_token_size, kda_page_stride,
                             attn_pack_size, num_ple_layers, ple_block_group, ple_conv_elem_size,
                             ple_conv_state_shape, ple_conv_channel_dims)
+        if mc_layers is not None and mc_size > 1:
+            mc = [[int(a)] if isinstance(a, int) else [int(x) for x in a] for a in mc_layers]
+            assert len(mc) == len(layer_addrs) and all(len(a) == len(b) for a, b in zip(mc, layer_addrs))
+            kw["mc_layers"], kw["mc_size"] = mc, int(mc_size)
         ops_protocols = [p.to_ops_protocol() for p in protocols]
         logger.info("init kvt server: instid=%s tpsize=%s wid=%s wrank=%s blockbytes=%s tokenbytes=%s naming=%s "
                     "protocols=%s device_id=%s num_blocks=%s num_layers=%s cache_shape=%s", inst_id, tp_size,

@@ -598,3 +598,25 @@ def test_server_refuses_oversized_frames_and_oversized_shm_attach(ops):
         seg.close()
         seg.unlink()
         srv.stop()
+
+
+def test_relayed_transfer_is_refused_by_host_transports(ops, sink):
+    """fanout=k hands the request to one worker of a multicast group for all k: only the NVLINK transport
+    with a pull session on a worker that advertises such a group can do that.  Anything else fails the
+    request (once, not k times) instead of reporting k deliveries after one."""
+    src, dst = make_cache(8), make_cache()
+    srv = KVTransferServer("D|0|1", 1, 0, 0, BLK, TOK, "fake://", dst, [PT.TCP], num_kv_heads=H, cache_shape=2)
+    cli = KVTransferClient("P|0|1", 1, 0, 0, BLK, TOK, "fake://", src, [PT.TCP], num_kv_heads=H, cache_shape=2)
+    try:
+        cli.submit_req_send2("D|0|1", 0, "fan", 0, 8, True, [1], [2], srv.worker_info(), stepid=1, fanout=3)
+        cli.start_send_step(1, 1)
+        for layer in range(L):
+            cli.record_event(layer)
+        cli.flush_send_step()
+        cli.drain()
+        reports = [r for m in sink.wait_for(1) if m[0] == 0x20181219 for r in m[3]]
+        assert [(r[0], r[2]) for r in reports] == [("fan", 500)] * 3       # one report per worker it stood for
+        assert cli.failed_batches() == 1
+        assert all(float(d.abs().sum()) == 0.0 for d in dst)
+    finally:
+        srv.stop()

@@ -172,3 +172,125 @@ def test_multicast_fanout_reaches_every_member():
             p.join(120)
     assert sorted(reports) == list(range(world))
     assert all(not e for e in reports.values()), reports
+
+
+# ---- the relay inside the transport ----------------------------------------------------------------
+# Rank 0 is a prefill worker (TP 1), ranks 1..k the tensor-parallel workers of ONE decode instance whose MLA-like
+# caches (two tensors per layer, identical on every rank) live in symmetric allocations bound to a multicast
+# group.  The prefill worker hands each request to ONE decode worker with fanout=k; that worker's pull session
+# loads the bytes over NVLink and stores them to the whole group.  Every decode rank must end up with both
+# requests, the prefill worker's link having carried each of them once.
+R_LAYERS, R_TOKS, R_NTPB, R_BLOCKS = 3, [132, 656], 64, 24
+R_SIZES = [t * R_NTPB for t in R_TOKS]
+
+
+def _relay_src(layer: int, t: int, dev) -> torch.Tensor:
+    g = torch.Generator(device="cpu").manual_seed(1000 + 10 * layer + t)
+    return torch.randint(1, 255, (R_SIZES[t] * R_BLOCKS,), dtype=torch.uint8, generator=g).to(dev)
+
+
+def _relay_requests(k: int):
+    # (request id, relay worker, tokens, prefill blocks, decode blocks)
+    return [("ra", 0, 150, [3, 9, 4], [7, 2, 11]), ("rb", 1 % k, 64 + 17, [12, 1], [5, 20]), ("rc", (k - 1), 40, [6], [15])]
+
+
+def _relay_child(rank: int, world: int, port: int, tmp: str, q) -> None:
+    errors = []
+    caches, srv, cli = [], None, None
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      BLLM_KVTRANS_QUIET_ENV="1")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    import datetime
+
+    limit = datetime.timedelta(seconds=120)
+    dist.init_process_group("nccl", device_id=dev, timeout=limit)
+    host = dist.new_group(backend="gloo", timeout=limit)   # ranks wait for one another on the host, never inside a NCCL kernel
+    k = world - 1
+    d_group = dist.new_group(list(range(1, world)))
+    try:
+        from llumnix_kv_b200.kv_transfer_impl import KVTransferClient, KVTransferProtocolType as PT, KVTransferServer
+        from llumnix_kv_b200.parallel.nvls import MulticastKVCache
+
+        inst = f"D|0|{k}"
+        if rank > 0:
+            caches = [MulticastKVCache(R_LAYERS, R_SIZES[t] * R_BLOCKS, d_group, dev) for t in range(2)]
+            layers = [[caches[t].layers[layer] for t in range(2)] for layer in range(R_LAYERS)]
+            mc = [[caches[t].mc_ptr + layer * caches[t].layer_bytes for t in range(2)] for layer in range(R_LAYERS)]
+            srv = KVTransferServer(inst, k, rank - 1, rank - 1, list(R_SIZES), list(R_TOKS), f"file:{tmp}", layers, [PT.NVLINK],
+                                   cache_shape=4, num_kv_heads=1, mc_layers=mc, mc_size=k)
+        dist.barrier(group=host)
+        if rank == 0:
+            src = [[_relay_src(layer, t, dev) for t in range(2)] for layer in range(R_LAYERS)]
+            cli = KVTransferClient("P|0|1", 1, 0, 0, list(R_SIZES), list(R_TOKS), f"file:{tmp}", src, [PT.NVLINK], cache_shape=4,
+                                   num_kv_heads=1)
+            for rid, relay, tokens, sb, db in _relay_requests(k):
+                cli.submit_req_send2(inst, relay, rid, 0, tokens, True, [sb], [db], None, stepid=1, fanout=k)
+            cli.start_send_step(1, 1)
+            for layer in range(R_LAYERS):
+                cli.record_event(layer)
+            cli.flush_send_step()
+            if not cli.wait_inflight(0, 30.0):
+                errors.append("the relayed step did not complete")
+            if cli.failed_batches():
+                errors.append(f"{cli.failed_batches()} batches failed")
+        dist.barrier(group=host)
+        if rank > 0:
+            torch.cuda.synchronize()
+            for layer in range(R_LAYERS):
+                for t in range(2):
+                    want = torch.zeros(R_SIZES[t] * R_BLOCKS, dtype=torch.uint8, device=dev)
+                    ref = _relay_src(layer, t, dev)
+                    for _, _, tokens, sb, db in _relay_requests(k):
+                        for i, (s, d) in enumerate(zip(sb, db)):
+                            n = min(R_NTPB, tokens - i * R_NTPB) * R_TOKS[t]
+                            want[d * R_SIZES[t]:d * R_SIZES[t] + n] = ref[s * R_SIZES[t]:s * R_SIZES[t] + n]
+                    if not torch.equal(caches[t].layers[layer], want):
+                        bad = (caches[t].layers[layer] != want).nonzero()
+                        errors.append(f"rank {rank} layer {layer} tensor {t}: {bad.numel()} bytes differ, first at {int(bad[0])}")
+        dist.barrier(group=host)
+    except Exception:
+        errors.append(f"rank {rank}: {traceback.format_exc()}")
+    finally:
+        try:
+            if srv is not None:
+                srv.stop()
+            dist.barrier(group=host)
+            for c in caches:
+                c.close()
+        except Exception:
+            errors.append(f"rank {rank} teardown: {traceback.format_exc()}")
+        q.put((rank, errors))
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def test_transport_relays_a_request_through_the_decode_groups_multicast(tmp_path):
+    n = torch.cuda.device_count()
+    if n < 3:
+        pytest.skip("needs three GPUs: a prefill worker and a decode group of two")
+    world = min(n, 4)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_relay_child, args=(r, world, port, str(tmp_path), q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    reports = {}
+    try:
+        for _ in range(world):
+            rank, errors = q.get(timeout=300)
+            reports[rank] = errors
+    finally:
+        for p in procs:
+            p.join(150)
+            if p.is_alive():
+                p.kill()
+    assert sorted(reports) == list(range(world))
+    assert all(not e for e in reports.values()), reports
