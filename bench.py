@@ -51,7 +51,7 @@ def parse_args():
     ap.add_argument("--streams", type=int, default=8, help="transfer streams the layers alternate over")
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--small", action="store_true", help="tiny case for profiler captures")
-    ap.add_argument("--mode", default="p2d", choices=["p2d", "kvstore", "migration", "ttft", "quant", "gdn", "mla", "fanout", "linkprobe"],
+    ap.add_argument("--mode", default="p2d", choices=["p2d", "kvstore", "migration", "ttft", "quant", "gdn", "mla", "fanout", "relay", "linkprobe"],
                     help="p2d: prefill->decode transfer (the headline); kvstore: host-DRAM store save/load GB/s; "
                          "migration: decode->decode latency against the number of blocks; fanout (4 or 8 GPUs): replicated "
                          "MLA pages to a decode TP group, unicast against the NVLS relay; linkprobe: the transfer "
@@ -228,6 +228,22 @@ def main():
                                            "every decode TP rank", "seq_len": res["tokens"],
                                   "parallelism": f"1 prefill GPU -> decode TP{world - 1} group",
                                   "paths": "unicast peer stores per rank vs one peer copy + multimem.st relay through NVSwitch"},
+                              "result": res}))
+        dist.destroy_process_group()
+        return
+    if args.mode == "relay":
+        from benchmarks.support import relay_bandwidth
+
+        assert world >= 3, "--mode relay needs --gpus 4 or 8 (one prefill worker, a decode instance on the others)"
+        res = relay_bandwidth(K, rank, world, dev, tokens=2048 if args.small else 8192, n_layers=8 if args.small else 61)
+        if rank == 0:
+            print(json.dumps({"metric": "replicated_kv_relay_speedup", "value": res["speedup"], "unit": "x", "n_gpus": args.gpus,
+                              "higher_is_better": True, "dtype": "bytes", "config": {
+                                  "model": "deepseek-v3.2-like MLA caches (indexer 132 B/token + latent 656 B/token, 64-token "
+                                           "blocks), identical on every decode TP rank",
+                                  "parallelism": f"1 prefill worker -> decode instance TP{world - 1}",
+                                  "api": "KVTransferClient.submit_req_send2(..., fanout=k): the destination worker's pull "
+                                         "session relays to its NVLink multicast group"},
                               "result": res}))
         dist.destroy_process_group()
         return

@@ -1286,3 +1286,146 @@ def post_checks(K, rank: int, world: int, dev) -> dict:
         res = hybrid_state_bandwidth(K, rank, world, dev, which=which, tokens=2048, steps=1, warmup=1, small=True)
         out[f"{which}_through_engine"] = bool(res["verified"])
     return out
+
+
+def relay_bandwidth(K, rank: int, world: int, dev, tokens: int = 8192, n_layers: int = 61, requests_per_worker: int = 1,
+                    steps: int = 6, warmup: int = 2) -> dict:
+    """Replicated MLA-like caches (indexer 132 B/token + latent 656 B/token, 64-token blocks, the same bytes
+    on every tensor-parallel decode rank) from ONE prefill worker (rank 0) to a decode instance of
+    k = world - 1 workers, through KVTransferClient both ways:
+
+      unicast   the prefill worker submits every request to each of the k decode workers
+                (what the reference's P<D fan-out does, blade_kvt/hybrid_connector/kvtbackend.py:637-664):
+                k copies cross its link;
+      relay     the prefill worker submits every request once, with fanout=k, to one decode worker (round
+                robin over the group); that worker's pull session loads the bytes and stores what it wrote to
+                the group's NVLink multicast mapping: one copy crosses the prefill worker's link.
+
+    A step moves k * requests_per_worker requests of ``tokens`` tokens.  Timed on the prefill rank (the steps
+    end when their completion records have been read), one step in flight ahead; every decode rank verifies
+    every request in every layer afterwards."""
+    import datetime
+    import tempfile
+
+    import torch.distributed as dist
+
+    from llumnix_kv_b200.kv_transfer_impl import KVTransferClient, KVTransferProtocolType as PT, KVTransferServer
+    from llumnix_kv_b200.parallel.nvls import MulticastKVCache
+
+    assert world >= 3
+    k = world - 1
+    toks, ntpb = [132, 656], 64
+    sizes = [t * ntpb for t in toks]
+    n_req = k * requests_per_worker
+    blocks_per_req = (tokens + ntpb - 1) // ntpb
+    n_blocks = n_req * blocks_per_req + 2
+    d_group = dist.new_group(list(range(1, world)))
+    tmp = [tempfile.mkdtemp() if rank == 0 else None]
+    HS.all_gather_object(got := [None] * world, tmp[0])
+    naming = f"file:{got[0]}"
+    rng = random.Random(29)
+    ids_s, ids_d = rng.sample(range(1, n_blocks), n_req * blocks_per_req), rng.sample(range(1, n_blocks), n_req * blocks_per_req)
+    reqs = [(i, ids_s[i * blocks_per_req:(i + 1) * blocks_per_req], ids_d[i * blocks_per_req:(i + 1) * blocks_per_req])
+            for i in range(n_req)]
+
+    def src_tensor(layer: int, t: int) -> torch.Tensor:
+        g = torch.Generator(device=dev)
+        g.manual_seed(31 * layer + t + 1)
+        return torch.randint(1, 255, (sizes[t] * n_blocks,), dtype=torch.uint8, device=dev, generator=g)
+
+    inst = f"DR|0|{k}"
+    caches, srv, cli = [], None, None
+    if rank > 0:
+        caches = [MulticastKVCache(n_layers, sizes[t] * n_blocks, d_group, dev) for t in range(2)]
+        layers = [[caches[t].layers[layer] for t in range(2)] for layer in range(n_layers)]
+        mc = [[caches[t].mc_ptr + layer * caches[t].layer_bytes for t in range(2)] for layer in range(n_layers)]
+        srv = KVTransferServer(inst, k, rank - 1, rank - 1, list(sizes), list(toks), naming, layers, [PT.NVLINK], cache_shape=4,
+                               num_kv_heads=1, mc_layers=mc, mc_size=k)
+    HS.barrier()
+    bytes_per_req = sum(toks) * tokens * n_layers
+    result = {"decode_workers": k, "requests_per_step": n_req, "tokens_per_request": tokens, "layers": n_layers,
+              "bytes_per_request": bytes_per_req}
+    seq = [0]
+    if rank == 0:
+        src = [[src_tensor(layer, t) for t in range(2)] for layer in range(n_layers)]
+        cli = KVTransferClient("PR|0|1", 1, 0, 0, list(sizes), list(toks), naming, src, [PT.NVLINK], cache_shape=4, num_kv_heads=1)
+        stream = torch.cuda.current_stream(dev)
+
+        def step(relay: bool, ahead: int):
+            seq[0] += 1
+            stepid = 9000 + seq[0]
+            for i, sb, db in reqs:
+                if relay:
+                    cli.submit_req_send2(inst, i % k, f"q{seq[0]}.{i}", 0, tokens, True, [sb], [db], None, stepid=stepid, fanout=k)
+                else:
+                    for w in range(k):
+                        cli.submit_req_send2(inst, w, f"q{seq[0]}.{i}", 0, tokens, True, [sb], [db], None, stepid=stepid)
+            cli.start_send_step(stepid, 1)
+            for layer in range(n_layers):
+                cli.record_event(layer, stream)
+            cli.flush_send_step()
+            assert cli.wait_inflight(ahead, 60.0)
+
+        def timed(relay: bool) -> float:
+            for _ in range(warmup):
+                step(relay, 1)
+            assert cli.wait_inflight(0, 60.0)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                step(relay, 1)
+            assert cli.wait_inflight(0, 60.0)
+            e1.record(stream)
+            torch.cuda.synchronize()
+            assert cli.failed_batches() == 0, "transfer steps failed"
+            return e0.elapsed_time(e1) / steps
+
+    def verify(tag: str) -> bool:
+        ok = True
+        if rank > 0:
+            torch.cuda.synchronize()
+            for layer in range(n_layers):
+                for t in range(2):
+                    ref, have = src_tensor(layer, t), caches[t].layers[layer]
+                    for _, sb, db in reqs:
+                        s_idx = torch.tensor(sb, device=dev, dtype=torch.int64)
+                        d_idx = torch.tensor(db, device=dev, dtype=torch.int64)
+                        full = tokens // ntpb
+                        a = ref.view(n_blocks, sizes[t])[s_idx[:full]]
+                        b = have.view(n_blocks, sizes[t])[d_idx[:full]]
+                        ok = ok and bool(torch.equal(a, b))
+                        rest = tokens - full * ntpb
+                        if rest:
+                            n = rest * toks[t]
+                            ok = ok and bool(torch.equal(ref.view(n_blocks, sizes[t])[sb[full], :n],
+                                                         have.view(n_blocks, sizes[t])[db[full], :n]))
+            for c in caches:
+                c.buffer.zero_()
+            torch.cuda.synchronize()
+        t_ok = torch.tensor([1.0 if ok else 0.0])
+        HS.all_reduce(t_ok, op=dist.ReduceOp.MIN)
+        return bool(t_ok.item())
+
+    for name, relay in (("unicast", False), ("relay", True)):
+        ms = timed(relay) if rank == 0 else 0.0
+        HS.barrier()
+        t_ms = torch.tensor([ms], dtype=torch.float64)
+        HS.all_reduce(t_ms, op=dist.ReduceOp.MAX)
+        ms = float(t_ms.item())
+        verified = verify(name)
+        HS.barrier()
+        copies = 1 if relay else k
+        result[name] = {"ms_per_step": round(ms, 3), "verified": verified,
+                        "prefill_egress_bytes_per_step": copies * n_req * bytes_per_req,
+                        "prefill_egress_GBps": round(copies * n_req * bytes_per_req / ms / 1e6, 1) if ms > 0 else 0.0,
+                        "delivered_GBps": round(k * n_req * bytes_per_req / ms / 1e6, 1) if ms > 0 else 0.0}
+    result["speedup"] = round(result["unicast"]["ms_per_step"] / result["relay"]["ms_per_step"], 2) \
+        if result["relay"]["ms_per_step"] > 0 else 0.0
+    if srv is not None:
+        srv.stop()
+    HS.barrier()
+    for c in caches:
+        c.close()
+    HS.barrier()
+    return result

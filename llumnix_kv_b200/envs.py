@@ -17,6 +17,7 @@ _DEFS: dict[str, tuple[Callable[[str], Any], Any]] = {
     "VLLM_ENABLE_BYPASS_SUBSTEP": (lambda v: v not in ("0", "", "false"), False),
     "VLLM_KVT_MAX_DELAY_MS": (float, 3000.0),
     "VLLM_KVT_GONE_REQ_TTL_S": (int, 60),
+    "VLLM_KVT_NVLS_FANOUT": (lambda v: v not in ("0", "", "false"), True),   # relay replicated caches through a decode group's multicast
     "VLLM_PD_TRY_CONNECT_TIMEOUT_SECONDS": (float, 120.0),
     "VLLM_PD_CONNMANAGER_CAP": (int, 512),
     "VLLM_KVS_IO_TIMEOUT_SECONDS": (float, 30.0),

@@ -173,6 +173,49 @@ def reg_naming(naming_cli, cfg: VllmConfig) -> None:
     naming_cli.store(f"endpoint{info.dprank}", info.serialize())
 
 
+def multicast_kwargs(layers) -> dict:
+    """Server arguments that advertise the worker's NVLink multicast group, when every cache tensor it
+    registers lives in a ``parallel.nvls.MulticastKVCache`` of this process (the decode group allocated
+    its caches symmetrically); empty otherwise."""
+    import torch
+
+    from llumnix_kv_b200.parallel.nvls import multicast_address_of
+
+    rows = [[layer] if isinstance(layer, torch.Tensor) else list(layer) for layer in layers]
+    found = [[multicast_address_of(t) if t.is_cuda else None for t in row] for row in rows]
+    if not found or any(f is None for row in found for f in row):
+        return {}
+    sizes = {f[1] for row in found for f in row}
+    if len(sizes) != 1 or next(iter(sizes)) < 2:
+        return {}
+    return {"mc_layers": [[f[0] for f in row] for row in found], "mc_size": next(iter(sizes))}
+
+
+def choose_relay(reqid: str, dist: list, total_kv_heads: int, src_tpsize: int) -> Optional[int]:
+    """Index into ``dist`` (the decode workers this prefill rank would serve one by one) of the worker
+    that receives the request for all of them, or None when each must be served separately.
+
+    A relay needs: several targets; the same bytes for every one of them, which is the case when the
+    prefill rank holds a single KV head or the MLA latent (``total_kv_heads <= src_tpsize``: the decode
+    ranks it serves all replicate that head); every target advertising a multicast group that covers
+    them (``mcn`` in its worker info); ``VLLM_KVT_NVLS_FANOUT`` not switched off.  The choice is a pure
+    function of the request id, so every chunk of a request takes the same relay."""
+    import zlib
+
+    if len(dist) < 2 or not envs.VLLM_KVT_NVLS_FANOUT or total_kv_heads <= 0 or total_kv_heads > src_tpsize:
+        return None
+    for _, _, winfo in dist:
+        if not isinstance(winfo, str) or ";mcn=" not in winfo and ":mcn=" not in winfo:
+            return None
+        try:
+            group = int(winfo.split("mcn=", 1)[1].split(";", 1)[0])
+        except ValueError:
+            return None
+        if group < len(dist):
+            return None
+    return zlib.crc32(reqid.encode()) % len(dist)
+
+
 def get_dist(d_inst_id: str, src_tprank: int, src_tpsize: int) -> list:
     """(dst instance, dst worker id, dst tp rank) targets of this prefill rank.  One target, except
     P TP < D TP where one rank fans out to D_tp / P_tp ranks.  Empty: TP sizes do not divide."""
@@ -373,6 +416,10 @@ class PBackend(HybridBackend):
 
     def _loop(self):
         return self._engine.get_hybrid_sched_loop()
+
+    def _total_kv_heads(self) -> int:
+        mc = self._cfg.model_config
+        return 1 if getattr(mc, "use_mla", False) else int(getattr(mc, "num_kv_heads", 0) or 0)
 
     def _kvt_signals_per_worker(self, dinfo: KVTDInfo) -> int:
         """A prefill rank that fans out to several decode ranks reports once per target."""
@@ -814,6 +861,14 @@ class PBackend(HybridBackend):
                 failed.append(m.reqid)
                 continue
             try:
+                relay = choose_relay(m.reqid, dist, self._total_kv_heads(), tp)
+                if relay is not None:
+                    # one decode worker receives the request and stores it to its group through NVSwitch:
+                    # this rank's link carries the bytes once instead of len(dist) times
+                    name, wid, winfo = dist[relay]
+                    self._kvt_cli.submit_req_send2(name, wid, m.reqid, m.seen_tokens, m.new_tokens, m.has_last_token,
+                                                   m.p_block_ids, m.d_block_ids, winfo, stepid=meta.stepid, fanout=len(dist))
+                    continue
                 for name, wid, winfo in dist:
                     self._kvt_cli.submit_req_send2(name, wid, m.reqid, m.seen_tokens, m.new_tokens, m.has_last_token,
                                                    m.p_block_ids, m.d_block_ids, winfo, stepid=meta.stepid)
@@ -1128,6 +1183,7 @@ class DBackend(HybridBackend):
         llumnix_kv_b200.set_envs()
         rank = self._worker.get_tensor_model_parallel_rank()
         args = build_kvt_args(self, kv_caches, rank)
+        args.update(multicast_kwargs(args["layers"]))
         self._kvt_srv = KVTransferServer(mx_scaled=self._cfg.cache_config.mx_scaled, **args)
         winfo = self._kvt_srv.worker_info()
         logger.info("register_kv_caches (decode). worker_id=%s winfo=%s", args["worker_id"], winfo)

@@ -34,6 +34,19 @@ from llumnix_kv_b200 import load_ops
 
 _FLAG_BYTES = 256     # completion word + padding, at the end of the symmetric buffer
 
+_live_caches: "list[MulticastKVCache]" = []     # caches of this process, for multicast_address_of()
+
+
+def multicast_address_of(tensor: torch.Tensor):
+    """``(multicast address, group size)`` of a tensor that lives inside a MulticastKVCache of this
+    process, else None.  The transfer server uses it to tell senders that this worker can relay a
+    request to its whole group."""
+    ptr, end = tensor.data_ptr(), tensor.data_ptr() + tensor.numel() * tensor.element_size()
+    for c in _live_caches:
+        if c.buffer is not None and c.local_ptr <= ptr and end <= c.local_ptr + c.num_layers * c.layer_bytes:
+            return c.mc_ptr + (ptr - c.local_ptr), c.world
+    return None
+
 
 class MulticastKVCache:
     """``num_layers`` cache tensors of ``layer_bytes`` each, in one symmetric allocation of the group."""
@@ -74,6 +87,7 @@ class MulticastKVCache:
         self._ops = load_ops()
         self._closed = False
         self._keep = collections.deque(maxlen=256)
+        _live_caches.append(self)
 
     # ---- the member that received the blocks -----------------------------------------------------------
     def _ids(self, block_ids) -> torch.Tensor:
@@ -145,6 +159,8 @@ class MulticastKVCache:
         if self._closed:
             return
         self._closed = True
+        if self in _live_caches:
+            _live_caches.remove(self)
         torch.cuda.synchronize(self.device)
         self._dist.barrier(self.group)
         self.layers = []

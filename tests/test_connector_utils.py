@@ -209,3 +209,29 @@ def test_set_envs_fills_defaults_without_overriding(monkeypatch):
     assert os.environ["BLLM_KVTRANS_RDMA_SP"] == "2"                 # two connections per target, as the reference's Python layer
     assert os.environ["BLLM_KVTRANS_FSNAMING_KEEPALIVE_S"] == "7"    # what the operator set stays
     monkeypatch.delenv("BLLM_KVTRANS_RDMA_SP", raising=False)
+
+
+def test_relay_choice_for_replicated_caches(monkeypatch):
+    """One decode worker takes a request for its whole group only when every target holds the same bytes
+    (a single KV head or the MLA latent per prefill rank), every target advertises a multicast group that
+    covers them, and the knob is on; the choice depends on the request id alone."""
+    from llumnix_kv_b200.hybrid_connector.kvtbackend import choose_relay, multicast_kwargs
+
+    def winfo(mcn):
+        tail = f";mcn={mcn}" if mcn else ""
+        return f"D|0|4,0,4,0,4096,256,8,2,4,16,0,1,0,10.0.0.1,x:dev=0;heads=1{tail};pid=1;port=2;shape=4"
+
+    four = [("D", i, winfo(4)) for i in range(4)]
+    r = choose_relay("req-1", four, total_kv_heads=1, src_tpsize=1)
+    assert r is not None and 0 <= r < 4 and r == choose_relay("req-1", four, 1, 1)      # stable per request
+    assert {choose_relay(f"req-{i}", four, 1, 1) for i in range(64)} == {0, 1, 2, 3}     # spread over the group
+    assert choose_relay("req-1", four, total_kv_heads=8, src_tpsize=2) is None           # distinct head slices
+    assert choose_relay("req-1", four, total_kv_heads=2, src_tpsize=2) is not None       # one head per prefill rank
+    assert choose_relay("req-1", four[:1], 1, 1) is None                                 # a single target
+    assert choose_relay("req-1", [("D", i, winfo(2)) for i in range(4)], 1, 1) is None   # group smaller than the targets
+    assert choose_relay("req-1", [("D", 0, winfo(4)), ("D", 1, winfo(0))], 1, 1) is None
+    assert choose_relay("req-1", [("D", 0, winfo(4)), ("D", 1, None)], 1, 1) is None     # worker info unknown here
+    monkeypatch.setenv("VLLM_KVT_NVLS_FANOUT", "0")
+    assert choose_relay("req-1", four, 1, 1) is None
+    import torch
+    assert multicast_kwargs([torch.zeros(16)]) == {}                                     # plain memory: nothing advertised
