@@ -172,6 +172,20 @@ def main():
     if args.mode == "quant":
         from benchmarks.support import quant_reshard_bandwidth
 
+        if world in (4, 8) and args.e2e_path == "engine":
+            from benchmarks.support import tp_mismatch_fp8_engine
+
+            res = tp_mismatch_fp8_engine(K, rank, world, dev, n_layers=8 if args.small else 80,
+                                         min_tokens=512 if args.small else 4096, max_tokens=2048 if args.small else 16384)
+            if rank == 0:
+                print(json.dumps({"metric": "tp_mismatch_fp8_transfer_GBps", "value": res["aggregate_src_GBps"], "unit": "GB/s",
+                                  "n_gpus": args.gpus, "higher_is_better": True, "dtype": "bf16->mxfp8", "config": {
+                                      "model": "llama-3-70b-kv (80L, 8 kv heads, 128d, block 16), bf16 NHD -> block-scaled e4m3 HND",
+                                      "parallelism": f"prefill TP{world // 2} -> 2 x decode TP{max(world // 4, 1)}",
+                                      "seq_len": "uniform 4k-16k", "api": "KVTransferClient (engine, NVLINK transport)"},
+                                  "result": res}))
+            dist.destroy_process_group()
+            return
         if world > 1:
             from benchmarks.support import quant_reshard_nvlink
 
@@ -191,6 +205,20 @@ def main():
             print(json.dumps({"metric": "tp_mismatch_fp8_transfer_GBps", "unit": "GB/s", "n_gpus": 1, "dtype": "bf16->mxfp8",
                               "config": {"model": "llama-3-70b-kv (80L, 8 kv heads, 128d), prefill TP4 rank -> decode TP2 rank, "
                                                   "NHD -> HND", "seq_len": args.tokens}, "result": res}))
+        return
+    if args.mode == "kvstore" and world > 1:
+        from benchmarks.support import kvstore_concurrent
+
+        res = kvstore_concurrent(K, rank, world, dev, n_requests=32 if args.small else 256,
+                                 min_tokens=512 if args.small else 4096, max_tokens=2048 if args.small else 16384,
+                                 store_gib=2.0 if args.small else 24.0, n_layers=4 if args.small else 32)
+        if rank == 0:
+            print(json.dumps({"metric": "kvstore_shared_save_load_GBps", "value": res["save"]["aggregate_GBps"], "unit": "GB/s",
+                              "n_gpus": args.gpus, "higher_is_better": True, "dtype": "bf16", "config": {
+                                  "model": "llama-3-8b-kv (32L, 8 kv heads, 128d, bf16, block 16)",
+                                  "requests": "256 concurrent, 4k-16k tokens, one pinned host-DRAM store shared by all ranks"},
+                              "result": res}))
+        dist.destroy_process_group()
         return
     if args.mode == "kvstore":
         from benchmarks.support import kvstore_bandwidth

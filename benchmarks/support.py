@@ -1429,3 +1429,249 @@ def relay_bandwidth(K, rank: int, world: int, dev, tokens: int = 8192, n_layers:
         c.close()
     HS.barrier()
     return result
+
+
+def tp_mismatch_fp8_engine(K, rank: int, world: int, dev, n_layers: int = 80, steps: int = 16, warmup: int = 4,
+                           min_tokens: int = 4096, max_tokens: int = 16384) -> dict:
+    """Llama-3-70B-shaped KV (80 layers, 8 KV heads, head_dim 128, block 16) with a TP mismatch, through
+    KVTransferClient: the first world/2 ranks are the tensor-parallel workers of ONE prefill instance
+    (TP = world/2: 4 on eight GPUs, each holding 8/TP heads in bf16, NHD); the other ranks form TWO decode
+    instances of TP = world/4 (2 on eight GPUs, each worker holding 8/TP heads as block-scaled e4m3 with one
+    scale per 32 values, HND).  Every step sends one request of a random prompt length (uniform
+    ``min_tokens``..``max_tokens``) to the decode instances in turn; the heads are resharded and quantised
+    inside the transfer kernel.  Timed on the prefill ranks, one step in flight ahead, max over ranks; the
+    decode workers compare the last request they received with the quantiser's oracle."""
+    import datetime
+
+    import torch.distributed as dist
+
+    from llumnix_kv_b200.kv_transfer_impl import KVTransferClient, KVTransferProtocolType as PT, KVTransferServer
+    from llumnix_kv_b200.ops.p2d_attn import mx_quantize_reference
+
+    assert world in (4, 8), "prefill TP world/2 against two decode instances of TP world/4"
+    n_p = world // 2
+    d_tp = max(n_p // 2, 1)
+    p_heads, d_heads = 8 // n_p, 8 // d_tp
+    group = n_p // d_tp                         # prefill ranks that feed one decode worker
+    sender = rank < n_p
+    inst_of = lambda r: (r - n_p) // d_tp       # decode rank -> instance 0 / 1
+    rng = random.Random(41)
+    lengths = [rng.randint(min_tokens, max_tokens) for _ in range(warmup + steps)]
+    max_blk = (max_tokens + BLOCK - 1) // BLOCK
+    pool = max_blk + 8
+    src_l = AttnLayout(CacheShape.FLASH, pool, BLOCK, p_heads, HEAD_DIM, 2)
+    dst_l = AttnLayout(CacheShape.FLASHINFER, pool, BLOCK, d_heads, HEAD_DIM, 1, mx_scaled=True)
+    tables = []
+    for n_tok in lengths:
+        nb = (n_tok + BLOCK - 1) // BLOCK
+        tables.append((rng.sample(range(1, pool), nb), rng.sample(range(1, pool), nb)))
+    srv = cli = None
+    winfo = None
+    dst = src = None
+    if not sender:
+        dst = [dst_l.alloc(dev) for _ in range(n_layers)]
+        srv = KVTransferServer(f"D70{inst_of(rank)}|0|{d_tp}", d_tp, (rank - n_p) % d_tp, (rank - n_p) % d_tp, dst_l.block_bytes,
+                               dst_l.token_bytes, "fake://", dst, [PT.NVLINK], num_kv_heads=8, cache_shape=5, mx_scaled=True)
+        winfo = srv.worker_info()
+    infos = [None] * world
+    HS.all_gather_object(infos, winfo)
+    HS.barrier()
+    ms = 0.0
+    moved = sum(lengths[warmup:]) * src_l.token_bytes * n_layers        # source bytes this prefill rank sends in the timed steps
+    if sender:
+        src = [src_l.alloc(dev, fill="normal", seed=1000 * rank + i) for i in range(n_layers)]
+        cli = KVTransferClient(f"P70|0|{n_p}", n_p, rank, rank, src_l.block_bytes, src_l.token_bytes, "fake://", src, [PT.NVLINK],
+                               num_kv_heads=8, cache_shape=2)
+        stream = torch.cuda.current_stream(dev)
+        d_local = rank // group                 # decode tp rank this prefill rank feeds
+
+        def step(i: int):
+            inst = i % 2
+            d_rank = n_p + inst * d_tp + d_local
+            sb, db = tables[i]
+            stepid = 5000 + i
+            cli.submit_req_send2(f"D70{inst}|0|{d_tp}", d_local, f"m{i}", 0, lengths[i], True, sb, db, infos[d_rank], stepid=stepid)
+            cli.start_send_step(stepid, 1)
+            for layer in range(n_layers):
+                cli.record_event(layer, stream)
+            cli.flush_send_step()
+            assert cli.wait_inflight(1, 60.0)
+
+        for i in range(warmup):
+            step(i)
+        assert cli.wait_inflight(0, 60.0)
+    HS.barrier()
+    torch.cuda.synchronize()
+    if sender:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(warmup, warmup + steps):
+            step(i)
+        assert cli.wait_inflight(0, 60.0)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        assert cli.failed_batches() == 0, "transfer steps failed"
+        ms = e0.elapsed_time(e1)
+    t = torch.tensor([ms], dtype=torch.float64)
+    HS.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    HS.barrier()
+    ok = True
+    if not sender:
+        torch.cuda.synchronize()
+        inst = inst_of(rank)
+        last = max(i for i in range(warmup + steps) if i % 2 == inst)
+        sb, db = tables[last]
+        nb = min(lengths[last] // BLOCK, 48)
+        d_local = (rank - n_p) % d_tp
+        for layer in (0, n_layers - 1):
+            for j in range(group):
+                p_rank = d_local * group + j
+                s0 = src_l.alloc(dev, fill="normal", seed=1000 * p_rank + layer)
+                x = src_l.view(s0, torch.bfloat16)[torch.tensor(sb[:nb], device=dev)].float()
+                codes, exps = mx_quantize_reference(x)
+                # both views are [block, kv, slot, head, ...] whatever the memory order
+                got_c = dst_l.view(dst[layer], torch.uint8)[torch.tensor(db[:nb], device=dev)][:, :, :, j * p_heads:(j + 1) * p_heads]
+                got_e = dst_l.scale_view(dst[layer])[torch.tensor(db[:nb], device=dev)][:, :, :, j * p_heads:(j + 1) * p_heads]
+                ok = ok and bool(torch.equal(got_c, codes)) and bool(torch.equal(got_e, exps))
+    t = torch.tensor([1.0 if ok else 0.0])
+    HS.all_reduce(t, op=dist.ReduceOp.MIN)
+    if srv is not None:
+        srv.stop()
+    HS.barrier()
+    agg = n_p * moved / (ms * 1e-3) / 1e9 if ms > 0 else 0.0
+    return {"prefill_tp": n_p, "decode_instances": 2, "decode_tp": d_tp, "layers": n_layers, "steps": steps,
+            "prompt_tokens_min_max": [min(lengths[warmup:]), max(lengths[warmup:])],
+            "src_bytes_per_prefill_rank": moved, "ms_total": round(ms, 3), "ms_per_step": round(ms / max(steps, 1), 3),
+            "aggregate_src_GBps": round(agg, 1), "src_GBps_per_prefill_rank": round(agg / n_p, 1),
+            "link_GBps_per_prefill_rank": round(agg / n_p * dst_l.token_bytes / d_heads * p_heads / src_l.token_bytes, 1),
+            "steps_in_flight": 2, "verified": bool(t.item())}
+
+
+def kvstore_concurrent(K, rank: int, world: int, dev, n_requests: int = 256, min_tokens: int = 4096, max_tokens: int = 16384,
+                       store_gib: float = 24.0, n_layers: int = 32) -> dict:
+    """256 requests of 4k-16k tokens (Llama-3-8B KV shape, bf16) saved to and loaded from ONE pinned host-DRAM
+    store that every rank of the box attaches to.  The requests are dealt round robin to the ranks; every rank
+    saves its requests back to back (reserve -> gather kernel on the store's stream -> seal), all ranks at the
+    same time, then loads back the requests of its NEIGHBOUR rank that are still resident (the store holds
+    ``store_gib`` GiB and evicts least recently used blocks), which shows the sharing between ranks.  Device-timed
+    per rank on the store's stream, aggregate = all bytes / slowest rank's time; the loaded blocks are compared
+    with what the saving rank held."""
+    import os
+
+    import torch.distributed as dist
+
+    from llumnix_kv_b200 import load_ops
+    from llumnix_kv_b200.kvstore import PinnedKVStore
+
+    rng = random.Random(53)
+    lengths = [rng.randint(min_tokens, max_tokens) for _ in range(n_requests)]
+    max_blk = (max_tokens + BLOCK - 1) // BLOCK
+    lay = AttnLayout(CacheShape.FLASH, 2 * max_blk + 1, BLOCK, KV_HEADS, HEAD_DIM, 2)
+    slot_bytes = lay.block_bytes * n_layers
+    n_slots = int(store_gib * (1 << 30) // slot_bytes)
+    name = "kvx_shared_bench"
+    names = [None] * world
+    HS.all_gather_object(names, f"{name}_{os.getpid()}" if rank == 0 else None)
+    name = names[0]
+
+    def fill(owner: int):
+        return [lay.alloc(dev, fill="normal", seed=100 * owner + i) for i in range(n_layers)]
+
+    layers = fill(rank)
+    st = None
+    if rank == 0:
+        st = PinnedKVStore(name, lay, layers, 0, 1, n_slots, create=True)
+    HS.barrier()
+    if rank != 0:
+        st = PinnedKVStore(name, lay, layers, 0, 1, n_slots, create=False)
+    HS.barrier()
+    mine = [i for i in range(n_requests) if i % world == rank]
+    theirs = [i for i in range(n_requests) if i % world == (rank + 1) % world]
+
+    def tokens_of(i: int):
+        return list(range(i * 100000, i * 100000 + lengths[i]))
+
+    def blocks_of(i: int, base: int):
+        nb = lengths[i] // BLOCK            # whole blocks are what a store keeps
+        return list(range(base, base + nb))
+
+    # ---- save: all ranks at once -------------------------------------------------------------------
+    saved_bytes = 0
+    torch.cuda.synchronize()
+    HS.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(st.stream)
+    pending = []
+    for i in mine:
+        blocks = blocks_of(i, 1)
+        keys = st.keys(tokens_of(i), len(blocks))
+        new, _full = st.reserve(keys)
+        if new:
+            ev = st.save_layers(0, n_layers, [blocks[j] for j, _ in new], [s for _, s in new])
+            pending.append((ev, [keys[j] for j, _ in new]))
+            saved_bytes += len(new) * slot_bytes
+        while len(pending) > 2:             # seal a request once its gather has finished; two in flight
+            ev, ks = pending.pop(0)
+            ev.synchronize()
+            st.seal(ks)
+    for ev, ks in pending:
+        ev.synchronize()
+        st.seal(ks)
+    e1.record(st.stream)
+    torch.cuda.synchronize()
+    save_ms = e0.elapsed_time(e1)
+    st.check_status()
+    HS.barrier()
+    # ---- load what the neighbour saved and is still resident --------------------------------------
+    ref = fill((rank + 1) % world)
+    loaded_bytes, hits, asked, ok = 0, 0, 0, True
+    torch.cuda.synchronize()
+    HS.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(st.stream)
+    checks = []
+    for i in reversed(theirs):
+        blocks = blocks_of(i, 1)
+        keys = st.keys(tokens_of(i), len(blocks))
+        asked += len(keys)
+        slots = st.pin(keys)                # leading resident blocks, protected from eviction while they are read
+        if not slots:
+            continue
+        dst_blocks = list(range(max_blk + 1, max_blk + 1 + len(slots)))
+        ev = st.load_layers(0, n_layers, dst_blocks, slots)
+        hits += len(slots)
+        loaded_bytes += len(slots) * slot_bytes
+        ev.synchronize()
+        st.unpin(keys[:len(slots)])
+        if len(checks) < 2:
+            n = min(len(slots), 32)
+            for layer in (0, n_layers - 1):
+                a = lay.view(layers[layer], torch.int16)[torch.tensor(dst_blocks[:n], device=dev)]
+                b = lay.view(ref[layer], torch.int16)[torch.tensor(blocks[:n], device=dev)]
+                ok = ok and bool(torch.equal(a, b))
+            checks.append(i)
+    e1.record(st.stream)
+    torch.cuda.synchronize()
+    load_ms = e0.elapsed_time(e1)
+    st.check_status()
+    stats = st.stats()
+    t = torch.tensor([save_ms, load_ms, float(saved_bytes), float(loaded_bytes), float(hits), float(asked), 0.0 if ok else 1.0],
+                     dtype=torch.float64)
+    tmax = t.clone()
+    HS.all_reduce(tmax, op=dist.ReduceOp.MAX)
+    tsum = t.clone()
+    HS.all_reduce(tsum, op=dist.ReduceOp.SUM)
+    HS.barrier()
+    st.close()
+    HS.barrier()
+    if rank == 0:
+        load_ops().KvStore.unlink(name)
+    return {"requests": n_requests, "ranks": world, "prompt_tokens_min_max": [min(lengths), max(lengths)],
+            "store_GiB": store_gib, "slot_bytes": slot_bytes, "slots": n_slots,
+            "save": {"bytes": int(tsum[2]), "ms_slowest_rank": round(float(tmax[0]), 1),
+                     "aggregate_GBps": round(float(tsum[2]) / float(tmax[0]) / 1e6, 1) if tmax[0] > 0 else 0.0},
+            "load_from_neighbour_rank": {"bytes": int(tsum[3]), "ms_slowest_rank": round(float(tmax[1]), 1),
+                                         "aggregate_GBps": round(float(tsum[3]) / float(tmax[1]) / 1e6, 1) if tmax[1] > 0 else 0.0,
+                                         "blocks_resident_of_asked": [int(tsum[4]), int(tsum[5])]},
+            "evictions": int(stats.get("evictions", 0)), "verified": float(tmax[6]) == 0.0}
