@@ -115,10 +115,15 @@ class PinnedKVStore:
                 self.stream = torch.cuda.Stream(self.device)
                 eng_ptrs = [t.data_ptr() for t in self.layers]
                 page_ptrs = [dev_ptr + i * self.page_bytes for i in range(self.num_layers)]
+                # BLLM_KVSTORE_TMA=1: tiles travel through the TMA engine (tensor maps over the mapped host arena)
+                # instead of the SIMT warps; bf16 pages only (the fp8 pages are written by the quantiser)
+                tma = os.environ.get("BLLM_KVSTORE_TMA", "0") not in ("0", "") and not fp8
+                self.uses_tma = tma
                 self._save_xfer = AttnTransfer(engine_layout, self.page, eng_ptrs, page_ptrs, self.device,
-                                               mode=MODE_BF16_TO_MXFP8 if fp8 else MODE_COPY, use_tma=False, simt_tile=2)
+                                               mode=MODE_BF16_TO_MXFP8 if fp8 else MODE_COPY, use_tma=tma, simt_tile=2)
                 self._load_xfer = AttnTransfer(self.page, engine_layout, page_ptrs, eng_ptrs, self.device,
-                                               mode=MODE_MXFP8_TO_BF16 if fp8 else MODE_COPY, use_tma=False, simt_tile=2)
+                                               mode=MODE_MXFP8_TO_BF16 if fp8 else MODE_COPY, use_tma=tma, simt_tile=2)
+                self.uses_tma = tma and self._save_xfer.use_tma and self._load_xfer.use_tma
 
     # ---- index ----------------------------------------------------------------------------------
     def keys(self, token_ids: Sequence[int], n_blocks: int) -> List[bytes]:
