@@ -142,11 +142,24 @@ __global__ void __launch_bounds__(256) kvt_walk_fanout_kernel(const __grid_const
     char* mc = reinterpret_cast<char*>(mc_ptrs[idx]) + pc.dst_off;
     const uintptr_t a = reinterpret_cast<uintptr_t>(own) | reinterpret_cast<uintptr_t>(mc) | (uintptr_t)pc.dst_step | pc.len;
     if ((a & 15u) == 0) {
+      // four independent 16-byte loads per lane before the first store: a unit is a few KiB, so the loop is
+      // short and its latency, not its instruction count, is what a warp spends
       const uint32_t cpp = pc.len >> 4, n16 = cpp * pc.n;
-      for (uint32_t i = lane; i < n16; i += 32) {
-        const uint32_t j = i / cpp, c = i - j * cpp;
-        const int64_t off = (int64_t)j * pc.dst_step + ((int64_t)c << 4);
-        mc_st_16(mc + off, ld_nc_16(own + off));
+      for (uint32_t i0 = lane; i0 < n16; i0 += 128) {
+        int4 v[4];
+        int64_t off[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t i = i0 + 32u * k;
+          if (i < n16) {
+            const uint32_t j = i / cpp, c = i - j * cpp;
+            off[k] = (int64_t)j * pc.dst_step + ((int64_t)c << 4);
+            v[k] = ld_nc_16(own + off[k]);
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (i0 + 32u * k < n16) mc_st_16(mc + off[k], v[k]);
       }
     } else if ((a & 3u) == 0) {
       const uint32_t cpp = pc.len >> 2, n4 = cpp * pc.n;
