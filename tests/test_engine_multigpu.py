@@ -199,6 +199,21 @@ def main():
             cli2.record_event(layer)
         cli2.flush_send_step()
         assert cli2.wait_inflight(0, 30.0) and cli2.failed_batches() == 0
+        # a relayed request (fanout) to a worker that advertises no multicast group fails cleanly, on the host,
+        # and the channel keeps serving
+        cli2.submit_req_send2("D|0|1", 0, "fan", 0, 16, True, [1], [2], None, stepid=2, fanout=2)
+        cli2.start_send_step(2, 1)
+        for layer in range(T.L):
+            cli2.record_event(layer)
+        cli2.flush_send_step()
+        assert cli2.wait_inflight(0, 30.0) and cli2.failed_batches() == 1
+        rid, sb, db, total = reqs[0]
+        cli2.submit_req_send2("D|0|1", 0, rid + ".again", 0, total, True, sb, db, None, stepid=3)
+        cli2.start_send_step(3, 1)
+        for layer in range(T.L):
+            cli2.record_event(layer)
+        cli2.flush_send_step()
+        assert cli2.wait_inflight(0, 30.0) and cli2.failed_batches() == 1
         go.set()
         got = [torch.from_numpy(a) for a in result.get(timeout=120)]
         for i in range(T.L):
