@@ -173,6 +173,19 @@ def reg_naming(naming_cli, cfg: VllmConfig) -> None:
     naming_cli.store(f"endpoint{info.dprank}", info.serialize())
 
 
+def _worker_process_envs(cfg) -> None:
+    """A worker that owns its process (one engine worker per process, as vLLM runs them) publishes its cache
+    shape and the scheduler's send-done address through the environment, where the process-global engine
+    functions of the reference binding look for them (``kvt_args.set_worker_envs``).  Off by default: several
+    engines can share a process here, and each client is given its address explicitly; switched on with
+    ``kv_connector_extra_config["kvt_worker_process_envs"]``."""
+    if not cfg.kv_transfer_config.get_from_extra_config("kvt_worker_process_envs", False):
+        return
+    from .kvt_args import set_worker_envs
+
+    set_worker_envs(cfg.cache_config.cache_shape, scheduler_rpc_host(cfg), sched_rpc_server_port(cfg))
+
+
 def multicast_kwargs(layers) -> dict:
     """Server arguments that advertise the worker's NVLink multicast group, when every cache tensor it
     registers lives in a ``parallel.nvls.MulticastKVCache`` of this process (the decode group allocated
@@ -782,6 +795,7 @@ class PBackend(HybridBackend):
         from llumnix_kv_b200.kv_transfer_impl import KVTransferClient
 
         llumnix_kv_b200.set_envs()
+        _worker_process_envs(self._cfg)
         args = build_kvt_args(self, kv_caches, self._worker.get_tensor_model_parallel_rank())
         self._kvt_cli = KVTransferClient(send_done_addr=self._send_done_addr, **args)
         self._layer_index = {name: extract_layer_index(name) for name in kv_caches}
@@ -1181,6 +1195,7 @@ class DBackend(HybridBackend):
         from llumnix_kv_b200.kv_transfer_impl import KVTransferServer
 
         llumnix_kv_b200.set_envs()
+        _worker_process_envs(self._cfg)
         rank = self._worker.get_tensor_model_parallel_rank()
         args = build_kvt_args(self, kv_caches, rank)
         args.update(multicast_kwargs(args["layers"]))
