@@ -128,6 +128,18 @@ __device__ __forceinline__ Resolved resolve(const KvtWalkLaunch& p, const KvtWal
   return r;
 }
 
+// Work item w = layer * units_per_layer + unit, with 32-bit divisions where the numbers allow.
+__device__ __forceinline__ void split_unit(uint64_t w, uint64_t per_layer, uint64_t* unit, uint32_t* layer) {
+  if (((w | per_layer) >> 32) == 0) {
+    const uint32_t q = (uint32_t)w / (uint32_t)per_layer;
+    *layer = q;
+    *unit = (uint32_t)w - q * (uint32_t)per_layer;
+  } else {
+    *layer = (uint32_t)(w / per_layer);
+    *unit = w % per_layer;
+  }
+}
+
 __device__ __forceinline__ bool bulk_ok(const Resolved& r) {
   return r.n == 1 && !r.zero && r.len != 0 &&
          ((reinterpret_cast<uintptr_t>(r.src) | reinterpret_cast<uintptr_t>(r.dst) | r.len) & 15u) == 0;
@@ -211,7 +223,12 @@ __global__ void __launch_bounds__(256) kvt_walk_kernel(const __grid_constant__ K
       r.src = nullptr;
       r.dst = nullptr;
       r.zero = false;
-      if (w < bulk_total) r = resolve(p, bulk_ops, p.n_bulk_ops, w % p.bulk_units, p.layer_begin + (uint32_t)(w / p.bulk_units), true);
+      if (w < bulk_total) {
+        uint64_t unit;
+        uint32_t layer;
+        split_unit(w, p.bulk_units, &unit, &layer);
+        r = resolve(p, bulk_ops, p.n_bulk_ops, unit, p.layer_begin + layer, true);
+      }
       const unsigned any = __ballot_sync(0xffffffffu, w < bulk_total);
       unsigned mask = __ballot_sync(0xffffffffu, w < bulk_total && bulk_ok(r));
       if (any == 0u) break;
@@ -255,13 +272,19 @@ __global__ void __launch_bounds__(256) kvt_walk_kernel(const __grid_constant__ K
     for (uint64_t k = w0;; k += nw) {
       const uint64_t w = blockIdx.x + k * (uint64_t)gridDim.x;
       if (w >= simt_total) break;
-      const Resolved r = resolve(p, simt_ops, p.n_simt_ops, w % p.simt_units, p.layer_begin + (uint32_t)(w / p.simt_units), lane == 0);
+      uint64_t unit;
+      uint32_t layer;
+      split_unit(w, p.simt_units, &unit, &layer);
+      const Resolved r = resolve(p, simt_ops, p.n_simt_ops, unit, p.layer_begin + layer, lane == 0);
       if (r.n != 0) warp_pieces(r, lane);
     }
     for (uint64_t k = w0;; k += nw) {
       const uint64_t w = blockIdx.x + k * (uint64_t)gridDim.x;
       if (w >= bulk_total) break;
-      const Resolved r = resolve(p, bulk_ops, p.n_bulk_ops, w % p.bulk_units, p.layer_begin + (uint32_t)(w / p.bulk_units), false);
+      uint64_t unit;
+      uint32_t layer;
+      split_unit(w, p.bulk_units, &unit, &layer);
+      const Resolved r = resolve(p, bulk_ops, p.n_bulk_ops, unit, p.layer_begin + layer, false);
       if (r.n != 0 && !bulk_ok(r)) warp_pieces(r, lane);
     }
   }

@@ -32,12 +32,25 @@ KVT_HD KvtWalkPieces kvt_walk_unit(const KvtWalkOp& op, const uint32_t* pool, ui
   out.n = 0;
   out.error = 0;
   uint32_t seg = 0;
-  if (op.flags & KVT_WALK_BULK) {
-    seg = (uint32_t)(local_unit % op.segs);
-    local_unit /= op.segs;
+  uint32_t inner_idx;
+  uint64_t slot;
+  if ((local_unit >> 32) == 0) {
+    // the usual case: 32-bit divisions (a 64-bit one costs several times as much on the device)
+    uint32_t u = (uint32_t)local_unit;
+    if (op.flags & KVT_WALK_BULK) {
+      seg = u % op.segs;
+      u /= op.segs;
+    }
+    inner_idx = u % op.inner_total;
+    slot = (uint64_t)(op.pos_lo / op.run) + u / op.inner_total;
+  } else {
+    if (op.flags & KVT_WALK_BULK) {
+      seg = (uint32_t)(local_unit % op.segs);
+      local_unit /= op.segs;
+    }
+    inner_idx = (uint32_t)(local_unit % op.inner_total);
+    slot = op.pos_lo / op.run + local_unit / op.inner_total;
   }
-  uint32_t inner_idx = (uint32_t)(local_unit % op.inner_total);
-  const uint64_t slot = op.pos_lo / op.run + local_unit / op.inner_total;
   const uint64_t lo = slot * op.run, hi = lo + op.run;
   const uint32_t p0 = (uint32_t)(lo > op.pos_lo ? lo : op.pos_lo);
   const uint32_t p1 = (uint32_t)(hi < op.pos_hi ? hi : op.pos_hi);
