@@ -88,11 +88,17 @@ KVT_HD KvtWalkPieces kvt_walk_unit(const KvtWalkOp& op, const uint32_t* pool, ui
   if (op.flags & KVT_WALK_CONTIG) {
     uint64_t piece = (uint64_t)n * op.len;
     if (op.flags & KVT_WALK_BULK) {
-      const uint64_t off = (uint64_t)seg * KVT_WALK_SEG;
+      // the piece in op.segs segments of (nearly) one size, each a multiple of 16 bytes and at most KVT_WALK_SEG:
+      // a 41984-byte page is six segments of about 7 KiB, not five of 8 KiB and a 1 KiB tail that would hold a
+      // pipeline stage for a fraction of the bytes
+      uint64_t seg_len;
+      if ((piece >> 32) == 0) seg_len = (((uint32_t)piece + op.segs - 1) / op.segs + 15u) & ~15u;
+      else seg_len = ((piece + op.segs - 1) / op.segs + 15u) & ~(uint64_t)15u;
+      const uint64_t off = (uint64_t)seg * seg_len;
       if (off >= piece) return out;
       out.src_off += (int64_t)off;
       out.dst_off += (int64_t)off;
-      piece = piece - off < KVT_WALK_SEG ? piece - off : KVT_WALK_SEG;
+      piece = piece - off < seg_len ? piece - off : seg_len;
     }
     out.len = (uint32_t)piece;
     out.n = 1;
