@@ -8,6 +8,7 @@ The numbers are the expectations of the reference's own tests, read as data:
     Kimi-K3 page with its replicated MLA prefix (kvtransfer/tests/parse_block_kda_test.cpp:78-260).
 """
 import pytest
+import torch
 
 from test_planner import mk_worker
 
@@ -111,3 +112,40 @@ def test_kimi_k3_p_eq_d_copies_mla_prefix_and_kda_page(K):
     got = K.plan_ipc_blocks(src, dst, 8, [("k3", 0, 1, True, [[1], [3]], [[2], [4]])])[0][0]
     assert got == [(3 * 64, 4 * 64, 8),     # replicated MLA: one manager block of 4 tokens x 2 bytes
                    (1 * 64, 2 * 64, 64)]    # full KDA page
+
+
+def test_bulk_pieces_are_cut_into_even_segments(K):
+    """A 41984-byte MLA page travels as six segments of about 7 KiB (multiples of 16 bytes, none above the
+    8 KiB stage), not five of 8 KiB and a 1 KiB tail; the 8448-byte indexer page as two of 4224."""
+    from llumnix_kv_b200.kv_transfer_impl import KVTransferClient, KVTransferProtocolType as PT, KVTransferServer
+
+    toks, ntpb, nb = [132, 656], 64, 8
+    sizes = [t * ntpb for t in toks]
+
+    def alloc():
+        return [[torch.zeros(bs * nb, dtype=torch.uint8) for bs in sizes] for _ in range(2)]
+
+    cli = KVTransferClient("P|0|1", 1, 0, 0, list(sizes), list(toks), "fake://", alloc(), [PT.TCP], cache_shape=4, num_kv_heads=1)
+    srv = KVTransferServer("D|0|1", 1, 0, 0, list(sizes), list(toks), "fake://", alloc(), [PT.TCP], cache_shape=4, num_kv_heads=1)
+    try:
+        pw, dw = K.WorkerInfo.from_string(cli.worker_info()), K.WorkerInfo.from_string(srv.worker_info())
+        for w in (pw, dw):
+            w.num_kv_heads = 1
+        plan = K.plan_walk(pw, dw, 4, [("x", 0, 192, True, [[3, 5, 6]], [[2, 4, 7]])])
+        caps = [bs * nb for bs in sizes]
+        pieces = plan.expand(caps, caps)
+        by_tensor = {0: [], 1: []}
+        for t, zero, so, do, n in pieces:
+            assert not zero and n % 16 == 0 and 0 < n <= 8192
+            by_tensor[t].append((so, do, n))
+        assert sorted(n for _, _, n in by_tensor[1]) == sorted([7008] * 5 * 3 + [6944] * 3)      # three latent pages
+        assert sorted(n for _, _, n in by_tensor[0]) == [4224] * 6                                 # three indexer pages
+        for t, src_b, dst_b in ((1, 3, 2), (1, 5, 4), (1, 6, 7), (0, 3, 2)):                       # the segments tile the page
+            segs = sorted(p for p in by_tensor[t] if src_b * sizes[t] <= p[0] < (src_b + 1) * sizes[t])
+            pos = src_b * sizes[t]
+            for so, do, n in segs:
+                assert so == pos and do - dst_b * sizes[t] == so - src_b * sizes[t]
+                pos += n
+            assert pos == (src_b + 1) * sizes[t]
+    finally:
+        srv.stop()
