@@ -32,9 +32,12 @@ bool finalize_one(KvtWalkOp& op) {
   op.segs = 1;
   const uint64_t piece = contig ? static_cast<uint64_t>(op.run) * op.len : op.len;
   if (piece > 0xffffffffull) return false;
-  bool al = aligned16(op.len) && aligned16(op.src_block_stride) && aligned16(op.dst_block_stride) &&
-            aligned16(op.src_kb_stride) && aligned16(op.dst_kb_stride) && aligned16(op.src_pos_stride) &&
-            aligned16(op.dst_pos_stride) && aligned16(op.src_add) && aligned16(op.dst_add);
+  // A contiguous unit starts at a multiple of run x len inside its kernel block, so whole 16-byte words are
+  // asked of the unit, not of a single position (rows of 132 bytes form 8448-byte pages).  A unit cut short by
+  // the request's first or last position may still start or end off a word: the kernel checks every segment's
+  // addresses and hands those to its SIMT warps.
+  bool al = aligned16(piece) && aligned16(op.src_block_stride) && aligned16(op.dst_block_stride) &&
+            aligned16(op.src_kb_stride) && aligned16(op.dst_kb_stride) && aligned16(op.src_add) && aligned16(op.dst_add);
   for (uint32_t k = 0; k < op.n_inner; ++k) al = al && aligned16(op.inner[k].src_stride) && aligned16(op.inner[k].dst_stride);
   if (contig && !zero && al && piece >= 2048) {
     op.flags |= KVT_WALK_BULK;
