@@ -15,7 +15,7 @@
 namespace kvx {
 
 namespace {
-constexpr uint64_t kMagic = 0x4b5653544f524532ull;  // "KVSTORE2"
+constexpr uint64_t kMagic = 0x4b5653544f524533ull;  // "KVSTORE3"
 constexpr uint32_t kEmpty = 0, kWriting = 1, kSealed = 2;
 constexpr uint64_t kPage = 4096;
 
@@ -35,10 +35,12 @@ struct KvStore::Header {
   uint32_t n_free;
   uint32_t n_entries;
   uint64_t clock;  // LRU stamp source
+  uint32_t lru_head, lru_tail;  // slots of the most / least recently used SEALED entries (kNoSlot: empty list)
   uint64_t hits, misses, evictions, expired, reserve_fail, discards;
 };
 
 constexpr uint32_t kPinOwners = 4;
+constexpr uint32_t kNoSlot = 0xffffffffu;
 
 struct KvStore::Entry {
   uint64_t hi, lo;
@@ -80,7 +82,9 @@ KvStore* KvStore::open(const std::string& name, uint64_t slot_bytes, uint32_t n_
   while (cap < 2 * n_slots) cap <<= 1;
   const uint64_t table_off = round_up(sizeof(Header), 64);
   const uint64_t free_off = table_off + (uint64_t)cap * sizeof(Entry);
-  const uint64_t data_off = round_up(free_off + (uint64_t)n_slots * 4, kPage);
+  // after the free list, three arrays indexed by slot: the recency list's links and the bucket that owns the slot
+  const uint64_t links_off = free_off + (uint64_t)n_slots * 4;
+  const uint64_t data_off = round_up(links_off + (uint64_t)n_slots * 12, kPage);
   const uint64_t total = data_off + round_up(slot_bytes * n_slots, kPage);
 
   int fd;
@@ -127,6 +131,9 @@ KvStore* KvStore::open(const std::string& name, uint64_t slot_bytes, uint32_t n_
   s->hdr_ = reinterpret_cast<Header*>(map);
   s->table_ = reinterpret_cast<Entry*>(reinterpret_cast<uint8_t*>(map) + table_off);
   s->free_ = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(map) + free_off);
+  s->lru_prev_ = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(map) + links_off);
+  s->lru_next_ = s->lru_prev_ + n_slots;
+  s->slot_bucket_ = s->lru_next_ + n_slots;
   s->data_ = reinterpret_cast<uint8_t*>(map) + data_off;
   Header* h = s->hdr_;
   if (create) {
@@ -147,6 +154,7 @@ KvStore* KvStore::open(const std::string& name, uint64_t slot_bytes, uint32_t n_
     pthread_mutexattr_destroy(&at);
     for (uint32_t i = 0; i < n_slots; ++i) s->free_[i] = n_slots - 1 - i;  // pop order 0, 1, 2, ...
     h->n_free = n_slots;
+    h->lru_head = h->lru_tail = kNoSlot;
     __atomic_store_n(&h->magic, kMagic, __ATOMIC_RELEASE);
   } else {
     for (int spin = 0; spin < 500 && __atomic_load_n(&h->magic, __ATOMIC_ACQUIRE) != kMagic; ++spin) usleep(10000);
@@ -186,7 +194,31 @@ KvStore::Entry* KvStore::find(const StoreKey& key, bool for_insert) {
 
 // Removes an entry and closes the gap in its probe run (backward-shift deletion), so that the
 // table needs no tombstones.
+void KvStore::lru_unlink(uint32_t slot) {
+  const uint32_t p = lru_prev_[slot], n = lru_next_[slot];
+  if (p != kNoSlot) lru_next_[p] = n; else hdr_->lru_head = n;
+  if (n != kNoSlot) lru_prev_[n] = p; else hdr_->lru_tail = p;
+  lru_prev_[slot] = lru_next_[slot] = kNoSlot;
+}
+
+void KvStore::lru_push_front(uint32_t slot) {
+  lru_prev_[slot] = kNoSlot;
+  lru_next_[slot] = hdr_->lru_head;
+  if (hdr_->lru_head != kNoSlot) lru_prev_[hdr_->lru_head] = slot; else hdr_->lru_tail = slot;
+  hdr_->lru_head = slot;
+}
+
+// A sealed entry was used: it becomes the most recent one.
+void KvStore::touch(Entry* e) {
+  e->last_use = ++hdr_->clock;
+  if (e->state == kSealed && hdr_->lru_head != e->slot) {
+    lru_unlink(e->slot);
+    lru_push_front(e->slot);
+  }
+}
+
 void KvStore::free_entry(Entry* e) {
+  if (e->state == kSealed) lru_unlink(e->slot);
   free_[hdr_->n_free++] = e->slot;
   hdr_->n_entries--;
   const uint32_t mask = hdr_->table_cap - 1;
@@ -202,26 +234,31 @@ void KvStore::free_entry(Entry* e) {
     const bool between = hole <= j ? (home > hole && home <= j) : (home > hole || home <= j);
     if (!between) {
       table_[hole] = *c;
+      slot_bucket_[c->slot] = hole;     // the list finds an entry through its slot
       c->state = kEmpty;
       hole = j;
     }
   }
 }
 
-// Frees one unpinned sealed entry: an expired one if any, else the least recently used.
+// Frees one unpinned sealed entry.  The recency list is walked from its old end: the first unpinned entry is
+// the victim, unless one of the next few is past its lease, which then goes first.  A handful of list steps
+// whatever the size of the store (the table is never scanned).
 bool KvStore::evict_one(int64_t now) {
+  constexpr int kLookahead = 32;
   Entry* victim = nullptr;
   bool victim_expired = false;
-  for (uint32_t i = 0; i < hdr_->table_cap; ++i) {
-    Entry* e = &table_[i];
-    if (e->state != kSealed || e->pins != 0) continue;
-    const bool exp = e->expire_ns != 0 && e->expire_ns <= now;
-    if (exp) {
+  int seen = 0;
+  for (uint32_t s = hdr_->lru_tail; s != kNoSlot; s = lru_prev_[s]) {
+    Entry* e = &table_[slot_bucket_[s]];
+    if (e->state != kSealed || e->slot != s || e->pins != 0) continue;   // pinned: a reader is copying from it
+    if (e->expire_ns != 0 && e->expire_ns <= now) {
       victim = e;
       victim_expired = true;
       break;
     }
-    if (victim == nullptr || e->last_use < victim->last_use) victim = e;
+    if (victim == nullptr) victim = e;
+    if (++seen >= kLookahead) break;
   }
   if (victim == nullptr) return false;
   if (victim_expired)
@@ -247,7 +284,7 @@ uint32_t KvStore::lookup_prefix(const std::vector<StoreKey>& keys) {
       hdr_->misses++;
       break;
     }
-    e->last_use = ++hdr_->clock;
+    touch(e);
     hdr_->hits++;
     ++n;
   }
@@ -264,7 +301,7 @@ ReserveResult KvStore::reserve(const StoreKey& key, int64_t ttl_ms, uint32_t* sl
         hdr_->expired++;
         free_entry(e);
       } else {
-        e->last_use = ++hdr_->clock;
+        touch(e);
         if (ttl_ms > 0 && e->expire_ns != 0) e->expire_ns = now + ttl_ms * 1000000;  // a re-save renews the lease
         return ReserveResult::kExists;
       }
@@ -291,6 +328,8 @@ ReserveResult KvStore::reserve(const StoreKey& key, int64_t ttl_ms, uint32_t* sl
   e->owner_pid = (uint32_t)getpid();
   e->expire_ns = ttl_ms > 0 ? now + ttl_ms * 1000000 : 0;
   e->last_use = ++hdr_->clock;
+  slot_bucket_[e->slot] = (uint32_t)(e - table_);
+  lru_prev_[e->slot] = lru_next_[e->slot] = kNoSlot;      // joins the recency list when it is sealed
   hdr_->n_entries++;
   *slot = e->slot;
   return ReserveResult::kNew;
@@ -302,6 +341,7 @@ bool KvStore::seal(const StoreKey& key) {
   if (e == nullptr || e->state != kWriting || e->owner_pid != (uint32_t)getpid()) return false;
   e->state = kSealed;
   e->last_use = ++hdr_->clock;
+  lru_push_front(e->slot);
   return true;
 }
 
@@ -340,7 +380,7 @@ std::vector<uint32_t> KvStore::pin_prefix(const std::vector<StoreKey>& keys) {
       }
       if (e->pin_cnt[r] == 0 && spare == kPinOwners) spare = r;
     }
-    e->last_use = ++hdr_->clock;
+    touch(e);
     out.push_back(e->slot);
   }
   return out;
@@ -407,6 +447,7 @@ uint32_t KvStore::clear() {
     for (uint32_t i = 0; i < hdr_->n_slots; ++i) free_[i] = hdr_->n_slots - 1 - i;
     hdr_->n_free = hdr_->n_slots;
     hdr_->n_entries = 0;
+    hdr_->lru_head = hdr_->lru_tail = kNoSlot;
     return 0;
   }
   // a reader is still copying out of a pinned slot: drop everything else, entry by entry

@@ -88,6 +88,9 @@ class KvStore {
   Entry* find(const StoreKey& key, bool for_insert);
   void free_entry(Entry* e);
   bool evict_one(int64_t now);
+  void lru_unlink(uint32_t slot);
+  void lru_push_front(uint32_t slot);
+  void touch(Entry* e);
   int64_t now_ns() const;
 
   std::string name_;
@@ -96,6 +99,9 @@ class KvStore {
   Header* hdr_ = nullptr;
   Entry* table_ = nullptr;
   uint32_t* free_ = nullptr;
+  uint32_t* lru_prev_ = nullptr;      // per slot: neighbours in the recency list of sealed entries
+  uint32_t* lru_next_ = nullptr;
+  uint32_t* slot_bucket_ = nullptr;   // per slot: table bucket of the entry that owns it
   uint8_t* data_ = nullptr;
   int64_t clock_skew_ns_ = 0;
 };

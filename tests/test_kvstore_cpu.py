@@ -195,3 +195,69 @@ def test_pins_of_a_dead_reader_are_released_and_clear_keeps_pinned_slots(store):
     assert s.reserve(k(2))[0] == K.STORE_RESERVE_NEW             # freed slots are usable again
     s.unpin(k(1))
     assert s.reap_dead_readers() == 0 and s.clear() == 0 and s.stats()["used"] == 0
+
+
+def test_recency_list_matches_a_model_under_random_traffic(store):
+    """Evictions come from the recency list, never from a scan of the table.  Random reserve / seal / lookup /
+    discard / pin traffic against a model that keeps the same order: every eviction must take the model's
+    least recently used unpinned sealed key, through thousands of deletions that move entries between buckets."""
+    import random
+
+    K, s, _ = store          # 8 slots
+    rng = random.Random(7)
+    order: list = []         # sealed keys, least recent first
+    writing: set = set()
+    pinned: dict = {}
+    for step in range(6000):
+        i = rng.randrange(40)
+        op = rng.random()
+        if op < 0.45:
+            code, _slot = s.reserve(k(i))
+            if i in order:
+                assert code == K.STORE_RESERVE_EXISTS
+                order.remove(i)
+                order.append(i)
+            elif i in writing:
+                assert code == K.STORE_RESERVE_BUSY
+            else:
+                used = len(order) + len(writing)
+                if used == 8:
+                    victims = [x for x in order if pinned.get(x, 0) == 0]
+                    if not victims:
+                        assert code == K.STORE_RESERVE_FULL
+                        continue
+                    order.remove(victims[0])
+                    assert s.lookup_prefix(k(victims[0])) == 0, (step, victims[0])      # exactly that key went
+                assert code == K.STORE_RESERVE_NEW, (step, code)
+                writing.add(i)
+        elif op < 0.70:
+            if i in writing:
+                assert s.seal(k(i))
+                writing.discard(i)
+                order.append(i)
+        elif op < 0.85:
+            hit = s.lookup_prefix(k(i))
+            assert hit == (1 if i in order else 0)
+            if i in order:
+                order.remove(i)
+                order.append(i)
+        elif op < 0.92:
+            ok = s.discard(k(i))
+            assert ok == ((i in order and pinned.get(i, 0) == 0) or i in writing)
+            if ok:
+                writing.discard(i)
+                if i in order:
+                    order.remove(i)
+        elif op < 0.97:
+            got = s.pin_prefix(k(i))
+            assert len(got) == (1 if i in order else 0)
+            if i in order:
+                pinned[i] = pinned.get(i, 0) + 1
+                order.remove(i)
+                order.append(i)
+        else:
+            if pinned.get(i, 0) > 0:
+                s.unpin(k(i))
+                pinned[i] -= 1
+        st = s.stats()
+        assert st["used"] == len(order) + len(writing) and st["sealed"] == len(order), step
