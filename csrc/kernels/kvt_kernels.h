@@ -229,7 +229,8 @@ typedef struct KvtWalkLaunch {
   const uint64_t* dst_ptrs;    // device: the same for the destination (local / peer / host-mapped)
   uint32_t n_tensors;
   uint32_t layer_begin, layer_end;
-  uint32_t reserved;
+  uint32_t shape;              // launch shape, 0 = default: threads per CTA in the low 16 bits (a multiple of 32, at
+                               // least 64: one warp drives the bulk pipeline, the others are SIMT), pipeline stages above
   uint64_t src_cap[KVT_WALK_MAX_TENSORS];   // bytes of each tensor: every piece is checked against them
   uint64_t dst_cap[KVT_WALK_MAX_TENSORS];
   const KvtWalkOp* ops;        // device: [bulk ops][simt ops]

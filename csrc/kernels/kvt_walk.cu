@@ -305,10 +305,14 @@ extern "C" int kvt_launch_walk(const KvtWalkLaunch* args, int grid_ctas, void* s
   // four CTAs per SM, each with four 8 KiB segments in flight through the TMA engine and seven SIMT warps
   int grid = grid_ctas > 0 ? grid_ctas : 4 * sms;
   const uint64_t n_layers = a.layer_end - a.layer_begin;
-  const uint64_t most = (a.bulk_units > a.simt_units / 7 ? a.bulk_units : (a.simt_units + 6) / 7) * n_layers;
+  uint32_t threads = a.shape & 0xffffu, stages = a.shape >> 16;
+  if (threads == 0) threads = 256;
+  if (stages == 0) stages = 4;
+  if (threads < 64 || threads > 256 || (threads & 31u) != 0 || stages > kMaxStagesW) return (int)cudaErrorInvalidValue;
+  const uint64_t simt_warps = threads / 32 - 1;
+  const uint64_t most = (a.bulk_units > a.simt_units / simt_warps ? a.bulk_units : (a.simt_units + simt_warps - 1) / simt_warps) * n_layers;
   if ((uint64_t)grid > most && most > 0) grid = (int)most;
-  const uint32_t stages = 4;
   const size_t smem = (size_t)stages * KVT_WALK_SEG + kMaxStagesW * sizeof(uint64_t);
-  kvt_walk_kernel<<<grid, 256, smem, reinterpret_cast<cudaStream_t>(stream)>>>(a, stages);
+  kvt_walk_kernel<<<grid, threads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(a, stages);
   return (int)cudaGetLastError();
 }

@@ -291,6 +291,7 @@ void BatchEngine::launch_walk(const KvtWalkCounts& c, size_t n_ops, size_t pool_
   RTASSERT(a.n_tensors <= KVT_WALK_MAX_TENSORS && src_caps_.size() >= a.n_tensors && dst_caps_.size() >= a.n_tensors);
   a.layer_begin = static_cast<uint32_t>(lo);
   a.layer_end = static_cast<uint32_t>(hi);
+  a.shape = (static_cast<uint32_t>(std::max(0, env_walk_stages())) << 16) | (static_cast<uint32_t>(std::max(0, env_walk_threads())) & 0xffffu);
   for (uint32_t t = 0; t < a.n_tensors; ++t) {
     a.src_cap[t] = src_caps_[t];
     a.dst_cap[t] = dst_caps_[t];
