@@ -1589,6 +1589,32 @@ def kvstore_concurrent(K, rank: int, world: int, dev, n_requests: int = 256, min
     mine = [i for i in range(n_requests) if i % world == rank]
     theirs = [i for i in range(n_requests) if i % world == (rank + 1) % world]
 
+    # ---- the ceiling of this box for that traffic: every rank copies 1 GiB between its GPU and pinned host
+    #      memory at the same time (the GPUs share PCIe switches and the host's memory) ------------------------
+    def concurrent_copy(d2h: bool) -> float:
+        n = 1 << 30
+        h = torch.empty(n, dtype=torch.uint8, pin_memory=True)
+        d = torch.empty(n, dtype=torch.uint8, device=dev)
+        best = 1e30
+        for _ in range(3):
+            torch.cuda.synchronize()
+            HS.barrier()
+            c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            c0.record()
+            if d2h:
+                h.copy_(d, non_blocking=True)
+            else:
+                d.copy_(h, non_blocking=True)
+            c1.record()
+            torch.cuda.synchronize()
+            t_c = torch.tensor([c0.elapsed_time(c1)], dtype=torch.float64)
+            HS.all_reduce(t_c, op=dist.ReduceOp.MAX)
+            best = min(best, float(t_c.item()))
+        del h, d
+        return world * n / best / 1e6
+
+    ceil_d2h, ceil_h2d = concurrent_copy(True), concurrent_copy(False)
+
     def tokens_of(i: int):
         return list(range(i * 100000, i * 100000 + lengths[i]))
 
@@ -1674,4 +1700,5 @@ def kvstore_concurrent(K, rank: int, world: int, dev, n_requests: int = 256, min
             "load_from_neighbour_rank": {"bytes": int(tsum[3]), "ms_slowest_rank": round(float(tmax[1]), 1),
                                          "aggregate_GBps": round(float(tsum[3]) / float(tmax[1]) / 1e6, 1) if tmax[1] > 0 else 0.0,
                                          "blocks_resident_of_asked": [int(tsum[4]), int(tsum[5])]},
+            "concurrent_pinned_cudaMemcpy_GBps": {"d2h_all_ranks": round(ceil_d2h, 1), "h2d_all_ranks": round(ceil_h2d, 1)},
             "evictions": int(stats.get("evictions", 0)), "verified": float(tmax[6]) == 0.0}
