@@ -1657,6 +1657,8 @@ def kvstore_concurrent(K, rank: int, world: int, dev, n_requests: int = 256, min
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(st.stream)
     last = None
+    inflight = []                           # (event, pinned keys): two requests in flight, into alternating halves of the cache
+    started = 0
     for i in reversed(theirs):
         blocks = blocks_of(i, 1)
         keys = st.keys(tokens_of(i), len(blocks))
@@ -1664,13 +1666,21 @@ def kvstore_concurrent(K, rank: int, world: int, dev, n_requests: int = 256, min
         slots = st.pin(keys)                # leading resident blocks, protected from eviction while they are read
         if not slots:
             continue
-        dst_blocks = list(range(max_blk + 1, max_blk + 1 + len(slots)))
+        base = 1 if started % 2 == 0 else max_blk + 1      # the load before the previous one has been waited for
+        started += 1
+        dst_blocks = list(range(base, base + len(slots)))
         ev = st.load_layers(0, n_layers, dst_blocks, slots)
         hits += len(slots)
         loaded_bytes += len(slots) * slot_bytes
-        ev.synchronize()                    # the blocks are in the cache: the pins can go
-        st.unpin(keys[:len(slots)])
+        inflight.append((ev, keys[:len(slots)], base))
         last = (dst_blocks, blocks)
+        while len(inflight) > 1:            # the older one has landed: its pins can go
+            ev0, ks0, _ = inflight.pop(0)
+            ev0.synchronize()
+            st.unpin(ks0)
+    for ev0, ks0, _ in inflight:
+        ev0.synchronize()
+        st.unpin(ks0)
     e1.record(st.stream)
     torch.cuda.synchronize()
     load_ms = e0.elapsed_time(e1)
