@@ -170,8 +170,8 @@ __global__ void __launch_bounds__(128) kvt_copy_blocks_bulk_kernel(const __grid_
   const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
   if (warp == 0) {
     // ---- bulk pass: lanes decode 32 units at a time, lane 0 runs the pipeline --------------------
-    char* sdst[kMaxStagesB];
-    uint32_t slen[kMaxStagesB];
+    char* sdst[kMaxStagesB] = {};
+    uint32_t slen[kMaxStagesB] = {};
     uint32_t issued = 0, stored = 0;
     bool failed = false;
     auto consume_one = [&]() {

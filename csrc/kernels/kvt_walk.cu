@@ -192,8 +192,8 @@ __global__ void __launch_bounds__(256) kvt_walk_kernel(const __grid_constant__ K
   const uint64_t bulk_total = p.bulk_units * n_layers, simt_total = p.simt_units * n_layers;
   if (warp == 0) {
     // ---- bulk pass: lanes decode 32 units at a time, lane 0 runs the pipeline -----------------------
-    char* sdst[kMaxStagesW];
-    uint32_t slen[kMaxStagesW];
+    char* sdst[kMaxStagesW] = {};
+    uint32_t slen[kMaxStagesW] = {};
     uint32_t issued = 0, stored = 0;
     bool failed = false;
     auto consume_one = [&]() {
