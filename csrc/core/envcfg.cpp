@@ -96,6 +96,7 @@ int env_use_tma() { return (int)anyint("BLLM_KVTRANS_USE_TMA", 1); }
 int env_completion_timeout_ms() { return (int)posint("BLLM_KVTRANS_COMPLETION_TIMEOUT_MS", env_rpc_timeout_s() * 1000); }
 int env_nvlink_pull() { return (int)anyint("BLLM_KVTRANS_NVLINK_PULL", 1); }
 int env_nvlink_walk() { return (int)anyint("BLLM_KVTRANS_NVLINK_WALK", 1); }
+int env_fanout_weak() { return (int)anyint("BLLM_KVTRANS_FANOUT_WEAK", 0); }
 int env_walk_threads() { return (int)anyint("BLLM_KVTRANS_WALK_THREADS", 0); }
 int env_walk_stages() { return (int)anyint("BLLM_KVTRANS_WALK_STAGES", 0); }
 int env_tile_order() { return (int)anyint("BLLM_KVTRANS_TILE_ORDER", -1); }

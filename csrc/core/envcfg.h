@@ -63,6 +63,7 @@ int env_use_tma();
 // destination's own order) and how they leave (0 tensor store, 1 one linear bulk store, -1 = linear when legal).
 // 0: the NVLink channel plans hybrid / MLA / KDA shapes on the CPU and uploads byte ranges instead of walk ops.
 int env_nvlink_walk();
+int env_fanout_weak();    // multicast fan-out with weak stores (1) or relaxed system-scope stores (0)
 int env_walk_threads();   // threads per CTA of the walk kernel (0: the kernel's default)
 int env_walk_stages();    // bulk pipeline stages per CTA of the walk kernel (0: default)
 // 0: the NVLink channel always pushes (kernels on the prefill GPU); default: it asks the destination for a pull session

@@ -99,6 +99,12 @@ __global__ void __launch_bounds__(512) kvt_mc_fanout_kernel(const __grid_constan
 // read from this GPU's cache and stored to the same offsets of the multicast mapping.  Nothing but the
 // transferred bytes is touched, so members may relay different requests, or different chunks of one
 // request, without overwriting one another.
+__device__ __forceinline__ void mc_st_16_weak(void* mc, int4 v) {
+  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(__int_as_float(v.x)),
+               "f"(__int_as_float(v.y)), "f"(__int_as_float(v.z)), "f"(__int_as_float(v.w))
+               : "memory");
+}
+
 __device__ __forceinline__ void mc_st_4(void* mc, int v) {
   asm volatile("multimem.st.relaxed.sys.global.u32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
 }
@@ -116,6 +122,7 @@ __device__ __forceinline__ uint32_t find_walk_op(const KvtWalkOp* __restrict__ o
 __global__ void __launch_bounds__(256) kvt_walk_fanout_kernel(const __grid_constant__ KvtWalkLaunch p,
                                                                const KvtWalkOp* __restrict__ ops, const uint32_t n_ops,
                                                                const uint64_t units, const uint64_t* __restrict__ mc_ptrs) {
+  const bool weak = (p.shape & 0x80000000u) != 0;      // weak multicast stores (ordered by the fence at the end of the grid)
   const uint32_t n_layers = p.layer_end - p.layer_begin;
   const uint64_t total = units * n_layers;
   const uint32_t warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -158,8 +165,11 @@ __global__ void __launch_bounds__(256) kvt_walk_fanout_kernel(const __grid_const
           }
         }
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          if (i0 + 32u * k < n16) mc_st_16(mc + off[k], v[k]);
+        for (int k = 0; k < 4; ++k) {
+          if (i0 + 32u * k < n16) {
+            if (weak) mc_st_16_weak(mc + off[k], v[k]); else mc_st_16(mc + off[k], v[k]);
+          }
+        }
       }
     } else if ((a & 3u) == 0) {
       const uint32_t cpp = pc.len >> 2, n4 = cpp * pc.n;

@@ -353,6 +353,7 @@ void BatchEngine::launch_walk_fanout(const KvtWalkCounts& c, size_t n_ops, size_
   a.pool = reinterpret_cast<const uint32_t*>(sl.d_plan + n_ops * sizeof(KvtWalkOp));
   a.pool_len = static_cast<uint32_t>(pool_len);
   a.status = sl.d_status;
+  if (env_fanout_weak() != 0) a.shape |= 0x80000000u;
   cuda_check(kvt_launch_walk_fanout(&a, c.n_zero, c.zero_units, d_walk_mc_.p, grid(), st.stream()), "kvt_launch_walk_fanout");
 }
 
