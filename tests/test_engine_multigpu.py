@@ -252,3 +252,71 @@ def test_kernels_on_the_decode_gpu_or_on_the_prefill_gpu(pull):
     modes = re.findall(r"SendStubMetrics\..*Proto=nvlink,Mode=(\w+),Path=fused", r.stderr)
     assert modes[:3] == ["push"] * 3 and len(modes) >= 4, modes
     assert set(modes[3:]) == {"pull" if pull else "push"}, modes
+
+
+def _send_step(cli, stepid, reqs, tag):
+    for rid, sb, db, total in reqs:
+        cli.submit_req_send2("D|0|1", 0, f"{rid}.{tag}", 0, total, True, sb, db, None, stepid=stepid)
+    cli.start_send_step(stepid, 1)
+    for layer in range(L):
+        cli.record_event(layer)
+    cli.flush_send_step()
+
+
+def test_decode_worker_leaves_between_steps_and_a_new_one_takes_over(tmp_path):
+    """The decode worker's process ends between two steps, with nothing in flight.  The prefill worker's next
+    step fails on the host (its requests are reported failed, the wait returns well inside its limit, nothing
+    hangs); a new decode worker that registers under the same name serves the step after that."""
+    import time
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    torch.cuda.set_device(0)
+    src = [SRC_L.alloc("cuda:0", "normal", seed=i) for i in range(L)]
+    cli = KVTransferClient("P|0|1", 1, 0, 0, SRC_L.block_bytes, SRC_L.token_bytes, f"file:{tmp_path}", src, [PT.NVLINK],
+                           num_kv_heads=8, cache_shape=2)
+    reqs = _requests()
+    chunks = [ReqChunk(sb, db, 0, t) for _, sb, db, t in reqs]
+
+    def expect_ok(got):
+        for i in range(L):
+            want = torch.zeros_like(src[i])
+            reference_transfer(SRC_L, DST_L, src[i], want, chunks)
+            assert torch.equal(got[i], want.cpu()), i
+
+    procs = []
+    try:
+        # ---- first decode worker: one good step, then it leaves ------------------------------------------
+        ready, go, result = ctx.Event(), ctx.Event(), ctx.Queue()
+        a = ctx.Process(target=_decode_proc, args=(str(tmp_path), ready, go, result))
+        a.start()
+        procs.append((a, go))
+        assert ready.wait(180)
+        _send_step(cli, 1, reqs, "one")
+        assert cli.wait_inflight(0, 30.0) and cli.failed_batches() == 0
+        go.set()
+        expect_ok([torch.from_numpy(x) for x in result.get(timeout=120)])
+        a.join(60)
+        assert not a.is_alive()
+        # ---- nobody there: the step fails, quickly and on the host ------------------------------------------
+        t0 = time.time()
+        _send_step(cli, 2, reqs, "two")
+        assert cli.wait_inflight(0, 60.0)
+        assert cli.failed_batches() == 1 and time.time() - t0 < 30.0
+        # ---- a new worker under the same name -----------------------------------------------------------
+        ready2, go2, result2 = ctx.Event(), ctx.Event(), ctx.Queue()
+        b = ctx.Process(target=_decode_proc, args=(str(tmp_path), ready2, go2, result2))
+        b.start()
+        procs.append((b, go2))
+        assert ready2.wait(180)
+        _send_step(cli, 3, reqs, "three")
+        assert cli.wait_inflight(0, 60.0) and cli.failed_batches() == 1
+        go2.set()
+        expect_ok([torch.from_numpy(x) for x in result2.get(timeout=120)])
+    finally:
+        for p, g in procs:
+            g.set()
+            p.join(60)
+            if p.is_alive():
+                p.kill()
