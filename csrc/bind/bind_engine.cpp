@@ -21,6 +21,7 @@
 #include "plan/planner.h"
 #include "topo/topology.h"
 #include "transport/channel.h"
+#include "transport/peer_memory.h"
 
 namespace py = pybind11;
 
@@ -657,6 +658,8 @@ void bind_engine(py::module_& m) {
   m.def("fault_inject_arm", &fault_inject_arm);
   m.def("fault_inject_arm_drop_completion", &fault_inject_arm_drop_completion);
   m.def("completions_pending", [] { return CompletionPoller::instance().pending(); });
+  m.def("ipc_mappings_open", [] { return ipc_mappings_open(); },
+        "Peer allocations this process has mapped through CUDA IPC handles right now.");
   m.def("envcfg_reset_for_test", &envcfg_reset_for_test);
   m.def("env_cache_shape", &env_cache_shape);
   m.def("env_port_base", &env_port_base);

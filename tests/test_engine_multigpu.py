@@ -320,3 +320,72 @@ def test_decode_worker_leaves_between_steps_and_a_new_one_takes_over(tmp_path):
             p.join(60)
             if p.is_alive():
                 p.kill()
+
+
+def _prefill_proc(naming_dir, seed0, done, result):
+    """A prefill worker's whole life: register, one step to D|0|1, report, exit."""
+    os.environ["BLLM_KVTRANS_QUIET_ENV"] = "1"
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch as t2
+    from llumnix_kv_b200.kv_transfer_impl import KVTransferClient as Cli, KVTransferProtocolType as P2
+    t2.cuda.set_device(0)
+    src = [SRC_L.alloc("cuda:0", "normal", seed=seed0 + i) for i in range(L)]
+    cli = Cli("P|0|1", 1, 0, 0, SRC_L.block_bytes, SRC_L.token_bytes, f"file:{naming_dir}", src, [P2.NVLINK], num_kv_heads=8,
+              cache_shape=2)
+    _send_step(cli, 1, _requests(), f"s{seed0}")
+    ok = cli.wait_inflight(0, 30.0) and cli.failed_batches() == 0
+    t2.cuda.synchronize()
+    result.put(bool(ok))
+    done.wait(60)          # stays until the decode side has looked at its cache, then leaves with nothing in flight
+
+
+def test_prefill_worker_leaves_and_another_connects_to_the_same_decode_worker(tmp_path):
+    """The decode worker outlives its senders: a prefill worker's process does a step and ends; its pull session
+    goes with the connection and the mapping of its cache is released; the next prefill worker is served
+    by a new session."""
+    import time
+
+    from llumnix_kv_b200 import load_ops
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    K = load_ops()
+    torch.cuda.set_device(1)
+    dst = [DST_L.alloc("cuda:1") for _ in range(L)]
+    srv = KVTransferServer("D|0|1", 1, 0, 0, DST_L.block_bytes, DST_L.token_bytes, f"file:{tmp_path}", dst, [PT.NVLINK],
+                           num_kv_heads=8, cache_shape=5)
+    ctx = mp.get_context("spawn")
+    reqs = _requests()
+    chunks = [ReqChunk(sb, db, 0, t) for _, sb, db, t in reqs]
+    procs = []
+    try:
+        for seed0 in (300, 700):
+            for d in dst:
+                d.zero_()
+            torch.cuda.synchronize(1)
+            done, result = ctx.Event(), ctx.Queue()
+            p = ctx.Process(target=_prefill_proc, args=(str(tmp_path), seed0, done, result))
+            p.start()
+            procs.append((p, done))
+            assert result.get(timeout=240) is True
+            torch.cuda.synchronize(1)
+            for i in range(L):
+                src_i = SRC_L.alloc("cuda:1", "normal", seed=seed0 + i)
+                want = torch.zeros_like(dst[i])
+                reference_transfer(SRC_L, DST_L, src_i, want, chunks)
+                assert torch.equal(dst[i], want), (seed0, i)
+            assert K.ipc_mappings_open() >= 1                    # the sender's cache is mapped here while its session lives
+            done.set()
+            p.join(60)
+            assert not p.is_alive()
+            t0 = time.time()
+            while K.ipc_mappings_open() != 0 and time.time() - t0 < 20:
+                time.sleep(0.05)
+            assert K.ipc_mappings_open() == 0                    # gone with the connection
+    finally:
+        for p, done in procs:
+            done.set()
+            p.join(30)
+            if p.is_alive():
+                p.kill()
+        srv.stop()
