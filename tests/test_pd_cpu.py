@@ -370,3 +370,55 @@ def test_injected_transport_failures_fail_requests_cleanly_and_later_ones_recove
         assert not p.connector._sched._saving and not d.connector._sched._loading
     finally:
         ops.fault_inject_arm(0)
+
+
+def test_prefill_worker_hands_replicated_requests_to_one_decode_worker():
+    """A prefill worker (TP 1) of an MLA model whose decode instance has four workers submits every chunk
+    to each of them - unless they advertise a multicast group: then one of them gets the request with
+    fanout=4, the same one for every chunk of that request."""
+    from pd_helpers import make_cfg
+
+    from llumnix_kv_b200.engine.core import MiniEngineCore
+    from llumnix_kv_b200.hybrid_connector.kvtbackend import KVTPMeta, PReqMeta
+
+    p = MiniEngineCore(make_cfg("kv_producer", "PX", cache_shape=4, mla=(512, 64, 132), block_size=64, num_blocks=16))
+    try:
+        backend = p.workers[0].connector._worker._backend
+        calls = []
+
+        class Recorder:
+            def submit_req_send2(self, inst, wid, reqid, seen, new, last, sb, db, winfo, stepid=0, fanout=0):
+                calls.append((inst, wid, reqid, seen, new, fanout))
+
+            def submit_delta_send(self, *a, **k):
+                calls.append(("delta",) + a)
+
+            def start_send_step(self, **k):
+                pass
+
+        backend._kvt_cli = Recorder()
+
+        def winfo(rank, mcn):
+            tail = f";mcn={mcn}" if mcn else ""
+            return f"DX|0|4,{rank},4,{rank},4096,256,8,2,4,16,0,1,0,10.0.0.1,x:dev={rank};heads=1{tail};pid=1;port=2;shape=4"
+
+        def step(stepid, reqid, seen, new, infos):
+            meta = KVTPMeta(stepid=stepid, sched_tokens=new)
+            meta.nonfreeze_metas = [PReqMeta(reqid=reqid, d_inst_id="DX|0|4", p_block_ids=[[1, 2]], d_block_ids=[[3, 4]],
+                                             new_tokens=new, has_last_token=False, seen_tokens=seen, d_workers_info=infos)]
+            backend.bind_backend_metadata(meta)
+
+        step(1, "plain", 0, 64, [winfo(r, 0) for r in range(4)])
+        assert [(c[1], c[5]) for c in calls] == [(0, 0), (1, 0), (2, 0), (3, 0)]        # one send per decode worker
+        calls.clear()
+        step(2, "grouped", 0, 64, [winfo(r, 4) for r in range(4)])
+        step(3, "grouped", 64, 32, [winfo(r, 4) for r in range(4)])
+        assert len(calls) == 2 and calls[0][5] == calls[1][5] == 4 and calls[0][1] == calls[1][1]    # one relay, kept
+        relays = set()
+        for i in range(32):
+            calls.clear()
+            step(10 + i, f"r{i}", 0, 64, [winfo(r, 4) for r in range(4)])
+            relays.add(calls[0][1])
+        assert relays == {0, 1, 2, 3}                                                   # the group shares the work
+    finally:
+        p.shutdown()
