@@ -309,27 +309,26 @@ class PeerManager:
         return out
 
     async def refresh(self) -> None:
-        fresh = dict(self._list_instance())
-        gone, changed = [], {}
-        for pid, peer in self._running.items():
-            new = fresh.pop(pid, None)
-            if new is None:
-                gone.append(pid)
-                logger.info("PeerManager peer exited. peer=%s", peer)
-            elif new.ctime_us != peer.ctime_us:
-                changed[pid] = new
-                logger.info("PeerManager peer updated. before=%s after=%s", peer, new)
-        for pid in gone:
-            info = self._running.pop(pid)
-            if info is not None:
-                self._conn_mgr.pop((info.addr, info.port), None)
-        for pid, new in changed.items():
-            old = self._running[pid]
+        """One poll of the naming service.  A peer is identified by (instance, dp rank, tp size) and versioned by
+        its creation time: a peer that disappeared, or came back with another creation time, loses its pooled
+        connections before anybody is handed its address again."""
+        seen = dict(self._list_instance())
+        known = dict(self._running.items())
+        departed = known.keys() - seen.keys()
+        restarted = {pid for pid in known.keys() & seen.keys() if known[pid].ctime_us != seen[pid].ctime_us}
+        arrived = seen.keys() - known.keys()
+        for pid in departed | restarted:
+            old = known[pid]
             self._conn_mgr.pop((old.addr, old.port), None)
-            self._running[pid] = new
-        if fresh:
-            logger.info("PeerManager peer added. peers=%s", fresh)
-            self._running.update(fresh)
+            if pid in departed:
+                self._running.pop(pid)
+                logger.info("peer left: %s", old)
+            else:
+                self._running[pid] = seen[pid]
+                logger.info("peer restarted: %s -> %s", old, seen[pid])
+        if arrived:
+            self._running.update({pid: seen[pid] for pid in arrived})
+            logger.info("peers arrived: %s", {pid: seen[pid] for pid in arrived})
 
     @kill_me_if_exception
     async def _main(self):
