@@ -71,3 +71,30 @@ def test_worker_half_serves_a_transfer_like_the_in_repo_worker():
     finally:
         d.shutdown()
         p.shutdown()
+
+
+def test_scheduler_half_over_an_engine_seam():
+    """With an engine seam object the scheduler-role instance is the same HybridScheduler the in-repo engine
+    drives: vLLM's own entry points answer as the reference's do (no external tokens through that hook), and the
+    hooks stock vLLM never calls are reachable through ``.hybrid``."""
+    from llumnix_kv_b200.engine.core import MiniEngineCore
+    from llumnix_kv_b200.engine.types import Request
+
+    from llumnix_kv_b200.hybrid_connector.engine_proxy import EngineProxy
+
+    cls = vllm_adapter.connector_class()
+    plain = make_cfg("kv_producer", "H")
+    plain.kv_transfer_config = None
+    host = MiniEngineCore(plain)                                     # an engine without a connector of its own
+    try:
+        cfg = make_cfg("kv_producer", "S", extra={"rpc_port": 0})
+        cfg.kv_transfer_config.kv_connector_extra_config["engine_proxy"] = EngineProxy(host, cfg)
+        conn = cls(cfg, vllm_base.KVConnectorRole.SCHEDULER, None)
+        req = Request("r", [1, 2, 3])
+        assert conn.get_num_new_matched_tokens(req, 0) == (0, False)
+        assert conn.request_finished(req, [1, 2]) == (False, None)
+        assert conn.request_finished_all_groups(req, ([1, 2],)) == (False, None)
+        assert conn.hybrid.has_requests() is False and conn.hybrid.step() is None or conn.hybrid.step() == {}
+        conn.shutdown()
+    finally:
+        host.shutdown()
