@@ -1300,6 +1300,10 @@ def relay_bandwidth(K, rank: int, world: int, dev, tokens: int = 8192, n_layers:
       relay     the prefill worker submits every request once, with fanout=k, to one decode worker (round
                 robin over the group); that worker's pull session loads the bytes and stores what it wrote to
                 the group's NVLink multicast mapping: one copy crosses the prefill worker's link.
+      multicast the prefill GPU is itself bound to the group's multicast object (a member of the same symmetric
+                allocation, with memory that only absorbs the echo) and a second client is given its mapping of
+                it: the same fanout=k submissions leave as multicast stores from the prefill GPU; one copy
+                crosses its link and one arrives at every decode worker.
 
     A step moves k * requests_per_worker requests of ``tokens`` tokens.  Timed on the prefill rank (the steps
     end when their completion records have been read), one step in flight ahead; every decode rank verifies
@@ -1319,7 +1323,7 @@ def relay_bandwidth(K, rank: int, world: int, dev, tokens: int = 8192, n_layers:
     n_req = k * requests_per_worker
     blocks_per_req = (tokens + ntpb - 1) // ntpb
     n_blocks = n_req * blocks_per_req + 2
-    d_group = dist.new_group(list(range(1, world)))
+    d_group = dist.group.WORLD          # the prefill GPU joins the multicast group for the third arm
     tmp = [tempfile.mkdtemp() if rank == 0 else None]
     HS.all_gather_object(got := [None] * world, tmp[0])
     naming = f"file:{got[0]}"
@@ -1335,12 +1339,12 @@ def relay_bandwidth(K, rank: int, world: int, dev, tokens: int = 8192, n_layers:
 
     inst = f"DR|0|{k}"
     caches, srv, cli = [], None, None
+    caches = [MulticastKVCache(n_layers, sizes[t] * n_blocks, d_group, dev) for t in range(2)]
+    mc_mine = [[caches[t].mc_ptr + layer * caches[t].layer_bytes for t in range(2)] for layer in range(n_layers)]
     if rank > 0:
-        caches = [MulticastKVCache(n_layers, sizes[t] * n_blocks, d_group, dev) for t in range(2)]
         layers = [[caches[t].layers[layer] for t in range(2)] for layer in range(n_layers)]
-        mc = [[caches[t].mc_ptr + layer * caches[t].layer_bytes for t in range(2)] for layer in range(n_layers)]
         srv = KVTransferServer(inst, k, rank - 1, rank - 1, list(sizes), list(toks), naming, layers, [PT.NVLINK], cache_shape=4,
-                               num_kv_heads=1, mc_layers=mc, mc_size=k)
+                               num_kv_heads=1, mc_layers=mc_mine, mc_size=world)
     HS.barrier()
     bytes_per_req = sum(toks) * tokens * n_layers
     result = {"decode_workers": k, "requests_per_step": n_req, "tokens_per_request": tokens, "layers": n_layers,
@@ -1349,9 +1353,11 @@ def relay_bandwidth(K, rank: int, world: int, dev, tokens: int = 8192, n_layers:
     if rank == 0:
         src = [[src_tensor(layer, t) for t in range(2)] for layer in range(n_layers)]
         cli = KVTransferClient("PR|0|1", 1, 0, 0, list(sizes), list(toks), naming, src, [PT.NVLINK], cache_shape=4, num_kv_heads=1)
+        cli_mc = KVTransferClient("PM|0|1", 1, 0, 0, list(sizes), list(toks), naming, src, [PT.NVLINK], cache_shape=4, num_kv_heads=1,
+                                  mc_layers=mc_mine, mc_size=world)
         stream = torch.cuda.current_stream(dev)
 
-        def step(relay: bool, ahead: int):
+        def step(cli, relay: bool, ahead: int):
             seq[0] += 1
             stepid = 9000 + seq[0]
             for i, sb, db in reqs:
@@ -1366,15 +1372,15 @@ def relay_bandwidth(K, rank: int, world: int, dev, tokens: int = 8192, n_layers:
             cli.flush_send_step()
             assert cli.wait_inflight(ahead, 60.0)
 
-        def timed(relay: bool) -> float:
+        def timed(cli, relay: bool) -> float:
             for _ in range(warmup):
-                step(relay, 1)
+                step(cli, relay, 1)
             assert cli.wait_inflight(0, 60.0)
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(stream)
             for _ in range(steps):
-                step(relay, 1)
+                step(cli, relay, 1)
             assert cli.wait_inflight(0, 60.0)
             e1.record(stream)
             torch.cuda.synchronize()
@@ -1407,8 +1413,8 @@ def relay_bandwidth(K, rank: int, world: int, dev, tokens: int = 8192, n_layers:
         HS.all_reduce(t_ok, op=dist.ReduceOp.MIN)
         return bool(t_ok.item())
 
-    for name, relay in (("unicast", False), ("relay", True)):
-        ms = timed(relay) if rank == 0 else 0.0
+    for name, relay in (("unicast", False), ("relay", True), ("multicast", True)):
+        ms = timed(cli_mc if name == "multicast" else cli, relay) if rank == 0 else 0.0
         HS.barrier()
         t_ms = torch.tensor([ms], dtype=torch.float64)
         HS.all_reduce(t_ms, op=dist.ReduceOp.MAX)
@@ -1416,12 +1422,14 @@ def relay_bandwidth(K, rank: int, world: int, dev, tokens: int = 8192, n_layers:
         verified = verify(name)
         HS.barrier()
         copies = 1 if relay else k
-        result[name] = {"ms_per_step": round(ms, 3), "verified": verified,
+        result[name] = {"ms_per_step": round(ms, 3), "verified": verified, "speedup_over_unicast": 0.0,
                         "prefill_egress_bytes_per_step": copies * n_req * bytes_per_req,
                         "prefill_egress_GBps": round(copies * n_req * bytes_per_req / ms / 1e6, 1) if ms > 0 else 0.0,
                         "delivered_GBps": round(k * n_req * bytes_per_req / ms / 1e6, 1) if ms > 0 else 0.0}
-    result["speedup"] = round(result["unicast"]["ms_per_step"] / result["relay"]["ms_per_step"], 2) \
-        if result["relay"]["ms_per_step"] > 0 else 0.0
+    for name in ("relay", "multicast"):
+        if result[name]["ms_per_step"] > 0:
+            result[name]["speedup_over_unicast"] = round(result["unicast"]["ms_per_step"] / result[name]["ms_per_step"], 2)
+    result["speedup"] = max(result["relay"]["speedup_over_unicast"], result["multicast"]["speedup_over_unicast"])
     if srv is not None:
         srv.stop()
     HS.barrier()

@@ -346,6 +346,12 @@ int kvt_launch_mc_fanout(const KvtMcFanout* args, int grid_ctas, void* stream);
 // 4-byte words (16-byte ones take the wide store); anything else reports KVT_ERR_BAD_ARGS.
 int kvt_launch_walk_fanout(const KvtWalkLaunch* args, uint32_t n_zero_ops, uint64_t zero_units,
                            const uint64_t* mc_ptrs, int grid_ctas, void* stream);
+// The sender's form: a GPU that is itself bound to the group's multicast object (so that it holds a mapping of
+// it) stores the ops' SOURCE pieces, read from its own cache (args->src_ptrs), to the destination offsets behind
+// mc_ptrs, and zeros for the zero-fill class.  No member receives the request first: the sender's link carries the
+// bytes once and every member's link receives them once.  args->dst_ptrs is not used.
+int kvt_launch_walk_multicast(const KvtWalkLaunch* args, uint32_t n_zero_ops, uint64_t zero_units,
+                              const uint64_t* mc_ptrs, int grid_ctas, void* stream);
 
 // ---- completion flags ---------------------------------------------------------------------
 // Bounded device-side wait: returns through status[0]=KVT_ERR_FLAG_TIMEOUT when *flag has not

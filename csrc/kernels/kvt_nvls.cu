@@ -119,6 +119,10 @@ __device__ __forceinline__ uint32_t find_walk_op(const KvtWalkOp* __restrict__ o
 }
 
 // One class of ops (bulk, simt or zero: first_unit counts within the class), `units` units per layer.
+// FROM_SRC = false: the member that received the request stores what the ops WROTE (its own destination pieces).
+// FROM_SRC = true: a sender whose GPU is bound to the group's multicast object stores the ops' SOURCE pieces
+// straight to the group (and zeros for the zero-fill class): no member has to receive the request first.
+template <bool FROM_SRC>
 __global__ void __launch_bounds__(256) kvt_walk_fanout_kernel(const __grid_constant__ KvtWalkLaunch p,
                                                                const KvtWalkOp* __restrict__ ops, const uint32_t n_ops,
                                                                const uint64_t units, const uint64_t* __restrict__ mc_ptrs) {
@@ -138,16 +142,26 @@ __global__ void __launch_bounds__(256) kvt_walk_fanout_kernel(const __grid_const
     }
     if (pc.n == 0) continue;
     const uint32_t t = op.tensor;
+    const bool zero = FROM_SRC && (op.flags & KVT_WALK_ZERO) != 0;
     const int64_t d_last = pc.dst_off + (int64_t)(pc.n - 1) * pc.dst_step;
-    if (t >= p.n_tensors || pc.dst_off < 0 || d_last < 0 || (uint64_t)pc.dst_off + pc.len > p.dst_cap[t] ||
-        (uint64_t)d_last + pc.len > p.dst_cap[t]) {
+    bool bad = t >= p.n_tensors || pc.dst_off < 0 || d_last < 0 || (uint64_t)pc.dst_off + pc.len > p.dst_cap[t] ||
+               (uint64_t)d_last + pc.len > p.dst_cap[t];
+    if (FROM_SRC && !zero && !bad) {
+      const int64_t s_last = pc.src_off + (int64_t)(pc.n - 1) * pc.src_step;
+      bad = pc.src_off < 0 || s_last < 0 || (uint64_t)pc.src_off + pc.len > p.src_cap[t] || (uint64_t)s_last + pc.len > p.src_cap[t];
+    }
+    if (bad) {
       if (lane == 0) set_status(p.status, KVT_ERR_BLOCK_RANGE, oi);
       continue;
     }
     const uint64_t idx = (uint64_t)layer * p.n_tensors + t;
-    const char* own = reinterpret_cast<const char*>(p.dst_ptrs[idx]) + pc.dst_off;
+    // where the bytes are read: this GPU's copy of the destination pieces, or the source pieces
+    const char* own = FROM_SRC ? (zero ? nullptr : reinterpret_cast<const char*>(p.src_ptrs[idx]) + pc.src_off)
+                               : reinterpret_cast<const char*>(p.dst_ptrs[idx]) + pc.dst_off;
+    const int64_t rd_step = FROM_SRC ? (zero ? 0 : pc.src_step) : pc.dst_step;
     char* mc = reinterpret_cast<char*>(mc_ptrs[idx]) + pc.dst_off;
-    const uintptr_t a = reinterpret_cast<uintptr_t>(own) | reinterpret_cast<uintptr_t>(mc) | (uintptr_t)pc.dst_step | pc.len;
+    const uintptr_t a = reinterpret_cast<uintptr_t>(own) | reinterpret_cast<uintptr_t>(mc) | (uintptr_t)pc.dst_step |
+                        (uintptr_t)rd_step | pc.len;
     if ((a & 15u) == 0) {
       // four independent 16-byte loads per lane before the first store: a unit is a few KiB, so the loop is
       // short and its latency, not its instruction count, is what a warp spends
@@ -158,10 +172,12 @@ __global__ void __launch_bounds__(256) kvt_walk_fanout_kernel(const __grid_const
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const uint32_t i = i0 + 32u * k;
+          v[k] = make_int4(0, 0, 0, 0);
+          off[k] = 0;
           if (i < n16) {
             const uint32_t j = i / cpp, c = i - j * cpp;
             off[k] = (int64_t)j * pc.dst_step + ((int64_t)c << 4);
-            v[k] = ld_nc_16(own + off[k]);
+            if (!zero) v[k] = ld_nc_16(own + (int64_t)j * rd_step + ((int64_t)c << 4));
           }
         }
 #pragma unroll
@@ -175,8 +191,8 @@ __global__ void __launch_bounds__(256) kvt_walk_fanout_kernel(const __grid_const
       const uint32_t cpp = pc.len >> 2, n4 = cpp * pc.n;
       for (uint32_t i = lane; i < n4; i += 32) {
         const uint32_t j = i / cpp, c = i - j * cpp;
-        const int64_t off = (int64_t)j * pc.dst_step + ((int64_t)c << 2);
-        mc_st_4(mc + off, *reinterpret_cast<const int*>(own + off));
+        const int v = zero ? 0 : *reinterpret_cast<const int*>(own + (int64_t)j * rd_step + ((int64_t)c << 2));
+        mc_st_4(mc + (int64_t)j * pc.dst_step + ((int64_t)c << 2), v);
       }
     } else {
       // multicast stores are at least four bytes wide; cache pieces are made of 2- and 4-byte elements in
@@ -189,12 +205,31 @@ __global__ void __launch_bounds__(256) kvt_walk_fanout_kernel(const __grid_const
 
 }  // namespace
 
+namespace {
+
+int launch_walk_fanout(const KvtWalkLaunch* args, uint32_t n_zero_ops, uint64_t zero_units, const uint64_t* mc_ptrs,
+                       int grid_ctas, void* stream, bool from_src);
+
+}  // namespace
+
 extern "C" int kvt_launch_walk_fanout(const KvtWalkLaunch* args, uint32_t n_zero_ops, uint64_t zero_units,
                                       const uint64_t* mc_ptrs, int grid_ctas, void* stream) {
+  return launch_walk_fanout(args, n_zero_ops, zero_units, mc_ptrs, grid_ctas, stream, false);
+}
+
+extern "C" int kvt_launch_walk_multicast(const KvtWalkLaunch* args, uint32_t n_zero_ops, uint64_t zero_units,
+                                         const uint64_t* mc_ptrs, int grid_ctas, void* stream) {
+  return launch_walk_fanout(args, n_zero_ops, zero_units, mc_ptrs, grid_ctas, stream, true);
+}
+
+namespace {
+
+int launch_walk_fanout(const KvtWalkLaunch* args, uint32_t n_zero_ops, uint64_t zero_units, const uint64_t* mc_ptrs,
+                       int grid_ctas, void* stream, bool from_src) {
   const KvtWalkLaunch& a = *args;
   if (a.layer_end <= a.layer_begin) return (int)cudaSuccess;
   if (a.n_tensors == 0 || a.n_tensors > KVT_WALK_MAX_TENSORS || a.ops == nullptr || a.pool == nullptr || mc_ptrs == nullptr ||
-      a.dst_ptrs == nullptr)
+      (from_src ? a.src_ptrs == nullptr : a.dst_ptrs == nullptr))
     return (int)cudaErrorInvalidValue;
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
@@ -209,7 +244,10 @@ extern "C" int kvt_launch_walk_fanout(const KvtWalkLaunch* args, uint32_t n_zero
       const uint64_t need = (units[c] * n_layers + 7) / 8;       // eight warps per CTA
       int grid = grid_ctas > 0 ? grid_ctas : 4 * sms;
       if ((uint64_t)grid > need) grid = (int)need;
-      kvt_walk_fanout_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a, ops, counts[c], units[c], mc_ptrs);
+      if (from_src)
+        kvt_walk_fanout_kernel<true><<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a, ops, counts[c], units[c], mc_ptrs);
+      else
+        kvt_walk_fanout_kernel<false><<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a, ops, counts[c], units[c], mc_ptrs);
       const cudaError_t e = cudaGetLastError();
       if (e != cudaSuccess) return (int)e;
     }
@@ -217,6 +255,8 @@ extern "C" int kvt_launch_walk_fanout(const KvtWalkLaunch* args, uint32_t n_zero
   }
   return (int)cudaSuccess;
 }
+
+}  // namespace
 
 extern "C" int kvt_launch_mc_fanout(const KvtMcFanout* args, int grid_ctas, void* stream) {
   const KvtMcFanout& a = *args;

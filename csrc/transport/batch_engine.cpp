@@ -357,6 +357,37 @@ void BatchEngine::launch_walk_fanout(const KvtWalkCounts& c, size_t n_ops, size_
   cuda_check(kvt_launch_walk_fanout(&a, c.n_zero, c.zero_units, d_walk_mc_.p, grid(), st.stream()), "kvt_launch_walk_fanout");
 }
 
+void BatchEngine::launch_walk_multicast(const KvtWalkCounts& c, size_t n_ops, size_t pool_len, size_t lo, size_t hi,
+                                        size_t stage_idx, void* wait_event) {
+  if (n_ops == 0 || hi <= lo) return;
+  RTASSERT(has_multicast());
+  cuda_check(cudaSetDevice(cfg_.device), "cudaSetDevice");
+  ensure_walk_arrays();
+  DeviceStage& st = stage(stage_idx);
+  if (wait_event != nullptr) st.wait_event(wait_event);
+  Slot& sl = cur();
+  KvtWalkLaunch a{};
+  a.src_ptrs = d_walk_src_.p;
+  a.dst_ptrs = d_walk_dst_.p;
+  a.n_tensors = static_cast<uint32_t>(dst_ptrs_[0].size());
+  a.layer_begin = static_cast<uint32_t>(lo);
+  a.layer_end = static_cast<uint32_t>(hi);
+  for (uint32_t t = 0; t < a.n_tensors; ++t) {
+    a.src_cap[t] = src_caps_[t];
+    a.dst_cap[t] = dst_caps_[t];
+  }
+  a.ops = reinterpret_cast<const KvtWalkOp*>(sl.d_plan);
+  a.n_bulk_ops = c.n_bulk;
+  a.n_simt_ops = c.n_simt;
+  a.bulk_units = c.bulk_units;
+  a.simt_units = c.simt_units;
+  a.pool = reinterpret_cast<const uint32_t*>(sl.d_plan + n_ops * sizeof(KvtWalkOp));
+  a.pool_len = static_cast<uint32_t>(pool_len);
+  a.status = sl.d_status;
+  if (env_fanout_weak() != 0) a.shape |= 0x80000000u;
+  cuda_check(kvt_launch_walk_multicast(&a, c.n_zero, c.zero_units, d_walk_mc_.p, grid(), st.stream()), "kvt_launch_walk_multicast");
+}
+
 uint64_t BatchEngine::flush_async(std::string metrics, bool drop_record) {
   cuda_check(cudaSetDevice(cfg_.device), "cudaSetDevice");
   if (batch_slot_ < 0) begin(0);     // a batch without data still completes through a record

@@ -83,6 +83,10 @@ class BatchEngine {
   // Behind launch_walk on the same stage: store what those ops wrote into this GPU's cache to every member
   // of the group (multimem stores through NVSwitch).
   void launch_walk_fanout(const KvtWalkCounts& counts, size_t n_ops, size_t pool_len, size_t lo, size_t hi, size_t stage_idx);
+  // The sender's form, on an engine whose "destination" is the multicast mapping itself: the ops' source pieces
+  // go from this GPU's cache straight to every member of the group (behind `wait_event` of the forward pass).
+  void launch_walk_multicast(const KvtWalkCounts& counts, size_t n_ops, size_t pool_len, size_t lo, size_t hi, size_t stage_idx,
+                             void* wait_event);
 
   uint64_t flush_async(std::string metrics, bool drop_record = false);
   // DONE: `out` holds the record; FAILED: the ticket is unknown or was never flushed.

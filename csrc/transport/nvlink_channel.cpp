@@ -94,6 +94,7 @@ class NvlinkChannel : public IChannel {
       dst_caps_.push_back(dst.block_sizes[t] * static_cast<uint64_t>(dst.layer_num_blocks));
     // ---- pull session on the destination, where that is the faster way ----------------------------
     pull_ = false;
+    push_unavailable_ = false;
     if (dst_remote_ && !dst_mx_ && env_nvlink_pull() != 0) pull_ = open_pull(sock);
     if (pull_) {
       // the decode GPU reads this worker's cache; its own cache is never mapped here, so it may live in memory that
@@ -101,24 +102,50 @@ class NvlinkChannel : public IChannel {
       pull_sock_ = std::move(sock);
     } else {
       // ---- push: the destination's cache mapped here, streams and plan slots on this GPU ------------
-      dst_map_.map(info, ctx_->device_id());
+      const bool can_multicast = !ctx_->multicast_address().empty() && dst.ext_int("mcn", 0) > 1 && !dst_mx_;
+      try {
+        dst_map_.map(info, ctx_->device_id());
+      } catch (const std::exception& ex) {
+        // a cache in a symmetric allocation has no IPC handle; with a mapping of its multicast object this worker
+        // can still serve the requests meant for the whole group
+        if (!can_multicast) throw;
+        LOG(INFO) << "nvlink: destination cache cannot be mapped (" << ex.what() << "); multicast transfers only";
+        push_unavailable_ = true;
+      }
+      if (!push_unavailable_) {
+        BatchEngineConfig cfg;
+        cfg.device = ctx_->device_id();
+        cfg.n_streams = std::max(1, env_nvlink_streams());
+        // A plan holds one descriptor per request and the block tables of both sides.  Sized for every block of
+        // both caches in every block group, plus room for a few thousand request descriptors / walk ops.
+        const size_t groups = std::max<size_t>(1, ctx_->worker_info().num_gdn_layers + ctx_->worker_info().num_ple_layers + 2);
+        const size_t table = (static_cast<size_t>(ctx_->layer_num_blocks()) + dst.layer_num_blocks) * sizeof(uint32_t);
+        cfg.plan_capacity = std::max<size_t>(table * std::min<size_t>(groups, 8) + (1u << 20), 2u << 20);
+        cfg.stamps = env_device_timestamps();
+        cfg.dst_remote = dst_remote_;
+        cfg.grid_ctas = env_nvlink_ctas();
+        eng_ = std::make_unique<BatchEngine>(cfg, ctx_->layer_data_address(), dst_map_.ptrs(), src_caps_, dst_caps_);
+      }
+    }
+    // ---- this worker's GPU is bound to the destination group's multicast object: relayed requests leave as
+    //      multicast stores from here, whichever of pull and push serves the others ----------------------------
+    mc_eng_.reset();
+    if (!ctx_->multicast_address().empty() && dst.ext_int("mcn", 0) > 1 && !dst_mx_) {
       BatchEngineConfig cfg;
       cfg.device = ctx_->device_id();
       cfg.n_streams = std::max(1, env_nvlink_streams());
-      // A plan holds one descriptor per request and the block tables of both sides.  Sized for every block of
-      // both caches in every block group, plus room for a few thousand request descriptors / walk ops.
-      const size_t groups = std::max<size_t>(1, ctx_->worker_info().num_gdn_layers + ctx_->worker_info().num_ple_layers + 2);
       const size_t table = (static_cast<size_t>(ctx_->layer_num_blocks()) + dst.layer_num_blocks) * sizeof(uint32_t);
-      cfg.plan_capacity = std::max<size_t>(table * std::min<size_t>(groups, 8) + (1u << 20), 2u << 20);
+      cfg.plan_capacity = std::max<size_t>(table * 8 + (1u << 20), 2u << 20);
       cfg.stamps = env_device_timestamps();
-      cfg.dst_remote = dst_remote_;
+      cfg.dst_remote = true;
       cfg.grid_ctas = env_nvlink_ctas();
-      eng_ = std::make_unique<BatchEngine>(cfg, ctx_->layer_data_address(), dst_map_.ptrs(), src_caps_, dst_caps_);
+      mc_eng_ = std::make_unique<BatchEngine>(cfg, ctx_->layer_data_address(), ctx_->multicast_address(), src_caps_, dst_caps_);
+      mc_eng_->set_multicast(ctx_->multicast_address());
     }
     active_ = true;
     LOG(INFO) << "nvlink channel connected. dst=" << dst.to_string() << " same_process=" << same_process_
               << " src_shape=" << src_shape_ << " dst_shape=" << dst_shape_ << " dst_mx=" << dst_mx_
-              << " mode=" << (pull_ ? "pull" : "push");
+              << " mode=" << (pull_ ? "pull" : "push") << (mc_eng_ ? "+multicast" : "");
   }
 
   bool register_tasks(const PlanEnv& env, const std::vector<const ReqSendTask*>& tasks) override {
@@ -137,12 +164,19 @@ class NvlinkChannel : public IChannel {
     }
     // requests that the destination relays to its multicast group: all of a batch or none of it
     fanout_ = 0;
+    mc_batch_ = false;
     for (const ReqSendTask* t : tasks) fanout_ = std::max(fanout_, t->req().replicas > 1 ? t->req().replicas : 0u);
     if (fanout_ != 0) {
       for (const ReqSendTask* t : tasks)
         if (t->req().replicas != fanout_)
           throw KVTransferException(ErrorKind::INVALID_OPERATION, "nvlink: a batch mixes relayed and plain requests");
       const uint32_t group = static_cast<uint32_t>(dst_.ext_int("mcn", 0));
+      if (mc_eng_ && group >= fanout_) {
+        if (src_shape_ != dst_shape_)
+          throw KVTransferException(ErrorKind::INVALID_OPERATION, "nvlink: a multicast transfer keeps the cache layout");
+        mc_batch_ = true;
+        return register_walk(e, choice, tasks);
+      }
       if (!pull_ || group < fanout_)
         throw KVTransferException(ErrorKind::INVALID_OPERATION,
                                   "nvlink: the destination cannot relay to " + std::to_string(fanout_) +
@@ -153,6 +187,9 @@ class NvlinkChannel : public IChannel {
       // the relay replicates what walk ops wrote, so these batches take the walk path whatever their shape
       return register_walk(e, choice, tasks);
     }
+    if (!pull_ && !eng_)
+      throw KVTransferException(ErrorKind::INVALID_OPERATION,
+                                "nvlink: this destination is reachable by multicast only (submit with fanout)");
     DeviceAttnParams p;
     std::string why = "the layer has several cache tensors";
     if (n_tensors_ != 1 || !device_attn_params(e, choice.kind, src_shape_, dst_shape_, dst_mx_, &p, &why)) {
@@ -189,7 +226,7 @@ class NvlinkChannel : public IChannel {
 
   bool register_walk(const PlanEnv& e, const PlannerChoice& choice, const std::vector<const ReqSendTask*>& tasks) {
     if (env_nvlink_walk() == 0 || e.cast_bf16_to_fp8 || n_tensors_ > KVT_WALK_MAX_TENSORS) {
-      if (pull_) throw KVTransferException(ErrorKind::INVALID_OPERATION, "nvlink: the pull mode needs the walk kernel for this shape");
+      if (pull_ || mc_batch_) throw KVTransferException(ErrorKind::INVALID_OPERATION, "nvlink: the pull mode needs the walk kernel for this shape");
       return false;
     }
     walk_plan_.clear();
@@ -204,7 +241,7 @@ class NvlinkChannel : public IChannel {
     if (walk_plan_.empty()) return true;       // this rank has nothing to send (not a representative rank)
     const size_t ops_bytes = walk_plan_.ops.size() * sizeof(KvtWalkOp);
     const size_t pool_bytes = walk_plan_.pool.size() * sizeof(uint32_t);
-    if (pull_) {
+    if (pull_ && !mc_batch_) {
       PullPlanHead h{};
       h.kind = PULL_KIND_WALK;
       h.n_ops = static_cast<uint32_t>(walk_plan_.ops.size());
@@ -214,10 +251,11 @@ class NvlinkChannel : public IChannel {
       send_plan(h, walk_plan_.ops.data(), ops_bytes, walk_plan_.pool.data(), pool_bytes);
       return true;
     }
-    BatchEngine::SlotView sl = eng_->begin(ops_bytes + pool_bytes);
+    BatchEngine& eng = mc_batch_ ? *mc_eng_ : *eng_;
+    BatchEngine::SlotView sl = eng.begin(ops_bytes + pool_bytes);
     memcpy(sl.h_plan, walk_plan_.ops.data(), ops_bytes);
     memcpy(sl.h_plan + ops_bytes, walk_plan_.pool.data(), pool_bytes);
-    eng_->upload(ops_bytes + pool_bytes);
+    eng.upload(ops_bytes + pool_bytes);
     return true;
   }
 
@@ -227,7 +265,7 @@ class NvlinkChannel : public IChannel {
                                 "nvlink: the unscaled bf16->fp8 cast belongs to the host-staged transports; over NVLink an "
                                 "fp8 decode cache is filled by the block-scaled quantiser (BLLM_KVTRANS_DST_MXFP8)");
     }
-    if (pull_) throw KVTransferException(ErrorKind::INVALID_OPERATION, "nvlink: byte-range descriptors are a push-mode path");
+    if (pull_ || !eng_) throw KVTransferException(ErrorKind::INVALID_OPERATION, "nvlink: byte-range descriptors are a push-mode path");
     fused_ = false;
     walk_ = false;
     generic_.assign(data.size(), {});
@@ -278,6 +316,11 @@ class NvlinkChannel : public IChannel {
     // migration; a large one is faster layer by layer over several streams (measured crossover
     // around half a GiB).
     if (moved_bytes_per_layer_ * (layer_end - layer_begin) > (512ull << 20)) return false;
+    if (mc_batch_) {
+      void* mev = ctx_->cuda_barrier()->event(static_cast<uint32_t>(layer_end - 1));
+      mc_eng_->launch_walk_multicast(walk_counts_, walk_plan_.ops.size(), walk_plan_.pool.size(), layer_begin, layer_end, 0, mev);
+      return true;
+    }
     if (pull_) {
       send_layers_msg(layer_begin, layer_end, true);
       return true;
@@ -292,6 +335,11 @@ class NvlinkChannel : public IChannel {
   void send_data(size_t layer, Step* step) override {
     (void)step;
     if (nothing_to_send()) return;
+    if (mc_batch_) {
+      mc_eng_->launch_walk_multicast(walk_counts_, walk_plan_.ops.size(), walk_plan_.pool.size(), layer, layer + 1,
+                                     layer % mc_eng_->n_stages(), ctx_->cuda_barrier()->event(static_cast<uint32_t>(layer)));
+      return;
+    }
     if (pull_) {
       send_layers_msg(layer, layer + 1, false);
       return;
@@ -356,6 +404,13 @@ class NvlinkChannel : public IChannel {
 
   size_t send_range(size_t lo, size_t hi, Step* step) override {
     if (nothing_to_send()) return hi - lo;
+    if (mc_batch_) {
+      // the layers recorded so far in one launch, behind the last of their events
+      const size_t n = std::min<size_t>(hi - lo, 8);
+      mc_eng_->launch_walk_multicast(walk_counts_, walk_plan_.ops.size(), walk_plan_.pool.size(), lo, lo + n, mc_eng_->next_stage(),
+                                     ctx_->cuda_barrier()->event(static_cast<uint32_t>(lo + n - 1)));
+      return n;
+    }
     if (pull_) {
       // one message for everything recorded so far; the session launches layer by layer (attention) or once (walk)
       const size_t n = walk_ ? std::min<size_t>(hi - lo, 8) : hi - lo;
@@ -396,11 +451,12 @@ class NvlinkChannel : public IChannel {
   }
 
   bool async_flush() const override { return true; }
-  bool relays_to_group() const override { return pull_ && dst_.ext_int("mcn", 0) > 1; }
+  bool relays_to_group() const override { return (pull_ || mc_eng_) && dst_.ext_int("mcn", 0) > 1; }
 
   std::string metrics_prefix() const {
     std::ostringstream ss;
-    ss << "Proto=nvlink,Mode=" << (pull_ ? "pull" : "push") << ",Path=" << (fused_ ? "fused" : (walk_ ? "walk" : "descriptors"))
+    ss << "Proto=nvlink,Mode=" << (mc_batch_ ? "multicast" : (pull_ ? "pull" : "push")) << ",Path="
+       << (fused_ ? "fused" : (walk_ ? "walk" : "descriptors"))
        << ",OriginSbNum=" << origin_blocks_ << ",MergedSbNum=" << merged_blocks_ << ",BytesPerLayer=" << moved_bytes_per_layer_
        << ",Tiles=" << (walk_ ? walk_plan_.bulk_units + walk_plan_.simt_units : plan_.total_tiles);
     if (fanout_ > 1) ss << ",Fanout=" << fanout_;
@@ -413,7 +469,13 @@ class NvlinkChannel : public IChannel {
     const bool drop = fault_inject_drop_completion();
     TimeWatch tw;
     uint64_t ticket = 0;
-    if (pull_) {
+    if (mc_batch_) {
+      cuda_check(cudaSetDevice(ctx_->device_id()), "cudaSetDevice");
+      ticket = mc_eng_->flush_async(metrics_prefix(), drop) | kMcTicket;
+      mc_batch_ = false;
+      std::lock_guard<std::mutex> g(pull_mu_);
+      pull_metrics_[ticket] = ",FlushUs=" + std::to_string(tw.get_elapse_us());
+    } else if (pull_) {
       if (!pull_batch_open_) {        // a batch without data still completes through the session, in order
         PullPlanHead h{};
         h.kind = PULL_KIND_WALK;
@@ -440,7 +502,20 @@ class NvlinkChannel : public IChannel {
   PollResult poll_completion(uint64_t ticket, std::string& out) override {
     BatchEngine::Done d;
     std::string tail;
-    if (pull_) {
+    if ((ticket & kMcTicket) != 0) {
+      const PollResult r = mc_eng_ ? mc_eng_->poll(ticket & ~kMcTicket, &d) : PollResult::FAILED;
+      if (r == PollResult::PENDING) return r;
+      if (r == PollResult::FAILED) {
+        out = "completion ticket unknown";
+        return r;
+      }
+      std::lock_guard<std::mutex> g(pull_mu_);
+      auto mt = pull_metrics_.find(ticket);
+      if (mt != pull_metrics_.end()) {
+        tail = mt->second;
+        pull_metrics_.erase(mt);
+      }
+    } else if (pull_) {
       std::lock_guard<std::mutex> g(pull_mu_);
       drain_done_frames();
       auto it = pull_done_.find(ticket);
@@ -509,6 +584,8 @@ class NvlinkChannel : public IChannel {
     if (ctx_->device_id() >= 0) cudaSetDevice(ctx_->device_id());
     if (eng_) eng_->close();
     eng_.reset();
+    if (mc_eng_) mc_eng_->close();
+    mc_eng_.reset();
     pull_sock_.reset();      // the server ends the session when the connection goes away
     dst_map_.release();
   }
@@ -616,6 +693,10 @@ class NvlinkChannel : public IChannel {
   uint32_t n_tensors_{0};
   std::vector<uint64_t> src_caps_, dst_caps_;
   std::unique_ptr<BatchEngine> eng_;     // push mode
+  std::unique_ptr<BatchEngine> mc_eng_;  // this GPU holds a mapping of the destination group's multicast object
+  bool mc_batch_{false};                 // the batch being assembled leaves through mc_eng_
+  bool push_unavailable_{false};         // the destination cache has no IPC handle and no pull session serves it
+  static constexpr uint64_t kMcTicket = 1ull << 63;   // marks the tickets of such batches
   int src_shape_{0}, dst_shape_{0};
   bool dst_mx_{false};
   bool dst_remote_{false};       // the destination cache lives on another GPU

@@ -199,7 +199,12 @@ class KVTransferClient:
                  kda_page_stride: int = 0, attn_pack_size: int = 1, num_ple_layers: int = 0,
                  ple_block_group: int = 0, ple_conv_elem_size: int = 1, ple_conv_state_shape=None,
                  ple_conv_channel_dims=None, cache_shape: int = -1, process_global: bool = False,
-                 send_done_addr: Optional[str] = None):
+                 send_done_addr: Optional[str] = None, mc_layers=None, mc_size: int = 0):
+        """``mc_layers`` / ``mc_size``: this worker's GPU is bound to the NVLink multicast object of a decode
+        group's caches (it is a member of the same symmetric allocation, with memory of its own that only
+        absorbs the echo), and ``mc_layers`` gives ITS mapping of the multicast address of every decode cache
+        tensor, shaped like ``layers``.  Requests submitted with ``fanout=k`` to a worker of that group then
+        leave as multicast stores from this GPU: no decode worker has to receive and relay them."""
         block_bytes, token_bytes, layers, layer_num_blocks, device_id = _normalise(block_bytes, token_bytes, layers)
         self._num_layers = len(layers)
         self._device_id = device_id
@@ -210,6 +215,10 @@ class KVTransferClient:
                             gdn_conv_channel_dims, kda_conv_dim_first, hybrid_attn_token_size, kda_page_stride,
                             attn_pack_size, num_ple_layers, ple_block_group, ple_conv_elem_size,
                             ple_conv_state_shape, ple_conv_channel_dims)
+        if mc_layers is not None and mc_size > 1:
+            mc = [[int(a)] if isinstance(a, int) else [int(x) for x in a] for a in mc_layers]
+            assert len(mc) == len(layer_addrs) and all(len(a) == len(b) for a, b in zip(mc, layer_addrs))
+            kw["mc_layers"], kw["mc_size"] = mc, int(mc_size)
         ops_protocols = [p.to_ops_protocol() for p in protocols]
         logger.info("init kvt client: instid=%s tpsize=%s wid=%s wrank=%s blockbytes=%s tokenbytes=%s naming=%s "
                     "protocols=%s device_id=%s num_blocks=%s num_layers=%s cache_shape=%s", inst_id, tp_size,

@@ -194,7 +194,7 @@ def _relay_requests(k: int):
     return [("ra", 0, 150, [3, 9, 4], [7, 2, 11]), ("rb", 1 % k, 64 + 17, [12, 1], [5, 20]), ("rc", (k - 1), 40, [6], [15])]
 
 
-def _relay_child(rank: int, world: int, port: int, tmp: str, q) -> None:
+def _relay_child(rank: int, world: int, port: int, tmp: str, q, sender_in_group: bool = False) -> None:
     errors = []
     caches, srv, cli = [], None, None
     import torch.distributed as dist
@@ -209,7 +209,11 @@ def _relay_child(rank: int, world: int, port: int, tmp: str, q) -> None:
     dist.init_process_group("nccl", device_id=dev, timeout=limit)
     host = dist.new_group(backend="gloo", timeout=limit)   # ranks wait for one another on the host, never inside a NCCL kernel
     k = world - 1
-    d_group = dist.new_group(list(range(1, world)))
+    # sender_in_group: the prefill GPU is bound to the multicast object too (memory of its own that only absorbs
+    # the echo), holds a mapping of it, and stores to the group itself; no pull session, no relay
+    d_group = dist.group.WORLD if sender_in_group else dist.new_group(list(range(1, world)))
+    if sender_in_group and rank == 0:
+        os.environ["BLLM_KVTRANS_NVLINK_PULL"] = "0"     # a relay would need a pull session: only the multicast path is left
     try:
         from llumnix_kv_b200.kv_transfer_impl import KVTransferClient, KVTransferProtocolType as PT, KVTransferServer
         from llumnix_kv_b200.parallel.nvls import MulticastKVCache
@@ -220,12 +224,18 @@ def _relay_child(rank: int, world: int, port: int, tmp: str, q) -> None:
             layers = [[caches[t].layers[layer] for t in range(2)] for layer in range(R_LAYERS)]
             mc = [[caches[t].mc_ptr + layer * caches[t].layer_bytes for t in range(2)] for layer in range(R_LAYERS)]
             srv = KVTransferServer(inst, k, rank - 1, rank - 1, list(R_SIZES), list(R_TOKS), f"file:{tmp}", layers, [PT.NVLINK],
-                                   cache_shape=4, num_kv_heads=1, mc_layers=mc, mc_size=k)
+                                   cache_shape=4, num_kv_heads=1, mc_layers=mc, mc_size=world if sender_in_group else k)
+        elif sender_in_group:
+            caches = [MulticastKVCache(R_LAYERS, R_SIZES[t] * R_BLOCKS, d_group, dev) for t in range(2)]
         dist.barrier(group=host)
         if rank == 0:
             src = [[_relay_src(layer, t, dev) for t in range(2)] for layer in range(R_LAYERS)]
+            extra = {}
+            if sender_in_group:
+                extra = dict(mc_layers=[[caches[t].mc_ptr + layer * caches[t].layer_bytes for t in range(2)]
+                                        for layer in range(R_LAYERS)], mc_size=world)
             cli = KVTransferClient("P|0|1", 1, 0, 0, list(R_SIZES), list(R_TOKS), f"file:{tmp}", src, [PT.NVLINK], cache_shape=4,
-                                   num_kv_heads=1)
+                                   num_kv_heads=1, **extra)
             for rid, relay, tokens, sb, db in _relay_requests(k):
                 cli.submit_req_send2(inst, relay, rid, 0, tokens, True, [sb], [db], None, stepid=1, fanout=k)
             cli.start_send_step(1, 1)
@@ -269,7 +279,10 @@ def _relay_child(rank: int, world: int, port: int, tmp: str, q) -> None:
             pass
 
 
-def test_transport_relays_a_request_through_the_decode_groups_multicast(tmp_path):
+@pytest.mark.parametrize("sender_in_group", [False, True])
+def test_transport_relays_a_request_through_the_decode_groups_multicast(tmp_path, sender_in_group):
+    """sender_in_group=False: one decode worker pulls the request and relays it.  True: the prefill GPU is bound
+    to the group's multicast object and stores to every decode cache itself (`kvt_walk_multicast`)."""
     n = torch.cuda.device_count()
     if n < 3:
         pytest.skip("needs three GPUs: a prefill worker and a decode group of two")
@@ -279,7 +292,7 @@ def test_transport_relays_a_request_through_the_decode_groups_multicast(tmp_path
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_relay_child, args=(r, world, port, str(tmp_path), q)) for r in range(world)]
+    procs = [ctx.Process(target=_relay_child, args=(r, world, port, str(tmp_path), q, sender_in_group)) for r in range(world)]
     for p in procs:
         p.start()
     reports = {}
