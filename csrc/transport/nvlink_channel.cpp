@@ -2,8 +2,9 @@
 // memory (NVLink 5 / NVSwitch).  No staging buffer, no library copy.
 //
 // connect() asks the destination's server for the CUDA IPC handles of its layer tensors
-// (MEM_HANDLES_REQ) and maps them; a destination in the same process is used by pointer after
-// enabling peer access.  Then one of two modes serves the channel:
+// (MEM_HANDLES_REQ); a push channel maps them (a destination in the same process is used by pointer
+// after enabling peer access), a pull channel never touches the destination's memory.  One of two
+// modes serves the channel:
 //
 //   push   the transfer kernels run on the prefill GPU: local loads, stores into the peer cache.  Serves a
 //          destination on the same GPU, a block-scaled fp8 destination (the quantiser halves the bytes that
@@ -12,6 +13,14 @@
 //          and layer events, and executes the plans this channel sends (transport/pull_session.h).  TMA loads
 //          over NVLink run at the copy engine's rate (measured 772 against 705 GB/s for SM-issued stores of any
 //          form), and the prefill GPU spends no SM on the transfer.
+//
+// Requests for a whole multicast group (RequestInfo::replicas > 1: data that every worker of a decode group
+// holds identically) take one of two further forms, both through walk ops:
+//   relay      over a pull session: the destination worker loads the request and stores what the ops wrote to
+//              its group's multicast mapping (kvt_walk_fanout);
+//   multicast  when THIS worker's GPU is bound to that multicast object and holds a mapping of it
+//              (Context::multicast_address): the source pieces leave as multicast stores from here
+//              (kvt_walk_multicast), whatever serves the channel's other requests.
 //
 // In both modes the kernels are the same two:
 //   * kvt_p2d_attn walks the requests' block tables, converts the layout (NHD<->HND), re-shards heads for
@@ -23,7 +32,8 @@
 // The channel is device ordered: a layer's kernel is enqueued behind the layer's CUDA event, nothing on the
 // host waits for the forward pass.  Nothing on the host waits for the transfer either: flush_async()
 // enqueues a completion record behind the batch and returns; the completion poller reads it and finishes
-// the batch.  Only plain peer loads and stores are used; loads with cluster multicast are never issued.
+// the batch.  Only plain peer loads and stores and multimem stores are used; loads with cluster multicast
+// are never issued.
 #include <cuda_runtime.h>
 #include <poll.h>
 #include <sys/socket.h>
