@@ -657,6 +657,7 @@ void bind_engine(py::module_& m) {
   });
   m.def("fault_inject_arm", &fault_inject_arm);
   m.def("fault_inject_arm_drop_completion", &fault_inject_arm_drop_completion);
+  m.def("fault_inject_arm_corrupt_check", &fault_inject_arm_corrupt_check);
   m.def("completions_pending", [] { return CompletionPoller::instance().pending(); });
   m.def("ipc_mappings_open", [] { return ipc_mappings_open(); },
         "Peer allocations this process has mapped through CUDA IPC handles right now.");

@@ -290,6 +290,21 @@ void bind_kernels(py::module_& m) {
         },
         py::arg("src_base"), py::arg("dst_base"), py::arg("triples"), py::arg("n"), py::arg("src_capacity"),
         py::arg("dst_capacity"), py::arg("status"), py::arg("grid"), py::arg("stream"));
+  // end-to-end transfer check: the CPU function, and the kernel over device arrays of {off u64, len u32, index0 u32}
+  m.def("kvt_checksum_host", [](py::buffer data, uint32_t index0) {
+    const py::buffer_info bi = data.request();
+    return kvt_checksum_host(bi.ptr, static_cast<uint64_t>(bi.size) * static_cast<uint64_t>(bi.itemsize), index0);
+  }, py::arg("data"), py::arg("index0") = 0);
+  m.def("kvt_launch_checksum",
+        [](uint64_t base, uint64_t capacity, uint64_t chunks, uint32_t n, uint64_t out, uint64_t status, int grid,
+           uint64_t stream) {
+          check_cuda(kvt_launch_checksum(base, capacity, reinterpret_cast<const KvtCheckChunk*>(chunks), n,
+                                         reinterpret_cast<uint64_t*>(out), reinterpret_cast<uint32_t*>(status), grid,
+                                         reinterpret_cast<void*>(stream)),
+                     "kvt_launch_checksum");
+        },
+        py::arg("base"), py::arg("capacity"), py::arg("chunks"), py::arg("n"), py::arg("out"), py::arg("status"),
+        py::arg("grid"), py::arg("stream"));
   m.def("kvt_bf16_to_e4m3", [](uint16_t bits) { return static_cast<int>(kvt_bf16_to_e4m3(bits)); });
 
   m.def("kvt_launch_wait_flag", [](uint64_t flag, uint64_t value, uint64_t timeout_ns, uint64_t status,

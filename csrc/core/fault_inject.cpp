@@ -44,6 +44,18 @@ bool fault_inject_drop_completion() {
   return false;
 }
 
+static std::atomic<int> g_corrupt_checks{0};
+
+void fault_inject_arm_corrupt_check(int n) { g_corrupt_checks.store(n > 0 ? n : 0); }
+
+bool fault_inject_corrupt_check() {
+  int c = g_corrupt_checks.load();
+  while (c > 0) {
+    if (g_corrupt_checks.compare_exchange_weak(c, c - 1)) return true;
+  }
+  return false;
+}
+
 void fault_inject_sleep(int max_us) {
   if (max_us <= 0 || !roll()) return;
   const int delay_ms = env_debug_tx_delay_ms();

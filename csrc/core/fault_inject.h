@@ -12,4 +12,8 @@ void fault_inject_arm(int throw_after_n);  // test hook: the n-th next call to f
 // GPU is not involved: the kernels of the batch run and finish as usual, only the record is left out.
 void fault_inject_arm_drop_completion(int n);
 bool fault_inject_drop_completion();
+// Test hook for the end-to-end transfer check: the sender's next n checks perturb their own sum, so the
+// comparison with the destination's sum fails although the data is intact.
+void fault_inject_arm_corrupt_check(int n);
+bool fault_inject_corrupt_check();
 }  // namespace kvx

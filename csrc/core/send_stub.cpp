@@ -11,6 +11,7 @@
 #include "core/envcfg.h"
 #include "core/fault_inject.h"
 #include "plan/planner.h"
+#include "transport/verify.h"
 
 namespace kvx {
 
@@ -111,6 +112,9 @@ struct PendingBatch {
   std::string flush_out;
   int64_t queue_us = 0, plan_us = 0, wait_us = 0;
   Timepoint iter_start, enqueued;
+  // end-to-end check: the batch's byte ranges and the destination they were sent to (empty: not checked)
+  std::vector<std::vector<IpcBlock>> check_blocks;
+  WorkerInfo check_dst;
 };
 
 struct KvSendStub::Impl {
@@ -130,6 +134,8 @@ struct KvSendStub::Impl {
   std::atomic<int> completing{0};          // batches handed to the completion poller and not yet finished
 
   std::vector<std::vector<IpcBlock>> send_blocks;
+  Context* check_ctx{nullptr};              // set: batches are verified end to end
+  bool check_unavailable_logged{false};
 
   Impl(KvSendStub* s, const WorkerInfo& src, std::shared_ptr<INamingWorkerClient> n, uint32_t sl, uint32_t nl,
        std::unique_ptr<IChannelFactory> f, int shape, std::string sd_addr)
@@ -181,6 +187,55 @@ struct KvSendStub::Impl {
     LOG(INFO) << "create channel. dst=" << dstinfo->to_string() << ";ch=" << ch.get() << ";proto=" << ch->name();
   }
 
+  // End-to-end check, first half: remember the batch's byte ranges.  `planned` is the host plan of the
+  // batch; a device-planned batch (nullptr) is planned once more here, on the CPU, for the check alone.
+  void keep_check_blocks(PendingBatch& pb, const std::vector<std::vector<IpcBlock>>* planned) {
+    const int dst_shape = dstinfo->cache_shape_or(cache_shape);
+    const char* why = nullptr;
+    if (dst_shape != cache_shape) why = "it converts the cache layout";
+    else if (dstinfo->ext_int("mx", env_dst_mxfp8()) != 0 || env.cast_bf16_to_fp8) why = "it converts the dtype";
+    if (why == nullptr) {
+      try {
+        if (planned != nullptr) {
+          pb.check_blocks = *planned;
+        } else {
+          for (const ReqSendTask* t : pb.send_req) plan_request(planner, env, *t, pb.check_blocks);
+        }
+        pb.check_dst = *dstinfo;
+        return;
+      } catch (const std::exception& ex) {
+        pb.check_blocks.clear();
+        why = "byte ranges cannot describe it";
+      }
+    }
+    if (!check_unavailable_logged) {
+      check_unavailable_logged = true;
+      LOG(WARNING) << "KVT transfer check is on (BLLM_KVTRANS_CRC) but this transfer goes unchecked: " << why
+                   << ". DstId=" << stub->dstid() << ",DstWorkerId=" << stub->dstworkerid();
+    }
+  }
+
+  // Second half, when the batch has landed: compare the two caches.  False fails the batch.
+  bool run_check(PendingBatch& pb) noexcept {
+    try {
+      const CheckOutcome o = verify_transfer(check_ctx, pb.check_dst, start_layer, num_layers, pb.check_blocks);
+      pb.flush_out += ",Check=" + std::string(o.ok ? "ok" : "MISMATCH") + ",CheckLocalUs=" + std::to_string(o.local_us) +
+                      ",CheckRemoteUs=" + std::to_string(o.remote_us);
+      if (!o.ok) {
+        LOG(ERROR) << "KVT transfer check failed: source and destination differ. DstId=" << stub->dstid()
+                   << ",DstWorkerId=" << stub->dstworkerid() << ",StepIdx=" << pb.batch.step->step_idx << "."
+                   << pb.batch.substepid << ",local=" << o.local << ",remote=" << o.remote;
+        drop_channel.store(true);
+      }
+      return o.ok;
+    } catch (const std::exception& ex) {
+      LOG(ERROR) << "KVT transfer check could not run. DstId=" << stub->dstid() << ",DstWorkerId=" << stub->dstworkerid()
+                 << ",ex=" << ex.what();
+      pb.flush_out += ",Check=error";
+      return false;
+    }
+  }
+
   // Returns true when the batch completes asynchronously (pb.ticket names its completion record).
   bool do_send(PendingBatch& pb) {
     BatchSendTask& batch = pb.batch;
@@ -217,6 +272,11 @@ struct KvSendStub::Impl {
     BatchSendTask& batch = pb.batch;
     const size_t step_idx = batch.step->step_idx;
     Timepoint send_finish = SteadyClock::now();
+    if (ok && !pb.check_blocks.empty()) {
+      ok = run_check(pb);
+      pb.check_blocks.clear();
+      send_finish = SteadyClock::now();
+    }
     const int64_t wait_and_send_us = elapse_us(pb.iter_start, send_finish);
     if (!ok) {
       for (const auto& task : batch.tasks) task.set_state(ReqState::FAILED);
@@ -293,7 +353,10 @@ struct KvSendStub::Impl {
           send_blocks.clear();
           for (const ReqSendTask* t : pb.send_req) plan_request(planner, env, *t, send_blocks);
           have_data = !send_blocks.empty() && !send_blocks[0].empty();
+          if (have_data && check_ctx != nullptr) keep_check_blocks(pb, &send_blocks);
           if (have_data) ch->register_data(send_blocks, planner.kind);
+        } else if (check_ctx != nullptr) {
+          keep_check_blocks(pb, nullptr);
         }
         pb.plan_us = elapse_us(pb.iter_start, SteadyClock::now());   // channel, planning, descriptor upload
         if (have_data) async = do_send(pb);
@@ -353,6 +416,8 @@ KvSendStub::~KvSendStub() {
     std::this_thread::sleep_for(std::chrono::microseconds(200));
 }
 
+void KvSendStub::enable_check(Context* ctx) { impl_->check_ctx = ctx; }
+
 bool KvSendStub::idle() const { return impl_->completing.load(std::memory_order_acquire) == 0; }
 
 void KvSendStub::send_batch(BatchSendTask batch) noexcept {
@@ -374,9 +439,11 @@ SendStub KvSendStubFactory::create_stub(const InstanceId& dst, WorkerId dst_work
   else nw = naming_worker_;
   if (!nw) throw std::runtime_error("no naming service and no destination info in the request");
   const int shape = ctx_->worker_info().cache_shape_or(env_cache_shape());
-  return std::make_unique<KvSendStub>(dst, dst_worker, ctx_->worker_info(), start_layer, num_layers,
-                                      std::make_unique<ChannelFactory>(ctx_, proto), std::move(nw), shape,
-                                      ctx_->worker_info().ext_str("sdaddr"));
+  auto stub = std::make_unique<KvSendStub>(dst, dst_worker, ctx_->worker_info(), start_layer, num_layers,
+                                           std::make_unique<ChannelFactory>(ctx_, proto), std::move(nw), shape,
+                                           ctx_->worker_info().ext_str("sdaddr"));
+  if (env_crc() != 0) stub->enable_check(ctx_);
+  return stub;
 }
 
 }  // namespace kvx

@@ -79,6 +79,9 @@ class KvSendStub : public ISendStub {
   ~KvSendStub() override;
   void send_batch(BatchSendTask batch) noexcept override;
   bool idle() const override;
+  // Turns the end-to-end check on (transport/verify.h): every batch whose transfer byte ranges can describe
+  // is verified against the destination's cache before its requests are reported; a mismatch fails the batch.
+  void enable_check(Context* ctx);
 
  private:
   struct Impl;

@@ -377,6 +377,21 @@ int kvt_launch_complete(uint32_t* status, KvtCompletion* record, uint64_t seq, v
 // node, without CUDA events.
 int kvt_launch_stamp(uint64_t* slot, void* stream);
 
+// ---- end-to-end transfer check -------------------------------------------------------------
+// Position-keyed 64-bit checksum of byte ranges of one tensor (kvt_checksum.cu): each byte adds
+// mix32(((i & 0xFFFFFF) << 8) | byte), i = its index in its piece.  Chunks are pieces cut to <= 64 KiB;
+// index0 is the index of the chunk's first byte in its piece.  The kernel ADDS to *d_out (zero it first), skips
+// a chunk outside [0, capacity) and reports it in d_status {KVT_ERR_BLOCK_RANGE, chunk number}.
+typedef struct {
+  uint64_t off;
+  uint32_t len;
+  uint32_t index0;
+} KvtCheckChunk;
+#define KVT_CHECK_CHUNK 65536u
+int kvt_launch_checksum(uint64_t base, uint64_t capacity, const KvtCheckChunk* d_chunks, uint32_t n, uint64_t* d_out,
+                        uint32_t* d_status, int grid_ctas, void* stream);
+uint64_t kvt_checksum_host(const void* data, uint64_t len, uint32_t index0);
+
 // ---- peer memory / topology ---------------------------------------------------------------
 int kvt_device_count(void);
 int kvt_can_access_peer(int dev, int peer);

@@ -9,7 +9,9 @@
 //   * attaches a POSIX shm segment named by the sender and scatters blobs out of it;
 //   * answers MEM_HANDLES_REQ with CUDA IPC handles of every layer tensor, which is how a
 //     prefill worker's NVLink transport maps this worker's cache (the role the RDMA
-//     rkey exchange plays in kvtransfer/src/rdma_channel.cpp:77-99,298-316).
+//     rkey exchange plays in kvtransfer/src/rdma_channel.cpp:77-99,298-316);
+//   * answers CHECK_REQ with the checksum of the named ranges of this worker's cache (the receiving half of
+//     the end-to-end check, the role of resp_remote_crc in kvtransfer/src/rdma_channel.cpp:201-296).
 #include <cuda_runtime.h>
 #include <fcntl.h>
 #include <netinet/in.h>
@@ -32,6 +34,7 @@
 #include "transport/channel.h"
 #include "transport/device_stage.h"
 #include "transport/pull_session.h"
+#include "transport/verify.h"
 #include "transport/wire.h"
 
 namespace kvx {
@@ -211,6 +214,8 @@ class TransferServer : public ITransferServer {
           else if (magic == PULL_LAYERS_REQ) pull->on_layers(seq, buf + RPC_HEADER, n - RPC_HEADER);
           else pull->on_flush(seq, buf + RPC_HEADER, n - RPC_HEADER);
           continue;     // one-way: a flushed batch is answered with PULL_DONE when its completion record arrives
+        } else if (magic == CHECK_REQ) {
+          resp = answer_check(ctx_, buf, n);
         } else if (magic == PING_REQ) {
           resp.assign(buf, std::min<size_t>(n, RPC_HEADER));
           put(resp, static_cast<uint32_t>(WIRE_OK));

@@ -34,6 +34,9 @@ constexpr uint32_t PULL_PLAN_REQ = 0x4B565050;         // 'KVPP': a batch's plan
 constexpr uint32_t PULL_LAYERS_REQ = 0x4B56504C;       // 'KVPL': layers [lo, hi) of the batch are recorded: enqueue them
 constexpr uint32_t PULL_FLUSH_REQ = 0x4B565046;        // 'KVPF': the batch is complete: enqueue its completion record
 constexpr uint32_t PULL_DONE = 0x4B565044;             // 'KVPD': [status u32][detail u32][t_start u64][t_end u64]
+// End-to-end check of a finished batch (transport/verify.h): the ranges a batch wrote, answered with the
+// checksum of what the destination's cache holds there.
+constexpr uint32_t CHECK_REQ = 0x4B56436B;             // 'KVCk'
 constexpr size_t RPC_HEADER = sizeof(uint32_t) + sizeof(uint64_t);
 
 enum WireStatus : uint32_t { WIRE_OK = 0, WIRE_BAD_REQUEST = 400, WIRE_INTERNAL = 500 };

@@ -620,3 +620,112 @@ def test_relayed_transfer_is_refused_by_host_transports(ops, sink):
         assert all(float(d.abs().sum()) == 0.0 for d in dst)
     finally:
         srv.stop()
+
+
+# ---- end-to-end transfer check ------------------------------------------------------------------
+def _mix32(x):
+    x = (x * 0x9E3779B1) & 0xFFFFFFFF
+    x ^= x >> 15
+    x = (x * 0x85EBCA77) & 0xFFFFFFFF
+    x ^= x >> 13
+    return x
+
+
+def _piece_sum(data: bytes, index0=0):
+    return sum(_mix32((((index0 + i) & 0xFFFFFF) << 8) | b) for i, b in enumerate(data)) & 0xFFFFFFFFFFFFFFFF
+
+
+def _rotl64(v, r):
+    r &= 63
+    return v if r == 0 else ((v << r) | (v >> (64 - r))) & 0xFFFFFFFFFFFFFFFF
+
+
+def test_checksum_function_matches_its_definition(ops):
+    rng = random.Random(3)
+    data = bytes(rng.randrange(256) for _ in range(1000))
+    assert ops.kvt_checksum_host(data) == _piece_sum(data)
+    assert ops.kvt_checksum_host(data[100:], 100) == _piece_sum(data[100:], 100)
+    # a piece cut into chunks that carry their starting index sums to the whole piece
+    cuts = [0, 17, 256, 640, 1000]
+    assert sum(ops.kvt_checksum_host(data[a:b], a) for a, b in zip(cuts, cuts[1:])) & 0xFFFFFFFFFFFFFFFF == _piece_sum(data)
+    # the value depends on where a byte sits in its piece, not only on the multiset of bytes
+    swapped = bytearray(data)
+    swapped[3], swapped[4] = swapped[4], swapped[3]
+    assert data[3] != data[4] and ops.kvt_checksum_host(bytes(swapped)) != _piece_sum(data)
+
+
+def test_server_answers_a_check_request_with_the_checksum_of_its_cache(ops):
+    """CHECK_REQ names byte ranges per tensor for a span of layers; the answer is the sum over layers of the
+    rotated per-layer sums.  Ranges outside the tensor are refused, not read."""
+    dst = make_cache(21)
+    srv = KVTransferServer("D|0|1", 1, 0, 0, BLK, TOK, "fake://", dst, [PT.TCP], num_kv_heads=H, cache_shape=2)
+    port = int(ops.WorkerInfo.from_string(srv.worker_info()).ext["port"])
+    ranges = [(5 * BLK // 2 + 64, 300), (40 * BLK // 2, 4096), (7, 1)]
+    cap = dst[0].numel() * 2
+
+    def ask(c, lb, le, rs):
+        body = struct.pack("=IIII", lb, le, 1, 0) + struct.pack("=Q", len(rs)) + b"".join(struct.pack("=QQ", o, n) for o, n in rs)
+        msg = struct.pack("=IQ", 0x4B56436B, 9) + body
+        c.sendall(struct.pack("=I", len(msg)) + msg)
+        n = struct.unpack("=I", c.recv(4, socket.MSG_WAITALL))[0]
+        resp = c.recv(n, socket.MSG_WAITALL)
+        magic, reqid, status, total = struct.unpack("=IQIQ", resp[:24])
+        assert (magic, reqid) == (0x4B56436B, 9)
+        return status, total
+
+    def expect(lb, le):
+        total = 0
+        for layer in range(lb, le):
+            raw = dst[layer].numpy().tobytes()
+            total += _rotl64(sum(_piece_sum(raw[o:o + n]) for o, n in ranges) & 0xFFFFFFFFFFFFFFFF, layer * 7)
+        return total & 0xFFFFFFFFFFFFFFFF
+
+    try:
+        with socket.create_connection(("127.0.0.1", port), timeout=10) as c:
+            assert ask(c, 0, L, ranges) == (0, expect(0, L))
+            assert ask(c, 1, 2, ranges) == (0, expect(1, 2))
+            before = expect(0, L)
+            dst[1].view(torch.int16).view(-1)[(40 * BLK // 2) // 2 + 9] ^= 0x0100       # one bit of one byte in a checked range
+            after = ask(c, 0, L, ranges)
+            assert after == (0, expect(0, L)) and after[1] != before
+            assert ask(c, 0, L, [(cap - 8, 16)])[0] == 400
+            assert ask(c, 0, L + 1, ranges)[0] == 400
+    finally:
+        srv.stop()
+
+
+@pytest.mark.parametrize("proto", [PT.TCP, PT.SHM])
+def test_transfer_check_passes_intact_batches_and_fails_a_mismatch(proto, ops, sink):
+    """BLLM_KVTRANS_CRC=1: after a batch has landed the sender compares a checksum of its source ranges with
+    the destination's checksum of the ranges it wrote.  Intact batches finish as before; a batch whose two
+    sums differ (the sender's sum perturbed through the host-side hook) reports its requests failed, and
+    the stub carries on with the next batch."""
+    os.environ["BLLM_KVTRANS_CRC"] = "1"
+    ops.envcfg_reset_for_test()
+    src, dst = make_cache(31), make_cache()
+    srv = KVTransferServer("D|0|1", 1, 0, 0, BLK, TOK, "fake://", dst, [proto], num_kv_heads=H, cache_shape=2)
+    cli = KVTransferClient("P|0|1", 1, 0, 0, BLK, TOK, "fake://", src, [proto], num_kv_heads=H, cache_shape=2)
+    try:
+        def step(stepid, reqs):
+            for rid, sb, db, n in reqs:
+                cli.submit_req_send2("D|0|1", 0, rid, 0, n, True, sb, db, srv.worker_info(), stepid=stepid)
+            cli.start_send_step(stepid, 1)
+            for layer in range(L):
+                cli.record_event(layer)
+            cli.flush_send_step()
+            cli.drain()
+
+        step(1, [("a", [3, 9, 4], [7, 1, 8], 41), ("b", [20], [21], 16)])
+        check_tokens(src, dst, [3, 9, 4], [7, 1, 8], 0, 41)
+        ops.fault_inject_arm_corrupt_check(1)
+        step(2, [("c", [5], [6], 12)])
+        step(3, [("d", [11, 12], [13, 14], 32)])
+        check_tokens(src, dst, [11, 12], [13, 14], 0, 32)
+        codes = {r[0]: r[2] for m in sink.wait_for(3) if m[0] == 0x20181219 for r in m[3]}
+        assert codes == {"a": 0, "b": 0, "c": 500, "d": 0}
+        assert cli.failed_batches() == 1
+    finally:
+        ops.fault_inject_arm_corrupt_check(0)
+        srv.stop()
+        os.environ.pop("BLLM_KVTRANS_CRC", None)
+        ops.envcfg_reset_for_test()

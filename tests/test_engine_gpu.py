@@ -355,3 +355,123 @@ def test_a_completion_record_that_never_arrives_fails_the_request_within_its_dea
         os.environ.pop("BLLM_KVTRANS_COMPLETION_TIMEOUT_MS", None)
         K.envcfg_reset_for_test()
         srv.stop()
+
+
+# ---- end-to-end transfer check ------------------------------------------------------------------
+def test_checksum_kernel_matches_the_host_function(ops):
+    """Chunks of every alignment class (16-byte vector path, byte path, odd offsets and lengths, a chunk
+    that continues a piece at a non-zero index) against the CPU function; a chunk outside the tensor is
+    skipped and reported."""
+    import numpy as np
+
+    g = torch.Generator(device=DEV).manual_seed(11)
+    cap = 1 << 20
+    buf = torch.randint(0, 256, (cap,), dtype=torch.uint8, device=DEV, generator=g)
+    host = buf.cpu().numpy()
+    chunks = [(0, 65536, 0), (65536, 65536, 65536), (131072 + 16, 4096, 0), (200001, 777, 5), (300000, 1, 0),
+              (400000, 65535, 123456), (cap - 48, 48, 0x1FFFFF0)]
+    arr = np.zeros(len(chunks), dtype=[("off", "<u8"), ("len", "<u4"), ("idx", "<u4")])
+    for i, c in enumerate(chunks):
+        arr[i] = c
+    d_chunks = torch.from_numpy(arr.view(np.uint8).copy()).to(DEV)
+    out = torch.zeros(2, dtype=torch.int64, device=DEV)     # [sum, status words]
+    s = torch.cuda.current_stream().cuda_stream
+    ops.kvt_launch_checksum(buf.data_ptr(), cap, d_chunks.data_ptr(), len(chunks), out.data_ptr(), out.data_ptr() + 8, 0, s)
+    torch.cuda.synchronize()
+    expect = sum(ops.kvt_checksum_host(host[o:o + n], i) for o, n, i in chunks) & 0xFFFFFFFFFFFFFFFF
+    assert int(out[0].item()) & 0xFFFFFFFFFFFFFFFF == expect
+    assert int(out[1].item()) == 0
+    # one grid of 3 CTAs gives the same sum as the default grid: the order of visits does not matter
+    out.zero_()
+    ops.kvt_launch_checksum(buf.data_ptr(), cap, d_chunks.data_ptr(), len(chunks), out.data_ptr(), out.data_ptr() + 8, 3, s)
+    torch.cuda.synchronize()
+    assert int(out[0].item()) & 0xFFFFFFFFFFFFFFFF == expect
+    # a chunk that leaves the tensor is not read
+    arr[2] = (cap - 8, 16, 0)
+    d_bad = torch.from_numpy(arr.view(np.uint8).copy()).to(DEV)
+    out.zero_()
+    ops.kvt_launch_checksum(buf.data_ptr(), cap, d_bad.data_ptr(), len(chunks), out.data_ptr(), out.data_ptr() + 8, 0, s)
+    torch.cuda.synchronize()
+    status = int(out[1].item())
+    assert status & 0xFFFFFFFF != 0 and status >> 32 == 2
+
+
+@pytest.mark.parametrize("proto", [PT.NVLINK, PT.TCP])
+def test_transfer_check_between_device_caches(proto, ops):
+    """BLLM_KVTRANS_CRC=1 with GPU caches: each side sums its own ranges with the checksum kernel.  Intact
+    batches pass (two chunks of a request, ragged edges); the batch whose sender-side sum is perturbed fails;
+    the next one passes on a fresh channel."""
+    os.environ["BLLM_KVTRANS_CRC"] = "1"
+    ops.envcfg_reset_for_test()
+    lay = AttnLayout(CacheShape.FLASHINFER, 48, 16, 8, 128, 2)
+    src = [lay.alloc(DEV, "normal", seed=i) for i in range(L)]
+    dst = [lay.alloc(DEV) for _ in range(L)]
+    srv = KVTransferServer("D|0|1", 1, 0, 0, lay.block_bytes, lay.token_bytes, "fake://", dst, [proto], num_kv_heads=8,
+                           cache_shape=5)
+    cli = KVTransferClient("P|0|1", 1, 0, 0, lay.block_bytes, lay.token_bytes, "fake://", src, [proto], num_kv_heads=8,
+                           cache_shape=5)
+    try:
+        w = srv.worker_info()
+        run_step(cli, "D|0|1", 0, w, [("a", [3, 9, 4], [7, 1, 8], 0, 21, False, True), ("b", [20], [21], 0, 16, True, True)], 1)
+        run_step(cli, "D|0|1", 0, w, [("a", [3, 9, 4], [7, 1, 8], 21, 20, True, False)], 2)
+        assert cli.failed_batches() == 0
+        ops.fault_inject_arm_corrupt_check(1)
+        run_step(cli, "D|0|1", 0, w, [("c", [5], [6], 0, 12, True, True)], 3)
+        assert cli.failed_batches() == 1
+        run_step(cli, "D|0|1", 0, w, [("d", [11, 12], [13, 14], 0, 32, True, True)], 4)
+        assert cli.failed_batches() == 1
+        chunks = [ReqChunk([3, 9, 4], [7, 1, 8], 0, 41), ReqChunk([20], [21], 0, 16), ReqChunk([5], [6], 0, 12),
+                  ReqChunk([11, 12], [13, 14], 0, 32)]
+        for i in range(L):
+            expect = torch.zeros_like(dst[i])
+            reference_transfer(lay, lay, src[i], expect, chunks)
+            assert torch.equal(dst[i], expect)
+    finally:
+        ops.fault_inject_arm_corrupt_check(0)
+        srv.stop()
+        os.environ.pop("BLLM_KVTRANS_CRC", None)
+        ops.envcfg_reset_for_test()
+
+
+def test_server_check_request_over_a_device_cache(ops):
+    """The destination half alone: CHECK_REQ over a GPU cache answers the sum that the CPU function gives
+    for the same bytes, and the sum moves when one checked byte changes."""
+    import socket
+    import struct
+
+    lay = AttnLayout(CacheShape.FLASH, 48, 16, 8, 128, 2)
+    dst = [lay.alloc(DEV, "normal", seed=40 + i) for i in range(L)]
+    srv = KVTransferServer("D|0|1", 1, 0, 0, lay.block_bytes, lay.token_bytes, "fake://", dst, [PT.TCP], num_kv_heads=8,
+                           cache_shape=2)
+    port = int(ops.WorkerInfo.from_string(srv.worker_info()).ext["port"])
+    ranges = [(5 * lay.block_bytes + 64, 300), (10 * lay.block_bytes, 3 * 65536 + 32), (7, 1)]
+
+    def ask(c):
+        body = struct.pack("=IIII", 0, L, 1, 0) + struct.pack("=Q", len(ranges)) + b"".join(struct.pack("=QQ", o, n) for o, n in ranges)
+        msg = struct.pack("=IQ", 0x4B56436B, 9) + body
+        c.sendall(struct.pack("=I", len(msg)) + msg)
+        n = struct.unpack("=I", c.recv(4, socket.MSG_WAITALL))[0]
+        _, _, status, total = struct.unpack("=IQIQ", c.recv(n, socket.MSG_WAITALL)[:24])
+        return status, total
+
+    def rotl(v, r):
+        r &= 63
+        return v if r == 0 else ((v << r) | (v >> (64 - r))) & 0xFFFFFFFFFFFFFFFF
+
+    def expect():
+        total = 0
+        for layer in range(L):
+            raw = dst[layer].view(torch.uint8).flatten().cpu().numpy()
+            total += rotl(sum(ops.kvt_checksum_host(raw[o:o + n]) for o, n in ranges) & 0xFFFFFFFFFFFFFFFF, layer * 7)
+        return total & 0xFFFFFFFFFFFFFFFF
+
+    try:
+        with socket.create_connection(("127.0.0.1", port), timeout=10) as c:
+            first = ask(c)
+            assert first == (0, expect())
+            dst[2].view(torch.uint8).flatten()[10 * lay.block_bytes + 70000] ^= 1
+            torch.cuda.synchronize()
+            second = ask(c)
+            assert second == (0, expect()) and second[1] != first[1]
+    finally:
+        srv.stop()
