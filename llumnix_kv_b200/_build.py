@@ -33,6 +33,9 @@ GENCODE = ["-gencode", "arch=compute_100a,code=sm_100a"]
 # reference configures none).  Run the CPU tests of such a build with the sanitizer runtime preloaded:
 #   KVX_SANITIZE=address python -m llumnix_kv_b200._build -f
 #   LD_PRELOAD=$(gcc -print-file-name=libasan.so) ASAN_OPTIONS=detect_leaks=0 python -m pytest tests -m "not gpu"
+# KVX_SANITIZE=coverage builds the host code with gcov instrumentation instead (the reference's test build uses
+# --coverage, kvtransfer/CMakeLists.txt:49-51): the .gcda files appear beside the objects in build_coverage/ when
+# the test process exits.
 SANITIZE = os.environ.get("KVX_SANITIZE", "")
 if SANITIZE:
     BUILD = ROOT / f"build_{SANITIZE}"
@@ -81,6 +84,8 @@ def _compile_one(src: Path, hdr_digest: str, verbose: bool) -> Path:
         return obj
     common = ["-O3", "-std=c++17", "-DNDEBUG"] + _includes()
     san = [f"-fsanitize={SANITIZE}", "-g", "-fno-omit-frame-pointer"] if SANITIZE else []
+    if SANITIZE == "coverage":
+        san = ["--coverage", "-g"]
     if src.suffix == ".cu":
         cmd = [NVCC, *GENCODE, "-lineinfo", "-Xcompiler", ",".join(["-fPIC", "-g1", "-Wall", "-Wextra", "-Wno-unused-parameter"] + san),
                "--expt-relaxed-constexpr", "-Xptxas", "-v" if verbose else "-O3", *common,
@@ -109,13 +114,20 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         objs = list(ex.map(lambda s: _compile_one(s, digest, verbose), srcs))
     target = target_path()
     newest = max(o.stat().st_mtime for o in objs)
-    if not target.exists() or target.stat().st_mtime < newest or force:
+    # every mode links to the same in-tree target: remember which one it holds
+    mode_file = ROOT / "build" / ".linked_mode"
+    mode_file.parent.mkdir(exist_ok=True)
+    linked = mode_file.read_text() if mode_file.exists() else ""
+    if not target.exists() or target.stat().st_mtime < newest or force or linked != SANITIZE:
         cmd = [NVCC, *GENCODE, "-shared", "-o", str(target), *map(str, objs), "-lpthread", "-lrt", "-ldl"]
-        if SANITIZE:
+        if SANITIZE == "coverage":
+            cmd += ["-Xcompiler", "--coverage", "-lgcov"]
+        elif SANITIZE:
             cmd += ["-Xcompiler", f"-fsanitize={SANITIZE}"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+        mode_file.write_text(SANITIZE)
     return target
 
 
