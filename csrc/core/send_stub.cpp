@@ -10,6 +10,7 @@
 #include "core/completion.h"
 #include "core/envcfg.h"
 #include "core/fault_inject.h"
+#include "plan/device_plan.h"
 #include "plan/planner.h"
 #include "transport/verify.h"
 
@@ -114,6 +115,7 @@ struct PendingBatch {
   Timepoint iter_start, enqueued;
   // end-to-end check: the batch's byte ranges and the destination they were sent to (empty: not checked)
   std::vector<std::vector<IpcBlock>> check_blocks;
+  AttnCheck check_src_rows, check_dst_rows;   // the row form, for a batch that changes the layout
   WorkerInfo check_dst;
 };
 
@@ -192,8 +194,30 @@ struct KvSendStub::Impl {
   void keep_check_blocks(PendingBatch& pb, const std::vector<std::vector<IpcBlock>>* planned) {
     const int dst_shape = dstinfo->cache_shape_or(cache_shape);
     const char* why = nullptr;
-    if (dst_shape != cache_shape) why = "it converts the cache layout";
-    else if (dstinfo->ext_int("mx", env_dst_mxfp8()) != 0 || env.cast_bf16_to_fp8) why = "it converts the dtype";
+    if (dstinfo->ext_int("mx", env_dst_mxfp8()) != 0 || env.cast_bf16_to_fp8) {
+      why = "it converts the dtype";
+    } else if (dst_shape != cache_shape) {
+      // no common byte ranges, but common rows: what the fused attention kernel moves
+      DeviceAttnParams p;
+      why = "it converts a cache layout that has no row description";
+      if (planned == nullptr && check_ctx->device_id() >= 0 && device_attn_params(env, planner.kind, cache_shape, dst_shape, false, &p, nullptr)) {
+        if (p.skip) return;          // this rank holds only replicas: it sent nothing
+        pb.check_src_rows.layout = p.src;
+        pb.check_src_rows.head0 = p.src_head0;
+        pb.check_dst_rows.layout = p.dst;
+        pb.check_dst_rows.head0 = p.dst_head0;
+        pb.check_src_rows.n_heads = pb.check_dst_rows.n_heads = p.n_heads;
+        uint32_t index = 0;
+        for (const ReqSendTask* t : pb.send_req) {
+          if (t->src_blocks().empty() || t->dst_blocks().empty()) continue;
+          pb.check_src_rows.add(t->src_blocks()[0], t->seen_tokens, t->new_tokens, index);
+          pb.check_dst_rows.add(t->dst_blocks()[0], t->seen_tokens, t->new_tokens, index);
+          ++index;
+        }
+        pb.check_dst = *dstinfo;
+        return;
+      }
+    }
     if (why == nullptr) {
       try {
         if (planned != nullptr) {
@@ -218,7 +242,10 @@ struct KvSendStub::Impl {
   // Second half, when the batch has landed: compare the two caches.  False fails the batch.
   bool run_check(PendingBatch& pb) noexcept {
     try {
-      const CheckOutcome o = verify_transfer(check_ctx, pb.check_dst, start_layer, num_layers, pb.check_blocks);
+      const CheckOutcome o = pb.check_blocks.empty()
+                                 ? verify_attn_transfer(check_ctx, pb.check_dst, start_layer, num_layers, pb.check_src_rows,
+                                                        pb.check_dst_rows)
+                                 : verify_transfer(check_ctx, pb.check_dst, start_layer, num_layers, pb.check_blocks);
       pb.flush_out += ",Check=" + std::string(o.ok ? "ok" : "MISMATCH") + ",CheckLocalUs=" + std::to_string(o.local_us) +
                       ",CheckRemoteUs=" + std::to_string(o.remote_us);
       if (!o.ok) {
@@ -272,7 +299,7 @@ struct KvSendStub::Impl {
     BatchSendTask& batch = pb.batch;
     const size_t step_idx = batch.step->step_idx;
     Timepoint send_finish = SteadyClock::now();
-    if (ok && !pb.check_blocks.empty()) {
+    if (ok && (!pb.check_blocks.empty() || !pb.check_src_rows.reqs.empty())) {
       ok = run_check(pb);
       pb.check_blocks.clear();
       send_finish = SteadyClock::now();

@@ -391,6 +391,19 @@ typedef struct {
 int kvt_launch_checksum(uint64_t base, uint64_t capacity, const KvtCheckChunk* d_chunks, uint32_t n, uint64_t* d_out,
                         uint32_t* d_status, int grid_ctas, void* stream);
 uint64_t kvt_checksum_host(const void* data, uint64_t len, uint32_t index0);
+// The same sum over the rows of an attention cache: for every request, token t in [seen, seen + new_tokens), K / V
+// and head j in [0, n_heads), the head_bytes at
+//   table[t / ntpb] * block_stride + kv * kv_stride + (t % ntpb) * token_stride + (head0 + j) * head_stride
+// with the byte at position b of the row keyed by index
+//   ((((index * 131 + t) * kv_count + kv) * n_heads + j) * head_bytes + b)        (32-bit arithmetic),
+// which names the row by coordinates that do not depend on the layout.  `first` is the exclusive prefix sum of
+// new_tokens over the requests; tables are [blk_off, blk_off + n_blocks) of the pool.
+typedef struct {
+  uint32_t blk_off, n_blocks, seen, new_tokens, first, index;
+} KvtCheckReq;
+int kvt_launch_checksum_attn(uint64_t base, uint64_t capacity, const KvtLayout* layout, uint32_t head0, uint32_t n_heads,
+                             const KvtCheckReq* d_reqs, uint32_t n_reqs, uint32_t total_tokens, const uint32_t* d_pool,
+                             uint32_t pool_len, uint64_t* d_out, uint32_t* d_status, int grid_ctas, void* stream);
 
 // ---- peer memory / topology ---------------------------------------------------------------
 int kvt_device_count(void);

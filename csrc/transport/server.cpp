@@ -216,6 +216,8 @@ class TransferServer : public ITransferServer {
           continue;     // one-way: a flushed batch is answered with PULL_DONE when its completion record arrives
         } else if (magic == CHECK_REQ) {
           resp = answer_check(ctx_, buf, n);
+        } else if (magic == CHECK_ATTN_REQ) {
+          resp = answer_check_attn(ctx_, buf, n);
         } else if (magic == PING_REQ) {
           resp.assign(buf, std::min<size_t>(n, RPC_HEADER));
           put(resp, static_cast<uint32_t>(WIRE_OK));

@@ -9,9 +9,11 @@
 // side reads its own memory where it lives (a kernel for GPU caches, a loop for host caches), so no CPU
 // mapping of device memory is needed; and the value is a 64-bit sum, not a CRC-32.
 //
-// Only transfers that byte ranges can describe are checked: source and destination cache of one layout
-// and dtype.  A transfer that converts the layout or quantises says so once and goes unchecked, as the
-// reference goes unchecked where it has no CPU mapping of a tensor.
+// Two forms.  Byte ranges (CHECK_REQ): source and destination cache of one layout and dtype, any shape, any
+// transport.  Rows (CHECK_ATTN_REQ): a transfer of the fused attention kernel that changes the layout or moves a
+// head window (GPU caches); each side walks its own block tables with its own strides and keys every byte by the
+// logical coordinates of its row.  A transfer that changes the dtype (quantises) says so once and goes unchecked:
+// its two sides differ by design.
 //
 // The per-(layer, tensor) sums are rotated by a layer- and tensor-dependent amount before they are added,
 // so that data landing in the wrong layer or tensor changes the result.
@@ -22,6 +24,7 @@
 
 #include "core/context.h"
 #include "core/types.h"
+#include "kernels/kvt_kernels.h"
 
 namespace kvx {
 
@@ -46,7 +49,23 @@ struct CheckOutcome {
 CheckOutcome verify_transfer(Context* ctx, const WorkerInfo& dst, uint32_t layer_begin, uint32_t layer_end,
                              const std::vector<std::vector<IpcBlock>>& blocks);
 
-// Server side: the whole response frame for a CHECK_REQ frame (`buf` starts at the RPC header).
+// Row form: one side of a transfer between attention caches (tensor 0 of every layer).
+struct AttnCheck {
+  KvtLayout layout{};
+  uint32_t head0{0}, n_heads{0};
+  std::vector<KvtCheckReq> reqs;      // `first` and `index` are filled by add()
+  std::vector<uint32_t> pool;
+  uint32_t total_tokens{0};
+  // tokens [seen, seen + new_tokens) of a request whose block table on this side is `blocks`; `index` is the
+  // request's number in the batch (the same on both sides)
+  void add(const std::vector<uint32_t>& blocks, uint32_t seen, uint32_t new_tokens, uint32_t index);
+};
+uint64_t checksum_attn(Context* ctx, uint32_t layer_begin, uint32_t layer_end, const AttnCheck& side);
+CheckOutcome verify_attn_transfer(Context* ctx, const WorkerInfo& dst, uint32_t layer_begin, uint32_t layer_end,
+                                  const AttnCheck& src_side, const AttnCheck& dst_side);
+
+// Server side: the whole response frame for a CHECK_REQ / CHECK_ATTN_REQ frame (`buf` starts at the RPC header).
 std::string answer_check(Context* ctx, const char* buf, size_t len);
+std::string answer_check_attn(Context* ctx, const char* buf, size_t len);
 
 }  // namespace kvx

@@ -37,6 +37,7 @@ constexpr uint32_t PULL_DONE = 0x4B565044;             // 'KVPD': [status u32][d
 // End-to-end check of a finished batch (transport/verify.h): the ranges a batch wrote, answered with the
 // checksum of what the destination's cache holds there.
 constexpr uint32_t CHECK_REQ = 0x4B56436B;             // 'KVCk'
+constexpr uint32_t CHECK_ATTN_REQ = 0x4B56436C;        // 'KVCl': the row form, for transfers that change the layout
 constexpr size_t RPC_HEADER = sizeof(uint32_t) + sizeof(uint64_t);
 
 enum WireStatus : uint32_t { WIRE_OK = 0, WIRE_BAD_REQUEST = 400, WIRE_INTERNAL = 500 };

@@ -475,3 +475,112 @@ def test_server_check_request_over_a_device_cache(ops):
             assert second == (0, expect()) and second[1] != first[1]
     finally:
         srv.stop()
+
+
+def _rows_oracle(ops, lay, flat, head0, n_heads, reqs):
+    """The row form of the check, spelled out: every (request, token, K / V, head) row keyed by its logical
+    coordinates, summed with the CPU function."""
+    import dataclasses
+
+    as_bytes = dataclasses.replace(lay, head_dim=lay.head_bytes, elem_bytes=1)
+    v = as_bytes.view(flat.cpu(), torch.uint8).numpy()           # [block, kv, slot, head, byte]
+    total = 0
+    for blocks, seen, new, index in reqs:
+        for t in range(seen, seen + new):
+            blk, slot = blocks[t // lay.ntpb], t % lay.ntpb
+            for kv in range(lay.kv_count):
+                for j in range(n_heads):
+                    row_id = (((index * 131 + t) * lay.kv_count + kv) * n_heads + j) & 0xFFFFFFFF
+                    total += ops.kvt_checksum_host(v[blk, kv, slot, head0 + j].copy(), (row_id * lay.head_bytes) & 0xFFFFFFFF)
+    return total & 0xFFFFFFFFFFFFFFFF
+
+
+def _rows_kernel(ops, lay, flat, head0, n_heads, reqs, grid=0):
+    import numpy as np
+
+    pool, rows, first = [], [], 0
+    for blocks, seen, new, index in reqs:
+        rows.append((len(pool), len(blocks), seen, new, first, index))
+        pool += blocks
+        first += new
+    d_reqs = torch.tensor(np.array(rows, dtype=np.uint32).view(np.int32), device=DEV)
+    d_pool = torch.tensor(np.array(pool, dtype=np.uint32).view(np.int32), device=DEV)
+    out = torch.zeros(2, dtype=torch.int64, device=DEV)
+    ops.kvt_launch_checksum_attn(flat.data_ptr(), flat.numel(), lay.to_kvt(), head0, n_heads, d_reqs.data_ptr(), len(rows), first,
+                                 d_pool.data_ptr(), len(pool), out.data_ptr(), out.data_ptr() + 8, grid,
+                                 torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    return int(out[0].item()) & 0xFFFFFFFFFFFFFFFF, int(out[1].item())
+
+
+def test_row_checksum_is_the_same_on_both_sides_of_a_layout_change(ops):
+    """NHD pages with 8 heads against HND pages with 4 heads that received heads 4..7: the kernel's sums
+    over the two layouts agree with each other and with the spelled-out oracle; one flipped bit in a moved row,
+    or two rows exchanged, changes the destination's sum."""
+    src_l = AttnLayout(CacheShape.FLASH, 24, 16, 8, 64, 2)
+    dst_l = AttnLayout(CacheShape.FLASHINFER, 30, 32, 4, 64, 2)
+    src = src_l.alloc(DEV, "normal", seed=3)
+    dst = dst_l.alloc(DEV)
+    moves = [([3, 9, 1], [7, 2], 5, 40), ([5, 6], [11], 0, 21), ([20], [21], 0, 16)]     # src blocks, dst blocks, seen, new
+    chunks = [ReqChunk(sb, db, seen, new) for sb, db, seen, new in moves]
+    reference_transfer(src_l, dst_l, src, dst, chunks, HeadMap(4, 0, 4))
+    s_reqs = [(sb, seen, new, i) for i, (sb, _, seen, new) in enumerate(moves)]
+    d_reqs = [(db, seen, new, i) for i, (_, db, seen, new) in enumerate(moves)]
+    s_sum, s_st = _rows_kernel(ops, src_l, src, 4, 4, s_reqs)
+    d_sum, d_st = _rows_kernel(ops, dst_l, dst, 0, 4, d_reqs)
+    assert (s_st, d_st) == (0, 0)
+    assert s_sum == d_sum == _rows_oracle(ops, src_l, src, 4, 4, s_reqs) == _rows_oracle(ops, dst_l, dst, 0, 4, d_reqs)
+    assert _rows_kernel(ops, dst_l, dst, 0, 4, d_reqs, grid=2)[0] == d_sum
+    v = dst_l.view(dst, torch.bfloat16)
+    keep = v[7, 1, 9, 2].clone()
+    v[7, 1, 9, 2, 5] = -v[7, 1, 9, 2, 5]                      # token 9 of request 0, V, head 2: sign bit of one value
+    assert _rows_kernel(ops, dst_l, dst, 0, 4, d_reqs)[0] != d_sum
+    v[7, 1, 9, 2] = keep
+    assert _rows_kernel(ops, dst_l, dst, 0, 4, d_reqs)[0] == d_sum
+    other = v[7, 1, 10, 2].clone()
+    v[7, 1, 10, 2] = keep                                     # two tokens' rows exchanged: same bytes, other places
+    v[7, 1, 9, 2] = other
+    assert _rows_kernel(ops, dst_l, dst, 0, 4, d_reqs)[0] != d_sum
+    # a block id outside the tensor is reported, not read
+    bad = [([40], 0, 16, 0)]
+    assert _rows_kernel(ops, dst_l, dst, 0, 4, bad)[1] & 0xFFFFFFFF != 0
+
+
+@pytest.mark.parametrize("tp", ["equal", "p_gt_d"])
+def test_transfer_check_of_a_layout_converting_transfer(tp, ops):
+    """BLLM_KVTRANS_CRC=1 on the fused NHD -> HND path (equal TP, and prefill TP 2 -> decode TP 1 where this
+    rank's heads land in the upper half of the destination's): the row form passes intact batches, chunked
+    included, and fails the batch whose sender-side sum is perturbed."""
+    os.environ["BLLM_KVTRANS_CRC"] = "1"
+    ops.envcfg_reset_for_test()
+    p_heads, p_tp, p_rank = (8, 1, 0) if tp == "equal" else (4, 2, 1)
+    src_l = AttnLayout(CacheShape.FLASH, 40, 16, p_heads, 128, 2)
+    dst_l = AttnLayout(CacheShape.FLASHINFER, 56, 16, 8, 128, 2)
+    src = [src_l.alloc(DEV, "normal", seed=60 + i) for i in range(L)]
+    dst = [dst_l.alloc(DEV) for _ in range(L)]
+    srv = KVTransferServer("D|0|1", 1, 0, 0, dst_l.block_bytes, dst_l.token_bytes, "fake://", dst, [PT.NVLINK],
+                           num_kv_heads=8, cache_shape=5)
+    cli = KVTransferClient(f"P|0|{p_tp}", p_tp, p_rank, p_rank, src_l.block_bytes, src_l.token_bytes, "fake://", src, [PT.NVLINK],
+                           num_kv_heads=8, cache_shape=2)
+    try:
+        w = srv.worker_info()
+        run_step(cli, "D|0|1", 0, w, [("a", [3, 9, 4], [7, 1, 8], 0, 21, False, True), ("b", [20], [21], 0, 16, True, True)], 1)
+        run_step(cli, "D|0|1", 0, w, [("a", [3, 9, 4], [7, 1, 8], 21, 20, True, False)], 2)
+        assert cli.failed_batches() == 0
+        ops.fault_inject_arm_corrupt_check(1)
+        run_step(cli, "D|0|1", 0, w, [("c", [5], [6], 0, 12, True, True)], 3)
+        assert cli.failed_batches() == 1
+        run_step(cli, "D|0|1", 0, w, [("d", [11, 12], [13, 14], 0, 32, True, True)], 4)
+        assert cli.failed_batches() == 1
+        chunks = [ReqChunk([3, 9, 4], [7, 1, 8], 0, 41), ReqChunk([20], [21], 0, 16), ReqChunk([5], [6], 0, 12),
+                  ReqChunk([11, 12], [13, 14], 0, 32)]
+        hm = HeadMap(0, 0, 8) if tp == "equal" else HeadMap(0, 4, 4)
+        for i in range(L):
+            expect = torch.zeros_like(dst[i])
+            reference_transfer(src_l, dst_l, src[i], expect, chunks, hm)
+            assert torch.equal(dst[i], expect)
+    finally:
+        ops.fault_inject_arm_corrupt_check(0)
+        srv.stop()
+        os.environ.pop("BLLM_KVTRANS_CRC", None)
+        ops.envcfg_reset_for_test()

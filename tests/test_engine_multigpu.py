@@ -237,14 +237,15 @@ def test_kernels_on_the_decode_gpu_or_on_the_prefill_gpu(pull):
     """Pull (default between two worker processes): a session on the decode worker's server maps the
     prefill cache and its layer events and runs the kernels there, loading over NVLink.  Push: the
     prefill GPU stores; two workers inside one process always push.  Same bytes either way; the
-    metrics line names the mode."""
+    metrics line names the mode.  The run has the end-to-end check on (BLLM_KVTRANS_CRC=1)."""
     import re
     import subprocess
     import sys
 
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    env = dict(os.environ, BLLM_KVTRANS_NVLINK_PULL=str(pull), LLMOPS_CPP_MIN_LOG_LEVEL="0", NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, BLLM_KVTRANS_NVLINK_PULL=str(pull), LLMOPS_CPP_MIN_LOG_LEVEL="0", NCCL_NVLS_ENABLE="0",
+               BLLM_KVTRANS_CRC="1")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     r = subprocess.run([sys.executable, "-c", _MODE_SCRIPT], cwd=root, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stderr[-3000:]
@@ -252,6 +253,10 @@ def test_kernels_on_the_decode_gpu_or_on_the_prefill_gpu(pull):
     modes = re.findall(r"SendStubMetrics\..*Proto=nvlink,Mode=(\w+),Path=fused", r.stderr)
     assert modes[:3] == ["push"] * 3 and len(modes) >= 4, modes
     assert set(modes[3:]) == {"pull" if pull else "push"}, modes
+    # with the end-to-end check on, every batch that moved data was compared across the two GPUs (each summing its
+    # own cache in its own layout) before it was reported
+    checks = re.findall(r"SendStubMetrics\..*Check=(\w+)", r.stderr)
+    assert len(checks) >= 5 and set(checks) == {"ok"}, checks
 
 
 def _send_step(cli, stepid, reqs, tag):
