@@ -16,6 +16,17 @@ from llumnix_kv_b200.kv_transfer_impl import KVTransferClient, KVTransferProtoco
 L = 2
 
 
+@pytest.fixture(autouse=True)
+def _end_to_end_check_on(ops):
+    """Every transfer of this file also runs the end-to-end check (byte-range form): multi-tensor layers, block
+    groups, zero fills and every TP relation must give the same sum on both sides."""
+    os.environ["BLLM_KVTRANS_CRC"] = "1"
+    ops.envcfg_reset_for_test()
+    yield
+    os.environ.pop("BLLM_KVTRANS_CRC", None)
+    ops.envcfg_reset_for_test()
+
+
 def _tensors(sizes, nblocks, fill):
     g = torch.Generator().manual_seed(11)
     out = []
@@ -47,6 +58,7 @@ def _run(ops, shape, p, d, tasks, kw_p=None, kw_d=None, proto=PT.TCP):
             cli.record_event(layer)
         cli.flush_send_step()
         cli.drain()
+        assert cli.failed_batches() == 0
         W = ops.WorkerInfo
         pw, dw = W.from_string(cli.worker_info()), W.from_string(srv.worker_info())
         for w, kw in ((pw, kw_p), (dw, kw_d)):
