@@ -1308,7 +1308,6 @@ def relay_bandwidth(K, rank: int, world: int, dev, tokens: int = 8192, n_layers:
     A step moves k * requests_per_worker requests of ``tokens`` tokens.  Timed on the prefill rank (the steps
     end when their completion records have been read), one step in flight ahead; every decode rank verifies
     every request in every layer afterwards."""
-    import datetime
     import tempfile
 
     import torch.distributed as dist
@@ -1449,7 +1448,6 @@ def tp_mismatch_fp8_engine(K, rank: int, world: int, dev, n_layers: int = 80, st
     ``min_tokens``..``max_tokens``) to the decode instances in turn; the heads are resharded and quantised
     inside the transfer kernel.  Timed on the prefill ranks, one step in flight ahead, max over ranks; the
     decode workers compare the last request they received with the quantiser's oracle."""
-    import datetime
 
     import torch.distributed as dist
 

@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import dataclasses
 from collections.abc import AsyncGenerator
-from typing import Any, Optional
+from typing import Optional
 
 import msgspec
 

@@ -31,7 +31,7 @@ import time
 import uuid
 from collections import OrderedDict, defaultdict, deque
 from dataclasses import dataclass, field
-from typing import Any, Optional
+from typing import Optional
 
 import msgspec
 

@@ -19,7 +19,6 @@ Lifecycle (blade_kvt/hybrid_connector/__init__.py:699-1538):
 from __future__ import annotations
 
 import asyncio
-import contextlib
 import json
 import logging
 import struct

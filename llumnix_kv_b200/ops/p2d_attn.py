@@ -11,7 +11,7 @@ reference's channel ``register_data`` / ``send_data(layer)`` pair
 from __future__ import annotations
 
 import dataclasses
-from typing import List, Optional, Sequence, Tuple
+from typing import Optional, Sequence, Tuple
 
 import torch
 
