@@ -108,7 +108,7 @@ uint64_t checksum_device(Context* ctx, uint32_t lb, uint32_t le, const std::vect
       const size_t n = first[t + 1] - first[t];
       if (n == 0) continue;
       const int rc = kvt_launch_checksum(addrs[l][t], ctx->tensor_capacity(t), d_chunks + first[t], static_cast<uint32_t>(n),
-                                         s.sums + (l - lb) * n_tensors + t, status, sms > 0 ? sms * 4 : 0, s.stream);
+                                         s.sums + (l - lb) * n_tensors + t, status, sms > 0 ? sms * 8 : 0, s.stream);
       if (rc != 0) cu(static_cast<cudaError_t>(rc), "launch");
     }
   }
@@ -319,7 +319,7 @@ uint64_t checksum_attn(Context* ctx, uint32_t lb, uint32_t le, const AttnCheck& 
     const int rc = kvt_launch_checksum_attn(addrs[l][0], capacity, &c.layout, c.head0, c.n_heads,
                                             reinterpret_cast<const KvtCheckReq*>(s.buf), static_cast<uint32_t>(c.reqs.size()),
                                             c.total_tokens, reinterpret_cast<const uint32_t*>(s.buf + pool_at),
-                                            static_cast<uint32_t>(c.pool.size()), s.sums + (l - lb), status, sms > 0 ? sms * 4 : 0,
+                                            static_cast<uint32_t>(c.pool.size()), s.sums + (l - lb), status, sms > 0 ? sms * 8 : 0,
                                             s.stream);
     if (rc != 0) cu(static_cast<cudaError_t>(rc), "launch");
   }
