@@ -296,27 +296,28 @@ void bind_kernels(py::module_& m) {
     return kvt_checksum_host(bi.ptr, static_cast<uint64_t>(bi.size) * static_cast<uint64_t>(bi.itemsize), index0);
   }, py::arg("data"), py::arg("index0") = 0);
   m.def("kvt_launch_checksum",
-        [](uint64_t base, uint64_t capacity, uint64_t chunks, uint32_t n, uint64_t out, uint64_t status, int grid,
-           uint64_t stream) {
-          check_cuda(kvt_launch_checksum(base, capacity, reinterpret_cast<const KvtCheckChunk*>(chunks), n,
-                                         reinterpret_cast<uint64_t*>(out), reinterpret_cast<uint32_t*>(status), grid,
-                                         reinterpret_cast<void*>(stream)),
+        [](uint64_t bases, uint32_t n_bases, uint64_t capacity, uint64_t chunks, uint32_t n, uint64_t out, uint64_t status,
+           int grid, uint64_t stream) {
+          check_cuda(kvt_launch_checksum(reinterpret_cast<const uint64_t*>(bases), n_bases, capacity,
+                                         reinterpret_cast<const KvtCheckChunk*>(chunks), n, reinterpret_cast<uint64_t*>(out),
+                                         reinterpret_cast<uint32_t*>(status), grid, reinterpret_cast<void*>(stream)),
                      "kvt_launch_checksum");
         },
-        py::arg("base"), py::arg("capacity"), py::arg("chunks"), py::arg("n"), py::arg("out"), py::arg("status"),
-        py::arg("grid"), py::arg("stream"));
+        py::arg("bases"), py::arg("n_bases"), py::arg("capacity"), py::arg("chunks"), py::arg("n"), py::arg("out"),
+        py::arg("status"), py::arg("grid"), py::arg("stream"));
   // the row form: device arrays of {blk_off, n_blocks, seen, new_tokens, first, index} (u32 x 6) and of block ids
   m.def("kvt_launch_checksum_attn",
-        [](uint64_t base, uint64_t capacity, const KvtLayout& layout, uint32_t head0, uint32_t n_heads, uint64_t reqs,
-           uint32_t n_reqs, uint32_t total_tokens, uint64_t pool, uint32_t pool_len, uint64_t out, uint64_t status, int grid,
-           uint64_t stream) {
-          check_cuda(kvt_launch_checksum_attn(base, capacity, &layout, head0, n_heads, reinterpret_cast<const KvtCheckReq*>(reqs),
-                                              n_reqs, total_tokens, reinterpret_cast<const uint32_t*>(pool), pool_len,
-                                              reinterpret_cast<uint64_t*>(out), reinterpret_cast<uint32_t*>(status), grid,
-                                              reinterpret_cast<void*>(stream)),
+        [](uint64_t bases, uint32_t n_bases, uint64_t capacity, const KvtLayout& layout, uint32_t head0, uint32_t n_heads,
+           uint64_t reqs, uint32_t n_reqs, uint32_t total_tokens, uint64_t pool, uint32_t pool_len, uint64_t out, uint64_t status,
+           int grid, uint64_t stream) {
+          check_cuda(kvt_launch_checksum_attn(reinterpret_cast<const uint64_t*>(bases), n_bases, capacity, &layout, head0, n_heads,
+                                              reinterpret_cast<const KvtCheckReq*>(reqs), n_reqs, total_tokens,
+                                              reinterpret_cast<const uint32_t*>(pool), pool_len, reinterpret_cast<uint64_t*>(out),
+                                              reinterpret_cast<uint32_t*>(status), grid, reinterpret_cast<void*>(stream)),
                      "kvt_launch_checksum_attn");
         },
-        py::arg("base"), py::arg("capacity"), py::arg("layout"), py::arg("head0"), py::arg("n_heads"), py::arg("reqs"),
+        py::arg("bases"), py::arg("n_bases"), py::arg("capacity"), py::arg("layout"), py::arg("head0"), py::arg("n_heads"),
+        py::arg("reqs"),
         py::arg("n_reqs"), py::arg("total_tokens"), py::arg("pool"), py::arg("pool_len"), py::arg("out"), py::arg("status"),
         py::arg("grid"), py::arg("stream"));
   m.def("kvt_bf16_to_e4m3", [](uint16_t bits) { return static_cast<int>(kvt_bf16_to_e4m3(bits)); });

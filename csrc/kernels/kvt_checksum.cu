@@ -43,10 +43,13 @@ __device__ __forceinline__ uint64_t word_terms(uint32_t w, uint32_t index) {
          term(index + 3, w >> 24);
 }
 
-__global__ void __launch_bounds__(256) kvt_checksum_kernel(const uint8_t* __restrict__ base, uint64_t capacity,
+// blockIdx.y names the tensor instance (one per layer): the same chunks are summed over bases[y] into out[y].
+__global__ void __launch_bounds__(256) kvt_checksum_kernel(const uint64_t* __restrict__ bases, uint64_t capacity,
                                                            const KvtCheckChunk* __restrict__ chunks, uint32_t n,
                                                            unsigned long long* __restrict__ out,
                                                            uint32_t* __restrict__ status) {
+  const uint8_t* __restrict__ base = reinterpret_cast<const uint8_t*>(bases[blockIdx.y]);
+  out += blockIdx.y;
   uint64_t acc = 0;
   for (uint32_t c = blockIdx.x; c < n; c += gridDim.x) {
     const KvtCheckChunk ch = chunks[c];
@@ -71,12 +74,14 @@ __global__ void __launch_bounds__(256) kvt_checksum_kernel(const uint8_t* __rest
 }
 
 // One CTA per token, one warp per (K or V, head) row of it.
-__global__ void __launch_bounds__(256) kvt_checksum_attn_kernel(const uint8_t* __restrict__ base, uint64_t capacity,
+__global__ void __launch_bounds__(256) kvt_checksum_attn_kernel(const uint64_t* __restrict__ bases, uint64_t capacity,
                                                                 const KvtLayout lay, uint32_t head0, uint32_t n_heads,
                                                                 const KvtCheckReq* __restrict__ reqs, uint32_t n_reqs,
                                                                 uint32_t total_tokens, const uint32_t* __restrict__ pool,
                                                                 uint32_t pool_len, unsigned long long* __restrict__ out,
                                                                 uint32_t* __restrict__ status) {
+  const uint8_t* __restrict__ base = reinterpret_cast<const uint8_t*>(bases[blockIdx.y]);
+  out += blockIdx.y;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, n_warps = blockDim.x >> 5;
   const uint32_t rows = lay.kv_count * n_heads;
   uint64_t acc = 0;
@@ -127,26 +132,30 @@ __global__ void __launch_bounds__(256) kvt_checksum_attn_kernel(const uint8_t* _
 
 }  // namespace
 
-extern "C" int kvt_launch_checksum_attn(uint64_t base, uint64_t capacity, const KvtLayout* layout, uint32_t head0,
-                                        uint32_t n_heads, const KvtCheckReq* d_reqs, uint32_t n_reqs, uint32_t total_tokens,
-                                        const uint32_t* d_pool, uint32_t pool_len, uint64_t* d_out, uint32_t* d_status,
-                                        int grid_ctas, void* stream) {
-  if (n_reqs == 0 || total_tokens == 0 || n_heads == 0) return 0;
-  if (layout->ntpb == 0 || layout->head_bytes == 0 || layout->kv_count == 0) return (int)cudaErrorInvalidValue;
-  const uint32_t grid = (uint32_t)(grid_ctas > 0 ? grid_ctas : 148 * 4);
-  kvt_checksum_attn_kernel<<<grid < total_tokens ? grid : total_tokens, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const uint8_t*>(base), capacity, *layout, head0, n_heads, d_reqs, n_reqs, total_tokens, d_pool, pool_len,
+extern "C" int kvt_launch_checksum_attn(const uint64_t* d_bases, uint32_t n_bases, uint64_t capacity, const KvtLayout* layout,
+                                        uint32_t head0, uint32_t n_heads, const KvtCheckReq* d_reqs, uint32_t n_reqs,
+                                        uint32_t total_tokens, const uint32_t* d_pool, uint32_t pool_len, uint64_t* d_out,
+                                        uint32_t* d_status, int grid_ctas, void* stream) {
+  if (n_reqs == 0 || total_tokens == 0 || n_heads == 0 || n_bases == 0) return 0;
+  if (layout->ntpb == 0 || layout->head_bytes == 0 || layout->kv_count == 0 || n_bases > 65535u) return (int)cudaErrorInvalidValue;
+  const uint32_t want = (uint32_t)(grid_ctas > 0 ? grid_ctas : 148 * 8);
+  const uint32_t per = (want + n_bases - 1) / n_bases;        // the grid is spread over the tensors
+  const dim3 grid(per < total_tokens ? (per > 0 ? per : 1) : total_tokens, n_bases);
+  kvt_checksum_attn_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      d_bases, capacity, *layout, head0, n_heads, d_reqs, n_reqs, total_tokens, d_pool, pool_len,
       reinterpret_cast<unsigned long long*>(d_out), d_status);
   return (int)cudaGetLastError();
 }
 
-extern "C" int kvt_launch_checksum(uint64_t base, uint64_t capacity, const KvtCheckChunk* d_chunks, uint32_t n,
-                                   uint64_t* d_out, uint32_t* d_status, int grid_ctas, void* stream) {
-  if (n == 0) return 0;
-  const uint32_t grid = (uint32_t)(grid_ctas > 0 ? grid_ctas : 148 * 4);
-  kvt_checksum_kernel<<<grid < n ? grid : n, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const uint8_t*>(base), capacity, d_chunks, n, reinterpret_cast<unsigned long long*>(d_out),
-      d_status);
+extern "C" int kvt_launch_checksum(const uint64_t* d_bases, uint32_t n_bases, uint64_t capacity, const KvtCheckChunk* d_chunks,
+                                   uint32_t n, uint64_t* d_out, uint32_t* d_status, int grid_ctas, void* stream) {
+  if (n == 0 || n_bases == 0) return 0;
+  if (n_bases > 65535u) return (int)cudaErrorInvalidValue;
+  const uint32_t want = (uint32_t)(grid_ctas > 0 ? grid_ctas : 148 * 8);
+  const uint32_t per = (want + n_bases - 1) / n_bases;
+  const dim3 grid(per < n ? (per > 0 ? per : 1) : n, n_bases);
+  kvt_checksum_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      d_bases, capacity, d_chunks, n, reinterpret_cast<unsigned long long*>(d_out), d_status);
   return (int)cudaGetLastError();
 }
 

@@ -380,16 +380,18 @@ int kvt_launch_stamp(uint64_t* slot, void* stream);
 // ---- end-to-end transfer check -------------------------------------------------------------
 // Position-keyed 64-bit checksum of byte ranges of one tensor (kvt_checksum.cu): each byte adds
 // mix32(((i & 0xFFFFFF) << 8) | byte), i = its index in its piece.  Chunks are pieces cut to <= 64 KiB;
-// index0 is the index of the chunk's first byte in its piece.  The kernel ADDS to *d_out (zero it first), skips
-// a chunk outside [0, capacity) and reports it in d_status {KVT_ERR_BLOCK_RANGE, chunk number}.
+// index0 is the index of the chunk's first byte in its piece.  One launch sums the same chunks over n_bases tensors of
+// one shape (the layers of a cache): d_bases is a device array of their addresses and d_out[i] receives tensor i's
+// sum.  The kernel ADDS to d_out (zero it first), skips a chunk outside [0, capacity) and reports it in d_status
+// {KVT_ERR_BLOCK_RANGE, chunk number}.  grid_ctas is the total over all tensors.
 typedef struct {
   uint64_t off;
   uint32_t len;
   uint32_t index0;
 } KvtCheckChunk;
 #define KVT_CHECK_CHUNK 65536u
-int kvt_launch_checksum(uint64_t base, uint64_t capacity, const KvtCheckChunk* d_chunks, uint32_t n, uint64_t* d_out,
-                        uint32_t* d_status, int grid_ctas, void* stream);
+int kvt_launch_checksum(const uint64_t* d_bases, uint32_t n_bases, uint64_t capacity, const KvtCheckChunk* d_chunks, uint32_t n,
+                        uint64_t* d_out, uint32_t* d_status, int grid_ctas, void* stream);
 uint64_t kvt_checksum_host(const void* data, uint64_t len, uint32_t index0);
 // The same sum over the rows of an attention cache: for every request, token t in [seen, seen + new_tokens), K / V
 // and head j in [0, n_heads), the head_bytes at
@@ -401,9 +403,10 @@ uint64_t kvt_checksum_host(const void* data, uint64_t len, uint32_t index0);
 typedef struct {
   uint32_t blk_off, n_blocks, seen, new_tokens, first, index;
 } KvtCheckReq;
-int kvt_launch_checksum_attn(uint64_t base, uint64_t capacity, const KvtLayout* layout, uint32_t head0, uint32_t n_heads,
-                             const KvtCheckReq* d_reqs, uint32_t n_reqs, uint32_t total_tokens, const uint32_t* d_pool,
-                             uint32_t pool_len, uint64_t* d_out, uint32_t* d_status, int grid_ctas, void* stream);
+int kvt_launch_checksum_attn(const uint64_t* d_bases, uint32_t n_bases, uint64_t capacity, const KvtLayout* layout, uint32_t head0,
+                             uint32_t n_heads, const KvtCheckReq* d_reqs, uint32_t n_reqs, uint32_t total_tokens,
+                             const uint32_t* d_pool, uint32_t pool_len, uint64_t* d_out, uint32_t* d_status, int grid_ctas,
+                             void* stream);
 
 // ---- peer memory / topology ---------------------------------------------------------------
 int kvt_device_count(void);

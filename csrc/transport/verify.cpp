@@ -99,23 +99,32 @@ uint64_t checksum_device(Context* ctx, uint32_t lb, uint32_t le, const std::vect
   std::lock_guard<std::mutex> g(g_mu);
   cu(cudaSetDevice(dev), "cudaSetDevice");   // the calling threads are the transport's own: nothing to restore
   DeviceScratch& s = g_scratch[dev];
-  const size_t n_sums = static_cast<size_t>(le - lb) * n_tensors;
-  uint32_t* status = s.prepare(host.data(), host.size() * sizeof(KvtCheckChunk), n_sums);
-  const KvtCheckChunk* d_chunks = reinterpret_cast<const KvtCheckChunk*>(s.buf);
+  const size_t n_layers = le - lb;
+  const size_t n_sums = n_layers * n_tensors;
+  // device image: [tensor t: the n_layers base addresses][chunks]; sums[t * n_layers + layer]
+  std::vector<uint64_t> bases;
+  bases.reserve(n_sums);
+  for (size_t t = 0; t < n_tensors; ++t)
+    for (uint32_t l = lb; l < le; ++l) bases.push_back(addrs[l][t]);
+  std::string image(reinterpret_cast<const char*>(bases.data()), bases.size() * sizeof(uint64_t));
+  const size_t chunks_at = image.size();
+  image.append(reinterpret_cast<const char*>(host.data()), host.size() * sizeof(KvtCheckChunk));
+  uint32_t* status = s.prepare(image.data(), image.size(), n_sums);
+  const uint64_t* d_bases = reinterpret_cast<const uint64_t*>(s.buf);
+  const KvtCheckChunk* d_chunks = reinterpret_cast<const KvtCheckChunk*>(s.buf + chunks_at);
   const int sms = kvt_sm_count(dev);
-  for (uint32_t l = lb; l < le; ++l) {
-    for (size_t t = 0; t < n_tensors; ++t) {
-      const size_t n = first[t + 1] - first[t];
-      if (n == 0) continue;
-      const int rc = kvt_launch_checksum(addrs[l][t], ctx->tensor_capacity(t), d_chunks + first[t], static_cast<uint32_t>(n),
-                                         s.sums + (l - lb) * n_tensors + t, status, sms > 0 ? sms * 8 : 0, s.stream);
-      if (rc != 0) cu(static_cast<cudaError_t>(rc), "launch");
-    }
+  for (size_t t = 0; t < n_tensors; ++t) {
+    const size_t n = first[t + 1] - first[t];
+    if (n == 0) continue;
+    const int rc = kvt_launch_checksum(d_bases + t * n_layers, static_cast<uint32_t>(n_layers), ctx->tensor_capacity(t),
+                                       d_chunks + first[t], static_cast<uint32_t>(n), s.sums + t * n_layers, status,
+                                       sms > 0 ? sms * 8 : 0, s.stream);
+    if (rc != 0) cu(static_cast<cudaError_t>(rc), "launch");
   }
   const std::vector<uint64_t> out = s.collect(n_sums);
   uint64_t total = 0;
   for (uint32_t l = lb; l < le; ++l)
-    for (size_t t = 0; t < n_tensors; ++t) total += fold(out[(l - lb) * n_tensors + t], l, static_cast<uint32_t>(t));
+    for (size_t t = 0; t < n_tensors; ++t) total += fold(out[t * n_layers + (l - lb)], l, static_cast<uint32_t>(t));
   return total;
 }
 
@@ -306,7 +315,12 @@ uint64_t checksum_attn(Context* ctx, uint32_t lb, uint32_t le, const AttnCheck& 
   const uint64_t capacity = ctx->tensor_capacity(0);
   validate_attn_check(c, capacity);
   if (c.reqs.empty() || lb == le) return 0;
-  std::string host(reinterpret_cast<const char*>(c.reqs.data()), c.reqs.size() * sizeof(KvtCheckReq));
+  // device image: [the layers' base addresses][requests][block ids]
+  std::vector<uint64_t> bases;
+  for (uint32_t l = lb; l < le; ++l) bases.push_back(addrs[l][0]);
+  std::string host(reinterpret_cast<const char*>(bases.data()), bases.size() * sizeof(uint64_t));
+  const size_t reqs_at = host.size();
+  host.append(reinterpret_cast<const char*>(c.reqs.data()), c.reqs.size() * sizeof(KvtCheckReq));
   const size_t pool_at = host.size();
   host.append(reinterpret_cast<const char*>(c.pool.data()), c.pool.size() * sizeof(uint32_t));
   std::lock_guard<std::mutex> g(g_mu);
@@ -315,14 +329,12 @@ uint64_t checksum_attn(Context* ctx, uint32_t lb, uint32_t le, const AttnCheck& 
   const size_t n_sums = le - lb;
   uint32_t* status = s.prepare(host.data(), host.size(), n_sums);
   const int sms = kvt_sm_count(dev);
-  for (uint32_t l = lb; l < le; ++l) {
-    const int rc = kvt_launch_checksum_attn(addrs[l][0], capacity, &c.layout, c.head0, c.n_heads,
-                                            reinterpret_cast<const KvtCheckReq*>(s.buf), static_cast<uint32_t>(c.reqs.size()),
-                                            c.total_tokens, reinterpret_cast<const uint32_t*>(s.buf + pool_at),
-                                            static_cast<uint32_t>(c.pool.size()), s.sums + (l - lb), status, sms > 0 ? sms * 8 : 0,
-                                            s.stream);
-    if (rc != 0) cu(static_cast<cudaError_t>(rc), "launch");
-  }
+  const int rc = kvt_launch_checksum_attn(reinterpret_cast<const uint64_t*>(s.buf), static_cast<uint32_t>(n_sums), capacity, &c.layout,
+                                          c.head0, c.n_heads, reinterpret_cast<const KvtCheckReq*>(s.buf + reqs_at),
+                                          static_cast<uint32_t>(c.reqs.size()), c.total_tokens,
+                                          reinterpret_cast<const uint32_t*>(s.buf + pool_at), static_cast<uint32_t>(c.pool.size()),
+                                          s.sums, status, sms > 0 ? sms * 8 : 0, s.stream);
+  if (rc != 0) cu(static_cast<cudaError_t>(rc), "launch");
   const std::vector<uint64_t> out = s.collect(n_sums);
   uint64_t total = 0;
   for (uint32_t l = lb; l < le; ++l) total += fold(out[l - lb], l, 0);

@@ -374,23 +374,29 @@ def test_checksum_kernel_matches_the_host_function(ops):
     for i, c in enumerate(chunks):
         arr[i] = c
     d_chunks = torch.from_numpy(arr.view(np.uint8).copy()).to(DEV)
-    out = torch.zeros(2, dtype=torch.int64, device=DEV)     # [sum, status words]
+    # one launch sums the same chunks over several tensors of one shape (the layers of a cache)
+    buf2 = torch.randint(0, 256, (cap,), dtype=torch.uint8, device=DEV, generator=g)
+    host2 = buf2.cpu().numpy()
+    bases = torch.tensor([buf.data_ptr(), buf2.data_ptr()], dtype=torch.int64, device=DEV)
+    out = torch.zeros(3, dtype=torch.int64, device=DEV)     # [sum of buf, sum of buf2, status words]
     s = torch.cuda.current_stream().cuda_stream
-    ops.kvt_launch_checksum(buf.data_ptr(), cap, d_chunks.data_ptr(), len(chunks), out.data_ptr(), out.data_ptr() + 8, 0, s)
+    ops.kvt_launch_checksum(bases.data_ptr(), 2, cap, d_chunks.data_ptr(), len(chunks), out.data_ptr(), out.data_ptr() + 16, 0, s)
     torch.cuda.synchronize()
     expect = sum(ops.kvt_checksum_host(host[o:o + n], i) for o, n, i in chunks) & 0xFFFFFFFFFFFFFFFF
+    expect2 = sum(ops.kvt_checksum_host(host2[o:o + n], i) for o, n, i in chunks) & 0xFFFFFFFFFFFFFFFF
     assert int(out[0].item()) & 0xFFFFFFFFFFFFFFFF == expect
-    assert int(out[1].item()) == 0
+    assert int(out[1].item()) & 0xFFFFFFFFFFFFFFFF == expect2 != expect
+    assert int(out[2].item()) == 0
     # one grid of 3 CTAs gives the same sum as the default grid: the order of visits does not matter
-    out.zero_()
-    ops.kvt_launch_checksum(buf.data_ptr(), cap, d_chunks.data_ptr(), len(chunks), out.data_ptr(), out.data_ptr() + 8, 3, s)
+    out = torch.zeros(2, dtype=torch.int64, device=DEV)     # [sum, status words]
+    ops.kvt_launch_checksum(bases.data_ptr(), 1, cap, d_chunks.data_ptr(), len(chunks), out.data_ptr(), out.data_ptr() + 8, 3, s)
     torch.cuda.synchronize()
     assert int(out[0].item()) & 0xFFFFFFFFFFFFFFFF == expect
     # a chunk that leaves the tensor is not read
     arr[2] = (cap - 8, 16, 0)
     d_bad = torch.from_numpy(arr.view(np.uint8).copy()).to(DEV)
     out.zero_()
-    ops.kvt_launch_checksum(buf.data_ptr(), cap, d_bad.data_ptr(), len(chunks), out.data_ptr(), out.data_ptr() + 8, 0, s)
+    ops.kvt_launch_checksum(bases.data_ptr(), 1, cap, d_bad.data_ptr(), len(chunks), out.data_ptr(), out.data_ptr() + 8, 0, s)
     torch.cuda.synchronize()
     status = int(out[1].item())
     assert status & 0xFFFFFFFF != 0 and status >> 32 == 2
@@ -506,7 +512,8 @@ def _rows_kernel(ops, lay, flat, head0, n_heads, reqs, grid=0):
     d_reqs = torch.tensor(np.array(rows, dtype=np.uint32).view(np.int32), device=DEV)
     d_pool = torch.tensor(np.array(pool, dtype=np.uint32).view(np.int32), device=DEV)
     out = torch.zeros(2, dtype=torch.int64, device=DEV)
-    ops.kvt_launch_checksum_attn(flat.data_ptr(), flat.numel(), lay.to_kvt(), head0, n_heads, d_reqs.data_ptr(), len(rows), first,
+    bases = torch.tensor([flat.data_ptr()], dtype=torch.int64, device=DEV)
+    ops.kvt_launch_checksum_attn(bases.data_ptr(), 1, flat.numel(), lay.to_kvt(), head0, n_heads, d_reqs.data_ptr(), len(rows), first,
                                  d_pool.data_ptr(), len(pool), out.data_ptr(), out.data_ptr() + 8, grid,
                                  torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
