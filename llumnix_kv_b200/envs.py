@@ -1,7 +1,6 @@
 """Environment knobs of the Python control plane.
 
-The reference reads these through a forked ``vllm.envs`` (names listed in its survey of
-settings: VLLM_KV_TRANS_PROTOCOL, VLLM_ENABLE_BYPASS_TASK/SUBSTEP, VLLM_KVT_MAX_DELAY_MS,
+The reference reads these through a forked ``vllm.envs`` (VLLM_KV_TRANS_PROTOCOL, VLLM_ENABLE_BYPASS_TASK/SUBSTEP, VLLM_KVT_MAX_DELAY_MS,
 VLLM_KVT_GONE_REQ_TTL_S, VLLM_PD_TRY_CONNECT_TIMEOUT_SECONDS, VLLM_PD_CONNMANAGER_CAP,
 VLLM_KVS_*, LLUMNIX_MAX_*_MIG_IN ...).  Values are read at attribute access so tests can
 change them with ``os.environ``.
