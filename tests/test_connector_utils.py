@@ -235,3 +235,63 @@ def test_relay_choice_for_replicated_caches(monkeypatch):
     assert choose_relay("req-1", four, 1, 1) is None
     import torch
     assert multicast_kwargs([torch.zeros(16)]) == {}                                     # plain memory: nothing advertised
+
+
+# ---- the ledger against a recomputation from the full signal history -------------------------------
+def _replay(history, names, quota, tpsize):
+    """What a ledger that rescans every signal on each arrival would answer: which signals count, how many
+    ranks are complete, and the merged outcome."""
+    accepted, per_rank = [], {}
+    for rank, sig in history:
+        got = per_rank.setdefault(rank, [])
+        if names:
+            if sig.source not in names or any(s.source == sig.source for s in got):
+                continue
+        elif len(got) >= quota:
+            continue
+        got.append(sig)
+        accepted.append((rank, sig))
+    need = len(names) if names else quota
+    full = sum(1 for got in per_rank.values() if len(got) == need)
+    merged = None
+    if accepted:
+        sigs = [s for _, s in accepted]
+        failure = next((s.ex for s in sigs if s.ex is not None), None)
+        n = None if any(s.n is None for s in sigs) else min(s.n for s in sigs)
+        merged = (failure, n)
+    return [id(s) for _, s in accepted], full, merged, full >= tpsize
+
+
+def test_ledger_agrees_with_a_recomputation_over_random_signal_histories():
+    from hypothesis import given, settings, strategies as st
+
+    signal = st.tuples(st.integers(0, 3),                                   # rank
+                       st.sampled_from([None, "kvt", "kvs", "other"]),      # source
+                       st.one_of(st.none(), st.integers(0, 50)),            # token count
+                       st.booleans())                                       # failed
+
+    @settings(max_examples=300, deadline=None)
+    @given(st.lists(signal, max_size=24), st.sampled_from([(), ("kvt",), ("kvt", "kvs")]), st.integers(1, 3), st.integers(1, 4))
+    def run(raw, names, quota, tpsize):
+        led = IoState(signals_per_worker=quota)
+        led.expected_sources = names
+        table = {"r": led}
+        history, counted = [], []
+        for rank, source, n, failed in raw:
+            sig = IoRet(reqid="r", n=n, ex=CodeError(500, f"rank {rank}") if failed else None, source=source)
+            history.append((rank, sig))
+            done = try_advance(table, sig, rank, tpsize, on_signal_advanced=lambda _s, s: counted.append(id(s)))
+            want_ids, want_full, want_merged, want_done = _replay(history, names, quota, tpsize)
+            assert counted == want_ids
+            assert led.full_ranks() == want_full
+            # the ledger is handed out by the signal that completes the request and by every accepted one after it
+            assert (done is led) == (want_done and bool(counted) and counted[-1] == id(sig))
+            if want_merged is not None:
+                m = led.merge()
+                assert (m.ex, m.n) == want_merged
+            for src in ("kvt", "kvs"):
+                seen = [s for _, s in history if id(s) in want_ids and s.source == src]
+                assert led.ranks_reporting(src) == len(seen)
+                assert led.source_moved_nothing(src) == any(s.n == 0 for s in seen)
+
+    run()
