@@ -3,20 +3,22 @@
 //
 // The reference checks an RDMA transfer by CRC-32 over the source ranges on the sender's CPU (through a
 // gdrcopy mapping) and over the destination ranges on the receiver's CPU (kvtransfer/src/
-// rdma_channel.cpp:143-296, 845-852).  A CRC is a serial recurrence; a GPU wants a sum.  Here every byte
-// contributes  mix32(((i & 0xFFFFFF) << 8) | byte)  where i is the byte's index inside its piece (a piece
-// is one {offset, length} range of the transfer; both sides use the sender's piece list, so i is the same
-// on both), and a piece's value is the 64-bit sum of its bytes' terms: independent of the order in which
-// pieces and bytes are visited, sensitive to a byte's value and to its place in the piece.  Each GPU reads
-// only its own memory: nothing crosses the link for the check except the piece list and one number.
+// rdma_channel.cpp:143-296, 845-852).  A CRC is a serial recurrence; a GPU wants a sum.  Here a piece (one
+// {offset, length} range of the transfer; both sides use the sender's piece list) is read as little-endian
+// 32-bit words, the last one padded with zero bytes, and word k with value w contributes
+//   term(k, w) = mix(w * 0x9E3779B1 ^ rotl(k * 0x85EBCA77, 13)),   mix(x) = (x ^ x >> 15) * 0xC2B2AE3D, then x ^ x >> 13
+// to the piece's 64-bit sum: independent of the order in which pieces and words are visited, sensitive to a
+// word's value and to its place in the piece, three multiplies per four bytes.  Where a piece starts in memory
+// does not enter: a side whose copy of the piece is not word-aligned assembles the words from bytes.  Each GPU
+// reads only its own memory: nothing crosses the link for the check except the piece list and one number.
 //
 // A transfer that changes the cache layout (NHD pages to HND pages, a head window of a TP-mismatched pair) has no
 // common byte ranges, but it has common ROWS: the head_bytes of one (request, token, K or V, head).  The second
 // kernel walks the block tables of one side with that side's strides (the KvtLayout of the fused transfer kernel)
-// and keys every byte by its row's logical coordinates, which are the same on both sides; the sums agree exactly
+// and keys every word by its row's logical coordinates, which are the same on both sides; the sums agree exactly
 // when every row arrived intact at the slot and head the layout rule names.
 //
-// The host splits pieces into chunks of at most 64 KiB {offset, length, index of the first byte in its
+// The host splits pieces into chunks of at most 64 KiB {offset, length, index of the first word in its
 // piece} so that one long merged piece still spreads over the whole GPU; kvt_checksum_host is the same
 // function on the CPU (host-resident caches, and the oracle of the kernel's test).
 #include <cuda_runtime.h>
@@ -26,21 +28,48 @@
 
 namespace {
 
-__host__ __device__ __forceinline__ uint32_t mix32(uint32_t x) {
-  x *= 0x9E3779B1u;
+__host__ __device__ __forceinline__ uint32_t term(uint32_t k, uint32_t w) {
+  const uint32_t key = k * 0x85EBCA77u;
+  uint32_t x = (w * 0x9E3779B1u) ^ ((key << 13) | (key >> 19));
   x ^= x >> 15;
-  x *= 0x85EBCA77u;
+  x *= 0xC2B2AE3Du;
   x ^= x >> 13;
   return x;
 }
 
-__host__ __device__ __forceinline__ uint32_t term(uint32_t index, uint32_t byte) {
-  return mix32(((index & 0xFFFFFFu) << 8) | byte);
+// Word k of a piece of `len` bytes at p, whatever p's alignment; bytes past the end read as zero.
+__host__ __device__ __forceinline__ uint32_t word_at(const uint8_t* p, uint64_t len, uint64_t k) {
+  const uint64_t at = k << 2;
+  uint32_t w = 0;
+#pragma unroll
+  for (uint32_t b = 0; b < 4; ++b)
+    if (at + b < len) w |= (uint32_t)p[at + b] << (8 * b);
+  return w;
 }
 
-__device__ __forceinline__ uint64_t word_terms(uint32_t w, uint32_t index) {
-  return (uint64_t)term(index, w & 0xFFu) + term(index + 1, (w >> 8) & 0xFFu) + term(index + 2, (w >> 16) & 0xFFu) +
-         term(index + 3, w >> 24);
+// Sum of the words [0, ceil(len / 4)) of the piece part at p, the first of which is word k0 of its piece; the
+// calling threads are `lane` of `width`.
+__device__ __forceinline__ uint64_t part_sum(const uint8_t* __restrict__ p, uint32_t len, uint32_t k0, uint32_t lane,
+                                             uint32_t width) {
+  uint64_t acc = 0;
+  const uint32_t n_words = (len + 3u) >> 2;
+  uint32_t done = 0;                                   // words covered by the vector path
+  if ((reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
+    const uint4* p4 = reinterpret_cast<const uint4*>(p);
+    const uint32_t n16 = len >> 4;
+    for (uint32_t i = lane; i < n16; i += width) {
+      const uint4 v = p4[i];
+      const uint32_t k = k0 + (i << 2);
+      acc += (uint64_t)term(k, v.x) + term(k + 1, v.y) + term(k + 2, v.z) + term(k + 3, v.w);
+    }
+    done = n16 << 2;
+  }
+  const bool aligned4 = (reinterpret_cast<uintptr_t>(p) & 3u) == 0;
+  for (uint32_t k = done + lane; k < n_words; k += width) {
+    const uint32_t w = (aligned4 && (k << 2) + 4u <= len) ? reinterpret_cast<const uint32_t*>(p)[k] : word_at(p, len, k);
+    acc += term(k0 + k, w);
+  }
+  return acc;
 }
 
 // blockIdx.y names the tensor instance (one per layer): the same chunks are summed over bases[y] into out[y].
@@ -57,17 +86,7 @@ __global__ void __launch_bounds__(256) kvt_checksum_kernel(const uint64_t* __res
       if (threadIdx.x == 0 && atomicCAS(status, 0u, KVT_ERR_BLOCK_RANGE) == 0u) status[1] = c;
       continue;
     }
-    const uint8_t* p = base + ch.off;
-    if (((reinterpret_cast<uintptr_t>(p) | ch.len) & 15u) == 0) {
-      const uint4* p4 = reinterpret_cast<const uint4*>(p);
-      for (uint32_t i = threadIdx.x; i < (ch.len >> 4); i += blockDim.x) {
-        const uint4 v = p4[i];
-        const uint32_t at = ch.index0 + (i << 4);
-        acc += word_terms(v.x, at) + word_terms(v.y, at + 4) + word_terms(v.z, at + 8) + word_terms(v.w, at + 12);
-      }
-    } else {
-      for (uint32_t i = threadIdx.x; i < ch.len; i += blockDim.x) acc += term(ch.index0 + i, p[i]);
-    }
+    acc += part_sum(base + ch.off, ch.len, ch.index0, threadIdx.x, blockDim.x);
   }
   for (int d = 16; d > 0; d >>= 1) acc += __shfl_down_sync(0xFFFFFFFFu, acc, d);
   if ((threadIdx.x & 31u) == 0 && acc != 0) atomicAdd(out, (unsigned long long)acc);
@@ -84,6 +103,9 @@ __global__ void __launch_bounds__(256) kvt_checksum_attn_kernel(const uint64_t* 
   out += blockIdx.y;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, n_warps = blockDim.x >> 5;
   const uint32_t rows = lay.kv_count * n_heads;
+  const uint32_t row_words = (lay.head_bytes + 3u) >> 2;
+  const uint32_t lanes_per_row = lay.head_bytes <= 256u ? 16u : 32u, rows_per_warp = 32u / lanes_per_row;
+  const uint32_t sub = lane / lanes_per_row, sub_lane = lane % lanes_per_row;
   uint64_t acc = 0;
   for (uint32_t u = blockIdx.x; u < total_tokens; u += gridDim.x) {
     uint32_t lo = 0, hi = n_reqs;
@@ -103,27 +125,17 @@ __global__ void __launch_bounds__(256) kvt_checksum_attn_kernel(const uint64_t* 
       if (threadIdx.x == 0 && atomicCAS(status, 0u, KVT_ERR_BLOCK_RANGE) == 0u) status[1] = u;
       continue;
     }
-    for (uint32_t row = warp; row < rows; row += n_warps) {
+    // rows of up to 256 bytes take half a warp each: two rows per warp per pass
+    for (uint32_t row = warp * rows_per_warp + sub; row < rows; row += n_warps * rows_per_warp) {
       const uint32_t kv = row / n_heads, j = row % n_heads;
       const int64_t off = (int64_t)blk * lay.block_stride + (int64_t)kv * lay.kv_stride + (int64_t)slot * lay.token_stride +
                           (int64_t)(head0 + j) * lay.head_stride;
       if (off < 0 || (uint64_t)off > capacity || lay.head_bytes > capacity - (uint64_t)off) {
-        if (lane == 0 && atomicCAS(status, 0u, KVT_ERR_BLOCK_RANGE) == 0u) status[1] = u;
+        if (sub_lane == 0 && atomicCAS(status, 0u, KVT_ERR_BLOCK_RANGE) == 0u) status[1] = u;
         continue;
       }
       const uint32_t row_id = ((r.index * 131u + t) * lay.kv_count + kv) * n_heads + j;
-      const uint32_t at0 = row_id * lay.head_bytes;
-      const uint8_t* p = base + off;
-      if (((reinterpret_cast<uintptr_t>(p) | lay.head_bytes) & 15u) == 0) {
-        const uint4* p4 = reinterpret_cast<const uint4*>(p);
-        for (uint32_t i = lane; i < (lay.head_bytes >> 4); i += 32) {
-          const uint4 v = p4[i];
-          const uint32_t at = at0 + (i << 4);
-          acc += word_terms(v.x, at) + word_terms(v.y, at + 4) + word_terms(v.z, at + 8) + word_terms(v.w, at + 12);
-        }
-      } else {
-        for (uint32_t i = lane; i < lay.head_bytes; i += 32) acc += term(at0 + i, p[i]);
-      }
+      acc += part_sum(base + off, lay.head_bytes, row_id * row_words, sub_lane, lanes_per_row);
     }
   }
   for (int d = 16; d > 0; d >>= 1) acc += __shfl_down_sync(0xFFFFFFFFu, acc, d);
@@ -162,6 +174,7 @@ extern "C" int kvt_launch_checksum(const uint64_t* d_bases, uint32_t n_bases, ui
 extern "C" uint64_t kvt_checksum_host(const void* data, uint64_t len, uint32_t index0) {
   const uint8_t* p = static_cast<const uint8_t*>(data);
   uint64_t acc = 0;
-  for (uint64_t i = 0; i < len; ++i) acc += term(index0 + (uint32_t)i, p[i]);
+  const uint64_t n_words = (len + 3u) >> 2;
+  for (uint64_t k = 0; k < n_words; ++k) acc += term(index0 + (uint32_t)k, word_at(p, len, k));
   return acc;
 }

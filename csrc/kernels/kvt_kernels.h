@@ -378,12 +378,13 @@ int kvt_launch_complete(uint32_t* status, KvtCompletion* record, uint64_t seq, v
 int kvt_launch_stamp(uint64_t* slot, void* stream);
 
 // ---- end-to-end transfer check -------------------------------------------------------------
-// Position-keyed 64-bit checksum of byte ranges of one tensor (kvt_checksum.cu): each byte adds
-// mix32(((i & 0xFFFFFF) << 8) | byte), i = its index in its piece.  Chunks are pieces cut to <= 64 KiB;
-// index0 is the index of the chunk's first byte in its piece.  One launch sums the same chunks over n_bases tensors of
-// one shape (the layers of a cache): d_bases is a device array of their addresses and d_out[i] receives tensor i's
-// sum.  The kernel ADDS to d_out (zero it first), skips a chunk outside [0, capacity) and reports it in d_status
-// {KVT_ERR_BLOCK_RANGE, chunk number}.  grid_ctas is the total over all tensors.
+// Position-keyed 64-bit checksum of byte ranges of one tensor (kvt_checksum.cu): a piece is read as little-endian
+// 32-bit words (the last padded with zero bytes) and word k with value w adds term(k, w), a 32-bit mix of both.
+// Chunks are pieces cut to <= 64 KiB; index0 is the index of the chunk's first word in its piece.  One launch sums
+// the same chunks over n_bases tensors of one shape (the layers of a cache): d_bases is a device array of their
+// addresses and d_out[i] receives tensor i's sum.  The kernel ADDS to d_out (zero it first), skips a chunk outside
+// [0, capacity) and reports it in d_status {KVT_ERR_BLOCK_RANGE, chunk number}.  grid_ctas is the total over all
+// tensors.
 typedef struct {
   uint64_t off;
   uint32_t len;
@@ -396,8 +397,8 @@ uint64_t kvt_checksum_host(const void* data, uint64_t len, uint32_t index0);
 // The same sum over the rows of an attention cache: for every request, token t in [seen, seen + new_tokens), K / V
 // and head j in [0, n_heads), the head_bytes at
 //   table[t / ntpb] * block_stride + kv * kv_stride + (t % ntpb) * token_stride + (head0 + j) * head_stride
-// with the byte at position b of the row keyed by index
-//   ((((index * 131 + t) * kv_count + kv) * n_heads + j) * head_bytes + b)        (32-bit arithmetic),
+// with word k of the row keyed by index
+//   ((((index * 131 + t) * kv_count + kv) * n_heads + j) * ceil(head_bytes / 4) + k)        (32-bit arithmetic),
 // which names the row by coordinates that do not depend on the layout.  `first` is the exclusive prefix sum of
 // new_tokens over the requests; tables are [blk_off, blk_off + n_blocks) of the pool.
 typedef struct {

@@ -83,14 +83,15 @@ uint64_t checksum_device(Context* ctx, uint32_t lb, uint32_t le, const std::vect
   const int dev = ctx->device_id();
   const auto& addrs = ctx->layer_data_address();
   const size_t n_tensors = per_tensor.size();
-  // pieces cut to chunks; index0 restarts at every piece
+  // pieces cut to chunks of a whole number of words; index0 (in words) restarts at every piece
+  static_assert(KVT_CHECK_CHUNK % 4 == 0, "a chunk boundary must be a word boundary of its piece");
   std::vector<KvtCheckChunk> host;
   std::vector<size_t> first(n_tensors + 1, 0);
   for (size_t t = 0; t < n_tensors; ++t) {
     for (const CheckRange& r : per_tensor[t]) {
       for (uint64_t done = 0; done < r.len; done += KVT_CHECK_CHUNK) {
         const uint64_t n = std::min<uint64_t>(KVT_CHECK_CHUNK, r.len - done);
-        host.push_back(KvtCheckChunk{r.off + done, static_cast<uint32_t>(n), static_cast<uint32_t>(done)});
+        host.push_back(KvtCheckChunk{r.off + done, static_cast<uint32_t>(n), static_cast<uint32_t>(done >> 2)});
       }
     }
     first[t + 1] = host.size();

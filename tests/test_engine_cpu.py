@@ -623,16 +623,20 @@ def test_relayed_transfer_is_refused_by_host_transports(ops, sink):
 
 
 # ---- end-to-end transfer check ------------------------------------------------------------------
-def _mix32(x):
-    x = (x * 0x9E3779B1) & 0xFFFFFFFF
+def _term(k, w):
+    key = (k * 0x85EBCA77) & 0xFFFFFFFF
+    x = ((w * 0x9E3779B1) & 0xFFFFFFFF) ^ (((key << 13) | (key >> 19)) & 0xFFFFFFFF)
     x ^= x >> 15
-    x = (x * 0x85EBCA77) & 0xFFFFFFFF
+    x = (x * 0xC2B2AE3D) & 0xFFFFFFFF
     x ^= x >> 13
     return x
 
 
 def _piece_sum(data: bytes, index0=0):
-    return sum(_mix32((((index0 + i) & 0xFFFFFF) << 8) | b) for i, b in enumerate(data)) & 0xFFFFFFFFFFFFFFFF
+    """A piece as little-endian 32-bit words, the last padded with zero bytes; word k adds term(index0 + k, word)."""
+    padded = data + b"\0" * (-len(data) % 4)
+    words = struct.unpack(f"<{len(padded) // 4}I", padded)
+    return sum(_term((index0 + k) & 0xFFFFFFFF, w) for k, w in enumerate(words)) & 0xFFFFFFFFFFFFFFFF
 
 
 def _rotl64(v, r):
@@ -644,10 +648,11 @@ def test_checksum_function_matches_its_definition(ops):
     rng = random.Random(3)
     data = bytes(rng.randrange(256) for _ in range(1000))
     assert ops.kvt_checksum_host(data) == _piece_sum(data)
-    assert ops.kvt_checksum_host(data[100:], 100) == _piece_sum(data[100:], 100)
-    # a piece cut into chunks that carry their starting index sums to the whole piece
-    cuts = [0, 17, 256, 640, 1000]
-    assert sum(ops.kvt_checksum_host(data[a:b], a) for a, b in zip(cuts, cuts[1:])) & 0xFFFFFFFFFFFFFFFF == _piece_sum(data)
+    assert ops.kvt_checksum_host(data[100:], 25) == _piece_sum(data[100:], 25)
+    assert ops.kvt_checksum_host(data[:997]) == _piece_sum(data[:997])            # a ragged tail is one padded word
+    # a piece cut at word boundaries into chunks that carry their starting word index sums to the whole piece
+    cuts = [0, 16, 256, 640, 1000]
+    assert sum(ops.kvt_checksum_host(data[a:b], a // 4) for a, b in zip(cuts, cuts[1:])) & 0xFFFFFFFFFFFFFFFF == _piece_sum(data)
     # the value depends on where a byte sits in its piece, not only on the multiset of bytes
     swapped = bytearray(data)
     swapped[3], swapped[4] = swapped[4], swapped[3]

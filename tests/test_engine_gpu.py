@@ -359,17 +359,17 @@ def test_a_completion_record_that_never_arrives_fails_the_request_within_its_dea
 
 # ---- end-to-end transfer check ------------------------------------------------------------------
 def test_checksum_kernel_matches_the_host_function(ops):
-    """Chunks of every alignment class (16-byte vector path, byte path, odd offsets and lengths, a chunk
-    that continues a piece at a non-zero index) against the CPU function; a chunk outside the tensor is
-    skipped and reported."""
+    """Chunks of every alignment class (16-byte vector path, word path, words assembled from bytes at odd
+    offsets, ragged tails, a chunk that continues a piece at a non-zero index, an index that wraps) against the
+    CPU function; a chunk outside the tensor is skipped and reported."""
     import numpy as np
 
     g = torch.Generator(device=DEV).manual_seed(11)
     cap = 1 << 20
     buf = torch.randint(0, 256, (cap,), dtype=torch.uint8, device=DEV, generator=g)
     host = buf.cpu().numpy()
-    chunks = [(0, 65536, 0), (65536, 65536, 65536), (131072 + 16, 4096, 0), (200001, 777, 5), (300000, 1, 0),
-              (400000, 65535, 123456), (cap - 48, 48, 0x1FFFFF0)]
+    chunks = [(0, 65536, 0), (65536, 65536, 16384), (131072 + 16, 4096, 0), (200001, 777, 5), (300000, 1, 0), (300004, 6, 9),
+              (400000, 65535, 123456), (cap - 48, 48, 0xFFFFFFF8)]        # offset, length, index of the first word
     arr = np.zeros(len(chunks), dtype=[("off", "<u8"), ("len", "<u4"), ("idx", "<u4")])
     for i, c in enumerate(chunks):
         arr[i] = c
@@ -497,7 +497,7 @@ def _rows_oracle(ops, lay, flat, head0, n_heads, reqs):
             for kv in range(lay.kv_count):
                 for j in range(n_heads):
                     row_id = (((index * 131 + t) * lay.kv_count + kv) * n_heads + j) & 0xFFFFFFFF
-                    total += ops.kvt_checksum_host(v[blk, kv, slot, head0 + j].copy(), (row_id * lay.head_bytes) & 0xFFFFFFFF)
+                    total += ops.kvt_checksum_host(v[blk, kv, slot, head0 + j].copy(), (row_id * ((lay.head_bytes + 3) // 4)) & 0xFFFFFFFF)
     return total & 0xFFFFFFFFFFFFFFFF
 
 
@@ -520,12 +520,13 @@ def _rows_kernel(ops, lay, flat, head0, n_heads, reqs, grid=0):
     return int(out[0].item()) & 0xFFFFFFFFFFFFFFFF, int(out[1].item())
 
 
-def test_row_checksum_is_the_same_on_both_sides_of_a_layout_change(ops):
+@pytest.mark.parametrize("head_dim", [64, 256])       # rows of 128 bytes (half a warp each) and of 512 bytes (a warp each)
+def test_row_checksum_is_the_same_on_both_sides_of_a_layout_change(ops, head_dim):
     """NHD pages with 8 heads against HND pages with 4 heads that received heads 4..7: the kernel's sums
     over the two layouts agree with each other and with the spelled-out oracle; one flipped bit in a moved row,
     or two rows exchanged, changes the destination's sum."""
-    src_l = AttnLayout(CacheShape.FLASH, 24, 16, 8, 64, 2)
-    dst_l = AttnLayout(CacheShape.FLASHINFER, 30, 32, 4, 64, 2)
+    src_l = AttnLayout(CacheShape.FLASH, 24, 16, 8, head_dim, 2)
+    dst_l = AttnLayout(CacheShape.FLASHINFER, 30, 32, 4, head_dim, 2)
     src = src_l.alloc(DEV, "normal", seed=3)
     dst = dst_l.alloc(DEV)
     moves = [([3, 9, 1], [7, 2], 5, 40), ([5, 6], [11], 0, 21), ([20], [21], 0, 16)]     # src blocks, dst blocks, seen, new
