@@ -422,3 +422,59 @@ def test_prefill_worker_hands_replicated_requests_to_one_decode_worker():
         assert relays == {0, 1, 2, 3}                                                   # the group shares the work
     finally:
         p.shutdown()
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_random_arrivals_aborts_and_transport_faults_leak_nothing(pd, seed):
+    """Requests arrive in bursts with random prompt lengths; some are aborted on the decode side at a random
+    moment (before the prefill engine has them, while their KV is moving, or while they decode), and a few
+    transfers hit an injected transport fault.  Whatever the interleaving: every request ends (LENGTH or
+    ABORT), one that was neither aborted nor hit by a fault decodes its tokens, both engines get every block
+    back and neither connector keeps a request."""
+    import random
+
+    from llumnix_kv_b200 import load_ops
+
+    ops = load_ops()
+    rng = random.Random(seed)
+    p, d = pd
+    params = {"remote_host": "127.0.0.1", "remote_port": p.proxy.rpc_port()}
+    reqs, aborted = [], set()
+    faults = 0
+    try:
+        for burst in range(4):
+            batch = [make_req(f"s{seed}.{burst}.{i}", rng.randint(5, 90), max_tokens=rng.randint(1, 4), seed=seed * 100 + burst * 10 + i,
+                              params=params) for i in range(rng.randint(2, 5))]
+            if rng.random() < 0.5:
+                ops.fault_inject_arm(rng.randint(1, 3))      # one of the next few fault points throws
+                faults += 1
+            for r in batch:
+                d.add_request(r)
+                reqs.append(r)
+                if rng.random() < 0.3:
+                    time.sleep(rng.choice([0.0, 0.002, 0.02, 0.1]))
+                    d.abort_requests([r.request_id])
+                    aborted.add(r.request_id)
+            time.sleep(rng.choice([0.0, 0.05, 0.2]))
+        ops.fault_inject_arm(0)
+        ended = {}
+        for r in reqs:
+            out = d.wait_finished(r.request_id, 60)
+            assert out is not None, r.request_id
+            ended[r.request_id] = out.finish_reason.name
+        assert set(ended.values()) <= {"LENGTH", "ABORT"}, ended
+        clean = [rid for rid, how in ended.items() if how == "LENGTH"]
+        # one fault fails the whole batch it hits: up to a burst of five requests
+        assert len(clean) >= len(reqs) - len(aborted) - 6 * faults, (ended, aborted, faults)
+        for r in reqs:
+            if ended[r.request_id] == "LENGTH":
+                assert len(d.output_tokens(r.request_id)) == r.sampling_params.max_tokens, r.request_id
+        deadline = time.time() + 15
+        pools = [e.scheduler.kv_cache_manager.block_pool for e in (p, d)]
+        while time.time() < deadline and (any(pl.num_free_blocks() != 63 for pl in pools) or p.connector._sched._saving
+                                          or d.connector._sched._loading):
+            time.sleep(0.01)
+        assert [pl.num_free_blocks() for pl in pools] == [63, 63]
+        assert not p.connector._sched._saving and not d.connector._sched._loading
+    finally:
+        ops.fault_inject_arm(0)
