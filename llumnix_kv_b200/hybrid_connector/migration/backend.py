@@ -34,7 +34,7 @@ from ..engine_proxy import (EngineCoreRequest, KVCacheBlocks, KVConnectorRole, R
                             SchedulerOutput, VllmConfig, core_get_param, core_update_params, get_param, set_param)
 from ..kvtbackend import (CODE_MIGRATE_REJECTED_BUSY, CODE_OK, CODE_REQNOTFOUND, TRANSFER_KV_RESP, KVTDInfo, KVTResp,
                           RKVTDInfo, get_inst_id)
-from ..utils import ConnManager, ConnPool, IoRet, kill_me_if_exception, spawn_task
+from ..utils import ConnManager, ConnPool, DeclinedError, IoRet, kill_me_if_exception, spawn_task
 from . import (ABORT_REQS_REQ, ABORT_REQS_RESP, KVT_SUSPEND_REQ, MIGRATE_TO_REQ, MIGRATE_TO_RESP, NEW_OUTPUT_REQ,
                NEW_OUTPUT_RESP, NEW_REQ_REQ, NEW_REQ_RESP, OUTPUT_TOKENS_N, SRC_INFO, SUSPEND_EVT, SUSPEND_REQ,
                SUSPEND_RESP, EngineCoreOutputs, MigrateResp, SuspendReq, SuspendResp, WireOutput, int2ipport,
@@ -86,6 +86,7 @@ class MigrationBackend(HybridBackend):
         self._mig_lock = threading.Lock()
         self._mig_in: dict[str, int] = {}                # reqid -> tokens it will occupy
         self._mig_out: set = set()
+        self._arriving: set = set()                      # accepted over RPC, not yet seen by the core thread
         total_tokens = vllm_config.cache_config.num_gpu_blocks * vllm_config.cache_config.block_size
         ratio = float(vllm_config.kv_transfer_config.get_from_extra_config("max_block_ratio_mig_in", 1.0))
         self.max_migrate_in_tokens = min(envs.LLUMNIX_MAX_TOKEN_MIG_IN, int(total_tokens * ratio))
@@ -97,7 +98,9 @@ class MigrationBackend(HybridBackend):
             logger.info("suspend: already finished. reqid=%s", susreq.reqid)
             return SuspendResp(code=CODE_REQNOTFOUND)
         if get_param(req, SUSPEND_EVT) is not None:
-            raise RuntimeError(f"suspend requested twice for {susreq.reqid}")
+            # someone else is already taking this request over: the second asker is told so and keeps its hands off
+            logger.warning("suspend: already being suspended. reqid=%s", susreq.reqid)
+            return SuspendResp(code=CODE_MIGRATE_REJECTED_BUSY)
         evt = asyncio.Event()
         set_param(req, SUSPEND_EVT, evt)
         self._mig_out.add(susreq.reqid)
@@ -149,12 +152,22 @@ class MigrationBackend(HybridBackend):
             writer.write(pack_msg(MIGRATE_TO_RESP, MigrateResp(code=CODE_MIGRATE_REJECTED_BUSY)))
             await writer.drain()
             return
+        with self._mig_lock:
+            known = req.request_id in self._mig_in or req.request_id in self._arriving
+        if known or req.request_id in self._reqstate:
+            # the request was here a moment ago (it is still being let go, or its end has not been booked yet) or is
+            # already on its way in: taking it now would run two lives of one id side by side
+            logger.warning("migrate_to rejected, the request is still known here: reqid=%s", req.request_id)
+            writer.write(pack_msg(MIGRATE_TO_RESP, MigrateResp(code=CODE_MIGRATE_REJECTED_BUSY)))
+            await writer.drain()
+            return
         srcinfo = core_get_param(req, SRC_INFO)
         assert srcinfo is not None, "MIGRATE_TO without the source engine's address"
         core_update_params(req, {SRC_INFO: tuple(srcinfo), PREALLOC_KEY: prealloc,
                                  "migration_start_time": time.monotonic()})
         with self._mig_lock:
             self._mig_in[req.request_id] = len(req.prompt_token_ids) + prealloc
+            self._arriving.add(req.request_id)
         writer.write(pack_msg(MIGRATE_TO_RESP, MigrateResp(code=CODE_OK)))
         self._engine.core_add_req(req)
         logger.info("migrate in. reqid=%s prealloc=%s src=%s", req.request_id, prealloc, srcinfo)
@@ -170,6 +183,8 @@ class MigrationBackend(HybridBackend):
     async def _on_new_req(self, reader, writer):
         req: EngineCoreRequest = self._reqdec.decode(await read_body(reader))
         writer.write(struct.pack("=I", NEW_REQ_RESP))
+        with self._mig_lock:
+            self._arriving.add(req.request_id)     # known from now on, although the core thread has yet to book it
         self._engine.core_add_req(req)
         await writer.drain()
 
@@ -215,8 +230,11 @@ class MigrationBackend(HybridBackend):
                                         TRANSFER_KV_RESP, self._kvtrespdec)
         logger.info("migrate end kvt: dur_ms=%.2f reqid=%s cached=%s max=%s resp=%s", (time.monotonic() - t0) * 1000,
                     req.request_id, req.num_computed_tokens, alltokens, resp)
-        if resp.code != CODE_OK or resp.output_token_ids is None or \
-                not (req.num_computed_tokens <= resp.cached <= alltokens):
+        if resp.code != CODE_OK:
+            # the source kept the request (it does not know it yet or any more, it is busy letting it go to someone
+            # else, or its transfer failed before it let go): nothing changed hands
+            raise DeclinedError(f"migration declined by the source: {resp}")
+        if resp.output_token_ids is None or not (req.num_computed_tokens <= resp.cached <= alltokens):
             raise RuntimeError(f"migration kvt rpc failed: {resp}")
         return resp
 
@@ -224,6 +242,8 @@ class MigrationBackend(HybridBackend):
     def get_operations(self, req: Request) -> OperationPlan:
         assert req.request_id not in self._reqstate
         self._reqstate[req.request_id] = req
+        with self._mig_lock:
+            self._arriving.discard(req.request_id)
         load = int(get_param(req, SRC_INFO) is not None)
         return load, 0, (self.source_label(),) if load else (), ()
 

@@ -126,6 +126,8 @@ class MigrationCli:
                 continue
             first = not st.tokens and bool(o.new_token_ids)
             st.tokens.extend(o.new_token_ids)
+            if (src[0], src[1]) in self.engines:
+                st.engine = (src[0], src[1])       # where it really runs: an accepted migration may yet be declined by the source
             if o.finish_reason is not None:
                 st.finish_reason = o.finish_reason
                 st.done.set()

@@ -446,7 +446,10 @@ class HybridScheduler:
             self._engine.sched_add_req(req)
             self._add_ts(req, "done")
             if load_failed:
-                self.on_abort_req(AbortReq(req.request_id, output=not req_aborted(req), reason="load fail"), iscore=True)
+                # a load that the other side declined leaves the request alive where it was: no word to the client
+                declined = getattr(ioret.ex, "silent", False)
+                self.on_abort_req(AbortReq(req.request_id, output=not req_aborted(req) and not declined, reason="load fail"),
+                                  iscore=True)
 
     def on_add_req(self, req: Request) -> bool:
         load_count, save_count, load_sources, save_sources = self._backend.get_operations(req)

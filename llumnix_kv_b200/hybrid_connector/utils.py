@@ -455,6 +455,14 @@ def try_advance(state_dict: dict, ioret: IoRet, worker_tprank: int, tpsize: int,
         return state if state.full_ranks() >= tpsize else None
 
 
+class DeclinedError(RuntimeError):
+    """A load that the other side declined before anything changed hands: the request still lives (or has
+    ended) where it was, so the copy that asked for it goes away without a word to the client.  The scheduler
+    reads ``silent`` off a failed load's exception."""
+
+    silent = True
+
+
 class CodeError(Exception):
     def __init__(self, code: int, msg: str):
         super().__init__(f"{code}: {msg}")

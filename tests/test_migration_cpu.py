@@ -128,3 +128,55 @@ def test_abort_through_the_frontend(two):
         assert wait_free(a, 63) == 63
     finally:
         cli.close()
+
+
+@pytest.mark.parametrize("seed", [1, 2])
+def test_random_migrations_keep_every_stream_intact(two, seed):
+    """Several requests decode on two engines while the frontend keeps asking, at random moments, to move a
+    random one of them to the other engine (some asks come too early, some too late, some are refused).
+    Whatever happened to a request on the way, its token stream is the one a single engine produces, every
+    block returns to its pool and no engine remembers a migration."""
+    import random
+
+    rng = random.Random(seed)
+    a, b = two
+    for e in (a, b):
+        step = e.step
+        e.step = (lambda s: lambda: (time.sleep(0.004), s())[1])(step)       # slow decoding: migrations land mid-stream
+    cli = MigrationCli([addr(a), addr(b)])
+    shapes = [(rng.randint(10, 70), rng.randint(15, 40)) for _ in range(6)]
+    try:
+        # the reference streams, from one engine, before anything migrates
+        ref = MiniEngineCore(make_cfg("kv_both", "base", backend="kvt+migration"))
+        try:
+            for i, (n, m) in enumerate(shapes):
+                ref.add_request(make_req(f"b{i}", n, max_tokens=m, seed=seed * 50 + i, params=LOCAL))
+            want = []
+            for i in range(len(shapes)):
+                assert ref.wait_finished(f"b{i}", 60) is not None
+                want.append(ref.output_tokens(f"b{i}"))
+        finally:
+            ref.shutdown()
+        for i, (n, m) in enumerate(shapes):
+            cli.add_request(make_req(f"q{i}", n, max_tokens=m, seed=seed * 50 + i, params=LOCAL))
+        codes = []
+        end = time.time() + 1.5
+        while time.time() < end:
+            i = rng.randrange(len(shapes))
+            st = cli._reqs[f"q{i}"]
+            other = addr(b) if st.engine == addr(a) else addr(a)
+            codes.append(cli.migrate(f"q{i}", other))
+            time.sleep(rng.choice([0.0, 0.01, 0.05]))
+        moved = 0
+        for i in range(len(shapes)):
+            st = cli.wait(f"q{i}", 90)
+            assert st is not None and st.finish_reason == 1, (i, codes)
+            assert st.tokens == want[i], (i, st.migrations, codes)
+            moved += st.migrations
+        assert moved >= 1, codes                                  # the test did migrate something
+        assert wait_free(a, 63, 15) == 63 and wait_free(b, 63, 15) == 63
+        for e in (a, b):
+            assert not e.connector._sched._saving and not e.connector._sched._loading
+            assert e.connector._sched._backend.migration_status() == {"migrate_in": {}, "migrate_out": []}
+    finally:
+        cli.close()
