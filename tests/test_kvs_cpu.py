@@ -250,3 +250,57 @@ def test_trace_context_reaches_the_store_operations(store_name):
         assert "c" in [c for c in e.workers[0].connector._worker._backend.request_contexts if c.startswith("c")]
     finally:
         e.shutdown()
+
+
+@pytest.mark.parametrize("seed", [1, 2])
+def test_random_requests_and_aborts_on_two_engines_sharing_a_store(store_name, seed):
+    """Two engines of a node share one store that is too small for everything; requests over a handful of prompts
+    (so prefixes are shared, saved by one engine and loaded by the other) arrive at random and some are aborted
+    while they load, prefill or save.  Every request that was not aborted produces the tokens its prompt always
+    produces, both engines get every block back, and the store keeps nothing reserved or pinned."""
+    import random
+
+    rng = random.Random(seed)
+    kw = dict(num_blocks=128, max_batched=64, extra={"kvs_slots": 24, "kvs_abort_grace_s": 0.05})
+    a, b = make_kvs("A", store_name, **kw), make_kvs("B", store_name, **kw)
+    try:
+        lens = [40, 75, 130, 200, 260]
+        want = {}
+        for k, n in enumerate(lens):                              # what each prompt decodes to, before the store holds anything
+            run(a, f"ref{k}", n, max_tokens=3, seed=k, params={"kvs_nosave": True})
+            want[k] = a.output_tokens(f"ref{k}")
+        issued, aborted = [], set()
+        for i in range(40):
+            k = rng.randrange(len(lens))
+            e = rng.choice((a, b))
+            rid = f"s{seed}.{i}"
+            e.add_request(make_req(rid, lens[k], max_tokens=3, seed=k))
+            issued.append((rid, k, e))
+            if rng.random() < 0.25:
+                time.sleep(rng.choice([0.0, 0.003, 0.02, 0.08]))
+                e.abort_requests([rid])
+                aborted.add(rid)
+            if rng.random() < 0.3:
+                time.sleep(rng.choice([0.01, 0.05]))
+        done = 0
+        for rid, k, e in issued:
+            out = e.wait_finished(rid, 60)
+            assert out is not None, rid
+            if out.finish_reason.name == "LENGTH":
+                assert e.output_tokens(rid) == want[k], rid
+                done += 1
+            else:
+                assert out.finish_reason.name == "ABORT" and rid in aborted, (rid, out.finish_reason.name)
+        assert done >= len(issued) - len(aborted)
+        for e in (a, b):
+            assert wait_free(e, 127, 15) == 127
+            assert not e.connector._sched._saving and not e.connector._sched._loading
+        deadline = time.time() + 10
+        store = a.workers[0].connector._worker._backend._store
+        while time.time() < deadline and (store.stats()["writing"] or store.stats()["pinned"]):
+            time.sleep(0.02)
+        st = store.stats()
+        assert st["writing"] == 0 and st["pinned"] == 0 and st["sealed"] <= 24, st
+    finally:
+        a.shutdown()
+        b.shutdown()
