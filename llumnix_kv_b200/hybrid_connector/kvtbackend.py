@@ -416,6 +416,7 @@ class PBackend(HybridBackend):
         self._enc = msgspec.msgpack.Encoder()
         self._kvtreqdec = msgspec.msgpack.Decoder(RKVTDInfo)
         self._dual_req_done: "OrderedDict[str, DualReq]" = OrderedDict()
+        self._dual_timer_armed = False     # a wake-up is scheduled for the oldest finished prefill half
         self._infly_kvt: dict[str, PReqMeta] = {}
         self._dinfoq: deque = deque()
         self._gone_reqs: "OrderedDict[str, float]" = OrderedDict()
@@ -690,8 +691,19 @@ class PBackend(HybridBackend):
             if not dual.finished:
                 continue
             if dual.insert_ts + timeout_s > now:
+                # Its time is checked where the engine steps; an idle engine does not step.  One timer wakes the
+                # scheduler when the oldest parked half is due, so its blocks come back on time either way.
+                if not self._dual_timer_armed:
+                    self._dual_timer_armed = True
+                    delay = dual.insert_ts + timeout_s - now + 0.05
+                    loop = self._loop()
+                    loop.call_soon_threadsafe(lambda: loop.call_later(delay, self._dual_timer_fired))
                 break
             self._engine.core_abort_req(reqid, "dual_req_done.timeout", True)
+
+    def _dual_timer_fired(self) -> None:     # backend loop
+        self._dual_timer_armed = False
+        self._connector.wakeup_scheduler()
 
     def _plan_chunk(self, req: Request, reqid: str, seen: int, end: int, p_block_ids: Optional[list], ret: list,
                     substep_mode: bool) -> None:

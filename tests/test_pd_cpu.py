@@ -478,3 +478,70 @@ def test_random_arrivals_aborts_and_transport_faults_leak_nothing(pd, seed):
         assert not p.connector._sched._saving and not d.connector._sched._loading
     finally:
         ops.fault_inject_arm(0)
+
+
+@pytest.mark.parametrize("ptp,dtp,seed", [(1, 1, 1), (2, 1, 2), (1, 2, 3)])
+def test_random_dual_requests_with_aborts_on_either_side(ptp, dtp, seed):
+    """Dual-request mode under a careless frontend: the two halves of a request reach the prefill and the
+    decode engine in either order and at random distances, prompts are longer than the prefill engine's token
+    budget (chunked prefill, deltas), the engines may be tensor-parallel with different sizes, and some
+    requests are aborted on the prefill side, on the decode side or on both, at random moments.  Every
+    decode-side request ends; one that nobody aborted decodes; both engines get every block back and neither
+    connector keeps a request."""
+    import random
+
+    rng = random.Random(seed)
+    # a prefill half whose decode half never comes (aborted before it got in touch) is given up after this long
+    import os
+    before = os.environ.get("VLLM_PD_TRY_CONNECT_TIMEOUT_SECONDS")
+    os.environ["VLLM_PD_TRY_CONNECT_TIMEOUT_SECONDS"] = "1.5"
+    p, d = make_pd(p_kw={"tp": ptp, "max_batched": 48}, d_kw={"tp": dtp})
+    try:
+        reqs, touched = [], set()
+        for i in range(14):
+            rid = f"u{seed}.{i}"
+            n = rng.randint(8, 140)
+            preq = make_req(rid, n, max_tokens=1, seed=i, params={"do_remote_decode": True})
+            dreq = make_req(rid, n, max_tokens=rng.randint(1, 3), seed=i, params=_dual_params(p))
+            first, second = ((p, preq), (d, dreq)) if rng.random() < 0.5 else ((d, dreq), (p, preq))
+            first[0].add_request(first[1])
+            time.sleep(rng.choice([0.0, 0.0, 0.01, 0.06]))
+            second[0].add_request(second[1])
+            reqs.append(dreq)
+            roll = rng.random()
+            if roll < 0.35:
+                time.sleep(rng.choice([0.0, 0.005, 0.03, 0.1]))
+                if roll < 0.15:
+                    p.abort_requests([rid])
+                elif roll < 0.3:
+                    d.abort_requests([rid])
+                else:
+                    d.abort_requests([rid])
+                    p.abort_requests([rid])
+                touched.add(rid)
+        for r in reqs:
+            out = d.wait_finished(r.request_id, 60)
+            assert out is not None, r.request_id
+            how = out.finish_reason.name
+            assert how in ("LENGTH", "ABORT"), (r.request_id, how)
+            if r.request_id not in touched:
+                assert how == "LENGTH", r.request_id
+                assert len(d.output_tokens(r.request_id)) == r.sampling_params.max_tokens
+        deadline = time.time() + 20
+        pools = [e.scheduler.kv_cache_manager.block_pool for e in (p, d)]
+        while time.time() < deadline and (any(pl.num_free_blocks() != 63 for pl in pools) or p.connector._sched._saving
+                                          or d.connector._sched._loading):
+            time.sleep(0.01)
+        left = {"free": [pl.num_free_blocks() for pl in pools], "p_saving": list(p.connector._sched._saving),
+                "d_loading": list(d.connector._sched._loading), "p_running": [r.request_id for r in p.scheduler.running],
+                "p_waiting": [r.request_id for r in p.scheduler.waiting], "d_running": [r.request_id for r in d.scheduler.running],
+                "touched": sorted(touched)}
+        assert left["free"] == [63, 63], left
+        assert not p.connector._sched._saving and not d.connector._sched._loading
+    finally:
+        d.shutdown()
+        p.shutdown()
+        if before is None:
+            os.environ.pop("VLLM_PD_TRY_CONNECT_TIMEOUT_SECONDS", None)
+        else:
+            os.environ["VLLM_PD_TRY_CONNECT_TIMEOUT_SECONDS"] = before
