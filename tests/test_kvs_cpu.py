@@ -252,22 +252,22 @@ def test_trace_context_reaches_the_store_operations(store_name):
         e.shutdown()
 
 
-@pytest.mark.parametrize("seed", [1, 2])
-def test_random_requests_and_aborts_on_two_engines_sharing_a_store(store_name, seed):
-    """Two engines of a node share one store that is too small for everything; requests over a handful of prompts
+@pytest.mark.parametrize("backend,seed", [("kvs", 1), ("kvs", 2), ("mooncake", 3), ("v6d_object", 4)])
+def test_random_requests_and_aborts_on_two_engines_sharing_a_store(store_name, seed, backend):
+    """Two engines of a node share one store (any flavour) that is too small for everything; requests over a handful of prompts
     (so prefixes are shared, saved by one engine and loaded by the other) arrive at random and some are aborted
     while they load, prefill or save.  Every request that was not aborted produces the tokens its prompt always
     produces, both engines get every block back, and the store keeps nothing reserved or pinned."""
     import random
 
     rng = random.Random(seed)
-    kw = dict(num_blocks=128, max_batched=64, extra={"kvs_slots": 24, "kvs_abort_grace_s": 0.05})
-    a, b = make_kvs("A", store_name, **kw), make_kvs("B", store_name, **kw)
+    extra = {"kvs_name": store_name, "kvs_slots": 24, "kvs_abort_grace_s": 0.05}
+    a, b = (MiniEngineCore(make_cfg("kv_both", n, backend=backend, num_blocks=128, max_batched=64, extra=dict(extra))) for n in "AB")
     try:
         lens = [40, 75, 130, 200, 260]
         want = {}
-        for k, n in enumerate(lens):                              # what each prompt decodes to, before the store holds anything
-            run(a, f"ref{k}", n, max_tokens=3, seed=k, params={"kvs_nosave": True})
+        for k, n in enumerate(lens):                              # what each prompt decodes to
+            run(a, f"ref{k}", n, max_tokens=3, seed=k)
             want[k] = a.output_tokens(f"ref{k}")
         issued, aborted = [], set()
         for i in range(40):
