@@ -220,6 +220,16 @@ class HybridBackend:
     async def async_cleanup(self, req: Request) -> None:
         return
 
+    # core thread
+    def on_queued_req_aborted(self, req: Request) -> None:
+        """The scheduler dropped a request that was still queued in the connector: no block was allocated, no load
+        or save was set up, so none of the abort paths that go through those will ever run for it.  A backend that
+        holds something on the request's behalf from before (a peer waiting for an answer) settles it here.
+        Composites pass the call on to their parts."""
+        for part in vars(self).values():
+            if isinstance(part, HybridBackend):
+                part.on_queued_req_aborted(req)
+
     # core thread.  (load_count, save_count, load_sources, save_sources)
     def get_operations(self, req: Request) -> OperationPlan:
         return 0, 0, (), ()

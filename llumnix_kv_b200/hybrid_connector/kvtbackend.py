@@ -680,6 +680,13 @@ class PBackend(HybridBackend):
                 self._loop().call_soon_threadsafe(self._mark_send_done, IoRet(reqid=areq.request_id, ex=err))
             self._connector.mark_backend_save_done(areq, source=self.source_label())
 
+    def on_queued_req_aborted(self, req: Request) -> None:
+        # a decode engine that pushed this request here is waiting for its answer: nothing will ever be sent
+        if req.request_id in self._sending:
+            self._mark_gone(req.request_id, "abort_queued")
+            err = CodeError(CODE_REQGONE, "aborted before it was scheduled")
+            self._loop().call_soon_threadsafe(self._mark_send_done, IoRet(reqid=req.request_id, ex=err))
+
     def _step_stop0(self, sout: HCSchedOutput) -> None:
         for req in sout.hc_stop0:
             assert get_param(req, P_KVT_STATE) is None and req.request_id not in self._dual_req_done

@@ -486,6 +486,7 @@ class HybridScheduler:
         req = self._waiting[pos][0]
         del self._waiting[pos]
         logger.info("abort of a queued request: %s", areq)
+        self._backend.on_queued_req_aborted(req)
         # the engine frees what it knows: hand the request over and finish it at once
         self._engine.sched_add_req(req)
         self._engine.sched_finish_req(areq.reqid)

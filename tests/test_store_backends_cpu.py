@@ -94,3 +94,90 @@ def test_kvs_plus_kvt_prefill_engine():
         d.shutdown()
         p.shutdown()
         load_ops().KvStore.unlink(name)
+
+
+def _find_store(backend, depth=0):
+    """The store object behind a (possibly composite) worker backend."""
+    st = getattr(backend, "_store", None)
+    if st is not None and hasattr(st, "stats"):
+        return st
+    if depth < 3:
+        for v in vars(backend).values():
+            if hasattr(v, "__dict__") and type(v).__module__.startswith("llumnix_kv_b200.hybrid_connector"):
+                found = _find_store(v, depth + 1)
+                if found is not None:
+                    return found
+    return None
+
+
+@pytest.mark.parametrize("backend,seed", [("kvt+kvs", 1), ("v6d_object+kvt", 2), ("file+kvt", 3)])
+def test_random_requests_and_aborts_through_a_prefill_engine_that_also_stores(backend, seed, tmp_path):
+    """A prefill engine that sends every prompt to the decode engine AND keeps it (shared store, object store
+    flavour, or files): each request has two save sources on it, repeated prompts are served from what was kept,
+    some requests are aborted on the decode side at random moments, a few transfers hit an injected fault.
+    Every request ends, an untouched one decodes what its prompt always decodes, both engines get every block
+    back and nothing stays reserved in the store."""
+    import random
+
+    from llumnix_kv_b200 import load_ops as _ops
+
+    ops = _ops()
+    rng = random.Random(seed)
+    name = f"kvx_cmp_{os.getpid()}_{seed}"
+    if backend == "file+kvt":
+        p_cfg = make_cfg("kv_both", "P", backend="kvt", max_batched=64, extra={"cachedir": str(tmp_path)})
+    else:
+        p_cfg = make_cfg("kv_producer", "P", backend=backend, max_batched=64, extra={"kvs_name": name, "kvs_slots": 24})
+    p, d = _pd_with_store(p_cfg)
+    params = {"remote_host": "127.0.0.1", "remote_port": p.proxy.rpc_port()}
+    try:
+        lens = [30, 70, 120, 180]
+        want = {}
+        issued, touched = [], set()
+        for i in range(24):
+            k = rng.randrange(len(lens))
+            rid = f"m{seed}.{i}"
+            if rng.random() < 0.12:
+                ops.fault_inject_arm(rng.randint(1, 3))
+                touched.add("fault")
+            d.add_request(make_req(rid, lens[k], max_tokens=2, seed=k, params=params))
+            issued.append((rid, k))
+            if rng.random() < 0.25:
+                time.sleep(rng.choice([0.0, 0.004, 0.03, 0.1]))
+                d.abort_requests([rid])
+                touched.add(rid)
+            if rng.random() < 0.4:
+                time.sleep(rng.choice([0.01, 0.06]))
+        ops.fault_inject_arm(0)
+        for rid, k in issued:
+            out = d.wait_finished(rid, 60)
+            assert out is not None, rid
+            how = out.finish_reason.name
+            assert how in ("LENGTH", "ABORT"), (rid, how)
+            if how == "LENGTH":
+                want.setdefault(k, d.output_tokens(rid))
+                assert d.output_tokens(rid) == want[k], rid
+            else:
+                assert rid in touched or "fault" in touched, rid
+        deadline = time.time() + 20
+        pools = [e.scheduler.kv_cache_manager.block_pool for e in (p, d)]
+        while time.time() < deadline and (any(pl.num_free_blocks() != 63 for pl in pools) or p.connector._sched._saving
+                                          or d.connector._sched._loading):
+            time.sleep(0.01)
+        left = {"free": [pl.num_free_blocks() for pl in pools], "p_saving": list(p.connector._sched._saving),
+                "p_loading": list(p.connector._sched._loading), "d_loading": list(d.connector._sched._loading)}
+        assert left["free"] == [63, 63] and not left["p_saving"] and not left["d_loading"], left
+        if backend != "file+kvt":
+            store = _find_store(p.workers[0].connector._worker._backend)
+            assert store is not None
+            end = time.time() + 10
+            while time.time() < end and (store.stats()["writing"] or store.stats()["pinned"]):
+                time.sleep(0.02)
+            st = store.stats()
+            assert st["writing"] == 0 and st["pinned"] == 0, st
+    finally:
+        ops.fault_inject_arm(0)
+        d.shutdown()
+        p.shutdown()
+        if backend != "file+kvt":
+            ops.KvStore.unlink(name)
