@@ -424,8 +424,16 @@ def test_prefill_worker_hands_replicated_requests_to_one_decode_worker():
         p.shutdown()
 
 
-@pytest.mark.parametrize("seed", [1, 2, 3])
-def test_random_arrivals_aborts_and_transport_faults_leak_nothing(pd, seed):
+_MODELS = {
+    "llama": (dict(), 63),
+    "gdn": (dict(cache_shape=3, layers=8, gdn_groups=3), 63),
+    "mla": (dict(cache_shape=4, mla=(64, 16, 36), block_size=64, num_blocks=24), 23),
+}
+
+
+@pytest.mark.parametrize("model,ptp,dtp,seed", [("llama", 1, 1, 1), ("llama", 1, 1, 2), ("llama", 2, 1, 3), ("gdn", 1, 1, 4),
+                                                ("gdn", 2, 1, 5), ("mla", 1, 2, 6)])
+def test_random_arrivals_aborts_and_transport_faults_leak_nothing(model, ptp, dtp, seed):
     """Requests arrive in bursts with random prompt lengths; some are aborted on the decode side at a random
     moment (before the prefill engine has them, while their KV is moving, or while they decode), and a few
     transfers hit an injected transport fault.  Whatever the interleaving: every request ends (LENGTH or
@@ -437,7 +445,8 @@ def test_random_arrivals_aborts_and_transport_faults_leak_nothing(pd, seed):
 
     ops = load_ops()
     rng = random.Random(seed)
-    p, d = pd
+    kw, free_all = _MODELS[model]
+    p, d = make_pd(p_kw=dict(tp=ptp, max_batched=64, **kw), d_kw=dict(tp=dtp, **kw))
     params = {"remote_host": "127.0.0.1", "remote_port": p.proxy.rpc_port()}
     reqs, aborted = [], set()
     faults = 0
@@ -471,13 +480,16 @@ def test_random_arrivals_aborts_and_transport_faults_leak_nothing(pd, seed):
                 assert len(d.output_tokens(r.request_id)) == r.sampling_params.max_tokens, r.request_id
         deadline = time.time() + 15
         pools = [e.scheduler.kv_cache_manager.block_pool for e in (p, d)]
-        while time.time() < deadline and (any(pl.num_free_blocks() != 63 for pl in pools) or p.connector._sched._saving
+        while time.time() < deadline and (any(pl.num_free_blocks() != free_all for pl in pools) or p.connector._sched._saving
                                           or d.connector._sched._loading):
             time.sleep(0.01)
-        assert [pl.num_free_blocks() for pl in pools] == [63, 63]
-        assert not p.connector._sched._saving and not d.connector._sched._loading
+        left = {"free": [pl.num_free_blocks() for pl in pools], "p_saving": list(p.connector._sched._saving),
+                "d_loading": list(d.connector._sched._loading)}
+        assert left["free"] == [free_all, free_all] and not left["p_saving"] and not left["d_loading"], left
     finally:
         ops.fault_inject_arm(0)
+        d.shutdown()
+        p.shutdown()
 
 
 @pytest.mark.parametrize("ptp,dtp,seed", [(1, 1, 1), (2, 1, 2), (1, 2, 3)])
