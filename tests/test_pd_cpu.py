@@ -492,21 +492,22 @@ def test_random_arrivals_aborts_and_transport_faults_leak_nothing(model, ptp, dt
         p.shutdown()
 
 
-@pytest.mark.parametrize("ptp,dtp,seed", [(1, 1, 1), (2, 1, 2), (1, 2, 3)])
-def test_random_dual_requests_with_aborts_on_either_side(ptp, dtp, seed):
+@pytest.mark.parametrize("ptp,dtp,seed,bypass", [(1, 1, 1, False), (2, 1, 2, False), (1, 2, 3, False), (1, 1, 4, True), (2, 2, 5, True)])
+def test_random_dual_requests_with_aborts_on_either_side(ptp, dtp, seed, bypass, monkeypatch):
     """Dual-request mode under a careless frontend: the two halves of a request reach the prefill and the
     decode engine in either order and at random distances, prompts are longer than the prefill engine's token
     budget (chunked prefill, deltas), the engines may be tensor-parallel with different sizes, and some
     requests are aborted on the prefill side, on the decode side or on both, at random moments.  Every
     decode-side request ends; one that nobody aborted decodes; both engines get every block back and neither
-    connector keeps a request."""
+    connector keeps a request.  With ``bypass`` the engines run with bypass tasks and substeps on."""
     import random
 
     rng = random.Random(seed)
     # a prefill half whose decode half never comes (aborted before it got in touch) is given up after this long
-    import os
-    before = os.environ.get("VLLM_PD_TRY_CONNECT_TIMEOUT_SECONDS")
-    os.environ["VLLM_PD_TRY_CONNECT_TIMEOUT_SECONDS"] = "1.5"
+    monkeypatch.setenv("VLLM_PD_TRY_CONNECT_TIMEOUT_SECONDS", "1.5")
+    if bypass:          # late transfers go to the workers as substeps, without a forward pass
+        monkeypatch.setenv("VLLM_ENABLE_BYPASS_TASK", "1")
+        monkeypatch.setenv("VLLM_ENABLE_BYPASS_SUBSTEP", "1")
     p, d = make_pd(p_kw={"tp": ptp, "max_batched": 48}, d_kw={"tp": dtp})
     try:
         reqs, touched = [], set()
@@ -553,7 +554,3 @@ def test_random_dual_requests_with_aborts_on_either_side(ptp, dtp, seed):
     finally:
         d.shutdown()
         p.shutdown()
-        if before is None:
-            os.environ.pop("VLLM_PD_TRY_CONNECT_TIMEOUT_SECONDS", None)
-        else:
-            os.environ["VLLM_PD_TRY_CONNECT_TIMEOUT_SECONDS"] = before
