@@ -734,3 +734,98 @@ def test_transfer_check_passes_intact_batches_and_fails_a_mismatch(proto, ops, s
         srv.stop()
         os.environ.pop("BLLM_KVTRANS_CRC", None)
         ops.envcfg_reset_for_test()
+
+
+# ---- randomized ------------------------------------------------------------------------------------
+@pytest.mark.parametrize("proto,seed", [(PT.TCP, 1), (PT.SHM, 2), (PT.TCP, 3)])
+def test_random_chunked_requests_to_several_destinations_with_faults(proto, seed, ops, sink):
+    """One client, four destinations, forty steps: every step starts some requests (random block tables,
+    random destination) and continues some that are in flight with another chunk; now and then a fault is
+    armed so that a batch fails somewhere on its way.  Steps are not drained one by one, so batches of
+    several steps and destinations overlap.  At the end every request has been reported exactly once; one
+    reported good has every token of every chunk at its destination; one reported failed stayed failed
+    whatever was sent for it afterwards; the client has nothing in flight."""
+    rng = random.Random(seed)
+    src = make_cache(40 + seed)
+    n_dst = 4
+    dsts = [make_cache() for _ in range(n_dst)]
+    srvs = [KVTransferServer(f"D{i}|0|1", 1, 0, 0, BLK, TOK, "fake://", dsts[i], [proto], num_kv_heads=H, cache_shape=2)
+            for i in range(n_dst)]
+    cli = KVTransferClient("P|0|1", 1, 0, 0, BLK, TOK, "fake://", src, [proto], num_kv_heads=H, cache_shape=2)
+    free_d = [list(range(1, NB)) for _ in range(n_dst)]
+    for f in free_d:
+        rng.shuffle(f)
+    live, finished = {}, {}          # rid -> dict(dst, sb, db, total, sent)
+    try:
+        stepid = 5000
+        n_req = 0
+        for step in range(40):
+            if rng.random() < 0.15:
+                ops.fault_inject_arm(rng.randint(1, 4))
+            submitted = 0
+            for rid, r in list(live.items()):           # continue some of the requests in flight
+                if rng.random() < 0.6:
+                    new = min(r["total"] - r["sent"], rng.randint(1, 40))
+                    last = r["sent"] + new == r["total"]
+                    cli.submit_delta_send(rid, r["sent"], new, last, stepid=stepid)
+                    r["sent"] += new
+                    submitted += 1
+                    if last:
+                        finished[rid] = live.pop(rid)
+            for _ in range(rng.randint(0, 3)):            # start new ones
+                i = rng.randrange(n_dst)
+                nb = rng.randint(1, 5)
+                if len(free_d[i]) < nb:
+                    continue
+                total = nb * T - rng.randint(0, T - 1)
+                sb = [rng.randrange(1, NB) for _ in range(nb)]
+                db = [free_d[i].pop() for _ in range(nb)]
+                rid = f"z{seed}.{n_req}"
+                n_req += 1
+                new = rng.randint(1, total)
+                last = new == total
+                cli.submit_req_send2(f"D{i}|0|1", 0, rid, 0, new, last, sb, db, srvs[i].worker_info(), stepid=stepid)
+                rec = dict(dst=i, sb=sb, db=db, total=total, sent=new)
+                (finished if last else live)[rid] = rec
+                submitted += 1
+            cli.start_send_step(stepid, 1 if submitted else 0)
+            if submitted:
+                for layer in range(L):
+                    cli.record_event(layer)
+            cli.flush_send_step()
+            stepid += 1
+            if rng.random() < 0.2:
+                assert cli.wait_inflight(0, 30.0)
+        ops.fault_inject_arm(0)
+        for rid, r in list(live.items()):                # close what is still open
+            cli.submit_delta_send(rid, r["sent"], r["total"] - r["sent"], True, stepid=stepid)
+            r["sent"] = r["total"]
+            finished[rid] = live.pop(rid)
+        cli.start_send_step(stepid, 1)
+        for layer in range(L):
+            cli.record_event(layer)
+        cli.flush_send_step()
+        assert cli.wait_inflight(0, 30.0) and cli.inflight() == 0
+        deadline = time.time() + 10
+        def reports():
+            return [r for m in list(sink.msgs) if m[0] == 0x20181219 for r in m[3]]
+        while time.time() < deadline and len(reports()) < len(finished):
+            time.sleep(0.01)
+        got = {}
+        for rid, plen, code in reports():
+            assert rid not in got, f"{rid} reported twice"
+            got[rid] = (plen, code)
+        assert set(got) == set(finished)
+        good = 0
+        for rid, r in finished.items():
+            plen, code = got[rid]
+            assert code in (0, 500), (rid, code)
+            if code == 0:
+                assert plen == r["total"]
+                check_tokens(src, dsts[r["dst"]], r["sb"], r["db"], 0, r["total"])
+                good += 1
+        assert good >= len(finished) // 3, (good, len(finished))
+    finally:
+        ops.fault_inject_arm(0)
+        for s in srvs:
+            s.stop()
