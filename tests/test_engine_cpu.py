@@ -27,11 +27,11 @@ TOK = 2 * H * D * 2
 BLK = TOK * T
 
 
-def make_cache(seed=None):
+def make_cache(seed=None, device="cpu"):
     if seed is None:
-        return [torch.zeros(2, NB, T, H, D, dtype=torch.float16) for _ in range(L)]
+        return [torch.zeros(2, NB, T, H, D, dtype=torch.float16, device=device) for _ in range(L)]
     g = torch.Generator().manual_seed(seed)
-    return [torch.randn(2, NB, T, H, D, dtype=torch.float16, generator=g) for _ in range(L)]
+    return [torch.randn(2, NB, T, H, D, dtype=torch.float16, generator=g).to(device) for _ in range(L)]
 
 
 def check_tokens(src, dst, sb, db, lo, hi):
@@ -739,16 +739,21 @@ def test_transfer_check_passes_intact_batches_and_fails_a_mismatch(proto, ops, s
 # ---- randomized ------------------------------------------------------------------------------------
 @pytest.mark.parametrize("proto,seed", [(PT.TCP, 1), (PT.SHM, 2), (PT.TCP, 3)])
 def test_random_chunked_requests_to_several_destinations_with_faults(proto, seed, ops, sink):
+    random_chunked_requests(proto, seed, ops, sink, "cpu")
+
+
+def random_chunked_requests(proto, seed, ops, sink, device, drop_completions=False):
     """One client, four destinations, forty steps: every step starts some requests (random block tables,
     random destination) and continues some that are in flight with another chunk; now and then a fault is
     armed so that a batch fails somewhere on its way.  Steps are not drained one by one, so batches of
     several steps and destinations overlap.  At the end every request has been reported exactly once; one
     reported good has every token of every chunk at its destination; one reported failed stayed failed
-    whatever was sent for it afterwards; the client has nothing in flight."""
+    whatever was sent for it afterwards; the client has nothing in flight.  ``drop_completions`` (device
+    transports) also leaves out a batch's completion record now and then, so that its deadline has to fail it."""
     rng = random.Random(seed)
-    src = make_cache(40 + seed)
+    src = make_cache(40 + seed, device)
     n_dst = 4
-    dsts = [make_cache() for _ in range(n_dst)]
+    dsts = [make_cache(None, device) for _ in range(n_dst)]
     srvs = [KVTransferServer(f"D{i}|0|1", 1, 0, 0, BLK, TOK, "fake://", dsts[i], [proto], num_kv_heads=H, cache_shape=2)
             for i in range(n_dst)]
     cli = KVTransferClient("P|0|1", 1, 0, 0, BLK, TOK, "fake://", src, [proto], num_kv_heads=H, cache_shape=2)
@@ -762,6 +767,8 @@ def test_random_chunked_requests_to_several_destinations_with_faults(proto, seed
         for step in range(40):
             if rng.random() < 0.15:
                 ops.fault_inject_arm(rng.randint(1, 4))
+            if drop_completions and rng.random() < 0.08:
+                ops.fault_inject_arm_drop_completion(1)
             submitted = 0
             for rid, r in list(live.items()):           # continue some of the requests in flight
                 if rng.random() < 0.6:
@@ -824,8 +831,9 @@ def test_random_chunked_requests_to_several_destinations_with_faults(proto, seed
                 assert plen == r["total"]
                 check_tokens(src, dsts[r["dst"]], r["sb"], r["db"], 0, r["total"])
                 good += 1
-        assert good >= len(finished) // 3, (good, len(finished))
+        assert good >= max(1, len(finished) // 5), (good, len(finished))
     finally:
         ops.fault_inject_arm(0)
+        ops.fault_inject_arm_drop_completion(0)
         for s in srvs:
             s.stop()

@@ -592,3 +592,23 @@ def test_transfer_check_of_a_layout_converting_transfer(tp, ops):
         srv.stop()
         os.environ.pop("BLLM_KVTRANS_CRC", None)
         ops.envcfg_reset_for_test()
+
+
+# ---- randomized ------------------------------------------------------------------------------------
+from test_engine_cpu import random_chunked_requests, sink  # noqa: E402,F401  (the send-done sink fixture)
+
+
+@pytest.mark.parametrize("seed", [1, 2])
+def test_random_chunked_requests_over_the_device_transport_with_faults_and_lost_completions(seed, ops, sink):
+    """The randomized engine test of the CPU suite with GPU caches over the NVLINK transport: plan slots,
+    per-layer launches and completion records of several destinations and steps overlap, some batches fail on
+    their way (injected on the host) and some lose their completion record, which their deadline turns into a
+    failed batch.  No kernel waits on anything that may not come."""
+    os.environ["BLLM_KVTRANS_COMPLETION_TIMEOUT_MS"] = "300"
+    ops.envcfg_reset_for_test()
+    try:
+        random_chunked_requests(PT.NVLINK, seed, ops, sink, DEV, drop_completions=True)
+        torch.cuda.synchronize()
+    finally:
+        os.environ.pop("BLLM_KVTRANS_COMPLETION_TIMEOUT_MS", None)
+        ops.envcfg_reset_for_test()
