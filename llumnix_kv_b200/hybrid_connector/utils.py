@@ -104,6 +104,7 @@ class RpcServer:
         self._methods: dict[int, _RpcMethod] = {}
         self._started = threading.Event()
         self._server: Optional[asyncio.AbstractServer] = None
+        self._clients: set = set()           # writers of the accepted connections (loop thread only)
 
     def register_method(self, head: int, cb: _RpcMethod) -> None:
         assert head not in self._methods, f"rpc head {head:#x} registered twice"
@@ -118,6 +119,7 @@ class RpcServer:
             self._started.wait(30)
 
     async def _client_main(self, reader, writer):
+        self._clients.add(writer)
         try:
             while True:
                 (head,) = struct.unpack("=I", await reader.readexactly(4))
@@ -135,6 +137,7 @@ class RpcServer:
             logger.exception("%s: rpc handler failed", self._name)
             if ABORT_ON_TASK_EXCEPTION:
                 os.abort()
+        self._clients.discard(writer)
         try:
             writer.close()
             await writer.wait_closed()
@@ -151,8 +154,19 @@ class RpcServer:
             await self._server.serve_forever()
 
     def close(self, loop: asyncio.AbstractEventLoop) -> None:
-        if self._server is not None:
-            loop.call_soon_threadsafe(self._server.close)
+        """Stops listening and hangs up on every peer: one that waits for an answer sees the connection end, as it
+        would when this process died, instead of waiting for a handler that will never finish."""
+        def hang_up():
+            if self._server is not None:
+                self._server.close()
+            for w in list(self._clients):
+                try:
+                    w.close()
+                except Exception:
+                    pass
+            self._clients.clear()
+
+        loop.call_soon_threadsafe(hang_up)
 
 
 Conn = tuple

@@ -554,3 +554,46 @@ def test_random_dual_requests_with_aborts_on_either_side(ptp, dtp, seed, bypass,
     finally:
         d.shutdown()
         p.shutdown()
+
+
+def test_prefill_engine_goes_away_mid_stream_and_a_new_one_serves_the_next_requests():
+    """The prefill engine stops while the decode engine has requests with it (some being computed, some
+    queued, some moving).  Every one of them ends on the decode side in bounded time - none waits for an answer
+    that cannot come - the decode engine gets its blocks back, and requests sent to a fresh prefill engine
+    afterwards decode as usual."""
+    p, d = make_pd(p_kw={"max_batched": 32})
+    p2 = None
+    try:
+        params = {"remote_host": "127.0.0.1", "remote_port": p.proxy.rpc_port()}
+        slow = p.step
+        p.step = lambda: (time.sleep(0.01), slow())[1]                  # keep requests in the prefill engine for a while
+        reqs = [make_req(f"g{i}", 60 + 20 * i, max_tokens=2, seed=i, params=params) for i in range(6)]
+        for r in reqs:
+            d.add_request(r)
+        time.sleep(0.08)
+        p.shutdown()                                                    # RPC server, workers and transfer client go away
+        ended = {}
+        for r in reqs:
+            out = d.wait_finished(r.request_id, 60)
+            assert out is not None, r.request_id
+            ended[r.request_id] = out.finish_reason.name
+        assert set(ended.values()) <= {"LENGTH", "ABORT"} and "ABORT" in ended.values(), ended
+        deadline = time.time() + 15
+        pool = d.scheduler.kv_cache_manager.block_pool
+        while time.time() < deadline and (pool.num_free_blocks() != 63 or d.connector._sched._loading):
+            time.sleep(0.01)
+        assert pool.num_free_blocks() == 63 and not d.connector._sched._loading
+        from pd_helpers import make_cfg
+        from llumnix_kv_b200.engine.core import MiniEngineCore
+
+        p2 = MiniEngineCore(make_cfg("kv_producer", "P2"))
+        params2 = {"remote_host": "127.0.0.1", "remote_port": p2.proxy.rpc_port()}
+        for i in range(3):
+            d.add_request(make_req(f"n{i}", 50 + i, max_tokens=2, seed=20 + i, params=params2))
+        for i in range(3):
+            out = d.wait_finished(f"n{i}", 30)
+            assert out is not None and out.finish_reason.name == "LENGTH", i
+    finally:
+        d.shutdown()
+        if p2 is not None:
+            p2.shutdown()
