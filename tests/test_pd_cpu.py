@@ -597,3 +597,40 @@ def test_prefill_engine_goes_away_mid_stream_and_a_new_one_serves_the_next_reque
         d.shutdown()
         if p2 is not None:
             p2.shutdown()
+
+
+def test_decode_engine_goes_away_mid_stream_and_the_prefill_engine_lets_go_of_everything():
+    """The mirror image: the decode engine stops while the prefill engine computes and ships its requests.  The
+    transfers fail on the host (nobody listens any more), the prefill engine finishes or fails every request, gets
+    every block back, keeps no request in its connector, and serves a fresh decode engine afterwards."""
+    p, d = make_pd(p_kw={"max_batched": 32})
+    d2 = None
+    try:
+        params = {"remote_host": "127.0.0.1", "remote_port": p.proxy.rpc_port()}
+        slow = p.step
+        p.step = lambda: (time.sleep(0.01), slow())[1]
+        for i in range(6):
+            d.add_request(make_req(f"v{i}", 60 + 20 * i, max_tokens=2, seed=i, params=params))
+        time.sleep(0.08)
+        d.shutdown()
+        deadline = time.time() + 30
+        pool = p.scheduler.kv_cache_manager.block_pool
+        sched = p.connector._sched
+        while time.time() < deadline and (pool.num_free_blocks() != 63 or sched._saving or p.scheduler.running or p.scheduler.waiting):
+            time.sleep(0.01)
+        left = {"free": pool.num_free_blocks(), "saving": list(sched._saving), "running": [r.request_id for r in p.scheduler.running],
+                "waiting": [r.request_id for r in p.scheduler.waiting]}
+        assert left == {"free": 63, "saving": [], "running": [], "waiting": []}, left
+        from pd_helpers import make_cfg
+        from llumnix_kv_b200.engine.core import MiniEngineCore
+
+        d2 = MiniEngineCore(make_cfg("kv_consumer", "D2"))
+        for i in range(3):
+            d2.add_request(make_req(f"w{i}", 50 + i, max_tokens=2, seed=30 + i, params=params))
+        for i in range(3):
+            out = d2.wait_finished(f"w{i}", 30)
+            assert out is not None and out.finish_reason.name == "LENGTH", i
+    finally:
+        p.shutdown()
+        if d2 is not None:
+            d2.shutdown()
