@@ -9,6 +9,7 @@
 // Connections: BLLM_KVTRANS_RDMA_SP sockets per target, layers round-robin over them.
 #include <fcntl.h>
 #include <sys/mman.h>
+#include <poll.h>
 #include <sys/socket.h>
 #include <unistd.h>
 
@@ -257,7 +258,21 @@ class HostChannel : public IChannel {
     data_.clear();
   }
 
-  bool is_active() override { return active_; }
+  // Between batches nothing is outstanding on the connections, so anything readable is the peer hanging up
+  // (its process ended, or its server was stopped): the stub then builds a fresh channel, resolving the
+  // destination again, before the next batch instead of failing that batch on a dead socket
+  // (the role of XChannel::IsActive in kvtransfer/src/protocol/barex_protocol.cpp:701-711).
+  bool is_active() override {
+    if (!active_) return false;
+    for (const auto& s : socks_) {
+      struct pollfd p{s.fd(), POLLIN | POLLRDHUP, 0};
+      if (::poll(&p, 1, 0) > 0 && (p.revents & (POLLIN | POLLRDHUP | POLLHUP | POLLERR)) != 0) {
+        active_ = false;
+        break;
+      }
+    }
+    return active_;
+  }
 
   void close() override {
     for (auto& sl : slots_) {

@@ -634,3 +634,51 @@ def test_decode_engine_goes_away_mid_stream_and_the_prefill_engine_lets_go_of_ev
         p.shutdown()
         if d2 is not None:
             d2.shutdown()
+
+
+def test_engines_come_and_go_behind_a_naming_service(tmp_path, monkeypatch):
+    """With a registry, the engines find each other by name and role.  The decode engine is replaced by a new
+    one under the same name (new process in real life: new ports, new worker infos), then the prefill engine is
+    replaced as well: each side notices through the registry, drops what it knew about the old peer, and the
+    requests that follow a replacement are served as the first ones were."""
+    from pd_helpers import make_cfg
+    from llumnix_kv_b200.engine.core import MiniEngineCore
+
+    from llumnix_kv_b200.hybrid_connector.utils import PeerManager
+
+    monkeypatch.setattr(PeerManager, "POLL_S", 0.2)          # the registry is polled every 7 s in production
+    url = f"file:{tmp_path}"
+    ex = {"naming_url": url}
+    p = MiniEngineCore(make_cfg("kv_producer", "P", extra=dict(ex)))
+    d = MiniEngineCore(make_cfg("kv_consumer", "D", extra=dict(ex)))
+    engines = [p, d]
+
+    def serve(dec, pre, tag, n=3):
+        deadline = time.time() + 20
+        want = ("127.0.0.1", pre.proxy.rpc_port())
+        while time.time() < deadline and dec.connector._sched._backend.get_peer() != want:
+            time.sleep(0.05)
+        assert dec.connector._sched._backend.get_peer() == want, tag
+        cap = _spy_add(dec)
+        reqs = [make_req(f"{tag}{i}", 40 + 9 * i, max_tokens=2, seed=i) for i in range(n)]
+        for r in reqs:
+            dec.add_request(r)
+        for r in reqs:
+            out = dec.wait_finished(r.request_id, 30)
+            assert out is not None and out.finish_reason.name == "LENGTH", r.request_id
+            computed, blocks = cap[r.request_id]
+            check_decode_cache(dec, r.request_id, r.prompt_token_ids, blocks[0], computed)
+
+    try:
+        serve(d, p, "a")
+        d.shutdown()
+        d = MiniEngineCore(make_cfg("kv_consumer", "D", extra=dict(ex)))      # same name, everything else new
+        engines[1] = d
+        serve(d, p, "b")
+        p.shutdown()
+        p = MiniEngineCore(make_cfg("kv_producer", "P", extra=dict(ex)))
+        engines[0] = p
+        serve(d, p, "c")
+    finally:
+        for e in engines:
+            e.shutdown()
