@@ -837,3 +837,92 @@ def random_chunked_requests(proto, seed, ops, sink, device, drop_completions=Fal
         ops.fault_inject_arm_drop_completion(0)
         for s in srvs:
             s.stop()
+
+
+def test_server_survives_malformed_and_mutated_frames(ops):
+    """Hundreds of frames that no sender of ours produces - valid messages of every kind with bytes flipped,
+    fields blown up, tails cut off or junk appended, and pure noise - against one server.  It answers or hangs
+    up, never crashes, never writes outside the ranges a well-formed message names, and still serves a
+    well-formed transfer afterwards."""
+    rng = random.Random(99)
+    dst = make_cache()
+    srv = KVTransferServer("D|0|1", 1, 0, 0, BLK, TOK, "fake://", dst, [PT.TCP], num_kv_heads=H, cache_shape=2)
+    port = int(ops.WorkerInfo.from_string(srv.worker_info()).ext["port"])
+    payload = bytes(rng.randrange(256) for _ in range(512))
+
+    def data_msg():
+        blocks = [(0, 3 * BLK // 2 + 64, 256), (256, 9 * BLK // 2, 256)]            # src (in blob), dst, len
+        body = struct.pack("=QQ", 1, 1) + struct.pack("=Q", len(blocks)) + b"".join(struct.pack("=QQQ", *b) for b in blocks)
+        return struct.pack("=IQ", 0x4B564361, 5) + body + struct.pack("=Q", len(payload)) + payload
+
+    def check_msg():
+        rs = [(64, 128), (BLK, 4096)]
+        return (struct.pack("=IQ", 0x4B56436B, 6) + struct.pack("=IIII", 0, L, 1, 0) + struct.pack("=Q", len(rs))
+                + b"".join(struct.pack("=QQ", *r) for r in rs))
+
+    def check_rows_msg():
+        layout = struct.pack("=8q6I", BLK // 2, NB * BLK // 2, H * D * 2, D * 2, 0, 0, 0, 0, T, H, D * 2, NB, 2, 0)
+        reqs = struct.pack("=6I", 0, 2, 0, 20, 0, 0)
+        return (struct.pack("=IQ", 0x4B56436C, 7) + struct.pack("=IIII", 0, L, 0, H) + layout + struct.pack("=II", 1, 2) + reqs
+                + struct.pack("=II", 3, 4))
+
+    def attach_msg():
+        name = b"/kvx_no_such_segment"
+        return struct.pack("=IQ", 0x4B565341, 8) + struct.pack("=I", len(name)) + name + struct.pack("=Q", 4096)
+
+    seeds = [data_msg(), check_msg(), check_rows_msg(), attach_msg(), struct.pack("=IQ", 0x20181218, 9),
+             struct.pack("=IQ", 0x4B56504F, 10) + b"\\0" * 64, struct.pack("=IQ", 0x4B565050, 11) + b"\\0" * 40,
+             struct.pack("=IQ", 0x4B565069, 12)]
+
+    def mutate(m: bytes) -> bytes:
+        b = bytearray(m)
+        kind = rng.randrange(6)
+        if kind == 0 and len(b) > 12:
+            for _ in range(rng.randint(1, 6)):
+                b[rng.randrange(4, len(b))] = rng.randrange(256)
+        elif kind == 1 and len(b) > 20:
+            at = rng.randrange(12, len(b) - 7)
+            b[at:at + 8] = struct.pack("=Q", rng.choice([0, 1 << 31, 1 << 40, (1 << 64) - 1, 1 << 62]))
+        elif kind == 2 and len(b) > 13:
+            del b[rng.randrange(12, len(b)):]
+        elif kind == 3:
+            b += bytes(rng.randrange(256) for _ in range(rng.randint(1, 64)))
+        elif kind == 4:
+            b = bytearray(rng.randrange(256) for _ in range(rng.randint(0, 80)))
+        return bytes(b)
+
+    def talk(c, msg):
+        c.sendall(struct.pack("=I", len(msg)) + msg)
+        head = c.recv(4, socket.MSG_WAITALL)
+        if len(head) < 4:
+            return None
+        return c.recv(struct.unpack("=I", head)[0], socket.MSG_WAITALL)
+
+    try:
+        c = socket.create_connection(("127.0.0.1", port), timeout=5)
+        answered = hung_up = 0
+        for i in range(400):
+            msg = mutate(rng.choice(seeds)) if i % 5 else rng.choice(seeds[:3] + seeds[7:])
+            try:
+                r = talk(c, msg)
+            except (OSError, socket.timeout):
+                r = None
+            if r is None:
+                hung_up += 1
+                c.close()
+                c = socket.create_connection(("127.0.0.1", port), timeout=5)
+            else:
+                answered += 1
+        assert answered > 50 and hung_up > 20, (answered, hung_up)
+        # still in service: a ping, and an intact transfer lands where it says
+        assert struct.unpack("=I", talk(c, struct.pack("=IQ", 0x4B565069, 1))[12:16])[0] == 0
+        for d in dst:
+            d.zero_()
+        assert struct.unpack("=I", talk(c, data_msg())[12:16])[0] == 0
+        flat = dst[1].view(torch.uint8).flatten()
+        assert bytes(flat[3 * BLK // 2 + 64:3 * BLK // 2 + 64 + 256].tolist()) == payload[:256]
+        assert bytes(flat[9 * BLK // 2:9 * BLK // 2 + 256].tolist()) == payload[256:]
+        assert int(flat.count_nonzero()) <= 512 and int(dst[0].count_nonzero()) == 0
+        c.close()
+    finally:
+        srv.stop()
