@@ -134,9 +134,9 @@ class RpcServer:
         except (ConnectionResetError, BrokenPipeError):
             pass
         except Exception:
+            # whatever a peer sent, or whatever broke while answering it, costs that peer its connection and
+            # nothing else (blade_kvt/hybrid_connector/utils.py:109-137 logs and closes likewise)
             logger.exception("%s: rpc handler failed", self._name)
-            if ABORT_ON_TASK_EXCEPTION:
-                os.abort()
         self._clients.discard(writer)
         try:
             writer.close()

@@ -682,3 +682,42 @@ def test_engines_come_and_go_behind_a_naming_service(tmp_path, monkeypatch):
     finally:
         for e in engines:
             e.shutdown()
+
+
+def test_control_plane_survives_malformed_messages(pd, monkeypatch):
+    """Every RPC the two schedulers answer, with bodies no peer of ours sends (noise, truncated msgpack, wrong
+    types, absurd lengths) and with unknown heads: the sender loses its connection at most; both engines stay
+    up, with the default setting that aborts the process on a failed background task, and serve the next
+    request."""
+    import random
+    import socket
+    import struct
+
+    import llumnix_kv_b200.hybrid_connector.utils as U
+
+    monkeypatch.setattr(U, "ABORT_ON_TASK_EXCEPTION", True)          # production default; the tests run with it off
+    rng = random.Random(5)
+    p, d = pd
+    heads = [0x20181218, 0x20210912, 0x20181219, 20250820, 0x20181221, 0x20181222, 0x20181223, 0x20181224, 0x20181226,
+             20080818, 20080901, 20080903, 20080828, 0x20240912, 0xDEADBEEF, 0]
+    bodies = [b"", b"\\xff" * 7, struct.pack("=I", 5) + b"\\x93\\x01\\x02", struct.pack("=I", 1 << 30) + b"x" * 16,
+              struct.pack("=I", 12) + b"\\x91\\xa3abc" + b"\\0" * 8, struct.pack("=II", 0x40000001, 3) + b"\\0" * 11]
+    for eng in (p, d):
+        port = eng.proxy.rpc_port()
+        for head in heads:
+            for _ in range(4):
+                body = rng.choice(bodies) if rng.random() < 0.7 else bytes(rng.randrange(256) for _ in range(rng.randint(1, 60)))
+                try:
+                    with socket.create_connection(("127.0.0.1", port), timeout=2) as c:
+                        c.sendall(struct.pack("=I", head) + body)
+                        c.settimeout(0.05)
+                        try:
+                            c.recv(64)
+                        except (socket.timeout, OSError):
+                            pass
+                except OSError:
+                    pass
+    req = make_req("after", 44, max_tokens=2, params={"remote_host": "127.0.0.1", "remote_port": p.proxy.rpc_port()})
+    d.add_request(req)
+    out = d.wait_finished("after", 30)
+    assert out is not None and out.finish_reason.name == "LENGTH"
