@@ -356,7 +356,6 @@ class HostChannel : public IChannel {
       drain(0);
       if (shm_registered_) kvt_host_unregister_(shm_base_);
       munmap(shm_base_, shm_bytes_);
-      shm_unlink(shm_name_.c_str());
       shm_base_ = nullptr;
     }
     static std::atomic<int> seq{0};
@@ -382,7 +381,16 @@ class HostChannel : public IChannel {
       shm_dev_ = dev;
       shm_registered_ = true;
     }
-    // tell every connection's server thread to map the segment
+    // Tell every connection's server thread to map the segment.  Whatever happens, the name goes away before this
+    // function returns: the mappings keep the memory alive for as long as both sides use it, and a process that
+    // dies (or never closes its channels) leaves nothing behind in /dev/shm.
+    struct Unlink {
+      std::string* name;
+      ~Unlink() {
+        shm_unlink(name->c_str());
+        name->clear();
+      }
+    } unlink_on_exit{&shm_name_};
     for (auto& s : socks_) {
       std::string req(RPC_HEADER, '\0');
       const uint64_t reqid = new_id();
@@ -398,7 +406,7 @@ class HostChannel : public IChannel {
       }
       if (status != WIRE_OK) {
         active_ = false;
-        throw KVTransferException(ErrorKind::TRANSPORT, "receiver could not attach shm segment " + shm_name_);
+        throw KVTransferException(ErrorKind::TRANSPORT, "receiver could not attach shm segment " + std::string(shm_name_));
       }
     }
   }

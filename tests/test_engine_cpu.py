@@ -926,3 +926,27 @@ def test_server_survives_malformed_and_mutated_frames(ops):
         c.close()
     finally:
         srv.stop()
+
+
+def test_shm_transport_leaves_no_name_behind(sink):
+    """The segment that carries the SHM transport's data is unlinked as soon as both sides have mapped it: while
+    transfers run there is no name of this process under /dev/shm, so a process that dies, or never closes its
+    channels, leaves nothing behind."""
+    import glob
+
+    src, dst = make_cache(77), make_cache()
+    srv = KVTransferServer("D|0|1", 1, 0, 0, BLK, TOK, "fake://", dst, [PT.SHM], num_kv_heads=H, cache_shape=2)
+    cli = KVTransferClient("P|0|1", 1, 0, 0, BLK, TOK, "fake://", src, [PT.SHM], num_kv_heads=H, cache_shape=2)
+    try:
+        for step, nb in enumerate((2, 30)):              # the second batch outgrows the first segment
+            sb, db = list(range(1, 1 + nb)), list(range(30, 30 + nb))
+            cli.submit_req_send2("D|0|1", 0, f"s{step}", 0, nb * T, True, sb, db, srv.worker_info(), stepid=step + 1)
+            cli.start_send_step(step + 1, 1)
+            for layer in range(L):
+                cli.record_event(layer)
+            cli.flush_send_step()
+            cli.drain()
+            check_tokens(src, dst, sb, db, 0, nb * T)
+            assert glob.glob(f"/dev/shm/kvx_{os.getpid()}_*") == []
+    finally:
+        srv.stop()
