@@ -99,6 +99,9 @@ class MiniEngineCore:
         self.input_queue.put_nowait((EngineCoreRequestType.WAKEUP, None))
         if self._thread is not None:
             self._thread.join(10)
+        for w in self.workers:
+            if w.connector is not None:
+                w.connector._worker.closing = True
         if self.connector is not None and self.proxy is not None:
             self.connector._sched.close_bypass()
             self.proxy.rpc_server.close(self.proxy.sched_loop)

@@ -12,7 +12,9 @@ import logging
 import os
 import random
 import struct
+import sys
 import threading
+import traceback
 from collections import OrderedDict
 from dataclasses import dataclass
 from typing import Any, Callable, Coroutine, Optional
@@ -47,6 +49,10 @@ def kill_me_if_exception(async_func):
         except Exception:
             logger.exception("task %s failed", getattr(async_func, "__name__", async_func))
             if ABORT_ON_TASK_EXCEPTION:
+                # the reason must be readable even where logging goes nowhere
+                sys.stderr.write(f"aborting: background task {getattr(async_func, '__name__', async_func)} failed\n")
+                traceback.print_exc(file=sys.stderr)
+                sys.stderr.flush()
                 os.abort()
             raise
 

@@ -33,6 +33,7 @@ class _WSavingReq:
 
 class HybridWorker:
     def __init__(self, vllm_config: VllmConfig, kv_cache_config, worker: WorkerProxy):
+        self.closing = False          # set by the engine before it stops the scheduler's RPC server
         from llumnix_kv_b200 import envs
 
         self._cfg = vllm_config
@@ -146,18 +147,25 @@ class HybridWorker:
         body = self._ioenc.encode(req)
         msg = struct.pack("=II", head, len(body)) + body
         for attempt in range(2):
-            reader, writer = await self._connpool._acquire(force_new=attempt > 0)
+            writer = None
             try:
+                reader, writer = await self._connpool._acquire(force_new=attempt > 0)
                 writer.write(msg)
                 await writer.drain()
                 (resphead,) = struct.unpack("=I", await reader.readexactly(4))
                 assert resphead == reshead
                 self._connpool._release((reader, writer))
                 return
-            except (asyncio.IncompleteReadError, ConnectionError):
-                if attempt == 1:
-                    raise
-                writer.close()
+            except (asyncio.IncompleteReadError, ConnectionError, OSError):
+                if writer is not None:
+                    writer.close()
+                if attempt == 0:
+                    continue
+                if self.closing:
+                    # the engine is shutting down and its scheduler no longer listens: the report has nobody to go to
+                    logger.info("io done report dropped at shutdown: %s", req)
+                    return
+                raise
 
     @kill_me_if_exception
     async def _async_load_kv(self, m: HybridMetadata):
