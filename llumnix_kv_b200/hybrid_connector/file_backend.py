@@ -156,8 +156,10 @@ class FileBackend(HybridBackend):
                 await loop.run_in_executor(None, load)
                 yield IoRet(reqid=r.reqid, source=self.source_label())
             except Exception as ex:
-                logger.warning("local_file: load failed. reqid=%s ex=%r", r.reqid, ex)
-                yield IoRet(reqid=r.reqid, n=0, ex=ex, source=self.source_label())
+                # a cache that cannot deliver is a miss, not a failed request: nothing counts as loaded and the engine
+                # computes the prompt itself (as the reference's store backends report fewer tokens, never a failure)
+                logger.warning("local_file: load failed, the request computes its prompt. reqid=%s ex=%r", r.reqid, ex)
+                yield IoRet(reqid=r.reqid, n=0, source=self.source_label())
 
     def async_save_kv_layer(self, layer_name: str, kv_layer, m: BackendMeta) -> Optional[AsyncGenerator]:
         assert isinstance(m, FileMeta)

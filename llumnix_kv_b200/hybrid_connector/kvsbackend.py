@@ -347,9 +347,9 @@ class KVSBackend(HybridBackend):
                 await self._wait_event(ev)
                 st.check_status()
                 ioret = IoRet(reqid=r.reqid, n=loaded, source=self.source_label())
-            except Exception as ex:   # the request falls back to computing everything itself
-                logger.warning("kvs: load failed. reqid=%s ex=%r", r.reqid, ex)
-                ioret = IoRet(reqid=r.reqid, n=0, ex=ex, source=self.source_label())
+            except Exception as ex:   # a miss, not a failed request: it falls back to computing everything itself
+                logger.warning("kvs: load failed, the request computes its prompt. reqid=%s ex=%r", r.reqid, ex)
+                ioret = IoRet(reqid=r.reqid, n=0, source=self.source_label())
             finally:
                 st.unpin(keys[:n])
             yield ioret

@@ -584,7 +584,11 @@ class HybridScheduler:
 
     async def _read_iodone(self, reader) -> IoDoneReqs:
         (n,) = struct.unpack("=I", await reader.readexactly(4))
-        return self._iodonedec.decode(await reader.readexactly(n))
+        reqs = self._iodonedec.decode(await reader.readexactly(n))
+        for r in reqs.reqids:
+            if r.ex is not None and not isinstance(r.ex, BaseException):
+                r.ex = RuntimeError(f"worker {reqs.worker_tprank}: {r.ex}")      # a worker's failure travels as text
+        return reqs
 
     async def _on_save_done(self, reader, writer):
         reqs = await self._read_iodone(reader)

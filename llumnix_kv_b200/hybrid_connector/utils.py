@@ -50,9 +50,15 @@ def kill_me_if_exception(async_func):
             logger.exception("task %s failed", getattr(async_func, "__name__", async_func))
             if ABORT_ON_TASK_EXCEPTION:
                 # the reason must be readable even where logging goes nowhere
-                sys.stderr.write(f"aborting: background task {getattr(async_func, '__name__', async_func)} failed\n")
-                traceback.print_exc(file=sys.stderr)
+                why = f"aborting: background task {getattr(async_func, '__name__', async_func)} failed\n{traceback.format_exc()}"
+                sys.stderr.write(why)
                 sys.stderr.flush()
+                try:        # stderr may be captured or closed: leave the reason where it can be found afterwards
+                    import tempfile
+                    with open(os.path.join(tempfile.gettempdir(), f"llumnix_kv_abort.{os.getpid()}.txt"), "w") as f:
+                        f.write(why)
+                except OSError:
+                    pass
                 os.abort()
             raise
 

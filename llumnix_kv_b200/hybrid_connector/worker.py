@@ -31,6 +31,12 @@ class _WSavingReq:
         self._ready_layers: list = []
 
 
+def _failure_as_text(obj):
+    if isinstance(obj, BaseException):
+        return f"{type(obj).__name__}: {obj}"
+    raise NotImplementedError(f"objects of type {type(obj).__name__} do not travel in a completion report")
+
+
 class HybridWorker:
     def __init__(self, vllm_config: VllmConfig, kv_cache_config, worker: WorkerProxy):
         self.closing = False          # set by the engine before it stops the scheduler's RPC server
@@ -43,7 +49,9 @@ class HybridWorker:
         self._meta: Optional[HybridMetadata] = None          # model-runner thread
         self._saving: dict[str, _WSavingReq] = {}             # disaggw thread
         self._connpool = ConnPool(scheduler_rpc_host(vllm_config), sched_rpc_server_port(vllm_config), 3)
-        self._ioenc = msgspec.msgpack.Encoder()
+        # A failure crosses the wire as text ("Type: message"): msgspec does not encode exception objects, and a worker
+        # that tried used to end its process (the reference warns of exactly that next to IoRet.ex and never sets it).
+        self._ioenc = msgspec.msgpack.Encoder(enc_hook=_failure_as_text)
         self._strdec = msgspec.msgpack.Decoder(str)
         BackendCls = get_backend_cls(vllm_config)
         self._backend = BackendCls(vllm_config, KVConnectorRole.WORKER, kv_cache_config, worker=worker, connector=self)

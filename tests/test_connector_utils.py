@@ -295,3 +295,23 @@ def test_ledger_agrees_with_a_recomputation_over_random_signal_histories():
                 assert led.source_moved_nothing(src) == any(s.n == 0 for s in seen)
 
     run()
+
+
+def test_a_workers_failure_travels_in_its_completion_report():
+    """A worker backend that reports a failed load or save puts the exception into the IoRet; on its way to the
+    scheduler the exception becomes text and comes out as an exception again (msgspec cannot encode exception
+    objects, and a worker that tried used to end its process)."""
+    import msgspec
+
+    from llumnix_kv_b200.hybrid_connector.backend import IoDoneReqs
+    from llumnix_kv_b200.hybrid_connector.worker import _failure_as_text
+
+    enc = msgspec.msgpack.Encoder(enc_hook=_failure_as_text)
+    dec = msgspec.msgpack.Decoder(IoDoneReqs)
+    report = IoDoneReqs(worker_tprank=1, reqids=[IoRet(reqid="a", n=0, ex=FileNotFoundError("block 7 is gone"), source="local_file"),
+                                                 IoRet(reqid="b", n=32, source="kvs")])
+    back = dec.decode(enc.encode(report))
+    assert back.worker_tprank == 1 and back.reqids[1] == IoRet(reqid="b", n=32, source="kvs")
+    assert back.reqids[0].ex == "FileNotFoundError: block 7 is gone" and back.reqids[0].n == 0
+    with pytest.raises(NotImplementedError):
+        enc.encode(IoDoneReqs(worker_tprank=0, reqids=[IoRet(reqid="c", ex=object())]))

@@ -181,3 +181,27 @@ def test_random_requests_and_aborts_through_a_prefill_engine_that_also_stores(ba
         p.shutdown()
         if backend != "file+kvt":
             ops.KvStore.unlink(name)
+
+
+def test_a_stored_block_that_cannot_be_read_is_a_miss_not_a_failed_request(tmp_path):
+    """The second request finds its prefix in the file store, but one block's data has been damaged since it was
+    written.  The load reports nothing loaded, the engine computes the prompt itself, and the request decodes
+    what it always decodes: a cache that cannot deliver costs time, never the request (and never the worker:
+    a failure object in a completion report used to end its process)."""
+    e = MiniEngineCore(make_cfg("kv_both", "F", backend="local_file", extra={"cachedir": str(tmp_path)}))
+    try:
+        cap = spy(e)
+        r1 = run(e, "a", 50)
+        want = e.output_tokens("a")
+        assert wait_free(e, 63) == 63
+        d = tmp_path / "_".join(str(t) for t in r1.prompt_token_ids[:16])           # the first block of the prefix
+        assert (d / "ready").is_file()
+        (d / "0.model.layers.1.self_attn.attn.data").write_bytes(b"not a tensor")
+        for t in e.workers[0].kv_caches.values():
+            t.zero_()
+        run(e, "b", 50)
+        assert cap["b"][0] == 0                       # nothing counted as loaded: everything was computed here
+        assert e.output_tokens("b") == want
+        assert wait_free(e, 63) == 63 and not e.connector._sched._loading
+    finally:
+        e.shutdown()
