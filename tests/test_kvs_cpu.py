@@ -252,17 +252,19 @@ def test_trace_context_reaches_the_store_operations(store_name):
         e.shutdown()
 
 
-@pytest.mark.parametrize("backend,seed", [("kvs", 1), ("kvs", 2), ("mooncake", 3), ("v6d_object", 4)])
-def test_random_requests_and_aborts_on_two_engines_sharing_a_store(store_name, seed, backend):
+@pytest.mark.parametrize("backend,seed,tp", [("kvs", 1, 1), ("kvs", 2, 1), ("mooncake", 3, 1), ("v6d_object", 4, 1), ("kvs", 5, 2)])
+def test_random_requests_and_aborts_on_two_engines_sharing_a_store(store_name, seed, backend, tp):
     """Two engines of a node share one store (any flavour) that is too small for everything; requests over a handful of prompts
     (so prefixes are shared, saved by one engine and loaded by the other) arrive at random and some are aborted
     while they load, prefill or save.  Every request that was not aborted produces the tokens its prompt always
-    produces, both engines get every block back, and the store keeps nothing reserved or pinned."""
+    produces, both engines get every block back, and the store keeps nothing reserved or pinned.  With ``tp`` 2
+    every rank of an engine keeps its own pages of a block and a prefix counts only when all ranks have it."""
     import random
 
     rng = random.Random(seed)
     extra = {"kvs_name": store_name, "kvs_slots": 24, "kvs_abort_grace_s": 0.05}
-    a, b = (MiniEngineCore(make_cfg("kv_both", n, backend=backend, num_blocks=128, max_batched=64, extra=dict(extra))) for n in "AB")
+    a, b = (MiniEngineCore(make_cfg("kv_both", n, backend=backend, num_blocks=128, max_batched=64, tp=tp, extra=dict(extra)))
+            for n in "AB")
     try:
         lens = [40, 75, 130, 200, 260]
         want = {}
