@@ -37,7 +37,7 @@ import msgspec
 
 from llumnix_kv_b200 import envs
 
-from .backend import BackendMeta, HCSchedOutput, HybridBackend, OperationPlan, req_aborted
+from .backend import BackendMeta, HCSchedOutput, HybridBackend, OperationPlan, has_setup_save, req_aborted
 from .engine_proxy import (EngineCoreRequest, KVCacheBlocks, KVConnectorRole, Request, SchedulerOutput, VllmConfig,
                            core_get_param, core_update_params, get_p_node_pop_len, get_param,
                            sched_rpc_server_port, scheduler_rpc_host, set_param)
@@ -506,6 +506,16 @@ class PBackend(HybridBackend):
         logger.info("disagg start kvt. reqid=%s peer=%s computed=%s max=%s", req.reqid, req.dinfo.instid,
                     req.dinfo.cached_tokens, req.dinfo.max_tokens)
         assert self._check_kvtdinfo(req.dinfo)
+        if req.migration:
+            known = self.get_request(req.reqid)
+            if req.reqid in self._sending or (known is not None and (get_param(known, P_KVT_STATE) is not None
+                                                                      or has_setup_save(known))):
+                # This request's KV has been shipped from here before, for a migration that did not take it away
+                # in the end (or one is under way).  Its save cannot be set up a second time: the asker is told to
+                # keep its hands off instead of tripping the engine over it.
+                logger.warning("transfer for migration refused, the request was shipped before: reqid=%s", req.reqid)
+                return KVTResp(code=CODE_MIGRATE_REJECTED_BUSY, cached=0, computed=known.num_computed_tokens if known else 0,
+                               output_token_ids=[])
         assert req.reqid not in self._sending
         state = _SendingReq(self._kvt_signals_per_worker(req.dinfo))
         self._sending[req.reqid] = state

@@ -210,7 +210,8 @@ class MigrationBackend(HybridBackend):
         bs = self._cfg.cache_config.block_size
         n_out = get_param(req, OUTPUT_TOKENS_N, 0)
         alltokens = n_out + len(req.prompt_token_ids)
-        assert len(blockids[0]) * bs >= alltokens
+        # the attention group (the longest one; hybrid models put their one-block state groups first) must hold it all
+        assert max(len(g) for g in blockids) * bs >= alltokens
         t0 = time.monotonic()
         if n_out == 0:
             # still waiting (or prefilling) on the source: nothing worth moving, just take it over

@@ -130,8 +130,29 @@ def test_abort_through_the_frontend(two):
         cli.close()
 
 
-@pytest.mark.parametrize("seed", [1, 2])
-def test_random_migrations_keep_every_stream_intact(two, seed):
+_VARIANTS = {
+    "plain": {},
+    "tp2": dict(tp=2),
+    "gdn": dict(cache_shape=3, layers=8, gdn_groups=3),
+    "mla": dict(cache_shape=4, mla=(64, 16, 36), block_size=64, num_blocks=64),
+}
+
+
+@pytest.mark.parametrize("variant,seed", [("plain", 1), ("plain", 2), ("tp2", 3), ("gdn", 4), ("mla", 5)])
+def test_random_migrations_on_every_kind_of_engine(variant, seed):
+    """The random migrations below on tensor-parallel engines, on a hybrid model (recurrent state pages travel with
+    the attention pages) and on an MLA model."""
+    kw = _VARIANTS[variant]
+    a, b = make_engine("A", **kw), make_engine("B", **kw)
+    try:
+        test_random_migrations_keep_every_stream_intact((a, b), seed, kw)
+    finally:
+        a.shutdown()
+        b.shutdown()
+
+
+@pytest.mark.parametrize("seed", [6])
+def test_random_migrations_keep_every_stream_intact(two, seed, kw=None):
     """Several requests decode on two engines while the frontend keeps asking, at random moments, to move a
     random one of them to the other engine (some asks come too early, some too late, some are refused).
     Whatever happened to a request on the way, its token stream is the one a single engine produces, every
@@ -147,7 +168,7 @@ def test_random_migrations_keep_every_stream_intact(two, seed):
     shapes = [(rng.randint(10, 70), rng.randint(15, 40)) for _ in range(6)]
     try:
         # the reference streams, from one engine, before anything migrates
-        ref = MiniEngineCore(make_cfg("kv_both", "base", backend="kvt+migration"))
+        ref = MiniEngineCore(make_cfg("kv_both", "base", backend="kvt+migration", **(kw or {})))
         try:
             for i, (n, m) in enumerate(shapes):
                 ref.add_request(make_req(f"b{i}", n, max_tokens=m, seed=seed * 50 + i, params=LOCAL))
@@ -174,7 +195,8 @@ def test_random_migrations_keep_every_stream_intact(two, seed):
             assert st.tokens == want[i], (i, st.migrations, codes)
             moved += st.migrations
         assert moved >= 1, codes                                  # the test did migrate something
-        assert wait_free(a, 63, 15) == 63 and wait_free(b, 63, 15) == 63
+        free_all = a.cfg.cache_config.num_gpu_blocks - 1
+        assert wait_free(a, free_all, 15) == free_all and wait_free(b, free_all, 15) == free_all
         for e in (a, b):
             assert not e.connector._sched._saving and not e.connector._sched._loading
             assert e.connector._sched._backend.migration_status() == {"migrate_in": {}, "migrate_out": []}
