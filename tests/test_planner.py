@@ -440,3 +440,43 @@ def test_diff_kimi_k3(K, oracle, dim_first, seed):
             p_rank = d_rank // (d_tp // p_tp)
         src, dst = worker("p", p_tp, p_rank), worker("d", d_tp, d_rank)
         check(K, oracle, 8, fn, src, dst, [task(f"r{i}") for i in range(3)])
+
+
+def test_merge_interval_moves_the_same_bytes_as_the_unmerged_list(K):
+    """Random lists of ranges (runs adjacent on both sides, on one side only, gaps, shuffled order; the reference's
+    test also feeds it overlapping prompt-cache ranges, kvtransfer/tests/send_stub_test.cpp:1212-1277, which carry
+    the same bytes twice): applying the merged list to a memory image gives what the original list gives, the
+    merged list is sorted by source offset with no two neighbours adjacent on both sides, and the statistics
+    describe it."""
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=200, deadline=None)
+    @given(st.lists(st.tuples(st.integers(1, 6), st.integers(0, 3), st.integers(0, 3), st.booleans()), min_size=0, max_size=40),
+           st.randoms(use_true_random=False))
+    def run(spec, rnd):
+        blocks, s, d = [], 0, 4096
+        for length, sgap, dgap, dup in spec:
+            s += sgap * 8
+            d += dgap * 8
+            blocks.append((s, d, length * 8))
+            if dup:
+                blocks.append((s, d, length * 8))          # the same range twice
+            s += length * 8
+            d += length * 8
+        rnd.shuffle(blocks)
+        src = bytes((i * 7 + 3) & 0xFF for i in range(s + 64))
+        want = bytearray(d + 64)
+        for so, do, n in blocks:
+            want[do:do + n] = src[so:so + n]
+        merged, mn, mx, total, cnt = K.merge_interval(blocks)
+        got = bytearray(d + 64)
+        for so, do, n in merged:
+            got[do:do + n] = src[so:so + n]
+        assert got == want
+        assert [m[0] for m in merged] == sorted(m[0] for m in merged)
+        for (s0, d0, n0), (s1, d1, _n1) in zip(merged, merged[1:]):
+            assert not (s0 + n0 == s1 and d0 + n0 == d1)
+        if merged:
+            assert (mn, mx, total, cnt) == (min(m[2] for m in merged), max(m[2] for m in merged), sum(m[2] for m in merged), len(merged))
+
+    run()
