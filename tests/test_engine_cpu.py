@@ -950,3 +950,48 @@ def test_shm_transport_leaves_no_name_behind(sink):
             assert glob.glob(f"/dev/shm/kvx_{os.getpid()}_*") == []
     finally:
         srv.stop()
+
+
+def test_worker_info_survives_a_round_trip_whatever_it_holds(ops):
+    """Random worker descriptions (several block groups, every optional field, addresses with and without colons,
+    extension entries) through to_string / from_string, and malformed strings that must be refused, not crash."""
+    from hypothesis import given, settings, strategies as st
+
+    W = ops.WorkerInfo
+    name = st.text(alphabet="abcdefghijklmnopqrstuvwxyzABCDEFGHIJKLMNOPQRSTUVWXYZ0123456789-_.", min_size=1, max_size=12)
+    addr = st.sampled_from(["", "10.0.0.7", "fe80::1", "host-3.cluster.local", "127.0.0.1"])
+    ext = st.dictionaries(st.sampled_from(["dev", "port", "shape", "host", "pid", "mx", "mcn", "heads"]),
+                          st.integers(0, 1 << 40).map(str), max_size=5)
+
+    @settings(max_examples=200, deadline=None)
+    @given(name, st.integers(0, 7), st.integers(0, 64), st.sampled_from([1, 2, 4, 8, 16]),
+           st.lists(st.tuples(st.integers(1, 1 << 24), st.integers(1, 1 << 16)), min_size=1, max_size=5),
+           st.integers(1, 1 << 20), st.integers(1, 128), st.integers(0, 255), st.integers(1, 256), st.integers(0, 256),
+           st.integers(1, 8), st.integers(0, 1 << 20), addr, ext)
+    def run(inst, dp, wid, tp, groups, nblocks, layers, protos, ntpb, idx_ntpb, pack, stride, address, extension):
+        w = W()
+        w.inst_id = f"{inst}|{dp}|{tp}"
+        w.worker_id, w.engine_tp_size, w.worker_tp_rank = wid, tp, wid % tp
+        w.block_sizes, w.token_sizes = [g[0] for g in groups], [g[1] for g in groups]
+        w.layer_num_blocks, w.num_layers, w.transfer_protocols = nblocks, layers, protos
+        w.attn_kernel_blk_ntpb, w.indexer_blk_ntpb, w.attn_pack_size, w.kda_page_stride = ntpb, idx_ntpb, pack, stride
+        w.addr = address
+        w.ext = extension
+        back = W.from_string(w.to_string())
+        for f in ("inst_id", "worker_id", "engine_tp_size", "worker_tp_rank", "block_sizes", "token_sizes", "layer_num_blocks",
+                  "num_layers", "transfer_protocols", "attn_kernel_blk_ntpb", "indexer_blk_ntpb", "attn_pack_size",
+                  "kda_page_stride", "addr", "ext"):
+            assert getattr(back, f) == getattr(w, f), (f, w.to_string())
+        assert back.to_string() == w.to_string()
+
+    run()
+
+    @settings(max_examples=200, deadline=None)
+    @given(st.text(alphabet="a0,|:;=x.-", max_size=60))
+    def noise(s):
+        try:
+            W.from_string(s)
+        except Exception:
+            pass
+
+    noise()
