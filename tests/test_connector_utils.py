@@ -315,3 +315,30 @@ def test_a_workers_failure_travels_in_its_completion_report():
     assert back.reqids[0].ex == "FileNotFoundError: block 7 is gone" and back.reqids[0].n == 0
     with pytest.raises(NotImplementedError):
         enc.encode(IoDoneReqs(worker_tprank=0, reqids=[IoRet(reqid="c", ex=object())]))
+
+
+def test_what_the_native_stub_encodes_is_what_the_scheduler_parses():
+    """Random finished-request lists through the C++ send-done encoder and the scheduler's parser: ranks, request
+    ids (any UTF-8), token counts and outcomes arrive as sent, under both head kinds."""
+    from hypothesis import given, settings, strategies as st
+
+    import llumnix_kv_b200
+
+    ops = llumnix_kv_b200.load_ops()
+    reqs = st.lists(st.tuples(st.text(min_size=1, max_size=24).filter(lambda s: "\\x00" not in s), st.integers(0, (1 << 31) - 1),
+                              st.booleans()), min_size=1, max_size=12)
+
+    @settings(max_examples=150, deadline=None)
+    @given(st.integers(0, 0xFFFE), reqs, st.sampled_from([1, 2]))
+    def run(rank, rs, head_kind):
+        buf, _resp = ops.encode_send_done(rank, rs, head_kind)
+        body = bytes(buf)
+        if head_kind == 2:
+            half = len(body) // 2
+            assert body[4:half] == body[half + 4:]          # the same body again under the save-done head
+            body = body[:half]
+        assert struct.unpack_from("=I", body, 0)[0] == 0x20181219
+        got = _parse(body[4:])
+        assert got == [(rank, rid, plen, None if ok else 500) for rid, plen, ok in rs]
+
+    run()
