@@ -157,6 +157,7 @@ class RpcServer:
             pass
 
     async def _main(self):
+        self._task = asyncio.current_task()
         self._server = await asyncio.start_server(self._client_main, "0.0.0.0", self._port)
         if self._port == 0:
             self._port = self._server.sockets[0].getsockname()[1]
@@ -171,6 +172,9 @@ class RpcServer:
         def hang_up():
             if self._server is not None:
                 self._server.close()
+            task = getattr(self, "_task", None)
+            if task is not None and not task.done():
+                task.cancel()          # serve_forever would otherwise stay pending until the interpreter exits
             for w in list(self._clients):
                 try:
                     w.close()
