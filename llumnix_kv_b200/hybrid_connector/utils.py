@@ -117,6 +117,7 @@ class RpcServer:
         self._started = threading.Event()
         self._server: Optional[asyncio.AbstractServer] = None
         self._clients: set = set()           # writers of the accepted connections (loop thread only)
+        self._client_tasks: set = set()      # and the tasks that serve them
 
     def register_method(self, head: int, cb: _RpcMethod) -> None:
         assert head not in self._methods, f"rpc head {head:#x} registered twice"
@@ -132,6 +133,14 @@ class RpcServer:
 
     async def _client_main(self, reader, writer):
         self._clients.add(writer)
+        me = asyncio.current_task()
+        self._client_tasks.add(me)
+        try:
+            await self._serve_client(reader, writer)
+        finally:
+            self._client_tasks.discard(me)
+
+    async def _serve_client(self, reader, writer):
         try:
             while True:
                 (head,) = struct.unpack("=I", await reader.readexactly(4))
@@ -181,6 +190,8 @@ class RpcServer:
                 except Exception:
                     pass
             self._clients.clear()
+            for t in list(self._client_tasks):
+                t.cancel()         # a handler may be waiting for something that will never come now
 
         loop.call_soon_threadsafe(hang_up)
 
